@@ -1,0 +1,179 @@
+"""Decoder configuration, read from / written to Hugging Face ``config.json``.
+
+Covers the Llama / Qwen2 / Mistral / Granite-style family the reference trains through
+``AutoModelForCausalLM`` (setup_model_for_training.py:86-130): pre-norm decoder blocks with
+RMSNorm, rotary GQA attention (optional q/k/v bias), SwiGLU MLP, tied or untied LM head.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Optional
+
+
+@dataclass
+class ModelConfig:
+    vocab_size: int
+    hidden_size: int
+    intermediate_size: int
+    num_hidden_layers: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    head_dim: Optional[int] = None
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[dict] = None
+    attention_bias: bool = False
+    tie_word_embeddings: bool = False
+    max_position_embeddings: int = 131072
+    model_type: str = "llama"
+    architectures: list = field(default_factory=lambda: ["LlamaForCausalLM"])
+    pad_token_id: Optional[int] = None
+    bos_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = None
+    extra: dict = field(default_factory=dict)  # unknown keys of config.json, written back verbatim
+
+    def __post_init__(self):
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if self.num_attention_heads % self.num_key_value_heads:
+            raise ValueError("num_attention_heads must be a multiple of num_key_value_heads")
+
+    # sizes -------------------------------------------------------------------------
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def qkv_size(self) -> int:
+        return self.q_size + 2 * self.kv_size
+
+    def block_param_count(self) -> int:
+        h, f = self.hidden_size, self.intermediate_size
+        n = 2 * h + self.qkv_size * h + self.q_size * h + 3 * h * f
+        return n + (self.qkv_size if self.attention_bias else 0)
+
+    def param_count(self) -> int:
+        emb = self.vocab_size * self.hidden_size
+        return self.num_hidden_layers * self.block_param_count() + self.hidden_size + emb * (1 if self.tie_word_embeddings else 2)
+
+    def flops_per_token(self, avg_context: float = 0.0, recompute: bool = True) -> float:
+        """Training FLOPs per token: 6 x matmul params (+2 x with full recompute) + attention."""
+        h, f = self.hidden_size, self.intermediate_size
+        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + 3 * h * f)
+        head = self.vocab_size * h
+        k = 8 if recompute else 6
+        attn = self.num_hidden_layers * 2 * 2 * self.q_size * avg_context  # QK^T and PV, forward
+        return k * mm + 6 * head + (4 if recompute else 3) * attn
+
+    # rotary ------------------------------------------------------------------------
+    def rope_inv_freq(self):
+        """fp32 inverse frequencies [head_dim/2], with ``linear`` and ``llama3`` scaling."""
+        import torch
+        d = self.head_dim
+        inv = 1.0 / (self.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float64) / d))
+        rs = self.rope_scaling or {}
+        kind = rs.get("rope_type", rs.get("type", "default"))
+        if kind in (None, "default"):
+            pass
+        elif kind == "linear":
+            inv = inv / float(rs["factor"])
+        elif kind == "llama3":
+            factor = float(rs["factor"])
+            lo, hi = float(rs.get("low_freq_factor", 1.0)), float(rs.get("high_freq_factor", 4.0))
+            old = float(rs.get("original_max_position_embeddings", 8192))
+            wavelen = 2 * math.pi / inv
+            smooth = (old / wavelen - lo) / (hi - lo)
+            mid = (1 - smooth) * inv / factor + smooth * inv
+            inv = torch.where(wavelen > old / lo, inv / factor, torch.where(wavelen < old / hi, inv, mid))
+        else:
+            raise ValueError(f"unsupported rope scaling {kind!r}")
+        return inv.to(torch.float32)
+
+    # HF I/O -------------------------------------------------------------------------
+    _KNOWN = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+              "num_key_value_heads", "head_dim", "rms_norm_eps", "rope_theta", "rope_scaling", "attention_bias",
+              "tie_word_embeddings", "max_position_embeddings", "model_type", "architectures",
+              "pad_token_id", "bos_token_id", "eos_token_id")
+
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "ModelConfig":
+        d = dict(d)
+        kw = {k: d.pop(k) for k in list(d) if k in cls._KNOWN}
+        kw.setdefault("num_key_value_heads", kw.get("num_attention_heads"))
+        rp = d.get("rope_parameters")  # transformers >= 5 nests rope settings
+        if isinstance(rp, dict):
+            kw.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
+            if rp.get("rope_type", "default") != "default":
+                kw.setdefault("rope_scaling", rp)
+        if kw.get("model_type") == "qwen2":
+            kw.setdefault("attention_bias", True)  # Qwen2 always has q/k/v biases
+        for k in ("bos_token_id", "eos_token_id", "pad_token_id"):
+            if isinstance(kw.get(k), list):
+                d[k + "_list"] = kw[k]
+                kw[k] = kw[k][0]
+        return cls(**kw, extra=d)
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            return cls.from_hf_dict(json.load(f))
+
+    def to_hf_dict(self) -> dict:
+        d = asdict(self)
+        extra = d.pop("extra")
+        out = dict(extra)
+        for k in ("bos_token_id", "eos_token_id", "pad_token_id"):
+            lst = out.pop(k + "_list", None)
+            if lst is not None:
+                d[k] = lst
+        out.update(d)
+        out.setdefault("hidden_act", "silu")
+        out.setdefault("torch_dtype", "bfloat16")
+        out["use_cache"] = False
+        if self.model_type == "qwen2":
+            out.pop("attention_bias", None)
+        return out
+
+    def to_json_file(self, path: str) -> None:
+        with open(path, "w") as f:
+            json.dump(self.to_hf_dict(), f, indent=2, sort_keys=True)
+            f.write("\n")
+
+
+def _llama(**kw):
+    return ModelConfig(model_type="llama", architectures=["LlamaForCausalLM"], **kw)
+
+
+def _qwen2(**kw):
+    return ModelConfig(model_type="qwen2", architectures=["Qwen2ForCausalLM"], attention_bias=True, **kw)
+
+
+PRESETS = {
+    # the five benchmark architectures (random-init; sizes only)
+    "tiny-qwen2": lambda: _qwen2(vocab_size=32000, hidden_size=256, intermediate_size=688, num_hidden_layers=2,
+                                 num_attention_heads=4, num_key_value_heads=2, rope_theta=1e6,
+                                 tie_word_embeddings=True, rms_norm_eps=1e-6),
+    "qwen2.5-1.5b": lambda: _qwen2(vocab_size=151936, hidden_size=1536, intermediate_size=8960, num_hidden_layers=28,
+                                   num_attention_heads=12, num_key_value_heads=2, rope_theta=1e6,
+                                   tie_word_embeddings=True, rms_norm_eps=1e-6),
+    "llama-3.1-8b": lambda: _llama(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                                   num_attention_heads=32, num_key_value_heads=8, rope_theta=5e5, rms_norm_eps=1e-5),
+    "qwen2.5-7b": lambda: _qwen2(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+                                 num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6, rms_norm_eps=1e-6),
+    "llama-3.1-70b": lambda: _llama(vocab_size=128256, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
+                                    num_attention_heads=64, num_key_value_heads=8, rope_theta=5e5, rms_norm_eps=1e-5),
+    # a small Llama used by GPU smoke tests (head_dim 128, GQA 4:1)
+    "smoke-llama": lambda: _llama(vocab_size=4096, hidden_size=512, intermediate_size=1536, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=1, rope_theta=5e5, rms_norm_eps=1e-5),
+}
+
+
+def get_preset(name: str) -> ModelConfig:
+    return PRESETS[name]()

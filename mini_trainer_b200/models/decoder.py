@@ -1,0 +1,145 @@
+"""Decoder math with hand-written forward AND backward passes.
+
+There is no autograd graph on the training path: each decoder block is a pair of functions over
+explicit tensors, which is what lets the sharding engine decide exactly when parameters are
+gathered, what is kept between forward and backward, and when each gradient buffer is complete
+and can be reduced. The same functions run on the PyTorch reference ops (CPU, tests) and on the
+sm_100a kernels; ``ops`` is the backend object.
+
+Architecture (HF Llama/Qwen2, modeling_llama.py:303-332): ``x + Attn(RMSNorm(x))`` followed by
+``h + MLP(RMSNorm(h))`` with rotary GQA attention and a SwiGLU MLP. Activation checkpointing is
+per block as in the reference (setup_model_for_training.py:28-29): forward keeps only the block
+input; backward first re-runs the block forward (``block_forward(..., keep=True)``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .config import ModelConfig
+
+
+@dataclass
+class PackedBatch:
+    """One padding-free minibatch on the compute device."""
+    input_ids: torch.Tensor      # [T] int64
+    targets: torch.Tensor        # [T] int64, labels shifted left by one, -100 = no loss
+    position_ids: torch.Tensor   # [T] int64/int32, restarts at 0 per sample
+    cu_seqlens: torch.Tensor     # [n+1] int32 (device)
+    cu_seqlens_host: list        # same values as Python ints
+    max_seqlen: int
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.input_ids.shape[0])
+
+
+def shift_labels(labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """Target of position t is label t+1 over the whole packed row (HF causal-LM convention)."""
+    out = torch.full_like(labels, ignore_index)
+    out[..., :-1] = labels[..., 1:]
+    return out
+
+
+def make_packed_batch(mb: dict, device, non_blocking: bool = True) -> PackedBatch:
+    """Moves a collated minibatch (see ``data.sampler.mb_collate_fn``) to ``device``."""
+    ids = mb["input_ids"].reshape(-1)
+    targets = shift_labels(mb["labels"].reshape(-1))
+    pos = mb["position_ids"].reshape(-1)
+    if "cu_seqlens" in mb:
+        cu = mb["cu_seqlens"].to(torch.int32)
+    else:  # recover sample boundaries from restarting position ids (host side, once)
+        starts = (pos == 0).nonzero().flatten().to(torch.int32)
+        cu = torch.cat([starts, torch.tensor([pos.numel()], dtype=torch.int32)])
+    cu_host = cu.tolist()
+    max_seqlen = int(mb.get("max_seqlen", max(b - a for a, b in zip(cu_host[:-1], cu_host[1:]))))
+    mv = lambda t: t.to(device, non_blocking=non_blocking)
+    return PackedBatch(mv(ids), mv(targets), mv(pos.to(torch.int32)), mv(cu), cu_host, max_seqlen)
+
+
+@dataclass
+class BlockActs:
+    """Everything the block backward reads, produced by ``block_forward(keep=True)``."""
+    x: torch.Tensor
+    n1: torch.Tensor
+    rstd1: torch.Tensor
+    qkv: torch.Tensor
+    attn: torch.Tensor
+    lse: torch.Tensor
+    h1: torch.Tensor
+    n2: torch.Tensor
+    rstd2: torch.Tensor
+    gu: torch.Tensor
+    act: torch.Tensor
+
+
+def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: PackedBatch, inv_freq, keep: bool = False):
+    """Returns the block output, plus ``BlockActs`` when ``keep`` (used by recompute)."""
+    n1, rstd1 = ops.rmsnorm(x, p["ln1"], cfg.rms_norm_eps)
+    qkv = ops.linear(n1, p["wqkv"], p.get("bqkv"))
+    ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+    attn, lse = ops.attention(qkv, batch.cu_seqlens, batch.cu_seqlens_host, batch.max_seqlen,
+                              cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+    h1 = ops.linear(attn, p["wo"], None, x)
+    n2, rstd2 = ops.rmsnorm(h1, p["ln2"], cfg.rms_norm_eps)
+    gu = ops.linear(n2, p["wgu"])
+    act = ops.swiglu(gu)
+    out = ops.linear(act, p["wd"], None, h1)
+    if keep:
+        return out, BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, gu, act)
+    return out, None
+
+
+def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dout: torch.Tensor,
+                   batch: PackedBatch, inv_freq) -> torch.Tensor:
+    """Writes every parameter gradient of the block into ``g`` (views of the block's flat
+    gradient buffer, same names as ``p``) and returns the gradient of the block input."""
+    a = acts
+    # MLP
+    dact = ops.linear_dgrad(dout, p["wd"])
+    ops.linear_wgrad(dout, a.act, g["wd"])
+    dgu = ops.swiglu_bwd(dact, a.gu)
+    del dact
+    dn2 = ops.linear_dgrad(dgu, p["wgu"])
+    ops.linear_wgrad(dgu, a.n2, g["wgu"])
+    del dgu
+    dh1 = ops.rmsnorm_bwd(dn2, a.h1, a.rstd2, p["ln2"], g["ln2"], add_to=dout)
+    del dn2
+    # attention
+    dattn = ops.linear_dgrad(dh1, p["wo"])
+    ops.linear_wgrad(dh1, a.attn, g["wo"])
+    dqkv = ops.attention_bwd(dattn, a.qkv, a.attn, a.lse, batch.cu_seqlens, batch.cu_seqlens_host,
+                             batch.max_seqlen, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+    del dattn
+    ops.rope_(dqkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+              inverse=True)
+    dn1 = ops.linear_dgrad(dqkv, p["wqkv"])
+    ops.linear_wgrad(dqkv, a.n1, g["wqkv"], g.get("bqkv"))
+    del dqkv
+    dx = ops.rmsnorm_bwd(dn1, a.x, a.rstd1, p["ln1"], g["ln1"], add_to=dh1)
+    return dx
+
+
+def head_forward_backward(ops, cfg: ModelConfig, head_p: dict, head_g: dict, lm_w: torch.Tensor, lm_g: torch.Tensor,
+                          accumulate_lm_grad: bool, x: torch.Tensor, batch: PackedBatch, grad_scale: float):
+    """Final norm + fused linear/CE. Returns ``(per_token_loss [T] fp32, dx)``.
+
+    The CE op produces its gradients in the same pass, scaled by ``grad_scale`` (the reciprocal
+    of the global batch's loss-token count), so backward starts here without a separate call.
+    """
+    n, rstd = ops.rmsnorm(x, head_p["norm"], cfg.rms_norm_eps)
+    loss, dn = ops.linear_ce(n, lm_w, batch.targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad)
+    dx = ops.rmsnorm_bwd(dn, x, rstd, head_p["norm"], head_g["norm"])
+    return loss, dx
+
+
+@torch.no_grad()
+def forward_logits(ops, cfg: ModelConfig, embed_w, blocks: list, norm_w, lm_w, batch: PackedBatch) -> torch.Tensor:
+    """Plain inference forward returning ``[T, V]`` logits (tests, checkpoint round-trips)."""
+    inv_freq = cfg.rope_inv_freq().to(embed_w.device)
+    x = ops.embedding(embed_w, batch.input_ids)
+    for p in blocks:
+        x, _ = block_forward(ops, cfg, p, x, batch, inv_freq)
+    n, _ = ops.rmsnorm(x, norm_w, cfg.rms_norm_eps)
+    return n.float() @ lm_w.float().t()

@@ -1,0 +1,118 @@
+"""Flat parameter layouts and the mapping to Hugging Face tensor names.
+
+The sharding engine keeps each parameter *group* (one decoder block, the embedding, the head)
+in ONE flat buffer; a rank owns one contiguous ``1/world`` slice of it. This replaces FSDP2's
+per-parameter dim-0 sharding and its copy-in / copy-out glue
+(torch/distributed/fsdp/_fully_shard/_fsdp_collectives.py:175-233): the all-gather target IS the
+buffer the GEMMs read, with every tensor starting on a 256-byte boundary so that TMA descriptors
+can point straight at it.
+
+Within a block, q/k/v are stored as one ``[Hq*D + 2*Hkv*D, H]`` matrix and gate/up as one
+``[2F, H]`` matrix, so each pair of projections is a single GEMM. Checkpoints split and merge
+them back to the HF names (``q_proj``, ``k_proj``, ``v_proj``, ``gate_proj``, ``up_proj``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Iterator
+
+import torch
+
+from .config import ModelConfig
+
+ALIGN_ELEMS = 128  # every tensor starts at a multiple of 128 elements (256 B in bf16)
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    name: str            # engine-local name, e.g. "wqkv"
+    shape: tuple
+    offset: int          # element offset in the group's flat buffer
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+
+class GroupLayout:
+    """Ordered tensors of one group inside a flat buffer padded to ``world * ALIGN_ELEMS``."""
+
+    def __init__(self, name: str, entries: list, world: int):
+        self.name = name
+        self.specs: dict[str, ParamSpec] = {}
+        off = 0
+        for pname, shape in entries:
+            spec = ParamSpec(pname, tuple(shape), off)
+            self.specs[pname] = spec
+            off += -(-spec.numel // ALIGN_ELEMS) * ALIGN_ELEMS
+        self.numel = off
+        q = world * ALIGN_ELEMS
+        self.padded_numel = -(-off // q) * q
+        self.shard_numel = self.padded_numel // world
+
+    def views(self, flat: torch.Tensor) -> dict:
+        """Named tensor views into a full (gathered) flat buffer."""
+        return {n: flat[s.offset: s.offset + s.numel].view(s.shape) for n, s in self.specs.items()}
+
+
+def block_entries(cfg: ModelConfig) -> list:
+    h, f = cfg.hidden_size, cfg.intermediate_size
+    e = [("ln1", (h,)), ("wqkv", (cfg.qkv_size, h))]
+    if cfg.attention_bias:
+        e.append(("bqkv", (cfg.qkv_size,)))
+    e += [("wo", (h, cfg.q_size)), ("ln2", (h,)), ("wgu", (2 * f, h)), ("wd", (h, f))]
+    return e
+
+
+def embed_entries(cfg: ModelConfig) -> list:
+    return [("embed", (cfg.vocab_size, cfg.hidden_size))]
+
+
+def head_entries(cfg: ModelConfig) -> list:
+    e = [("norm", (cfg.hidden_size,))]
+    if not cfg.tie_word_embeddings:
+        e.append(("lm_head", (cfg.vocab_size, cfg.hidden_size)))
+    return e
+
+
+# ------------------------------------------------------------------------------------------
+# HF name mapping
+# ------------------------------------------------------------------------------------------
+def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[tuple]:
+    """Yields ``(hf_name, tensor_view)`` for one block, in HF ``state_dict`` order."""
+    p = f"model.layers.{layer}."
+    q, kv = cfg.q_size, cfg.kv_size
+    w = views["wqkv"]
+    yield p + "self_attn.q_proj.weight", w[:q]
+    if cfg.attention_bias:
+        yield p + "self_attn.q_proj.bias", views["bqkv"][:q]
+    yield p + "self_attn.k_proj.weight", w[q: q + kv]
+    if cfg.attention_bias:
+        yield p + "self_attn.k_proj.bias", views["bqkv"][q: q + kv]
+    yield p + "self_attn.v_proj.weight", w[q + kv:]
+    if cfg.attention_bias:
+        yield p + "self_attn.v_proj.bias", views["bqkv"][q + kv:]
+    yield p + "self_attn.o_proj.weight", views["wo"]
+    f = cfg.intermediate_size
+    yield p + "mlp.gate_proj.weight", views["wgu"][:f]
+    yield p + "mlp.up_proj.weight", views["wgu"][f:]
+    yield p + "mlp.down_proj.weight", views["wd"]
+    yield p + "input_layernorm.weight", views["ln1"]
+    yield p + "post_attention_layernorm.weight", views["ln2"]
+
+
+def hf_tensors_of_embed(cfg: ModelConfig, views: dict) -> Iterator[tuple]:
+    yield "model.embed_tokens.weight", views["embed"]
+
+
+def hf_tensors_of_head(cfg: ModelConfig, views: dict) -> Iterator[tuple]:
+    yield "model.norm.weight", views["norm"]
+    if not cfg.tie_word_embeddings:
+        yield "lm_head.weight", views["lm_head"]
+
+
+def group_names(cfg: ModelConfig) -> list:
+    return ["embed"] + [f"block{i}" for i in range(cfg.num_hidden_layers)] + ["head"]

@@ -1,0 +1,61 @@
+"""Autograd reference of the decoder, written independently of ``decoder.py``.
+
+Used only by tests: it takes HF-named tensors, runs a plain differentiable forward with stock
+PyTorch functions (``scaled_dot_product_attention`` per sample, ``F.cross_entropy`` with
+``reduction='none'`` as the reference's unfused path does, none_reduction_losses.py:27-36) and
+lets autograd produce the gradients the hand-written backward must match.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .config import ModelConfig
+
+
+def _rms(x, w, eps):
+    xf = x.float()
+    return ((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)) * w
+
+
+def _rope(x, pos, inv_freq):
+    # x: [T, heads, D]
+    ang = pos.float()[:, None] * inv_freq[None, :]
+    cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, :]
+    sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, :]
+    d = x.shape[-1]
+    rot = torch.cat([-x[..., d // 2:], x[..., : d // 2]], -1)
+    return (x.float() * cos + rot.float() * sin).to(x.dtype)
+
+
+def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, position_ids, return_logits=False):
+    """``sd``: HF-named tensors (requires_grad as needed). Inputs are 1-D packed rows."""
+    T = input_ids.shape[0]
+    inv_freq = cfg.rope_inv_freq().to(input_ids.device)
+    starts = (position_ids == 0).nonzero().flatten().tolist() + [T]
+    x = sd["model.embed_tokens.weight"][input_ids]
+    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        n = _rms(x, sd[p + "input_layernorm.weight"], cfg.rms_norm_eps)
+        q = F.linear(n, sd[p + "self_attn.q_proj.weight"], sd.get(p + "self_attn.q_proj.bias")).view(T, hq, d)
+        k = F.linear(n, sd[p + "self_attn.k_proj.weight"], sd.get(p + "self_attn.k_proj.bias")).view(T, hkv, d)
+        v = F.linear(n, sd[p + "self_attn.v_proj.weight"], sd.get(p + "self_attn.v_proj.bias")).view(T, hkv, d)
+        q, k = _rope(q, position_ids, inv_freq), _rope(k, position_ids, inv_freq)
+        outs = []
+        for a, b in zip(starts[:-1], starts[1:]):
+            o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1)[None], k[a:b].transpose(0, 1)[None],
+                                               v[a:b].transpose(0, 1)[None], is_causal=True, enable_gqa=True)
+            outs.append(o[0].transpose(0, 1).reshape(b - a, hq * d))
+        x = x + F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"])
+        n = _rms(x, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
+        act = F.silu(F.linear(n, sd[p + "mlp.gate_proj.weight"])) * F.linear(n, sd[p + "mlp.up_proj.weight"])
+        x = x + F.linear(act, sd[p + "mlp.down_proj.weight"])
+    n = _rms(x, sd["model.norm.weight"], cfg.rms_norm_eps)
+    lm = sd["model.embed_tokens.weight"] if cfg.tie_word_embeddings else sd["lm_head.weight"]
+    logits = F.linear(n, lm).float()
+    if return_logits:
+        return logits
+    targets = torch.full_like(labels, -100)
+    targets[:-1] = labels[1:]
+    return F.cross_entropy(logits, targets, ignore_index=-100, reduction="none")

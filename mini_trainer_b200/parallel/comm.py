@@ -1,0 +1,101 @@
+"""Communication backends of the sharding engine.
+
+The engine needs exactly three collectives over flat buffers:
+
+* ``all_gather(shard, full)``                   — parameters, before a group is used;
+* ``reduce_scatter_accumulate(full, acc, ...)`` — gradients of a group, summed over ranks and
+  added into this rank's fp32 accumulator shard;
+* ``all_reduce_sum(vec)``                       — a few scalars per step (grad-norm, metrics).
+
+Backends:
+
+* ``LocalComm``      world size 1: no copies at all (the shard IS the full buffer).
+* ``TorchDistComm``  ``torch.distributed`` collectives — NCCL on GPUs, gloo on CPU. This is the
+  baseline-grade path (what FSDP2 does underneath, torch/distributed/fsdp/_fully_shard/
+  _fsdp_collectives.py:89-131) and the one multi-node launches use.
+* ``SymmetricComm``  (``parallel/symmetric.py``) single-node NVSwitch path: buffers live in
+  symmetric memory and hand-written kernels move the data with peer loads, no NCCL call.
+
+Gradients are SUM-reduced; the loss scale already contains ``1 / global_loss_tokens``, so no
+``world_size`` factor appears anywhere (the reference multiplies by ``world_size`` only to
+cancel FSDP's AVG reduction, train.py:98-102).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+class LocalComm:
+    name = "local"
+    world = 1
+    rank = 0
+
+    def all_gather(self, shard, full):
+        if full.data_ptr() != shard.data_ptr():
+            full.copy_(shard)
+
+    def reduce_scatter_accumulate(self, full, acc, accumulate: bool, scratch=None):
+        if accumulate:
+            acc.add_(full)
+        else:
+            acc.copy_(full)
+
+    def all_reduce_sum(self, vec):
+        return vec
+
+    def barrier(self):
+        pass
+
+
+class TorchDistComm:
+    name = "torchdist"
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def all_gather(self, shard, full):
+        dist.all_gather_into_tensor(full, shard, group=self.group)
+
+    def reduce_scatter_accumulate(self, full, acc, accumulate: bool, scratch=None):
+        s = acc.numel()
+        if scratch is None or scratch.numel() < s or scratch.dtype != full.dtype:
+            scratch = torch.empty(s, dtype=full.dtype, device=full.device)
+        out = scratch[:s]
+        if full.device.type == "cpu":
+            # gloo has no reduce_scatter: all-reduce a copy and keep the local slice
+            tmp = full.clone()
+            dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=self.group)
+            out = tmp[self.rank * s:(self.rank + 1) * s]
+        else:
+            dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=self.group)
+        if accumulate:
+            acc.add_(out)
+        else:
+            acc.copy_(out)
+
+    def all_reduce_sum(self, vec):
+        dist.all_reduce(vec, op=dist.ReduceOp.SUM, group=self.group)
+        return vec
+
+    def barrier(self):
+        dist.barrier(group=self.group)
+
+
+def make_comm(kind: str = "auto", device=None):
+    """``auto``: local for one rank, otherwise torch.distributed (NCCL/gloo).
+
+    ``symmetric`` selects the in-kernel NVLink path and falls back to an error (never silently)
+    if symmetric memory cannot be set up.
+    """
+    world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    if world == 1:
+        return LocalComm()
+    if kind in ("auto", "torchdist", "nccl", "gloo"):
+        return TorchDistComm()
+    if kind == "symmetric":
+        from .symmetric import SymmetricComm
+        return SymmetricComm(device)
+    raise ValueError(f"unknown comm backend {kind!r}")

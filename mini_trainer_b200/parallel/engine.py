@@ -1,0 +1,378 @@
+"""The sharding engine: fully sharded parameters, gradients and optimizer state.
+
+Role of the reference's ``wrap_fsdp2`` + ``AdamW`` + ``clip_grad_norm_`` + ``take_gradient_step``
+(setup_model_for_training.py:14-48,132-152; train.py:22-28), built as one explicit schedule
+instead of hooks on an autograd graph:
+
+* Parameters are grouped as ``embed | block0 .. blockL-1 | head``. Each group lives in one flat
+  buffer; a rank permanently owns one contiguous ``1/world`` slice of it: the working copy in the
+  compute dtype, an fp32 master copy, AdamW moments and an fp32 gradient accumulator.
+* Forward walks the blocks, gathering block ``i+1`` on a side stream while block ``i`` computes,
+  and keeps only each block's input (per-block activation checkpointing, as the reference).
+* Backward walks them in reverse: gather, recompute the block forward, run the hand-written
+  backward into the block's flat gradient buffer, then reduce-scatter that buffer (SUM) into the
+  fp32 accumulator shard on the side stream while the next block computes.
+* After the last microbatch: one sum of squares over the accumulator shards, one scalar
+  all-reduce, the clip coefficient ``min(1, max_norm / (norm + 1e-6))`` kept on the device, and a
+  fused AdamW pass that updates master weights and refreshes the working shard.
+
+The gradient of a step is that of ``sum(token CE over all ranks and microbatches) /
+batch_num_loss_counted_tokens`` (reference train.py:98-102 after FSDP's averaging).
+
+Precision: compute dtype bf16 on GPUs (fp32 in the CPU oracle runs); gradients are produced in
+the compute dtype per microbatch and accumulated in fp32; master weights fp32; moments fp32 or
+bf16 (``state_dtype``). The reference keeps everything, moments included, in bf16.
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+from dataclasses import dataclass, field
+from typing import Iterator, Optional
+
+import torch
+
+from ..models import decoder as D
+from ..models import layout as L
+from ..models.config import ModelConfig
+from .comm import LocalComm
+
+
+@dataclass
+class OptimConfig:
+    lr: float = 5e-6
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    max_grad_norm: float = 1.0
+
+
+class ShardedGroup:
+    """One parameter group: layout + this rank's shard of params, master, moments, grads."""
+
+    def __init__(self, layout: L.GroupLayout, device, param_dtype, state_dtype):
+        self.layout = layout
+        s = layout.shard_numel
+        self.shard = torch.zeros(s, dtype=param_dtype, device=device)
+        self.master = torch.zeros(s, dtype=torch.float32, device=device)
+        self.m = torch.zeros(s, dtype=state_dtype, device=device)
+        self.v = torch.zeros(s, dtype=state_dtype, device=device)
+        self.gacc = torch.zeros(s, dtype=torch.float32, device=device)
+        self.has_grad = False
+
+    def state_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.shard, self.master, self.m, self.v, self.gacc))
+
+
+class _Side:
+    """A side CUDA stream with event hand-offs; degenerates to inline execution on CPU."""
+
+    def __init__(self, device):
+        self.cuda = device.type == "cuda"
+        self.stream = torch.cuda.Stream(device=device, priority=-1) if self.cuda else None
+
+    @contextlib.contextmanager
+    def run(self, wait_current: bool = True):
+        if not self.cuda:
+            yield
+            return
+        if wait_current:
+            self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            yield
+
+    def record(self):
+        if not self.cuda:
+            return None
+        ev = torch.cuda.Event()
+        ev.record(self.stream)
+        return ev
+
+    @staticmethod
+    def wait(ev):
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+
+class ShardedEngine:
+    def __init__(self, cfg: ModelConfig, device, ops, comm=None, param_dtype=None, state_dtype=None,
+                 optim: Optional[OptimConfig] = None):
+        self.cfg, self.device, self.ops = cfg, torch.device(device), ops
+        self.comm = comm if comm is not None else LocalComm()
+        self.world, self.rank = self.comm.world, self.comm.rank
+        self.param_dtype = param_dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
+        self.state_dtype = state_dtype or torch.float32
+        self.optim = optim or OptimConfig()
+        self.step_count = 0
+        self.inv_freq = cfg.rope_inv_freq().to(self.device)
+
+        mk = lambda name, entries: ShardedGroup(L.GroupLayout(name, entries, self.world), self.device,
+                                                self.param_dtype, self.state_dtype)
+        self.embed = mk("embed", L.embed_entries(cfg))
+        self.blocks = [mk(f"block{i}", L.block_entries(cfg)) for i in range(cfg.num_hidden_layers)]
+        self.head = mk("head", L.head_entries(cfg))
+        self.groups = [self.embed] + self.blocks + [self.head]
+
+        self.side = _Side(self.device)
+        blk = self.blocks[0].layout.padded_numel
+        nbuf = 2
+        # rotating full-size buffers for gathered block parameters and block gradients
+        self._pbufs = [] if self.world == 1 else [torch.zeros(blk, dtype=self.param_dtype, device=self.device) for _ in range(nbuf)]
+        self._gbufs = [torch.zeros(blk, dtype=self.param_dtype, device=self.device) for _ in range(nbuf)]
+        self._pbuf_free = [None] * nbuf   # event after which the buffer may be overwritten
+        self._gbuf_free = [None] * nbuf
+        self._rs_scratch = None
+        if self.world > 1:
+            smax = max(g.layout.shard_numel for g in self.groups)
+            self._rs_scratch = torch.empty(smax, dtype=self.param_dtype, device=self.device)
+        self.launch_count = 0
+
+    # ------------------------------------------------------------------------------------
+    # initialisation / state exchange
+    # ------------------------------------------------------------------------------------
+    def _set_group_from_full(self, grp: ShardedGroup, full: torch.Tensor) -> None:
+        s = grp.layout.shard_numel
+        sl = full[self.rank * s:(self.rank + 1) * s]
+        grp.master.copy_(sl.float())
+        grp.shard.copy_(grp.master.to(self.param_dtype))
+
+    def init_random(self, seed: int = 0, std: float = 0.02, on_device: bool = False) -> None:
+        """Same weights on every world size: each group is generated in full from its own seeded
+        generator and the rank keeps its slice. ``on_device`` draws with the device generator
+        (fast for multi-billion-parameter benchmarks; a different stream than the CPU one)."""
+        dev = self.device if on_device else torch.device("cpu")
+        for gi, grp in enumerate(self.groups):
+            gen = torch.Generator(device=dev).manual_seed(seed * 1000003 + gi)
+            full = torch.zeros(grp.layout.padded_numel, dtype=torch.float32, device=dev)
+            for name, spec in grp.layout.specs.items():
+                v = full[spec.offset: spec.offset + spec.numel]
+                if len(spec.shape) == 1:
+                    v.fill_(0.0 if name.startswith("b") else 1.0)
+                else:
+                    v.normal_(0.0, std, generator=gen)
+            self._set_group_from_full(grp, full.to(self.device))
+            del full
+
+    def load_hf_tensors(self, get_tensor) -> None:
+        """``get_tensor(hf_name) -> torch.Tensor`` (any dtype, CPU). Every rank reads the tensors
+        of one group at a time, so host memory holds one block, not the model."""
+        cfg = self.cfg
+        for grp, it in self._hf_iters():
+            full = torch.zeros(grp.layout.padded_numel, dtype=torch.float32)
+            views = grp.layout.views(full)
+            for name, view in it(views):
+                view.copy_(get_tensor(name).to(torch.float32).reshape(view.shape))
+            self._set_group_from_full(grp, full.to(self.device))
+        del cfg
+
+    def _hf_iters(self):
+        cfg = self.cfg
+        yield self.embed, (lambda v: L.hf_tensors_of_embed(cfg, v))
+        for i, b in enumerate(self.blocks):
+            yield b, (lambda v, i=i: L.hf_tensors_of_block(cfg, i, v))
+        yield self.head, (lambda v: L.hf_tensors_of_head(cfg, v))
+
+    @torch.no_grad()
+    def iter_hf_tensors(self, dtype=torch.bfloat16, source: str = "master") -> Iterator[tuple]:
+        """Yields ``(hf_name, cpu_tensor)`` group by group on every rank (collective call).
+
+        Only one gathered group is alive at a time, so exporting a 70B model needs one block
+        of device memory, not a full replica per rank as the reference's
+        ``get_model_state_dict(full_state_dict=True)`` does (train.py:41-42).
+        """
+        for grp, it in self._hf_iters():
+            src = grp.master if source == "master" else grp.shard
+            if self.world == 1:
+                full = src
+            else:
+                full = torch.empty(grp.layout.padded_numel, dtype=src.dtype, device=self.device)
+                self.comm.all_gather(src, full)
+            views = grp.layout.views(full)
+            for name, view in it(views):
+                yield name, view.to(dtype).cpu()
+            del full, views
+
+    # ------------------------------------------------------------------------------------
+    # gather / reduce plumbing
+    # ------------------------------------------------------------------------------------
+    def _gather_block(self, i: int):
+        """Starts gathering block ``i`` on the side stream; returns (views, ready_event, slot)."""
+        grp = self.blocks[i]
+        if self.world == 1:
+            return grp.layout.views(grp.shard), None, -1
+        slot = i % len(self._pbufs)
+        buf = self._pbufs[slot]
+        with self.side.run(wait_current=False):
+            if self.side.cuda and self._pbuf_free[slot] is not None:
+                self.side.stream.wait_event(self._pbuf_free[slot])
+            self.comm.all_gather(grp.shard, buf)
+            ev = self.side.record()
+        return grp.layout.views(buf), ev, slot
+
+    def _release_pbuf(self, slot: int):
+        if slot >= 0 and self.side.cuda:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self._pbuf_free[slot] = ev
+
+    def _gather_group(self, grp: ShardedGroup):
+        """Synchronous gather of the embed / head group into a fresh buffer."""
+        if self.world == 1:
+            return grp.layout.views(grp.shard), grp.shard
+        full = torch.empty(grp.layout.padded_numel, dtype=self.param_dtype, device=self.device)
+        self.comm.all_gather(grp.shard, full)
+        return grp.layout.views(full), full
+
+    def _reduce(self, grp: ShardedGroup, gfull: torch.Tensor, slot: int = -1):
+        """Reduce-scatter ``gfull`` into the group's fp32 accumulator on the side stream."""
+        with self.side.run(wait_current=True):
+            self.comm.reduce_scatter_accumulate(gfull, grp.gacc, grp.has_grad, self._rs_scratch)
+            ev = self.side.record()
+        grp.has_grad = True
+        if slot >= 0:
+            self._gbuf_free[slot] = ev
+        return ev
+
+    def _grad_buffer(self, i: int):
+        slot = i % len(self._gbufs)
+        _Side.wait(self._gbuf_free[slot])
+        self._gbuf_free[slot] = None
+        return self._gbufs[slot], slot
+
+    # ------------------------------------------------------------------------------------
+    # one microbatch
+    # ------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward_backward(self, batch: D.PackedBatch, grad_scale: float) -> torch.Tensor:
+        """Runs forward and backward of one packed minibatch; accumulates gradients.
+
+        Returns the per-token loss vector ``[T]`` (fp32, on device)."""
+        cfg, ops = self.cfg, self.ops
+        nL = len(self.blocks)
+        tied = cfg.tie_word_embeddings
+
+        # ---- forward ----
+        emb_views, emb_full = self._gather_group(self.embed)
+        x = ops.embedding(emb_views["embed"], batch.input_ids)
+        if not tied:
+            del emb_views, emb_full
+        saved = []
+        nxt = self._gather_block(0)
+        for i in range(nL):
+            p, ev, slot = nxt
+            _Side.wait(ev)
+            nxt = self._gather_block(i + 1) if i + 1 < nL else None
+            saved.append(x)
+            x, _ = D.block_forward(ops, cfg, p, x, batch, self.inv_freq)
+            if i + 1 < nL or self.world == 1:
+                self._release_pbuf(slot)
+            last = (p, slot)  # the last block stays gathered for backward (reshard_after_forward=False)
+
+        # ---- head: loss and its gradients in one pass ----
+        head_views, head_full = self._gather_group(self.head)
+        hg_full = torch.zeros(self.head.layout.padded_numel, dtype=self.param_dtype, device=self.device)
+        head_g = self.head.layout.views(hg_full)
+        if tied:
+            eg_full = torch.zeros(self.embed.layout.padded_numel, dtype=self.param_dtype, device=self.device)
+            emb_g = self.embed.layout.views(eg_full)
+            loss, dx = D.head_forward_backward(ops, cfg, head_views, head_g, emb_views["embed"], emb_g["embed"], True,
+                                               x, batch, grad_scale)
+        else:
+            loss, dx = D.head_forward_backward(ops, cfg, head_views, head_g, head_views["lm_head"], head_g["lm_head"],
+                                               False, x, batch, grad_scale)
+        del x, head_views, head_full
+        self._reduce(self.head, hg_full)
+
+        # ---- backward through the blocks ----
+        cur = (last[0], None, last[1])
+        for i in range(nL - 1, -1, -1):
+            p, ev, slot = cur
+            _Side.wait(ev)
+            cur = self._gather_block(i - 1) if i > 0 else None
+            gbuf, gslot = self._grad_buffer(i)
+            g = self.blocks[i].layout.views(gbuf)
+            xin = saved.pop()
+            _, acts = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True)
+            dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq)
+            del acts, xin
+            self._release_pbuf(slot)
+            self._reduce(self.blocks[i], gbuf, gslot)
+
+        # ---- embedding ----
+        if not tied:
+            eg_full = torch.zeros(self.embed.layout.padded_numel, dtype=self.param_dtype, device=self.device)
+            emb_g = self.embed.layout.views(eg_full)
+        ops.embedding_bwd(emb_g["embed"], batch.input_ids, dx)
+        ev = self._reduce(self.embed, eg_full)
+        # transient buffers handed to the side stream must outlive its work
+        if self.side.cuda:
+            for t in (hg_full, eg_full):
+                t.record_stream(self.side.stream)
+        return loss
+
+    # ------------------------------------------------------------------------------------
+    # optimizer
+    # ------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def optimizer_step(self, lr: float) -> torch.Tensor:
+        """Global-norm clip + AdamW on the shards. Returns the pre-clip gradient norm (0-dim)."""
+        if self.side.cuda:
+            torch.cuda.current_stream().wait_stream(self.side.stream)
+        o = self.optim
+        live = [g for g in self.groups if g.has_grad]
+        sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for g in live:
+            sq += self.ops.sumsq(g.gacc)
+        self.comm.all_reduce_sum(sq)
+        norm = sq.sqrt().squeeze(0)
+        if o.max_grad_norm and o.max_grad_norm > 0:
+            coef = torch.clamp(o.max_grad_norm / (norm + 1e-6), max=1.0)
+        else:
+            coef = torch.ones((), dtype=torch.float32, device=self.device)
+        self.step_count += 1
+        for g in live:
+            self.ops.adamw_step(g.master, g.m, g.v, g.gacc, g.shard, lr, o.beta1, o.beta2, o.eps, o.weight_decay,
+                                self.step_count, coef)
+            g.has_grad = False
+        if self.side.cuda:
+            self.side.stream.wait_stream(torch.cuda.current_stream())
+        return norm
+
+    def zero_grad(self) -> None:
+        for g in self.groups:
+            g.has_grad = False
+
+    # ------------------------------------------------------------------------------------
+    # convenience: a full training step over this rank's minibatches
+    # ------------------------------------------------------------------------------------
+    def train_step(self, minibatches: list, lr: float) -> dict:
+        """``minibatches``: collated dicts (``data.sampler.mb_collate_fn``). One optimizer step.
+
+        Device work is queued without host synchronisation; the returned tensors
+        (``loss_sum``, ``grad_norm``) are read by the caller when it logs.
+        """
+        loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
+        ntok = 0
+        for mb in minibatches:
+            batch = D.make_packed_batch(mb, self.device)
+            denom = float(mb["batch_num_loss_counted_tokens"]) or 1.0
+            loss = self.forward_backward(batch, 1.0 / denom)
+            loss_sum += loss.sum()
+            ntok += batch.num_tokens
+        gnorm = self.optimizer_step(lr)
+        return {"loss_sum": loss_sum, "grad_norm": gnorm, "num_tokens": ntok}
+
+    def state_bytes(self) -> int:
+        return sum(g.state_bytes() for g in self.groups)
+
+
+def plan_state_dtype(cfg: ModelConfig, world: int, hbm_bytes: float, tokens: int) -> torch.dtype:
+    """fp32 moments when they fit comfortably next to activations, else bf16.
+
+    Per-parameter bytes on a rank: 2 (working) + 4 (master) + 4 (grad accumulator) + 2x moment.
+    """
+    p = cfg.param_count() / world
+    act = tokens * cfg.hidden_size * 2 * (cfg.num_hidden_layers + 24) + tokens * cfg.intermediate_size * 2 * 8
+    fixed = p * 10 + act + 3 * cfg.block_param_count() * 2 * (world > 1) + 6e9
+    return torch.float32 if fixed + p * 8 < 0.85 * hbm_bytes else torch.bfloat16
