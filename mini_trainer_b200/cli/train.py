@@ -1,0 +1,106 @@
+"""``train`` command line: the reference's twelve options with the same names and defaults
+(train.py:160-178), plus opt-in extras that default to the reference's behaviour."""
+from __future__ import annotations
+
+import json
+import os
+from enum import Enum
+from pathlib import Path
+from typing import Optional
+
+from typer import Option, Typer
+
+app = Typer(pretty_exceptions_show_locals=False, pretty_exceptions_short=True)
+
+
+class LogLevelEnum(str, Enum):
+    DEBUG = "DEBUG"
+    INFO = "INFO"
+    WARNING = "WARNING"
+    ERROR = "ERROR"
+    CRITICAL = "CRITICAL"
+
+
+@app.command()
+def main(
+    model_name_or_path: str = Option("Qwen/Qwen2.5-1.5B-Instruct", help="HF checkpoint directory, or random:<preset>"),
+    data_path: str = Option("test.jsonl", help="Path to the training data JSONL file, or synthetic:<preset>[:num_samples]"),
+    batch_size: int = Option(1024, help="Initial batch size before dynamic splitting"),
+    max_tokens_per_gpu: int = Option(10000, help="Maximum tokens per GPU per minibatch"),
+    learning_rate: float = Option(5e-6, help="Peak learning rate"),
+    num_warmup_steps: int = Option(10, help="Number of warmup steps for the LR scheduler"),
+    lr_scheduler: str = Option("constant_with_warmup", help="Learning rate scheduler type"),
+    seed: int = Option(42, help="Random seed for reproducibility"),
+    use_liger_kernels: bool = Option(False, help="Accepted for parity; the fused linear+CE kernel is always used on GPUs"),
+    output_dir: str = Option(..., help="Directory to save checkpoints and logs (required)"),
+    logging_level: LogLevelEnum = Option(LogLevelEnum.INFO, help="Logging level", case_sensitive=False),
+    min_samples_per_checkpoint: int = Option(..., help="Minimum number of samples processed before saving a checkpoint (required)"),
+    # ---- extras (not in the reference) ----
+    max_steps: Optional[int] = Option(None, help="Stop after this many optimizer steps (the reference runs forever)"),
+    comm_backend: str = Option("auto", help="auto | torchdist | symmetric"),
+    num_workers: int = Option(0, help="DataLoader worker processes (0 = packing thread)"),
+    max_grad_norm: float = Option(1.0, help="Global gradient-norm clip"),
+    weight_decay: float = Option(0.0, help="AdamW weight decay"),
+    optimizer_state_dtype: str = Option("auto", help="auto | fp32 | bf16 (AdamW moments)"),
+    osft: bool = Option(False, help="Orthogonal-subspace fine-tuning of the attention/MLP projections"),
+    osft_rank_ratio: float = Option(0.5, help="Fraction of each projection's singular directions that is frozen"),
+    resume_from: Optional[str] = Option(None, help="Directory of a training-state checkpoint to resume from"),
+):
+    import torch
+
+    from ..data.sampler import get_data_loader
+    from ..data.synthetic import CONFIG_DATA, synthetic_dataset
+    from ..parallel.engine import OptimConfig
+    from ..trainer import setup_model, setup_training_components, train
+    from ..utils.dist import init_distributed_environment
+    from ..utils.log import setup_logger
+
+    device = init_distributed_environment()
+    output_path = Path(output_dir)
+    output_path.mkdir(parents=True, exist_ok=True)
+    rank = int(os.environ.get("RANK", 0))
+    if rank == 0:
+        params = {
+            "model_name_or_path": model_name_or_path, "data_path": data_path, "batch_size": batch_size,
+            "max_tokens_per_gpu": max_tokens_per_gpu, "learning_rate": learning_rate,
+            "num_warmup_steps": num_warmup_steps, "lr_scheduler": lr_scheduler, "seed": seed,
+            "use_liger_kernels": use_liger_kernels, "output_dir": output_dir, "logging_level": logging_level.value,
+            "min_samples_per_checkpoint": min_samples_per_checkpoint, "RANK": rank,
+            "WORLD_SIZE": int(os.environ.get("WORLD_SIZE", 1)),
+        }
+        params_path = output_path / "training_params.json"
+        with open(params_path, "w") as f:
+            json.dump(params, f, indent=4)
+        print(f"Training with parameters: {json.dumps(params, separators=(',', ':'), indent=4)}")
+        print(f"Training parameters saved to {params_path}")
+    setup_logger(level=logging_level.value)
+    sd = {"auto": None, "fp32": torch.float32, "bf16": torch.bfloat16}[optimizer_state_dtype]
+    model = setup_model(model_name_or_path=model_name_or_path, use_liger_kernels=use_liger_kernels, device=device,
+                        comm_backend=comm_backend, state_dtype=sd, seed=seed, max_tokens_per_gpu=max_tokens_per_gpu,
+                        optim=OptimConfig(max_grad_norm=max_grad_norm, weight_decay=weight_decay))
+    if osft:
+        from ..parallel.osft import enable_osft
+        enable_osft(model, rank_ratio=osft_rank_ratio)
+    model, optimizer, sched = setup_training_components(model, learning_rate=learning_rate,
+                                                        num_warmup_steps=num_warmup_steps, lr_scheduler=lr_scheduler)
+    if resume_from:
+        from ..ckpt.train_state import load_train_state
+        meta = load_train_state(model, resume_from)
+        if "scheduler" in meta:
+            sched.load_state_dict(meta["scheduler"])
+    if data_path.startswith("synthetic:"):
+        parts = data_path.split(":")
+        spec, vocab, _, _ = CONFIG_DATA[parts[1]]
+        n = int(parts[2]) if len(parts) > 2 else 4096
+        dataset = synthetic_dataset(n, spec, min(vocab, model.cfg.vocab_size), seed=seed)
+        loader = get_data_loader(dataset=dataset, batch_size=batch_size, max_tokens_per_gpu=max_tokens_per_gpu,
+                                 seed=seed, pin_memory=device.type == "cuda")
+    else:
+        loader = get_data_loader(data_path=data_path, batch_size=batch_size, max_tokens_per_gpu=max_tokens_per_gpu,
+                                 seed=seed, num_workers=num_workers, pin_memory=device.type == "cuda")
+    train(model, optimizer, sched, loader, output_dir, min_samples_per_checkpoint, model_name_or_path,
+          max_steps=max_steps)
+
+
+if __name__ == "__main__":
+    app()
