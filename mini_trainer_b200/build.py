@@ -29,7 +29,7 @@ CUDA_LIB = OUT / "libmtb200_cuda.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo", "--use_fast_math",
+    "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-O3",
     "--expt-relaxed-constexpr",
 ]

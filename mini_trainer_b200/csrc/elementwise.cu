@@ -1,0 +1,531 @@
+// Bandwidth-bound kernels: RMSNorm (+residual gradient), RoPE, SwiGLU, embedding gather,
+// cross-entropy over a logits chunk, column sums (bias gradient), gradient accumulation,
+// sum of squares and the fused AdamW update. All use 128-bit accesses, fp32 math and bf16 storage.
+//
+// These replace what the reference gets from Liger's Triton kernels (rms_norm, rope, swiglu,
+// cross_entropy) and ATen foreach ops (clip, AdamW).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace mtb {
+
+constexpr int EW_THREADS = 256;
+
+struct bf16x8 {
+  uint4 u;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = u; }
+  __device__ __forceinline__ void to_float(float (&f)[8]) const {
+    float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+  }
+  __device__ __forceinline__ void from_float(const float (&f)[8]) {
+    u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]); u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
+  }
+};
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (w == 0) t = warp_sum(t);
+  if (threadIdx.x == 0) red[0] = t;
+  __syncthreads();
+  return red[0];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : -INFINITY;
+  if (w == 0) t = warp_max(t);
+  if (threadIdx.x == 0) red[0] = t;
+  __syncthreads();
+  return red[0];
+}
+
+// ------------------------------------------------------------------------------ RMSNorm fwd
+// y = bf16(x * rstd) * w ; rstd saved. One block per row; the row is read twice (second read hits L1/L2).
+__global__ void __launch_bounds__(EW_THREADS) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                                __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
+                                                                float eps, int H) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 8; c < H; c += EW_THREADS * 8) {
+    bf16x8 v; v.load(xr + c);
+    float f[8]; v.to_float(f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / H + eps);
+  if (threadIdx.x == 0) rstd_out[row] = rstd;
+  __nv_bfloat16* yr = y + row * H;
+  for (int c = threadIdx.x * 8; c < H; c += EW_THREADS * 8) {
+    bf16x8 v, wv; v.load(xr + c); wv.load(w + c);
+    float f[8], g[8]; v.to_float(f); wv.to_float(g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] * rstd)) * g[i];
+    v.from_float(f); v.store(yr + c);
+  }
+}
+
+// ------------------------------------------------------------------------------ RMSNorm bwd
+// dx = rstd * (g - xhat * mean(g * xhat)) (+ add_to), g = dy * w, xhat = x * rstd
+// dw partial per block in fp32: dwp[block, H] += dy * bf16(xhat). Persistent blocks loop over rows.
+template <int VPT>  // 8-wide vectors per thread; H <= VPT * 8 * EW_THREADS
+__global__ void __launch_bounds__(EW_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ w,
+                                                                const __nv_bfloat16* __restrict__ add_to, __nv_bfloat16* __restrict__ dx,
+                                                                float* __restrict__ dwp, int T, int H) {
+  __shared__ float red[32];
+  float dwacc[VPT][8];
+  float wreg[VPT][8];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int c = (threadIdx.x + v * EW_THREADS) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dwacc[v][i] = 0.f; wreg[v][i] = 0.f; }
+    if (c < H) { bf16x8 wv; wv.load(w + c); wv.to_float(wreg[v]); }
+  }
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+    const float rstd = rstd_in[row];
+    float g[VPT][8], xh[VPT][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = (threadIdx.x + v * EW_THREADS) * 8;
+      if (c < H) {
+        bf16x8 a, b; a.load(dy + row * H + c); b.load(x + row * H + c);
+        float fa[8], fb[8]; a.to_float(fa); b.to_float(fb);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[v][i] = fb[i] * rstd;
+          g[v][i] = fa[i] * wreg[v][i];
+          dot += g[v][i] * xh[v][i];
+          dwacc[v][i] += fa[i] * __bfloat162float(__float2bfloat16(xh[v][i]));
+        }
+      }
+    }
+    dot = block_sum(dot, red) / H;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = (threadIdx.x + v * EW_THREADS) * 8;
+      if (c < H) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (g[v][i] - xh[v][i] * dot);
+        if (add_to != nullptr) {
+          bf16x8 r; r.load(add_to + row * H + c);
+          float fr[8]; r.to_float(fr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += fr[i];
+        }
+        bf16x8 ov; ov.from_float(o); ov.store(dx + row * H + c);
+      }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int c = (threadIdx.x + v * EW_THREADS) * 8;
+    if (c < H) {
+      float* dst = dwp + static_cast<long long>(blockIdx.x) * H + c;
+      *reinterpret_cast<float4*>(dst) = make_float4(dwacc[v][0], dwacc[v][1], dwacc[v][2], dwacc[v][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[v][4], dwacc[v][5], dwacc[v][6], dwacc[v][7]);
+    }
+  }
+}
+
+// out[c] = bf16(sum_r part[r, c]); one thread per column, coalesced across threads.
+__global__ void reduce_rows_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int R, int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f;
+  for (int r = 0; r < R; ++r) s += part[static_cast<long long>(r) * C + c];
+  out[c] = __float2bfloat16(s);
+}
+
+// ------------------------------------------------------------------------------ RoPE
+// In place on the first n_heads (q then k) heads of each row of qkv[T, ld]. Rotate-half
+// convention: (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin), angle = fp32(pos) * inv_freq[i].
+// The angle is reduced in double precision so positions up to 2^17 stay exact.
+__global__ void __launch_bounds__(EW_THREADS) rope_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos,
+                                                         const float* __restrict__ inv_freq, int T, long long ld,
+                                                         int n_heads, int D, float sign) {
+  const int half = D >> 1;
+  const int vec_per_tok = half >> 3;  // 8 frequencies per thread
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= static_cast<long long>(T) * vec_per_tok) return;
+  const int t = static_cast<int>(gid / vec_per_tok);
+  const int i0 = static_cast<int>(gid % vec_per_tok) * 8;
+  const float p = static_cast<float>(pos[t]);
+  float cs[8], sn[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float ang = p * inv_freq[i0 + i];
+    double s, c;
+    sincos(static_cast<double>(ang), &s, &c);
+    cs[i] = static_cast<float>(c);
+    sn[i] = static_cast<float>(s) * sign;
+  }
+  __nv_bfloat16* row = qkv + static_cast<long long>(t) * ld;
+  for (int h = 0; h < n_heads; ++h) {
+    __nv_bfloat16* p1 = row + h * D + i0;
+    __nv_bfloat16* p2 = p1 + half;
+    bf16x8 a, b; a.load(p1); b.load(p2);
+    float x1[8], x2[8], o1[8], o2[8]; a.to_float(x1); b.to_float(x2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { o1[i] = x1[i] * cs[i] - x2[i] * sn[i]; o2[i] = x2[i] * cs[i] + x1[i] * sn[i]; }
+    a.from_float(o1); b.from_float(o2); a.store(p1); b.store(p2);
+  }
+}
+
+// ------------------------------------------------------------------------------ SwiGLU
+__global__ void __launch_bounds__(EW_THREADS) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
+                                                               long long T, int F) {
+  const int vpr = F >> 3;
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= T * vpr) return;
+  const long long t = gid / vpr;
+  const int c = static_cast<int>(gid % vpr) * 8;
+  bf16x8 g, u; g.load(gu + t * 2 * F + c); u.load(gu + t * 2 * F + F + c);
+  float fg[8], fu[8], o[8]; g.to_float(fg); u.to_float(fu);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = fg[i] / (1.f + __expf(-fg[i])) * fu[i];
+  g.from_float(o); g.store(act + t * F + c);
+}
+
+__global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gu,
+                                                               __nv_bfloat16* __restrict__ dgu, long long T, int F) {
+  const int vpr = F >> 3;
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= T * vpr) return;
+  const long long t = gid / vpr;
+  const int c = static_cast<int>(gid % vpr) * 8;
+  bf16x8 g, u, d; g.load(gu + t * 2 * F + c); u.load(gu + t * 2 * F + F + c); d.load(dact + t * F + c);
+  float fg[8], fu[8], fd[8], og[8], ou[8]; g.to_float(fg); u.to_float(fu); d.to_float(fd);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float sig = 1.f / (1.f + __expf(-fg[i]));
+    og[i] = fd[i] * fu[i] * sig * (1.f + fg[i] * (1.f - sig));
+    ou[i] = fd[i] * fg[i] * sig;
+  }
+  g.from_float(og); u.from_float(ou);
+  g.store(dgu + t * 2 * F + c); u.store(dgu + t * 2 * F + F + c);
+}
+
+// ------------------------------------------------------------------------------ embedding
+__global__ void __launch_bounds__(128) embedding_fwd_kernel(const __nv_bfloat16* __restrict__ w, const long long* __restrict__ ids,
+                                                           __nv_bfloat16* __restrict__ out, int H) {
+  const long long t = blockIdx.x;
+  const __nv_bfloat16* src = w + ids[t] * H;
+  __nv_bfloat16* dst = out + t * H;
+  for (int c = threadIdx.x * 8; c < H; c += 128 * 8) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+}
+
+// dW[ids[t], :] += dx[t, :] with packed bf16x2 atomics (rows of one token id may collide).
+__global__ void __launch_bounds__(128) embedding_bwd_kernel(__nv_bfloat16* __restrict__ dw, const long long* __restrict__ ids,
+                                                           const __nv_bfloat16* __restrict__ dx, int H) {
+  const long long t = blockIdx.x;
+  __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(dw + ids[t] * H);
+  const __nv_bfloat162* src = reinterpret_cast<const __nv_bfloat162*>(dx + t * H);
+  for (int c = threadIdx.x; c < (H >> 1); c += 128) atomicAdd(dst + c, src[c]);
+}
+
+// ------------------------------------------------------------------------------ cross-entropy
+// One block per row of a logits chunk (fp32 [R, V], leading dimension ld). Pass 1: online
+// max / sum-exp. Pass 2: dlogits = (softmax - onehot) * scale in bf16. Rows whose target is
+// ignore_index get zero loss and zero gradient.
+__global__ void __launch_bounds__(1024) ce_fwd_bwd_kernel(const float* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                                                         float* __restrict__ loss, __nv_bfloat16* __restrict__ dlogits, long long ldd,
+                                                         int V, float grad_scale, long long ignore_index) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const float* lr = logits + row * ld;
+  __nv_bfloat16* dr = dlogits + row * ldd;
+  const long long tgt = targets[row];
+  if (tgt == ignore_index) {
+    for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) *reinterpret_cast<uint4*>(dr + c) = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) loss[row] = 0.f;
+    return;
+  }
+  float m = -INFINITY, s = 0.f;
+  for (int c = threadIdx.x * 4; c < V; c += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(lr + c);
+    const float mx = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+    if (mx > m) { s *= __expf(m - mx); m = mx; }
+    s += __expf(v.x - m) + __expf(v.y - m) + __expf(v.z - m) + __expf(v.w - m);
+  }
+  const float gm = block_max(m, red);
+  s *= __expf(m - gm);
+  const float gs = block_sum(s, red);
+  const float lse = gm + logf(gs);
+  if (threadIdx.x == 0) loss[row] = lse - lr[tgt];
+  const float inv = grad_scale / gs;
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    const float4 a = *reinterpret_cast<const float4*>(lr + c);
+    const float4 b = *reinterpret_cast<const float4*>(lr + c + 4);
+    float o[8] = {__expf(a.x - gm) * inv, __expf(a.y - gm) * inv, __expf(a.z - gm) * inv, __expf(a.w - gm) * inv,
+                  __expf(b.x - gm) * inv, __expf(b.y - gm) * inv, __expf(b.z - gm) * inv, __expf(b.w - gm) * inv};
+    if (tgt >= c && tgt < c + 8) o[tgt - c] -= grad_scale;
+    bf16x8 ov; ov.from_float(o); ov.store(dr + c);
+  }
+}
+
+// ------------------------------------------------------------------------------ column sums (bias grad)
+// part[split, c] = sum over this split's rows of x[r, c]; then reduce_rows_kernel.
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long long ld, float* __restrict__ part,
+                                                            int T, int N) {
+  __shared__ float sm[8][64];
+  const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+  const int c = blockIdx.x * 64 + lane * 2;
+  const int rows_per = (T + gridDim.y - 1) / gridDim.y;
+  const int r0 = blockIdx.y * rows_per, r1 = min(T, r0 + rows_per);
+  float a = 0.f, b = 0.f;
+  if (c < N) {
+    for (int r = r0 + wy; r < r1; r += 8) {
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + static_cast<long long>(r) * ld + c));
+      a += v.x; b += v.y;
+    }
+  }
+  sm[wy][lane * 2] = a; sm[wy][lane * 2 + 1] = b;
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += sm[i][threadIdx.x];
+    const int cc = blockIdx.x * 64 + threadIdx.x;
+    if (cc < N) part[static_cast<long long>(blockIdx.y) * N + cc] = s;
+  }
+}
+
+// ------------------------------------------------------------------------------ optimizer-side
+// acc = (accumulate ? acc : 0) + src   (fp32 accumulator, bf16 or fp32 source)
+template <typename SrcT>
+__global__ void __launch_bounds__(EW_THREADS) accumulate_kernel(float* __restrict__ acc, const SrcT* __restrict__ src, long long n, int accumulate) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  float f[8];
+  if constexpr (sizeof(SrcT) == 2) { bf16x8 v; v.load(reinterpret_cast<const __nv_bfloat16*>(src) + i); v.to_float(f); }
+  else {
+    const float4 a = *reinterpret_cast<const float4*>(src + i), b = *reinterpret_cast<const float4*>(src + i + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  float4* d = reinterpret_cast<float4*>(acc + i);
+  if (accumulate) {
+    const float4 a = d[0], b = d[1];
+    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w; f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+  }
+  d[0] = make_float4(f[0], f[1], f[2], f[3]);
+  d[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+
+// dst(bf16) = (accumulate ? dst : 0) + src(fp32)
+__global__ void __launch_bounds__(EW_THREADS) f32_to_bf16_kernel(__nv_bfloat16* __restrict__ dst, const float* __restrict__ src, long long n, int accumulate) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  const float4 a = *reinterpret_cast<const float4*>(src + i), b = *reinterpret_cast<const float4*>(src + i + 4);
+  float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  if (accumulate) {
+    bf16x8 v; v.load(dst + i); float g[8]; v.to_float(g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] += g[k];
+  }
+  bf16x8 o; o.from_float(f); o.store(dst + i);
+}
+
+// out[0] += sum(x^2): per-block partial sums combined with one atomic per block.
+__global__ void __launch_bounds__(EW_THREADS) sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(x + i);
+    s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+// Fused AdamW on a shard: g = grad * coef[0]; moments in fp32 or bf16; master fp32; bf16 working copy refreshed.
+template <typename StateT>
+__global__ void __launch_bounds__(EW_THREADS) adamw_kernel(float* __restrict__ master, StateT* __restrict__ m, StateT* __restrict__ v,
+                                                          const float* __restrict__ grad, __nv_bfloat16* __restrict__ param,
+                                                          long long n, float lr, float beta1, float beta2, float eps, float wd,
+                                                          float inv_bc1, float inv_sqrt_bc2, const float* __restrict__ coef) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  const float c = coef[0];
+  const float4 g4 = *reinterpret_cast<const float4*>(grad + i);
+  float4 w4 = *reinterpret_cast<float4*>(master + i);
+  float g[4] = {g4.x * c, g4.y * c, g4.z * c, g4.w * c};
+  float w[4] = {w4.x, w4.y, w4.z, w4.w};
+  float mm[4], vv[4];
+  if constexpr (sizeof(StateT) == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(m + i), b = *reinterpret_cast<const float4*>(v + i);
+    mm[0] = a.x; mm[1] = a.y; mm[2] = a.z; mm[3] = a.w; vv[0] = b.x; vv[1] = b.y; vv[2] = b.z; vv[3] = b.w;
+  } else {
+    const uint2 a = *reinterpret_cast<const uint2*>(m + i), b = *reinterpret_cast<const uint2*>(v + i);
+    float2 t;
+    t = unpack_bf16(a.x); mm[0] = t.x; mm[1] = t.y; t = unpack_bf16(a.y); mm[2] = t.x; mm[3] = t.y;
+    t = unpack_bf16(b.x); vv[0] = t.x; vv[1] = t.y; t = unpack_bf16(b.y); vv[2] = t.x; vv[3] = t.y;
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    w[k] *= (1.f - lr * wd);
+    mm[k] = beta1 * mm[k] + (1.f - beta1) * g[k];
+    vv[k] = beta2 * vv[k] + (1.f - beta2) * g[k] * g[k];
+    const float denom = sqrtf(vv[k]) * inv_sqrt_bc2 + eps;
+    w[k] -= lr * inv_bc1 * mm[k] / denom;
+  }
+  *reinterpret_cast<float4*>(master + i) = make_float4(w[0], w[1], w[2], w[3]);
+  if constexpr (sizeof(StateT) == 4) {
+    *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+  } else {
+    *reinterpret_cast<uint2*>(m + i) = make_uint2(pack_bf16(mm[0], mm[1]), pack_bf16(mm[2], mm[3]));
+    *reinterpret_cast<uint2*>(v + i) = make_uint2(pack_bf16(vv[0], vv[1]), pack_bf16(vv[2], vv[3]));
+  }
+  *reinterpret_cast<uint2*>(param + i) = make_uint2(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]));
+}
+
+static inline int cdiv(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
+static inline int launch_ok() { return cudaGetLastError() == cudaSuccess ? 0 : -5; }
+static int num_sms() {
+  static int n = 0;
+  if (n == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev); }
+  return n;
+}
+
+}  // namespace mtb
+
+using namespace mtb;
+typedef __nv_bfloat16 bf16;
+
+extern "C" {
+
+int mtb200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, float eps, int T, int H, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8) return -10;
+  rmsnorm_fwd_kernel<<<T, EW_THREADS, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, eps, H);
+  return launch_ok();
+}
+
+// Number of row-partials the backward writes (rows of the dw_partial scratch, [blocks, H] fp32).
+int mtb200_rmsnorm_bwd_blocks(int T) { const int b = num_sms() * 2; return T < b ? (T > 0 ? T : 1) : b; }
+
+int mtb200_rmsnorm_bwd(const void* dy, const void* x, const float* rstd, const void* w, const void* add_to, void* dx,
+                       float* dw_partial, void* dw_out, int T, int H, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8 || H > 4 * 8 * EW_THREADS) return -10;
+  const int blocks = mtb200_rmsnorm_bwd_blocks(T);
+  const int vpt = cdiv(H, 8 * EW_THREADS);
+#define RB(V) rmsnorm_bwd_kernel<V><<<blocks, EW_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)x, rstd, (const bf16*)w, (const bf16*)add_to, (bf16*)dx, dw_partial, T, H)
+  if (vpt <= 1) RB(1); else if (vpt == 2) RB(2); else if (vpt == 3) RB(3); else RB(4);
+#undef RB
+  reduce_rows_kernel<<<cdiv(H, 256), 256, 0, st>>>(dw_partial, (bf16*)dw_out, blocks, H);
+  return launch_ok();
+}
+
+int mtb200_rope(void* qkv, const int* pos, const float* inv_freq, int T, long long ld, int n_heads, int D, int inverse, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (D % 16 || ld % 8) return -10;
+  const long long n = static_cast<long long>(T) * (D / 16);
+  rope_kernel<<<cdiv(n, EW_THREADS), EW_THREADS, 0, st>>>((bf16*)qkv, pos, inv_freq, T, ld, n_heads, D, inverse ? -1.f : 1.f);
+  return launch_ok();
+}
+
+int mtb200_swiglu_fwd(const void* gu, void* act, long long T, int F, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (F % 8) return -10;
+  swiglu_fwd_kernel<<<cdiv(T * (F / 8), EW_THREADS), EW_THREADS, 0, st>>>((const bf16*)gu, (bf16*)act, T, F);
+  return launch_ok();
+}
+
+int mtb200_swiglu_bwd(const void* dact, const void* gu, void* dgu, long long T, int F, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (F % 8) return -10;
+  swiglu_bwd_kernel<<<cdiv(T * (F / 8), EW_THREADS), EW_THREADS, 0, st>>>((const bf16*)dact, (const bf16*)gu, (bf16*)dgu, T, F);
+  return launch_ok();
+}
+
+int mtb200_embedding_fwd(const void* w, const long long* ids, void* out, int T, int H, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8) return -10;
+  embedding_fwd_kernel<<<T, 128, 0, st>>>((const bf16*)w, ids, (bf16*)out, H);
+  return launch_ok();
+}
+
+int mtb200_embedding_bwd(void* dw, const long long* ids, const void* dx, int T, int H, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 2) return -10;
+  embedding_bwd_kernel<<<T, 128, 0, st>>>((bf16*)dw, ids, (const bf16*)dx, H);
+  return launch_ok();
+}
+
+int mtb200_ce_fwd_bwd(const float* logits, long long ld, const long long* targets, float* loss, void* dlogits, long long ldd,
+                      int R, int V, float grad_scale, long long ignore_index, cudaStream_t st) {
+  if (R <= 0) return 0;
+  if (V % 8 || ld % 4 || ldd % 8) return -10;
+  ce_fwd_bwd_kernel<<<R, 1024, 0, st>>>(logits, ld, targets, loss, (bf16*)dlogits, ldd, V, grad_scale, ignore_index);
+  return launch_ok();
+}
+
+// out[N] (bf16) = column sums of x[T, N]. scratch: fp32 [32, N].
+int mtb200_colsum(const void* x, long long ld, void* out, float* scratch, int T, int N, cudaStream_t st) {
+  if (T <= 0 || N <= 0) return 0;
+  if (N % 2) return -10;
+  const int splits = T < 32 ? 1 : 32;
+  colsum_partial_kernel<<<dim3(cdiv(N, 64), splits), 256, 0, st>>>((const bf16*)x, ld, scratch, T, N);
+  reduce_rows_kernel<<<cdiv(N, 256), 256, 0, st>>>(scratch, (bf16*)out, splits, N);
+  return launch_ok();
+}
+
+int mtb200_accumulate(float* acc, const void* src, long long n, int src_is_f32, int accumulate, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 8) return -10;
+  if (src_is_f32) accumulate_kernel<float><<<cdiv(n / 8, EW_THREADS), EW_THREADS, 0, st>>>(acc, (const float*)src, n, accumulate);
+  else accumulate_kernel<bf16><<<cdiv(n / 8, EW_THREADS), EW_THREADS, 0, st>>>(acc, (const bf16*)src, n, accumulate);
+  return launch_ok();
+}
+
+int mtb200_f32_to_bf16(void* dst, const float* src, long long n, int accumulate, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 8) return -10;
+  f32_to_bf16_kernel<<<cdiv(n / 8, EW_THREADS), EW_THREADS, 0, st>>>((bf16*)dst, src, n, accumulate);
+  return launch_ok();
+}
+
+int mtb200_sumsq(const float* x, long long n, float* out, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 4) return -10;
+  const int blocks = static_cast<int>(min(static_cast<long long>(num_sms() * 8), (n / 4 + EW_THREADS - 1) / EW_THREADS));
+  sumsq_kernel<<<blocks, EW_THREADS, 0, st>>>(x, n, out);
+  return launch_ok();
+}
+
+int mtb200_adamw(float* master, void* m, void* v, int state_is_f32, const float* grad, void* param, long long n, float lr,
+                 float beta1, float beta2, float eps, float wd, int step, const float* coef, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 4) return -10;
+  const float inv_bc1 = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
+  const float inv_sqrt_bc2 = 1.f / sqrtf(1.f - powf(beta2, static_cast<float>(step)));
+  const int blocks = cdiv(n / 4, EW_THREADS);
+  if (state_is_f32)
+    adamw_kernel<float><<<blocks, EW_THREADS, 0, st>>>(master, (float*)m, (float*)v, grad, (bf16*)param, n, lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2, coef);
+  else
+    adamw_kernel<bf16><<<blocks, EW_THREADS, 0, st>>>(master, (bf16*)m, (bf16*)v, grad, (bf16*)param, n, lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2, coef);
+  return launch_ok();
+}
+
+}  // extern "C"

@@ -1,0 +1,324 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory ->
+// tcgen05.mma with the fp32 accumulator in tensor memory -> tcgen05.ld epilogue.
+//
+//   D[M, N] = A * B (+ bias[N]) (+ R[M, N])        bf16 inputs, fp32 accumulate, bf16 or fp32 out
+//
+// A is an "M x K" operand and B an "N x K" operand; each may be stored K-major (row-major
+// [rows, K]) or MN-major (row-major [K, rows]), which covers the three products of a linear layer
+// without any transposed copies:
+//   forward  Y[T,N]  = X[T,K]  * W[N,K]^T   A K-major,  B K-major
+//   dgrad    dX[T,K] = dY[T,N] * W[N,K]     A K-major,  B MN-major (W read as [red=N, out=K])
+//   wgrad    dW[N,K] = dY[T,N]^T * X[T,K]   A MN-major, B MN-major (both read as [red=T, .])
+//
+// CTA layout (192 threads, one CTA per SM, grid = min(tiles, SMs)):
+//   warp 0     TMA producer: fills a STAGES-deep ring of {A 128x64, B 256x64} tiles
+//   warp 1     allocates 512 TMEM columns (two 128x256 fp32 accumulators) and issues the MMAs
+//   warps 2-5  epilogue: each reads its 32-lane quarter of the accumulator, adds bias / residual,
+//              converts and stores; runs concurrently with the next tile's MMAs (double buffer)
+// Tiles are visited in bands of GROUP_M row-tiles so the A band stays in L2 while B streams.
+//
+// Out-of-range rows/columns/K are zero-filled by TMA and masked in the epilogue, so M, N and K
+// need no padding (N and the leading dimensions must be multiples of 8 elements: TMA strides
+// are multiples of 16 bytes).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace mtb {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GROUP_M = 16;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct GemmParams {
+  int M, N, K;
+  void* D;
+  long long ldd;
+  const void* R;          // optional residual / accumulate source, same dtype as D
+  long long ldr;
+  const __nv_bfloat16* bias;  // optional, [N]
+  int* status;            // device word; set non-zero when a bounded wait expired
+};
+
+template <bool A_MN, bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;   // [2] accumulator ready for the epilogue
+  uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int kblocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int t, int& tm, int& tn) {
+    const int band = t / (GROUP_M * tiles_n);
+    const int first_m = band * GROUP_M;
+    const int rows = min(GROUP_M, tiles_m - first_m);
+    const int local = t - band * GROUP_M * tiles_n;
+    tm = first_m + local % rows;
+    tn = local / rows;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, tm, tn);
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { atomicExch(p.status, 1); goto done; }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_TILE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[s], tm * BM + j * 64, kb * BK);
+          } else {
+            tma_load_2d(sa, &tmap_a, &full_bar[s], kb * BK, tm * BM);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[s], tn * BN + j * 64, kb * BK);
+          } else {
+            tma_load_2d(sb, &tmap_b, &full_bar[s], kb * BK, tn * BN);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      uint32_t it = 0, tl = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tl) {
+        const int acc = tl & 1;
+        const uint32_t aph = (tl >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag)) { atomicExch(p.status, 2); goto done; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { atomicExch(p.status, 3); goto done; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
+        }
+        umma_commit(&tfull_bar[acc]);   // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint32_t tl = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tl) {
+      int tm, tn;
+      tile_coords(t, tm, tn);
+      const int acc = tl & 1;
+      const uint32_t aph = (tl >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], aph, abort_flag)) { atomicExch(p.status, 4); goto done; }
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = tn * BN + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        if (row_ok) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                const uint4 b = *reinterpret_cast<const uint4*>(p.bias + col0 + j);
+                const float2 b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y), b2 = unpack_bf16(b.z), b3 = unpack_bf16(b.w);
+                f[j] += b0.x; f[j + 1] += b0.y; f[j + 2] += b1.x; f[j + 3] += b1.y;
+                f[j + 4] += b2.x; f[j + 5] += b2.y; f[j + 6] += b3.x; f[j + 7] += b3.y;
+              }
+            }
+          }
+          if (OUT_F32) {
+            float* dptr = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+            const float* rptr = p.R ? reinterpret_cast<const float*>(p.R) + static_cast<long long>(row) * p.ldr + col0 : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col0 + j < p.N) {
+                float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                if (rptr) { const float4 r = *reinterpret_cast<const float4*>(rptr + j); o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w; }
+                *reinterpret_cast<float4*>(dptr + j) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* dptr = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+            const __nv_bfloat16* rptr = p.R ? reinterpret_cast<const __nv_bfloat16*>(p.R) + static_cast<long long>(row) * p.ldr + col0 : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                if (rptr) {
+                  const uint4 r = *reinterpret_cast<const uint4*>(rptr + j);
+                  const float2 r0 = unpack_bf16(r.x), r1 = unpack_bf16(r.y), r2 = unpack_bf16(r.z), r3 = unpack_bf16(r.w);
+                  f[j] += r0.x; f[j + 1] += r0.y; f[j + 2] += r1.x; f[j + 3] += r1.y;
+                  f[j + 4] += r2.x; f[j + 5] += r2.y; f[j + 6] += r3.x; f[j + 7] += r3.y;
+                }
+                uint4 o;
+                o.x = pack_bf16(f[j], f[j + 1]); o.y = pack_bf16(f[j + 2], f[j + 3]);
+                o.z = pack_bf16(f[j + 4], f[j + 5]); o.w = pack_bf16(f[j + 6], f[j + 7]);
+                *reinterpret_cast<uint4*>(dptr + j) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [outer, inner] matrix with leading dimension `ld`.
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16) return -2;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+static int g_num_sms = 0;
+
+template <bool A_MN, bool B_MN, bool OUT_F32>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = gemm_kernel<A_MN, B_MN, OUT_F32>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess) return -4;
+    configured = true;
+  }
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace mtb
+
+extern "C" {
+
+// D[M,N] = op(A) * op(B) (+bias) (+R).
+//   a_mn = 0: A is row-major [M, K] (lda >= K);  a_mn = 1: A is row-major [K, M] (lda >= M)
+//   b_mn = 0: B is row-major [N, K] (ldb >= K);  b_mn = 1: B is row-major [K, N] (ldb >= N)
+//   out_f32: D and R are fp32, else bf16. R may alias D (accumulate). bias is bf16 [N] or null.
+// Returns 0 on success, a negative code on invalid arguments or launch failure.
+int mtb200_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* D,
+                     long long ldd, int out_f32, const void* R, long long ldr, const void* bias, int M, int N, int K,
+                     int* status, cudaStream_t stream) {
+  using namespace mtb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (N % 8 || ldd % 8 || (R && ldr % 8)) return -10;
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn) rc = make_tmap_2d_bf16(&ta, A, M, K, lda, 64, 64);
+  else rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
+  if (rc) return rc;
+  if (b_mn) rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, 64);
+  else rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);
+  if (rc) return rc - 10;
+  GemmParams p{M, N, K, D, ldd, R, ldr, reinterpret_cast<const __nv_bfloat16*>(bias), status};
+  const int sel = (a_mn ? 4 : 0) | (b_mn ? 2 : 0) | (out_f32 ? 1 : 0);
+  switch (sel) {
+    case 0: return launch<false, false, false>(ta, tb, p, stream);
+    case 1: return launch<false, false, true>(ta, tb, p, stream);
+    case 2: return launch<false, true, false>(ta, tb, p, stream);
+    case 3: return launch<false, true, true>(ta, tb, p, stream);
+    case 4: return launch<true, false, false>(ta, tb, p, stream);
+    case 5: return launch<true, false, true>(ta, tb, p, stream);
+    case 6: return launch<true, true, false>(ta, tb, p, stream);
+    default: return launch<true, true, true>(ta, tb, p, stream);
+  }
+}
+
+}  // extern "C"

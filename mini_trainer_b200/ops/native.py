@@ -1,0 +1,296 @@
+"""sm_100a kernel backend: ctypes bindings over ``_native/libmtb200_cuda.so``.
+
+Same method set as ``TorchOps``; tensors are bf16 on a CUDA device, 2-D, row-major. Every call
+launches on the current torch CUDA stream. A missing library or a non-zero return code raises —
+there is no silent fallback to PyTorch on a GPU machine.
+
+``launches`` counts kernels launched through this backend (reported by the benchmark).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .. import build as _build
+
+_LIB = None
+
+
+def load_library():
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = _build.CUDA_LIB
+    if not path.exists() or os.environ.get("MTB200_REBUILD"):
+        _build.build_cuda()
+    if not path.exists():
+        raise RuntimeError(f"native CUDA library {path} is missing and could not be built (nvcc not found)")
+    lib = ctypes.CDLL(str(path))
+    for name in dir(_Sig):
+        if name.startswith("mtb200_") and hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.restype = c_int
+            fn.argtypes = getattr(_Sig, name)
+    _LIB = lib
+    return lib
+
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+
+class _Sig:
+    mtb200_gemm_bf16 = [P, L, I, P, L, I, P, L, I, P, L, P, I, I, I, P, P]
+    mtb200_rmsnorm_fwd = [P, P, P, P, F, I, I, P]
+    mtb200_rmsnorm_bwd_blocks = [I]
+    mtb200_rmsnorm_bwd = [P, P, P, P, P, P, P, P, I, I, P]
+    mtb200_rope = [P, P, P, I, L, I, I, I, P]
+    mtb200_swiglu_fwd = [P, P, L, I, P]
+    mtb200_swiglu_bwd = [P, P, P, L, I, P]
+    mtb200_embedding_fwd = [P, P, P, I, I, P]
+    mtb200_embedding_bwd = [P, P, P, I, I, P]
+    mtb200_ce_fwd_bwd = [P, L, P, P, P, L, I, I, F, L, P]
+    mtb200_colsum = [P, L, P, P, I, I, P]
+    mtb200_accumulate = [P, P, L, I, I, P]
+    mtb200_f32_to_bf16 = [P, P, L, I, P]
+    mtb200_sumsq = [P, L, P, P]
+    mtb200_adamw = [P, P, P, I, P, P, L, F, F, F, F, F, I, P, P]
+    mtb200_attn_fwd = [P, L, P, L, P, P, I, I, I, I, I, I, F, P, P]
+    mtb200_attn_bwd = [P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, F, P, P]
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+class NativeOps:
+    name = "native"
+
+    def __init__(self, device, ce_chunk: int = 2048, attention: str | None = None):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("NativeOps needs a CUDA device")
+        self.lib = load_library()
+        self.ce_chunk = ce_chunk
+        self.attention_impl = attention or os.environ.get("MTB200_ATTENTION", "native")
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0
+        self._scratch = {}
+        self._attn_plan_cache = {}
+
+    # -- plumbing ---------------------------------------------------------------------
+    def _st(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _call(self, name, *args, n=1):
+        rc = getattr(self.lib, name)(*args)
+        if rc != 0:
+            raise RuntimeError(f"{name} failed with code {rc}")
+        self.launches += n
+
+    def _buf(self, key, numel, dtype):
+        b = self._scratch.get(key)
+        if b is None or b.numel() < numel or b.dtype != dtype:
+            b = torch.empty(numel, dtype=dtype, device=self.device)
+            self._scratch[key] = b
+        return b[:numel]
+
+    def check_status(self):
+        """Raises if any kernel recorded an expired bounded wait (one host sync)."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise RuntimeError(f"a device-side bounded wait expired (code {code})")
+
+    # -- GEMM -------------------------------------------------------------------------
+    def gemm(self, a, a_mn, b, b_mn, out, M, N, K, residual=None, bias=None):
+        """out[M,N] = A*B (+bias) (+residual). ``a_mn``/``b_mn``: operand stored [K, rows]."""
+        out_f32 = out.dtype == torch.float32
+        assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+        assert residual is None or residual.dtype == out.dtype
+        self._call("mtb200_gemm_bf16", a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
+                   out.data_ptr(), out.stride(0), int(out_f32), _ptr(residual),
+                   residual.stride(0) if residual is not None else 0, _ptr(bias), M, N, K,
+                   self.status.data_ptr(), self._st())
+        return out
+
+    # -- embedding --------------------------------------------------------------------
+    def embedding(self, weight, ids):
+        T, H = ids.shape[0], weight.shape[1]
+        out = torch.empty(T, H, dtype=weight.dtype, device=self.device)
+        self._call("mtb200_embedding_fwd", weight.data_ptr(), ids.data_ptr(), out.data_ptr(), T, H, self._st())
+        return out
+
+    def embedding_bwd(self, dweight, ids, dx):
+        self._call("mtb200_embedding_bwd", dweight.data_ptr(), ids.data_ptr(), dx.data_ptr(), ids.shape[0],
+                   dweight.shape[1], self._st())
+
+    # -- rmsnorm ----------------------------------------------------------------------
+    def rmsnorm(self, x, w, eps):
+        T, H = x.shape
+        y = torch.empty_like(x)
+        rstd = torch.empty(T, dtype=torch.float32, device=self.device)
+        self._call("mtb200_rmsnorm_fwd", x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), eps, T, H, self._st())
+        return y, rstd
+
+    def rmsnorm_bwd(self, dy, x, rstd, w, dw_out, add_to=None):
+        T, H = x.shape
+        dx = torch.empty_like(x)
+        blocks = self.lib.mtb200_rmsnorm_bwd_blocks(T)
+        part = self._buf("rms_part", blocks * H, torch.float32)
+        self._call("mtb200_rmsnorm_bwd", dy.data_ptr(), x.data_ptr(), rstd.data_ptr(), w.data_ptr(), _ptr(add_to),
+                   dx.data_ptr(), part.data_ptr(), dw_out.data_ptr(), T, H, self._st(), n=2)
+        return dx
+
+    # -- linear -----------------------------------------------------------------------
+    def linear(self, x, w, bias=None, residual=None):
+        T, K = x.shape
+        N = w.shape[0]
+        out = torch.empty(T, N, dtype=x.dtype, device=self.device)
+        return self.gemm(x, False, w, False, out, T, N, K, residual=residual, bias=bias)
+
+    def linear_dgrad(self, dy, w):
+        T, N = dy.shape
+        K = w.shape[1]
+        out = torch.empty(T, K, dtype=dy.dtype, device=self.device)
+        return self.gemm(dy, False, w, True, out, T, K, N)
+
+    def linear_wgrad(self, dy, x, dw_out, dbias_out=None):
+        T, N = dy.shape
+        K = x.shape[1]
+        self.gemm(dy, True, x, True, dw_out, N, K, T)
+        if dbias_out is not None:
+            scratch = self._buf("colsum", 32 * N, torch.float32)
+            self._call("mtb200_colsum", dy.data_ptr(), dy.stride(0), dbias_out.data_ptr(), scratch.data_ptr(), T, N,
+                       self._st(), n=2)
+
+    # -- rope -------------------------------------------------------------------------
+    def rope_(self, qkv, position_ids, inv_freq, n_q_heads, n_kv_heads, head_dim, inverse=False):
+        assert position_ids.dtype == torch.int32
+        self._call("mtb200_rope", qkv.data_ptr(), position_ids.data_ptr(), inv_freq.data_ptr(), qkv.shape[0],
+                   qkv.stride(0), n_q_heads + n_kv_heads, head_dim, int(inverse), self._st())
+        return qkv
+
+    # -- attention --------------------------------------------------------------------
+    def _attn_plan(self, cu_host, block_m):
+        """Work table for the attention kernels: one row (seq_start, seq_len, q0) per 128-row query
+        block, longest causal span first. Built once per minibatch and reused by every layer."""
+        key = (id(cu_host), block_m)
+        hit = self._attn_plan_cache.get(key)
+        if hit is not None and hit[0] is cu_host:
+            return hit[1]
+        items = []
+        for a, b in zip(cu_host[:-1], cu_host[1:]):
+            for q0 in range(0, b - a, block_m):
+                items.append((a, b - a, q0))
+        items.sort(key=lambda it: -it[2])
+        table = torch.tensor(items, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        self._attn_plan_cache = {key: (cu_host, table)}
+        return table
+
+    def attention(self, qkv, cu_seqlens, cu_host, max_seqlen, hq, hkv, d):
+        T = qkv.shape[0]
+        if self.attention_impl == "flash_attn":
+            return self._fa_fwd(qkv, cu_seqlens, max_seqlen, hq, hkv, d)
+        out = torch.empty(T, hq * d, dtype=qkv.dtype, device=self.device)
+        lse = torch.empty(hq, T, dtype=torch.float32, device=self.device)
+        plan = self._attn_plan(cu_host, 128)
+        self._call("mtb200_attn_fwd", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), lse.data_ptr(),
+                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, 0, d ** -0.5, self.status.data_ptr(), self._st())
+        return out, lse
+
+    def attention_bwd(self, dout, qkv, out, lse, cu_seqlens, cu_host, max_seqlen, hq, hkv, d):
+        T = qkv.shape[0]
+        if self.attention_impl == "flash_attn":
+            return self._fa_bwd(dout, qkv, out, lse, cu_seqlens, max_seqlen, hq, hkv, d)
+        dqkv = torch.empty_like(qkv)
+        plan = self._attn_plan(cu_host, 128)
+        delta = torch.empty(hq, T, dtype=torch.float32, device=self.device)
+        dq_acc = torch.zeros(T, hq * d, dtype=torch.float32, device=self.device)
+        self._call("mtb200_attn_bwd", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), dout.data_ptr(),
+                   dout.stride(0), dqkv.data_ptr(), dqkv.stride(0), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(),
+                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, 0, d ** -0.5, self.status.data_ptr(), self._st(), n=3)
+        return dqkv
+
+    # library baseline (flash-attn 2), selectable for A/B comparisons only
+    def _fa_fwd(self, qkv, cu, max_seqlen, hq, hkv, d):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_forward
+        T = qkv.shape[0]
+        q = qkv[:, : hq * d].view(T, hq, d)
+        k = qkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
+        v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        out, lse, _, _ = _flash_attn_varlen_forward(q, k, v, cu, cu, max_seqlen, max_seqlen, 0.0, d ** -0.5, causal=True)
+        return out.reshape(T, hq * d), lse
+
+    def _fa_bwd(self, dout, qkv, out, lse, cu, max_seqlen, hq, hkv, d):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+        T = qkv.shape[0]
+        q = qkv[:, : hq * d].view(T, hq, d)
+        k = qkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
+        v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        dqkv = torch.empty_like(qkv)
+        dq = dqkv[:, : hq * d].view(T, hq, d)
+        dk = dqkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
+        dv = dqkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        _flash_attn_varlen_backward(dout.view(T, hq, d), q, k, v, out.view(T, hq, d), lse, dq, dk, dv, cu, cu,
+                                    max_seqlen, max_seqlen, 0.0, d ** -0.5, True, -1, -1, 0.0, None, False)
+        return dqkv
+
+    # -- swiglu -----------------------------------------------------------------------
+    def swiglu(self, gate_up):
+        T, F2 = gate_up.shape
+        act = torch.empty(T, F2 // 2, dtype=gate_up.dtype, device=self.device)
+        self._call("mtb200_swiglu_fwd", gate_up.data_ptr(), act.data_ptr(), T, F2 // 2, self._st())
+        return act
+
+    def swiglu_bwd(self, dact, gate_up):
+        T, F2 = gate_up.shape
+        dgu = torch.empty_like(gate_up)
+        self._call("mtb200_swiglu_bwd", dact.data_ptr(), gate_up.data_ptr(), dgu.data_ptr(), T, F2 // 2, self._st())
+        return dgu
+
+    # -- fused linear + cross-entropy ---------------------------------------------------
+    def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100):
+        """Chunked over tokens: logits chunk (fp32) -> per-row softmax statistics, loss and bf16
+        dlogits -> dX chunk and dW accumulation, all with the tcgen05 GEMM. Only ``[chunk, V]``
+        logits ever exist. dW is accumulated in fp32 and rounded to bf16 once at the end."""
+        T, H = x.shape
+        V = w.shape[0]
+        loss = torch.empty(T, dtype=torch.float32, device=self.device)
+        dx = torch.empty_like(x)
+        ck = min(self.ce_chunk, T)
+        logits = self._buf("ce_logits", ck * V, torch.float32).view(ck, V)
+        dlog = self._buf("ce_dlogits", ck * V, torch.bfloat16).view(ck, V)
+        dw32 = self._buf("ce_dw", V * H, torch.float32).view(V, H)
+        first = True
+        for a in range(0, T, ck):
+            n = min(ck, T - a)
+            self.gemm(x[a:a + n], False, w, False, logits, n, V, H)
+            self._call("mtb200_ce_fwd_bwd", logits.data_ptr(), V, targets[a:a + n].data_ptr(), loss[a:a + n].data_ptr(),
+                       dlog.data_ptr(), V, n, V, float(grad_scale), ignore_index, self._st())
+            self.gemm(dlog, False, w, True, dx[a:a + n], n, H, V)
+            self.gemm(dlog, True, x[a:a + n], True, dw32, V, H, n, residual=None if first else dw32)
+            first = False
+        self._call("mtb200_f32_to_bf16", dw_out.data_ptr(), dw32.data_ptr(), V * H, int(accumulate_dw), self._st())
+        return loss, dx
+
+    # -- optimizer --------------------------------------------------------------------
+    def sumsq(self, g):
+        out = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._call("mtb200_sumsq", g.data_ptr(), g.numel(), out.data_ptr(), self._st())
+        return out
+
+    def accumulate(self, acc, src, accumulate: bool):
+        """acc(fp32) = (acc if accumulate else 0) + src (bf16 or fp32)."""
+        self._call("mtb200_accumulate", acc.data_ptr(), src.data_ptr(), acc.numel(), int(src.dtype == torch.float32),
+                   int(accumulate), self._st())
+
+    def adamw_step(self, master, m, v, grad, param_out, lr, beta1, beta2, eps, weight_decay, step, grad_coef):
+        if not torch.is_tensor(grad_coef):
+            grad_coef = torch.full((1,), float(grad_coef), dtype=torch.float32, device=self.device)
+        grad_coef = grad_coef.reshape(1).float()
+        self._call("mtb200_adamw", master.data_ptr(), m.data_ptr(), v.data_ptr(), int(m.dtype == torch.float32),
+                   grad.data_ptr(), param_out.data_ptr(), master.numel(), lr, beta1, beta2, eps, weight_decay, step,
+                   grad_coef.data_ptr(), self._st())

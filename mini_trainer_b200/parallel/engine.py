@@ -227,7 +227,10 @@ class ShardedEngine:
     def _reduce(self, grp: ShardedGroup, gfull: torch.Tensor, slot: int = -1):
         """Reduce-scatter ``gfull`` into the group's fp32 accumulator on the side stream."""
         with self.side.run(wait_current=True):
-            self.comm.reduce_scatter_accumulate(gfull, grp.gacc, grp.has_grad, self._rs_scratch)
+            if self.world == 1 and hasattr(self.ops, "accumulate"):
+                self.ops.accumulate(grp.gacc, gfull[: grp.gacc.numel()], grp.has_grad)
+            else:
+                self.comm.reduce_scatter_accumulate(gfull, grp.gacc, grp.has_grad, self._rs_scratch)
             ev = self.side.record()
         grp.has_grad = True
         if slot >= 0:

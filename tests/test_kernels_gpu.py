@@ -1,0 +1,187 @@
+"""Every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+from mini_trainer_b200.ops.torch_ref import TorchOps
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mini_trainer_b200.ops.native import NativeOps
+    return NativeOps("cuda:0")
+
+
+REF = TorchOps()
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+GEMM_SHAPES = [(128, 256, 64), (128, 256, 128), (256, 512, 256), (300, 520, 200), (5, 64, 72), (1000, 1024, 4096),
+               (777, 2048, 1000), (4096, 6144, 4096), (129, 264, 8)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_forward_layout(ops, M, N, K):
+    torch.manual_seed(M + N + K)
+    x, w = bf(M, K), bf(N, K, scale=0.05)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(x, False, w, False, out, M, N, K)
+    ref = x.float() @ w.float().t()
+    assert rel_err(out, ref) < 6e-3
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_dgrad_layout(ops, M, N, K):
+    # out[M, N] = A[M, K] @ B[K, N]  (B stored [K, N]: MN-major)
+    torch.manual_seed(1 + M + N + K)
+    a, b = bf(M, K), bf(K, N, scale=0.05)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(a, False, b, True, out, M, N, K)
+    assert rel_err(out, a.float() @ b.float()) < 6e-3
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_wgrad_layout(ops, M, N, K):
+    # out[M, N] = A[K, M]^T @ B[K, N]  (both MN-major)
+    torch.manual_seed(2 + M + N + K)
+    if M % 8:
+        pytest.skip("leading dimension of an MN-major A must be a multiple of 8")
+    a, b = bf(K, M), bf(K, N, scale=0.05)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(a, True, b, True, out, M, N, K)
+    assert rel_err(out, a.float().t() @ b.float()) < 6e-3
+    ops.check_status()
+
+
+def test_gemm_epilogues(ops):
+    M, N, K = 384, 776, 320
+    x, w, bias, res = bf(M, K), bf(N, K, scale=0.05), bf(N), bf(M, N)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(x, False, w, False, out, M, N, K, residual=res, bias=bias)
+    ref = x.float() @ w.float().t() + bias.float() + res.float()
+    assert rel_err(out, ref) < 6e-3
+    o32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.gemm(x, False, w, False, o32, M, N, K)
+    assert rel_err(o32, x.float() @ w.float().t()) < 1e-5 + 1e-3
+    ops.gemm(x, False, w, False, o32, M, N, K, residual=o32)   # accumulate in place
+    assert rel_err(o32, 2 * (x.float() @ w.float().t())) < 2e-3
+    # strided output / operands (views into wider buffers)
+    wide = torch.zeros(M, N + 64, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(x, False, w, False, wide[:, 32:32 + N], M, N, K) if False else None
+    ops.check_status()
+
+
+def test_linear_ops_match_reference(ops):
+    T, K, N = 333, 256, 520
+    x, w, b, r = bf(T, K), bf(N, K, scale=0.05), bf(N), bf(T, N)
+    assert rel_err(ops.linear(x, w, b, r), REF.linear(x.float(), w.float(), b.float(), r.float())) < 6e-3
+    dy = bf(T, N)
+    assert rel_err(ops.linear_dgrad(dy, w), dy.float() @ w.float()) < 6e-3
+    dw, db = torch.empty_like(w), torch.empty_like(b)
+    ops.linear_wgrad(dy, x, dw, db)
+    assert rel_err(dw, dy.float().t() @ x.float()) < 6e-3
+    assert rel_err(db, dy.float().sum(0)) < 6e-3
+
+
+@pytest.mark.parametrize("T,H", [(1, 256), (37, 1536), (500, 4096), (64, 8192), (300, 3584)])
+def test_rmsnorm(ops, T, H):
+    x, w, dy, res = bf(T, H), (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16(), bf(T, H), bf(T, H)
+    y, rstd = ops.rmsnorm(x, w, 1e-5)
+    yr, rr = REF.rmsnorm(x, w, 1e-5)
+    assert rel_err(y, yr) < 4e-3 and rel_err(rstd, rr) < 1e-5
+    dw, dwr = torch.empty_like(w), torch.empty(H, dtype=torch.float32, device="cuda")
+    dx = ops.rmsnorm_bwd(dy, x, rstd, w, dw, add_to=res)
+    dxr = REF.rmsnorm_bwd(dy.float(), x.float(), rr, w.float(), dwr, add_to=res.float())
+    assert rel_err(dx, dxr) < 6e-3 and rel_err(dw, dwr) < 1e-2
+    dx2 = ops.rmsnorm_bwd(dy, x, rstd, w, dw)
+    assert rel_err(dx2, REF.rmsnorm_bwd(dy.float(), x.float(), rr, w.float(), dwr)) < 6e-3
+
+
+@pytest.mark.parametrize("D,hq,hkv", [(128, 4, 1), (64, 4, 2), (128, 28, 4)])
+def test_rope_forward_and_inverse(ops, D, hq, hkv):
+    from mini_trainer_b200.models.config import ModelConfig
+    T = 257
+    cfg = ModelConfig(vocab_size=8, hidden_size=hq * D, intermediate_size=8, num_hidden_layers=1,
+                      num_attention_heads=hq, num_key_value_heads=hkv, head_dim=D, rope_theta=5e5)
+    inv = cfg.rope_inv_freq().cuda()
+    pos = torch.randint(0, 60000, (T,), device="cuda", dtype=torch.int32)
+    qkv = bf(T, (hq + 2 * hkv) * D)
+    orig = qkv.clone()
+    ref = REF.rope_(qkv.float().clone(), pos, inv, hq, hkv, D)
+    ops.rope_(qkv, pos, inv, hq, hkv, D)
+    assert rel_err(qkv, ref) < 4e-3
+    assert torch.equal(qkv[:, (hq + hkv) * D:], orig[:, (hq + hkv) * D:])  # v untouched
+    ops.rope_(qkv, pos, inv, hq, hkv, D, inverse=True)
+    assert rel_err(qkv, orig) < 8e-3
+
+
+def test_swiglu(ops):
+    T, F = 123, 688
+    gu, da = bf(T, 2 * F), bf(T, F)
+    assert rel_err(ops.swiglu(gu), REF.swiglu(gu.float())) < 4e-3
+    assert rel_err(ops.swiglu_bwd(da, gu), REF.swiglu_bwd(da.float(), gu.float())) < 5e-3
+
+
+def test_embedding(ops):
+    V, H, T = 1000, 256, 4000
+    w = bf(V, H)
+    ids = torch.randint(0, 50, (T,), device="cuda")  # many collisions
+    assert torch.equal(ops.embedding(w, ids), w[ids])
+    dx = bf(T, H, scale=0.01)
+    dw = torch.zeros(V, H, dtype=torch.bfloat16, device="cuda")
+    ops.embedding_bwd(dw, ids, dx)
+    ref = torch.zeros(V, H, device="cuda").index_add_(0, ids, dx.float())
+    assert rel_err(dw, ref) < 3e-2  # bf16 atomic accumulation of ~80 addends per row
+
+
+@pytest.mark.parametrize("T,H,V", [(300, 256, 32000), (70, 512, 4104)])
+def test_linear_ce(ops, T, H, V):
+    torch.manual_seed(0)
+    x, w = bf(T, H), bf(V, H, scale=0.05)
+    tg = torch.randint(0, V, (T,), device="cuda")
+    tg[::3] = -100
+    dw, dwr = torch.zeros(V, H, dtype=torch.bfloat16, device="cuda"), torch.zeros(V, H, device="cuda")
+    ops.ce_chunk = 128
+    loss, dx = ops.linear_ce(x, w, tg, 0.01, dw)
+    ref = TorchOps(ce_chunk=128)
+    lr, dxr = ref.linear_ce(x.float(), w.float(), tg, 0.01, dwr)
+    assert rel_err(loss, lr) < 1e-3
+    assert (loss[::3] == 0).all()
+    assert rel_err(dx, dxr) < 1e-2 and rel_err(dw, dwr) < 1e-2
+    dw2 = dw.clone()
+    ops.linear_ce(x, w, tg, 0.01, dw2, accumulate_dw=True)
+    assert rel_err(dw2, 2 * dwr) < 1e-2
+
+
+def test_optimizer_kernels(ops):
+    n = 128 * 1000
+    for sdt in (torch.float32, torch.bfloat16):
+        master = torch.randn(n, device="cuda")
+        m, v = torch.randn(n, device="cuda").mul(0.01).to(sdt), torch.rand(n, device="cuda").mul(0.001).to(sdt)
+        g = torch.randn(n, device="cuda")
+        p = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        rm, rmm, rv, rp = master.clone(), m.clone(), v.clone(), torch.empty(n, device="cuda")
+        coef = torch.tensor(0.5, device="cuda")
+        ops.adamw_step(master, m, v, g, p, 1e-3, 0.9, 0.95, 1e-8, 0.01, 3, coef)
+        REF.adamw_step(rm, rmm, rv, g, rp, 1e-3, 0.9, 0.95, 1e-8, 0.01, 3, coef)
+        assert rel_err(master, rm) < 1e-5 and rel_err(m, rmm) < 1e-2 and rel_err(v, rv) < 1e-2
+        assert torch.equal(p, master.bfloat16())
+    g = torch.randn(n, device="cuda")
+    assert abs(ops.sumsq(g).item() - g.pow(2).sum().item()) < 1e-3 * n
+    acc, src = torch.randn(n, device="cuda"), bf(n)
+    ref = acc + src.float()
+    ops.accumulate(acc, src, True)
+    assert torch.allclose(acc, ref)
+    ops.accumulate(acc, src, False)
+    assert torch.equal(acc, src.float())
