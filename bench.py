@@ -1,0 +1,261 @@
+"""Headline benchmark: training tokens/s of Llama-3.1-8B-architecture full SFT (random init,
+synthetic data), device-timed, max over ranks.
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 3 --warmup 3
+    python bench.py --impl reference ...        # the unmodified reference stack, same config
+
+One "step" is one optimizer step over a global batch of 128 synthetic samples (lengths
+lognormal(7.5, 1.0) clipped to [64, 65536], -100 on a uniform 10-60 % prefix), LPT-packed to at
+most 64 000 tokens per GPU per minibatch, with gradient accumulation over this rank's minibatches,
+global-norm clipping and AdamW — nothing is skipped. The global batch is fixed, so the sweep over
+GPU counts is strong scaling.
+
+Two numbers are measured, each over exactly ``--steps`` steps after ``--warmup`` untimed ones,
+bracketed by barrier + synchronize and timed with CUDA events (max over ranks):
+
+* ``value``      — batches already resident on the device;
+* ``e2e.value``  — through the public training-step API (``ShardedEngine.train_step``) with every
+  minibatch copied from pinned host memory inside the timed region and the step's loss and
+  gradient norm read back to the host each step.
+
+Inputs (activations of 64 000 tokens x 4096 features per layer) are far larger than the 126 MB
+L2, so no explicit L2 flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+BASELINE_TOKENS_PER_S = None  # the reference publishes no throughput number
+
+MODEL = "llama-3.1-8b"
+GLOBAL_BATCH = 128
+MAX_TOKENS_PER_GPU = 64000
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx = float(r[2])
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# our implementation
+# ------------------------------------------------------------------------------------------
+def run_native(args) -> dict:
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, REPO)
+    from mini_trainer_b200.data.sampler import InfiniteSampler, MaxTokensPerRankCollator
+    from mini_trainer_b200.data.synthetic import CONFIG_DATA, synthetic_dataset
+    from mini_trainer_b200.models import decoder as D
+    from mini_trainer_b200.models.config import get_preset
+    from mini_trainer_b200.ops import get_ops
+    from mini_trainer_b200.parallel.comm import make_comm
+    from mini_trainer_b200.parallel.engine import OptimConfig, ShardedEngine, plan_state_dtype
+    from mini_trainer_b200.utils.dist import init_distributed_environment
+    from mini_trainer_b200.utils.lr import LRSchedule
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N>1")
+    device = init_distributed_environment()
+    rank = dist.get_rank()
+    cfg = get_preset(args.model)
+    spec, vocab, max_tokens, batch_size = CONFIG_DATA[args.model]
+    max_tokens = args.max_tokens_per_gpu or max_tokens
+    batch_size = args.batch_size or batch_size
+
+    comm = make_comm(args.comm, device)
+    hbm = torch.cuda.get_device_properties(device).total_memory
+    sdt = {"auto": plan_state_dtype(cfg, world, hbm, max(max_tokens, spec.hi)), "fp32": torch.float32,
+           "bf16": torch.bfloat16}[args.state_dtype]
+    ops = get_ops(device)
+    eng = ShardedEngine(cfg, device, ops, comm=comm, state_dtype=sdt, optim=OptimConfig(lr=1e-5))
+    eng.init_random(seed=893, on_device=True)
+    sched = LRSchedule(1e-5, "constant_with_warmup", 10)
+
+    # identical batches on every rank; each rank packs its own share
+    total_steps = 2 * (args.steps + args.warmup)
+    ds = synthetic_dataset(batch_size * total_steps, spec, cfg.vocab_size, seed=893)
+    sampler = iter(InfiniteSampler(len(ds), seed=893))
+    coll = MaxTokensPerRankCollator(max_tokens, rank=rank, world_size=world)
+    batches = []
+    for _ in range(total_steps):
+        idx = [next(sampler) for _ in range(batch_size)]
+        mbs = coll.collate_indices(ds, idx)
+        for mb in mbs:
+            for k, v in list(mb.items()):
+                if isinstance(v, torch.Tensor):
+                    mb[k] = v.pin_memory()
+        batches.append((mbs, int(ds.lengths[idx].sum())))
+
+    def sync():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, first):
+        for i in range(args.warmup):
+            step_fn(batches[first + i][0])
+        sync()
+        clocks = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+        if clocks:
+            clocks.start()
+        l0 = getattr(ops, "launches", 0)
+        t0 = time.time()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        toks = 0
+        for i in range(args.steps):
+            mbs, ntok = batches[first + args.warmup + i]
+            step_fn(mbs)
+            toks += ntok
+        e1.record()
+        sync()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return {"ms": ms.item(), "tokens": toks, "wall_s": time.time() - t0,
+                "clocks": clocks.stop() if clocks else None, "launches": getattr(ops, "launches", 0) - l0}
+
+    # (1) device-resident inputs: batches are moved to the GPU before the timed region
+    resident = {}
+
+    def step_resident(mbs):
+        key = id(mbs)
+        if key not in resident:
+            resident[key] = [(D.make_packed_batch(mb, device), 1.0 / max(1, mb["batch_num_loss_counted_tokens"])) for mb in mbs]
+        for pb, scale in resident[key]:
+            eng.forward_backward(pb, scale)
+        eng.optimizer_step(sched.current())
+        sched.step()
+
+    for i in range(args.steps + args.warmup):   # stage every batch of this phase on the device first
+        mbs = batches[i][0]
+        resident[id(mbs)] = [(D.make_packed_batch(mb, device), 1.0 / max(1, mb["batch_num_loss_counted_tokens"])) for mb in mbs]
+    r1 = timed(step_resident, 0)
+    resident.clear()
+
+    # (2) end to end through the public step API: pinned host -> device copies and the loss read-back
+    h2d = d2h = 0
+
+    def step_e2e(mbs):
+        nonlocal h2d, d2h
+        out = eng.train_step(mbs, sched.current())
+        sched.step()
+        host = torch.stack([out["loss_sum"], out["grad_norm"].reshape(())]).cpu()   # device -> host read of the result
+        d2h = host.numel() * host.element_size()
+        h2d = sum(sum(v.numel() * v.element_size() for v in (mb["input_ids"], mb["labels"], mb["position_ids"], mb["cu_seqlens"]))
+                  for mb in mbs)
+        return host
+
+    r2 = timed(step_e2e, args.steps + args.warmup)
+    if hasattr(ops, "check_status"):
+        ops.check_status()
+    if getattr(ops, "profile", None) is not None and rank == 0:
+        print("per-op device ms (all phases):", json.dumps({k: round(v, 1) for k, v in ops.profile_summary().items()}), file=sys.stderr)
+
+    tps = r1["tokens"] / (r1["ms"] / 1e3)
+    tps_e2e = r2["tokens"] / (r2["ms"] / 1e3)
+    peak_gb = torch.cuda.max_memory_allocated(device) / 1e9
+    result = {
+        "metric": "train tokens/sec, Llama-3.1-8B-architecture full SFT (device-timed, max over ranks)",
+        "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": r1["ms"] / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": (tps / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
+        "dtype": "bf16", "data": "synthetic (random-init weights, lognormal(7.5,1.0) lengths clipped to [64,65536], uniform token ids, -100 prefix masks)",
+        "impl": "native",
+        "config": {"model": args.model, "global_batch": batch_size, "seq_len": f"packed, max_tokens_per_gpu={max_tokens}",
+                   "parallelism": f"fsdp{world}" if world > 1 else "single", "comm": comm.name,
+                   "activation_checkpointing": "per block", "optimizer": "AdamW fp32 master, moments " + str(sdt).split(".")[-1],
+                   "attention": getattr(ops, "attention_impl", "torch"),
+                   "l2": "inputs larger than L2 (activations of tens of thousands of tokens per layer); no explicit flush",
+                   "tokens_per_step": r1["tokens"] / args.steps, "peak_mem_gb": round(peak_gb, 1)},
+        "clocks": r1["clocks"],
+        "e2e": {"value": tps_e2e, "unit": "tokens/s", "ms_per_step": r2["ms"] / args.steps,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "clocks": r2["clocks"]},
+        "gpu_launches": r1["launches"],
+    }
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    return result
+
+
+# ------------------------------------------------------------------------------------------
+# the unmodified reference (baseline/_ref): FSDP2 + flash-attn 2 + Liger through its own API
+# ------------------------------------------------------------------------------------------
+def run_reference(args) -> None:
+    from baseline.run_reference import main as ref_main
+    ref_main(args)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--model", default=MODEL)
+    ap.add_argument("--comm", default="auto")
+    ap.add_argument("--state-dtype", default="auto", choices=["auto", "fp32", "bf16"])
+    ap.add_argument("--batch-size", type=int, default=0)
+    ap.add_argument("--max-tokens-per-gpu", type=int, default=0)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        print("note: fewer than 3 warm-up steps requested; results are not a valid measurement", file=sys.stderr)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

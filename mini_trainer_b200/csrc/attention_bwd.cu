@@ -1,0 +1,330 @@
+// Varlen causal GQA attention backward for sm_100a.
+//
+// One CTA owns one (sequence, 128-key block, kv head): K and V of that block stay in shared memory
+// and dK, dV accumulate in tensor memory over every query head of the GQA group and every query
+// block at or below the causal diagonal, so they are written once, without atomics. Per
+// (query head, query block) the CTA runs five tcgen05 GEMMs:
+//   S  = Q K^T            dP = dO V^T                      (TMEM, 128 columns each)
+//   P  = exp(S*scale - lse), dS = P * (dP - delta) * scale  (4 warps; bf16 P and dS to smem)
+//   dQ = dS K  (into S's TMEM columns)   dV += P^T dO   dK += dS^T Q
+// dQ tiles are added into an fp32 [T, Hq*D] accumulator with vector atomics (several key blocks
+// contribute to one query block) and rounded to bf16 by a small kernel afterwards.
+// P and dS are stored once as [query, key] 128B-swizzled tiles and read both K-major (for dQ) and
+// MN-major (for dV / dK), so no transposes are materialised.
+//
+// Rows past the end of the sequence (queries or keys) are masked to zero contribution.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace mtb {
+
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
+
+constexpr int AB_B = 128;          // block edge (queries and keys)
+constexpr int AB_THREADS = 192;
+
+template <int D>
+struct AttBwdSmem {
+  static constexpr int TILE = AB_B * D * 2;         // a [128, D] bf16 tile
+  static constexpr int PT = AB_B * AB_B * 2;        // a [128, 128] bf16 tile
+  static constexpr int OFF_K = 0, OFF_V = TILE, OFF_Q = 2 * TILE, OFF_DO = 3 * TILE;
+  static constexpr int OFF_P = 4 * TILE, OFF_DS = OFF_P + PT;
+  static constexpr int OFF_BAR = OFF_DS + PT;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+struct AttBwdParams {
+  __nv_bfloat16* dqkv;
+  long long ldq;
+  const float* lse;
+  const float* delta;
+  float* dq_acc;        // [T, Hq*D] fp32, zero-initialised
+  const int* plan;      // [n_items, 3] = seq_start, seq_len, k0
+  int T, Hq, Hkv;
+  float scale;
+  int* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(AB_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do, AttBwdParams p) {
+  using L = AttBwdSmem<D>;
+  constexpr int KB = D / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* kv_full = bars;        // K and V resident
+  uint64_t* qdo_full = bars + 1;   // Q_i, dO_i landed
+  uint64_t* sdp_full = bars + 2;   // S and dP complete
+  uint64_t* pds_ready = bars + 3;  // P and dS written (4 arrivals)
+  uint64_t* dq_full = bars + 4;    // dQ tile complete
+  uint64_t* mma_done = bars + 5;   // dV / dK updates complete: Q, dO, P, dS reusable
+  uint64_t* dq_read = bars + 6;    // dQ tile drained (4 arrivals): S columns reusable
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int item = blockIdx.x / p.Hkv, hk = blockIdx.x % p.Hkv;
+  const int G = p.Hq / p.Hkv;
+  const int seq_start = p.plan[item * 3 + 0], seq_len = p.plan[item * 3 + 1], k0 = p.plan[item * 3 + 2];
+  const int jblk = k0 / AB_B;
+  const int nq = (seq_len + AB_B - 1) / AB_B;      // query blocks of the sequence
+  const int per_head = nq - jblk;                  // query blocks at or below the diagonal
+  const int n_iters = G * per_head;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(sdp_full, 1); mbar_init(pds_ready, 4);
+    mbar_init(dq_full, 1); mbar_init(mma_done, 1); mbar_init(dq_read, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_qkv);
+    tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 256 + D;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_arrive_expect_tx(kv_full, 2 * L::TILE);
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb) {
+        tma_load_2d(smem + L::OFF_K + kb * 16384, &tm_qkv, kv_full, (p.Hq + hk) * D + kb * 64, seq_start + k0);
+        tma_load_2d(smem + L::OFF_V + kb * 16384, &tm_qkv, kv_full, (p.Hq + p.Hkv + hk) * D + kb * 64, seq_start + k0);
+      }
+      for (int it = 0; it < n_iters; ++it) {
+        const int h = hk * G + it / per_head, i = jblk + it % per_head;
+        if (it > 0 && !mbar_wait(mma_done, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 21); goto done; }
+        mbar_arrive_expect_tx(qdo_full, 2 * L::TILE);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_2d(smem + L::OFF_Q + kb * 16384, &tm_qkv, qdo_full, h * D + kb * 64, seq_start + i * AB_B);
+          tma_load_2d(smem + L::OFF_DO + kb * 16384, &tm_do, qdo_full, h * D + kb * 64, seq_start + i * AB_B);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t id_nt = make_idesc_bf16(AB_B, AB_B, false, false);   // S, dP
+      constexpr uint32_t id_dq = make_idesc_bf16(AB_B, D, false, true);       // dQ = dS K
+      constexpr uint32_t id_tn = make_idesc_bf16(AB_B, D, true, true);        // dV, dK
+      const uint32_t sk = smem_u32(smem + L::OFF_K), sv = smem_u32(smem + L::OFF_V), sq = smem_u32(smem + L::OFF_Q);
+      const uint32_t sdo = smem_u32(smem + L::OFF_DO), spp = smem_u32(smem + L::OFF_P), sds = smem_u32(smem + L::OFF_DS);
+      if (!mbar_wait(kv_full, 0, abort_flag)) { atomicExch(p.status, 22); goto done; }
+      for (int it = 0; it < n_iters; ++it) {
+        if (!mbar_wait(qdo_full, it & 1, abort_flag)) { atomicExch(p.status, 23); goto done; }
+        if (it > 0 && !mbar_wait(dq_read, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 24); goto done; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16(t_s, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), id_nt, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16(t_dp, make_smem_desc(sdo + off, 16, 1024), make_smem_desc(sv + off, 16, 1024), id_nt, k != 0);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_ready, it & 1, abort_flag)) { atomicExch(p.status, 25); goto done; }
+        tc_fence_after();
+        // dQ = dS K  (A K-major over keys, B = K tile read MN-major)
+#pragma unroll
+        for (int k = 0; k < AB_B / 16; ++k)
+          umma_bf16(t_s, make_smem_desc(sds + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), make_smem_desc(sk + k * 2048, 16384, 1024), id_dq, k != 0);
+        umma_commit(dq_full);
+        // dV += P^T dO ; dK += dS^T Q  (A = [query, key] tile read MN-major, B = [query, D] tile read MN-major)
+#pragma unroll
+        for (int k = 0; k < AB_B / 16; ++k)
+          umma_bf16(t_dv, make_smem_desc(spp + k * 2048, 16384, 1024), make_smem_desc(sdo + k * 2048, 16384, 1024), id_tn, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < AB_B / 16; ++k)
+          umma_bf16(t_dk, make_smem_desc(sds + k * 2048, 16384, 1024), make_smem_desc(sq + k * 2048, 16384, 1024), id_tn, (it | k) != 0);
+        umma_commit(mma_done);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const int HqD = p.Hq * D;
+    for (int it = 0; it < n_iters; ++it) {
+      const int h = hk * G + it / per_head, i = jblk + it % per_head;
+      const int qpos = i * AB_B + r;
+      const bool qok = qpos < seq_len;
+      const long long tok = static_cast<long long>(seq_start) + qpos;
+      const float lse2 = qok ? p.lse[static_cast<long long>(h) * p.T + tok] * 1.4426950408889634f : 0.f;
+      const float delta = qok ? p.delta[static_cast<long long>(h) * p.T + tok] : 0.f;
+      if (!mbar_wait(sdp_full, it & 1, abort_flag)) { atomicExch(p.status, 26); goto done; }
+      if (it > 0 && !mbar_wait(mma_done, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 27); goto done; }
+      tc_fence_after();
+      const bool need_mask = (i == jblk) || (k0 + AB_B > seq_len);
+#pragma unroll 1
+      for (int c = 0; c < AB_B / 32; ++c) {
+        uint32_t sv_[32], dv_[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, sv_);
+        tmem_ld_32x32(t_dp + lane_addr + c * 32, dv_);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kpos = k0 + c * 32 + x + u;
+            float pe = exp2f(__uint_as_float(sv_[x + u]) * sl2 - lse2);
+            if (!qok || (need_mask && (kpos > qpos || kpos >= seq_len))) pe = 0.f;
+            pv[u] = pe;
+            dsv[u] = pe * (__uint_as_float(dv_[x + u]) - delta) * p.scale;
+          }
+          pk[x >> 1] = pack_bf16(pv[0], pv[1]);
+          dk[x >> 1] = pack_bf16(dsv[0], dsv[1]);
+        }
+        const int rowoff = (c >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (((c & 1) * 4 + g) ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(smem + L::OFF_P + rowoff + chunk) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+          *reinterpret_cast<uint4*>(smem + L::OFF_DS + rowoff + chunk) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_ready);
+      // drain dQ
+      if (!mbar_wait(dq_full, it & 1, abort_flag)) { atomicExch(p.status, 28); goto done; }
+      tc_fence_after();
+      float* dst = p.dq_acc + tok * HqD + h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        if (qok) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 4)
+            atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + x),
+                      make_float4(__uint_as_float(v[x]), __uint_as_float(v[x + 1]), __uint_as_float(v[x + 2]), __uint_as_float(v[x + 3])));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_read);
+    }
+    // epilogue: dK, dV (rows = keys)
+    if (n_iters > 0) {
+      if (!mbar_wait(mma_done, (n_iters - 1) & 1, abort_flag)) { atomicExch(p.status, 29); goto done; }
+      tc_fence_after();
+      const int kpos = k0 + r;
+      const bool ok = kpos < seq_len;
+      __nv_bfloat16* rowp = p.dqkv + (static_cast<long long>(seq_start) + kpos) * p.ldq;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t src = (which == 0 ? t_dk : t_dv) + lane_addr;
+        __nv_bfloat16* o = rowp + (which == 0 ? (p.Hq + hk) * D : (p.Hq + p.Hkv + hk) * D);
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(src + c * 32, v);
+          tmem_ld_wait();
+          if (ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              *reinterpret_cast<uint4*>(o + c * 32 + g * 8) =
+                  make_uint4(pack_bf16(__uint_as_float(v[g * 8]), __uint_as_float(v[g * 8 + 1])),
+                             pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3])),
+                             pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5])),
+                             pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7])));
+          }
+        }
+      }
+    }
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h).
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long ldo, const __nv_bfloat16* __restrict__ dout,
+                                                        long long lddo, float* __restrict__ delta, int T, int Hq, int D) {
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= static_cast<long long>(T) * Hq) return;
+  const int t = static_cast<int>(w / Hq), h = static_cast<int>(w % Hq);
+  const __nv_bfloat16* a = o + static_cast<long long>(t) * ldo + h * D;
+  const __nv_bfloat16* b = dout + static_cast<long long>(t) * lddo + h * D;
+  float s = 0.f;
+  for (int c = lane * 2; c < D; c += 64) {
+    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a + c));
+    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(b + c));
+    s += x.x * y.x + x.y * y.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[static_cast<long long>(h) * T + t] = s;
+}
+
+// dqkv[t, 0:Hq*D] = bf16(dq_acc[t, :])
+__global__ void __launch_bounds__(256) attn_dq_store_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dqkv, long long ldq,
+                                                           long long T, int HqD) {
+  const int vpr = HqD >> 3;
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= T * vpr) return;
+  const long long t = gid / vpr;
+  const int c = static_cast<int>(gid % vpr) * 8;
+  const float4 a = *reinterpret_cast<const float4*>(acc + t * HqD + c), b = *reinterpret_cast<const float4*>(acc + t * HqD + c + 4);
+  *reinterpret_cast<uint4*>(dqkv + t * ldq + c) =
+      make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+}
+
+template <int D>
+static int launch_bwd(const CUtensorMap& a, const CUtensorMap& b, const AttBwdParams& p, int n_items, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = attn_bwd_kernel<D>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttBwdSmem<D>::TOTAL) != cudaSuccess) return -4;
+    configured = true;
+  }
+  kern<<<n_items * p.Hkv, AB_THREADS, AttBwdSmem<D>::TOTAL, st>>>(a, b, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace mtb
+
+// plan: key-block work table [n_items, 3] = (seq_start, seq_len, k0), most work first.
+// dq_acc: zero-initialised fp32 [T, Hq*D] scratch; delta: fp32 [Hq, T] scratch.
+extern "C" int mtb200_attn_bwd(const void* qkv, long long ld, const void* out, long long ldo, const void* dout, long long lddo,
+                               void* dqkv, long long ldq, const float* lse, float* delta, float* dq_acc, const int* plan,
+                               int n_items, int T, int Hq, int Hkv, int D, int reserved, float scale, int* status, cudaStream_t st) {
+  using namespace mtb;
+  if (n_items <= 0 || T <= 0) return 0;
+  if ((D != 64 && D != 128) || Hq % Hkv || ld % 8 || ldo % 8 || lddo % 8 || ldq % 8) return -10;
+  CUtensorMap tq, tdo;
+  int rc = make_tmap_2d_bf16(&tq, qkv, static_cast<uint64_t>(ld), static_cast<uint64_t>(T), static_cast<uint64_t>(ld), 64, 128);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tdo, dout, static_cast<uint64_t>(Hq) * D, static_cast<uint64_t>(T), static_cast<uint64_t>(lddo), 64, 128);
+  if (rc) return rc - 10;
+  const long long warps = static_cast<long long>(T) * Hq;
+  attn_delta_kernel<<<static_cast<int>((warps * 32 + 255) / 256), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(out), ldo, reinterpret_cast<const __nv_bfloat16*>(dout), lddo, delta, T, Hq, D);
+  AttBwdParams p{reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, lse, delta, dq_acc, plan, T, Hq, Hkv, scale, status};
+  rc = D == 128 ? launch_bwd<128>(tq, tdo, p, n_items, st) : launch_bwd<64>(tq, tdo, p, n_items, st);
+  if (rc) return rc;
+  const long long n = static_cast<long long>(T) * (Hq * D / 8);
+  attn_dq_store_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, T, Hq * D);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

@@ -1,0 +1,295 @@
+// Varlen causal GQA attention forward for sm_100a.
+//
+// One CTA handles one (sequence, 128-row query block, query head). Q, K and V are read straight
+// out of the fused qkv activation [T, (Hq + 2 Hkv) * D] through ONE tensor map (128B swizzle):
+//   S = Q K^T      tcgen05.mma, M=128 queries, N=128 keys, K=D      (accumulator in TMEM, 2 buffers)
+//   P = softmax    4 warps, one query row per thread, reads S from TMEM, writes bf16 P to smem
+//   O += P V       tcgen05.mma, M=128, N=D, K=128 keys               (accumulator in TMEM)
+// Roles: warp 0 = TMA (K/V double-buffered), warp 1 = MMA issue, warps 2-5 = softmax + epilogue.
+// S is double-buffered so that Q K^T of tile j+1 runs under the softmax of tile j.
+//
+// The softmax keeps a per-row reference maximum and only rescales O when the running maximum
+// grew by more than 2^8 (exact: the final division by the row sum uses the same reference), so
+// the TMEM round trip for the rescale is rare. Only the last key tile of a query block touches
+// the causal diagonal / the end of the sequence and is masked.
+//
+// Outputs: out [T, Hq*D] bf16 and lse [Hq, T] fp32 (natural log, scaled scores), as needed by
+// the backward. Sequence boundaries come from a host-built work table (seq_start, seq_len, q0),
+// so there is no device-side search in cu_seqlens.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace mtb {
+
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
+
+constexpr int ATT_BM = 128, ATT_BN = 128;
+constexpr int ATT_THREADS = 192;
+
+template <int D>
+struct AttFwdSmem {
+  static constexpr int Q_BYTES = ATT_BM * D * 2;
+  static constexpr int KV_BYTES = ATT_BN * D * 2;
+  static constexpr int P_BYTES = ATT_BM * ATT_BN * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;        // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;   // 2 stages
+  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+struct AttFwdParams {
+  __nv_bfloat16* out;
+  long long ldo;
+  float* lse;
+  const int* plan;   // [n_items, 3] = seq_start, seq_len, q0
+  int T, Hq, Hkv;
+  float scale;
+  int* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, AttFwdParams p) {
+  using L = AttFwdSmem<D>;
+  constexpr int KB = D / 64;  // 64-element (128 B) column blocks of a D-wide row
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* k_full = bars + 1;        // 2
+  uint64_t* v_full = bars + 3;        // 2
+  uint64_t* kv_empty = bars + 5;      // 2
+  uint64_t* s_full = bars + 7;        // 2
+  uint64_t* p_ready = bars + 9;       // 1
+  uint64_t* p_empty = bars + 10;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int item = blockIdx.x / p.Hq, h = blockIdx.x % p.Hq;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int seq_start = p.plan[item * 3 + 0], seq_len = p.plan[item * 3 + 1], q0 = p.plan[item * 3 + 2];
+  const int n_tiles = q0 / ATT_BN + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&s_full[i], 1); }
+    mbar_init(p_ready, 4);
+    mbar_init(p_empty, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_arrive_expect_tx(q_full, L::Q_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb) tma_load_2d(smem + L::OFF_Q + kb * 16384, &tmap, q_full, h * D + kb * 64, seq_start + q0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) { atomicExch(p.status, 11); goto done; }
+        const int row = seq_start + j * ATT_BN;
+        mbar_arrive_expect_tx(&k_full[s], L::KV_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_2d(smem + L::OFF_K + s * L::KV_BYTES + kb * 16384, &tmap, &k_full[s], (p.Hq + hk) * D + kb * 64, row);
+        mbar_arrive_expect_tx(&v_full[s], L::KV_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_2d(smem + L::OFF_V + s * L::KV_BYTES + kb * 16384, &tmap, &v_full[s], (p.Hq + p.Hkv + hk) * D + kb * 64, row);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(ATT_BM, ATT_BN, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BM, D, false, true);
+      const uint32_t sq = smem_u32(smem + L::OFF_Q), sp = smem_u32(smem + L::OFF_P);
+      auto issue_qk = [&](int j) {
+        const uint32_t sk = smem_u32(smem + L::OFF_K + (j & 1) * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16(tmem_s0 + (j & 1) * ATT_BN, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), idesc_qk, k != 0);
+        }
+        umma_commit(&s_full[j & 1]);
+      };
+      if (!mbar_wait(q_full, 0, abort_flag)) { atomicExch(p.status, 12); goto done; }
+      if (!mbar_wait(&k_full[0], 0, abort_flag)) { atomicExch(p.status, 13); goto done; }
+      tc_fence_after();
+      issue_qk(0);
+      for (int j = 0; j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) {
+          if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { atomicExch(p.status, 14); goto done; }
+          tc_fence_after();
+          issue_qk(j + 1);
+        }
+        if (!mbar_wait(p_ready, j & 1, abort_flag)) { atomicExch(p.status, 15); goto done; }
+        if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag)) { atomicExch(p.status, 16); goto done; }
+        tc_fence_after();
+        const uint32_t sv = smem_u32(smem + L::OFF_V + (j & 1) * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < ATT_BN / 16; ++k) {
+          const uint64_t da = make_smem_desc(sp + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc(sv + k * 2048, 16384, 1024);
+          umma_bf16(tmem_o, da, db, idesc_pv, (j | k) != 0);
+        }
+        umma_commit(&kv_empty[j & 1]);
+        umma_commit(p_empty);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue
+    const int q = warp & 3;
+    const int r = q * 32 + lane;              // row inside the query block
+    const int qpos = q0 + r;                  // position inside the sequence
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    float m_ref = -INFINITY, l = 0.f;
+    uint8_t* sp = smem + L::OFF_P;
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag)) { atomicExch(p.status, 17); goto done; }
+      tc_fence_after();
+      const uint32_t ts = tmem_s0 + (j & 1) * ATT_BN + lane_addr;
+      const bool diag = (j == n_tiles - 1);
+      const int kbase = j * ATT_BN;
+      // pass 1: row maximum
+      float mt = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < ATT_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(ts + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (diag && (kbase + c * 32 + i > qpos)) s = -INFINITY;
+          mt = fmaxf(mt, s);
+        }
+      }
+      float factor = 1.f;
+      bool rescale = false;
+      if (mt > m_ref && (mt - m_ref) * sl2 > 8.f) {   // includes the first tile (m_ref = -inf)
+        factor = (m_ref == -INFINITY) ? 0.f : exp2f((m_ref - mt) * sl2);
+        m_ref = mt;
+        l *= factor;
+        rescale = (j > 0);
+      }
+      if (j > 0) {
+        if (!mbar_wait(p_empty, (j - 1) & 1, abort_flag)) { atomicExch(p.status, 18); goto done; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
+            tmem_st_32x32(tmem_o + lane_addr + c * 32, v);
+          }
+          tmem_st_wait();
+        }
+      }
+      // pass 2: probabilities -> bf16 P in shared memory (K-major, 128B swizzle), row sums
+      const float mo = m_ref * sl2;
+#pragma unroll 1
+      for (int c = 0; c < ATT_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(ts + c * 32, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = exp2f(__uint_as_float(v[i]) * sl2 - mo);
+          if (diag && (kbase + c * 32 + i > qpos)) e = 0.f;
+          pr[i] = e;
+          l += e;
+        }
+        uint8_t* rowp = sp + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (c & 1) * 4 + g;
+          uint4 o;
+          o.x = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]); o.y = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
+          o.z = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]); o.w = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = o;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+    }
+    // epilogue: O / l -> out, lse
+    if (!mbar_wait(p_empty, (n_tiles - 1) & 1, abort_flag)) { atomicExch(p.status, 19); goto done; }
+    tc_fence_after();
+    const bool ok = qpos < seq_len;
+    const float inv = 1.f / l;
+    const long long tok = static_cast<long long>(seq_start) + qpos;
+    __nv_bfloat16* orow = p.out + tok * p.ldo + h * D;
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t v[32];
+      tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+      tmem_ld_wait();
+      if (ok) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 o;
+          o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+          o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+          o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+          o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
+        }
+      }
+    }
+    if (ok) p.lse[static_cast<long long>(h) * p.T + tok] = m_ref * p.scale + logf(l);
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+static int launch_fwd(const CUtensorMap& tm, const AttFwdParams& p, int n_items, cudaStream_t st) {
+  static bool configured = false;
+  auto kern = attn_fwd_kernel<D>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttFwdSmem<D>::TOTAL) != cudaSuccess) return -4;
+    configured = true;
+  }
+  kern<<<n_items * p.Hq, ATT_THREADS, AttFwdSmem<D>::TOTAL, st>>>(tm, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace mtb
+
+extern "C" int mtb200_attn_fwd(const void* qkv, long long ld, void* out, long long ldo, float* lse, const int* plan, int n_items,
+                               int T, int Hq, int Hkv, int D, int reserved, float scale, int* status, cudaStream_t st) {
+  using namespace mtb;
+  if (n_items <= 0 || T <= 0) return 0;
+  if ((D != 64 && D != 128) || Hq % Hkv || ld % 8 || ldo % 8) return -10;
+  CUtensorMap tm;
+  const int rc = make_tmap_2d_bf16(&tm, qkv, static_cast<uint64_t>(ld), static_cast<uint64_t>(T), static_cast<uint64_t>(ld), 64, 128);
+  if (rc) return rc;
+  AttFwdParams p{reinterpret_cast<__nv_bfloat16*>(out), ldo, lse, plan, T, Hq, Hkv, scale, status};
+  return D == 128 ? launch_fwd<128>(tm, p, n_items, st) : launch_fwd<64>(tm, p, n_items, st);
+}

@@ -77,6 +77,7 @@ class NativeOps:
         self.attention_impl = attention or os.environ.get("MTB200_ATTENTION", "native")
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
+        self.profile = [] if os.environ.get("MTB200_PROFILE") else None
         self._scratch = {}
         self._attn_plan_cache = {}
 
@@ -84,11 +85,26 @@ class NativeOps:
     def _st(self):
         return torch.cuda.current_stream(self.device).cuda_stream
 
-    def _call(self, name, *args, n=1):
+    def _call(self, name, *args, n=1, tag=None):
+        if self.profile is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
         rc = getattr(self.lib, name)(*args)
         if rc != 0:
             raise RuntimeError(f"{name} failed with code {rc}")
         self.launches += n
+        if self.profile is not None:
+            e1.record()
+            self.profile.append((tag or name, e0, e1))
+
+    def profile_summary(self) -> dict:
+        """Device time per op (ms) since profiling was switched on (``MTB200_PROFILE=1``)."""
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for name, e0, e1 in self.profile or []:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        self.profile = [] if self.profile is not None else None
+        return dict(sorted(out.items(), key=lambda kv: -kv[1]))
 
     def _buf(self, key, numel, dtype):
         b = self._scratch.get(key)
@@ -96,6 +112,19 @@ class NativeOps:
             b = torch.empty(numel, dtype=dtype, device=self.device)
             self._scratch[key] = b
         return b[:numel]
+
+    def _ev(self):
+        if self.profile is None:
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def _ev_end(self, name, e0):
+        if e0 is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            self.profile.append((name, e0, e1))
 
     def check_status(self):
         """Raises if any kernel recorded an expired bounded wait (one host sync)."""
@@ -105,7 +134,7 @@ class NativeOps:
             raise RuntimeError(f"a device-side bounded wait expired (code {code})")
 
     # -- GEMM -------------------------------------------------------------------------
-    def gemm(self, a, a_mn, b, b_mn, out, M, N, K, residual=None, bias=None):
+    def gemm(self, a, a_mn, b, b_mn, out, M, N, K, residual=None, bias=None, tag=None):
         """out[M,N] = A*B (+bias) (+residual). ``a_mn``/``b_mn``: operand stored [K, rows]."""
         out_f32 = out.dtype == torch.float32
         assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
@@ -113,7 +142,7 @@ class NativeOps:
         self._call("mtb200_gemm_bf16", a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
                    out.data_ptr(), out.stride(0), int(out_f32), _ptr(residual),
                    residual.stride(0) if residual is not None else 0, _ptr(bias), M, N, K,
-                   self.status.data_ptr(), self._st())
+                   self.status.data_ptr(), self._st(), tag=tag or f"gemm_{'t' if a_mn else 'n'}{'n' if b_mn else 't'}")
         return out
 
     # -- embedding --------------------------------------------------------------------
@@ -174,20 +203,26 @@ class NativeOps:
         return qkv
 
     # -- attention --------------------------------------------------------------------
-    def _attn_plan(self, cu_host, block_m):
-        """Work table for the attention kernels: one row (seq_start, seq_len, q0) per 128-row query
-        block, longest causal span first. Built once per minibatch and reused by every layer."""
-        key = (id(cu_host), block_m)
+    def _attn_plan(self, cu_host, block, most_work_last_block: bool):
+        """Work table for the attention kernels: one row (seq_start, seq_len, block_start) per
+        128-row block of every sequence, most work first (forward: late query blocks see the most
+        keys; backward: early key blocks are seen by the most queries). Built once per minibatch
+        and reused by every layer."""
+        key = (id(cu_host), block, most_work_last_block)
         hit = self._attn_plan_cache.get(key)
         if hit is not None and hit[0] is cu_host:
             return hit[1]
         items = []
         for a, b in zip(cu_host[:-1], cu_host[1:]):
-            for q0 in range(0, b - a, block_m):
-                items.append((a, b - a, q0))
-        items.sort(key=lambda it: -it[2])
-        table = torch.tensor(items, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
-        self._attn_plan_cache = {key: (cu_host, table)}
+            n = b - a
+            for s0 in range(0, n, block):
+                work = s0 if most_work_last_block else n - s0
+                items.append((work, a, n, s0))
+        items.sort(key=lambda it: -it[0])
+        table = torch.tensor([it[1:] for it in items], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        if len(self._attn_plan_cache) > 8:
+            self._attn_plan_cache.clear()
+        self._attn_plan_cache[key] = (cu_host, table)
         return table
 
     def attention(self, qkv, cu_seqlens, cu_host, max_seqlen, hq, hkv, d):
@@ -196,7 +231,7 @@ class NativeOps:
             return self._fa_fwd(qkv, cu_seqlens, max_seqlen, hq, hkv, d)
         out = torch.empty(T, hq * d, dtype=qkv.dtype, device=self.device)
         lse = torch.empty(hq, T, dtype=torch.float32, device=self.device)
-        plan = self._attn_plan(cu_host, 128)
+        plan = self._attn_plan(cu_host, 128, True)
         self._call("mtb200_attn_fwd", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), lse.data_ptr(),
                    plan.data_ptr(), plan.shape[0], T, hq, hkv, d, 0, d ** -0.5, self.status.data_ptr(), self._st())
         return out, lse
@@ -206,7 +241,7 @@ class NativeOps:
         if self.attention_impl == "flash_attn":
             return self._fa_bwd(dout, qkv, out, lse, cu_seqlens, max_seqlen, hq, hkv, d)
         dqkv = torch.empty_like(qkv)
-        plan = self._attn_plan(cu_host, 128)
+        plan = self._attn_plan(cu_host, 128, False)
         delta = torch.empty(hq, T, dtype=torch.float32, device=self.device)
         dq_acc = torch.zeros(T, hq * d, dtype=torch.float32, device=self.device)
         self._call("mtb200_attn_bwd", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), dout.data_ptr(),
@@ -221,7 +256,9 @@ class NativeOps:
         q = qkv[:, : hq * d].view(T, hq, d)
         k = qkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
         v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        ev = self._ev()
         out, lse, _, _ = _flash_attn_varlen_forward(q, k, v, cu, cu, max_seqlen, max_seqlen, 0.0, d ** -0.5, causal=True)
+        self._ev_end("flash_attn_fwd", ev)
         return out.reshape(T, hq * d), lse
 
     def _fa_bwd(self, dout, qkv, out, lse, cu, max_seqlen, hq, hkv, d):
@@ -234,8 +271,10 @@ class NativeOps:
         dq = dqkv[:, : hq * d].view(T, hq, d)
         dk = dqkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
         dv = dqkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        ev = self._ev()
         _flash_attn_varlen_backward(dout.view(T, hq, d), q, k, v, out.view(T, hq, d), lse, dq, dk, dv, cu, cu,
                                     max_seqlen, max_seqlen, 0.0, d ** -0.5, True, -1, -1, 0.0, None, False)
+        self._ev_end("flash_attn_bwd", ev)
         return dqkv
 
     # -- swiglu -----------------------------------------------------------------------

@@ -185,3 +185,45 @@ def test_optimizer_kernels(ops):
     assert torch.allclose(acc, ref)
     ops.accumulate(acc, src, False)
     assert torch.equal(acc, src.float())
+
+
+ATTN_CASES = [(128, 4, 1, [300, 17, 129, 1, 640]), (64, 4, 2, [128, 256, 5]), (128, 8, 2, [1000]), (128, 4, 4, [127, 128, 129])]
+
+
+@pytest.mark.parametrize("D,hq,hkv,lens", ATTN_CASES)
+def test_attention_forward(ops, D, hq, hkv, lens):
+    torch.manual_seed(sum(lens))
+    T = sum(lens)
+    qkv = bf(T, (hq + 2 * hkv) * D)
+    cu_host = [0]
+    for n in lens:
+        cu_host.append(cu_host[-1] + n)
+    cu = torch.tensor(cu_host, dtype=torch.int32, device="cuda")
+    out, lse = ops.attention(qkv, cu, cu_host, max(lens), hq, hkv, D)
+    ro, rl = REF.attention(qkv.float(), cu, cu_host, max(lens), hq, hkv, D)
+    ops.check_status()
+    assert rel_err(lse, rl) < 2e-3
+    assert rel_err(out, ro) < 1e-2
+
+
+@pytest.mark.parametrize("D,hq,hkv,lens", ATTN_CASES)
+def test_attention_backward(ops, D, hq, hkv, lens):
+    if not hasattr(ops.lib, "mtb200_attn_bwd"):
+        pytest.skip("attention backward kernel not built")
+    torch.manual_seed(1 + sum(lens))
+    T = sum(lens)
+    qkv = bf(T, (hq + 2 * hkv) * D)
+    dout = bf(T, hq * D)
+    cu_host = [0]
+    for n in lens:
+        cu_host.append(cu_host[-1] + n)
+    cu = torch.tensor(cu_host, dtype=torch.int32, device="cuda")
+    out, lse = ops.attention(qkv, cu, cu_host, max(lens), hq, hkv, D)
+    dqkv = ops.attention_bwd(dout, qkv, out, lse, cu, cu_host, max(lens), hq, hkv, D)
+    ro, rl = REF.attention(qkv.float(), cu, cu_host, max(lens), hq, hkv, D)
+    rd = REF.attention_bwd(dout.float(), qkv.float(), ro, rl, cu, cu_host, max(lens), hq, hkv, D)
+    ops.check_status()
+    q_end, k_end = hq * D, (hq + hkv) * D
+    assert rel_err(dqkv[:, :q_end], rd[:, :q_end]) < 2e-2
+    assert rel_err(dqkv[:, q_end:k_end], rd[:, q_end:k_end]) < 2e-2
+    assert rel_err(dqkv[:, k_end:], rd[:, k_end:]) < 2e-2
