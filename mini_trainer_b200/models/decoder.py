@@ -74,21 +74,29 @@ class BlockActs:
     act: torch.Tensor
 
 
-def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: PackedBatch, inv_freq, keep: bool = False):
-    """Returns the block output, plus ``BlockActs`` when ``keep`` (used by recompute)."""
+def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: PackedBatch, inv_freq, keep: bool = False,
+                  saved_attn=None, want_attn: bool = False):
+    """Returns ``(out, acts, attn_state)``.
+
+    ``acts`` is a ``BlockActs`` when ``keep`` (everything backward reads), else ``None``.
+    ``saved_attn = (attn, lse)`` from an earlier forward skips the attention kernel (used by the
+    recompute of blocks whose attention output was kept); ``want_attn`` returns that pair.
+    """
     n1, rstd1 = ops.rmsnorm(x, p["ln1"], cfg.rms_norm_eps)
     qkv = ops.linear(n1, p["wqkv"], p.get("bqkv"))
     ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
-    attn, lse = ops.attention(qkv, batch.cu_seqlens, batch.cu_seqlens_host, batch.max_seqlen,
-                              cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+    if saved_attn is not None:
+        attn, lse = saved_attn
+    else:
+        attn, lse = ops.attention(qkv, batch.cu_seqlens, batch.cu_seqlens_host, batch.max_seqlen,
+                                  cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
     h1 = ops.linear(attn, p["wo"], None, x)
     n2, rstd2 = ops.rmsnorm(h1, p["ln2"], cfg.rms_norm_eps)
     gu = ops.linear(n2, p["wgu"])
     act = ops.swiglu(gu)
     out = ops.linear(act, p["wd"], None, h1)
-    if keep:
-        return out, BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, gu, act)
-    return out, None
+    acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, gu, act) if keep else None
+    return out, acts, ((attn, lse) if want_attn else None)
 
 
 def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dout: torch.Tensor,
@@ -140,6 +148,6 @@ def forward_logits(ops, cfg: ModelConfig, embed_w, blocks: list, norm_w, lm_w, b
     inv_freq = cfg.rope_inv_freq().to(embed_w.device)
     x = ops.embedding(embed_w, batch.input_ids)
     for p in blocks:
-        x, _ = block_forward(ops, cfg, p, x, batch, inv_freq)
+        x, _, _ = block_forward(ops, cfg, p, x, batch, inv_freq)
     n, _ = ops.rmsnorm(x, norm_w, cfg.rms_norm_eps)
     return n.float() @ lm_w.float().t()

@@ -97,7 +97,7 @@ class _Side:
 
 class ShardedEngine:
     def __init__(self, cfg: ModelConfig, device, ops, comm=None, param_dtype=None, state_dtype=None,
-                 optim: Optional[OptimConfig] = None):
+                 optim: Optional[OptimConfig] = None, activation_budget_bytes: Optional[int] = None):
         self.cfg, self.device, self.ops = cfg, torch.device(device), ops
         self.comm = comm if comm is not None else LocalComm()
         self.world, self.rank = self.comm.world, self.comm.rank
@@ -126,7 +126,8 @@ class ShardedEngine:
         if self.world > 1:
             smax = max(g.layout.shard_numel for g in self.groups)
             self._rs_scratch = torch.empty(smax, dtype=self.param_dtype, device=self.device)
-        self.launch_count = 0
+        # None = derive from free device memory; 0 = recompute every block like the reference
+        self.activation_budget_bytes = activation_budget_bytes
 
     # ------------------------------------------------------------------------------------
     # initialisation / state exchange
@@ -244,6 +245,56 @@ class ShardedEngine:
         return self._gbufs[slot], slot
 
     # ------------------------------------------------------------------------------------
+    # activation checkpointing plan
+    # ------------------------------------------------------------------------------------
+    def plan_checkpointing(self, tokens: int) -> list:
+        """Per-block checkpoint level for a minibatch of ``tokens`` tokens.
+
+        2 = keep only the block input and recompute the whole block in backward (what the reference
+        does for every block, setup_model_for_training.py:28-29); 1 = also keep the attention
+        output and its log-sum-exp so the recompute skips the attention kernel; 0 = keep every
+        intermediate, no recompute. Blocks are upgraded from the last one backwards (their
+        activations are freed first in backward) while the estimated footprint fits in
+        ``activation_budget_bytes``. ``activation_budget_bytes = 0`` gives the reference behaviour.
+        """
+        cfg, nL = self.cfg, len(self.blocks)
+        levels = [2] * nL
+        budget = self.activation_budget_bytes
+        if budget is None:
+            budget = self._auto_activation_budget(tokens)
+        if budget <= 0:
+            return levels
+        es = 2 if self.param_dtype != torch.float32 else 4
+        h, f = cfg.hidden_size, cfg.intermediate_size
+        lvl1 = tokens * (cfg.q_size * es + cfg.num_attention_heads * 4)
+        lvl0 = tokens * ((3 * h + cfg.qkv_size + cfg.q_size + 3 * f) * es + cfg.num_attention_heads * 4 + 8)
+        for i in range(nL - 1, -1, -1):      # cheapest upgrade first: keep attention everywhere it fits
+            if budget >= lvl1:
+                levels[i] = 1
+                budget -= lvl1
+        for i in range(nL - 1, -1, -1):
+            if levels[i] == 1 and budget >= lvl0 - lvl1:
+                levels[i] = 0
+                budget -= lvl0 - lvl1
+        return levels
+
+    def _auto_activation_budget(self, tokens: int) -> int:
+        """Memory that can hold extra saved activations: device capacity minus optimizer/parameter
+        state, the per-block inputs, the working set of one block's backward and the loss buffers."""
+        if self.device.type != "cuda":
+            return 0
+        cfg = self.cfg
+        total = torch.cuda.get_device_properties(self.device).total_memory
+        h, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+        base = tokens * 2 * h * len(self.blocks)
+        work = tokens * 2 * (7 * h + cfg.qkv_size + 6 * f)
+        ce = getattr(self.ops, "ce_chunk", 2048) * v * 6 + v * h * 4
+        root = 4 * v * h * 2
+        bufs = sum(b.numel() * b.element_size() for b in self._pbufs + self._gbufs)
+        used = self.state_bytes() + base + work + ce + root + bufs + (4 << 30)
+        return int(0.93 * total - used)
+
+    # ------------------------------------------------------------------------------------
     # one microbatch
     # ------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -261,13 +312,16 @@ class ShardedEngine:
         if not tied:
             del emb_views, emb_full
         saved = []
+        levels = self.plan_checkpointing(batch.num_tokens)
         nxt = self._gather_block(0)
         for i in range(nL):
             p, ev, slot = nxt
             _Side.wait(ev)
             nxt = self._gather_block(i + 1) if i + 1 < nL else None
-            saved.append(x)
-            x, _ = D.block_forward(ops, cfg, p, x, batch, self.inv_freq)
+            xin = x
+            x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq, keep=levels[i] == 0,
+                                                  want_attn=levels[i] == 1)
+            saved.append((xin, acts, attn_state))
             if i + 1 < nL or self.world == 1:
                 self._release_pbuf(slot)
             last = (p, slot)  # the last block stays gathered for backward (reshard_after_forward=False)
@@ -295,10 +349,11 @@ class ShardedEngine:
             cur = self._gather_block(i - 1) if i > 0 else None
             gbuf, gslot = self._grad_buffer(i)
             g = self.blocks[i].layout.views(gbuf)
-            xin = saved.pop()
-            _, acts = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True)
+            xin, acts, attn_state = saved.pop()
+            if acts is None:   # recompute the block forward (attention is skipped when its output was kept)
+                _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True, saved_attn=attn_state)
             dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq)
-            del acts, xin
+            del acts, xin, attn_state
             self._release_pbuf(slot)
             self._reduce(self.blocks[i], gbuf, gslot)
 
