@@ -529,3 +529,47 @@ int mtb200_adamw(float* master, void* m, void* v, int state_is_f32, const float*
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant of mtb200_colsum (declared in mtb200_noalloc.h).
+//
+// For callers that cannot allocate device memory when they need the kernel: the fp32 partial-sum
+// workspace lives in a file-scope device array. In host code the array's name is only a handle,
+// never a pointer a kernel could dereference, so its device address is looked up once per device
+// with cudaGetSymbolAddress and that address is what the kernels receive.
+// ------------------------------------------------------------------------------------------
+#include "mtb200_noalloc.h"
+
+static __device__ __align__(256) float g_colsum_noalloc_ws[32 * MTB200_COLSUM_NOALLOC_MAX_N];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_colsum_ws_addr[kMaxDevices] = {nullptr};
+
+// Device address of the workspace on the current device (looked up on first use per device).
+float* colsum_noalloc_workspace() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (g_colsum_ws_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_colsum_noalloc_ws) != cudaSuccess) return nullptr;
+    g_colsum_ws_addr[dev] = ptr;
+  }
+  return g_colsum_ws_addr[dev];
+}
+}  // namespace
+
+extern "C" int mtb200_colsum_noalloc(const void* x, long long ld, void* out, int T, int N, cudaStream_t st) {
+  if (T <= 0 || N <= 0) return 0;
+  if (N % 2 || ld < N) return -10;
+  if (N > MTB200_COLSUM_NOALLOC_MAX_N) return -11;   // beyond the built-in workspace
+  float* ws = colsum_noalloc_workspace();
+  if (ws == nullptr) return -12;
+  // Every element of ws[0 : splits * N] that the second kernel reads is written by the first one,
+  // so nothing left over from an earlier call can reach the result and no clearing pass is needed.
+  const int splits = T < 32 ? 1 : 32;
+  colsum_partial_kernel<<<dim3(cdiv(N, 64), splits), 256, 0, st>>>((const bf16*)x, ld, ws, T, N);
+  reduce_rows_kernel<<<cdiv(N, 256), 256, 0, st>>>(ws, (bf16*)out, splits, N);
+  return launch_ok();
+}
+
