@@ -171,8 +171,8 @@ def run_native(args) -> dict:
         key = id(mbs)
         if key not in resident:
             resident[key] = [(D.make_packed_batch(mb, device), 1.0 / max(1, mb["batch_num_loss_counted_tokens"])) for mb in mbs]
-        for pb, scale in resident[key]:
-            eng.forward_backward(pb, scale)
+        for k, (pb, scale) in enumerate(resident[key]):
+            eng.forward_backward(pb, scale, last=k == len(resident[key]) - 1)
         eng.optimizer_step(sched.current())
         sched.step()
 

@@ -1,0 +1,244 @@
+// NVLink / NVSwitch data path of the sharding engine over symmetric memory: every rank maps every
+// peer's arena, and these kernels move parameter shards and gradients with plain peer loads and
+// stores. No NCCL call is involved.
+//
+//   all-gather       pull: each rank copies every peer's parameter shard into its own full buffer.
+//                    Shards only change in the optimizer step, which is followed by a cross-rank
+//                    barrier, so pulling needs no per-transfer handshake.
+//   reduce-scatter   pull + reduce: each rank reads ITS slice of every peer's gradient buffer, sums
+//                    in fp32 and adds into its fp32 accumulator shard (optionally also the sum of
+//                    squares of the result, for the gradient norm). A peer's buffer is read only
+//                    after that peer signalled "complete" for the matching epoch; when the reader
+//                    is done it signals "consumed" so the owner may overwrite the buffer.
+//
+// Flags are 32-bit epochs in the owner's arena, written by peers with system-scope release
+// stores and polled with acquire loads. Every poll loop is bounded: when it runs out, the kernel
+// records {code, peer} in the status word, skips its transfers and returns, so a missing peer ends
+// in a host-side error instead of a hung GPU.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace mtb {
+
+constexpr int MAX_RANKS = 16;
+constexpr uint32_t FLAG_SPIN_LIMIT = 1u << 24;   // polls (each with a short sleep) before giving up
+
+struct PeerTable {
+  uint64_t base[MAX_RANKS];   // device address of every rank's arena, as mapped into this process
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Waits until *flag >= epoch (wrap-safe). Returns false when the bound is hit.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    __nanosleep(64);
+  }
+  return false;
+}
+
+// ---------------------------------------------------------------------------------- all-gather
+// dst[p * shard_bytes + i] = arena_p[src_off + i] for every rank p; 16-byte accesses.
+__global__ void __launch_bounds__(1024) symm_allgather_kernel(PeerTable peers, unsigned long long src_off, unsigned long long shard_bytes,
+                                                             uint8_t* __restrict__ dst, int world) {
+  const unsigned long long vec_per = shard_bytes >> 4;
+  const unsigned long long total = vec_per * world;
+  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+  unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // 4 independent loads in flight per thread
+  for (; i + 3 * stride < total; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const unsigned long long j = i + u * stride;
+      const int p = static_cast<int>(j / vec_per);
+      v[u] = *(reinterpret_cast<const uint4*>(peers.base[p] + src_off) + (j - p * vec_per));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) reinterpret_cast<uint4*>(dst)[i + u * stride] = v[u];
+  }
+  for (; i < total; i += stride) {
+    const int p = static_cast<int>(i / vec_per);
+    reinterpret_cast<uint4*>(dst)[i] = *(reinterpret_cast<const uint4*>(peers.base[p] + src_off) + (i - p * vec_per));
+  }
+}
+
+// ---------------------------------------------------------------------------------- signalling
+// Writes `epoch` into slot [flag_off + 4 * rank] of every peer's arena (one thread per peer).
+__global__ void symm_signal_kernel(PeerTable peers, unsigned long long flag_off, int rank, int world, uint32_t epoch) {
+  const int p = threadIdx.x;
+  if (p < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(peers.base[p] + flag_off) + rank, epoch);
+  }
+}
+
+// Waits until every peer's slot in MY flag row reached `epoch`. On expiry: status = code | peer << 8.
+__global__ void symm_wait_kernel(const uint32_t* __restrict__ my_flags, int world, uint32_t epoch, uint32_t limit, int code, int* status) {
+  const int p = threadIdx.x;
+  if (p < world && !wait_flag(my_flags + p, epoch, limit)) atomicExch(status, code | (p << 8));
+}
+
+// ---------------------------------------------------------------------------------- reduce-scatter
+// acc[i] (+)= sum_p bf16 grad_p[rank * n + i]; optional sumsq of the result. After all blocks have
+// read, the last one signals "consumed" (epoch) to every peer.
+__global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable peers, unsigned long long grad_off, long long n,
+                                                                 float* __restrict__ acc, int accumulate, float* __restrict__ sumsq,
+                                                                 const uint32_t* __restrict__ ready_flags, unsigned long long consumed_off,
+                                                                 uint32_t epoch, uint32_t limit, int rank, int world,
+                                                                 unsigned int* __restrict__ block_counter, int* status) {
+  __shared__ int ok_s;
+  __shared__ float red[32];
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < world && !wait_flag(ready_flags + threadIdx.x, epoch, limit)) {
+    ok_s = 0;
+    atomicExch(status, 41 | (threadIdx.x << 8));
+  }
+  __syncthreads();
+  float ss = 0.f;
+  if (ok_s) {
+    const long long nvec = n >> 3;
+    const unsigned long long slice_off = grad_off + static_cast<unsigned long long>(rank) * n * 2;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      uint4 v[MAX_RANKS];
+#pragma unroll
+      for (int p = 0; p < MAX_RANKS; ++p)
+        if (p < world) v[p] = *(reinterpret_cast<const uint4*>(peers.base[p] + slice_off) + i);
+#pragma unroll
+      for (int p = 0; p < MAX_RANKS; ++p) {
+        if (p < world) {
+          const float2 a = unpack_bf16(v[p].x), b = unpack_bf16(v[p].y), c = unpack_bf16(v[p].z), d = unpack_bf16(v[p].w);
+          f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y; f[4] += c.x; f[5] += c.y; f[6] += d.x; f[7] += d.y;
+        }
+      }
+      float4* dst = reinterpret_cast<float4*>(acc) + 2 * i;
+      if (accumulate) {
+        const float4 a = dst[0], b = dst[1];
+        f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w; f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+      }
+      dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+      dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+      if (sumsq != nullptr) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss += f[k] * f[k];
+      }
+    }
+  }
+  if (sumsq != nullptr) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+      t = warp_sum(t);
+      if (threadIdx.x == 0) atomicAdd(sumsq, t);
+    }
+  }
+  // last block out tells every peer that its buffer has been consumed by this rank
+  __threadfence();
+  __syncthreads();
+  __shared__ int last_s;
+  if (threadIdx.x == 0) last_s = (atomicAdd(block_counter, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (last_s) {
+    if (threadIdx.x == 0) *block_counter = 0;
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(peers.base[threadIdx.x] + consumed_off) + rank, epoch);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------- scalar all-reduce
+// Every rank deposits its value in slot [rank] of every peer's value row, then sums the row it
+// received in rank order (so all ranks get the bitwise-same result).
+__global__ void symm_allreduce_scalar_kernel(PeerTable peers, unsigned long long vals_off, unsigned long long flag_off,
+                                             const uint32_t* __restrict__ my_vals, const uint32_t* __restrict__ my_flags,
+                                             uint32_t epoch, uint32_t limit, float* __restrict__ inout, int rank, int world, int* status) {
+  __shared__ int ok_s;
+  const int p = threadIdx.x;
+  if (p == 0) ok_s = 1;
+  __syncthreads();
+  if (p < world) {
+    const float v = *inout;
+    *(reinterpret_cast<float*>(peers.base[p] + vals_off) + rank) = v;
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(peers.base[p] + flag_off) + rank, epoch);
+    if (!wait_flag(my_flags + p, epoch, limit)) { ok_s = 0; atomicExch(status, 44 | (p << 8)); }
+  }
+  __syncthreads();
+  if (p == 0 && ok_s) {
+    float s = 0.f;
+    for (int q = 0; q < world; ++q) s += __uint_as_float(ld_acquire_sys(my_vals + q));
+    *inout = s;
+  }
+}
+
+static inline PeerTable make_table(const unsigned long long* bases, int world) {
+  PeerTable t;
+  for (int i = 0; i < MAX_RANKS; ++i) t.base[i] = i < world ? bases[i] : 0;
+  return t;
+}
+
+}  // namespace mtb
+
+using namespace mtb;
+
+extern "C" {
+
+// bases: host array of `world` arena addresses. Offsets are byte offsets inside the arena.
+int mtb200_symm_allgather(const unsigned long long* bases, int world, unsigned long long src_off, unsigned long long shard_bytes,
+                          void* dst, int blocks, cudaStream_t st) {
+  if (world < 1 || world > MAX_RANKS || shard_bytes % 16 || src_off % 16) return -10;
+  symm_allgather_kernel<<<blocks, 1024, 0, st>>>(make_table(bases, world), src_off, shard_bytes, reinterpret_cast<uint8_t*>(dst), world);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+int mtb200_symm_signal(const unsigned long long* bases, int world, int rank, unsigned long long flag_off, unsigned int epoch, cudaStream_t st) {
+  if (world < 1 || world > MAX_RANKS) return -10;
+  symm_signal_kernel<<<1, 32, 0, st>>>(make_table(bases, world), flag_off, rank, world, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+int mtb200_symm_wait(const void* my_flags, int world, unsigned int epoch, unsigned int limit, int code, int* status, cudaStream_t st) {
+  if (world < 1 || world > MAX_RANKS) return -10;
+  symm_wait_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const uint32_t*>(my_flags), world, epoch, limit ? limit : FLAG_SPIN_LIMIT, code, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+int mtb200_symm_reduce_scatter(const unsigned long long* bases, int world, int rank, unsigned long long grad_off, long long n,
+                               float* acc, int accumulate, float* sumsq, const void* ready_flags, unsigned long long consumed_off,
+                               unsigned int epoch, unsigned int limit, unsigned int* block_counter, int* status, int blocks,
+                               cudaStream_t st) {
+  if (world < 1 || world > MAX_RANKS || n % 8 || grad_off % 16) return -10;
+  symm_reduce_scatter_kernel<<<blocks, 512, 0, st>>>(make_table(bases, world), grad_off, n, acc, accumulate, sumsq,
+                                                     reinterpret_cast<const uint32_t*>(ready_flags), consumed_off, epoch,
+                                                     limit ? limit : FLAG_SPIN_LIMIT, rank, world, block_counter, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+int mtb200_symm_allreduce_scalar(const unsigned long long* bases, int world, int rank, unsigned long long vals_off,
+                                 unsigned long long flag_off, const void* my_vals, const void* my_flags, unsigned int epoch,
+                                 unsigned int limit, float* inout, int* status, cudaStream_t st) {
+  if (world < 1 || world > MAX_RANKS) return -10;
+  symm_allreduce_scalar_kernel<<<1, 32, 0, st>>>(make_table(bases, world), vals_off, flag_off, reinterpret_cast<const uint32_t*>(my_vals),
+                                                 reinterpret_cast<const uint32_t*>(my_flags), epoch, limit ? limit : FLAG_SPIN_LIMIT, inout,
+                                                 rank, world, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // extern "C"

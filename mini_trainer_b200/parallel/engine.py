@@ -51,15 +51,16 @@ class OptimConfig:
 class ShardedGroup:
     """One parameter group: layout + this rank's shard of params, master, moments, grads."""
 
-    def __init__(self, layout: L.GroupLayout, device, param_dtype, state_dtype):
+    def __init__(self, layout: L.GroupLayout, device, param_dtype, state_dtype, shard=None):
         self.layout = layout
         s = layout.shard_numel
-        self.shard = torch.zeros(s, dtype=param_dtype, device=device)
+        self.shard = shard if shard is not None else torch.zeros(s, dtype=param_dtype, device=device)
         self.master = torch.zeros(s, dtype=torch.float32, device=device)
         self.m = torch.zeros(s, dtype=state_dtype, device=device)
         self.v = torch.zeros(s, dtype=state_dtype, device=device)
         self.gacc = torch.zeros(s, dtype=torch.float32, device=device)
         self.has_grad = False
+        self.sq_done = False   # sum of squares of gacc already added to the engine's norm scalar
 
     def state_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.shard, self.master, self.m, self.v, self.gacc))
@@ -107,19 +108,35 @@ class ShardedEngine:
         self.step_count = 0
         self.inv_freq = cfg.rope_inv_freq().to(self.device)
 
-        mk = lambda name, entries: ShardedGroup(L.GroupLayout(name, entries, self.world), self.device,
-                                                self.param_dtype, self.state_dtype)
-        self.embed = mk("embed", L.embed_entries(cfg))
-        self.blocks = [mk(f"block{i}", L.block_entries(cfg)) for i in range(cfg.num_hidden_layers)]
-        self.head = mk("head", L.head_entries(cfg))
+        layouts = ([L.GroupLayout("embed", L.embed_entries(cfg), self.world)]
+                   + [L.GroupLayout(f"block{i}", L.block_entries(cfg), self.world) for i in range(cfg.num_hidden_layers)]
+                   + [L.GroupLayout("head", L.head_entries(cfg), self.world)])
+        blk = layouts[1].padded_numel
+        nbuf = 2
+        # Buffers that peers read (parameter shards, gradient buffers) live in the comm backend's
+        # symmetric arena when it has one; otherwise they are ordinary device tensors.
+        self.symmetric = hasattr(self.comm, "setup")
+        if self.symmetric:
+            es = torch.empty(0, dtype=self.param_dtype).element_size()
+            payload = sum(l.shard_numel for l in layouts) + nbuf * blk + layouts[0].padded_numel + layouts[-1].padded_numel
+            self.comm.setup(payload * es + (len(layouts) + 8) * 512)
+        salloc = (lambda n: self.comm.alloc(n, self.param_dtype)) if self.symmetric else \
+                 (lambda n: torch.zeros(n, dtype=self.param_dtype, device=self.device))
+        mk = lambda lay: ShardedGroup(lay, self.device, self.param_dtype, self.state_dtype,
+                                      shard=salloc(lay.shard_numel) if self.symmetric else None)
+        self.embed = mk(layouts[0])
+        self.blocks = [mk(l) for l in layouts[1:-1]]
+        self.head = mk(layouts[-1])
         self.groups = [self.embed] + self.blocks + [self.head]
 
         self.side = _Side(self.device)
-        blk = self.blocks[0].layout.padded_numel
-        nbuf = 2
         # rotating full-size buffers for gathered block parameters and block gradients
         self._pbufs = [] if self.world == 1 else [torch.zeros(blk, dtype=self.param_dtype, device=self.device) for _ in range(nbuf)]
-        self._gbufs = [torch.zeros(blk, dtype=self.param_dtype, device=self.device) for _ in range(nbuf)]
+        self._gbufs = [salloc(blk) for _ in range(nbuf)]
+        self._eg_full = salloc(self.embed.layout.padded_numel)   # embedding gradient (full, reduced once per microbatch)
+        self._hg_full = salloc(self.head.layout.padded_numel)    # final norm / lm_head gradient
+        self._root_free = {"embed": None, "head": None}
+        self._sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._pbuf_free = [None] * nbuf   # event after which the buffer may be overwritten
         self._gbuf_free = [None] * nbuf
         self._rs_scratch = None
@@ -183,7 +200,7 @@ class ShardedEngine:
         ``get_model_state_dict(full_state_dict=True)`` does (train.py:41-42).
         """
         for grp, it in self._hf_iters():
-            src = grp.master if source == "master" else grp.shard
+            src = grp.master if source == "master" and not self.symmetric else grp.shard  # peers can only read arena tensors
             if self.world == 1:
                 full = src
             else:
@@ -225,11 +242,21 @@ class ShardedEngine:
         self.comm.all_gather(grp.shard, full)
         return grp.layout.views(full), full
 
-    def _reduce(self, grp: ShardedGroup, gfull: torch.Tensor, slot: int = -1):
-        """Reduce-scatter ``gfull`` into the group's fp32 accumulator on the side stream."""
+    def _reduce(self, grp: ShardedGroup, gfull: torch.Tensor, slot: int = -1, last: bool = False):
+        """Reduce-scatter ``gfull`` into the group's fp32 accumulator on the side stream.
+
+        With the symmetric backend the compute stream first publishes "my buffer is complete" to the
+        peers; the reduction kernel itself waits for the peers' matching signals. On the last
+        microbatch of a step that kernel also adds the sum of squares of the finished accumulator
+        to the step's norm scalar, so the optimizer does not have to read the accumulator again."""
+        if self.symmetric:
+            self.comm.grad_ready(gfull)
         with self.side.run(wait_current=True):
             if self.world == 1 and hasattr(self.ops, "accumulate"):
                 self.ops.accumulate(grp.gacc, gfull[: grp.gacc.numel()], grp.has_grad)
+            elif self.symmetric:
+                self.comm.reduce_scatter_accumulate(gfull, grp.gacc, grp.has_grad, sumsq=self._sq if last else None)
+                grp.sq_done = last
             else:
                 self.comm.reduce_scatter_accumulate(gfull, grp.gacc, grp.has_grad, self._rs_scratch)
             ev = self.side.record()
@@ -242,7 +269,18 @@ class ShardedEngine:
         slot = i % len(self._gbufs)
         _Side.wait(self._gbuf_free[slot])
         self._gbuf_free[slot] = None
+        if self.symmetric:
+            self.comm.wait_consumed(self._gbufs[slot])
         return self._gbufs[slot], slot
+
+    def _root_grad_buffer(self, which: str) -> torch.Tensor:
+        """Zeroed full gradient buffer of the embed / head group, once its previous reduction is over."""
+        buf = self._eg_full if which == "embed" else self._hg_full
+        _Side.wait(self._root_free[which])
+        if self.symmetric:
+            self.comm.wait_consumed(buf)
+        buf.zero_()
+        return buf
 
     # ------------------------------------------------------------------------------------
     # activation checkpointing plan
@@ -298,10 +336,12 @@ class ShardedEngine:
     # one microbatch
     # ------------------------------------------------------------------------------------
     @torch.no_grad()
-    def forward_backward(self, batch: D.PackedBatch, grad_scale: float) -> torch.Tensor:
+    def forward_backward(self, batch: D.PackedBatch, grad_scale: float, last: bool = False) -> torch.Tensor:
         """Runs forward and backward of one packed minibatch; accumulates gradients.
 
-        Returns the per-token loss vector ``[T]`` (fp32, on device)."""
+        ``last`` marks the final minibatch before ``optimizer_step`` (lets the reduction kernels
+        fold the gradient-norm partial sums in). Returns the per-token loss vector ``[T]``
+        (fp32, on device)."""
         cfg, ops = self.cfg, self.ops
         nL = len(self.blocks)
         tied = cfg.tie_word_embeddings
@@ -324,14 +364,14 @@ class ShardedEngine:
             saved.append((xin, acts, attn_state))
             if i + 1 < nL or self.world == 1:
                 self._release_pbuf(slot)
-            last = (p, slot)  # the last block stays gathered for backward (reshard_after_forward=False)
+            last_block = (p, slot)  # the last block stays gathered for backward (reshard_after_forward=False)
 
         # ---- head: loss and its gradients in one pass ----
         head_views, head_full = self._gather_group(self.head)
-        hg_full = torch.zeros(self.head.layout.padded_numel, dtype=self.param_dtype, device=self.device)
+        hg_full = self._root_grad_buffer("head")
         head_g = self.head.layout.views(hg_full)
         if tied:
-            eg_full = torch.zeros(self.embed.layout.padded_numel, dtype=self.param_dtype, device=self.device)
+            eg_full = self._root_grad_buffer("embed")
             emb_g = self.embed.layout.views(eg_full)
             loss, dx = D.head_forward_backward(ops, cfg, head_views, head_g, emb_views["embed"], emb_g["embed"], True,
                                                x, batch, grad_scale)
@@ -339,10 +379,10 @@ class ShardedEngine:
             loss, dx = D.head_forward_backward(ops, cfg, head_views, head_g, head_views["lm_head"], head_g["lm_head"],
                                                False, x, batch, grad_scale)
         del x, head_views, head_full
-        self._reduce(self.head, hg_full)
+        self._root_free["head"] = self._reduce(self.head, hg_full, last=last)
 
         # ---- backward through the blocks ----
-        cur = (last[0], None, last[1])
+        cur = (last_block[0], None, last_block[1])
         for i in range(nL - 1, -1, -1):
             p, ev, slot = cur
             _Side.wait(ev)
@@ -355,18 +395,14 @@ class ShardedEngine:
             dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq)
             del acts, xin, attn_state
             self._release_pbuf(slot)
-            self._reduce(self.blocks[i], gbuf, gslot)
+            self._reduce(self.blocks[i], gbuf, gslot, last=last)
 
         # ---- embedding ----
         if not tied:
-            eg_full = torch.zeros(self.embed.layout.padded_numel, dtype=self.param_dtype, device=self.device)
+            eg_full = self._root_grad_buffer("embed")
             emb_g = self.embed.layout.views(eg_full)
         ops.embedding_bwd(emb_g["embed"], batch.input_ids, dx)
-        ev = self._reduce(self.embed, eg_full)
-        # transient buffers handed to the side stream must outlive its work
-        if self.side.cuda:
-            for t in (hg_full, eg_full):
-                t.record_stream(self.side.stream)
+        self._root_free["embed"] = self._reduce(self.embed, eg_full, last=last)
         return loss
 
     # ------------------------------------------------------------------------------------
@@ -379,9 +415,10 @@ class ShardedEngine:
             torch.cuda.current_stream().wait_stream(self.side.stream)
         o = self.optim
         live = [g for g in self.groups if g.has_grad]
-        sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        sq = self._sq
         for g in live:
-            sq += self.ops.sumsq(g.gacc)
+            if not g.sq_done:
+                sq += self.ops.sumsq(g.gacc)
         self.comm.all_reduce_sum(sq)
         norm = sq.sqrt().squeeze(0)
         if o.max_grad_norm and o.max_grad_norm > 0:
@@ -393,6 +430,10 @@ class ShardedEngine:
             self.ops.adamw_step(g.master, g.m, g.v, g.gacc, g.shard, lr, o.beta1, o.beta2, o.eps, o.weight_decay,
                                 self.step_count, coef)
             g.has_grad = False
+            g.sq_done = False
+        self._sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if self.symmetric:
+            self.comm.barrier()   # no peer may pull a shard before every rank has finished updating its own
         if self.side.cuda:
             self.side.stream.wait_stream(torch.cuda.current_stream())
         return norm
@@ -400,6 +441,8 @@ class ShardedEngine:
     def zero_grad(self) -> None:
         for g in self.groups:
             g.has_grad = False
+            g.sq_done = False
+        self._sq.zero_()
 
     # ------------------------------------------------------------------------------------
     # convenience: a full training step over this rank's minibatches
@@ -412,10 +455,10 @@ class ShardedEngine:
         """
         loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
         ntok = 0
-        for mb in minibatches:
+        for k, mb in enumerate(minibatches):
             batch = D.make_packed_batch(mb, self.device)
             denom = float(mb["batch_num_loss_counted_tokens"]) or 1.0
-            loss = self.forward_backward(batch, 1.0 / denom)
+            loss = self.forward_backward(batch, 1.0 / denom, last=k == len(minibatches) - 1)
             loss_sum += loss.sum()
             ntok += batch.num_tokens
         gnorm = self.optimizer_step(lr)

@@ -1,0 +1,193 @@
+"""Single-node NVLink/NVSwitch communication backend over symmetric memory.
+
+Every rank allocates one arena with ``torch.distributed._symmetric_memory`` (CUDA VMM allocation
+whose handle is exchanged through the process group's store) and maps all peers' arenas. The
+engine places parameter shards, gradient buffers and flag words in the arena; the hand-written
+kernels in ``csrc/symm_comm.cu`` then move data with peer loads — there is no NCCL call in
+``all_gather`` / ``reduce_scatter_accumulate`` / ``all_reduce_sum`` / ``barrier``.
+NCCL (through ``torch.distributed``) is only used once, for the rendezvous.
+
+Protocol (epochs are per-channel counters that advance identically on all ranks, because all
+ranks execute the same sequence of collectives):
+
+* ``grad_ready(buf)``      my gradient buffer is complete         -> ``ready[ch][me] = epoch`` on all peers
+* ``reduce_scatter_...``   waits ``ready[ch][p] >= epoch`` for all p, reads, then
+                           ``consumed[ch][me] = epoch`` on all peers
+* ``wait_consumed(buf)``   before overwriting my buffer: ``consumed[ch][p] >= last epoch`` for all p
+* ``barrier()``            signal + wait on a dedicated channel (after the optimizer step, so that
+                           no peer pulls a half-updated shard)
+
+All device-side waits are bounded (``flag_spin_limit`` polls); an expired wait records a code in
+``status`` which ``check_status()`` turns into an exception on the host.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_int, c_longlong, c_uint, c_ulonglong, c_void_p
+
+import torch
+import torch.distributed as dist
+
+from ..ops.native import load_library
+
+MAX_CHANNELS = 16
+MAX_RANKS = 16
+_ALIGN = 256
+
+
+class SymmetricComm:
+    name = "symmetric"
+    fused_sumsq = True
+
+    def __init__(self, device, group=None, flag_spin_limit: int | None = None):
+        self.device = torch.device(device)
+        self.group = group or dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > MAX_RANKS:
+            raise ValueError(f"symmetric backend supports up to {MAX_RANKS} ranks on one node")
+        self.lib = load_library()
+        self._bind()
+        self.flag_spin_limit = int(flag_spin_limit or os.environ.get("MTB200_FLAG_SPIN_LIMIT", 0))
+        self.arena = None
+        self._off = 0
+        self._chan = {}
+        self._epoch = [0] * MAX_CHANNELS
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0
+
+    def _bind(self):
+        P, I, L, U, UL = c_void_p, c_int, c_longlong, c_uint, c_ulonglong
+        sig = {
+            "mtb200_symm_allgather": [P, I, UL, UL, P, I, P],
+            "mtb200_symm_signal": [P, I, I, UL, U, P],
+            "mtb200_symm_wait": [P, I, U, U, I, P, P],
+            "mtb200_symm_reduce_scatter": [P, I, I, UL, L, P, I, P, P, UL, U, U, P, P, I, P],
+            "mtb200_symm_allreduce_scalar": [P, I, I, UL, UL, P, P, U, U, P, P, P],
+        }
+        for name, args in sig.items():
+            fn = getattr(self.lib, name)
+            fn.restype = c_int
+            fn.argtypes = args
+
+    # -- arena ------------------------------------------------------------------------
+    def setup(self, payload_bytes: int) -> None:
+        """Allocates and rendezvouses the arena: ``payload_bytes`` for engine buffers + flag words."""
+        import torch.distributed._symmetric_memory as symm_mem
+        flag_bytes = MAX_CHANNELS * 3 * MAX_RANKS * 4 + 4096
+        total = -(-(payload_bytes + flag_bytes + 64 * _ALIGN) // 4096) * 4096
+        gname = self.group.group_name
+        try:
+            symm_mem.enable_symm_mem_for_group(gname)
+        except Exception:
+            pass
+        self.arena = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        self.arena.zero_()
+        self.handle = symm_mem.rendezvous(self.arena, gname)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._bases = (c_ulonglong * self.world)(*ptrs)
+        assert ptrs[self.rank] == self.arena.data_ptr()
+        self._off = 0
+        # flag rows: ready[ch][r], consumed[ch][r] (uint32) and vals[ch][r] (fp32 payload for scalar all-reduce)
+        self._flags = self.alloc(MAX_CHANNELS * 3 * MAX_RANKS, torch.int32)
+        self._counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._barrier_ch = self._new_channel("barrier")
+        self._scalar_ch = [self._new_channel("scalar0"), self._new_channel("scalar1")]
+        self._scalar_calls = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)   # every arena is zeroed before anyone signals
+
+    def alloc(self, numel: int, dtype) -> torch.Tensor:
+        es = torch.empty(0, dtype=dtype).element_size()
+        nbytes = numel * es
+        start = -(-self._off // _ALIGN) * _ALIGN
+        if self.arena is None or start + nbytes > self.arena.numel():
+            raise RuntimeError("symmetric arena exhausted")
+        self._off = start + nbytes
+        return self.arena[start:start + nbytes].view(dtype)
+
+    def _offset(self, t: torch.Tensor) -> int:
+        off = t.data_ptr() - self.arena.data_ptr()
+        if off < 0 or off >= self.arena.numel():
+            raise ValueError("tensor does not live in the symmetric arena")
+        return off
+
+    def _new_channel(self, key) -> int:
+        ch = len(self._chan)
+        if ch >= MAX_CHANNELS:
+            raise RuntimeError("out of flag channels")
+        self._chan[key] = ch
+        return ch
+
+    def _channel(self, t: torch.Tensor) -> int:
+        key = t.data_ptr()
+        ch = self._chan.get(key)
+        return self._new_channel(key) if ch is None else ch
+
+    def _ready_off(self, ch):
+        return self._offset(self._flags) + (ch * 3 + 0) * MAX_RANKS * 4
+
+    def _consumed_off(self, ch):
+        return self._offset(self._flags) + (ch * 3 + 1) * MAX_RANKS * 4
+
+    def _vals_off(self, ch):
+        return self._offset(self._flags) + (ch * 3 + 2) * MAX_RANKS * 4
+
+    def _st(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _call(self, name, *args):
+        rc = getattr(self.lib, name)(*args)
+        if rc != 0:
+            raise RuntimeError(f"{name} failed with code {rc}")
+        self.launches += 1
+
+    # -- collectives ------------------------------------------------------------------
+    def all_gather(self, shard, full, blocks: int = 32):
+        self._call("mtb200_symm_allgather", self._bases, self.world, self._offset(shard),
+                   shard.numel() * shard.element_size(), full.data_ptr(), blocks, self._st())
+
+    def grad_ready(self, gfull):
+        ch = self._channel(gfull)
+        self._epoch[ch] += 1
+        self._call("mtb200_symm_signal", self._bases, self.world, self.rank, self._ready_off(ch), self._epoch[ch], self._st())
+
+    def reduce_scatter_accumulate(self, gfull, acc, accumulate: bool, scratch=None, sumsq=None, blocks: int = 32):
+        ch = self._channel(gfull)
+        base = self.arena.data_ptr()
+        self._call("mtb200_symm_reduce_scatter", self._bases, self.world, self.rank, self._offset(gfull), acc.numel(),
+                   acc.data_ptr(), int(accumulate), None if sumsq is None else sumsq.data_ptr(),
+                   base + self._ready_off(ch), self._consumed_off(ch), self._epoch[ch], self.flag_spin_limit,
+                   self._counter.data_ptr(), self.status.data_ptr(), blocks, self._st())
+
+    def wait_consumed(self, gfull):
+        ch = self._channel(gfull)
+        if self._epoch[ch] == 0:
+            return
+        self._call("mtb200_symm_wait", self.arena.data_ptr() + self._consumed_off(ch), self.world, self._epoch[ch],
+                   self.flag_spin_limit, 42, self.status.data_ptr(), self._st())
+
+    def barrier(self):
+        ch = self._barrier_ch
+        self._epoch[ch] += 1
+        self._call("mtb200_symm_signal", self._bases, self.world, self.rank, self._ready_off(ch), self._epoch[ch], self._st())
+        self._call("mtb200_symm_wait", self.arena.data_ptr() + self._ready_off(ch), self.world, self._epoch[ch],
+                   self.flag_spin_limit, 43, self.status.data_ptr(), self._st())
+
+    def all_reduce_sum(self, vec):
+        """Sum of a 1-element fp32 tensor over ranks (the gradient-norm scalar), in rank order."""
+        assert vec.numel() == 1 and vec.dtype == torch.float32
+        ch = self._scalar_ch[self._scalar_calls & 1]   # alternate rows so a fast peer cannot overwrite an unread value
+        self._scalar_calls += 1
+        self._epoch[ch] += 1
+        self._call("mtb200_symm_allreduce_scalar", self._bases, self.world, self.rank, self._vals_off(ch), self._ready_off(ch),
+                   self.arena.data_ptr() + self._vals_off(ch), self.arena.data_ptr() + self._ready_off(ch), self._epoch[ch],
+                   self.flag_spin_limit, vec.data_ptr(), self.status.data_ptr(), self._st())
+        return vec
+
+    def check_status(self):
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise RuntimeError(f"symmetric comm: a bounded wait on a peer expired (code {code & 0xff}, peer {code >> 8})")

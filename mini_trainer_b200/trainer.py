@@ -145,7 +145,7 @@ def train(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule, data_loader
             batch_num_loss_counted_tokens = mb["batch_num_loss_counted_tokens"]
             pb = D.make_packed_batch(mb, device)
             scale = 1.0 / max(1, batch_num_loss_counted_tokens)
-            loss = model.forward_backward(pb, scale)
+            loss = model.forward_backward(pb, scale, last=grad_accum == len(batch) - 1)
             loss_sum += loss.sum()
             batch_totals.accumulate_minibatch_metrics(
                 num_loss_counted_tokens=mb["num_loss_counted_tokens"],

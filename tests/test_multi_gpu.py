@@ -1,0 +1,80 @@
+"""Sharded engine on 2 GPUs (NCCL and the symmetric-memory backend) against the 1-GPU engine.
+
+Runs as child processes, one per GPU, with NVLS disabled; skipped when fewer than two GPUs are
+visible. Ranks only stop between steps, with no kernel or collective in flight.
+"""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import json, os, sys, torch
+sys.path.insert(0, os.environ["MTB200_REPO"])
+import torch.distributed as dist
+from mini_trainer_b200.utils.dist import init_distributed_environment
+from mini_trainer_b200.models.config import get_preset
+from mini_trainer_b200.ops import get_ops
+from mini_trainer_b200.parallel.comm import make_comm
+from mini_trainer_b200.parallel.engine import OptimConfig, ShardedEngine
+from mini_trainer_b200.data.sampler import get_data_loader
+from mini_trainer_b200.data.synthetic import LengthSpec, synthetic_dataset
+
+device = init_distributed_environment(timeout_minutes=3)
+rank, world = dist.get_rank(), dist.get_world_size()
+cfg = get_preset("smoke-llama")
+comm = make_comm(os.environ.get("MTB200_COMM", "auto"), device)
+eng = ShardedEngine(cfg, device, get_ops(device), comm=comm, optim=OptimConfig(), activation_budget_bytes=0)
+eng.init_random(seed=5, std=0.05)
+ds = synthetic_dataset(64, LengthSpec(5.0, 0.7, 8, 700), cfg.vocab_size, seed=1)
+loader = iter(get_data_loader(dataset=ds, batch_size=16, max_tokens_per_gpu=1500, seed=3, rank=rank, world_size=world, prefetch=0))
+out = []
+for step in range(3):
+    res = eng.train_step(next(loader), lr=1e-3)
+    loss = res["loss_sum"].clone()
+    dist.all_reduce(loss)
+    out.append({"loss": loss.item(), "grad_norm": res["grad_norm"].item()})
+torch.cuda.synchronize()
+if hasattr(eng.ops, "check_status"):
+    eng.ops.check_status()
+if hasattr(comm, "check_status"):
+    comm.check_status()
+if rank == 0:
+    print("RESULT " + json.dumps(out), flush=True)
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+def _run(world: int, comm: str):
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    env = dict(os.environ, MTB200_REPO=REPO, MTB200_COMM=comm, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1",
+               MASTER_PORT=str(port))
+    if world == 1:
+        cmd = [sys.executable, "-c", WORKER]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), "--no-python", sys.executable, "-c", WORKER]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    for line in proc.stdout.splitlines():
+        if line.startswith("RESULT "):
+            return json.loads(line[7:])
+    raise AssertionError(f"worker failed (rc={proc.returncode}):\n{proc.stdout[-3000:]}\n{proc.stderr[-3000:]}")
+
+
+@pytest.mark.parametrize("comm", ["torchdist", "symmetric"])
+def test_two_gpus_match_one_gpu(comm):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    one = _run(1, "auto")
+    two = _run(2, comm)
+    for a, b in zip(one, two):
+        assert abs(a["loss"] - b["loss"]) < 2e-2 * abs(a["loss"]), (one, two)
+        assert abs(a["grad_norm"] - b["grad_norm"]) < 5e-2 * a["grad_norm"], (one, two)
