@@ -48,9 +48,37 @@ struct GemmParams {
   int* status;            // device word; set non-zero when a bounded wait expired
 };
 
-template <bool A_MN, bool B_MN, bool OUT_F32>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+// Fused all-gather: while the GEMM runs, four extra warps per CTA pull this parameter group's
+// shards from every peer's symmetric arena (plain peer loads over NVLink) into the local full
+// buffer that the B tensor map points at, 128 KB chunk by chunk, and publish each finished chunk
+// in a flag array. The TMA producer only loads a B tile after the chunks under it are flagged.
+constexpr int GATHER_THREADS = 128;
+constexpr int GATHER_CHUNK_BYTES = 128 * 1024;
+constexpr int GATHER_MAX_RANKS = 16;
+
+struct GatherParams {
+  unsigned long long peer_base[GATHER_MAX_RANKS];  // every rank's arena, as mapped here
+  unsigned long long shard_off;    // byte offset of this group's shard inside each arena
+  unsigned long long shard_bytes;  // bytes per rank
+  unsigned char* dst;              // local full buffer (world * shard_bytes)
+  unsigned int* flags;             // [n_chunks] epoch per chunk, local
+  unsigned int epoch;
+  int world;
+  int chunk_lo, chunk_hi;          // chunks this launch gathers
+  int chunk_first;                 // gather order starts here (the chunks under B), wraps inside [lo, hi)
+  unsigned long long b_byte_off;   // byte offset of B's first element inside dst
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? GEMM_THREADS + GATHER_THREADS : GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p,
+            const __grid_constant__ GatherParams g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -95,6 +123,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         int tm, tn;
         tile_coords(t, tm, tn);
+        if (GATHER) {
+          // rows [tn*BN, tn*BN+BN) of the K-major weight are one contiguous byte range of the full buffer
+          const unsigned long long lo = g.b_byte_off + static_cast<unsigned long long>(tn) * BN * p.K * 2;
+          const int rows = min(BN, p.N - tn * BN);
+          const unsigned long long hi = lo + static_cast<unsigned long long>(rows) * p.K * 2 - 1;
+          for (int c = static_cast<int>(lo / GATHER_CHUNK_BYTES); c <= static_cast<int>(hi / GATHER_CHUNK_BYTES); ++c) {
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(g.flags + c) != g.epoch) {
+              if (++spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; atomicExch(p.status, 5); goto done; }
+            }
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");   // peer data was written with ordinary stores, TMA reads it
+        }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -145,6 +186,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         umma_commit(&tfull_bar[acc]);   // accumulator complete
       }
+    }
+  } else if (GATHER && warp >= 6) {
+    // ------------------------------------------------------------------ gather warps (6..9)
+    const int gt = threadIdx.x - GEMM_THREADS;
+    const int n_chunks = g.chunk_hi - g.chunk_lo;
+    const unsigned long long total = g.shard_bytes * g.world;
+    const unsigned long long vec_per_shard = g.shard_bytes >> 4;
+    for (int k = blockIdx.x; k < n_chunks; k += gridDim.x) {
+      int c = g.chunk_first + k;
+      if (c >= g.chunk_hi) c -= n_chunks;
+      const unsigned long long b0 = static_cast<unsigned long long>(c) * GATHER_CHUNK_BYTES;
+      const unsigned long long b1 = min(b0 + GATHER_CHUNK_BYTES, total);
+      const unsigned long long v0 = b0 >> 4, nv = (b1 - b0) >> 4;
+      uint4* dst = reinterpret_cast<uint4*>(g.dst) + v0;
+      for (unsigned long long j = gt; j < nv; j += 4 * GATHER_THREADS) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const unsigned long long jj = j + u * GATHER_THREADS;
+          if (jj < nv) {
+            const unsigned long long gv = v0 + jj;
+            const unsigned long long pr = gv / vec_per_shard;
+            v[u] = *(reinterpret_cast<const uint4*>(g.peer_base[pr] + g.shard_off) + (gv - pr * vec_per_shard));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const unsigned long long jj = j + u * GATHER_THREADS;
+          if (jj < nv) dst[jj] = v[u];
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(GATHER_THREADS) : "memory");
+      if (gt == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.flags + c), "r"(g.epoch) : "memory");
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
@@ -265,10 +340,11 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
 
 static int g_num_sms = 0;
 
-template <bool A_MN, bool B_MN, bool OUT_F32>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream,
+                  const GatherParams* gp = nullptr) {
   static bool configured = false;
-  auto kern = gemm_kernel<A_MN, B_MN, OUT_F32>;
+  auto kern = gemm_kernel<A_MN, B_MN, OUT_F32, GATHER>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess) return -4;
     configured = true;
@@ -279,8 +355,10 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < g_num_sms ? tiles : g_num_sms;
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
+  // the gathering variant always uses every SM: its extra warps carry the transfer
+  const int grid = (GATHER || tiles >= g_num_sms) ? g_num_sms : tiles;
+  static const GatherParams none{};
+  kern<<<grid, GATHER ? GEMM_THREADS + GATHER_THREADS : GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p, gp ? *gp : none);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -319,6 +397,36 @@ int mtb200_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long
     case 6: return launch<true, true, false>(ta, tb, p, stream);
     default: return launch<true, true, true>(ta, tb, p, stream);
   }
+}
+
+// Fused all-gather + GEMM:  D[M,N] = A[M,K] * W[N,K]^T (+bias) with W living in `full`, the local
+// full parameter buffer of a sharded group that this same launch fills from the peers' shards.
+//   bases/world       arena address of every rank; shard_off/shard_bytes locate the group's shard
+//   full              local destination (world * shard_bytes); w_byte_off = offset of W inside it
+//   flags/epoch       per-chunk (128 KB) completion words; a chunk is ready when its word == epoch
+//   chunk_lo/chunk_hi chunks gathered by this launch (others must already carry `epoch`)
+// bias, if given, must lie in an already gathered part of `full` (or elsewhere).
+int mtb200_gemm_bf16_allgather(const void* A, long long lda, void* D, long long ldd, const void* bias, int M, int N, int K,
+                               const unsigned long long* bases, int world, unsigned long long shard_off,
+                               unsigned long long shard_bytes, void* full, unsigned long long w_byte_off, unsigned int* flags,
+                               unsigned int epoch, int chunk_lo, int chunk_hi, int* status, cudaStream_t stream) {
+  using namespace mtb;
+  if (M <= 0 || N <= 0 || K <= 0) return -10;
+  if (N % 8 || ldd % 8 || K % 8 || world < 1 || world > GATHER_MAX_RANKS || shard_bytes % 16 || w_byte_off % 16) return -10;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, reinterpret_cast<const unsigned char*>(full) + w_byte_off, K, N, K, BK, BN);
+  if (rc) return rc - 10;
+  GemmParams p{M, N, K, D, ldd, nullptr, 0, reinterpret_cast<const __nv_bfloat16*>(bias), status};
+  GatherParams g{};
+  for (int i = 0; i < world; ++i) g.peer_base[i] = bases[i];
+  g.shard_off = shard_off; g.shard_bytes = shard_bytes; g.dst = reinterpret_cast<unsigned char*>(full);
+  g.flags = flags; g.epoch = epoch; g.world = world; g.chunk_lo = chunk_lo; g.chunk_hi = chunk_hi;
+  g.b_byte_off = w_byte_off;
+  int first = static_cast<int>(w_byte_off / GATHER_CHUNK_BYTES);
+  g.chunk_first = first < chunk_lo ? chunk_lo : (first >= chunk_hi ? chunk_lo : first);
+  return launch<false, false, false, true>(ta, tb, p, stream, &g);
 }
 
 }  // extern "C"

@@ -50,12 +50,14 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
 
 // ---------------------------------------------------------------------------------- all-gather
 // dst[p * shard_bytes + i] = arena_p[src_off + i] for every rank p; 16-byte accesses.
+// Only 16-byte vectors [vec_lo, vec_hi) of the full buffer are copied (the whole buffer by default).
 __global__ void __launch_bounds__(1024) symm_allgather_kernel(PeerTable peers, unsigned long long src_off, unsigned long long shard_bytes,
-                                                             uint8_t* __restrict__ dst, int world) {
+                                                             uint8_t* __restrict__ dst, int world, unsigned long long vec_lo,
+                                                             unsigned long long vec_hi) {
   const unsigned long long vec_per = shard_bytes >> 4;
-  const unsigned long long total = vec_per * world;
+  const unsigned long long total = vec_hi;
   const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
-  unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  unsigned long long i = vec_lo + static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   // 4 independent loads in flight per thread
   for (; i + 3 * stride < total; i += 4 * stride) {
     uint4 v[4];
@@ -201,10 +203,14 @@ using namespace mtb;
 extern "C" {
 
 // bases: host array of `world` arena addresses. Offsets are byte offsets inside the arena.
+// byte_lo/byte_hi (multiples of 16) restrict the copy to that range of the full buffer; byte_hi = 0 means everything.
 int mtb200_symm_allgather(const unsigned long long* bases, int world, unsigned long long src_off, unsigned long long shard_bytes,
-                          void* dst, int blocks, cudaStream_t st) {
-  if (world < 1 || world > MAX_RANKS || shard_bytes % 16 || src_off % 16) return -10;
-  symm_allgather_kernel<<<blocks, 1024, 0, st>>>(make_table(bases, world), src_off, shard_bytes, reinterpret_cast<uint8_t*>(dst), world);
+                          void* dst, unsigned long long byte_lo, unsigned long long byte_hi, int blocks, cudaStream_t st) {
+  if (world < 1 || world > MAX_RANKS || shard_bytes % 16 || src_off % 16 || byte_lo % 16 || byte_hi % 16) return -10;
+  if (byte_hi == 0) byte_hi = shard_bytes * world;
+  if (byte_hi > shard_bytes * world || byte_lo > byte_hi) return -10;
+  symm_allgather_kernel<<<blocks, 1024, 0, st>>>(make_table(bases, world), src_off, shard_bytes, reinterpret_cast<uint8_t*>(dst), world,
+                                                 byte_lo >> 4, byte_hi >> 4);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

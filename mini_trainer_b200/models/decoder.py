@@ -82,8 +82,11 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     ``saved_attn = (attn, lse)`` from an earlier forward skips the attention kernel (used by the
     recompute of blocks whose attention output was kept); ``want_attn`` returns that pair.
     """
+    plan = p.get("_gather")   # all-gather of this block's parameters fused into its first GEMMs
+    if plan is not None:
+        plan.prefetch_small()
     n1, rstd1 = ops.rmsnorm(x, p["ln1"], cfg.rms_norm_eps)
-    qkv = ops.linear(n1, p["wqkv"], p.get("bqkv"))
+    qkv = ops.linear(n1, p["wqkv"], p.get("bqkv"), gather=None if plan is None else (plan, 0))
     ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
     if saved_attn is not None:
         attn, lse = saved_attn
@@ -92,7 +95,7 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
                                   cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
     h1 = ops.linear(attn, p["wo"], None, x)
     n2, rstd2 = ops.rmsnorm(h1, p["ln2"], cfg.rms_norm_eps)
-    gu = ops.linear(n2, p["wgu"])
+    gu = ops.linear(n2, p["wgu"], gather=None if plan is None else (plan, 1))
     act = ops.swiglu(gu)
     out = ops.linear(act, p["wd"], None, h1)
     acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, gu, act) if keep else None

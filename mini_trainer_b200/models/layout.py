@@ -60,10 +60,11 @@ class GroupLayout:
 
 def block_entries(cfg: ModelConfig) -> list:
     h, f = cfg.hidden_size, cfg.intermediate_size
-    e = [("ln1", (h,)), ("wqkv", (cfg.qkv_size, h))]
+    # the small tensors needed before the first GEMM come first (see parallel.symmetric.GatherPlan)
+    e = [("ln1", (h,))]
     if cfg.attention_bias:
         e.append(("bqkv", (cfg.qkv_size,)))
-    e += [("wo", (h, cfg.q_size)), ("ln2", (h,)), ("wgu", (2 * f, h)), ("wd", (h, f))]
+    e += [("wqkv", (cfg.qkv_size, h)), ("wo", (h, cfg.q_size)), ("ln2", (h,)), ("wgu", (2 * f, h)), ("wd", (h, f))]
     return e
 
 

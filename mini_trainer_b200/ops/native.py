@@ -174,10 +174,18 @@ class NativeOps:
         return dx
 
     # -- linear -----------------------------------------------------------------------
-    def linear(self, x, w, bias=None, residual=None):
+    def linear(self, x, w, bias=None, residual=None, gather=None):
+        """``gather = (GatherPlan, stage)`` runs the projection with the all-gather of its parameter
+        group fused into the same kernel (symmetric-memory backend only)."""
         T, K = x.shape
         N = w.shape[0]
         out = torch.empty(T, N, dtype=x.dtype, device=self.device)
+        if gather is not None:
+            assert residual is None
+            ev = self._ev()
+            gather[0].launch(self, x, w, bias, out, gather[1])
+            self._ev_end("gemm_nt_allgather", ev)
+            return out
         return self.gemm(x, False, w, False, out, T, N, K, residual=residual, bias=bias)
 
     def linear_dgrad(self, dy, w):

@@ -53,7 +53,7 @@ class TorchOps:
         return dx.to(x.dtype)
 
     # -- linear -----------------------------------------------------------------------
-    def linear(self, x, w, bias=None, residual=None):
+    def linear(self, x, w, bias=None, residual=None, gather=None):
         y = x @ w.t()
         if bias is not None:
             y = y + bias

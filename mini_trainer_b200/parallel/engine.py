@@ -27,6 +27,7 @@ from __future__ import annotations
 
 import contextlib
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Iterator, Optional
 
@@ -116,6 +117,7 @@ class ShardedEngine:
         # Buffers that peers read (parameter shards, gradient buffers) live in the comm backend's
         # symmetric arena when it has one; otherwise they are ordinary device tensors.
         self.symmetric = hasattr(self.comm, "setup")
+        self.fused_gather = self.symmetric and os.environ.get("MTB200_FUSED_GATHER", "1") != "0"
         if self.symmetric:
             es = torch.empty(0, dtype=self.param_dtype).element_size()
             payload = sum(l.shard_numel for l in layouts) + nbuf * blk + layouts[0].padded_numel + layouts[-1].padded_numel
@@ -214,13 +216,21 @@ class ShardedEngine:
     # ------------------------------------------------------------------------------------
     # gather / reduce plumbing
     # ------------------------------------------------------------------------------------
-    def _gather_block(self, i: int):
-        """Starts gathering block ``i`` on the side stream; returns (views, ready_event, slot)."""
+    def _gather_block(self, i: int, fused: bool = False):
+        """Starts gathering block ``i`` on the side stream; returns (views, ready_event, slot).
+
+        ``fused`` (symmetric backend): nothing is launched here; the views carry a gather plan and
+        the block's QKV and gate/up GEMMs pull the parameters from the peers while they run."""
         grp = self.blocks[i]
         if self.world == 1:
             return grp.layout.views(grp.shard), None, -1
         slot = i % len(self._pbufs)
         buf = self._pbufs[slot]
+        if fused and self.fused_gather:
+            _Side.wait(self._pbuf_free[slot])
+            views = grp.layout.views(buf)
+            views["_gather"] = self.comm.gather_plan(grp.shard, buf, grp.layout, split_before="wgu", small_until="wqkv")
+            return views, None, slot
         with self.side.run(wait_current=False):
             if self.side.cuda and self._pbuf_free[slot] is not None:
                 self.side.stream.wait_event(self._pbuf_free[slot])
@@ -353,11 +363,11 @@ class ShardedEngine:
             del emb_views, emb_full
         saved = []
         levels = self.plan_checkpointing(batch.num_tokens)
-        nxt = self._gather_block(0)
+        nxt = self._gather_block(0, fused=True)
         for i in range(nL):
             p, ev, slot = nxt
             _Side.wait(ev)
-            nxt = self._gather_block(i + 1) if i + 1 < nL else None
+            nxt = self._gather_block(i + 1, fused=True) if i + 1 < nL else None
             xin = x
             x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq, keep=levels[i] == 0,
                                                   want_attn=levels[i] == 1)
@@ -382,11 +392,13 @@ class ShardedEngine:
         self._root_free["head"] = self._reduce(self.head, hg_full, last=last)
 
         # ---- backward through the blocks ----
-        cur = (last_block[0], None, last_block[1])
+        cur = ({k: v for k, v in last_block[0].items() if k != "_gather"}, None, last_block[1])   # already gathered
         for i in range(nL - 1, -1, -1):
             p, ev, slot = cur
             _Side.wait(ev)
-            cur = self._gather_block(i - 1) if i > 0 else None
+            # a block that will be recomputed gathers inside its recompute GEMMs; one whose activations
+            # were all kept has no forward GEMM left, so its parameters are prefetched on the side stream
+            cur = self._gather_block(i - 1, fused=saved[i - 1][1] is None) if i > 0 else None
             gbuf, gslot = self._grad_buffer(i)
             g = self.blocks[i].layout.views(gbuf)
             xin, acts, attn_state = saved.pop()

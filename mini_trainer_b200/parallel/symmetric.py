@@ -60,7 +60,8 @@ class SymmetricComm:
     def _bind(self):
         P, I, L, U, UL = c_void_p, c_int, c_longlong, c_uint, c_ulonglong
         sig = {
-            "mtb200_symm_allgather": [P, I, UL, UL, P, I, P],
+            "mtb200_symm_allgather": [P, I, UL, UL, P, UL, UL, I, P],
+            "mtb200_gemm_bf16_allgather": [P, L, P, L, P, I, I, I, P, I, UL, UL, P, UL, P, U, I, I, P, P],
             "mtb200_symm_signal": [P, I, I, UL, U, P],
             "mtb200_symm_wait": [P, I, U, U, I, P, P],
             "mtb200_symm_reduce_scatter": [P, I, I, UL, L, P, I, P, P, UL, U, U, P, P, I, P],
@@ -144,9 +145,14 @@ class SymmetricComm:
         self.launches += 1
 
     # -- collectives ------------------------------------------------------------------
-    def all_gather(self, shard, full, blocks: int = 32):
+    def all_gather(self, shard, full, blocks: int = 32, byte_lo: int = 0, byte_hi: int = 0):
+        """Pulls every rank's shard into ``full`` (optionally only bytes [byte_lo, byte_hi) of it)."""
         self._call("mtb200_symm_allgather", self._bases, self.world, self._offset(shard),
-                   shard.numel() * shard.element_size(), full.data_ptr(), blocks, self._st())
+                   shard.numel() * shard.element_size(), full.data_ptr(), byte_lo, byte_hi, blocks, self._st())
+
+    def gather_plan(self, shard, full, layout, split_before: str, small_until: str):
+        """Plan for gathering one parameter group INSIDE its consuming GEMMs (see ``GatherPlan``)."""
+        return GatherPlan(self, shard, full, layout, split_before, small_until)
 
     def grad_ready(self, gfull):
         ch = self._channel(gfull)
@@ -191,3 +197,54 @@ class SymmetricComm:
         if code:
             self.status.zero_()
             raise RuntimeError(f"symmetric comm: a bounded wait on a peer expired (code {code & 0xff}, peer {code >> 8})")
+
+
+GATHER_CHUNK_BYTES = 128 * 1024
+
+
+class GatherPlan:
+    """All-gather of one parameter group fused into the GEMMs that first read it.
+
+    The group's full buffer is cut into 128 KB chunks. Launch ``stage 0`` (the QKV projection)
+    gathers the chunks up to the tensor named ``split_before`` while it multiplies; ``stage 1``
+    (the gate/up projection) gathers the rest. Inside each launch, extra warps pull the chunks
+    from the peers and flag them; the GEMM's TMA producer waits for the flags of the chunks under
+    each weight tile. The few parameters needed BEFORE the first GEMM (the input norm weight and
+    the q/k/v bias, laid out first in the buffer) are pulled by a tiny separate copy.
+    """
+
+    _state = {}   # per full buffer: (flags tensor, epoch)
+
+    def __init__(self, comm, shard, full, layout, split_before, small_until):
+        self.comm, self.shard, self.full, self.layout = comm, shard, full, layout
+        es = full.element_size()
+        total = full.numel() * es
+        self.n_chunks = -(-total // GATHER_CHUNK_BYTES)
+        self.split = min(self.n_chunks, -(-(layout.specs[split_before].offset * es) // GATHER_CHUNK_BYTES))
+        self.small_bytes = -(-(layout.specs[small_until].offset * es) // 16) * 16
+        key = full.data_ptr()
+        st = GatherPlan._state.get(key)
+        if st is None or st[0].numel() != self.n_chunks:
+            st = [torch.zeros(self.n_chunks, dtype=torch.int32, device=full.device), 0]
+            GatherPlan._state[key] = st
+        st[1] += 1
+        self.flags, self.epoch = st[0], st[1]
+
+    def prefetch_small(self):
+        if self.small_bytes:
+            self.comm.all_gather(self.shard, self.full, blocks=1, byte_lo=0, byte_hi=self.small_bytes)
+
+    def launch(self, ops, x, w, bias, out, stage: int):
+        c = self.comm
+        lo, hi = (0, self.split) if stage == 0 else (self.split, self.n_chunks)
+        M, K = x.shape
+        N = w.shape[0]
+        rc = c.lib.mtb200_gemm_bf16_allgather(
+            x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), None if bias is None else bias.data_ptr(), M, N, K,
+            c._bases, c.world, c._offset(self.shard), self.shard.numel() * self.shard.element_size(), self.full.data_ptr(),
+            w.data_ptr() - self.full.data_ptr(), self.flags.data_ptr(), self.epoch, lo, hi, ops.status.data_ptr(), ops._st())
+        if rc != 0:
+            raise RuntimeError(f"mtb200_gemm_bf16_allgather failed with code {rc}")
+        ops.launches += 1
+        c.launches += 1
+        return out

@@ -1,0 +1,73 @@
+"""OSFT: factor gradients, orthogonal projection and the recomposed update against a float64
+autograd oracle that trains the same low-subspace factors directly."""
+import torch
+
+from mini_trainer_b200.models.config import ModelConfig
+from mini_trainer_b200.models.torch_oracle import oracle_per_token_loss
+from mini_trainer_b200.ops import get_ops
+from mini_trainer_b200.parallel import osft as O
+from mini_trainer_b200.parallel.engine import OptimConfig, ShardedEngine
+from tests.test_engine_cpu import make_mb
+
+
+def test_projection_removes_frozen_subspace():
+    torch.manual_seed(0)
+    w = torch.randn(24, 40, dtype=torch.float64)
+    u_hi, s_hi, v_hi, u_lo, s_lo, v_lo = O.svd_split(w, 0.5)
+    assert torch.allclose((u_hi * s_hi) @ v_hi + (u_lo * s_lo) @ v_lo, w, atol=1e-10)
+    g = torch.randn_like(w)
+    du, ds, dv = O.factor_grads(g, u_lo, s_lo, v_lo)
+    # chain rule check against autograd
+    ul, sl, vl = (t.clone().requires_grad_(True) for t in (u_lo, s_lo, v_lo))
+    (((ul * sl) @ vl) * g).sum().backward()
+    assert torch.allclose(du, ul.grad) and torch.allclose(ds, sl.grad) and torch.allclose(dv, vl.grad)
+    du, dv = O.project_orthogonal(du + u_hi @ torch.randn(u_hi.shape[1], du.shape[1], dtype=torch.float64), dv, u_hi, v_hi)
+    assert (u_hi.t() @ du).abs().max() < 1e-10 and (dv @ v_hi.t()).abs().max() < 1e-10
+
+
+def test_osft_training_matches_float64_oracle():
+    cfg = ModelConfig(vocab_size=61, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, tie_word_embeddings=False, attention_bias=True)
+    eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), optim=OptimConfig(max_grad_norm=1.0))
+    eng.init_random(seed=4, std=0.2)
+    ctl = O.enable_osft(eng, rank_ratio=0.5)
+
+    # oracle parameters: the controller's own factors (an SVD is only unique up to signs) in float64
+    base = {k: v.double() for k, v in eng.iter_hf_tensors(dtype=torch.float32)}
+    label = {(n, r0): lab for n, r0, r1, lab in O.osft_targets(cfg)}
+    fac = {}
+    for mt in ctl.mats:
+        pre = f"model.layers.{mt.block}." + ("self_attn." if "proj" in label[(mt.name, mt.r0)] and label[(mt.name, mt.r0)][0] in "qkvo" else "mlp.")
+        key = pre + label[(mt.name, mt.r0)] + ".weight"
+        fac[key] = dict(w_hi=mt.w_hi.double(), u_hi=mt.u_hi.double(), v_hi=mt.v_hi.double(),
+                        p=[t.double().clone().requires_grad_(True) for t in mt.factors])
+        del base[key]
+    others = {k: v.clone().requires_grad_(True) for k, v in base.items()}
+    leaves = [t for f in fac.values() for t in f["p"]] + list(others.values())
+    opt = torch.optim.AdamW(leaves, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.0)
+
+    for step in range(2):
+        mb = make_mb([9, 5, 7], cfg.vocab_size, seed=step)
+        out = eng.train_step([mb], lr=1e-2)
+        sd = dict(others)
+        for k, f in fac.items():
+            u, s, v = f["p"]
+            sd[k] = f["w_hi"] + (u * s) @ v
+        loss = oracle_per_token_loss(cfg, sd, mb["input_ids"][0], mb["labels"][0], mb["position_ids"][0]).double()
+        (loss.sum() / mb["batch_num_loss_counted_tokens"]).backward()
+        for f in fac.values():
+            u, s, v = f["p"]
+            du, dv = O.project_orthogonal(u.grad, v.grad, f["u_hi"], f["v_hi"])
+            u.grad, v.grad = du, dv
+        gn = torch.nn.utils.clip_grad_norm_(leaves, 1.0)
+        opt.step(); opt.zero_grad()
+        assert abs(out["grad_norm"].item() - gn.item()) < 2e-3 * gn.item()
+        assert abs(out["loss_sum"].item() - loss.sum().item()) < 1e-3 * loss.sum().item()
+
+    new = {k: v for k, v in eng.iter_hf_tensors(dtype=torch.float32)}
+    for k, f in fac.items():
+        u, s, v = f["p"]
+        ref = (f["w_hi"] + (u * s) @ v).detach().float()
+        assert torch.allclose(new[k], ref, atol=3e-4, rtol=1e-3), k
+    for k, v in others.items():
+        assert torch.allclose(new[k], v.detach().float(), atol=3e-4, rtol=1e-3), k
