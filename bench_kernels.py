@@ -1,0 +1,143 @@
+"""Per-kernel microbenchmarks with roofline fractions.
+
+    python bench_kernels.py --op gemm --layout nt --m 8192 --n 8192 --k 8192
+    python bench_kernels.py --op attn_fwd --lens 16384,16384
+    python bench_kernels.py --op all
+
+Each op is timed with CUDA events on the launching stream after warm-up, with a synchronize on
+both sides. Inputs are larger than the 126 MB L2 (or an L2-sized buffer is rewritten between
+iterations with ``--flush-l2``). The achieved figure is compared with the MEASURED peaks in
+``MEASURED_PEAKS.json`` (cuBLAS bf16 burst throughput, STREAM-style copy bandwidth) when that file
+is present, else with the fallback 1.59 PFLOP/s and 6.65 TB/s ("of fallback").
+This script is also the small-case driver for ``ncu`` captures (``--iters 1 --warmup 1``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from mini_trainer_b200.ops.native import NativeOps  # noqa: E402
+
+
+def peaks():
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return d["bf16_tflops"], d["hbm_gbs"], "of measured"
+    return 1590.0, 6650.0, "of fallback"
+
+
+def timeit(fn, iters, warmup, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all")
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--lens", default="16384,16384")
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--d", type=int, default=128)
+    ap.add_argument("--tokens", type=int, default=32768)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--flush-l2", action="store_true")
+    a = ap.parse_args()
+    ops = NativeOps("cuda:0")
+    tf_peak, bw_peak, tag = peaks()
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda") if a.flush_l2 else None
+    out = []
+
+    def report(name, ms, flops=None, bytes_=None):
+        rec = {"op": name, "ms": round(ms, 4)}
+        if flops:
+            rec["tflops"] = round(flops / ms / 1e9, 1)
+            rec["frac_compute"] = f"{flops / ms / 1e9 / tf_peak:.3f} {tag} cuBLAS bf16"
+        if bytes_:
+            rec["gbs"] = round(bytes_ / ms / 1e6, 1)
+            rec["frac_hbm"] = f"{bytes_ / ms / 1e6 / bw_peak:.3f} {tag} copy bandwidth"
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
+
+    want = lambda n: a.op in ("all", n)
+    if want("gemm"):
+        M, N, K = a.m, a.n, a.k
+        for lay in (["nt", "nn", "tn"] if a.op == "all" else [a.layout]):
+            if lay == "nt":
+                x, w = bf(M, K), bf(N, K, scale=0.02)
+                o = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+                fn = lambda: ops.gemm(x, False, w, False, o, M, N, K)
+            elif lay == "nn":
+                x, w = bf(M, K), bf(K, N, scale=0.02)
+                o = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+                fn = lambda: ops.gemm(x, False, w, True, o, M, N, K)
+            else:
+                x, w = bf(K, M), bf(K, N, scale=0.02)
+                o = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+                fn = lambda: ops.gemm(x, True, w, True, o, M, N, K)
+            report(f"gemm_{lay}_{M}x{N}x{K}", timeit(fn, a.iters, a.warmup, flush), flops=2.0 * M * N * K)
+    if want("attn_fwd") or want("attn_bwd"):
+        lens = [int(v) for v in a.lens.split(",")]
+        T = sum(lens)
+        qkv, dout = bf(T, (a.hq + 2 * a.hkv) * a.d), bf(T, a.hq * a.d)
+        cu_host = [0]
+        for n in lens:
+            cu_host.append(cu_host[-1] + n)
+        cu = torch.tensor(cu_host, dtype=torch.int32, device="cuda")
+        fl = sum(4.0 * n * n / 2 * a.hq * a.d for n in lens)
+        o, lse = ops.attention(qkv, cu, cu_host, max(lens), a.hq, a.hkv, a.d)
+        if want("attn_fwd"):
+            report(f"attn_fwd_T{T}", timeit(lambda: ops.attention(qkv, cu, cu_host, max(lens), a.hq, a.hkv, a.d), a.iters, a.warmup, flush), flops=fl)
+        if want("attn_bwd"):
+            report(f"attn_bwd_T{T}", timeit(lambda: ops.attention_bwd(dout, qkv, o, lse, cu, cu_host, max(lens), a.hq, a.hkv, a.d), a.iters, a.warmup, flush), flops=2.5 * fl)
+    if want("rmsnorm"):
+        T, H = a.tokens, a.hidden
+        x, w, dy = bf(T, H), bf(H), bf(T, H)
+        y, rstd = ops.rmsnorm(x, w, 1e-5)
+        dw = torch.empty_like(w)
+        report(f"rmsnorm_fwd_{T}x{H}", timeit(lambda: ops.rmsnorm(x, w, 1e-5), a.iters, a.warmup, flush), bytes_=2.0 * T * H * 2)
+        report(f"rmsnorm_bwd_{T}x{H}", timeit(lambda: ops.rmsnorm_bwd(dy, x, rstd, w, dw, add_to=dy), a.iters, a.warmup, flush), bytes_=4.0 * T * H * 2)
+    if want("swiglu"):
+        T, F = a.tokens, 14336
+        gu, da = bf(T, 2 * F), bf(T, F)
+        report(f"swiglu_fwd_{T}x{F}", timeit(lambda: ops.swiglu(gu), a.iters, a.warmup, flush), bytes_=3.0 * T * F * 2)
+        report(f"swiglu_bwd_{T}x{F}", timeit(lambda: ops.swiglu_bwd(da, gu), a.iters, a.warmup, flush), bytes_=5.0 * T * F * 2)
+    if want("adamw"):
+        n = 512 * 1024 * 1024
+        master, m, v, g = (torch.zeros(n, device="cuda") for _ in range(4))
+        p = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        coef = torch.ones(1, device="cuda")
+        report(f"adamw_{n}", timeit(lambda: ops.adamw_step(master, m, v, g, p, 1e-4, 0.9, 0.95, 1e-8, 0.0, 2, coef), a.iters, a.warmup, flush),
+               bytes_=n * (4 * 4 + 3 * 4 + 2.0))
+    ops.check_status()
+
+
+if __name__ == "__main__":
+    main()
