@@ -227,3 +227,22 @@ def test_attention_backward(ops, D, hq, hkv, lens):
     assert rel_err(dqkv[:, :q_end], rd[:, :q_end]) < 2e-2
     assert rel_err(dqkv[:, q_end:k_end], rd[:, q_end:k_end]) < 2e-2
     assert rel_err(dqkv[:, k_end:], rd[:, k_end:]) < 2e-2
+
+
+def test_bounded_wait_expires_with_status_and_context_stays_usable(ops):
+    """A wait on a flag that nothing sets must run out, record {code, peer} and return."""
+    import ctypes
+    lib = ops.lib
+    fn = lib.mtb200_symm_wait
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_uint, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
+    flags[0] = 5                                   # "peer 0" already signalled epoch 5, "peer 1" never does
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = fn(flags.data_ptr(), 2, 5, 2000, 42, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    code = int(status.item())
+    assert code & 0xff == 42 and code >> 8 == 1
+    x = torch.ones(1024, device="cuda")
+    assert x.sum().item() == 1024                  # the context is still healthy
