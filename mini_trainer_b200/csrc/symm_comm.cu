@@ -95,6 +95,7 @@ __global__ void symm_wait_kernel(const uint32_t* __restrict__ my_flags, int worl
 // ---------------------------------------------------------------------------------- reduce-scatter
 // acc[i] (+)= sum_p bf16 grad_p[rank * n + i]; optional sumsq of the result. After all blocks have
 // read, the last one signals "consumed" (epoch) to every peer.
+template <int MAXW>   // compile-time bound on the rank count keeps the per-peer vectors in registers
 __global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable peers, unsigned long long grad_off, long long n,
                                                                  float* __restrict__ acc, int accumulate, float* __restrict__ sumsq,
                                                                  const uint32_t* __restrict__ ready_flags, unsigned long long consumed_off,
@@ -113,30 +114,41 @@ __global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable peer
   if (ok_s) {
     const long long nvec = n >> 3;
     const unsigned long long slice_off = grad_off + static_cast<unsigned long long>(rank) * n * 2;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-      float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      uint4 v[MAX_RANKS];
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    // two independent vectors per thread and iteration: 2 x world peer loads in flight
+    for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += 2 * stride) {
+      const long long idx[2] = {i0, i0 + stride};
+      uint4 v[2][MAXW];
 #pragma unroll
-      for (int p = 0; p < MAX_RANKS; ++p)
-        if (p < world) v[p] = *(reinterpret_cast<const uint4*>(peers.base[p] + slice_off) + i);
+      for (int u = 0; u < 2; ++u) {
+        if (idx[u] < nvec) {
 #pragma unroll
-      for (int p = 0; p < MAX_RANKS; ++p) {
-        if (p < world) {
-          const float2 a = unpack_bf16(v[p].x), b = unpack_bf16(v[p].y), c = unpack_bf16(v[p].z), d = unpack_bf16(v[p].w);
-          f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y; f[4] += c.x; f[5] += c.y; f[6] += d.x; f[7] += d.y;
+          for (int p = 0; p < MAXW; ++p)
+            if (p < world) v[u][p] = *(reinterpret_cast<const uint4*>(peers.base[p] + slice_off) + idx[u]);
         }
       }
-      float4* dst = reinterpret_cast<float4*>(acc) + 2 * i;
-      if (accumulate) {
-        const float4 a = dst[0], b = dst[1];
-        f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w; f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
-      }
-      dst[0] = make_float4(f[0], f[1], f[2], f[3]);
-      dst[1] = make_float4(f[4], f[5], f[6], f[7]);
-      if (sumsq != nullptr) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) ss += f[k] * f[k];
+      for (int u = 0; u < 2; ++u) {
+        if (idx[u] >= nvec) continue;
+        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int p = 0; p < MAXW; ++p) {
+          if (p < world) {
+            const float2 a = unpack_bf16(v[u][p].x), b = unpack_bf16(v[u][p].y), c = unpack_bf16(v[u][p].z), d = unpack_bf16(v[u][p].w);
+            f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y; f[4] += c.x; f[5] += c.y; f[6] += d.x; f[7] += d.y;
+          }
+        }
+        float4* dst = reinterpret_cast<float4*>(acc) + 2 * idx[u];
+        if (accumulate) {
+          const float4 a = dst[0], b = dst[1];
+          f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w; f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+        }
+        dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+        dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+        if (sumsq != nullptr) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) ss += f[k] * f[k];
+        }
       }
     }
   }
@@ -231,9 +243,12 @@ int mtb200_symm_reduce_scatter(const unsigned long long* bases, int world, int r
                                unsigned int epoch, unsigned int limit, unsigned int* block_counter, int* status, int blocks,
                                cudaStream_t st) {
   if (world < 1 || world > MAX_RANKS || n % 8 || grad_off % 16) return -10;
-  symm_reduce_scatter_kernel<<<blocks, 512, 0, st>>>(make_table(bases, world), grad_off, n, acc, accumulate, sumsq,
-                                                     reinterpret_cast<const uint32_t*>(ready_flags), consumed_off, epoch,
-                                                     limit ? limit : FLAG_SPIN_LIMIT, rank, world, block_counter, status);
+#define MTB_RS(W)                                                                                                       \
+  symm_reduce_scatter_kernel<W><<<blocks, 512, 0, st>>>(make_table(bases, world), grad_off, n, acc, accumulate, sumsq,    \
+                                                        reinterpret_cast<const uint32_t*>(ready_flags), consumed_off, epoch, \
+                                                        limit ? limit : FLAG_SPIN_LIMIT, rank, world, block_counter, status)
+  if (world <= 2) MTB_RS(2); else if (world <= 4) MTB_RS(4); else if (world <= 8) MTB_RS(8); else MTB_RS(16);
+#undef MTB_RS
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -24,6 +24,11 @@ from __future__ import annotations
 
 import ctypes
 import os
+
+# The arena is only ever accessed with plain peer loads/stores, so it is not bound to an NVLink
+# multicast object: a rank that dies while its memory is bound to one can fault its peers' GPUs.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
 from ctypes import c_int, c_longlong, c_uint, c_ulonglong, c_void_p
 
 import torch
@@ -145,7 +150,7 @@ class SymmetricComm:
         self.launches += 1
 
     # -- collectives ------------------------------------------------------------------
-    def all_gather(self, shard, full, blocks: int = 32, byte_lo: int = 0, byte_hi: int = 0):
+    def all_gather(self, shard, full, blocks: int = 96, byte_lo: int = 0, byte_hi: int = 0):
         """Pulls every rank's shard into ``full`` (optionally only bytes [byte_lo, byte_hi) of it)."""
         self._call("mtb200_symm_allgather", self._bases, self.world, self._offset(shard),
                    shard.numel() * shard.element_size(), full.data_ptr(), byte_lo, byte_hi, blocks, self._st())
@@ -159,7 +164,7 @@ class SymmetricComm:
         self._epoch[ch] += 1
         self._call("mtb200_symm_signal", self._bases, self.world, self.rank, self._ready_off(ch), self._epoch[ch], self._st())
 
-    def reduce_scatter_accumulate(self, gfull, acc, accumulate: bool, scratch=None, sumsq=None, blocks: int = 32):
+    def reduce_scatter_accumulate(self, gfull, acc, accumulate: bool, scratch=None, sumsq=None, blocks: int = 296):
         ch = self._channel(gfull)
         base = self.arena.data_ptr()
         self._call("mtb200_symm_reduce_scatter", self._bases, self.world, self.rank, self._offset(gfull), acc.numel(),
