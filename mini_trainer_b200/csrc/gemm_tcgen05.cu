@@ -48,11 +48,11 @@ struct GemmParams {
   int* status;            // device word; set non-zero when a bounded wait expired
 };
 
-// Fused all-gather: while the GEMM runs, four extra warps per CTA pull this parameter group's
+// Fused all-gather: while the GEMM runs, eight extra warps per CTA pull this parameter group's
 // shards from every peer's symmetric arena (plain peer loads over NVLink) into the local full
 // buffer that the B tensor map points at, 128 KB chunk by chunk, and publish each finished chunk
 // in a flag array. The TMA producer only loads a B tile after the chunks under it are flagged.
-constexpr int GATHER_THREADS = 128;
+constexpr int GATHER_THREADS = 256;
 constexpr int GATHER_CHUNK_BYTES = 128 * 1024;
 constexpr int GATHER_MAX_RANKS = 16;
 
@@ -188,7 +188,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
     }
   } else if (GATHER && warp >= 6) {
-    // ------------------------------------------------------------------ gather warps (6..9)
+    // ------------------------------------------------------------------ gather warps (6..13)
     const int gt = threadIdx.x - GEMM_THREADS;
     const int n_chunks = g.chunk_hi - g.chunk_lo;
     const unsigned long long total = g.shard_bytes * g.world;

@@ -84,18 +84,27 @@ class TorchDistComm:
         dist.barrier(group=self.group)
 
 
-def make_comm(kind: str = "auto", device=None):
-    """``auto``: local for one rank, otherwise torch.distributed (NCCL/gloo).
+def _single_node() -> bool:
+    import os
+    lws = os.environ.get("LOCAL_WORLD_SIZE")
+    return lws is not None and int(lws) == dist.get_world_size()
 
-    ``symmetric`` selects the in-kernel NVLink path and falls back to an error (never silently)
-    if symmetric memory cannot be set up.
+
+def make_comm(kind: str = "auto", device=None):
+    """``auto``: local for one rank; the symmetric-memory NVLink backend when all ranks are GPUs
+    of one node; otherwise ``torch.distributed`` (NCCL across nodes, gloo on CPU).
+
+    ``symmetric`` / ``torchdist`` force a backend. A requested symmetric backend that cannot be set
+    up is an error, never a silent fallback.
     """
+    import torch
     world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
     if world == 1:
         return LocalComm()
-    if kind in ("auto", "torchdist", "nccl", "gloo"):
-        return TorchDistComm()
-    if kind == "symmetric":
+    on_gpu = device is not None and torch.device(device).type == "cuda"
+    if kind == "symmetric" or (kind == "auto" and on_gpu and _single_node()):
         from .symmetric import SymmetricComm
         return SymmetricComm(device)
+    if kind in ("auto", "torchdist", "nccl", "gloo"):
+        return TorchDistComm()
     raise ValueError(f"unknown comm backend {kind!r}")

@@ -91,10 +91,22 @@ class _Side:
         ev.record(self.stream)
         return ev
 
+    # When a list is installed here, every wait of the compute stream on communication work is
+    # bracketed by two events, so the time the compute stream really stalled can be summed later.
+    stalls = None
+
     @staticmethod
     def wait(ev):
         if ev is not None:
-            torch.cuda.current_stream().wait_event(ev)
+            cur = torch.cuda.current_stream()
+            if _Side.stalls is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(cur)
+                cur.wait_event(ev)
+                e1.record(cur)
+                _Side.stalls.append((e0, e1))
+            else:
+                cur.wait_event(ev)
 
 
 class ShardedEngine:
@@ -280,7 +292,7 @@ class ShardedEngine:
         _Side.wait(self._gbuf_free[slot])
         self._gbuf_free[slot] = None
         if self.symmetric:
-            self.comm.wait_consumed(self._gbufs[slot])
+            self._timed_comm(lambda: self.comm.wait_consumed(self._gbufs[slot]))
         return self._gbufs[slot], slot
 
     def _root_grad_buffer(self, which: str) -> torch.Tensor:
@@ -288,7 +300,7 @@ class ShardedEngine:
         buf = self._eg_full if which == "embed" else self._hg_full
         _Side.wait(self._root_free[which])
         if self.symmetric:
-            self.comm.wait_consumed(buf)
+            self._timed_comm(lambda: self.comm.wait_consumed(buf))
         buf.zero_()
         return buf
 
@@ -424,7 +436,7 @@ class ShardedEngine:
     def optimizer_step(self, lr: float) -> torch.Tensor:
         """Global-norm clip + AdamW on the shards. Returns the pre-clip gradient norm (0-dim)."""
         if self.side.cuda:
-            torch.cuda.current_stream().wait_stream(self.side.stream)
+            _Side.wait(self.side.record())   # the last reductions must have landed
         o = self.optim
         live = [g for g in self.groups if g.has_grad]
         sq = self._sq
@@ -444,11 +456,37 @@ class ShardedEngine:
             g.has_grad = False
             g.sq_done = False
         self._sq = torch.zeros(1, dtype=torch.float32, device=self.device)
-        if self.symmetric:
-            self.comm.barrier()   # no peer may pull a shard before every rank has finished updating its own
+        if self.symmetric:   # no peer may pull a shard before every rank has finished updating its own
+            self._timed_comm(self.comm.barrier)
         if self.side.cuda:
             self.side.stream.wait_stream(torch.cuda.current_stream())
         return norm
+
+    def measure_exposed_comm(self, on: bool = True) -> None:
+        """Starts (or stops) recording how long the compute stream waits for communication: gathers
+        that are not ready, gradient buffers still being reduced, peers' "consumed" signals, the
+        reductions still running when the optimizer starts and the post-step barrier."""
+        _Side.stalls = [] if on else None
+
+    def exposed_comm_ms(self) -> float:
+        """Sum of the recorded stalls in milliseconds (synchronises the device); clears the record."""
+        if _Side.stalls is None:
+            return 0.0
+        torch.cuda.synchronize(self.device)
+        total = sum(a.elapsed_time(b) for a, b in _Side.stalls)
+        _Side.stalls = []
+        return total
+
+    def _timed_comm(self, fn):
+        """Runs a device-side wait (a kernel that polls peers' flags) inside a stall bracket."""
+        if _Side.stalls is None:
+            return fn()
+        cur = torch.cuda.current_stream()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(cur)
+        fn()
+        e1.record(cur)
+        _Side.stalls.append((e0, e1))
 
     def zero_grad(self) -> None:
         for g in self.groups:

@@ -150,7 +150,7 @@ class SymmetricComm:
         self.launches += 1
 
     # -- collectives ------------------------------------------------------------------
-    def all_gather(self, shard, full, blocks: int = 96, byte_lo: int = 0, byte_hi: int = 0):
+    def all_gather(self, shard, full, blocks: int = 296, byte_lo: int = 0, byte_hi: int = 0):
         """Pulls every rank's shard into ``full`` (optionally only bytes [byte_lo, byte_hi) of it)."""
         self._call("mtb200_symm_allgather", self._bases, self.world, self._offset(shard),
                    shard.numel() * shard.element_size(), full.data_ptr(), byte_lo, byte_hi, blocks, self._st())

@@ -48,3 +48,23 @@ def test_native_engine_matches_fp32_reference(attention):
     n1, n2 = eng.optimizer_step(1e-4), ref.optimizer_step(1e-4)
     assert abs(n1.item() - n2.item()) < 3e-2 * n2.item()
     assert ops.launches > 0
+
+
+def test_osft_step_runs_with_native_kernels():
+    from mini_trainer_b200.ops.native import NativeOps
+    from mini_trainer_b200.parallel.osft import enable_osft
+    cfg = get_preset("smoke-llama")
+    ops = NativeOps("cuda:0")
+    eng = ShardedEngine(cfg, "cuda:0", ops, optim=OptimConfig(), activation_budget_bytes=0)
+    eng.init_random(seed=2, std=0.05)
+    before = [g.master.clone() for g in eng.groups]
+    ctl = enable_osft(eng, rank_ratio=0.5)
+    mb = make_mb([200, 56, 384], cfg.vocab_size)
+    losses = []
+    for _ in range(3):
+        out = eng.train_step([mb], lr=2e-3)
+        losses.append(out["loss_sum"].item())
+    ops.check_status()
+    assert losses[-1] < losses[0]
+    assert any(not torch.equal(a, g.master) for a, g in zip(before, eng.groups))
+    assert len(ctl.mats) == 7 * cfg.num_hidden_layers
