@@ -7,8 +7,11 @@
 //   S  = Q K^T            dP = dO V^T                      (TMEM, 128 columns each)
 //   P  = exp(S*scale - lse), dS = P * (dP - delta) * scale  (4 warps; bf16 P and dS to smem)
 //   dQ = dS K  (into S's TMEM columns)   dV += P^T dO   dK += dS^T Q
-// dQ tiles are added into an fp32 [T, Hq*D] accumulator with vector atomics (several key blocks
-// contribute to one query block) and rounded to bf16 by a small kernel afterwards.
+// dQ tiles (several key blocks contribute to one query block) are staged in shared memory, in the
+// space of the P / dS tiles once the MMAs have read them, and added into an fp32 [T, Hq*D]
+// accumulator with TMA tensor reduces (cp.reduce.async.bulk.tensor .add, one 32-column x 128-row box
+// each, 128B-swizzled so the staging stores are free of bank conflicts); a small kernel rounds the
+// accumulator to bf16 afterwards.
 // P and dS are stored once as [query, key] 128B-swizzled tiles and read both K-major (for dQ) and
 // MN-major (for dV / dK), so no transposes are materialised.
 //
@@ -24,9 +27,11 @@ namespace mtb {
 
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer);
+int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                     uint32_t box_inner, uint32_t box_outer);
 
 constexpr int AB_B = 128;          // block edge (queries and keys)
-constexpr int AB_THREADS = 192;
+constexpr int AB_THREADS = 320;     // TMA warp, MMA warp, 8 softmax warps (two threads per query row)
 
 template <int D>
 struct AttBwdSmem {
@@ -48,11 +53,13 @@ struct AttBwdParams {
   int T, Hq, Hkv;
   float scale;
   int* status;
+  int debug_flags;      // bit 0: skip the dQ accumulation (timing experiments only; results are then wrong)
 };
 
 template <int D>
 __global__ void __launch_bounds__(AB_THREADS, 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do, AttBwdParams p) {
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                const __grid_constant__ CUtensorMap tm_dq, AttBwdParams p) {
   using L = AttBwdSmem<D>;
   constexpr int KB = D / 64;
   extern __shared__ uint8_t smem_raw[];
@@ -62,10 +69,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   uint64_t* qdo_full = bars + 1;   // Q_i, dO_i landed
   uint64_t* sdp_full = bars + 2;   // S and dP complete
   uint64_t* pds_ready = bars + 3;  // P and dS written (4 arrivals)
-  uint64_t* dq_full = bars + 4;    // dQ tile complete
-  uint64_t* mma_done = bars + 5;   // dV / dK updates complete: Q, dO, P, dS reusable
-  uint64_t* dq_read = bars + 6;    // dQ tile drained (4 arrivals): S columns reusable
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* stage_full = bars + 4; // dQ tile copied from TMEM to the smem staging area (8 arrivals)
+  uint64_t* mma_done = bars + 5;   // dV, dK, dQ complete: Q, dO, P, dS reusable, dQ readable
+  uint64_t* dq_read = bars + 6;    // dQ tile drained from TMEM (8 arrivals): S columns reusable
+  uint64_t* stage_free = bars + 7; // the tensor reduces have read the staging area: P / dS writable
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -78,12 +86,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   const int n_iters = G * per_head;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(sdp_full, 1); mbar_init(pds_ready, 4);
-    mbar_init(dq_full, 1); mbar_init(mma_done, 1); mbar_init(dq_read, 4);
+    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(sdp_full, 1); mbar_init(pds_ready, 8);
+    mbar_init(stage_full, 8); mbar_init(mma_done, 1); mbar_init(dq_read, 8); mbar_init(stage_free, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
     tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_dq);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -136,11 +145,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         umma_commit(sdp_full);
         if (!mbar_wait(pds_ready, it & 1, abort_flag)) { atomicExch(p.status, 25); goto done; }
         tc_fence_after();
-        // dQ = dS K  (A K-major over keys, B = K tile read MN-major)
-#pragma unroll
-        for (int k = 0; k < AB_B / 16; ++k)
-          umma_bf16(t_s, make_smem_desc(sds + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), make_smem_desc(sk + k * 2048, 16384, 1024), id_dq, k != 0);
-        umma_commit(dq_full);
         // dV += P^T dO ; dK += dS^T Q  (A = [query, key] tile read MN-major, B = [query, D] tile read MN-major)
 #pragma unroll
         for (int k = 0; k < AB_B / 16; ++k)
@@ -148,11 +152,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
 #pragma unroll
         for (int k = 0; k < AB_B / 16; ++k)
           umma_bf16(t_dk, make_smem_desc(sds + k * 2048, 16384, 1024), make_smem_desc(sq + k * 2048, 16384, 1024), id_tn, (it | k) != 0);
+        // dQ = dS K  (A K-major over keys, B = K tile read MN-major), into the columns S occupied
+#pragma unroll
+        for (int k = 0; k < AB_B / 16; ++k)
+          umma_bf16(t_s, make_smem_desc(sds + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), make_smem_desc(sk + k * 2048, 16384, 1024), id_dq, k != 0);
         umma_commit(mma_done);
       }
     }
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;      // which 64 key columns (softmax) / which half of the D columns (drains)
     const int r = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
@@ -165,11 +174,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       const float lse2 = qok ? p.lse[static_cast<long long>(h) * p.T + tok] * 1.4426950408889634f : 0.f;
       const float delta = qok ? p.delta[static_cast<long long>(h) * p.T + tok] : 0.f;
       if (!mbar_wait(sdp_full, it & 1, abort_flag)) { atomicExch(p.status, 26); goto done; }
-      if (it > 0 && !mbar_wait(mma_done, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 27); goto done; }
+      if (it > 0 && !mbar_wait(stage_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 27); goto done; }
       tc_fence_after();
       const bool need_mask = (i == jblk) || (k0 + AB_B > seq_len);
 #pragma unroll 1
-      for (int c = 0; c < AB_B / 32; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t sv_[32], dv_[32];
         tmem_ld_32x32(t_s + lane_addr + c * 32, sv_);
         tmem_ld_32x32(t_dp + lane_addr + c * 32, dv_);
@@ -201,26 +211,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_ready);
-      // drain dQ
-      if (!mbar_wait(dq_full, it & 1, abort_flag)) { atomicExch(p.status, 28); goto done; }
+      // drain dQ: TMEM -> fp32 staging rows in the (now idle) P / dS tiles -> one bulk reduce-add per row
+      if (!mbar_wait(mma_done, it & 1, abort_flag)) { atomicExch(p.status, 28); goto done; }
       tc_fence_after();
-      float* dst = p.dq_acc + tok * HqD + h * D;
+      uint8_t* stage = smem + L::OFF_P;   // D/32 boxes of [128 rows x 128 B], 128B-swizzled
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c = half * (D / 64) + cc;
         uint32_t v[32];
         tmem_ld_32x32(t_s + lane_addr + c * 32, v);
         tmem_ld_wait();
-        if (qok) {
+        uint8_t* rowp = stage + c * 16384 + r * 128;
 #pragma unroll
-          for (int x = 0; x < 32; x += 4)
-            atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + x),
-                      make_float4(__uint_as_float(v[x]), __uint_as_float(v[x + 1]), __uint_as_float(v[x + 2]), __uint_as_float(v[x + 3])));
-        }
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<uint4*>(rowp + ((g ^ (r & 7)) << 4)) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
       }
+      fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(dq_read);
+      if (lane == 0) { mbar_arrive(dq_read); mbar_arrive(stage_full); }
+      if (warp == 2 && lane == 0) {
+        if (!mbar_wait(stage_full, it & 1, abort_flag)) { atomicExch(p.status, 30); goto done; }
+        if (!(p.debug_flags & 1)) {
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c)
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage + c * 16384)), "r"(h * D + c * 32),
+                           "r"(seq_start + i * AB_B) : "memory");
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_arrive(stage_free);
+      }
     }
+    if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     // epilogue: dK, dV (rows = keys)
     if (n_iters > 0) {
       if (!mbar_wait(mma_done, (n_iters - 1) & 1, abort_flag)) { atomicExch(p.status, 29); goto done; }
@@ -233,7 +257,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         const uint32_t src = (which == 0 ? t_dk : t_dv) + lane_addr;
         __nv_bfloat16* o = rowp + (which == 0 ? (p.Hq + hk) * D : (p.Hq + p.Hkv + hk) * D);
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int c = half * (D / 64) + cc;
           uint32_t v[32];
           tmem_ld_32x32(src + c * 32, v);
           tmem_ld_wait();
@@ -292,14 +317,14 @@ __global__ void __launch_bounds__(256) attn_dq_store_kernel(const float* __restr
 }
 
 template <int D>
-static int launch_bwd(const CUtensorMap& a, const CUtensorMap& b, const AttBwdParams& p, int n_items, cudaStream_t st) {
+static int launch_bwd(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const AttBwdParams& p, int n_items, cudaStream_t st) {
   static bool configured = false;
   auto kern = attn_bwd_kernel<D>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttBwdSmem<D>::TOTAL) != cudaSuccess) return -4;
     configured = true;
   }
-  kern<<<n_items * p.Hkv, AB_THREADS, AttBwdSmem<D>::TOTAL, st>>>(a, b, p);
+  kern<<<n_items * p.Hkv, AB_THREADS, AttBwdSmem<D>::TOTAL, st>>>(a, b, c, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -313,16 +338,18 @@ extern "C" int mtb200_attn_bwd(const void* qkv, long long ld, const void* out, l
   using namespace mtb;
   if (n_items <= 0 || T <= 0) return 0;
   if ((D != 64 && D != 128) || Hq % Hkv || ld % 8 || ldo % 8 || lddo % 8 || ldq % 8) return -10;
-  CUtensorMap tq, tdo;
+  CUtensorMap tq, tdo, tdq;
   int rc = make_tmap_2d_bf16(&tq, qkv, static_cast<uint64_t>(ld), static_cast<uint64_t>(T), static_cast<uint64_t>(ld), 64, 128);
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&tdo, dout, static_cast<uint64_t>(Hq) * D, static_cast<uint64_t>(T), static_cast<uint64_t>(lddo), 64, 128);
   if (rc) return rc - 10;
+  rc = make_tmap_2d_f32(&tdq, dq_acc, static_cast<uint64_t>(Hq) * D, static_cast<uint64_t>(T), static_cast<uint64_t>(Hq) * D, 32, 128);
+  if (rc) return rc - 20;
   const long long warps = static_cast<long long>(T) * Hq;
   attn_delta_kernel<<<static_cast<int>((warps * 32 + 255) / 256), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(out), ldo, reinterpret_cast<const __nv_bfloat16*>(dout), lddo, delta, T, Hq, D);
-  AttBwdParams p{reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, lse, delta, dq_acc, plan, T, Hq, Hkv, scale, status};
-  rc = D == 128 ? launch_bwd<128>(tq, tdo, p, n_items, st) : launch_bwd<64>(tq, tdo, p, n_items, st);
+  AttBwdParams p{reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, lse, delta, dq_acc, plan, T, Hq, Hkv, scale, status, reserved};
+  rc = D == 128 ? launch_bwd<128>(tq, tdo, tdq, p, n_items, st) : launch_bwd<64>(tq, tdo, tdq, p, n_items, st);
   if (rc) return rc;
   const long long n = static_cast<long long>(T) * (Hq * D / 8);
   attn_dq_store_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, T, Hq * D);

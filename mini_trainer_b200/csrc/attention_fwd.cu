@@ -5,7 +5,8 @@
 //   S = Q K^T      tcgen05.mma, M=128 queries, N=128 keys, K=D      (accumulator in TMEM, 2 buffers)
 //   P = softmax    4 warps, one query row per thread, reads S from TMEM, writes bf16 P to smem
 //   O += P V       tcgen05.mma, M=128, N=D, K=128 keys               (accumulator in TMEM)
-// Roles: warp 0 = TMA (K/V double-buffered), warp 1 = MMA issue, warps 2-5 = softmax + epilogue.
+// Roles: warp 0 = TMA (K/V double-buffered), warp 1 = MMA issue, warps 2-9 = softmax + epilogue
+// (two threads per query row, each owning 64 of the 128 key columns of a tile).
 // S is double-buffered so that Q K^T of tile j+1 runs under the softmax of tile j.
 //
 // The softmax keeps a per-row reference maximum and only rescales O when the running maximum
@@ -29,7 +30,7 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
                       uint32_t box_inner, uint32_t box_outer);
 
 constexpr int ATT_BM = 128, ATT_BN = 128;
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps (two threads per query row)
 
 template <int D>
 struct AttFwdSmem {
@@ -41,7 +42,8 @@ struct AttFwdSmem {
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;   // 2 stages
   static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
   static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_MX = OFF_BAR + 256;          // float [2 tiles parity][2 halves][128 rows]
+  static constexpr int TOTAL = OFF_MX + 2 * 2 * 128 * 4 + 1024;
 };
 
 struct AttFwdParams {
@@ -68,7 +70,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   uint64_t* s_full = bars + 7;        // 2
   uint64_t* p_ready = bars + 9;       // 1
   uint64_t* p_empty = bars + 10;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* mx_bar = bars + 11;       // 1: the two threads of every row have published their partial maximum / sum
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,8 +83,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&s_full[i], 1); }
-    mbar_init(p_ready, 4);
+    mbar_init(p_ready, 8);
     mbar_init(p_empty, 1);
+    mbar_init(mx_bar, 8);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap);
@@ -152,23 +156,26 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue
-    const int q = warp & 3;
+    const int q = warp & 3;                   // TMEM lane quarter
+    const int half = (warp - 2) >> 2;         // which 64 key columns / which half of the O columns
     const int r = q * 32 + lane;              // row inside the query block
     const int qpos = q0 + r;                  // position inside the sequence
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     float m_ref = -INFINITY, l = 0.f;
     uint8_t* sp = smem + L::OFF_P;
+    float* mx = reinterpret_cast<float*>(smem + L::OFF_MX);
     for (int j = 0; j < n_tiles; ++j) {
       if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag)) { atomicExch(p.status, 17); goto done; }
       tc_fence_after();
       const uint32_t ts = tmem_s0 + (j & 1) * ATT_BN + lane_addr;
       const bool diag = (j == n_tiles - 1);
       const int kbase = j * ATT_BN;
-      // pass 1: row maximum
+      // pass 1: row maximum over this thread's 64 columns, combined with the partner thread's
       float mt = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t v[32];
         tmem_ld_32x32(ts + c * 32, v);
         tmem_ld_wait();
@@ -179,6 +186,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
           mt = fmaxf(mt, s);
         }
       }
+      float* mxj = mx + (j & 1) * 256;
+      mxj[half * 128 + r] = mt;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(mx_bar);
+      if (!mbar_wait(mx_bar, j & 1, abort_flag)) { atomicExch(p.status, 20); goto done; }   // bounded, unlike bar.sync
+      mt = fmaxf(mxj[r], mxj[128 + r]);
       float factor = 1.f;
       bool rescale = false;
       if (mt > m_ref && (mt - m_ref) * sl2 > 8.f) {   // includes the first tile (m_ref = -inf)
@@ -192,7 +205,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         tc_fence_after();
         if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
+          for (int cc = 0; cc < D / 64; ++cc) {
+            const int c = half * (D / 64) + cc;
             uint32_t v[32];
             tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
             tmem_ld_wait();
@@ -206,7 +220,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       // pass 2: probabilities -> bf16 P in shared memory (K-major, 128B swizzle), row sums
       const float mo = m_ref * sl2;
 #pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t v[32];
         tmem_ld_32x32(ts + c * 32, v);
         tmem_ld_wait();
@@ -233,15 +248,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
     }
-    // epilogue: O / l -> out, lse
+    // epilogue: O / l -> out, lse (row sums of the two column halves are combined first)
     if (!mbar_wait(p_empty, (n_tiles - 1) & 1, abort_flag)) { atomicExch(p.status, 19); goto done; }
     tc_fence_after();
+    float* lx = mx + (n_tiles & 1) * 256;   // the buffer the last tile did not use
+    lx[half * 128 + r] = l;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(mx_bar);
+    if (!mbar_wait(mx_bar, n_tiles & 1, abort_flag)) { atomicExch(p.status, 20); goto done; }
+    l = lx[r] + lx[128 + r];
     const bool ok = qpos < seq_len;
     const float inv = 1.f / l;
     const long long tok = static_cast<long long>(seq_start) + qpos;
     __nv_bfloat16* orow = p.out + tok * p.ldo + h * D;
 #pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
+    for (int cc = 0; cc < D / 64; ++cc) {
+      const int c = half * (D / 64) + cc;
       uint32_t v[32];
       tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
       tmem_ld_wait();
@@ -257,7 +279,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         }
       }
     }
-    if (ok) p.lse[static_cast<long long>(h) * p.T + tok] = m_ref * p.scale + logf(l);
+    if (ok && half == 0) p.lse[static_cast<long long>(h) * p.T + tok] = m_ref * p.scale + logf(l);
   }
 done:
   tc_fence_before();

@@ -254,7 +254,8 @@ class NativeOps:
         dq_acc = torch.zeros(T, hq * d, dtype=torch.float32, device=self.device)
         self._call("mtb200_attn_bwd", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), dout.data_ptr(),
                    dout.stride(0), dqkv.data_ptr(), dqkv.stride(0), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(),
-                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, 0, d ** -0.5, self.status.data_ptr(), self._st(), n=3)
+                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, int(os.environ.get("MTB200_ATTN_BWD_DEBUG", "0")), d ** -0.5,
+                   self.status.data_ptr(), self._st(), n=3)
         return dqkv
 
     # library baseline (flash-attn 2), selectable for A/B comparisons only
