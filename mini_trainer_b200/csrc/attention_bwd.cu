@@ -176,35 +176,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       if (!mbar_wait(sdp_full, it & 1, abort_flag)) { atomicExch(p.status, 26); goto done; }
       if (it > 0 && !mbar_wait(stage_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 27); goto done; }
       tc_fence_after();
-      const bool need_mask = (i == jblk) || (k0 + AB_B > seq_len);
-#pragma unroll 1
+      const bool need_mask = (i == jblk) || (k0 + AB_B > seq_len) || (i * AB_B + AB_B > seq_len);
+      // this thread's 64 columns of S and dP are fetched with all four loads in flight
+      uint32_t sv_[2][32], dv_[2][32];
+      tmem_ld_32x32(t_s + lane_addr + (half * 2) * 32, sv_[0]);
+      tmem_ld_32x32(t_dp + lane_addr + (half * 2) * 32, dv_[0]);
+      tmem_ld_32x32(t_s + lane_addr + (half * 2 + 1) * 32, sv_[1]);
+      tmem_ld_32x32(t_dp + lane_addr + (half * 2 + 1) * 32, dv_[1]);
+      tmem_ld_wait();
+      if (need_mask) {   // diagonal block, last key block or last query block: out-of-range entries get P = 0
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            const int kpos = k0 + (half * 2 + cc) * 32 + x;
+            if (!qok || kpos > qpos || kpos >= seq_len) sv_[cc][x] = 0xff800000u;   // exp2(-inf) = 0
+          }
+      }
+#pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
-        uint32_t sv_[32], dv_[32];
-        tmem_ld_32x32(t_s + lane_addr + c * 32, sv_);
-        tmem_ld_32x32(t_dp + lane_addr + c * 32, dv_);
-        tmem_ld_wait();
-        uint32_t pk[16], dk[16];
-#pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          float pv[2], dsv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int kpos = k0 + c * 32 + x + u;
-            float pe = exp2f(__uint_as_float(sv_[x + u]) * sl2 - lse2);
-            if (!qok || (need_mask && (kpos > qpos || kpos >= seq_len))) pe = 0.f;
-            pv[u] = pe;
-            dsv[u] = pe * (__uint_as_float(dv_[x + u]) - delta) * p.scale;
-          }
-          pk[x >> 1] = pack_bf16(pv[0], pv[1]);
-          dk[x >> 1] = pack_bf16(dsv[0], dsv[1]);
-        }
         const int rowoff = (c >> 1) * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
+          uint32_t pk[4], dk[4];
+#pragma unroll
+          for (int x = 0; x < 8; x += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(sv_[cc][g * 8 + x]), sl2, -lse2));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv_[cc][g * 8 + x + 1]), sl2, -lse2));
+            pk[x >> 1] = pack_bf16(p0, p1);
+            dk[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv_[cc][g * 8 + x]) - delta) * p.scale,
+                                   p1 * (__uint_as_float(dv_[cc][g * 8 + x + 1]) - delta) * p.scale);
+          }
           const int chunk = (((c & 1) * 4 + g) ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(smem + L::OFF_P + rowoff + chunk) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-          *reinterpret_cast<uint4*>(smem + L::OFF_DS + rowoff + chunk) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
+          *reinterpret_cast<uint4*>(smem + L::OFF_P + rowoff + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(smem + L::OFF_DS + rowoff + chunk) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
         }
       }
       fence_proxy_async_smem();

@@ -3,11 +3,12 @@
 // One CTA handles one (sequence, 128-row query block, query head). Q, K and V are read straight
 // out of the fused qkv activation [T, (Hq + 2 Hkv) * D] through ONE tensor map (128B swizzle):
 //   S = Q K^T      tcgen05.mma, M=128 queries, N=128 keys, K=D      (accumulator in TMEM, 2 buffers)
-//   P = softmax    4 warps, one query row per thread, reads S from TMEM, writes bf16 P to smem
+//   P = softmax    8 warps, two threads per query row, read S from TMEM, write bf16 P to smem (2 buffers)
 //   O += P V       tcgen05.mma, M=128, N=D, K=128 keys               (accumulator in TMEM)
 // Roles: warp 0 = TMA (K/V double-buffered), warp 1 = MMA issue, warps 2-9 = softmax + epilogue
 // (two threads per query row, each owning 64 of the 128 key columns of a tile).
-// S is double-buffered so that Q K^T of tile j+1 runs under the softmax of tile j.
+// S (TMEM) and P (smem) are double-buffered: Q K^T of tile j+1 and P V of tile j-1 both run under the
+// softmax of tile j, so the softmax warps never wait for the tensor core except to rescale O.
 //
 // The softmax keeps a per-row reference maximum and only rescales O when the running maximum
 // grew by more than 2^8 (exact: the final division by the row sum uses the same reference), so
@@ -40,10 +41,12 @@ struct AttFwdSmem {
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;        // 2 stages
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;   // 2 stages
-  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;   // 2 buffers
+  static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
   static constexpr int OFF_MX = OFF_BAR + 256;          // float [2 tiles parity][2 halves][128 rows]
-  static constexpr int TOTAL = OFF_MX + 2 * 2 * 128 * 4 + 1024;
+  // No alignment slack: with D = 128 the tiles fill 224 KB of the 227 KB a CTA can have. The kernel
+  // checks that the dynamic shared memory window starts on a 1024-byte boundary (swizzle atom).
+  static constexpr int TOTAL = OFF_MX + 2 * 2 * 128 * 4;
 };
 
 struct AttFwdParams {
@@ -61,17 +64,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   using L = AttFwdSmem<D>;
   constexpr int KB = D / 64;  // 64-element (128 B) column blocks of a D-wide row
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {   // uniform over the CTA: nothing has been allocated or armed yet
+    if (threadIdx.x == 0) atomicExch(p.status, 10);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* q_full = bars;            // 1
   uint64_t* k_full = bars + 1;        // 2
   uint64_t* v_full = bars + 3;        // 2
-  uint64_t* kv_empty = bars + 5;      // 2
-  uint64_t* s_full = bars + 7;        // 2
-  uint64_t* p_ready = bars + 9;       // 1
-  uint64_t* p_empty = bars + 10;      // 1
-  uint64_t* mx_bar = bars + 11;       // 1: the two threads of every row have published their partial maximum / sum
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* k_empty = bars + 5;       // 2: Q K^T of the tile in this stage has completed
+  uint64_t* v_empty = bars + 7;       // 2: P V of the tile in this stage has completed
+  uint64_t* s_full = bars + 9;        // 2
+  uint64_t* p_ready = bars + 11;      // 2: P buffer written and S buffer consumed (8 arrivals)
+  uint64_t* p_empty = bars + 13;      // 2: P V of the tile in this P buffer has completed
+  uint64_t* mx_bar = bars + 15;       // 1: the two threads of every row have published their partial maximum / sum
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -82,9 +90,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&s_full[i], 1); }
-    mbar_init(p_ready, 8);
-    mbar_init(p_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 8); mbar_init(&p_empty[i], 1);
+    }
     mbar_init(mx_bar, 8);
     *abort_flag = 0;
     fence_mbar_init();
@@ -104,12 +113,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       for (int kb = 0; kb < KB; ++kb) tma_load_2d(smem + L::OFF_Q + kb * 16384, &tmap, q_full, h * D + kb * 64, seq_start + q0);
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) { atomicExch(p.status, 11); goto done; }
+        if (!mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) { atomicExch(p.status, 11); goto done; }
         const int row = seq_start + j * ATT_BN;
         mbar_arrive_expect_tx(&k_full[s], L::KV_BYTES);
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb)
           tma_load_2d(smem + L::OFF_K + s * L::KV_BYTES + kb * 16384, &tmap, &k_full[s], (p.Hq + hk) * D + kb * 64, row);
+        if (!mbar_wait(&v_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) { atomicExch(p.status, 11); goto done; }
         mbar_arrive_expect_tx(&v_full[s], L::KV_BYTES);
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb)
@@ -129,29 +139,35 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
           umma_bf16(tmem_s0 + (j & 1) * ATT_BN, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), idesc_qk, k != 0);
         }
         umma_commit(&s_full[j & 1]);
+        umma_commit(&k_empty[j & 1]);
       };
       if (!mbar_wait(q_full, 0, abort_flag)) { atomicExch(p.status, 12); goto done; }
-      if (!mbar_wait(&k_full[0], 0, abort_flag)) { atomicExch(p.status, 13); goto done; }
-      tc_fence_after();
-      issue_qk(0);
-      for (int j = 0; j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) {
-          if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { atomicExch(p.status, 14); goto done; }
-          tc_fence_after();
-          issue_qk(j + 1);
-        }
-        if (!mbar_wait(p_ready, j & 1, abort_flag)) { atomicExch(p.status, 15); goto done; }
-        if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag)) { atomicExch(p.status, 16); goto done; }
+      for (int j = 0; j < 2 && j < n_tiles; ++j) {
+        if (!mbar_wait(&k_full[j], 0, abort_flag)) { atomicExch(p.status, 13); goto done; }
         tc_fence_after();
-        const uint32_t sv = smem_u32(smem + L::OFF_V + (j & 1) * L::KV_BYTES);
+        issue_qk(j);
+      }
+      for (int j = 0; j < n_tiles; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&p_ready[b], ph, abort_flag)) { atomicExch(p.status, 15); goto done; }
+        if (!mbar_wait(&v_full[b], ph, abort_flag)) { atomicExch(p.status, 16); goto done; }
+        tc_fence_after();
+        const uint32_t sv = smem_u32(smem + L::OFF_V + b * L::KV_BYTES);
+        const uint32_t spb = sp + b * L::P_BYTES;
 #pragma unroll
         for (int k = 0; k < ATT_BN / 16; ++k) {
-          const uint64_t da = make_smem_desc(sp + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t da = make_smem_desc(spb + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
           const uint64_t db = make_smem_desc(sv + k * 2048, 16384, 1024);
           umma_bf16(tmem_o, da, db, idesc_pv, (j | k) != 0);
         }
-        umma_commit(&kv_empty[j & 1]);
-        umma_commit(p_empty);
+        umma_commit(&v_empty[b]);
+        umma_commit(&p_empty[b]);
+        if (j + 2 < n_tiles) {   // S buffer b was consumed by the softmax of tile j: refill it with tile j+2
+          if (!mbar_wait(&k_full[b], ((j + 2) >> 1) & 1, abort_flag)) { atomicExch(p.status, 14); goto done; }
+          tc_fence_after();
+          issue_qk(j + 2);
+        }
       }
     }
   } else {
@@ -171,21 +187,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       const uint32_t ts = tmem_s0 + (j & 1) * ATT_BN + lane_addr;
       const bool diag = (j == n_tiles - 1);
       const int kbase = j * ATT_BN;
-      // pass 1: row maximum over this thread's 64 columns, combined with the partner thread's
-      float mt = -INFINITY;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
-        uint32_t v[32];
-        tmem_ld_32x32(ts + c * 32, v);
-        tmem_ld_wait();
+      // S is read from tensor memory once: this thread's 64 columns stay in registers for both the
+      // row maximum and the exponentials. Only the last tile touches the causal diagonal.
+      uint32_t sv[2][32];
+      tmem_ld_32x32(ts + (half * 2) * 32, sv[0]);
+      tmem_ld_32x32(ts + (half * 2 + 1) * 32, sv[1]);
+      tmem_ld_wait();
+      if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (diag && (kbase + c * 32 + i > qpos)) s = -INFINITY;
-          mt = fmaxf(mt, s);
-        }
+        for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kbase + (half * 2 + cc) * 32 + i > qpos) sv[cc][i] = 0xff800000u;   // -inf
       }
+      float mt = -INFINITY;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mt = fmaxf(mt, __uint_as_float(sv[cc][i]));
       float* mxj = mx + (j & 1) * 256;
       mxj[half * 128 + r] = mt;
       __syncwarp();
@@ -200,10 +219,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         l *= factor;
         rescale = (j > 0);
       }
+      if (j >= 2) {   // the P buffer of this tile must have been read by P V of tile j-2
+        if (!mbar_wait(&p_empty[j & 1], ((j - 2) >> 1) & 1, abort_flag)) { atomicExch(p.status, 18); goto done; }
+      }
       if (j > 0) {
-        if (!mbar_wait(p_empty, (j - 1) & 1, abort_flag)) { atomicExch(p.status, 18); goto done; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, rescale)) {
+        if (__any_sync(0xffffffffu, rescale)) {   // O must be complete through tile j-1 before it is rescaled
+          if (!mbar_wait(&p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { atomicExch(p.status, 18); goto done; }
+          tc_fence_after();
 #pragma unroll 1
           for (int cc = 0; cc < D / 64; ++cc) {
             const int c = half * (D / 64) + cc;
@@ -217,39 +239,33 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
           tmem_st_wait();
         }
       }
-      // pass 2: probabilities -> bf16 P in shared memory (K-major, 128B swizzle), row sums
+      // probabilities -> bf16 P in shared memory (K-major, 128B swizzle), row sums; exp2(-inf) = 0 masks
       const float mo = m_ref * sl2;
-#pragma unroll 1
+#pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
-        uint32_t v[32];
-        tmem_ld_32x32(ts + c * 32, v);
-        tmem_ld_wait();
-        float pr[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(v[i]) * sl2 - mo);
-          if (diag && (kbase + c * 32 + i > qpos)) e = 0.f;
-          pr[i] = e;
-          l += e;
-        }
-        uint8_t* rowp = sp + (c >> 1) * 16384 + r * 128;
+        uint8_t* rowp = sp + (j & 1) * L::P_BYTES + (c >> 1) * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
+          float e[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            e[i] = exp2f(fmaf(__uint_as_float(sv[cc][g * 8 + i]), sl2, -mo));
+            l += e[i];
+          }
           const int chunk = (c & 1) * 4 + g;
           uint4 o;
-          o.x = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]); o.y = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
-          o.z = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]); o.w = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          o.x = pack_bf16(e[0], e[1]); o.y = pack_bf16(e[2], e[3]); o.z = pack_bf16(e[4], e[5]); o.w = pack_bf16(e[6], e[7]);
           *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = o;
         }
       }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(&p_ready[j & 1]);
     }
     // epilogue: O / l -> out, lse (row sums of the two column halves are combined first)
-    if (!mbar_wait(p_empty, (n_tiles - 1) & 1, abort_flag)) { atomicExch(p.status, 19); goto done; }
+    if (!mbar_wait(&p_empty[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag)) { atomicExch(p.status, 19); goto done; }
     tc_fence_after();
     float* lx = mx + (n_tiles & 1) * 256;   // the buffer the last tile did not use
     lx[half * 128 + r] = l;
