@@ -43,6 +43,7 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
 class _Sig:
     mtb200_gemm_bf16 = [P, L, I, P, L, I, P, L, I, P, L, P, I, I, I, P, P]
+    mtb200_gemm2_bf16 = [P, L, I, P, L, I, P, L, I, P, L, P, I, I, I, P, P]
     mtb200_rmsnorm_fwd = [P, P, P, P, F, I, I, P]
     mtb200_rmsnorm_bwd_blocks = [I]
     mtb200_rmsnorm_bwd = [P, P, P, P, P, P, P, P, I, I, P]
@@ -76,6 +77,8 @@ class NativeOps:
         self.ce_chunk = ce_chunk
         self.attention_impl = attention or os.environ.get("MTB200_ATTENTION", "native")
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # two-CTA (cta_group::2) GEMM tiles for problems with at least a full wave of 256x256 tiles
+        self.use_gemm2 = os.environ.get("MTB200_GEMM2", "0") == "1"
         self.launches = 0
         self.profile = [] if os.environ.get("MTB200_PROFILE") else None
         self._scratch = {}
@@ -134,12 +137,15 @@ class NativeOps:
             raise RuntimeError(f"a device-side bounded wait expired (code {code})")
 
     # -- GEMM -------------------------------------------------------------------------
-    def gemm(self, a, a_mn, b, b_mn, out, M, N, K, residual=None, bias=None, tag=None):
-        """out[M,N] = A*B (+bias) (+residual). ``a_mn``/``b_mn``: operand stored [K, rows]."""
+    def gemm(self, a, a_mn, b, b_mn, out, M, N, K, residual=None, bias=None, tag=None, two_cta=None):
+        """out[M,N] = A*B (+bias) (+residual). ``a_mn``/``b_mn``: operand stored [K, rows].
+        ``two_cta``: force (True) or forbid (False) the cta_group::2 kernel; default by problem size."""
         out_f32 = out.dtype == torch.float32
         assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
         assert residual is None or residual.dtype == out.dtype
-        self._call("mtb200_gemm_bf16", a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
+        if two_cta is None:
+            two_cta = self.use_gemm2 and (-(-M // 256)) * (-(-N // 256)) >= 64
+        self._call("mtb200_gemm2_bf16" if two_cta else "mtb200_gemm_bf16", a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
                    out.data_ptr(), out.stride(0), int(out_f32), _ptr(residual),
                    residual.stride(0) if residual is not None else 0, _ptr(bias), M, N, K,
                    self.status.data_ptr(), self._st(), tag=tag or f"gemm_{'t' if a_mn else 'n'}{'n' if b_mn else 't'}")

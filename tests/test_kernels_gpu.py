@@ -246,3 +246,32 @@ def test_bounded_wait_expires_with_status_and_context_stays_usable(ops):
     assert code & 0xff == 42 and code >> 8 == 1
     x = torch.ones(1024, device="cuda")
     assert x.sum().item() == 1024                  # the context is still healthy
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (300, 520, 200), (1000, 1024, 4096), (4096, 6144, 4096), (264, 264, 72)])
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+def test_gemm_two_cta(ops, M, N, K, layout):
+    """cta_group::2 kernel (256x256 tiles per CTA pair) against the fp32 reference, all three layouts."""
+    torch.manual_seed(3 + M + N + K)
+    if layout == "tn" and M % 8:
+        pytest.skip("leading dimension of an MN-major A must be a multiple of 8")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    if layout == "nt":
+        a, b = bf(M, K), bf(N, K, scale=0.05)
+        ref = a.float() @ b.float().t()
+        ops.gemm(a, False, b, False, out, M, N, K, two_cta=True)
+    elif layout == "nn":
+        a, b = bf(M, K), bf(K, N, scale=0.05)
+        ref = a.float() @ b.float()
+        ops.gemm(a, False, b, True, out, M, N, K, two_cta=True)
+    else:
+        a, b = bf(K, M), bf(K, N, scale=0.05)
+        ref = a.float().t() @ b.float()
+        ops.gemm(a, True, b, True, out, M, N, K, two_cta=True)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert rel_err(out, ref) < 6e-3
+    res, bias = bf(M, N), bf(N)
+    if layout == "nt":
+        ops.gemm(a, False, b, False, out, M, N, K, residual=res, bias=bias, two_cta=True)
+        assert rel_err(out, ref + res.float() + bias.float()) < 6e-3
