@@ -126,7 +126,8 @@ def run_native(args) -> dict:
     total_steps = 2 * (args.steps + args.warmup)
     ds = synthetic_dataset(batch_size * total_steps, spec, cfg.vocab_size, seed=893)
     sampler = iter(InfiniteSampler(len(ds), seed=893))
-    coll = MaxTokensPerRankCollator(max_tokens, rank=rank, world_size=world)
+    cost_len = cfg.attention_cost_length() if args.balance == "cost" else None
+    coll = MaxTokensPerRankCollator(max_tokens, rank=rank, world_size=world, cost_len=cost_len)
     batches = []
     for _ in range(total_steps):
         idx = [next(sampler) for _ in range(batch_size)]
@@ -216,6 +217,7 @@ def run_native(args) -> dict:
         "impl": "native",
         "config": {"model": args.model, "global_batch": batch_size, "seq_len": f"packed, max_tokens_per_gpu={max_tokens}",
                    "parallelism": f"fsdp{world}" if world > 1 else "single", "comm": comm.name,
+                   "packer_balance": args.balance,
                    "activation_checkpointing": "per block", "optimizer": "AdamW fp32 master, moments " + str(sdt).split(".")[-1],
                    "attention": getattr(ops, "attention_impl", "torch"),
                    "l2": "inputs larger than L2 (activations of tens of thousands of tokens per layer); no explicit flush",
@@ -253,6 +255,9 @@ def main():
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--comm", default="auto")
     ap.add_argument("--state-dtype", default="auto", choices=["auto", "fp32", "bf16"])
+    ap.add_argument("--balance", default="cost", choices=["cost", "tokens"],
+                    help="what the LPT packer balances across ranks: estimated compute cost (GEMM + causal attention) "
+                         "or tokens (the reference's criterion); the global batch is identical either way")
     ap.add_argument("--batch-size", type=int, default=0)
     ap.add_argument("--max-tokens-per-gpu", type=int, default=0)
     args = ap.parse_args()

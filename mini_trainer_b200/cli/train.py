@@ -42,6 +42,7 @@ def main(
     max_grad_norm: float = Option(1.0, help="Global gradient-norm clip"),
     weight_decay: float = Option(0.0, help="AdamW weight decay"),
     optimizer_state_dtype: str = Option("auto", help="auto | fp32 | bf16 (AdamW moments)"),
+    balance_by: str = Option("cost", help="cost | tokens: what the LPT packer balances across ranks (same global batch either way)"),
     osft: bool = Option(False, help="Orthogonal-subspace fine-tuning of the attention/MLP projections"),
     osft_rank_ratio: float = Option(0.5, help="Fraction of each projection's singular directions that is frozen"),
     resume_from: Optional[str] = Option(None, help="Directory of a training-state checkpoint to resume from"),
@@ -88,16 +89,17 @@ def main(
         meta = load_train_state(model, resume_from)
         if "scheduler" in meta:
             sched.load_state_dict(meta["scheduler"])
+    cost_len = model.cfg.attention_cost_length() if balance_by == "cost" else None
     if data_path.startswith("synthetic:"):
         parts = data_path.split(":")
         spec, vocab, _, _ = CONFIG_DATA[parts[1]]
         n = int(parts[2]) if len(parts) > 2 else 4096
         dataset = synthetic_dataset(n, spec, min(vocab, model.cfg.vocab_size), seed=seed)
         loader = get_data_loader(dataset=dataset, batch_size=batch_size, max_tokens_per_gpu=max_tokens_per_gpu,
-                                 seed=seed, pin_memory=device.type == "cuda")
+                                 seed=seed, pin_memory=device.type == "cuda", cost_len=cost_len)
     else:
         loader = get_data_loader(data_path=data_path, batch_size=batch_size, max_tokens_per_gpu=max_tokens_per_gpu,
-                                 seed=seed, num_workers=num_workers, pin_memory=device.type == "cuda")
+                                 seed=seed, num_workers=num_workers, pin_memory=device.type == "cuda", cost_len=cost_len)
     train(model, optimizer, sched, loader, output_dir, min_samples_per_checkpoint, model_name_or_path,
           max_steps=max_steps)
 

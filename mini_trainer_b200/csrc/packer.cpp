@@ -112,6 +112,73 @@ int64_t mtb200_lpt_pack(const int64_t* lengths, int64_t n, int64_t max_tokens, i
   return n_mb;
 }
 
+// Cost-aware LPT. Same outer search as mtb200_lpt_pack (longest first, largest prefix that fits),
+// but ranks are balanced on an estimated COMPUTE cost  len * (1 + len / cost_len)  instead of on
+// tokens: the linear term stands for the GEMMs, the quadratic one for causal attention, and
+// `cost_len` is the sequence length at which both cost the same. The token budget stays a hard
+// per-rank limit. The global batch (hence the gradient) is unchanged; only which rank processes
+// which sample differs, so the slowest rank of a step is less slow.
+int64_t mtb200_lpt_pack_cost(const int64_t* lengths, int64_t n, int64_t max_tokens, int64_t num_ranks, double cost_len,
+                             int64_t* out_rank, int64_t* out_minibatch) {
+  if (n < 0 || num_ranks <= 0 || !(cost_len > 0)) return -1;
+  if (n == 0) return 0;
+  std::vector<int64_t> order(n);
+  std::iota(order.begin(), order.end(), 0);
+  std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return lengths[a] > lengths[b]; });
+  std::vector<int64_t> sorted(n), csum(n);
+  int64_t acc = 0;
+  for (int64_t i = 0; i < n; ++i) { sorted[i] = lengths[order[i]]; acc += sorted[i]; csum[i] = acc; }
+  auto cost = [&](int64_t len) { return static_cast<double>(len) * (1.0 + static_cast<double>(len) / cost_len); };
+  // binary min-heap over (cost, rank) with the token load carried along
+  std::vector<double> hc(num_ranks + 1);
+  std::vector<int64_t> ht(num_ranks + 1), hid(num_ranks + 1);
+  auto reset = [&]() { for (int64_t i = 0; i <= num_ranks; ++i) { hc[i] = 0.0; ht[i] = 0; hid[i] = i - 1; } };
+  auto sift = [&]() {
+    int64_t u = 1;
+    while ((u << 1) <= num_ranks) {
+      int64_t v = u << 1, r = v | 1;
+      if (r <= num_ranks && hc[r] < hc[v]) v = r;
+      if (hc[u] <= hc[v]) break;
+      std::swap(hc[u], hc[v]); std::swap(ht[u], ht[v]); std::swap(hid[u], hid[v]);
+      u = v;
+    }
+  };
+  // places `count` sequences from `first`; returns false when the cheapest rank would overflow its
+  // token budget (a sequence alone on an empty rank always passes, like the token packer)
+  auto place = [&](int64_t first, int64_t count, bool record, int64_t mb) {
+    reset();
+    for (int64_t i = 0; i < count; ++i) {
+      const int64_t len = sorted[first + i];
+      if (ht[1] > 0 && ht[1] + len > max_tokens) return false;
+      if (record) { out_rank[order[first + i]] = hid[1]; out_minibatch[order[first + i]] = mb; }
+      ht[1] += len;
+      hc[1] += cost(len);
+      sift();
+    }
+    return true;
+  };
+  int64_t start = 0, n_mb = 0;
+  while (start < n) {
+    const int64_t remaining = n - start;
+    const int64_t base = start > 0 ? csum[start - 1] : 0;
+    const int64_t ub = std::upper_bound(csum.begin() + start, csum.end(), base + max_tokens * num_ranks) - (csum.begin() + start);
+    int64_t left = 1, right = std::min(remaining + 1, ub + 1);
+    while (right - left > 1) {
+      const int64_t mid = (left + right) / 2;
+      if (place(start, mid, false, 0)) left = mid; else right = mid;
+    }
+    int64_t take = left;
+    if (take < num_ranks && take < remaining) {
+      const int64_t want = std::min(num_ranks, remaining);
+      if (place(start, want, false, 0)) take = want;
+    }
+    place(start, take, true, n_mb);
+    ++n_mb;
+    start += take;
+  }
+  return n_mb;
+}
+
 // Greedy first-come packer kept for comparison tests (reference sampler.py:41-95): walks the
 // sequences in the given order, always adding to the least-loaded rank of the open minibatch
 // and opening a new minibatch when even that rank would overflow.

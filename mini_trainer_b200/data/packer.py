@@ -48,6 +48,8 @@ def _load_lib():
             fn = getattr(lib, name)
             fn.restype = ctypes.c_int64
             fn.argtypes = [i64p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, i64p, i64p]
+        lib.mtb200_lpt_pack_cost.restype = ctypes.c_int64
+        lib.mtb200_lpt_pack_cost.argtypes = [i64p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_double, i64p, i64p]
         _LIB = lib
     except Exception:  # compiler missing: the Python oracle takes over
         _LIB = None
@@ -195,24 +197,119 @@ def lpt_pack_all_py(batch_lengths: Sequence[int], max_tokens_per_rank: int, num_
     return _to_lists(batch_lengths, r, m, n_mb, num_ranks, longest_first=True)
 
 
-def lpt_pack_all(batch_lengths: Sequence[int], max_tokens_per_rank: int, num_ranks: int):
-    """LPT schedule of every rank in one call (compiled when available)."""
+def _assign_cost_py(lengths: Sequence[int], max_tokens: int, num_ranks: int, cost_len: float):
+    """Python oracle of the cost-aware packer (``csrc/packer.cpp: mtb200_lpt_pack_cost``)."""
+    import heapq
+    n = len(lengths)
+    rank_of, mb_of = [0] * n, [0] * n
+    order = sorted(range(n), key=lambda i: -int(lengths[i]))
+    srt = [int(lengths[i]) for i in order]
+    csum = np.cumsum(np.asarray(srt, dtype=np.int64)) if n else np.zeros(0, np.int64)
+    cost = lambda ln: float(ln) * (1.0 + float(ln) / cost_len)
+
+    class H(_Heap):
+        def __init__(self, ranks):
+            super().__init__(ranks)
+            self.tok = [0] * (ranks + 1)
+            self.load = [0.0] * (ranks + 1)
+
+        def reset(self):
+            for i in range(self.n + 1):
+                self.load[i], self.tok[i], self.ids[i] = 0.0, 0, i - 1
+
+        def sift_root(self):
+            load, ids, tok, nn = self.load, self.ids, self.tok, self.n
+            u = 1
+            while (u << 1) <= nn:
+                v = u << 1
+                r = v | 1
+                if r <= nn and load[r] < load[v]:
+                    v = r
+                if load[u] <= load[v]:
+                    break
+                load[u], load[v] = load[v], load[u]
+                ids[u], ids[v] = ids[v], ids[u]
+                tok[u], tok[v] = tok[v], tok[u]
+                u = v
+
+    heap = H(num_ranks)
+
+    def place(first, count, record, mb):
+        heap.reset()
+        for i in range(count):
+            ln = srt[first + i]
+            if heap.tok[1] > 0 and heap.tok[1] + ln > max_tokens:
+                return False
+            if record:
+                rank_of[order[first + i]], mb_of[order[first + i]] = heap.ids[1], mb
+            heap.tok[1] += ln
+            heap.load[1] += cost(ln)
+            heap.sift_root()
+        return True
+
+    start = n_mb = 0
+    while start < n:
+        remaining = n - start
+        base = int(csum[start - 1]) if start > 0 else 0
+        ub = int(np.searchsorted(csum[start:], base + max_tokens * num_ranks, side="right"))
+        left, right = 1, min(remaining + 1, ub + 1)
+        while right - left > 1:
+            mid = (left + right) // 2
+            if place(start, mid, False, 0):
+                left = mid
+            else:
+                right = mid
+        take = left
+        if take < num_ranks and take < remaining:
+            want = min(num_ranks, remaining)
+            if place(start, want, False, 0):
+                take = want
+        place(start, take, True, n_mb)
+        n_mb += 1
+        start += take
+    return rank_of, mb_of, n_mb
+
+
+def lpt_pack_all(batch_lengths: Sequence[int], max_tokens_per_rank: int, num_ranks: int, cost_len: float | None = None,
+                 use_native: bool = True):
+    """LPT schedule of every rank in one call (compiled when available).
+
+    ``cost_len`` switches from balancing tokens (the reference's criterion) to balancing an estimated
+    compute cost ``len * (1 + len / cost_len)`` — ``cost_len`` is the sequence length at which causal
+    attention costs as much as the GEMMs of a token (see ``ModelConfig.attention_cost_length``). The
+    token budget stays a hard limit per rank; the global batch and therefore the gradient are the
+    same either way, only the slowest rank of each step gets faster.
+    """
     if num_ranks <= 0:
         raise ValueError("num_ranks must be positive")
     if len(batch_lengths) == 0:
         return [[] for _ in range(num_ranks)]
-    if _load_lib() is None:
+    native = use_native and _load_lib() is not None
+    if cost_len:
+        if native:
+            lib = _load_lib()
+            arr = np.ascontiguousarray(np.asarray(batch_lengths, dtype=np.int64))
+            r, m = np.zeros(arr.shape[0], np.int64), np.zeros(arr.shape[0], np.int64)
+            i64p = ctypes.POINTER(ctypes.c_int64)
+            n_mb = lib.mtb200_lpt_pack_cost(arr.ctypes.data_as(i64p), arr.shape[0], int(max_tokens_per_rank), int(num_ranks),
+                                            float(cost_len), r.ctypes.data_as(i64p), m.ctypes.data_as(i64p))
+            if n_mb < 0:
+                raise ValueError("invalid packer arguments")
+        else:
+            r, m, n_mb = _assign_cost_py(batch_lengths, max_tokens_per_rank, num_ranks, float(cost_len))
+        return _to_lists(batch_lengths, r, m, int(n_mb), num_ranks, longest_first=True)
+    if not native:
         return lpt_pack_all_py(batch_lengths, max_tokens_per_rank, num_ranks)
     r, m, n_mb = _native_assign("mtb200_lpt_pack", batch_lengths, max_tokens_per_rank, num_ranks)
     return _to_lists(batch_lengths, r, m, n_mb, num_ranks, longest_first=True)
 
 
 def batch_lengths_to_minibatches_lpt(batch_lengths: Sequence[int], max_tokens_per_rank: int,
-                                     num_ranks: int, rank: int):
+                                     num_ranks: int, rank: int, cost_len: float | None = None):
     """Reference-compatible entry point (batch_packer.py:190): this rank's minibatches."""
     if len(batch_lengths) == 0:
         return []
-    return lpt_pack_all(batch_lengths, max_tokens_per_rank, num_ranks)[rank]
+    return lpt_pack_all(batch_lengths, max_tokens_per_rank, num_ranks, cost_len=cost_len)[rank]
 
 
 def batch_lengths_to_minibatches(batch_lengths: Sequence[int], max_tokens_per_rank: int,

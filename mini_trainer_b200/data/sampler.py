@@ -150,7 +150,7 @@ class MaxTokensPerRankCollator:
 
     def __init__(self, max_tokens_per_rank: int, rank: Optional[int] = None,
                  world_size: Optional[int] = None, dummy_sample: Optional[dict] = None,
-                 packer=batch_lengths_to_minibatches_lpt):
+                 packer=batch_lengths_to_minibatches_lpt, cost_len: Optional[float] = None):
         import torch.distributed as dist
         self.max_tokens_per_rank = int(max_tokens_per_rank)
         self.rank = rank if rank is not None else (dist.get_rank() if dist.is_initialized() else 0)
@@ -158,6 +158,7 @@ class MaxTokensPerRankCollator:
             dist.get_world_size() if dist.is_initialized() else 1)
         self.dummy_sample = dummy_sample if dummy_sample is not None else default_dummy_sample()
         self.packer = packer
+        self.cost_len = cost_len   # None: balance tokens like the reference; else balance estimated compute cost
         self._warned = False
 
     def _plan(self, lengths):
@@ -165,6 +166,9 @@ class MaxTokensPerRankCollator:
         if n_long and not self._warned:
             print(f"\033[38;5;196m{n_long} samples exceed max tokens per gpu; each is scheduled alone\033[0m")
             self._warned = True
+        if self.cost_len:
+            return self.packer([int(x) for x in lengths], self.max_tokens_per_rank, self.world_size, self.rank,
+                               cost_len=self.cost_len)
         return self.packer([int(x) for x in lengths], self.max_tokens_per_rank, self.world_size, self.rank)
 
     def __call__(self, batch: list) -> list:
@@ -258,13 +262,14 @@ def get_data_loader(**kwargs):
 
     Keyword arguments: ``data_path`` (or ``dataset``), ``batch_size``, ``max_tokens_per_gpu``,
     ``seed``; optional ``rank``, ``world_size``, ``dummy_sample`` (bypass ``torch.distributed``,
-    which is how tests simulate several ranks in one process), ``num_workers`` (0 = packing
+    which is how tests simulate several ranks in one process), ``cost_len`` (balance ranks on estimated
+    compute cost instead of tokens, see ``data.packer.lpt_pack_all``), ``num_workers`` (0 = packing
     thread, >0 = DataLoader worker processes), ``prefetch`` and ``pin_memory``.
     """
     dataset = kwargs.get("dataset") or JsonlDataset(kwargs["data_path"])
     collator = MaxTokensPerRankCollator(kwargs["max_tokens_per_gpu"], rank=kwargs.get("rank"),
                                         world_size=kwargs.get("world_size"),
-                                        dummy_sample=kwargs.get("dummy_sample"))
+                                        dummy_sample=kwargs.get("dummy_sample"), cost_len=kwargs.get("cost_len"))
     sampler = InfiniteSampler(len(dataset), seed=kwargs["seed"])
     num_workers = int(kwargs.get("num_workers", 0))
     if num_workers > 0:

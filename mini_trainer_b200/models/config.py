@@ -72,6 +72,20 @@ class ModelConfig:
         attn = self.num_hidden_layers * 2 * 2 * self.q_size * avg_context  # QK^T and PV, forward
         return k * mm + 6 * head + (4 if recompute else 3) * attn
 
+    def attention_cost_length(self, recompute: bool = True, gemm_rate: float = 1.25e15, attn_rate: float = 0.75e15) -> float:
+        """Sequence length at which the causal attention of a token costs as much time as its GEMMs.
+
+        Used by the cost-aware packer. GEMM work per token: 6 (8 with recompute) FLOPs per matmul
+        parameter; attention work per token and per context token: forward 2*2*q_size per layer, halved
+        by causality, times 3.5 for forward + backward. The rates are typical sustained throughputs of
+        the two kernel families on a power-capped B200.
+        """
+        h, f = self.hidden_size, self.intermediate_size
+        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + 3 * h * f)
+        gemm = (8 if recompute else 6) * mm + 6 * self.vocab_size * h
+        attn = 3.5 * 2 * self.q_size * self.num_hidden_layers
+        return (gemm / gemm_rate) / (attn / attn_rate)
+
     # rotary ------------------------------------------------------------------------
     def rope_inv_freq(self):
         """fp32 inverse frequencies [head_dim/2], with ``linear`` and ``llama3`` scaling."""

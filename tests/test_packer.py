@@ -130,3 +130,23 @@ def test_speed_1000_sequences_8_ranks():
     ms = (time.perf_counter() - t0) / 10 * 1e3
     print(f"LPT all-ranks 1000 seqs x 8 ranks: {ms:.2f} ms")
     assert ms < 50
+
+
+def test_cost_aware_packing_balances_compute_not_tokens():
+    """Same samples, same budget: balancing len*(1+len/L0) lowers the slowest rank's cost."""
+    rng = np.random.default_rng(5)
+    lengths = np.clip(np.rint(rng.lognormal(7.5, 1.0, 128)), 64, 65536).astype(int).tolist()
+    L0 = 38574.0
+    cost = lambda l: l * (1 + l / L0)
+
+    def step_cost(per_rank):
+        n_mb = len(per_rank[0])
+        return sum(max(sum(cost(lengths[i]) for i in per_rank[r][m] if i >= 0) for r in range(8)) for m in range(n_mb))
+
+    tok = P.lpt_pack_all(lengths, 64000, 8)
+    cst = P.lpt_pack_all(lengths, 64000, 8, cost_len=L0)
+    check_invariants(lengths, 64000, 8, cst)
+    assert cst == P.lpt_pack_all(lengths, 64000, 8, cost_len=L0, use_native=False)
+    assert step_cost(cst) <= step_cost(tok)
+    ideal = sum(cost(l) for l in lengths) / 8
+    assert step_cost(cst) < 1.05 * ideal or step_cost(cst) < 0.97 * step_cost(tok)
