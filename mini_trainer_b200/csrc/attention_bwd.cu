@@ -33,6 +33,11 @@ int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_
 constexpr int AB_B = 128;          // block edge (queries and keys)
 constexpr int AB_THREADS = 320;     // TMA warp, MMA warp, 8 softmax warps (two threads per query row)
 
+// Optional phase timestamps (clock64) of CTA 0, switched on with debug_flags bit 1: per iteration
+// 4 values from the MMA thread and 5 from one softmax thread. Read back with mtb200_attn_bwd_debug_read.
+constexpr int DBG_ITERS = 256;
+__device__ long long g_attn_bwd_dbg[DBG_ITERS * 9];
+
 template <int D>
 struct AttBwdSmem {
   static constexpr int TILE = AB_B * D * 2;         // a [128, D] bf16 tile
@@ -66,14 +71,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* kv_full = bars;        // K and V resident
-  uint64_t* qdo_full = bars + 1;   // Q_i, dO_i landed
+  uint64_t* qdo_full = bars + 1;   // [2] Q_i landed / dO_i landed (at bars + 1 and bars + 9)
   uint64_t* sdp_full = bars + 2;   // S and dP complete
   uint64_t* pds_ready = bars + 3;  // P and dS written (4 arrivals)
   uint64_t* stage_full = bars + 4; // dQ tile copied from TMEM to the smem staging area (8 arrivals)
   uint64_t* mma_done = bars + 5;   // dV, dK, dQ complete: Q, dO, P, dS reusable, dQ readable
   uint64_t* dq_read = bars + 6;    // dQ tile drained from TMEM (8 arrivals): S columns reusable
   uint64_t* stage_free = bars + 7; // the tensor reduces have read the staging area: P / dS writable
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* q_free = bars + 8;     // dK has read Q: the next Q tile may be loaded while dV and dQ still run
+  uint64_t* do_full = bars + 9;    // dO_i landed
+  uint64_t* do_free = bars + 10;   // dV has read dO: the next dO tile may be loaded while dQ still runs
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,6 +96,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(sdp_full, 1); mbar_init(pds_ready, 8);
     mbar_init(stage_full, 8); mbar_init(mma_done, 1); mbar_init(dq_read, 8); mbar_init(stage_free, 1);
+    mbar_init(q_free, 1); mbar_init(do_full, 1); mbar_init(do_free, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -111,13 +120,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       }
       for (int it = 0; it < n_iters; ++it) {
         const int h = hk * G + it / per_head, i = jblk + it % per_head;
-        if (it > 0 && !mbar_wait(mma_done, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 21); goto done; }
-        mbar_arrive_expect_tx(qdo_full, 2 * L::TILE);
+        // Q is released first (after dK), dO second (after dV): both loads overlap the tail of the MMAs
+        if (it > 0 && !mbar_wait(q_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 21); goto done; }
+        mbar_arrive_expect_tx(qdo_full, L::TILE);
 #pragma unroll
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = 0; kb < KB; ++kb)
           tma_load_2d(smem + L::OFF_Q + kb * 16384, &tm_qkv, qdo_full, h * D + kb * 64, seq_start + i * AB_B);
-          tma_load_2d(smem + L::OFF_DO + kb * 16384, &tm_do, qdo_full, h * D + kb * 64, seq_start + i * AB_B);
-        }
+        if (it > 0 && !mbar_wait(do_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 21); goto done; }
+        mbar_arrive_expect_tx(do_full, L::TILE);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_2d(smem + L::OFF_DO + kb * 16384, &tm_do, do_full, h * D + kb * 64, seq_start + i * AB_B);
       }
     }
   } else if (warp == 1) {
@@ -127,36 +140,61 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       constexpr uint32_t id_tn = make_idesc_bf16(AB_B, D, true, true);        // dV, dK
       const uint32_t sk = smem_u32(smem + L::OFF_K), sv = smem_u32(smem + L::OFF_V), sq = smem_u32(smem + L::OFF_Q);
       const uint32_t sdo = smem_u32(smem + L::OFF_DO), spp = smem_u32(smem + L::OFF_P), sds = smem_u32(smem + L::OFF_DS);
+      // every tile lives at a fixed shared-memory address, so the descriptors are built once; inside
+      // the loop a k-step is one 64-bit add (start-address field, in 16-byte units)
+      const uint64_t dQk = make_smem_desc(sq, 16, 1024), dKk = make_smem_desc(sk, 16, 1024);
+      const uint64_t dDOk = make_smem_desc(sdo, 16, 1024), dVk = make_smem_desc(sv, 16, 1024);
+      const uint64_t dDSk = make_smem_desc(sds, 16, 1024);
+      const uint64_t dDSm = make_smem_desc(sds, 16384, 1024), dPm = make_smem_desc(spp, 16384, 1024);
+      const uint64_t dQm = make_smem_desc(sq, 16384, 1024), dDOm = make_smem_desc(sdo, 16384, 1024);
+      const uint64_t dKm = make_smem_desc(sk, 16384, 1024);
+      auto kstep = [](int k) { return static_cast<uint64_t>((k >> 2) * 1024 + (k & 3) * 2); };   // K-major: 32 B per step, 16 KB per 64
+      auto mstep = [](int k) { return static_cast<uint64_t>(k * 128); };                           // MN-major: 2048 B per step
       if (!mbar_wait(kv_full, 0, abort_flag)) { atomicExch(p.status, 22); goto done; }
       for (int it = 0; it < n_iters; ++it) {
         if (!mbar_wait(qdo_full, it & 1, abort_flag)) { atomicExch(p.status, 23); goto done; }
         if (it > 0 && !mbar_wait(dq_read, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 24); goto done; }
         tc_fence_after();
+        const bool dbg = (p.debug_flags & 2) && blockIdx.x == 0 && it < DBG_ITERS;
+        if (dbg) g_attn_bwd_dbg[it * 9 + 0] = clock64();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          umma_bf16(t_s, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), id_nt, k != 0);
+          umma_bf16(t_s, dQk + kstep(k), dKk + kstep(k), id_nt, k != 0);
         }
+        const long long dbg_a = dbg ? clock64() : 0;
+        if (!mbar_wait(do_full, it & 1, abort_flag)) { atomicExch(p.status, 23); goto done; }
+        tc_fence_after();
+        const long long dbg_b = dbg ? clock64() : 0;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          umma_bf16(t_dp, make_smem_desc(sdo + off, 16, 1024), make_smem_desc(sv + off, 16, 1024), id_nt, k != 0);
+          umma_bf16(t_dp, dDOk + kstep(k), dVk + kstep(k), id_nt, k != 0);
         }
         umma_commit(sdp_full);
+        if (dbg) {   // debug only: observe the completion of S and dP from the issuing thread itself
+          g_attn_bwd_dbg[it * 9 + 1] = clock64();
+          mbar_wait(sdp_full, it & 1, abort_flag);
+          g_attn_bwd_dbg[it * 9 + 4] = clock64();
+          g_attn_bwd_dbg[it * 9 + 5] = dbg_a;
+          g_attn_bwd_dbg[it * 9 + 6] = dbg_b;
+        }
         if (!mbar_wait(pds_ready, it & 1, abort_flag)) { atomicExch(p.status, 25); goto done; }
         tc_fence_after();
-        // dV += P^T dO ; dK += dS^T Q  (A = [query, key] tile read MN-major, B = [query, D] tile read MN-major)
+        if (dbg) g_attn_bwd_dbg[it * 9 + 2] = clock64();
+        // dK += dS^T Q, then dV += P^T dO  (A = [query, key] tile read MN-major, B = [query, D] tile read MN-major)
 #pragma unroll
         for (int k = 0; k < AB_B / 16; ++k)
-          umma_bf16(t_dv, make_smem_desc(spp + k * 2048, 16384, 1024), make_smem_desc(sdo + k * 2048, 16384, 1024), id_tn, (it | k) != 0);
+          umma_bf16(t_dk, dDSm + mstep(k), dQm + mstep(k), id_tn, (it | k) != 0);
+        umma_commit(q_free);
 #pragma unroll
         for (int k = 0; k < AB_B / 16; ++k)
-          umma_bf16(t_dk, make_smem_desc(sds + k * 2048, 16384, 1024), make_smem_desc(sq + k * 2048, 16384, 1024), id_tn, (it | k) != 0);
+          umma_bf16(t_dv, dPm + mstep(k), dDOm + mstep(k), id_tn, (it | k) != 0);
+        umma_commit(do_free);
         // dQ = dS K  (A K-major over keys, B = K tile read MN-major), into the columns S occupied
 #pragma unroll
         for (int k = 0; k < AB_B / 16; ++k)
-          umma_bf16(t_s, make_smem_desc(sds + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), make_smem_desc(sk + k * 2048, 16384, 1024), id_dq, k != 0);
+          umma_bf16(t_s, dDSk + kstep(k), dKm + mstep(k), id_dq, k != 0);
         umma_commit(mma_done);
+        if (dbg) g_attn_bwd_dbg[it * 9 + 3] = clock64();
       }
     }
   } else {
@@ -173,6 +211,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       const long long tok = static_cast<long long>(seq_start) + qpos;
       const float lse2 = qok ? p.lse[static_cast<long long>(h) * p.T + tok] * 1.4426950408889634f : 0.f;
       const float delta = qok ? p.delta[static_cast<long long>(h) * p.T + tok] : 0.f;
+      const bool dbg = (p.debug_flags & 2) && blockIdx.x == 0 && it < DBG_ITERS && threadIdx.x == 64;
       if (!mbar_wait(sdp_full, it & 1, abort_flag)) { atomicExch(p.status, 26); goto done; }
       if (it > 0 && !mbar_wait(stage_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 27); goto done; }
       tc_fence_after();
@@ -220,6 +259,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       // drain dQ: TMEM -> fp32 staging rows in the (now idle) P / dS tiles -> one bulk reduce-add per row
       if (!mbar_wait(mma_done, it & 1, abort_flag)) { atomicExch(p.status, 28); goto done; }
       tc_fence_after();
+      if (dbg) g_attn_bwd_dbg[it * 9 + 7] = clock64();
       uint8_t* stage = smem + L::OFF_P;   // D/32 boxes of [128 rows x 128 B], 128B-swizzled
 #pragma unroll 1
       for (int cc = 0; cc < D / 64; ++cc) {
@@ -236,6 +276,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) { mbar_arrive(dq_read); mbar_arrive(stage_full); }
+      if (dbg) g_attn_bwd_dbg[it * 9 + 8] = clock64();
       if (warp == 2 && lane == 0) {
         if (!mbar_wait(stage_full, it & 1, abort_flag)) { atomicExch(p.status, 30); goto done; }
         if (!(p.debug_flags & 1)) {
@@ -360,4 +401,10 @@ extern "C" int mtb200_attn_bwd(const void* qkv, long long ld, const void* out, l
   const long long n = static_cast<long long>(T) * (Hq * D / 8);
   attn_dq_store_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, T, Hq * D);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Copies the phase timestamps recorded by the last debug run (debug_flags bit 1) to the host.
+extern "C" int mtb200_attn_bwd_debug_read(long long* out, int n) {
+  if (n > mtb::DBG_ITERS * 9) n = mtb::DBG_ITERS * 9;
+  return cudaMemcpyFromSymbol(out, mtb::g_attn_bwd_dbg, sizeof(long long) * n) == cudaSuccess ? 0 : -1;
 }

@@ -131,13 +131,17 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       constexpr uint32_t idesc_qk = make_idesc_bf16(ATT_BM, ATT_BN, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BM, D, false, true);
       const uint32_t sq = smem_u32(smem + L::OFF_Q), sp = smem_u32(smem + L::OFF_P);
+      // descriptors of tiles at fixed addresses are built once; a k-step is one 64-bit add
+      const uint64_t dQ = make_smem_desc(sq, 16, 1024);
+      const uint64_t dK0 = make_smem_desc(smem_u32(smem + L::OFF_K), 16, 1024);
+      const uint64_t dV0 = make_smem_desc(smem_u32(smem + L::OFF_V), 16384, 1024);
+      const uint64_t dP0 = make_smem_desc(sp, 16, 1024);
+      auto kstep = [](int k) { return static_cast<uint64_t>((k >> 2) * 1024 + (k & 3) * 2); };
       auto issue_qk = [&](int j) {
-        const uint32_t sk = smem_u32(smem + L::OFF_K + (j & 1) * L::KV_BYTES);
+        const uint64_t dK = dK0 + static_cast<uint64_t>((j & 1) * (L::KV_BYTES >> 4));
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          umma_bf16(tmem_s0 + (j & 1) * ATT_BN, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), idesc_qk, k != 0);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(tmem_s0 + (j & 1) * ATT_BN, dQ + kstep(k), dK + kstep(k), idesc_qk, k != 0);
         umma_commit(&s_full[j & 1]);
         umma_commit(&k_empty[j & 1]);
       };
@@ -153,14 +157,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         if (!mbar_wait(&p_ready[b], ph, abort_flag)) { atomicExch(p.status, 15); goto done; }
         if (!mbar_wait(&v_full[b], ph, abort_flag)) { atomicExch(p.status, 16); goto done; }
         tc_fence_after();
-        const uint32_t sv = smem_u32(smem + L::OFF_V + b * L::KV_BYTES);
-        const uint32_t spb = sp + b * L::P_BYTES;
+        const uint64_t dV = dV0 + static_cast<uint64_t>(b * (L::KV_BYTES >> 4));
+        const uint64_t dP = dP0 + static_cast<uint64_t>(b * (L::P_BYTES >> 4));
 #pragma unroll
-        for (int k = 0; k < ATT_BN / 16; ++k) {
-          const uint64_t da = make_smem_desc(spb + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc(sv + k * 2048, 16384, 1024);
-          umma_bf16(tmem_o, da, db, idesc_pv, (j | k) != 0);
-        }
+        for (int k = 0; k < ATT_BN / 16; ++k)
+          umma_bf16(tmem_o, dP + kstep(k), dV + static_cast<uint64_t>(k * 128), idesc_pv, (j | k) != 0);
         umma_commit(&v_empty[b]);
         umma_commit(&p_empty[b]);
         if (j + 2 < n_tiles) {   // S buffer b was consumed by the softmax of tile j: refill it with tile j+2

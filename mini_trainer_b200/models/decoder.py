@@ -75,8 +75,12 @@ class BlockActs:
 
 
 def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: PackedBatch, inv_freq, keep: bool = False,
-                  saved_attn=None, want_attn: bool = False):
+                  saved_attn=None, want_attn: bool = False, need_out: bool = True):
     """Returns ``(out, acts, attn_state)``.
+
+    ``need_out=False`` (recompute inside backward) stops before the down projection: backward reads
+    the block's intermediates, never its output, so that GEMM (27 % of the block's forward FLOPs for
+    Llama-3.1-8B) would be wasted work.
 
     ``acts`` is a ``BlockActs`` when ``keep`` (everything backward reads), else ``None``.
     ``saved_attn = (attn, lse)`` from an earlier forward skips the attention kernel (used by the
@@ -97,7 +101,7 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     n2, rstd2 = ops.rmsnorm(h1, p["ln2"], cfg.rms_norm_eps)
     gu = ops.linear(n2, p["wgu"], gather=None if plan is None else (plan, 1))
     act = ops.swiglu(gu)
-    out = ops.linear(act, p["wd"], None, h1)
+    out = ops.linear(act, p["wd"], None, h1) if need_out else None
     acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, gu, act) if keep else None
     return out, acts, ((attn, lse) if want_attn else None)
 

@@ -415,7 +415,8 @@ class ShardedEngine:
             g = self.blocks[i].layout.views(gbuf)
             xin, acts, attn_state = saved.pop()
             if acts is None:   # recompute the block forward (attention is skipped when its output was kept)
-                _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True, saved_attn=attn_state)
+                _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True, saved_attn=attn_state,
+                                             need_out=False)
             dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq)
             del acts, xin, attn_state
             self._release_pbuf(slot)
