@@ -94,7 +94,7 @@ def save_hf_checkpoint(engine, save_directory: str, model_name_or_path: str | No
                 src = os.path.join(model_name_or_path, fn)
                 if os.path.exists(src):
                     shutil.copy(src, os.path.join(save_directory, fn))
-        elif model_name_or_path:
+        elif model_name_or_path and not model_name_or_path.startswith("random:"):
             try:  # hub id: let transformers resolve it from the local cache
                 from transformers import AutoTokenizer
                 AutoTokenizer.from_pretrained(model_name_or_path).save_pretrained(save_directory)

@@ -73,6 +73,35 @@ def project_orthogonal(du, dv, u_hi, v_hi):
     return du, dv
 
 
+def project_orthogonal_tcgen05(ops, du, dv, u_hi, v_hi):
+    """Same projection with the four products on the tcgen05 GEMM (bf16 operands, fp32 accumulate
+    and fp32 results; the subtraction is the GEMM's residual epilogue):
+
+        P = U_hi^T dU   (both operands read MN-major)      dU <- dU + U_hi (-P)
+        R = dV V_hi^T   (both K-major)                     dV <- dV + (-R) V_hi
+
+    Requires every dimension to be a multiple of 8 (TMA strides); callers fall back to
+    ``project_orthogonal`` otherwise.
+    """
+    k_hi = u_hi.shape[1]
+    if k_hi == 0:
+        return du, dv
+    bf = torch.bfloat16
+    rows, k_lo = du.shape
+    cols = dv.shape[1]
+    u16, v16 = u_hi.to(bf).contiguous(), v_hi.to(bf).contiguous()
+    du32, dv32 = du.float().contiguous(), dv.float().contiguous()
+    pmat = torch.empty(k_hi, k_lo, dtype=torch.float32, device=du.device)
+    ops.gemm(u16, True, du32.to(bf), True, pmat, k_hi, k_lo, rows)
+    du_out = torch.empty_like(du32)
+    ops.gemm(u16, False, (-pmat).to(bf), True, du_out, rows, k_lo, k_hi, residual=du32)
+    rmat = torch.empty(k_lo, k_hi, dtype=torch.float32, device=du.device)
+    ops.gemm(dv32.to(bf), False, v16, False, rmat, k_lo, k_hi, cols)
+    dv_out = torch.empty_like(dv32)
+    ops.gemm((-rmat).to(bf), False, v16, True, dv_out, k_lo, cols, k_hi, residual=dv32)
+    return du_out.to(du.dtype), dv_out.to(dv.dtype)
+
+
 @dataclass
 class _Matrix:
     block: int
@@ -91,8 +120,10 @@ class _Matrix:
 
 
 class OSFT:
-    def __init__(self, engine, rank_ratio: float = 0.5, factor_dtype=torch.float32):
+    def __init__(self, engine, rank_ratio: float = 0.5, factor_dtype=torch.float32, projection: str = "auto"):
         self.eng, self.rank_ratio, self.dtype = engine, rank_ratio, factor_dtype
+        # "tcgen05": projection GEMMs on the hand-written kernel (GPU, dims multiple of 8); "torch": PyTorch matmuls
+        self.projection = projection if projection != "auto" else ("tcgen05" if hasattr(engine.ops, "gemm") else "torch")
         self.world, self.rank = engine.world, engine.rank
         self.mats: list[_Matrix] = []
         idx = 0
@@ -152,7 +183,11 @@ class OSFT:
             for mt in (m for m in self.mats if m.block == b and m.owner == self.rank):
                 g = views[mt.name][mt.r0:mt.r1].to(self.dtype)
                 du, ds, dv = factor_grads(g, *mt.factors)
-                du, dv = project_orthogonal(du, dv, mt.u_hi, mt.v_hi)
+                dims = (du.shape[0], du.shape[1], dv.shape[1], mt.u_hi.shape[1])
+                if self.projection == "tcgen05" and all(d % 8 == 0 and d > 0 for d in dims):
+                    du, dv = project_orthogonal_tcgen05(eng.ops, du, dv, mt.u_hi, mt.v_hi)
+                else:
+                    du, dv = project_orthogonal(du, dv, mt.u_hi, mt.v_hi)
                 mt.grads = [du, ds, dv]
                 sq += sum(t.float().pow(2).sum() for t in mt.grads).to(dev)
             self._mask_targets(grp, b, grp.gacc, 0.0)

@@ -1,0 +1,30 @@
+"""The ``train.py`` entry point end to end on CPU: reference flag names, files it must leave behind."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_train_cli_runs_and_writes_reference_layout(tmp_path):
+    out = str(tmp_path / "run")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT="29641")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:tiny-qwen2",
+           "--data-path", "synthetic:tiny-qwen2:48", "--batch-size", "8", "--max-tokens-per-gpu", "2048",
+           "--output-dir", out, "--min-samples-per-checkpoint", "16", "--max-steps", "2", "--learning-rate", "1e-4",
+           "--num-warmup-steps", "2", "--lr-scheduler", "constant_with_warmup", "--seed", "893", "--use-liger-kernels",
+           "--logging-level", "WARNING"]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    params = json.load(open(os.path.join(out, "training_params.json")))
+    assert params["batch_size"] == 8 and params["max_tokens_per_gpu"] == 2048 and params["WORLD_SIZE"] == 1
+    assert set(params) >= {"model_name_or_path", "data_path", "learning_rate", "num_warmup_steps", "lr_scheduler", "seed",
+                           "use_liger_kernels", "output_dir", "logging_level", "min_samples_per_checkpoint", "RANK"}
+    rows = [json.loads(l) for l in open(os.path.join(out, "training_metrics_0.jsonl"))]
+    assert [r["step"] for r in rows] == [1, 2]
+    assert rows[0]["lr"] == 1e-4 and rows[0]["num_samples"] == 8
+    ckpt = os.path.join(out, "hf_format", "samples_16.0")
+    assert os.path.exists(os.path.join(ckpt, "model.safetensors")) and os.path.exists(os.path.join(ckpt, "config.json"))

@@ -275,3 +275,20 @@ def test_gemm_two_cta(ops, M, N, K, layout):
     if layout == "nt":
         ops.gemm(a, False, b, False, out, M, N, K, residual=res, bias=bias, two_cta=True)
         assert rel_err(out, ref + res.float() + bias.float()) < 6e-3
+
+
+def test_osft_projection_on_tcgen05_gemm(ops):
+    """G - U(U^T G) and G - (G V^T) V on the tcgen05 GEMM against float64 PyTorch."""
+    from mini_trainer_b200.parallel import osft as O
+    torch.manual_seed(0)
+    w = torch.randn(512, 1024, device="cuda", dtype=torch.float64)
+    u_hi, s_hi, v_hi, u_lo, s_lo, v_lo = O.svd_split(w, 0.5)
+    du = torch.randn(512, u_lo.shape[1], device="cuda", dtype=torch.float64)
+    dv = torch.randn(v_lo.shape[0], 1024, device="cuda", dtype=torch.float64)
+    ref_u, ref_v = O.project_orthogonal(du, dv, u_hi, v_hi)
+    got_u, got_v = O.project_orthogonal_tcgen05(ops, du.float(), dv.float(), u_hi.float(), v_hi.float())
+    ops.check_status()
+    assert rel_err(got_u, ref_u) < 1e-2 and rel_err(got_v, ref_v) < 1e-2
+    # what is left inside the frozen subspace is at bf16 rounding level
+    assert (u_hi.float().t() @ got_u).norm() < 2e-2 * du.float().norm()
+    assert (got_v @ v_hi.float().t()).norm() < 2e-2 * dv.float().norm()
