@@ -69,6 +69,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--two-cta", action="store_true", help="use the cta_group::2 GEMM kernel (256x256 tiles per CTA pair)")
     a = ap.parse_args()
     ops = NativeOps("cuda:0")
     tf_peak, bw_peak, tag = peaks()
@@ -93,16 +94,16 @@ def main():
             if lay == "nt":
                 x, w = bf(M, K), bf(N, K, scale=0.02)
                 o = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-                fn = lambda: ops.gemm(x, False, w, False, o, M, N, K)
+                fn = lambda: ops.gemm(x, False, w, False, o, M, N, K, two_cta=a.two_cta)
             elif lay == "nn":
                 x, w = bf(M, K), bf(K, N, scale=0.02)
                 o = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-                fn = lambda: ops.gemm(x, False, w, True, o, M, N, K)
+                fn = lambda: ops.gemm(x, False, w, True, o, M, N, K, two_cta=a.two_cta)
             else:
                 x, w = bf(K, M), bf(K, N, scale=0.02)
                 o = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-                fn = lambda: ops.gemm(x, True, w, True, o, M, N, K)
-            report(f"gemm_{lay}_{M}x{N}x{K}", timeit(fn, a.iters, a.warmup, flush), flops=2.0 * M * N * K)
+                fn = lambda: ops.gemm(x, True, w, True, o, M, N, K, two_cta=a.two_cta)
+            report(f"gemm{2 if a.two_cta else 1}cta_{lay}_{M}x{N}x{K}", timeit(fn, a.iters, a.warmup, flush), flops=2.0 * M * N * K)
     if want("attn_fwd") or want("attn_bwd"):
         lens = [int(v) for v in a.lens.split(",")]
         T = sum(lens)
