@@ -68,3 +68,28 @@ def test_osft_step_runs_with_native_kernels():
     assert losses[-1] < losses[0]
     assert any(not torch.equal(a, g.master) for a, g in zip(before, eng.groups))
     assert len(ctl.mats) == 7 * cfg.num_hidden_layers
+
+
+def test_gpu_engine_exports_hf_checkpoint_that_transformers_loads(tmp_path):
+    """bf16 safetensors written from the GPU engine load in transformers and give the same logits
+    as the engine's own kernels (bf16 tolerance)."""
+    from transformers import AutoModelForCausalLM
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_model
+    from mini_trainer_b200.ops.native import NativeOps
+    cfg = get_preset("smoke-llama")
+    ops = NativeOps("cuda:0")
+    eng = ShardedEngine(cfg, "cuda:0", ops, optim=OptimConfig())
+    eng.init_random(seed=9, std=0.05)
+    path = save_model(eng, 64.0, str(tmp_path), None)
+    hf = AutoModelForCausalLM.from_pretrained(path, torch_dtype=torch.float32)
+    ids = torch.randint(0, cfg.vocab_size, (200,))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    mb = mb_collate_fn([{"input_ids": ids, "labels": ids, "len": 200, "num_loss_counted_tokens": 200}], 200)
+    pb = D.make_packed_batch(mb, "cuda:0")
+    blocks = [g.layout.views(g.shard) for g in eng.blocks]
+    head = eng.head.layout.views(eng.head.shard)
+    mine = D.forward_logits(ops, cfg, eng.embed.layout.views(eng.embed.shard)["embed"], blocks, head["norm"], head["lm_head"], pb)
+    ops.check_status()
+    err = ((mine.cpu() - ref).norm() / ref.norm()).item()
+    assert err < 3e-2, err
