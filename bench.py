@@ -122,14 +122,15 @@ def run_native(args) -> dict:
     eng.init_random(seed=893, on_device=True)
     sched = LRSchedule(1e-5, "constant_with_warmup", 10)
 
-    # identical batches on every rank; each rank packs its own share
+    # identical batches on every rank; each rank packs its own share. The dataset has the size the
+    # reference arm generates (2 x batches), so both arms draw the same samples in the same order.
     total_steps = 2 * (args.steps + args.warmup)
     ds = synthetic_dataset(batch_size * total_steps, spec, cfg.vocab_size, seed=893)
     sampler = iter(InfiniteSampler(len(ds), seed=893))
     cost_len = cfg.attention_cost_length() if args.balance == "cost" else None
     coll = MaxTokensPerRankCollator(max_tokens, rank=rank, world_size=world, cost_len=cost_len)
     batches = []
-    for _ in range(total_steps):
+    for _ in range(args.steps + args.warmup):
         idx = [next(sampler) for _ in range(batch_size)]
         mbs = coll.collate_indices(ds, idx)
         for mb in mbs:
@@ -199,7 +200,7 @@ def run_native(args) -> dict:
                   for mb in mbs)
         return host
 
-    r2 = timed(step_e2e, args.steps + args.warmup)
+    r2 = timed(step_e2e, 0)   # the same batches as phase (1) and as the reference arm (same dataset, sampler and seed)
     if hasattr(ops, "check_status"):
         ops.check_status()
     if getattr(ops, "profile", None) is not None and rank == 0:

@@ -31,7 +31,9 @@ device = init_distributed_environment(timeout_minutes=3)
 rank, world = dist.get_rank(), dist.get_world_size()
 cfg = get_preset("smoke-llama")
 comm = make_comm(os.environ.get("MTB200_COMM", "auto"), device)
-eng = ShardedEngine(cfg, device, get_ops(device), comm=comm, optim=OptimConfig(), activation_budget_bytes=0)
+budget = os.environ.get("MTB200_TEST_BUDGET", "0")
+eng = ShardedEngine(cfg, device, get_ops(device), comm=comm, optim=OptimConfig(),
+                    activation_budget_bytes=None if budget == "auto" else int(budget))
 eng.init_random(seed=5, std=0.05)
 ds = synthetic_dataset(64, LengthSpec(5.0, 0.7, 8, 700), cfg.vocab_size, seed=1)
 loader = iter(get_data_loader(dataset=ds, batch_size=16, max_tokens_per_gpu=1500, seed=3, rank=rank, world_size=world, prefetch=0))
@@ -53,10 +55,10 @@ dist.destroy_process_group()
 '''
 
 
-def _run(world: int, comm: str):
+def _run(world: int, comm: str, budget: str = "0"):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     env = dict(os.environ, MTB200_REPO=REPO, MTB200_COMM=comm, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1",
-               MASTER_PORT=str(port))
+               MASTER_PORT=str(port), MTB200_TEST_BUDGET=budget)
     if world == 1:
         cmd = [sys.executable, "-c", WORKER]
     else:
@@ -69,12 +71,14 @@ def _run(world: int, comm: str):
     raise AssertionError(f"worker failed (rc={proc.returncode}):\n{proc.stdout[-3000:]}\n{proc.stderr[-3000:]}")
 
 
-@pytest.mark.parametrize("comm", ["torchdist", "symmetric"])
-def test_two_gpus_match_one_gpu(comm):
+@pytest.mark.parametrize("comm,budget", [("torchdist", "0"), ("symmetric", "0"), ("symmetric", "auto")])
+def test_two_gpus_match_one_gpu(comm, budget):
+    """budget 0: every block recomputed (parameters gathered inside the recompute GEMMs);
+    budget auto: activations kept (parameters prefetched by the stand-alone pull in backward)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     one = _run(1, "auto")
-    two = _run(2, comm)
+    two = _run(2, comm, budget)
     for a, b in zip(one, two):
         assert abs(a["loss"] - b["loss"]) < 2e-2 * abs(a["loss"]), (one, two)
         assert abs(a["grad_norm"] - b["grad_norm"]) < 5e-2 * a["grad_norm"], (one, two)
