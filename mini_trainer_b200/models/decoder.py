@@ -102,7 +102,11 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     gu = ops.linear(n2, p["wgu"], gather=None if plan is None else (plan, 1))
     act = ops.swiglu(gu)
     out = ops.linear(act, p["wd"], None, h1) if need_out else None
-    acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, gu, act) if keep else None
+    acts = None
+    if keep == "compact":   # kept from forward to backward: drop what one elementwise kernel can rebuild
+        acts = BlockActs(x, None, rstd1, qkv, attn, lse, h1, None, rstd2, gu, None)
+    elif keep:
+        acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, gu, act)
     return out, acts, ((attn, lse) if want_attn else None)
 
 
@@ -111,14 +115,19 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     """Writes every parameter gradient of the block into ``g`` (views of the block's flat
     gradient buffer, same names as ``p``) and returns the gradient of the block input."""
     a = acts
+    # activations kept in compact form: the normalised inputs and the SwiGLU output are rebuilt by
+    # bandwidth-bound kernels (about 1 ms per block) instead of being held for the whole step
+    act = a.act if a.act is not None else ops.swiglu(a.gu)
     # MLP
     dact = ops.linear_dgrad(dout, p["wd"])
-    ops.linear_wgrad(dout, a.act, g["wd"])
+    ops.linear_wgrad(dout, act, g["wd"])
+    del act
     dgu = ops.swiglu_bwd(dact, a.gu)
     del dact
     dn2 = ops.linear_dgrad(dgu, p["wgu"])
-    ops.linear_wgrad(dgu, a.n2, g["wgu"])
-    del dgu
+    n2 = a.n2 if a.n2 is not None else ops.rmsnorm(a.h1, p["ln2"], cfg.rms_norm_eps)[0]
+    ops.linear_wgrad(dgu, n2, g["wgu"])
+    del dgu, n2
     dh1 = ops.rmsnorm_bwd(dn2, a.h1, a.rstd2, p["ln2"], g["ln2"], add_to=dout)
     del dn2
     # attention
@@ -130,8 +139,9 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     ops.rope_(dqkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
               inverse=True)
     dn1 = ops.linear_dgrad(dqkv, p["wqkv"])
-    ops.linear_wgrad(dqkv, a.n1, g["wqkv"], g.get("bqkv"))
-    del dqkv
+    n1 = a.n1 if a.n1 is not None else ops.rmsnorm(a.x, p["ln1"], cfg.rms_norm_eps)[0]
+    ops.linear_wgrad(dqkv, n1, g["wqkv"], g.get("bqkv"))
+    del dqkv, n1
     dx = ops.rmsnorm_bwd(dn1, a.x, a.rstd1, p["ln1"], g["ln1"], add_to=dh1)
     return dx
 

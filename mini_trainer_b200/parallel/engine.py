@@ -312,8 +312,8 @@ class ShardedEngine:
 
         2 = keep only the block input and recompute the whole block in backward (what the reference
         does for every block, setup_model_for_training.py:28-29); 1 = also keep the attention
-        output and its log-sum-exp so the recompute skips the attention kernel; 0 = keep every
-        intermediate, no recompute. Blocks are upgraded from the last one backwards (their
+        output and its log-sum-exp so the recompute skips the attention kernel; 0 = keep every GEMM
+        output (qkv, attention, h1, gate/up), so backward runs no forward GEMM at all. Blocks are upgraded from the last one backwards (their
         activations are freed first in backward) while the estimated footprint fits in
         ``activation_budget_bytes``. ``activation_budget_bytes = 0`` gives the reference behaviour.
         """
@@ -327,7 +327,9 @@ class ShardedEngine:
         es = 2 if self.param_dtype != torch.float32 else 4
         h, f = cfg.hidden_size, cfg.intermediate_size
         lvl1 = tokens * (cfg.q_size * es + cfg.num_attention_heads * 4)
-        lvl0 = tokens * ((3 * h + cfg.qkv_size + cfg.q_size + 3 * f) * es + cfg.num_attention_heads * 4 + 8)
+        # level 0 keeps qkv, the attention output, h1 and gate/up (the normalised inputs and the SwiGLU
+        # output are rebuilt in backward by elementwise kernels)
+        lvl0 = lvl1 + tokens * ((h + cfg.qkv_size + 2 * f) * es + 8)
         for i in range(nL - 1, -1, -1):      # cheapest upgrade first: keep attention everywhere it fits
             if budget >= lvl1:
                 levels[i] = 1
@@ -381,8 +383,8 @@ class ShardedEngine:
             _Side.wait(ev)
             nxt = self._gather_block(i + 1, fused=True) if i + 1 < nL else None
             xin = x
-            x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq, keep=levels[i] == 0,
-                                                  want_attn=levels[i] == 1)
+            x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq,
+                                                  keep="compact" if levels[i] == 0 else False, want_attn=levels[i] == 1)
             saved.append((xin, acts, attn_state))
             if i + 1 < nL or self.world == 1:
                 self._release_pbuf(slot)

@@ -86,3 +86,22 @@ def test_adamw_matches_torch():
     new = hf_state(eng)
     for k, v in sd.items():
         assert torch.allclose(new[k], v.detach(), atol=2e-4, rtol=1e-3), k
+
+
+def test_checkpoint_levels_give_identical_gradients():
+    """Keeping the attention output (level 1) or every GEMM output (level 0) must not change the math."""
+    cfg = small_cfg(False, True)
+    mb = make_mb([11, 3, 8], cfg.vocab_size, seed=4)
+    grads = []
+    for budget in (0, None, 10 ** 12):
+        eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), optim=OptimConfig(), activation_budget_bytes=budget)
+        eng.init_random(seed=6, std=0.2)
+        if budget is None:   # force level 1 everywhere
+            eng.plan_checkpointing = lambda tokens: [1] * cfg.num_hidden_layers
+        else:
+            assert set(eng.plan_checkpointing(22)) == ({2} if budget == 0 else {0})
+        eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / mb["batch_num_loss_counted_tokens"])
+        grads.append([g.gacc.clone() for g in eng.groups])
+    for other in grads[1:]:
+        for a, b in zip(grads[0], other):
+            assert torch.allclose(a, b, atol=1e-6, rtol=1e-5)
