@@ -36,6 +36,7 @@ constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr int GROUP_M = 16;
+constexpr int GATHER_GROUP_N = 4;   // column-tiles per band in the all-gather variant
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct GemmParams {
@@ -53,6 +54,8 @@ struct GemmParams {
 // buffer that the B tensor map points at, 128 KB chunk by chunk, and publish each finished chunk
 // in a flag array. The TMA producer only loads a B tile after the chunks under it are flagged.
 constexpr int GATHER_THREADS = 256;
+constexpr int GATHER_EXTRA_THREADS = GATHER_THREADS + 32;   // gather warps + one flag-checker warp
+constexpr int GATHER_UNROLL = 8;     // 16-byte peer loads in flight per gather thread
 constexpr int GATHER_CHUNK_BYTES = 128 * 1024;
 constexpr int GATHER_MAX_RANKS = 16;
 
@@ -69,6 +72,14 @@ struct GatherParams {
   unsigned long long b_byte_off;   // byte offset of B's first element inside dst
 };
 
+__device__ __forceinline__ uint32_t ld_acquire_cta_shared(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_cta_shared(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -76,7 +87,7 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int* p) {
 }
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false>
-__global__ void __launch_bounds__(GATHER ? GEMM_THREADS + GATHER_THREADS : GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GATHER ? GEMM_THREADS + GATHER_EXTRA_THREADS : GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p,
             const __grid_constant__ GatherParams g) {
   extern __shared__ uint8_t smem_raw[];
@@ -87,6 +98,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint32_t* verified = tmem_slot + 2;   // gather variant: tiles of this CTA whose weight chunks have all arrived
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
@@ -97,6 +109,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
     *abort_flag = 0;
+    *verified = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -108,6 +121,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
 
   auto tile_coords = [&](int t, int& tm, int& tn) {
+    if constexpr (GATHER) {
+      // Bands of GROUP_N column-tiles, all row-tiles inside a band: the weight is consumed front to
+      // back at an even rate over the whole launch (a band of row-tiles would need the ENTIRE weight
+      // within its first band, i.e. within the first few waves, faster than the links deliver it).
+      const int band = t / (GATHER_GROUP_N * tiles_m);
+      const int first_n = band * GATHER_GROUP_N;
+      const int cols = min(GATHER_GROUP_N, tiles_n - first_n);
+      const int local = t - band * GATHER_GROUP_N * tiles_m;
+      tn = first_n + local % cols;
+      tm = local / cols;
+      return;
+    }
     const int band = t / (GROUP_M * tiles_n);
     const int first_m = band * GROUP_M;
     const int rows = min(GROUP_M, tiles_m - first_m);
@@ -119,22 +144,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      uint32_t it = 0;
+      uint32_t it = 0, tl = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         int tm, tn;
         tile_coords(t, tm, tn);
         if (GATHER) {
-          // rows [tn*BN, tn*BN+BN) of the K-major weight are one contiguous byte range of the full buffer
-          const unsigned long long lo = g.b_byte_off + static_cast<unsigned long long>(tn) * BN * p.K * 2;
-          const int rows = min(BN, p.N - tn * BN);
-          const unsigned long long hi = lo + static_cast<unsigned long long>(rows) * p.K * 2 - 1;
-          for (int c = static_cast<int>(lo / GATHER_CHUNK_BYTES); c <= static_cast<int>(hi / GATHER_CHUNK_BYTES); ++c) {
-            uint32_t spins = 0;
-            while (ld_acquire_gpu(g.flags + c) != g.epoch) {
-              if (++spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; atomicExch(p.status, 5); goto done; }
-            }
+          // the checker warp has seen the flags of every chunk under this tile's B rows
+          uint32_t spins = 0;
+          while (ld_acquire_cta_shared(verified) <= tl) {
+            if (++spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; atomicExch(p.status, 5); goto done; }
           }
           asm volatile("fence.proxy.async;" ::: "memory");   // peer data was written with ordinary stores, TMA reads it
+          ++tl;
         }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
@@ -187,6 +208,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         umma_commit(&tfull_bar[acc]);   // accumulator complete
       }
     }
+  } else if (GATHER && warp == 6 + GATHER_THREADS / 32) {
+    // ------------------------------------------------------------------ flag checker (warp 14)
+    // Runs ahead of the TMA producer: for each of this CTA's tiles, its lanes poll the flags of the
+    // chunks under the tile's B rows in parallel, then publish the tile count in shared memory. The
+    // producer thread therefore never waits on a chain of dependent global loads.
+    uint32_t tl = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tl) {
+      int tm, tn;
+      tile_coords(t, tm, tn);
+      // rows [tn*BN, tn*BN+BN) of the K-major weight are one contiguous byte range of the full buffer
+      const unsigned long long lo = g.b_byte_off + static_cast<unsigned long long>(tn) * BN * p.K * 2;
+      const int rows = min(BN, p.N - tn * BN);
+      const unsigned long long hi = lo + static_cast<unsigned long long>(rows) * p.K * 2 - 1;
+      const int c_hi = static_cast<int>(hi / GATHER_CHUNK_BYTES);
+      bool failed = false;
+      for (int c0 = static_cast<int>(lo / GATHER_CHUNK_BYTES); c0 <= c_hi && !failed; c0 += 32) {
+        const int c = c0 + lane;
+        bool ok = c > c_hi;
+        uint32_t spins = 0;
+        while (true) {
+          if (!ok) ok = ld_acquire_gpu(g.flags + c) == g.epoch;
+          if (__all_sync(0xffffffffu, ok)) break;
+          ++spins;
+          const bool stop = spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag);
+          if (__any_sync(0xffffffffu, stop)) { failed = true; break; }
+        }
+      }
+      __syncwarp();
+      if (failed) {
+        if (lane == 0) { *abort_flag = 1; atomicExch(p.status, 5); }
+        break;
+      }
+      if (lane == 0) st_release_cta_shared(verified, tl + 1);
+    }
   } else if (GATHER && warp >= 6) {
     // ------------------------------------------------------------------ gather warps (6..13)
     const int gt = threadIdx.x - GEMM_THREADS;
@@ -200,19 +255,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const unsigned long long b1 = min(b0 + GATHER_CHUNK_BYTES, total);
       const unsigned long long v0 = b0 >> 4, nv = (b1 - b0) >> 4;
       uint4* dst = reinterpret_cast<uint4*>(g.dst) + v0;
-      for (unsigned long long j = gt; j < nv; j += 4 * GATHER_THREADS) {
-        uint4 v[4];
+      // a chunk lies in one peer's shard, or straddles one boundary (shards are larger than a chunk);
+      // the peer is resolved once per chunk, not per vector
+      const unsigned long long pr0 = v0 / vec_per_shard;
+      const unsigned long long first = min(nv, (pr0 + 1) * vec_per_shard - v0);   // vectors that belong to peer pr0
+      const uint4* src0 = reinterpret_cast<const uint4*>(g.peer_base[pr0] + g.shard_off) + (v0 - pr0 * vec_per_shard);
+      const uint4* src1 = first < nv ? reinterpret_cast<const uint4*>(g.peer_base[pr0 + 1] + g.shard_off) - first : src0;
+      for (unsigned long long j = gt; j < nv; j += GATHER_UNROLL * GATHER_THREADS) {
+        uint4 v[GATHER_UNROLL];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < GATHER_UNROLL; ++u) {
           const unsigned long long jj = j + u * GATHER_THREADS;
-          if (jj < nv) {
-            const unsigned long long gv = v0 + jj;
-            const unsigned long long pr = gv / vec_per_shard;
-            v[u] = *(reinterpret_cast<const uint4*>(g.peer_base[pr] + g.shard_off) + (gv - pr * vec_per_shard));
-          }
+          if (jj < nv) v[u] = jj < first ? src0[jj] : src1[jj];
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < GATHER_UNROLL; ++u) {
           const unsigned long long jj = j + u * GATHER_THREADS;
           if (jj < nv) dst[jj] = v[u];
         }
@@ -376,7 +433,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   // the gathering variant always uses every SM: its extra warps carry the transfer
   const int grid = (GATHER || tiles >= g_num_sms) ? g_num_sms : tiles;
   static const GatherParams none{};
-  kern<<<grid, GATHER ? GEMM_THREADS + GATHER_THREADS : GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p, gp ? *gp : none);
+  kern<<<grid, GATHER ? GEMM_THREADS + GATHER_EXTRA_THREADS : GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p, gp ? *gp : none);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -431,6 +488,7 @@ int mtb200_gemm_bf16_allgather(const void* A, long long lda, void* D, long long 
   using namespace mtb;
   if (M <= 0 || N <= 0 || K <= 0) return -10;
   if (N % 8 || ldd % 8 || K % 8 || world < 1 || world > GATHER_MAX_RANKS || shard_bytes % 16 || w_byte_off % 16) return -10;
+  if (world > 1 && shard_bytes < static_cast<unsigned long long>(GATHER_CHUNK_BYTES)) return -11;   // a chunk may straddle one shard boundary at most
   CUtensorMap ta, tb;
   int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
   if (rc) return rc;

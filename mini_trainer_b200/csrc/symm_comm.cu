@@ -54,26 +54,26 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
 __global__ void __launch_bounds__(1024) symm_allgather_kernel(PeerTable peers, unsigned long long src_off, unsigned long long shard_bytes,
                                                              uint8_t* __restrict__ dst, int world, unsigned long long vec_lo,
                                                              unsigned long long vec_hi) {
+  // Block b copies from peer (b % world); the blocks of one peer stride over that peer's part of
+  // [vec_lo, vec_hi). No per-vector index arithmetic beyond an add: four independent loads in flight.
   const unsigned long long vec_per = shard_bytes >> 4;
-  const unsigned long long total = vec_hi;
-  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
-  unsigned long long i = vec_lo + static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  // 4 independent loads in flight per thread
-  for (; i + 3 * stride < total; i += 4 * stride) {
+  const int p = blockIdx.x % world;
+  const unsigned long long sub = blockIdx.x / world, nsub = gridDim.x / world;
+  const unsigned long long lo = max(vec_lo, static_cast<unsigned long long>(p) * vec_per);
+  const unsigned long long hi = min(vec_hi, static_cast<unsigned long long>(p + 1) * vec_per);
+  if (sub >= nsub || lo >= hi) return;
+  const uint4* __restrict__ src = reinterpret_cast<const uint4*>(peers.base[p] + src_off) - static_cast<unsigned long long>(p) * vec_per;
+  uint4* __restrict__ out = reinterpret_cast<uint4*>(dst);
+  const unsigned long long stride = nsub * blockDim.x;
+  unsigned long long i = lo + sub * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < hi; i += 4 * stride) {
     uint4 v[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const unsigned long long j = i + u * stride;
-      const int p = static_cast<int>(j / vec_per);
-      v[u] = *(reinterpret_cast<const uint4*>(peers.base[p] + src_off) + (j - p * vec_per));
-    }
+    for (int u = 0; u < 4; ++u) v[u] = src[i + u * stride];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) reinterpret_cast<uint4*>(dst)[i + u * stride] = v[u];
+    for (int u = 0; u < 4; ++u) out[i + u * stride] = v[u];
   }
-  for (; i < total; i += stride) {
-    const int p = static_cast<int>(i / vec_per);
-    reinterpret_cast<uint4*>(dst)[i] = *(reinterpret_cast<const uint4*>(peers.base[p] + src_off) + (i - p * vec_per));
-  }
+  for (; i < hi; i += stride) out[i] = src[i];
 }
 
 // ---------------------------------------------------------------------------------- signalling
@@ -221,6 +221,8 @@ int mtb200_symm_allgather(const unsigned long long* bases, int world, unsigned l
   if (world < 1 || world > MAX_RANKS || shard_bytes % 16 || src_off % 16 || byte_lo % 16 || byte_hi % 16) return -10;
   if (byte_hi == 0) byte_hi = shard_bytes * world;
   if (byte_hi > shard_bytes * world || byte_lo > byte_hi) return -10;
+  if (blocks < world) blocks = world;
+  blocks -= blocks % world;   // the same number of blocks per peer
   symm_allgather_kernel<<<blocks, 1024, 0, st>>>(make_table(bases, world), src_off, shard_bytes, reinterpret_cast<uint8_t*>(dst), world,
                                                  byte_lo >> 4, byte_hi >> 4);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

@@ -129,7 +129,9 @@ class ShardedEngine:
         # Buffers that peers read (parameter shards, gradient buffers) live in the comm backend's
         # symmetric arena when it has one; otherwise they are ordinary device tensors.
         self.symmetric = hasattr(self.comm, "setup")
-        self.fused_gather = self.symmetric and os.environ.get("MTB200_FUSED_GATHER", "1") != "0"
+        # the fused gather resolves one shard boundary per 128 KB chunk, so shards must be at least that large
+        self.fused_gather = (self.symmetric and os.environ.get("MTB200_FUSED_GATHER", "1") != "0"
+                             and layouts[1].shard_numel * torch.empty(0, dtype=self.param_dtype).element_size() >= 128 * 1024)
         if self.symmetric:
             es = torch.empty(0, dtype=self.param_dtype).element_size()
             payload = sum(l.shard_numel for l in layouts) + nbuf * blk + layouts[0].padded_numel + layouts[-1].padded_numel
