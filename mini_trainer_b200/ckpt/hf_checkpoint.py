@@ -102,12 +102,13 @@ def save_hf_checkpoint(engine, save_directory: str, model_name_or_path: str | No
                 log_rank_0(f"tokenizer not saved: {e}")
 
 
-def save_model(engine, samples_seen, output_dir: str, model_name_or_path: str | None = None) -> str:
+def save_model(engine, samples_seen, output_dir: str, model_name_or_path: str | None = None,
+               max_shard_bytes: int = MAX_SHARD_BYTES) -> str:
     """Reference-compatible wrapper: path naming, timing message, trailing barrier."""
     log_rank_0(f"Saving model at {samples_seen} samples")
     start = time.time()
     save_directory = str(Path(output_dir) / "hf_format" / f"samples_{samples_seen}")
-    save_hf_checkpoint(engine, save_directory, model_name_or_path)
+    save_hf_checkpoint(engine, save_directory, model_name_or_path, max_shard_bytes=max_shard_bytes)
     log_rank_0(f"\033[1;38;2;0;255;255mSaved model at\033[0m {samples_seen} samples in {time.time() - start:.2f} seconds")
     if dist.is_available() and dist.is_initialized():
         dist.barrier()

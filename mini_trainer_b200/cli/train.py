@@ -41,6 +41,11 @@ def main(
     num_workers: int = Option(0, help="DataLoader worker processes (0 = packing thread)"),
     max_grad_norm: float = Option(1.0, help="Global gradient-norm clip"),
     weight_decay: float = Option(0.0, help="AdamW weight decay"),
+    adam_beta1: float = Option(0.9, help="AdamW beta1"),
+    adam_beta2: float = Option(0.95, help="AdamW beta2"),
+    adam_eps: float = Option(1e-8, help="AdamW epsilon"),
+    max_shard_gb: float = Option(5.0, help="Largest safetensors shard of an exported checkpoint, in GB"),
+    dist_timeout_minutes: float = Option(180.0, help="Process-group timeout"),
     optimizer_state_dtype: str = Option("auto", help="auto | fp32 | bf16 (AdamW moments)"),
     balance_by: str = Option("cost", help="cost | tokens: what the LPT packer balances across ranks (same global batch either way)"),
     osft: bool = Option(False, help="Orthogonal-subspace fine-tuning of the attention/MLP projections"),
@@ -56,7 +61,7 @@ def main(
     from ..utils.dist import init_distributed_environment
     from ..utils.log import setup_logger
 
-    device = init_distributed_environment()
+    device = init_distributed_environment(timeout_minutes=dist_timeout_minutes)
     output_path = Path(output_dir)
     output_path.mkdir(parents=True, exist_ok=True)
     rank = int(os.environ.get("RANK", 0))
@@ -78,7 +83,8 @@ def main(
     sd = {"auto": None, "fp32": torch.float32, "bf16": torch.bfloat16}[optimizer_state_dtype]
     model = setup_model(model_name_or_path=model_name_or_path, use_liger_kernels=use_liger_kernels, device=device,
                         comm_backend=comm_backend, state_dtype=sd, seed=seed, max_tokens_per_gpu=max_tokens_per_gpu,
-                        optim=OptimConfig(max_grad_norm=max_grad_norm, weight_decay=weight_decay))
+                        optim=OptimConfig(max_grad_norm=max_grad_norm, weight_decay=weight_decay, beta1=adam_beta1,
+                                          beta2=adam_beta2, eps=adam_eps))
     if osft:
         from ..parallel.osft import enable_osft
         enable_osft(model, rank_ratio=osft_rank_ratio)
@@ -101,7 +107,7 @@ def main(
         loader = get_data_loader(data_path=data_path, batch_size=batch_size, max_tokens_per_gpu=max_tokens_per_gpu,
                                  seed=seed, num_workers=num_workers, pin_memory=device.type == "cuda", cost_len=cost_len)
     train(model, optimizer, sched, loader, output_dir, min_samples_per_checkpoint, model_name_or_path,
-          max_steps=max_steps)
+          max_steps=max_steps, max_shard_bytes=int(max_shard_gb * 1e9))
 
 
 if __name__ == "__main__":

@@ -121,7 +121,8 @@ def take_gradient_step(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule
 
 def train(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule, data_loader, output_dir: str,
           min_samples_per_checkpoint: int, model_name_or_path: Optional[str] = None,
-          max_steps: Optional[int] = None, log_echo: bool = True) -> dict:
+          max_steps: Optional[int] = None, log_echo: bool = True,
+          max_shard_bytes: Optional[int] = None) -> dict:
     rank = int(os.environ.get("RANK", 0))
     world_size = model.world
     is_main = rank == 0
@@ -184,7 +185,8 @@ def train(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule, data_loader
             }
             metric_logger.log_sync(dict(last))
         if total_samples_accumulated - last_saved_samples >= min_samples_per_checkpoint:
-            save_model(model, total_samples_accumulated, output_dir, model_name_or_path)
+            save_model(model, total_samples_accumulated, output_dir, model_name_or_path,
+                       **({} if max_shard_bytes is None else {"max_shard_bytes": max_shard_bytes}))
             last_saved_samples = total_samples_accumulated
         if max_steps is not None and step >= max_steps:
             break
