@@ -24,7 +24,7 @@ class LogLevelEnum(str, Enum):
 @app.command()
 def main(
     model_name_or_path: str = Option("Qwen/Qwen2.5-1.5B-Instruct", help="HF checkpoint directory, or random:<preset>"),
-    data_path: str = Option("test.jsonl", help="Path to the training data JSONL file, or synthetic:<preset>[:num_samples]"),
+    data_path: str = Option("test.jsonl", help="Path to the training data JSONL file, or synthetic:<preset>[:num_samples[:longest_sample]]"),
     batch_size: int = Option(1024, help="Initial batch size before dynamic splitting"),
     max_tokens_per_gpu: int = Option(10000, help="Maximum tokens per GPU per minibatch"),
     learning_rate: float = Option(5e-6, help="Peak learning rate"),
@@ -100,6 +100,9 @@ def main(
         parts = data_path.split(":")
         spec, vocab, _, _ = CONFIG_DATA[parts[1]]
         n = int(parts[2]) if len(parts) > 2 else 4096
+        if len(parts) > 3:   # synthetic:<preset>:<num_samples>:<longest sample>
+            import dataclasses
+            spec = dataclasses.replace(spec, hi=int(parts[3]))
         dataset = synthetic_dataset(n, spec, min(vocab, model.cfg.vocab_size), seed=seed)
         loader = get_data_loader(dataset=dataset, batch_size=batch_size, max_tokens_per_gpu=max_tokens_per_gpu,
                                  seed=seed, pin_memory=device.type == "cuda", cost_len=cost_len)
