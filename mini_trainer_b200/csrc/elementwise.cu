@@ -233,13 +233,32 @@ __global__ void __launch_bounds__(128) embedding_fwd_kernel(const __nv_bfloat16*
   for (int c = threadIdx.x * 8; c < H; c += 128 * 8) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
 }
 
-// dW[ids[t], :] += dx[t, :] with packed bf16x2 atomics (rows of one token id may collide).
-__global__ void __launch_bounds__(128) embedding_bwd_kernel(__nv_bfloat16* __restrict__ dw, const long long* __restrict__ ids,
-                                                           const __nv_bfloat16* __restrict__ dx, int H) {
-  const long long t = blockIdx.x;
-  __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(dw + ids[t] * H);
-  const __nv_bfloat162* src = reinterpret_cast<const __nv_bfloat162*>(dx + t * H);
-  for (int c = threadIdx.x; c < (H >> 1); c += 128) atomicAdd(dst + c, src[c]);
+// dW[id, :] += sum over the tokens t with ids[t] == id of dx[t, :], deterministic: the token ids arrive
+// sorted (stable, so equal ids keep their token order) with the permutation that sorted them. The block
+// at the first position of each run of equal ids sums the run's rows in fp32, in that fixed order, adds
+// what dW already holds (the LM-head gradient when the embeddings are tied) and rounds once. The other
+// blocks of the run exit at once. No atomics, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(128) embedding_bwd_kernel(__nv_bfloat16* __restrict__ dw, const long long* __restrict__ sorted_ids,
+                                                           const long long* __restrict__ order, const __nv_bfloat16* __restrict__ dx,
+                                                           int T, int H) {
+  const int j = blockIdx.x;
+  const long long id = sorted_ids[j];
+  if (j > 0 && sorted_ids[j - 1] == id) return;
+  __nv_bfloat16* dst = dw + id * H;
+  for (int c = threadIdx.x * 8; c < H; c += 128 * 8) {
+    float acc[8];
+    {
+      const uint4 v = *reinterpret_cast<const uint4*>(dst + c);
+      const float2 a0 = unpack_bf16(v.x), a1 = unpack_bf16(v.y), a2 = unpack_bf16(v.z), a3 = unpack_bf16(v.w);
+      acc[0] = a0.x; acc[1] = a0.y; acc[2] = a1.x; acc[3] = a1.y; acc[4] = a2.x; acc[5] = a2.y; acc[6] = a3.x; acc[7] = a3.y;
+    }
+    for (int k = j; k < T && sorted_ids[k] == id; ++k) {
+      const uint4 v = *reinterpret_cast<const uint4*>(dx + order[k] * H + c);
+      const float2 a0 = unpack_bf16(v.x), a1 = unpack_bf16(v.y), a2 = unpack_bf16(v.z), a3 = unpack_bf16(v.w);
+      acc[0] += a0.x; acc[1] += a0.y; acc[2] += a1.x; acc[3] += a1.y; acc[4] += a2.x; acc[5] += a2.y; acc[6] += a3.x; acc[7] += a3.y;
+    }
+    *reinterpret_cast<uint4*>(dst + c) = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+  }
 }
 
 // ------------------------------------------------------------------------------ cross-entropy
@@ -466,10 +485,10 @@ int mtb200_embedding_fwd(const void* w, const long long* ids, void* out, int T, 
   return launch_ok();
 }
 
-int mtb200_embedding_bwd(void* dw, const long long* ids, const void* dx, int T, int H, cudaStream_t st) {
+int mtb200_embedding_bwd(void* dw, const long long* sorted_ids, const long long* order, const void* dx, int T, int H, cudaStream_t st) {
   if (T <= 0) return 0;
-  if (H % 2) return -10;
-  embedding_bwd_kernel<<<T, 128, 0, st>>>((bf16*)dw, ids, (const bf16*)dx, H);
+  if (H % 8) return -10;
+  embedding_bwd_kernel<<<T, 128, 0, st>>>((bf16*)dw, sorted_ids, order, (const bf16*)dx, T, H);
   return launch_ok();
 }
 

@@ -51,7 +51,7 @@ class _Sig:
     mtb200_swiglu_fwd = [P, P, L, I, P]
     mtb200_swiglu_bwd = [P, P, P, L, I, P]
     mtb200_embedding_fwd = [P, P, P, I, I, P]
-    mtb200_embedding_bwd = [P, P, P, I, I, P]
+    mtb200_embedding_bwd = [P, P, P, P, I, I, P]
     mtb200_ce_fwd_bwd = [P, L, P, P, P, L, I, I, F, L, P]
     mtb200_colsum = [P, L, P, P, I, I, P]
     mtb200_accumulate = [P, P, L, I, I, P]
@@ -159,8 +159,10 @@ class NativeOps:
         return out
 
     def embedding_bwd(self, dweight, ids, dx):
-        self._call("mtb200_embedding_bwd", dweight.data_ptr(), ids.data_ptr(), dx.data_ptr(), ids.shape[0],
-                   dweight.shape[1], self._st())
+        """dweight[ids] += dx, deterministic: a stable sort groups equal ids; one block sums each group in fp32."""
+        sorted_ids, order = torch.sort(ids, stable=True)
+        self._call("mtb200_embedding_bwd", dweight.data_ptr(), sorted_ids.data_ptr(), order.data_ptr(), dx.data_ptr(),
+                   ids.shape[0], dweight.shape[1], self._st())
 
     # -- rmsnorm ----------------------------------------------------------------------
     def rmsnorm(self, x, w, eps):
