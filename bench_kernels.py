@@ -3,6 +3,7 @@
     python bench_kernels.py --op gemm --layout nt --m 8192 --n 8192 --k 8192
     python bench_kernels.py --op attn_fwd --lens 16384,16384
     python bench_kernels.py --op all
+    (ops: gemm, attn_fwd, attn_bwd, rmsnorm, swiglu, rope, ce, linear_ce, embedding, adamw)
 
 Each op is timed with CUDA events on the launching stream after warm-up, with a synchronize on
 both sides. Inputs are larger than the 126 MB L2 (or an L2-sized buffer is rewritten between
@@ -68,6 +69,8 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--adamw-n", type=int, default=512 * 1024 * 1024, help="elements of the AdamW shard (14 bytes each with fp32 moments)")
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--two-cta", action="store_true", help="use the cta_group::2 GEMM kernel (256x256 tiles per CTA pair)")
     a = ap.parse_args()
@@ -87,7 +90,14 @@ def main():
         out.append(rec)
         print(json.dumps(rec), flush=True)
 
-    want = lambda n: a.op in ("all", n)
+    EW = ("rmsnorm", "swiglu", "rope", "ce", "embedding", "adamw")   # --op ew: the bandwidth-bound kernels
+
+    def want(n):
+        ok = a.op in ("all", n) or (a.op == "ew" and n in EW)
+        if ok:
+            torch.cuda.empty_cache()   # the previous op's tensors are gone: keep the resident set small
+        return ok
+
     if want("gemm"):
         M, N, K = a.m, a.n, a.k
         for lay in (["nt", "nn", "tn"] if a.op == "all" else [a.layout]):
@@ -118,25 +128,61 @@ def main():
             report(f"attn_fwd_T{T}", timeit(lambda: ops.attention(qkv, cu, cu_host, max(lens), a.hq, a.hkv, a.d), a.iters, a.warmup, flush), flops=fl)
         if want("attn_bwd"):
             report(f"attn_bwd_T{T}", timeit(lambda: ops.attention_bwd(dout, qkv, o, lse, cu, cu_host, max(lens), a.hq, a.hkv, a.d), a.iters, a.warmup, flush), flops=2.5 * fl)
-    if want("rmsnorm"):
+    def op_rmsnorm():
         T, H = a.tokens, a.hidden
         x, w, dy = bf(T, H), bf(H), bf(T, H)
         y, rstd = ops.rmsnorm(x, w, 1e-5)
         dw = torch.empty_like(w)
         report(f"rmsnorm_fwd_{T}x{H}", timeit(lambda: ops.rmsnorm(x, w, 1e-5), a.iters, a.warmup, flush), bytes_=2.0 * T * H * 2)
         report(f"rmsnorm_bwd_{T}x{H}", timeit(lambda: ops.rmsnorm_bwd(dy, x, rstd, w, dw, add_to=dy), a.iters, a.warmup, flush), bytes_=4.0 * T * H * 2)
-    if want("swiglu"):
+    def op_swiglu():
         T, F = a.tokens, 14336
         gu, da = bf(T, 2 * F), bf(T, F)
         report(f"swiglu_fwd_{T}x{F}", timeit(lambda: ops.swiglu(gu), a.iters, a.warmup, flush), bytes_=3.0 * T * F * 2)
         report(f"swiglu_bwd_{T}x{F}", timeit(lambda: ops.swiglu_bwd(da, gu), a.iters, a.warmup, flush), bytes_=5.0 * T * F * 2)
-    if want("adamw"):
-        n = 512 * 1024 * 1024
+    def op_rope():
+        T = a.tokens
+        qkv = bf(T, (a.hq + 2 * a.hkv) * a.d)
+        pos = (torch.arange(T, device="cuda") % 4096).to(torch.int32)
+        inv = (1.0 / (5e5 ** (torch.arange(0, a.d, 2, device="cuda", dtype=torch.float32) / a.d))).contiguous()
+        # reads and rewrites the q and k heads in place
+        report(f"rope_{T}x{a.hq}+{a.hkv}x{a.d}", timeit(lambda: ops.rope_(qkv, pos, inv, a.hq, a.hkv, a.d), a.iters, a.warmup, flush),
+               bytes_=2.0 * T * (a.hq + a.hkv) * a.d * 2)
+    def op_ce():
+        R, V = 2048, a.vocab
+        logits = torch.randn(R, V, device="cuda")
+        tg = torch.randint(0, V, (R,), device="cuda")
+        loss = torch.empty(R, device="cuda")
+        dlog = torch.empty(R, V, dtype=torch.bfloat16, device="cuda")
+        fn = lambda: ops._call("mtb200_ce_fwd_bwd", logits.data_ptr(), V, tg.data_ptr(), loss.data_ptr(), dlog.data_ptr(), V, R, V,
+                               1.0, -100, ops._st())
+        # two passes over the fp32 logits (online max/sum, then gradient) + the bf16 gradient write
+        report(f"ce_fwd_bwd_{R}x{V}", timeit(fn, a.iters, a.warmup, flush), bytes_=R * V * (4.0 + 4.0 + 2.0))
+    def op_linear_ce():
+        T, H, V = min(a.tokens, 8192), a.hidden, a.vocab
+        x, w = bf(T, H), bf(V, H, scale=0.02)
+        tg = torch.randint(0, V, (T,), device="cuda")
+        dw = torch.empty(V, H, dtype=torch.bfloat16, device="cuda")
+        report(f"linear_ce_{T}x{H}x{V}", timeit(lambda: ops.linear_ce(x, w, tg, 1.0, dw), a.iters, a.warmup, flush), flops=6.0 * T * H * V)
+    def op_embedding():
+        T, H, V = a.tokens, a.hidden, a.vocab
+        w, dx = bf(V, H), bf(T, H)
+        ids = torch.randint(0, V, (T,), device="cuda")
+        dw = torch.zeros(V, H, dtype=torch.bfloat16, device="cuda")
+        report(f"embedding_fwd_{T}x{H}", timeit(lambda: ops.embedding(w, ids), a.iters, a.warmup, flush), bytes_=2.0 * T * H * 2)
+        # sort of the ids + read dx, read-modify-write the touched rows
+        report(f"embedding_bwd_{T}x{H}", timeit(lambda: ops.embedding_bwd(dw, ids, dx), a.iters, a.warmup, flush), bytes_=3.0 * T * H * 2)
+    def op_adamw():
+        n = a.adamw_n
         master, m, v, g = (torch.zeros(n, device="cuda") for _ in range(4))
         p = torch.empty(n, dtype=torch.bfloat16, device="cuda")
         coef = torch.ones(1, device="cuda")
         report(f"adamw_{n}", timeit(lambda: ops.adamw_step(master, m, v, g, p, 1e-4, 0.9, 0.95, 1e-8, 0.0, 2, coef), a.iters, a.warmup, flush),
                bytes_=n * (4 * 4 + 3 * 4 + 2.0))
+    for name, fn in (("rmsnorm", op_rmsnorm), ("swiglu", op_swiglu), ("rope", op_rope), ("ce", op_ce), ("linear_ce", op_linear_ce),
+                     ("embedding", op_embedding), ("adamw", op_adamw)):
+        if want(name):
+            fn()   # the op's tensors die with its frame
     ops.check_status()
 
 
