@@ -71,10 +71,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--adamw-n", type=int, default=512 * 1024 * 1024, help="elements of the AdamW shard (14 bytes each with fp32 moments)")
+    ap.add_argument("--ce-chunk", type=int, default=0, help="token rows per linear+CE chunk (0 = library default)")
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--two-cta", action="store_true", help="use the cta_group::2 GEMM kernel (256x256 tiles per CTA pair)")
     a = ap.parse_args()
     ops = NativeOps("cuda:0")
+    if a.ce_chunk:
+        ops.ce_chunk = a.ce_chunk
     tf_peak, bw_peak, tag = peaks()
     flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda") if a.flush_l2 else None
     out = []
@@ -163,7 +166,7 @@ def main():
         x, w = bf(T, H), bf(V, H, scale=0.02)
         tg = torch.randint(0, V, (T,), device="cuda")
         dw = torch.empty(V, H, dtype=torch.bfloat16, device="cuda")
-        report(f"linear_ce_{T}x{H}x{V}", timeit(lambda: ops.linear_ce(x, w, tg, 1.0, dw), a.iters, a.warmup, flush), flops=6.0 * T * H * V)
+        report(f"linear_ce_{T}x{H}x{V}_chunk{ops.ce_chunk}", timeit(lambda: ops.linear_ce(x, w, tg, 1.0, dw), a.iters, a.warmup, flush), flops=6.0 * T * H * V)
     def op_embedding():
         T, H, V = a.tokens, a.hidden, a.vocab
         w, dx = bf(V, H), bf(T, H)

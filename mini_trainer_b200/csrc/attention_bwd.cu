@@ -7,11 +7,13 @@
 //   S  = Q K^T            dP = dO V^T                      (TMEM, 128 columns each)
 //   P  = exp(S*scale - lse), dS = P * (dP - delta) * scale  (4 warps; bf16 P and dS to smem)
 //   dQ = dS K  (into S's TMEM columns)   dV += P^T dO   dK += dS^T Q
-// dQ tiles (several key blocks contribute to one query block) are staged in shared memory, in the
-// space of the P / dS tiles once the MMAs have read them, and added into an fp32 [T, Hq*D]
-// accumulator with TMA tensor reduces (cp.reduce.async.bulk.tensor .add, one 32-column x 128-row box
-// each, 128B-swizzled so the staging stores are free of bank conflicts); a small kernel rounds the
-// accumulator to bf16 afterwards.
+// dQ tiles (several key blocks contribute to one query block) are staged in shared memory and added
+// into an fp32 [T, Hq*D] accumulator with TMA tensor reduces (cp.reduce.async.bulk.tensor .add, one
+// 32-column x 128-row box each, 128B-swizzled so the staging stores are free of bank conflicts); a
+// small kernel rounds the accumulator to bf16 afterwards. The first half of the D columns is staged
+// in the P tile (idle once the MMAs have read it), the second half in a buffer of its own, and a
+// separate warp issues the reduces: those of the P tile first and alone, so that the next softmax, which
+// has to overwrite P, waits for half of the read-out only, and never for the thread that issued it.
 // P and dS are stored once as [query, key] 128B-swizzled tiles and read both K-major (for dQ) and
 // MN-major (for dV / dK), so no transposes are materialised.
 //
@@ -31,10 +33,11 @@ int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_
                      uint32_t box_inner, uint32_t box_outer);
 
 constexpr int AB_B = 128;          // block edge (queries and keys)
-constexpr int AB_THREADS = 320;     // TMA warp, MMA warp, 8 softmax warps (two threads per query row)
+constexpr int AB_THREADS = 352;     // TMA warp, MMA warp, 8 softmax warps (two threads per query row), dQ reduce warp
 
 // Optional phase timestamps (clock64) of CTA 0, switched on with debug_flags bit 1: per iteration
-// 4 values from the MMA thread and 5 from one softmax thread. Read back with mtb200_attn_bwd_debug_read.
+// 4 values from the MMA thread (start, S/dP issued, P/dS seen, late MMAs issued) and 5 from one softmax
+// thread (S/dP seen, P/dS computed, P tile free, dQ complete, dQ staged). Read back with mtb200_attn_bwd_debug_read.
 constexpr int DBG_ITERS = 256;
 __device__ long long g_attn_bwd_dbg[DBG_ITERS * 9];
 
@@ -44,7 +47,9 @@ struct AttBwdSmem {
   static constexpr int PT = AB_B * AB_B * 2;        // a [128, 128] bf16 tile
   static constexpr int OFF_K = 0, OFF_V = TILE, OFF_Q = 2 * TILE, OFF_DO = 3 * TILE;
   static constexpr int OFF_P = 4 * TILE, OFF_DS = OFF_P + PT;
-  static constexpr int OFF_BAR = OFF_DS + PT;
+  static constexpr int OFF_ST2 = OFF_DS + PT;       // staging of the second half of a dQ tile: D/64 boxes of [128 rows x 128 B]
+  static constexpr int ST2 = (D / 64) * 16384;
+  static constexpr int OFF_BAR = OFF_ST2 + ST2;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
@@ -77,11 +82,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   uint64_t* stage_full = bars + 4; // dQ tile copied from TMEM to the smem staging area (8 arrivals)
   uint64_t* mma_done = bars + 5;   // dV, dK, dQ complete: Q, dO, P, dS reusable, dQ readable
   uint64_t* dq_read = bars + 6;    // dQ tile drained from TMEM (8 arrivals): S columns reusable
-  uint64_t* stage_free = bars + 7; // the tensor reduces have read the staging area: P / dS writable
+  uint64_t* stage_free = bars + 7; // the tensor reduces have read the dQ half staged in the P tile: P writable
   uint64_t* q_free = bars + 8;     // dK has read Q: the next Q tile may be loaded while dV and dQ still run
   uint64_t* do_full = bars + 9;    // dO_i landed
   uint64_t* do_free = bars + 10;   // dV has read dO: the next dO tile may be loaded while dQ still runs
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* st2_free = bars + 11;  // the tensor reduces have read the second staging buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -96,7 +102,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(sdp_full, 1); mbar_init(pds_ready, 8);
     mbar_init(stage_full, 8); mbar_init(mma_done, 1); mbar_init(dq_read, 8); mbar_init(stage_free, 1);
-    mbar_init(q_free, 1); mbar_init(do_full, 1); mbar_init(do_free, 1);
+    mbar_init(q_free, 1); mbar_init(do_full, 1); mbar_init(do_free, 1); mbar_init(st2_free, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_qkv);
@@ -161,22 +167,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         for (int k = 0; k < D / 16; ++k) {
           umma_bf16(t_s, dQk + kstep(k), dKk + kstep(k), id_nt, k != 0);
         }
-        const long long dbg_a = dbg ? clock64() : 0;
         if (!mbar_wait(do_full, it & 1, abort_flag)) { atomicExch(p.status, 23); goto done; }
         tc_fence_after();
-        const long long dbg_b = dbg ? clock64() : 0;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           umma_bf16(t_dp, dDOk + kstep(k), dVk + kstep(k), id_nt, k != 0);
         }
         umma_commit(sdp_full);
-        if (dbg) {   // debug only: observe the completion of S and dP from the issuing thread itself
-          g_attn_bwd_dbg[it * 9 + 1] = clock64();
-          mbar_wait(sdp_full, it & 1, abort_flag);
-          g_attn_bwd_dbg[it * 9 + 4] = clock64();
-          g_attn_bwd_dbg[it * 9 + 5] = dbg_a;
-          g_attn_bwd_dbg[it * 9 + 6] = dbg_b;
-        }
+        if (dbg) g_attn_bwd_dbg[it * 9 + 1] = clock64();
         if (!mbar_wait(pds_ready, it & 1, abort_flag)) { atomicExch(p.status, 25); goto done; }
         tc_fence_after();
         if (dbg) g_attn_bwd_dbg[it * 9 + 2] = clock64();
@@ -197,6 +195,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         if (dbg) g_attn_bwd_dbg[it * 9 + 3] = clock64();
       }
     }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ dQ reduce warp
+    if (elect_one()) {
+      uint8_t* stage_a = smem + L::OFF_P;     // boxes 0 .. D/64-1
+      uint8_t* stage_b = smem + L::OFF_ST2;   // boxes D/64 .. D/32-1
+      for (int it = 0; it < n_iters; ++it) {
+        const int h = hk * G + it / per_head, i = jblk + it % per_head;
+        if (!mbar_wait(stage_full, it & 1, abort_flag)) { atomicExch(p.status, 30); goto done; }
+        if (!(p.debug_flags & 1)) {
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage_a + c * 16384)), "r"(h * D + c * 32),
+                           "r"(seq_start + i * AB_B) : "memory");
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        // The second half is only issued once the P tile has been read: boxes in flight together share
+        // the read-out bandwidth, and the next softmax is waiting for the P tile alone.
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_arrive(stage_free);
+        if (!(p.debug_flags & 1)) {
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage_b + c * 16384)), "r"(h * D + (D / 64 + c) * 32),
+                           "r"(seq_start + i * AB_B) : "memory");
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_arrive(st2_free);
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every add has been performed before the CTA exits
+    }
   } else {
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;      // which 64 key columns (softmax) / which half of the D columns (drains)
@@ -213,8 +244,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       const float delta = qok ? p.delta[static_cast<long long>(h) * p.T + tok] : 0.f;
       const bool dbg = (p.debug_flags & 2) && blockIdx.x == 0 && it < DBG_ITERS && threadIdx.x == 64;
       if (!mbar_wait(sdp_full, it & 1, abort_flag)) { atomicExch(p.status, 26); goto done; }
-      if (it > 0 && !mbar_wait(stage_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 27); goto done; }
       tc_fence_after();
+      if (dbg) g_attn_bwd_dbg[it * 9 + 4] = clock64();
       const bool need_mask = (i == jblk) || (k0 + AB_B > seq_len) || (i * AB_B + AB_B > seq_len);
       // this thread's 64 columns of S and dP are fetched with all four loads in flight
       uint32_t sv_[2][32], dv_[2][32];
@@ -232,66 +263,67 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
             if (!qok || kpos > qpos || kpos >= seq_len) sv_[cc][x] = 0xff800000u;   // exp2(-inf) = 0
           }
       }
+      // The P tile still holds half of the previous dQ tile until its reduces have read it. The first 32
+      // columns are computed before that wait; their stores then overlap the math of the other 32.
+      uint32_t pk[2][16], dk[2][16];
+      auto compute = [&](int cc) {
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+        for (int x = 0; x < 32; x += 2) {
+          const float p0 = exp2f(fmaf(__uint_as_float(sv_[cc][x]), sl2, -lse2));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv_[cc][x + 1]), sl2, -lse2));
+          pk[cc][x >> 1] = pack_bf16(p0, p1);
+          dk[cc][x >> 1] = pack_bf16(p0 * (__uint_as_float(dv_[cc][x]) - delta) * p.scale,
+                                     p1 * (__uint_as_float(dv_[cc][x + 1]) - delta) * p.scale);
+        }
+      };
+      auto store = [&](int cc) {
         const int c = half * 2 + cc;
         const int rowoff = (c >> 1) * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          uint32_t pk[4], dk[4];
-#pragma unroll
-          for (int x = 0; x < 8; x += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(sv_[cc][g * 8 + x]), sl2, -lse2));
-            const float p1 = exp2f(fmaf(__uint_as_float(sv_[cc][g * 8 + x + 1]), sl2, -lse2));
-            pk[x >> 1] = pack_bf16(p0, p1);
-            dk[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv_[cc][g * 8 + x]) - delta) * p.scale,
-                                   p1 * (__uint_as_float(dv_[cc][g * 8 + x + 1]) - delta) * p.scale);
-          }
           const int chunk = (((c & 1) * 4 + g) ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(smem + L::OFF_P + rowoff + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          *reinterpret_cast<uint4*>(smem + L::OFF_DS + rowoff + chunk) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+          *reinterpret_cast<uint4*>(smem + L::OFF_P + rowoff + chunk) = make_uint4(pk[cc][g * 4], pk[cc][g * 4 + 1], pk[cc][g * 4 + 2], pk[cc][g * 4 + 3]);
+          *reinterpret_cast<uint4*>(smem + L::OFF_DS + rowoff + chunk) = make_uint4(dk[cc][g * 4], dk[cc][g * 4 + 1], dk[cc][g * 4 + 2], dk[cc][g * 4 + 3]);
         }
-      }
+      };
+      compute(0);
+      if (dbg) g_attn_bwd_dbg[it * 9 + 5] = clock64();
+      if (it > 0 && !mbar_wait(stage_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 27); goto done; }
+      if (dbg) g_attn_bwd_dbg[it * 9 + 6] = clock64();
+      store(0);
+      compute(1);
+      store(1);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_ready);
-      // drain dQ: TMEM -> fp32 staging rows in the (now idle) P / dS tiles -> one bulk reduce-add per row
+      // drain dQ: TMEM -> fp32 staging (128B-swizzled boxes); the reduce warp adds the boxes into global memory
       if (!mbar_wait(mma_done, it & 1, abort_flag)) { atomicExch(p.status, 28); goto done; }
+      if (half == 1 && it > 0 && !mbar_wait(st2_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 31); goto done; }
       tc_fence_after();
       if (dbg) g_attn_bwd_dbg[it * 9 + 7] = clock64();
-      uint8_t* stage = smem + L::OFF_P;   // D/32 boxes of [128 rows x 128 B], 128B-swizzled
-#pragma unroll 1
-      for (int cc = 0; cc < D / 64; ++cc) {
-        const int c = half * (D / 64) + cc;
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + lane_addr + c * 32, v);
-        tmem_ld_wait();
-        uint8_t* rowp = stage + c * 16384 + r * 128;
+      uint8_t* stage = half == 0 ? smem + L::OFF_P : smem + L::OFF_ST2;
+      // both loads in flight; the S columns are released as soon as the tile is in registers, so the
+      // next S = Q K^T runs under the staging stores
+      uint32_t v[D / 64][32];
 #pragma unroll
-        for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<uint4*>(rowp + ((g ^ (r & 7)) << 4)) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-      }
-      fence_proxy_async_smem();
+      for (int cc = 0; cc < D / 64; ++cc) tmem_ld_32x32(t_s + lane_addr + (half * (D / 64) + cc) * 32, v[cc]);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(dq_read); mbar_arrive(stage_full); }
-      if (dbg) g_attn_bwd_dbg[it * 9 + 8] = clock64();
-      if (warp == 2 && lane == 0) {
-        if (!mbar_wait(stage_full, it & 1, abort_flag)) { atomicExch(p.status, 30); goto done; }
-        if (!(p.debug_flags & 1)) {
+      if (lane == 0) mbar_arrive(dq_read);
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c)
-            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
-                         ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage + c * 16384)), "r"(h * D + c * 32),
-                           "r"(seq_start + i * AB_B) : "memory");
-        }
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        mbar_arrive(stage_free);
+      for (int cc = 0; cc < D / 64; ++cc) {
+        uint8_t* rowp = stage + cc * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<uint4*>(rowp + ((g ^ (r & 7)) << 4)) = make_uint4(v[cc][g * 4], v[cc][g * 4 + 1], v[cc][g * 4 + 2], v[cc][g * 4 + 3]);
       }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(stage_full);
+      if (dbg) g_attn_bwd_dbg[it * 9 + 8] = clock64();
     }
-    if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     // epilogue: dK, dV (rows = keys)
     if (n_iters > 0) {
       if (!mbar_wait(mma_done, (n_iters - 1) & 1, abort_flag)) { atomicExch(p.status, 29); goto done; }

@@ -69,7 +69,7 @@ def _ptr(t):
 class NativeOps:
     name = "native"
 
-    def __init__(self, device, ce_chunk: int = 2048, attention: str | None = None):
+    def __init__(self, device, ce_chunk: int = 4096, attention: str | None = None):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("NativeOps needs a CUDA device")
