@@ -4,16 +4,21 @@
 // out of the fused qkv activation [T, (Hq + 2 Hkv) * D] through ONE tensor map (128B swizzle):
 //   S = Q K^T      tcgen05.mma, M=128 queries, N=128 keys, K=D      (accumulator in TMEM, 2 buffers)
 //   P = softmax    8 warps, two threads per query row, read S from TMEM, write bf16 P to smem (2 buffers)
-//   O += P V       tcgen05.mma, M=128, N=D, K=128 keys               (accumulator in TMEM)
+//   O += P V       tcgen05.mma, M=128, N=D, K=2 x 64 keys            (two accumulators in TMEM)
 // Roles: warp 0 = TMA (K/V double-buffered), warp 1 = MMA issue, warps 2-9 = softmax + epilogue
 // (two threads per query row, each owning 64 of the 128 key columns of a tile).
 // S (TMEM) and P (smem) are double-buffered: Q K^T of tile j+1 and P V of tile j-1 both run under the
 // softmax of tile j, so the softmax warps never wait for the tensor core except to rescale O.
 //
-// The softmax keeps a per-row reference maximum and only rescales O when the running maximum
-// grew by more than 2^8 (exact: the final division by the row sum uses the same reference), so
-// the TMEM round trip for the rescale is rare. Only the last key tile of a query block touches
-// the causal diagonal / the end of the sequence and is masked.
+// The two threads of a query row never talk to each other inside the key loop: each keeps its own
+// online-softmax state (reference maximum, row sum) for its 64 key columns of every tile, and P V is
+// issued as two half-K MMAs into two O accumulators in tensor memory (O_a: key columns 0-63 of each
+// tile, O_b: 64-127). The halves are merged once, in the epilogue, like a split-K softmax:
+//   m = max(m_a, m_b), O = (O_a 2^(m_a-m) + O_b 2^(m_b-m)) / (l_a 2^(m_a-m) + l_b 2^(m_b-m)).
+// (Exchanging the half-row maxima through shared memory and a barrier on every tile cost about a
+// fifth of the softmax time.) A state only rescales its accumulator when its running maximum grew
+// by more than 2^8 (exact: the final merge uses the same references), so the TMEM round trip for the
+// rescale is rare. Only the last key tile of a query block touches the causal diagonal and is masked.
 //
 // Outputs: out [T, Hq*D] bf16 and lse [Hq, T] fp32 (natural log, scaled scores), as needed by
 // the backward. Sequence boundaries come from a host-built work table (seq_start, seq_len, q0),
@@ -43,7 +48,7 @@ struct AttFwdSmem {
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;   // 2 stages
   static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;   // 2 buffers
   static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
-  static constexpr int OFF_MX = OFF_BAR + 256;          // float [2 tiles parity][2 halves][128 rows]
+  static constexpr int OFF_MX = OFF_BAR + 256;          // float [reference maximum, row sum][2 halves][128 rows], epilogue only
   // No alignment slack: with D = 128 the tiles fill 224 KB of the 227 KB a CTA can have. The kernel
   // checks that the dynamic shared memory window starts on a 1024-byte boundary (swizzle atom).
   static constexpr int TOTAL = OFF_MX + 2 * 2 * 128 * 4;
@@ -78,7 +83,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   uint64_t* s_full = bars + 9;        // 2
   uint64_t* p_ready = bars + 11;      // 2: P buffer written and S buffer consumed (8 arrivals)
   uint64_t* p_empty = bars + 13;      // 2: P V of the tile in this P buffer has completed
-  uint64_t* mx_bar = bars + 15;       // 1: the two threads of every row have published their partial maximum / sum
+  uint64_t* mx_bar = bars + 15;       // 1: epilogue, the two threads of every row have published their softmax state
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -104,7 +109,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;
+  const uint32_t tmem_s0 = tmem_base, tmem_oa = tmem_base + 256, tmem_ob = tmem_base + 384;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -160,8 +165,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         const uint64_t dV = dV0 + static_cast<uint64_t>(b * (L::KV_BYTES >> 4));
         const uint64_t dP = dP0 + static_cast<uint64_t>(b * (L::P_BYTES >> 4));
 #pragma unroll
-        for (int k = 0; k < ATT_BN / 16; ++k)
-          umma_bf16(tmem_o, dP + kstep(k), dV + static_cast<uint64_t>(k * 128), idesc_pv, (j | k) != 0);
+        for (int k = 0; k < ATT_BN / 16; ++k) {   // key columns 0-63 accumulate into O_a, 64-127 into O_b
+          constexpr int KH = ATT_BN / 32;
+          umma_bf16(k < KH ? tmem_oa : tmem_ob, dP + kstep(k), dV + static_cast<uint64_t>(k * 128), idesc_pv,
+                    j != 0 || (k != 0 && k != KH));
+        }
         umma_commit(&v_empty[b]);
         umma_commit(&p_empty[b]);
         if (j + 2 < n_tiles) {   // S buffer b was consumed by the softmax of tile j: refill it with tile j+2
@@ -179,9 +187,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     const int qpos = q0 + r;                  // position inside the sequence
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
-    float m_ref = -INFINITY, l = 0.f;
+    float m_ref = -INFINITY, l = 0.f;       // state of THIS thread's 64 key columns per tile
     uint8_t* sp = smem + L::OFF_P;
     float* mx = reinterpret_cast<float*>(smem + L::OFF_MX);
+    const uint32_t tmem_own = (half == 0 ? tmem_oa : tmem_ob) + lane_addr;
     for (int j = 0; j < n_tiles; ++j) {
       if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag)) { atomicExch(p.status, 17); goto done; }
       tc_fence_after();
@@ -189,7 +198,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       const bool diag = (j == n_tiles - 1);
       const int kbase = j * ATT_BN;
       // S is read from tensor memory once: this thread's 64 columns stay in registers for both the
-      // row maximum and the exponentials. Only the last tile touches the causal diagonal.
+      // maximum and the exponentials. Only the last tile touches the causal diagonal.
       uint32_t sv[2][32];
       tmem_ld_32x32(ts + (half * 2) * 32, sv[0]);
       tmem_ld_32x32(ts + (half * 2 + 1) * 32, sv[1]);
@@ -206,42 +215,36 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
         for (int i = 0; i < 32; ++i) mt = fmaxf(mt, __uint_as_float(sv[cc][i]));
-      float* mxj = mx + (j & 1) * 256;
-      mxj[half * 128 + r] = mt;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(mx_bar);
-      if (!mbar_wait(mx_bar, j & 1, abort_flag)) { atomicExch(p.status, 20); goto done; }   // bounded, unlike bar.sync
-      mt = fmaxf(mxj[r], mxj[128 + r]);
       float factor = 1.f;
       bool rescale = false;
-      if (mt > m_ref && (mt - m_ref) * sl2 > 8.f) {   // includes the first tile (m_ref = -inf)
+      if (mt > m_ref && (mt - m_ref) * sl2 > 8.f) {   // includes the first unmasked tile (m_ref = -inf)
         factor = (m_ref == -INFINITY) ? 0.f : exp2f((m_ref - mt) * sl2);
+        rescale = (j > 0) && (m_ref != -INFINITY);    // nothing but zeros was accumulated before the first maximum
         m_ref = mt;
         l *= factor;
-        rescale = (j > 0);
       }
       if (j >= 2) {   // the P buffer of this tile must have been read by P V of tile j-2
         if (!mbar_wait(&p_empty[j & 1], ((j - 2) >> 1) & 1, abort_flag)) { atomicExch(p.status, 18); goto done; }
       }
       if (j > 0) {
-        if (__any_sync(0xffffffffu, rescale)) {   // O must be complete through tile j-1 before it is rescaled
+        if (__any_sync(0xffffffffu, rescale)) {   // this half's O must be complete through tile j-1 before it is rescaled
           if (!mbar_wait(&p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { atomicExch(p.status, 18); goto done; }
           tc_fence_after();
 #pragma unroll 1
-          for (int cc = 0; cc < D / 64; ++cc) {
-            const int c = half * (D / 64) + cc;
+          for (int c = 0; c < D / 32; ++c) {
             uint32_t v[32];
-            tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+            tmem_ld_32x32(tmem_own + c * 32, v);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
-            tmem_st_32x32(tmem_o + lane_addr + c * 32, v);
+            tmem_st_32x32(tmem_own + c * 32, v);
           }
           tmem_st_wait();
         }
       }
-      // probabilities -> bf16 P in shared memory (K-major, 128B swizzle), row sums; exp2(-inf) = 0 masks
-      const float mo = m_ref * sl2;
+      // probabilities -> bf16 P in shared memory (K-major, 128B swizzle), row sums; exp2(-inf) = 0 masks.
+      // A state that has seen only masked entries so far (m_ref = -inf) writes zeros.
+      const float mo = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
@@ -265,38 +268,50 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[j & 1]);
     }
-    // epilogue: O / l -> out, lse (row sums of the two column halves are combined first)
+    // epilogue: merge the two half-row states, O -> out, lse
     if (!mbar_wait(&p_empty[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag)) { atomicExch(p.status, 19); goto done; }
     tc_fence_after();
-    float* lx = mx + (n_tiles & 1) * 256;   // the buffer the last tile did not use
-    lx[half * 128 + r] = l;
+    mx[half * 128 + r] = m_ref;
+    mx[256 + half * 128 + r] = l;
     __syncwarp();
     if (lane == 0) mbar_arrive(mx_bar);
-    if (!mbar_wait(mx_bar, n_tiles & 1, abort_flag)) { atomicExch(p.status, 20); goto done; }
-    l = lx[r] + lx[128 + r];
+    if (!mbar_wait(mx_bar, 0, abort_flag)) { atomicExch(p.status, 20); goto done; }   // bounded, unlike bar.sync
+    const float m_a = mx[r], m_b = mx[128 + r], l_a = mx[256 + r], l_b = mx[384 + r];
+    const float m_all = fmaxf(m_a, m_b);   // finite: the diagonal entry of every row is unmasked
+    const float f_a = (m_a == -INFINITY) ? 0.f : exp2f((m_a - m_all) * sl2);
+    const float f_b = (m_b == -INFINITY) ? 0.f : exp2f((m_b - m_all) * sl2);
+    const float l_all = l_a * f_a + l_b * f_b;
     const bool ok = qpos < seq_len;
-    const float inv = 1.f / l;
+    const float inv = 1.f / l_all;
+    const float w_a = f_a * inv, w_b = f_b * inv;
     const long long tok = static_cast<long long>(seq_start) + qpos;
     __nv_bfloat16* orow = p.out + tok * p.ldo + h * D;
 #pragma unroll 1
     for (int cc = 0; cc < D / 64; ++cc) {
-      const int c = half * (D / 64) + cc;
-      uint32_t v[32];
-      tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+      const int c = half * (D / 64) + cc;     // this thread writes half of the D columns of its row
+      uint32_t va[32], vb[32];
+      tmem_ld_32x32(tmem_oa + lane_addr + c * 32, va);
+      tmem_ld_32x32(tmem_ob + lane_addr + c * 32, vb);
       tmem_ld_wait();
       if (ok) {
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          // an accumulator whose half never saw an unmasked entry holds zeros; w = 0 also covers its garbage-free case
+          f[i] = __uint_as_float(va[i]) * w_a + __uint_as_float(vb[i]) * w_b;
+        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 o;
-          o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
-          o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
-          o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
-          o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+          o.x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
+          o.y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
+          o.z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
+          o.w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
           *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
         }
       }
     }
-    if (ok && half == 0) p.lse[static_cast<long long>(h) * p.T + tok] = m_ref * p.scale + logf(l);
+    if (ok && half == 0) p.lse[static_cast<long long>(h) * p.T + tok] = m_all * p.scale + logf(l_all);
   }
 done:
   tc_fence_before();
