@@ -269,8 +269,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       auto compute = [&](int cc) {
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
-          const float p0 = exp2f(fmaf(__uint_as_float(sv_[cc][x]), sl2, -lse2));
-          const float p1 = exp2f(fmaf(__uint_as_float(sv_[cc][x + 1]), sl2, -lse2));
+          // a quarter of the exponentials runs on the FMA pipe: the special-function unit bounds this phase
+          const float p0 = ex2_mufu(fmaf(__uint_as_float(sv_[cc][x]), sl2, -lse2));
+          const float a1 = fmaf(__uint_as_float(sv_[cc][x + 1]), sl2, -lse2);
+          const float p1 = (x & 2) ? ex2_fma(a1) : ex2_mufu(a1);
           pk[cc][x >> 1] = pack_bf16(p0, p1);
           dk[cc][x >> 1] = pack_bf16(p0 * (__uint_as_float(dv_[cc][x]) - delta) * p.scale,
                                      p1 * (__uint_as_float(dv_[cc][x + 1]) - delta) * p.scale);

@@ -204,4 +204,26 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
   return __bfloat1622float2(v);
 }
 
+// 2^x on the special-function unit: one MUFU.EX2 (16 per clock per SM). ex2(-inf) = +0.
+__device__ __forceinline__ float ex2_mufu(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 2^x on the FMA pipe (128 per clock per SM): x = n + f with n the nearest integer, 2^f by a cubic
+// fitted on [-0.5, 0.5] (maximum relative error 1.0e-4, a fortieth of a bf16 ulp), 2^n by an integer
+// add into the exponent field. Inputs below -126 (masked scores are -inf) give about 1e-38, not 0.
+// Softmax kernels use it for a fraction of their exponentials because the special-function unit, not
+// the tensor core, bounds them.
+__device__ __forceinline__ float ex2_fma(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;   // 1.5 * 2^23: the low mantissa bits of t now hold n
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.05500871f, 0.24221068f);
+  p = fmaf(f, p, 0.69328292f);
+  p = fmaf(f, p, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 }  // namespace mtb
