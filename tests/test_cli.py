@@ -28,3 +28,31 @@ def test_train_cli_runs_and_writes_reference_layout(tmp_path):
     assert rows[0]["lr"] == 1e-4 and rows[0]["num_samples"] == 8
     ckpt = os.path.join(out, "hf_format", "samples_16.0")
     assert os.path.exists(os.path.join(ckpt, "model.safetensors")) and os.path.exists(os.path.join(ckpt, "config.json"))
+
+
+def test_bench_reference_arm_reports_unavailable_without_a_gpu():
+    """Without CUDA the reference arm cannot run; the contract is one JSON line and exit code 0."""
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT="29643")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                          env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    rec = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert rec["impl"] == "reference" and "unavailable" in rec
+
+
+def test_train_cli_synthetic_spec_caps_sample_length(tmp_path):
+    out = str(tmp_path / "run")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT="29644")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:tiny-qwen2",
+           "--data-path", "synthetic:tiny-qwen2:32:100", "--batch-size", "8", "--max-tokens-per-gpu", "128",
+           "--output-dir", out, "--min-samples-per-checkpoint", "100000", "--max-steps", "1", "--adam-beta2", "0.99",
+           "--max-shard-gb", "0.001", "--logging-level", "WARNING"]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert "exceed max tokens per gpu" not in proc.stdout   # every sample is at most 100 tokens long
+    rows = [json.loads(l) for l in open(os.path.join(out, "training_metrics_0.jsonl"))]
+    assert rows[0]["num_samples"] == 8
