@@ -196,8 +196,7 @@ def run_native(args) -> dict:
         sched.step()
         host = torch.stack([out["loss_sum"], out["grad_norm"].reshape(())]).cpu()   # device -> host read of the result
         d2h = host.numel() * host.element_size()
-        h2d = sum(sum(v.numel() * v.element_size() for v in (mb["input_ids"], mb["labels"], mb["position_ids"], mb["cu_seqlens"]))
-                  for mb in mbs)
+        h2d = out["h2d_bytes"]   # counted where the copies are issued (models/decoder.py make_packed_batch)
         return host
 
     r2 = timed(step_e2e, 0)   # the same batches as phase (1) and as the reference arm (same dataset, sampler and seed)

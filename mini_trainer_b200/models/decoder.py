@@ -14,6 +14,7 @@ input; backward first re-runs the block forward (``block_forward(..., keep=True)
 from __future__ import annotations
 
 from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -29,6 +30,11 @@ class PackedBatch:
     cu_seqlens: torch.Tensor     # [n+1] int32 (device)
     cu_seqlens_host: list        # same values as Python ints
     max_seqlen: int
+    # Positions whose target is not -100 and their targets, found on the host where the labels are
+    # known (None when every position counts): the LM head only runs on these rows.
+    loss_rows: Optional[torch.Tensor] = None     # [T'] int64
+    loss_targets: Optional[torch.Tensor] = None  # [T'] int64
+    h2d_bytes: int = 0           # bytes of the host tensors copied to the device for this minibatch
 
     @property
     def num_tokens(self) -> int:
@@ -54,8 +60,19 @@ def make_packed_batch(mb: dict, device, non_blocking: bool = True) -> PackedBatc
         cu = torch.cat([starts, torch.tensor([pos.numel()], dtype=torch.int32)])
     cu_host = cu.tolist()
     max_seqlen = int(mb.get("max_seqlen", max(b - a for a, b in zip(cu_host[:-1], cu_host[1:]))))
-    mv = lambda t: t.to(device, non_blocking=non_blocking)
-    return PackedBatch(mv(ids), mv(targets), mv(pos.to(torch.int32)), mv(cu), cu_host, max_seqlen)
+    moved = [0]
+
+    def mv(t):
+        moved[0] += t.numel() * t.element_size()
+        return t.to(device, non_blocking=non_blocking)
+
+    rows = sel = None
+    counted = (targets != -100).nonzero().flatten()
+    if counted.numel() < targets.numel():
+        rows, sel = mv(counted), mv(targets[counted])
+    batch = PackedBatch(mv(ids), mv(targets), mv(pos.to(torch.int32)), mv(cu), cu_host, max_seqlen, rows, sel)
+    batch.h2d_bytes = moved[0]
+    return batch
 
 
 @dataclass
@@ -153,9 +170,26 @@ def head_forward_backward(ops, cfg: ModelConfig, head_p: dict, head_g: dict, lm_
     The CE op produces its gradients in the same pass, scaled by ``grad_scale`` (the reciprocal
     of the global batch's loss-token count), so backward starts here without a separate call.
     """
-    n, rstd = ops.rmsnorm(x, head_p["norm"], cfg.rms_norm_eps)
-    loss, dn = ops.linear_ce(n, lm_w, batch.targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad)
-    dx = ops.rmsnorm_bwd(dn, x, rstd, head_p["norm"], head_g["norm"])
+    rows = batch.loss_rows
+    if rows is None:
+        n, rstd = ops.rmsnorm(x, head_p["norm"], cfg.rms_norm_eps)
+        loss, dn = ops.linear_ce(n, lm_w, batch.targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad)
+        dx = ops.rmsnorm_bwd(dn, x, rstd, head_p["norm"], head_g["norm"])
+        return loss, dx
+    # Masked positions (prompt tokens, the last token of every sample) have zero loss and zero
+    # gradient, so the final norm, the three vocabulary-sized GEMMs and the CE kernel only see the
+    # rows that count; their input gradient is scattered back into a zero tensor. Exact, not an
+    # approximation; the reference's fused linear-CE computes logits for every row.
+    loss = torch.zeros(x.shape[0], dtype=torch.float32, device=x.device)
+    dx = torch.zeros_like(x)
+    if rows.numel() == 0:   # nothing to learn from in this minibatch (e.g. only the idle-rank dummy sample);
+        return loss, dx     # the gradient buffers of the head were zeroed by the caller
+    xs = ops.embedding(x, rows)   # row gather
+    n, rstd = ops.rmsnorm(xs, head_p["norm"], cfg.rms_norm_eps)
+    loss_s, dn = ops.linear_ce(n, lm_w, batch.loss_targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad)
+    dxs = ops.rmsnorm_bwd(dn, xs, rstd, head_p["norm"], head_g["norm"])
+    loss.index_copy_(0, rows, loss_s)
+    dx.index_copy_(0, rows, dxs)
     return loss, dx
 
 

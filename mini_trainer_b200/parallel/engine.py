@@ -509,15 +509,16 @@ class ShardedEngine:
         (``loss_sum``, ``grad_norm``) are read by the caller when it logs.
         """
         loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
-        ntok = 0
+        ntok = h2d = 0
         for k, mb in enumerate(minibatches):
             batch = D.make_packed_batch(mb, self.device)
+            h2d += batch.h2d_bytes
             denom = float(mb["batch_num_loss_counted_tokens"]) or 1.0
             loss = self.forward_backward(batch, 1.0 / denom, last=k == len(minibatches) - 1)
             loss_sum += loss.sum()
             ntok += batch.num_tokens
         gnorm = self.optimizer_step(lr)
-        return {"loss_sum": loss_sum, "grad_norm": gnorm, "num_tokens": ntok}
+        return {"loss_sum": loss_sum, "grad_norm": gnorm, "num_tokens": ntok, "h2d_bytes": h2d}
 
     def state_bytes(self) -> int:
         return sum(g.state_bytes() for g in self.groups)

@@ -105,3 +105,36 @@ def test_checkpoint_levels_give_identical_gradients():
     for other in grads[1:]:
         for a, b in zip(grads[0], other):
             assert torch.allclose(a, b, atol=1e-6, rtol=1e-5)
+
+
+def test_head_on_counted_rows_only_matches_full_head():
+    """The LM head runs on the rows whose target is not -100; loss and gradients equal the all-rows path."""
+    import dataclasses
+    cfg = small_cfg(False, False)
+    mb = make_mb([9, 3, 14], cfg.vocab_size, seed=5)
+    outs = []
+    for full in (False, True):
+        eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), optim=OptimConfig(lr=1e-3))
+        eng.init_random(seed=3, std=0.2)
+        batch = D.make_packed_batch(mb, "cpu")
+        assert batch.loss_rows is not None and 0 < batch.loss_rows.numel() < batch.num_tokens
+        if full:
+            batch = dataclasses.replace(batch, loss_rows=None, loss_targets=None)
+        loss = eng.forward_backward(batch, 0.1)
+        outs.append((loss, [g.gacc.clone() for g in eng.groups]))
+    assert torch.allclose(outs[0][0], outs[1][0], atol=1e-6)
+    for a, b in zip(outs[0][1], outs[1][1]):
+        assert torch.allclose(a, b, atol=1e-6, rtol=1e-5)
+
+
+def test_minibatch_without_counted_tokens_gives_zero_loss_and_head_gradient():
+    cfg = small_cfg(True, True)
+    eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), optim=OptimConfig(lr=1e-3))
+    eng.init_random(seed=3, std=0.2)
+    ids = torch.tensor([15, 14, 13, 12, 11])
+    mb = mb_collate_fn([{"input_ids": ids, "labels": torch.full((5,), -100), "len": 5, "num_loss_counted_tokens": 0}], 7)
+    batch = D.make_packed_batch(mb, "cpu")
+    assert batch.loss_rows.numel() == 0
+    loss = eng.forward_backward(batch, 1.0 / 7)
+    assert float(loss.abs().sum()) == 0.0
+    assert all(float(g.gacc.abs().sum()) == 0.0 for g in eng.groups)
