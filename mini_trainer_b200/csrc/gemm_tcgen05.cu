@@ -52,7 +52,9 @@ struct GemmParams {
 // Fused all-gather: while the GEMM runs, eight extra warps per CTA pull this parameter group's
 // shards from every peer's symmetric arena (plain peer loads over NVLink) into the local full
 // buffer that the B tensor map points at, 128 KB chunk by chunk, and publish each finished chunk
-// in a flag array. The TMA producer only loads a B tile after the chunks under it are flagged.
+// in a flag array. A ninth extra warp polls the flags of the chunks under each of the CTA's B tiles
+// (one lane per chunk) and publishes a tile count in shared memory; the TMA producer only loads a
+// B tile once that count covers it. Tiles are visited in bands of GATHER_GROUP_N column-tiles.
 constexpr int GATHER_THREADS = 256;
 constexpr int GATHER_EXTRA_THREADS = GATHER_THREADS + 32;   // gather warps + one flag-checker warp
 constexpr int GATHER_UNROLL = 8;     // 16-byte peer loads in flight per gather thread

@@ -212,9 +212,9 @@ class GatherPlan:
 
     The group's full buffer is cut into 128 KB chunks. Launch ``stage 0`` (the QKV projection)
     gathers the chunks up to the tensor named ``split_before`` while it multiplies; ``stage 1``
-    (the gate/up projection) gathers the rest. Inside each launch, extra warps pull the chunks
-    from the peers and flag them; the GEMM's TMA producer waits for the flags of the chunks under
-    each weight tile. The few parameters needed BEFORE the first GEMM (the input norm weight and
+    (the gate/up projection) gathers the rest. Inside each launch, eight extra warps pull the chunks
+    from the peers and flag them; one more warp polls the flags of the chunks under each weight tile
+    (all of a tile's flags in parallel) and tells the GEMM's TMA producer how many tiles are ready. The few parameters needed BEFORE the first GEMM (the input norm weight and
     the q/k/v bias, laid out first in the buffer) are pulled by a tiny separate copy.
     """
 
