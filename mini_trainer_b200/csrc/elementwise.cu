@@ -83,8 +83,10 @@ __global__ void __launch_bounds__(EW_THREADS) rmsnorm_fwd_kernel(const __nv_bflo
 // ------------------------------------------------------------------------------ RMSNorm bwd
 // dx = rstd * (g - xhat * mean(g * xhat)) (+ add_to), g = dy * w, xhat = x * rstd
 // dw partial per block in fp32: dwp[block, H] += dy * bf16(xhat). Persistent blocks loop over rows.
-template <int VPT>  // 8-wide vectors per thread; H <= VPT * 8 * EW_THREADS
-__global__ void __launch_bounds__(EW_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+// Wide rows use 512 threads with one or two vectors each: half the registers per thread of the 256-thread
+// form, so twice the warps stay resident and more loads are in flight around the per-row reduction.
+template <int VPT, int THREADS>  // 8-wide vectors per thread; H <= VPT * 8 * THREADS
+__global__ void __launch_bounds__(THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                                                 const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ w,
                                                                 const __nv_bfloat16* __restrict__ add_to, __nv_bfloat16* __restrict__ dx,
                                                                 float* __restrict__ dwp, int T, int H) {
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(EW_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
   float wreg[VPT][8];
 #pragma unroll
   for (int v = 0; v < VPT; ++v) {
-    const int c = (threadIdx.x + v * EW_THREADS) * 8;
+    const int c = (threadIdx.x + v * THREADS) * 8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) { dwacc[v][i] = 0.f; wreg[v][i] = 0.f; }
     if (c < H) { bf16x8 wv; wv.load(w + c); wv.to_float(wreg[v]); }
@@ -104,7 +106,7 @@ __global__ void __launch_bounds__(EW_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
     float dot = 0.f;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
-      const int c = (threadIdx.x + v * EW_THREADS) * 8;
+      const int c = (threadIdx.x + v * THREADS) * 8;
       if (c < H) {
         bf16x8 a, b; a.load(dy + row * H + c); b.load(x + row * H + c);
         float fa[8], fb[8]; a.to_float(fa); b.to_float(fb);
@@ -120,7 +122,7 @@ __global__ void __launch_bounds__(EW_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
     dot = block_sum(dot, red) / H;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
-      const int c = (threadIdx.x + v * EW_THREADS) * 8;
+      const int c = (threadIdx.x + v * THREADS) * 8;
       if (c < H) {
         float o[8];
 #pragma unroll
@@ -137,7 +139,7 @@ __global__ void __launch_bounds__(EW_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
   }
 #pragma unroll
   for (int v = 0; v < VPT; ++v) {
-    const int c = (threadIdx.x + v * EW_THREADS) * 8;
+    const int c = (threadIdx.x + v * THREADS) * 8;
     if (c < H) {
       float* dst = dwp + static_cast<long long>(blockIdx.x) * H + c;
       *reinterpret_cast<float4*>(dst) = make_float4(dwacc[v][0], dwacc[v][1], dwacc[v][2], dwacc[v][3]);
@@ -446,11 +448,14 @@ int mtb200_rmsnorm_bwd_blocks(int T) { const int b = num_sms() * 2; return T < b
 int mtb200_rmsnorm_bwd(const void* dy, const void* x, const float* rstd, const void* w, const void* add_to, void* dx,
                        float* dw_partial, void* dw_out, int T, int H, cudaStream_t st) {
   if (T <= 0) return 0;
-  if (H % 8 || H > 4 * 8 * EW_THREADS) return -10;
+  if (H % 8 || H > 4 * 8 * 512) return -10;
   const int blocks = mtb200_rmsnorm_bwd_blocks(T);
-  const int vpt = cdiv(H, 8 * EW_THREADS);
-#define RB(V) rmsnorm_bwd_kernel<V><<<blocks, EW_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)x, rstd, (const bf16*)w, (const bf16*)add_to, (bf16*)dx, dw_partial, T, H)
-  if (vpt <= 1) RB(1); else if (vpt == 2) RB(2); else if (vpt == 3) RB(3); else RB(4);
+#define RB(V, TH) rmsnorm_bwd_kernel<V, TH><<<blocks, TH, 0, st>>>((const bf16*)dy, (const bf16*)x, rstd, (const bf16*)w, (const bf16*)add_to, (bf16*)dx, dw_partial, T, H)
+  if (H <= 8 * EW_THREADS) RB(1, EW_THREADS);
+  else {
+    const int vpt = cdiv(H, 8 * 512);
+    if (vpt <= 1) RB(1, 512); else if (vpt == 2) RB(2, 512); else if (vpt == 3) RB(3, 512); else RB(4, 512);
+  }
 #undef RB
   reduce_rows_kernel<<<cdiv(H, 256), 256, 0, st>>>(dw_partial, (bf16*)dw_out, blocks, H);
   return launch_ok();
