@@ -56,3 +56,17 @@ def test_train_cli_synthetic_spec_caps_sample_length(tmp_path):
     assert "exceed max tokens per gpu" not in proc.stdout   # every sample is at most 100 tokens long
     rows = [json.loads(l) for l in open(os.path.join(out, "training_metrics_0.jsonl"))]
     assert rows[0]["num_samples"] == 8
+
+
+def test_smoke_run_two_gloo_ranks():
+    """The sharding smoke script (plain-collectives backend) on two CPU ranks."""
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_PORT"):
+        env.pop(k, None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29657", "-m", "mini_trainer_b200.cli.smoke_run", "--num-steps", "2", "--sequence-length", "32"]
+    proc = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert "smoke run ok" in proc.stdout
+    recs = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
+    assert [r["step"] for r in recs] == [1, 2] and recs[1]["loss"] < recs[0]["loss"]
