@@ -13,6 +13,7 @@ input; backward first re-runs the block forward (``block_forward(..., keep=True)
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -68,7 +69,8 @@ def make_packed_batch(mb: dict, device, non_blocking: bool = True) -> PackedBatc
 
     rows = sel = None
     counted = (targets != -100).nonzero().flatten()
-    if counted.numel() < targets.numel():
+    # MTB200_HEAD_ALL_ROWS=1 runs the head on every row, as the reference does (for A/B timing)
+    if counted.numel() < targets.numel() and os.environ.get("MTB200_HEAD_ALL_ROWS", "0") != "1":
         rows, sel = mv(counted), mv(targets[counted])
     batch = PackedBatch(mv(ids), mv(targets), mv(pos.to(torch.int32)), mv(cu), cu_host, max_seqlen, rows, sel)
     batch.h2d_bytes = moved[0]
