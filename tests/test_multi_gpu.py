@@ -82,3 +82,14 @@ def test_two_gpus_match_one_gpu(comm, budget):
     for a, b in zip(one, two):
         assert abs(a["loss"] - b["loss"]) < 2e-2 * abs(a["loss"]), (one, two)
         assert abs(a["grad_norm"] - b["grad_norm"]) < 5e-2 * a["grad_norm"], (one, two)
+
+
+def test_four_gpus_symmetric_match_one_gpu():
+    """World size 4 (its own reduce-scatter instantiation and shard padding) over the symmetric backend."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    one = _run(1, "auto")
+    four = _run(4, "symmetric", "0")
+    for a, b in zip(one, four):
+        assert abs(a["loss"] - b["loss"]) < 2e-2 * abs(a["loss"]), (one, four)
+        assert abs(a["grad_norm"] - b["grad_norm"]) < 5e-2 * a["grad_norm"], (one, four)
