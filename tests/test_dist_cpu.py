@@ -88,3 +88,20 @@ def test_two_ranks_match_one_rank_and_checkpoint_roundtrip(tmp_path):
     for a, b in zip(e1.groups, e2.groups):
         assert torch.allclose(a.master, b.master, atol=1e-2, rtol=2e-2)
     assert e1.cfg.tie_word_embeddings and e1.cfg.vocab_size == 32000
+
+
+@pytest.mark.timeout(900)
+def test_three_ranks_match_one_rank(tmp_path):
+    """An odd world size: group sizes do not divide evenly, so the shard padding and an idle rank's dummy
+    minibatches are exercised; one step is enough."""
+    one, three = str(tmp_path / "w1"), str(tmp_path / "w3")
+    os.makedirs(one); os.makedirs(three)
+    run_training(0, 1, free_port(), one, 1)
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    mp.spawn(_spawn_entry, args=(3, free_port(), three, 1), nprocs=3, join=True)
+    a = json.loads(open(os.path.join(one, "training_metrics_0.jsonl")).readline())
+    b = json.loads(open(os.path.join(three, "training_metrics_0.jsonl")).readline())
+    assert abs(a["loss"] - b["loss"]) < 2e-4 * abs(a["loss"]), (a["loss"], b["loss"])
+    assert abs(a["grad_norm"] - b["grad_norm"]) < 2e-3 * a["grad_norm"]
+    assert a["num_loss_counted_tokens"] == b["num_loss_counted_tokens"] and b["num_samples"] == 32
