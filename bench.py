@@ -37,6 +37,8 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 BASELINE_TOKENS_PER_S = None  # the reference publishes no throughput number
 
 MODEL = "llama-3.1-8b"
+MODEL_LABEL = {"llama-3.1-8b": "Llama-3.1-8B", "llama-3.1-70b": "Llama-3.1-70B", "qwen2.5-1.5b": "Qwen2.5-1.5B",
+               "qwen2.5-7b": "Qwen2.5-7B", "tiny-qwen2": "tiny-Qwen2"}
 GLOBAL_BATCH = 128
 MAX_TOKENS_PER_GPU = 64000
 
@@ -209,11 +211,11 @@ def run_native(args) -> dict:
     tps_e2e = r2["tokens"] / (r2["ms"] / 1e3)
     peak_gb = torch.cuda.max_memory_allocated(device) / 1e9
     result = {
-        "metric": "train tokens/sec, Llama-3.1-8B-architecture full SFT (device-timed, max over ranks)",
+        "metric": f"train tokens/sec, {MODEL_LABEL.get(args.model, args.model)}-architecture full SFT (device-timed, max over ranks)",
         "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": r1["ms"] / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": (tps / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
-        "dtype": "bf16", "data": "synthetic (random-init weights, lognormal(7.5,1.0) lengths clipped to [64,65536], uniform token ids, -100 prefix masks)",
+        "dtype": "bf16", "data": f"synthetic (random-init weights, lognormal({spec.mu},{spec.sigma}) lengths clipped to [{spec.lo},{spec.hi}], uniform token ids, -100 prefix masks)",
         "impl": "native",
         "config": {"model": args.model, "global_batch": batch_size, "seq_len": f"packed, max_tokens_per_gpu={max_tokens}",
                    "parallelism": f"fsdp{world}" if world > 1 else "single", "comm": comm.name,
