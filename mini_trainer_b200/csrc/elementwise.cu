@@ -195,30 +195,28 @@ __global__ void __launch_bounds__(EW_THREADS) rope_kernel(__nv_bfloat16* __restr
 // ------------------------------------------------------------------------------ SwiGLU
 __global__ void __launch_bounds__(EW_THREADS) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
                                                                long long T, int F) {
-  const int vpr = F >> 3;
-  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (gid >= T * vpr) return;
-  const long long t = gid / vpr;
-  const int c = static_cast<int>(gid % vpr) * 8;
+  // grid = (tokens, column blocks): no 64-bit division per thread
+  const long long t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= F) return;
   bf16x8 g, u; g.load(gu + t * 2 * F + c); u.load(gu + t * 2 * F + F + c);
   float fg[8], fu[8], o[8]; g.to_float(fg); u.to_float(fu);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) o[i] = fg[i] / (1.f + __expf(-fg[i])) * fu[i];
+  for (int i = 0; i < 8; ++i) o[i] = __fdividef(fg[i], 1.f + __expf(-fg[i])) * fu[i];
   g.from_float(o); g.store(act + t * F + c);
 }
 
 __global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gu,
                                                                __nv_bfloat16* __restrict__ dgu, long long T, int F) {
-  const int vpr = F >> 3;
-  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (gid >= T * vpr) return;
-  const long long t = gid / vpr;
-  const int c = static_cast<int>(gid % vpr) * 8;
+  // grid = (tokens, column blocks): no 64-bit division per thread
+  const long long t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= F) return;
   bf16x8 g, u, d; g.load(gu + t * 2 * F + c); u.load(gu + t * 2 * F + F + c); d.load(dact + t * F + c);
   float fg[8], fu[8], fd[8], og[8], ou[8]; g.to_float(fg); u.to_float(fu); d.to_float(fd);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float sig = 1.f / (1.f + __expf(-fg[i]));
+    const float sig = __fdividef(1.f, 1.f + __expf(-fg[i]));
     og[i] = fd[i] * fu[i] * sig * (1.f + fg[i] * (1.f - sig));
     ou[i] = fd[i] * fg[i] * sig;
   }
@@ -472,14 +470,14 @@ int mtb200_rope(void* qkv, const int* pos, const float* inv_freq, int T, long lo
 int mtb200_swiglu_fwd(const void* gu, void* act, long long T, int F, cudaStream_t st) {
   if (T <= 0) return 0;
   if (F % 8) return -10;
-  swiglu_fwd_kernel<<<cdiv(T * (F / 8), EW_THREADS), EW_THREADS, 0, st>>>((const bf16*)gu, (bf16*)act, T, F);
+  swiglu_fwd_kernel<<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((const bf16*)gu, (bf16*)act, T, F);
   return launch_ok();
 }
 
 int mtb200_swiglu_bwd(const void* dact, const void* gu, void* dgu, long long T, int F, cudaStream_t st) {
   if (T <= 0) return 0;
   if (F % 8) return -10;
-  swiglu_bwd_kernel<<<cdiv(T * (F / 8), EW_THREADS), EW_THREADS, 0, st>>>((const bf16*)dact, (const bf16*)gu, (bf16*)dgu, T, F);
+  swiglu_bwd_kernel<<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((const bf16*)dact, (const bf16*)gu, (bf16*)dgu, T, F);
   return launch_ok();
 }
 
