@@ -387,11 +387,10 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __
 // dqkv[t, 0:Hq*D] = bf16(dq_acc[t, :])
 __global__ void __launch_bounds__(256) attn_dq_store_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dqkv, long long ldq,
                                                            long long T, int HqD) {
-  const int vpr = HqD >> 3;
-  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (gid >= T * vpr) return;
-  const long long t = gid / vpr;
-  const int c = static_cast<int>(gid % vpr) * 8;
+  // grid = (tokens, column blocks): no 64-bit division per thread
+  const long long t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= HqD) return;
   const float4 a = *reinterpret_cast<const float4*>(acc + t * HqD + c), b = *reinterpret_cast<const float4*>(acc + t * HqD + c + 4);
   *reinterpret_cast<uint4*>(dqkv + t * ldq + c) =
       make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
@@ -432,8 +431,7 @@ extern "C" int mtb200_attn_bwd(const void* qkv, long long ld, const void* out, l
   AttBwdParams p{reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, lse, delta, dq_acc, plan, T, Hq, Hkv, scale, status, reserved};
   rc = D == 128 ? launch_bwd<128>(tq, tdo, tdq, p, n_items, st) : launch_bwd<64>(tq, tdo, tdq, p, n_items, st);
   if (rc) return rc;
-  const long long n = static_cast<long long>(T) * (Hq * D / 8);
-  attn_dq_store_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, T, Hq * D);
+  attn_dq_store_kernel<<<dim3(static_cast<unsigned>(T), (Hq * D / 8 + 255) / 256), 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, T, Hq * D);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
