@@ -206,7 +206,11 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_fwd_kernel(const __nv_bfloa
   g.from_float(o); g.store(act + t * F + c);
 }
 
-__global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gu,
+// WITH_ACT: the forward output silu(gate) * up is also produced, written over dact (each thread reads its
+// dact vector before it stores there), for a backward that did not keep it: one pass over gate/up
+// instead of a forward kernel plus this one.
+template <bool WITH_ACT>
+__global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(__nv_bfloat16* dact, const __nv_bfloat16* __restrict__ gu,
                                                                __nv_bfloat16* __restrict__ dgu, long long T, int F) {
   // grid = (tokens, column blocks): no 64-bit division per thread
   const long long t = blockIdx.x;
@@ -219,6 +223,12 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(const __nv_bfloa
     const float sig = __fdividef(1.f, 1.f + __expf(-fg[i]));
     og[i] = fd[i] * fu[i] * sig * (1.f + fg[i] * (1.f - sig));
     ou[i] = fd[i] * fg[i] * sig;
+  }
+  if (WITH_ACT) {
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = __fdividef(fg[i], 1.f + __expf(-fg[i])) * fu[i];   // same expression as the forward kernel
+    d.from_float(o); d.store(dact + t * F + c);
   }
   g.from_float(og); u.from_float(ou);
   g.store(dgu + t * 2 * F + c); u.store(dgu + t * 2 * F + F + c);
@@ -477,7 +487,15 @@ int mtb200_swiglu_fwd(const void* gu, void* act, long long T, int F, cudaStream_
 int mtb200_swiglu_bwd(const void* dact, const void* gu, void* dgu, long long T, int F, cudaStream_t st) {
   if (T <= 0) return 0;
   if (F % 8) return -10;
-  swiglu_bwd_kernel<<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((const bf16*)dact, (const bf16*)gu, (bf16*)dgu, T, F);
+  swiglu_bwd_kernel<false><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((bf16*)const_cast<void*>(dact), (const bf16*)gu, (bf16*)dgu, T, F);
+  return launch_ok();
+}
+
+// Same, and dact_inout is overwritten with the forward output silu(gate) * up.
+int mtb200_swiglu_bwd_act(void* dact_inout, const void* gu, void* dgu, long long T, int F, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (F % 8) return -10;
+  swiglu_bwd_kernel<true><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((bf16*)dact_inout, (const bf16*)gu, (bf16*)dgu, T, F);
   return launch_ok();
 }
 

@@ -119,7 +119,9 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     h1 = ops.linear(attn, p["wo"], None, x)
     n2, rstd2 = ops.rmsnorm(h1, p["ln2"], cfg.rms_norm_eps)
     gu = ops.linear(n2, p["wgu"], gather=None if plan is None else (plan, 1))
-    act = ops.swiglu(gu)
+    # a recompute that stops before the down projection does not need the SwiGLU output: backward rebuilds it
+    # inside the SwiGLU-gradient kernel
+    act = ops.swiglu(gu) if need_out else None
     out = ops.linear(act, p["wd"], None, h1) if need_out else None
     acts = None
     if keep == "compact":   # kept from forward to backward: drop what one elementwise kernel can rebuild
@@ -136,12 +138,15 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     a = acts
     # activations kept in compact form: the normalised inputs and the SwiGLU output are rebuilt by
     # bandwidth-bound kernels (about 1 ms per block) instead of being held for the whole step
-    act = a.act if a.act is not None else ops.swiglu(a.gu)
     # MLP
     dact = ops.linear_dgrad(dout, p["wd"])
-    ops.linear_wgrad(dout, act, g["wd"])
-    del act
-    dgu = ops.swiglu_bwd(dact, a.gu)
+    if a.act is not None:
+        ops.linear_wgrad(dout, a.act, g["wd"])
+        dgu = ops.swiglu_bwd(dact, a.gu)
+    else:   # one pass over gate/up gives its gradient and the SwiGLU output (written over dact)
+        dgu, act = ops.swiglu_bwd_act(dact, a.gu)
+        ops.linear_wgrad(dout, act, g["wd"])
+        del act
     del dact
     dn2 = ops.linear_dgrad(dgu, p["wgu"])
     n2 = a.n2 if a.n2 is not None else ops.rmsnorm(a.h1, p["ln2"], cfg.rms_norm_eps)[0]

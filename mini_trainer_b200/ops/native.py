@@ -50,6 +50,7 @@ class _Sig:
     mtb200_rope = [P, P, P, I, L, I, I, I, P]
     mtb200_swiglu_fwd = [P, P, L, I, P]
     mtb200_swiglu_bwd = [P, P, P, L, I, P]
+    mtb200_swiglu_bwd_act = [P, P, P, L, I, P]
     mtb200_embedding_fwd = [P, P, P, I, I, P]
     mtb200_embedding_bwd = [P, P, P, P, I, I, P]
     mtb200_ce_fwd_bwd = [P, L, P, P, P, L, I, I, F, L, P]
@@ -306,6 +307,13 @@ class NativeOps:
         dgu = torch.empty_like(gate_up)
         self._call("mtb200_swiglu_bwd", dact.data_ptr(), gate_up.data_ptr(), dgu.data_ptr(), T, F2 // 2, self._st())
         return dgu
+
+    def swiglu_bwd_act(self, dact, gate_up):
+        """Returns ``(dgate_up, act)``; ``act`` (the forward output) is written over ``dact``."""
+        T, F2 = gate_up.shape
+        dgu = torch.empty_like(gate_up)
+        self._call("mtb200_swiglu_bwd_act", dact.data_ptr(), gate_up.data_ptr(), dgu.data_ptr(), T, F2 // 2, self._st())
+        return dgu, dact
 
     # -- fused linear + cross-entropy ---------------------------------------------------
     def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100):

@@ -163,6 +163,10 @@ class TorchOps:
         du = da * g * sig
         return torch.cat([dg, du], 1).to(gate_up.dtype)
 
+    def swiglu_bwd_act(self, dact, gate_up):
+        """``(dgate_up, act)``: the gradient and the forward output in one call."""
+        return self.swiglu_bwd(dact, gate_up), self.swiglu(gate_up)
+
     # -- fused linear + cross-entropy ---------------------------------------------------
     def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100):
         """Per-token CE of ``x @ w.T`` against ``targets`` without materialising all logits.

@@ -131,6 +131,11 @@ def test_swiglu(ops):
     gu, da = bf(T, 2 * F), bf(T, F)
     assert rel_err(ops.swiglu(gu), REF.swiglu(gu.float())) < 4e-3
     assert rel_err(ops.swiglu_bwd(da, gu), REF.swiglu_bwd(da.float(), gu.float())) < 5e-3
+    # fused form: the gradient and the forward output (written over the incoming gradient) in one pass
+    act_ref, dgu_ref = ops.swiglu(gu), ops.swiglu_bwd(da, gu)
+    buf = da.clone()
+    dgu, act = ops.swiglu_bwd_act(buf, gu)
+    assert act.data_ptr() == buf.data_ptr() and torch.equal(act, act_ref) and torch.equal(dgu, dgu_ref)
 
 
 def test_embedding(ops):
