@@ -61,7 +61,7 @@ def _prepare_model_dir(path: str, model: str, device) -> None:
     open(os.path.join(path, "READY"), "w").write("ok")
 
 
-def _run(args) -> None:
+def _run(args, bench) -> None:
     if not os.path.exists(os.path.join(REF, "train.py")):
         return _unavailable("baseline/_ref is empty: the reference was not installed on this machine")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -80,19 +80,23 @@ def _run(args) -> None:
     device = torch.device("cuda", torch.cuda.current_device())
 
     sys.path.insert(0, os.path.dirname(HERE))
+    if bench is None:
+        import bench
     from mini_trainer_b200.data.synthetic import CONFIG_DATA, write_synthetic_jsonl
     spec, vocab, max_tokens, batch_size = CONFIG_DATA[args.model]
     max_tokens = args.max_tokens_per_gpu or max_tokens
     batch_size = args.batch_size or batch_size
+    budget = getattr(args, "time_budget_s", bench.DEFAULT_BUDGET_S)
+    steps, warmup = bench.plan_steps(args.model, world, args.steps, args.warmup, budget)   # the rule the native arm uses
     work = os.environ.get("MTB200_REF_WORKDIR", "/tmp/mtb200_ref")
     model_dir = os.path.join(work, args.model)
-    total_steps = args.steps + args.warmup
-    data_path = os.path.join(work, f"{args.model}_{batch_size * total_steps * 2}.jsonl")
+    n_samples = bench.dataset_size(batch_size, steps + warmup)   # same dataset as the native arm
+    data_path = os.path.join(work, f"{args.model}_{n_samples}.jsonl")
     if rank == 0:
         _prepare_model_dir(model_dir, args.model, device)
         if not os.path.exists(data_path):
             from mini_trainer_b200.models.config import get_preset
-            write_synthetic_jsonl(data_path + ".tmp", batch_size * total_steps * 2, spec, get_preset(args.model).vocab_size, seed=893)
+            write_synthetic_jsonl(data_path + ".tmp", n_samples, spec, get_preset(args.model).vocab_size, seed=893)
             os.replace(data_path + ".tmp", data_path)
     dist.barrier()
 
@@ -112,15 +116,19 @@ def _run(args) -> None:
     model.train()
     batch_totals = BatchMetrics()
 
+    h2d = d2h = 0
+
     def one_step(batch):
         # body of the reference's train() loop, train.py:85-122
+        nonlocal h2d, d2h
         batch_totals.reset_batch()
-        ntok = 0
+        ntok = h2d = d2h = 0
         for grad_accum, mb in enumerate(batch):
             mb_start = time.time()
             n_loss = mb.pop("num_loss_counted_tokens")
             n_samples = mb.pop("num_samples")
             bn = mb.pop("batch_num_loss_counted_tokens")
+            h2d += sum(v.numel() * v.element_size() for v in mb.values())
             mb = {k: v.to(device) for k, v in mb.items()}
             output = model(**mb)
             loss = output.loss.float().sum()
@@ -133,48 +141,64 @@ def _run(args) -> None:
                                                       num_samples=n_samples, loss=loss_metrics,
                                                       loss_backward=loss.detach().item() / world,
                                                       time_per_minibatch=time.time() - mb_start)
+            d2h += 8   # the two fp32 .item() reads above
         batch_totals.reduce_batch_metrics(device)
         grad_norm = take_gradient_step(model, optimizer, lr_scheduler)
+        d2h += 4 * len(batch_totals.totals) + 4   # the reduced metrics vector and the gradient norm
         return batch_totals.totals["num_total_tokens"], float(grad_norm)
 
-    for _ in range(args.warmup):
+    dist.barrier(); torch.cuda.synchronize()
+    tw = time.perf_counter()
+    for _ in range(warmup):
         one_step(next(loader))
     dist.barrier(); torch.cuda.synchronize()
-    from bench import ClockSampler
-    clocks = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    tw = torch.tensor([time.perf_counter() - tw], device=device)
+    dist.all_reduce(tw, op=dist.ReduceOp.MAX)
+    agreed = torch.tensor([bench.guard_steps(steps, tw.item(), warmup, budget)], device=device)
+    dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+    steps = int(agreed.item())
+    clocks = bench.ClockSampler(bench.physical_gpu_index(torch.cuda.current_device())) if rank == 0 else None
     if clocks:
         clocks.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
     e0.record()
     toks = 0.0
-    for _ in range(args.steps):
+    for _ in range(steps):
         t, _ = one_step(next(loader))
         toks += t
     e1.record()
     dist.barrier(); torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    ms = torch.tensor([e0.elapsed_time(e1), wall_ms], device=device)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    tps = toks / (ms.item() / 1e3)
+    tps = toks / (ms[0].item() / 1e3)
     if rank == 0:
         print(json.dumps({
             "impl": "reference",
-            "metric": "train tokens/sec, Llama-3.1-8B-architecture full SFT (device-timed, max over ranks)",
-            "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms.item() / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (same generator and seed as the native arm; includes dummy-sample tokens)",
-            "config": {"model": args.model, "global_batch": batch_size, "seq_len": f"packed, max_tokens_per_gpu={max_tokens}",
-                       "parallelism": f"fsdp2 x{world}", "stack": "torch FSDP2 + flash-attn 2 + Liger fused linear-CE",
-                       "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1)},
+            "metric": f"train tokens/sec, {bench.MODEL_LABEL.get(args.model, args.model)}-architecture full SFT (device-timed, max over ranks)",
+            "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "ms_per_step": ms[0].item() / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (same generator, dataset size, sampler and seed as the native arm; includes dummy-sample tokens)",
+            "config": bench.common_config(args.model, batch_size, max_tokens, world),
+            "detail": {"stack": "torch FSDP2 + flash-attn 2 + Liger fused linear-CE",
+                       "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1),
+                       "wall_s_total": round(time.time() - bench.T_START, 1)},
             "clocks": clocks.stop() if clocks else None,
-            "e2e": {"value": tps, "unit": "tokens/s", "note": "the reference loop always copies inputs and reads the loss"},
+            "e2e": {"value": toks / (ms[1].item() / 1e3), "unit": "tokens/s", "ms_per_step": ms[1].item() / steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "how": "host wall clock around the same steps; the reference loop copies every minibatch from host "
+                           "memory and reads the loss back twice per minibatch"},
         }), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def main(args) -> None:
+def main(args, bench=None) -> None:
+    """``bench`` is the already imported ``bench.py`` module (its start time and step plan are shared)."""
     try:
-        _run(args)
+        _run(args, bench)
     except BaseException as e:  # the contract is one JSON line and exit code 0
         if isinstance(e, KeyboardInterrupt):
             raise

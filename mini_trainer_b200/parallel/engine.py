@@ -473,14 +473,18 @@ class ShardedEngine:
         reductions still running when the optimizer starts and the post-step barrier."""
         _Side.stalls = [] if on else None
 
-    def exposed_comm_ms(self) -> float:
-        """Sum of the recorded stalls in milliseconds (synchronises the device); clears the record."""
+    def exposed_comm_ms(self) -> dict:
+        """Exposed communication since the last call, in milliseconds (synchronises the device; clears
+        the record): ``stream_ms`` is the sum of the recorded compute-stream stalls, ``in_kernel_ms``
+        the time the fused all-gather GEMMs' TMA producers spent waiting for weight chunks that had
+        not arrived yet (mean over the CTAs of each launch, summed over launches)."""
         if _Side.stalls is None:
-            return 0.0
+            return {"stream_ms": 0.0, "in_kernel_ms": 0.0}
         torch.cuda.synchronize(self.device)
         total = sum(a.elapsed_time(b) for a, b in _Side.stalls)
         _Side.stalls = []
-        return total
+        in_kernel = self.comm.take_gather_wait_ms() if hasattr(self.comm, "take_gather_wait_ms") else 0.0
+        return {"stream_ms": total, "in_kernel_ms": in_kernel}
 
     def _timed_comm(self, fn):
         """Runs a device-side wait (a kernel that polls peers' flags) inside a stall bracket."""
