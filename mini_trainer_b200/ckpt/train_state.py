@@ -2,8 +2,12 @@
 exports weights and restarts the optimizer from zero when a run continues from an export).
 
 Each rank writes ``rank<r>-of-<w>.safetensors`` with its slices of the fp32 master weights, both
-AdamW moments and the working copy for every group; rank 0 adds ``state.json`` (optimizer step,
-scheduler step, samples seen, sampler seed, world size). Resume requires the same world size.
+AdamW moments for every group (plus the OSFT factors it owns, when that mode is on); rank 0 adds
+``state.json``: optimizer step, world size and whatever the training loop passes in ``extra``
+(scheduler state, optimizer steps taken, global batches consumed, samples seen, samples at the
+last export). Resume requires the same world size. ``trainer.train`` writes one next to every
+exported checkpoint when ``save_train_state`` is on, and ``train.py --resume-from`` restores it
+and continues the data stream where it stopped.
 """
 from __future__ import annotations
 
@@ -24,6 +28,9 @@ def save_train_state(engine, directory: str, extra: dict | None = None) -> None:
         tensors[f"{n}.master"] = g.master
         tensors[f"{n}.m"] = g.m
         tensors[f"{n}.v"] = g.v
+    osft = getattr(engine, "osft", None)
+    if osft is not None:
+        tensors.update(osft.state_tensors())
     st.save_file({k: v.cpu() for k, v in tensors.items()},
                  os.path.join(directory, f"rank{engine.rank}-of-{engine.world}.safetensors"))
     if engine.rank == 0:
@@ -54,5 +61,8 @@ def load_train_state(engine, directory: str) -> dict:
             dst.copy_(src.to(dst.dtype))
         g.shard.copy_(g.master.to(g.shard.dtype))
         g.has_grad = False
+    osft = getattr(engine, "osft", None)
+    if osft is not None:
+        osft.load_state_tensors(tensors)
     engine.step_count = int(meta["step_count"])
     return meta

@@ -50,7 +50,11 @@ def main(
     balance_by: str = Option("cost", help="cost | tokens: what the LPT packer balances across ranks (same global batch either way)"),
     osft: bool = Option(False, help="Orthogonal-subspace fine-tuning of the attention/MLP projections"),
     osft_rank_ratio: float = Option(0.5, help="Fraction of each projection's singular directions that is frozen"),
-    resume_from: Optional[str] = Option(None, help="Directory of a training-state checkpoint to resume from"),
+    save_train_state: bool = Option(False, help="With every exported checkpoint also write the sharded training state "
+                                                "(fp32 master weights, AdamW moments, scheduler, data position) under "
+                                                "<output-dir>/train_state/samples_<N>"),
+    resume_from: Optional[str] = Option(None, help="A train_state/samples_<N> directory written by --save-train-state: "
+                                                   "weights, optimizer, scheduler, counters and the data stream continue from it"),
 ):
     import torch
 
@@ -90,11 +94,13 @@ def main(
         enable_osft(model, rank_ratio=osft_rank_ratio)
     model, optimizer, sched = setup_training_components(model, learning_rate=learning_rate,
                                                         num_warmup_steps=num_warmup_steps, lr_scheduler=lr_scheduler)
+    resume_state = None
     if resume_from:
         from ..ckpt.train_state import load_train_state
-        meta = load_train_state(model, resume_from)
-        if "scheduler" in meta:
-            sched.load_state_dict(meta["scheduler"])
+        resume_state = load_train_state(model, resume_from)
+        if "scheduler" in resume_state:
+            sched.load_state_dict(resume_state["scheduler"])
+    skip_batches = int((resume_state or {}).get("batches_consumed", 0))
     cost_len = model.cfg.attention_cost_length() if balance_by == "cost" else None
     if data_path.startswith("synthetic:"):
         parts = data_path.split(":")
@@ -105,12 +111,14 @@ def main(
             spec = dataclasses.replace(spec, hi=int(parts[3]))
         dataset = synthetic_dataset(n, spec, min(vocab, model.cfg.vocab_size), seed=seed)
         loader = get_data_loader(dataset=dataset, batch_size=batch_size, max_tokens_per_gpu=max_tokens_per_gpu,
-                                 seed=seed, pin_memory=device.type == "cuda", cost_len=cost_len)
+                                 seed=seed, pin_memory=device.type == "cuda", cost_len=cost_len, skip_batches=skip_batches)
     else:
         loader = get_data_loader(data_path=data_path, batch_size=batch_size, max_tokens_per_gpu=max_tokens_per_gpu,
-                                 seed=seed, num_workers=num_workers, pin_memory=device.type == "cuda", cost_len=cost_len)
+                                 seed=seed, num_workers=num_workers, pin_memory=device.type == "cuda", cost_len=cost_len,
+                                 skip_batches=skip_batches)
     train(model, optimizer, sched, loader, output_dir, min_samples_per_checkpoint, model_name_or_path,
-          max_steps=max_steps, max_shard_bytes=int(max_shard_gb * 1e9))
+          max_steps=max_steps, max_shard_bytes=int(max_shard_gb * 1e9), save_train_state=save_train_state,
+          resume_state=resume_state)
 
 
 if __name__ == "__main__":

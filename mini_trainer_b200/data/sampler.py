@@ -91,16 +91,20 @@ class JsonlDataset(torch.utils.data.Dataset):
 class InfiniteSampler(torch.utils.data.Sampler):
     """Endless shuffled index stream, the same on all ranks (reference: sampler.py:116-142)."""
 
-    def __init__(self, len_data: int, seed: int = 37):
+    def __init__(self, len_data: int, seed: int = 37, start_index: int = 0):
         self.len_data = len_data
         self.seed = seed
+        # indices already consumed by an earlier run (resume): the stream continues where it stopped
+        self.start_index = int(start_index)
 
     def __iter__(self) -> Iterator[int]:
-        epoch = 0
+        epoch, skip = divmod(self.start_index, max(1, self.len_data))
         while True:
             g = torch.Generator()
             g.manual_seed(self.seed + epoch)
-            yield from torch.randperm(self.len_data, generator=g).tolist()
+            perm = torch.randperm(self.len_data, generator=g).tolist()
+            yield from perm[skip:]
+            skip = 0
             epoch += 1
 
     def __len__(self) -> int:
@@ -264,13 +268,15 @@ def get_data_loader(**kwargs):
     ``seed``; optional ``rank``, ``world_size``, ``dummy_sample`` (bypass ``torch.distributed``,
     which is how tests simulate several ranks in one process), ``cost_len`` (balance ranks on estimated
     compute cost instead of tokens, see ``data.packer.lpt_pack_all``), ``num_workers`` (0 = packing
-    thread, >0 = DataLoader worker processes), ``prefetch`` and ``pin_memory``.
+    thread, >0 = DataLoader worker processes), ``prefetch``, ``pin_memory`` and ``skip_batches``
+    (global batches an earlier run already consumed; a resumed run continues the same stream).
     """
     dataset = kwargs.get("dataset") or JsonlDataset(kwargs["data_path"])
     collator = MaxTokensPerRankCollator(kwargs["max_tokens_per_gpu"], rank=kwargs.get("rank"),
                                         world_size=kwargs.get("world_size"),
                                         dummy_sample=kwargs.get("dummy_sample"), cost_len=kwargs.get("cost_len"))
-    sampler = InfiniteSampler(len(dataset), seed=kwargs["seed"])
+    sampler = InfiniteSampler(len(dataset), seed=kwargs["seed"],
+                              start_index=int(kwargs.get("skip_batches", 0)) * int(kwargs["batch_size"]))
     num_workers = int(kwargs.get("num_workers", 0))
     if num_workers > 0:
         return torch.utils.data.DataLoader(dataset, kwargs["batch_size"], sampler=sampler,

@@ -161,6 +161,7 @@ class ShardedEngine:
             self._rs_scratch = torch.empty(smax, dtype=self.param_dtype, device=self.device)
         # None = derive from free device memory; 0 = recompute every block like the reference
         self.activation_budget_bytes = activation_budget_bytes
+        self._oom_retries = 0
 
     # ------------------------------------------------------------------------------------
     # initialisation / state exchange
@@ -258,13 +259,24 @@ class ShardedEngine:
             ev.record(torch.cuda.current_stream())
             self._pbuf_free[slot] = ev
 
-    def _gather_group(self, grp: ShardedGroup):
-        """Synchronous gather of the embed / head group into a fresh buffer."""
+    def _gather_group(self, grp: ShardedGroup, prefetch: bool = False):
+        """Gathers the embed / head group into a fresh buffer; returns ``(views, buffer, event)``.
+
+        ``prefetch``: the gather runs on the side stream (which first waits for the work already
+        queued on the compute stream, so the fresh buffer cannot be written while its memory's
+        previous owner is still being read) and the caller waits on ``event`` before the first use.
+        Otherwise it runs on the compute stream inside an exposed-communication bracket."""
         if self.world == 1:
-            return grp.layout.views(grp.shard), grp.shard
+            return grp.layout.views(grp.shard), grp.shard, None
         full = torch.empty(grp.layout.padded_numel, dtype=self.param_dtype, device=self.device)
-        self.comm.all_gather(grp.shard, full)
-        return grp.layout.views(full), full
+        if prefetch and self.side.cuda:
+            with self.side.run(wait_current=True):
+                self.comm.all_gather(grp.shard, full)
+                ev = self.side.record()
+            full.record_stream(self.side.stream)
+            return grp.layout.views(full), full, ev
+        self._timed_comm(lambda: self.comm.all_gather(grp.shard, full))
+        return grp.layout.views(full), full, None
 
     def _reduce(self, grp: ShardedGroup, gfull: torch.Tensor, slot: int = -1, last: bool = False):
         """Reduce-scatter ``gfull`` into the group's fp32 accumulator on the side stream.
@@ -343,8 +355,16 @@ class ShardedEngine:
         return levels
 
     def _auto_activation_budget(self, tokens: int) -> int:
-        """Memory that can hold extra saved activations: device capacity minus optimizer/parameter
-        state, the per-block inputs, the working set of one block's backward and the loss buffers."""
+        """Memory that can hold extra saved activations. Two bounds, the smaller wins:
+
+        * a static plan: 93 % of the device minus optimizer/parameter state, the per-block inputs,
+          the working set of one block's backward and the loss buffers;
+        * what is actually obtainable right now: free device memory as the driver reports it (this
+          sees everything outside the caching allocator too: the symmetric arena's mappings, NCCL's
+          buffers, another process) plus the allocator's cached-but-unused blocks, minus the same
+          transient needs and a margin. Called at the start of a microbatch, when the previous one's
+          activations have been returned to the allocator.
+        """
         if self.device.type != "cuda":
             return 0
         cfg = self.cfg
@@ -355,8 +375,14 @@ class ShardedEngine:
         ce = getattr(self.ops, "ce_chunk", 2048) * v * 6 + v * h * 4
         root = 4 * v * h * 2
         bufs = sum(b.numel() * b.element_size() for b in self._pbufs + self._gbufs)
-        used = self.state_bytes() + base + work + ce + root + bufs + (4 << 30)
-        return int(0.93 * total - used)
+        transient = base + work + ce + root
+        static = int(0.93 * total - (self.state_bytes() + transient + bufs + (4 << 30)))
+        free, _ = torch.cuda.mem_get_info(self.device)
+        cached = torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+        live = int(0.97 * (free + cached) - transient - (3 << 30))
+        if self._oom_retries:   # an earlier microbatch ran out of memory: plan more cautiously from now on
+            live -= self._oom_retries * (8 << 30)
+        return min(static, live)
 
     # ------------------------------------------------------------------------------------
     # one microbatch
@@ -373,27 +399,22 @@ class ShardedEngine:
         tied = cfg.tie_word_embeddings
 
         # ---- forward ----
-        emb_views, emb_full = self._gather_group(self.embed)
-        x = ops.embedding(emb_views["embed"], batch.input_ids)
-        if not tied:
-            del emb_views, emb_full
-        saved = []
         levels = self.plan_checkpointing(batch.num_tokens)
-        nxt = self._gather_block(0, fused=True)
-        for i in range(nL):
-            p, ev, slot = nxt
-            _Side.wait(ev)
-            nxt = self._gather_block(i + 1, fused=True) if i + 1 < nL else None
-            xin = x
-            x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq,
-                                                  keep="compact" if levels[i] == 0 else False, want_attn=levels[i] == 1)
-            saved.append((xin, acts, attn_state))
-            if i + 1 < nL or self.world == 1:
-                self._release_pbuf(slot)
-            last_block = (p, slot)  # the last block stays gathered for backward (reshard_after_forward=False)
+        try:
+            x, saved, last_block, emb_views, head = self._forward(batch, levels)
+        except torch.OutOfMemoryError:
+            # Forward only pulls parameters and writes activations: nothing has been reduced or signalled
+            # yet, so with one-sided gathers (one rank, or the symmetric backend) it can simply run again
+            # with every block at the cheapest checkpoint level. Collective gathers cannot be re-issued.
+            if not (self.world == 1 or self.symmetric):
+                raise
+            self._oom_retries += 1
+            torch.cuda.empty_cache()
+            x, saved, last_block, emb_views, head = self._forward(batch, [2] * nL)
 
         # ---- head: loss and its gradients in one pass ----
-        head_views, head_full = self._gather_group(self.head)
+        head_views, head_full, head_ev = head
+        _Side.wait(head_ev)
         hg_full = self._root_grad_buffer("head")
         head_g = self.head.layout.views(hg_full)
         if tied:
@@ -404,7 +425,7 @@ class ShardedEngine:
         else:
             loss, dx = D.head_forward_backward(ops, cfg, head_views, head_g, head_views["lm_head"], head_g["lm_head"],
                                                False, x, batch, grad_scale)
-        del x, head_views, head_full
+        del x, head_views, head_full, head
         self._root_free["head"] = self._reduce(self.head, hg_full, last=last)
 
         # ---- backward through the blocks ----
@@ -433,6 +454,36 @@ class ShardedEngine:
         ops.embedding_bwd(emb_g["embed"], batch.input_ids, dx)
         self._root_free["embed"] = self._reduce(self.embed, eg_full, last=last)
         return loss
+
+    def _forward(self, batch: D.PackedBatch, levels: list):
+        """Forward through the embedding and the blocks; returns the last hidden state, what each
+        block kept for backward, the still-gathered last block, the embedding views (tied head) and
+        the head group's ``(views, buffer, ready event)``."""
+        cfg, ops = self.cfg, self.ops
+        nL = len(self.blocks)
+        emb_views, emb_full, _ = self._gather_group(self.embed)
+        x = ops.embedding(emb_views["embed"], batch.input_ids)
+        if not cfg.tie_word_embeddings:
+            emb_views = None
+        del emb_full
+        saved = []
+        nxt = self._gather_block(0, fused=True)
+        last_block = None
+        head = None
+        for i in range(nL):
+            p, ev, slot = nxt
+            _Side.wait(ev)
+            nxt = self._gather_block(i + 1, fused=True) if i + 1 < nL else None
+            if i == nL - 1:   # the head's parameters arrive while the last block computes
+                head = self._gather_group(self.head, prefetch=True)
+            xin = x
+            x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq,
+                                                  keep="compact" if levels[i] == 0 else False, want_attn=levels[i] == 1)
+            saved.append((xin, acts, attn_state))
+            if i + 1 < nL or self.world == 1:
+                self._release_pbuf(slot)
+            last_block = (p, slot)  # the last block stays gathered for backward (reshard_after_forward=False)
+        return x, saved, last_block, emb_views, head
 
     # ------------------------------------------------------------------------------------
     # optimizer

@@ -166,6 +166,25 @@ class OSFT:
             if a < bnd:
                 tensor[a - lo: bnd - lo] = value
 
+    # -- training-state checkpoints ------------------------------------------------------------
+    def state_tensors(self) -> dict:
+        """Trainable factors and their AdamW moments of the matrices this rank owns (the frozen part
+        is rebuilt from the weights at start-up and is not stored)."""
+        out = {}
+        for i, mt in enumerate(self.mats):
+            if mt.owner == self.rank:
+                for kind, lst in (("f", mt.factors), ("m", mt.m), ("v", mt.v)):
+                    for j, t in enumerate(lst):
+                        out[f"osft.{i}.{kind}{j}"] = t
+        return out
+
+    def load_state_tensors(self, tensors: dict) -> None:
+        for i, mt in enumerate(self.mats):
+            if mt.owner == self.rank:
+                for kind, lst in (("f", mt.factors), ("m", mt.m), ("v", mt.v)):
+                    for j, t in enumerate(lst):
+                        t.copy_(tensors[f"osft.{i}.{kind}{j}"].to(t.dtype))
+
     # -- the optimizer step -----------------------------------------------------------------
     @torch.no_grad()
     def optimizer_step(self, lr: float) -> torch.Tensor:

@@ -122,17 +122,28 @@ def take_gradient_step(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule
 def train(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule, data_loader, output_dir: str,
           min_samples_per_checkpoint: int, model_name_or_path: Optional[str] = None,
           max_steps: Optional[int] = None, log_echo: bool = True,
-          max_shard_bytes: Optional[int] = None) -> dict:
+          max_shard_bytes: Optional[int] = None, save_train_state: bool = False,
+          resume_state: Optional[dict] = None) -> dict:
+    """The training loop. ``save_train_state`` also writes a sharded training-state checkpoint
+    (``<output_dir>/train_state/samples_<N>``) with every export; ``resume_state`` is the metadata
+    ``load_train_state`` returned for such a directory: step, sample counters and checkpoint cadence
+    continue from it (the caller builds ``data_loader`` with ``skip_batches=resume_state["batches_consumed"]``).
+    ``max_steps`` counts optimizer steps of the whole run, resumed ones included."""
     rank = int(os.environ.get("RANK", 0))
     world_size = model.world
     is_main = rank == 0
     metric_logger = AsyncStructuredLogger(os.path.join(output_dir, f"training_metrics_{rank}.jsonl"), echo=log_echo)
     batch_totals = BatchMetrics()
     device = model.device
-    step = 0
-    total_samples_accumulated = 0.0
-    last_saved_samples = 0.0
+    rs = resume_state or {}
+    step = int(rs.get("train_step", 0))
+    total_samples_accumulated = float(rs.get("total_samples_accumulated", 0.0))
+    last_saved_samples = float(rs.get("last_saved_samples", 0.0))
+    batches_consumed = int(rs.get("batches_consumed", 0))
     last = {}
+    if max_steps is not None and step >= max_steps:
+        metric_logger.close()
+        return last
     for batch in data_loader:
         batch_start = time.time()
         batch_totals.reset_batch()
@@ -155,6 +166,7 @@ def train(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule, data_loader
                 time_per_minibatch=time.time() - mb_start,
             )
         step += 1
+        batches_consumed += 1
         grad_norm = take_gradient_step(model, optimizer, lr_scheduler)
         # the single device->host read of the step
         local_loss = float(loss_sum.item())
@@ -188,6 +200,13 @@ def train(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule, data_loader
             save_model(model, total_samples_accumulated, output_dir, model_name_or_path,
                        **({} if max_shard_bytes is None else {"max_shard_bytes": max_shard_bytes}))
             last_saved_samples = total_samples_accumulated
+            if save_train_state:
+                from .ckpt.train_state import save_train_state as _save_state
+                _save_state(model, os.path.join(output_dir, "train_state", f"samples_{total_samples_accumulated}"),
+                            extra={"scheduler": lr_scheduler.state_dict(), "train_step": step,
+                                   "batches_consumed": batches_consumed,
+                                   "total_samples_accumulated": total_samples_accumulated,
+                                   "last_saved_samples": last_saved_samples})
         if max_steps is not None and step >= max_steps:
             break
     metric_logger.close()

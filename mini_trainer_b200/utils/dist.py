@@ -24,6 +24,14 @@ def init_distributed_environment(backend: str | None = None, timeout_minutes: fl
     os.environ.setdefault("WORLD_SIZE", "1")
     os.environ.setdefault("LOCAL_RANK", "0")
     if use_cuda:
+        # Training targets ~90 % of device memory with a different token count and a different mix of
+        # kept activations every minibatch; fixed-size allocator segments fragment under that pattern.
+        # Expandable segments grow and shrink in place. An explicit PYTORCH_CUDA_ALLOC_CONF wins.
+        if "PYTORCH_CUDA_ALLOC_CONF" not in os.environ:
+            try:
+                torch.cuda.memory._set_allocator_settings("expandable_segments:True")
+            except Exception:
+                pass
         torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
         device = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     else:

@@ -70,3 +70,41 @@ def test_smoke_run_two_gloo_ranks():
     assert "smoke run ok" in proc.stdout
     recs = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
     assert [r["step"] for r in recs] == [1, 2] and recs[1]["loss"] < recs[0]["loss"]
+
+
+def _train_cli(out, extra, port):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT=str(port))
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:tiny-qwen2",
+           "--data-path", "synthetic:tiny-qwen2:40:200", "--batch-size", "8", "--max-tokens-per-gpu", "1024",
+           "--output-dir", out, "--learning-rate", "1e-3", "--num-warmup-steps", "3", "--seed", "893",
+           "--logging-level", "WARNING", "--save-train-state"] + extra
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+
+
+def test_resume_continues_weights_optimizer_schedule_and_data(tmp_path):
+    """4 steps in one go == 2 steps, stop, resume from the written training state, 2 more steps:
+    the same batches are drawn (the 40-sample dataset wraps into its second epoch at step 6, not
+    reached here, but step 3-4 must not replay step 1-2), the same learning rates are applied, the sample
+    counters and checkpoint names continue, and the final weights agree."""
+    import torch
+    from mini_trainer_b200.ckpt import safetensors_io as st
+    a, b = str(tmp_path / "straight"), str(tmp_path / "resumed")
+    _train_cli(a, ["--max-steps", "4", "--min-samples-per-checkpoint", "16"], 29651)
+    _train_cli(b, ["--max-steps", "2", "--min-samples-per-checkpoint", "16"], 29652)
+    state = os.path.join(b, "train_state", "samples_16.0")
+    meta = json.load(open(os.path.join(state, "state.json")))
+    assert meta["train_step"] == 2 and meta["batches_consumed"] == 2 and meta["total_samples_accumulated"] == 16.0
+    _train_cli(b, ["--max-steps", "4", "--min-samples-per-checkpoint", "16", "--resume-from", state], 29653)
+    rows_a = [json.loads(l) for l in open(os.path.join(a, "training_metrics_0.jsonl"))]
+    rows_b = [json.loads(l) for l in open(os.path.join(b, "training_metrics_0.jsonl"))]
+    assert [r["step"] for r in rows_b] == [1, 2, 3, 4]
+    for ra, rb in zip(rows_a, rows_b):
+        assert ra["lr"] == rb["lr"] and ra["num_total_tokens"] == rb["num_total_tokens"]
+        assert abs(ra["loss"] - rb["loss"]) < 1e-5 and abs(ra["grad_norm"] - rb["grad_norm"]) < 1e-4
+        assert ra["total_samples_accumulated"] == rb["total_samples_accumulated"]
+    wa = st.load_file(os.path.join(a, "hf_format", "samples_32.0", "model.safetensors"))
+    wb = st.load_file(os.path.join(b, "hf_format", "samples_32.0", "model.safetensors"))
+    assert set(wa) == set(wb) and all(torch.equal(wa[k], wb[k]) for k in wa)
