@@ -48,6 +48,7 @@ struct Params {
   const __nv_bfloat16* bias;
   int* status;
   int num_pairs;
+  float alpha;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -213,7 +214,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         if (row_ok) {
           float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
           if (p.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -312,7 +313,7 @@ extern "C" {
 // clusters of two cannot be scheduled on this device; callers then use the one-CTA kernel.
 int mtb200_gemm2_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* D,
                       long long ldd, int out_f32, const void* R, long long ldr, const void* bias, int M, int N, int K,
-                      int* status, cudaStream_t stream) {
+                      float alpha, int* status, cudaStream_t stream) {
   using namespace mtb;
   using namespace mtb::g2;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -325,7 +326,7 @@ int mtb200_gemm2_bf16(const void* A, long long lda, int a_mn, const void* B, lon
   if (b_mn) rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, 64);
   else rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BNH);
   if (rc) return rc - 10;
-  Params p{M, N, K, D, ldd, R, ldr, reinterpret_cast<const __nv_bfloat16*>(bias), status, 0};
+  Params p{M, N, K, D, ldd, R, ldr, reinterpret_cast<const __nv_bfloat16*>(bias), status, 0, alpha};
   const int sel = (a_mn ? 4 : 0) | (b_mn ? 2 : 0) | (out_f32 ? 1 : 0);
   switch (sel) {
     case 0: return launch<false, false, false>(ta, tb, p, stream);

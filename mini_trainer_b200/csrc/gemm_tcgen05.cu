@@ -47,6 +47,7 @@ struct GemmParams {
   long long ldr;
   const __nv_bfloat16* bias;  // optional, [N]
   int* status;            // device word; set non-zero when a bounded wait expired
+  float alpha;            // the product is multiplied by alpha before bias and residual are added
 };
 
 // Fused all-gather: while the GEMM runs, eight extra warps per CTA pull this parameter group's
@@ -304,7 +305,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (row_ok) {
           float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
           if (p.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -443,14 +444,14 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
 
 extern "C" {
 
-// D[M,N] = op(A) * op(B) (+bias) (+R).
+// D[M,N] = alpha * op(A) * op(B) (+bias) (+R).
 //   a_mn = 0: A is row-major [M, K] (lda >= K);  a_mn = 1: A is row-major [K, M] (lda >= M)
 //   b_mn = 0: B is row-major [N, K] (ldb >= K);  b_mn = 1: B is row-major [K, N] (ldb >= N)
 //   out_f32: D and R are fp32, else bf16. R may alias D (accumulate). bias is bf16 [N] or null.
 // Returns 0 on success, a negative code on invalid arguments or launch failure.
 int mtb200_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* D,
                      long long ldd, int out_f32, const void* R, long long ldr, const void* bias, int M, int N, int K,
-                     int* status, cudaStream_t stream) {
+                     float alpha, int* status, cudaStream_t stream) {
   using namespace mtb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (N % 8 || ldd % 8 || (R && ldr % 8)) return -10;
@@ -462,7 +463,7 @@ int mtb200_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long
   if (b_mn) rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, 64);
   else rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);
   if (rc) return rc - 10;
-  GemmParams p{M, N, K, D, ldd, R, ldr, reinterpret_cast<const __nv_bfloat16*>(bias), status};
+  GemmParams p{M, N, K, D, ldd, R, ldr, reinterpret_cast<const __nv_bfloat16*>(bias), status, alpha};
   const int sel = (a_mn ? 4 : 0) | (b_mn ? 2 : 0) | (out_f32 ? 1 : 0);
   switch (sel) {
     case 0: return launch<false, false, false>(ta, tb, p, stream);
@@ -496,7 +497,7 @@ int mtb200_gemm_bf16_allgather(const void* A, long long lda, void* D, long long 
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&tb, reinterpret_cast<const unsigned char*>(full) + w_byte_off, K, N, K, BK, BN);
   if (rc) return rc - 10;
-  GemmParams p{M, N, K, D, ldd, nullptr, 0, reinterpret_cast<const __nv_bfloat16*>(bias), status};
+  GemmParams p{M, N, K, D, ldd, nullptr, 0, reinterpret_cast<const __nv_bfloat16*>(bias), status, 1.0f};
   GatherParams g{};
   for (int i = 0; i < world; ++i) g.peer_base[i] = bases[i];
   g.shard_off = shard_off; g.shard_bytes = shard_bytes; g.dst = reinterpret_cast<unsigned char*>(full);

@@ -1,8 +1,16 @@
 """Decoder configuration, read from / written to Hugging Face ``config.json``.
 
-Covers the Llama / Qwen2 / Mistral / Granite-style family the reference trains through
+Covers the Llama / Qwen2 / Mistral / Granite family the reference trains through
 ``AutoModelForCausalLM`` (setup_model_for_training.py:86-130): pre-norm decoder blocks with
-RMSNorm, rotary GQA attention (optional q/k/v bias), SwiGLU MLP, tied or untied LM head.
+RMSNorm, rotary GQA attention (optional q/k/v bias), SwiGLU MLP, tied or untied LM head, plus
+Granite's four scalars (embedding, residual, attention and logits multipliers).
+
+The reference's allow-list (setup_model_for_training.py:111-123) also names GPTDolomite,
+Starcoder2, Gemma and Mixtral and merely warns for anything else, because whatever
+``AutoModelForCausalLM`` loads brings its own forward. Here the forward and backward are
+hand-written for ONE block structure, so an architecture whose math differs (LayerNorm or
+GeGLU blocks, MoE routing, sliding-window attention, biases on o_proj / the MLP) is refused by
+``validate_supported`` instead of being trained with the wrong function.
 """
 from __future__ import annotations
 
@@ -33,6 +41,16 @@ class ModelConfig:
     pad_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
     eos_token_id: Optional[int] = None
+    # Granite (modeling_granite.py): embeddings * embedding_multiplier, block outputs * residual_multiplier
+    # before the residual add, softmax scale = attention_multiplier, logits / logits_scaling
+    embedding_multiplier: float = 1.0
+    residual_multiplier: float = 1.0
+    attention_multiplier: Optional[float] = None
+    logits_scaling: float = 1.0
+    sliding_window: Optional[int] = None
+    use_sliding_window: Optional[bool] = None
+    mlp_bias: bool = False
+    hidden_act: str = "silu"
     extra: dict = field(default_factory=dict)  # unknown keys of config.json, written back verbatim
 
     def __post_init__(self):
@@ -40,6 +58,29 @@ class ModelConfig:
             self.head_dim = self.hidden_size // self.num_attention_heads
         if self.num_attention_heads % self.num_key_value_heads:
             raise ValueError("num_attention_heads must be a multiple of num_key_value_heads")
+
+    @property
+    def attention_scale(self) -> float:
+        """Scale applied to q.k before the softmax."""
+        return float(self.attention_multiplier) if self.attention_multiplier is not None else self.head_dim ** -0.5
+
+    def validate_supported(self) -> None:
+        """Raises ``ValueError`` when the hand-written block would not compute this model's function."""
+        arch = (self.architectures or ["?"])[0]
+        problems = []
+        if arch not in SUPPORTED_ARCHITECTURES:
+            problems.append(f"architecture {arch} is not one of {', '.join(SUPPORTED_ARCHITECTURES)}")
+        if self.hidden_act not in ("silu", "swish"):
+            problems.append(f"hidden_act={self.hidden_act!r} (only the SwiGLU MLP is implemented)")
+        if self.mlp_bias:
+            problems.append("mlp_bias=true (MLP biases are not implemented)")
+        if self.attention_bias and self.model_type != "qwen2":
+            problems.append("attention_bias=true outside Qwen2 adds an o_proj bias, which is not implemented")
+        windowed = self.sliding_window is not None and self.sliding_window < self.max_position_embeddings
+        if windowed and (self.use_sliding_window or (self.use_sliding_window is None and self.model_type == "mistral")):
+            problems.append(f"sliding_window={self.sliding_window} (attention here is full causal attention)")
+        if problems:
+            raise ValueError("this model cannot be trained faithfully: " + "; ".join(problems))
 
     # sizes -------------------------------------------------------------------------
     @property
@@ -114,7 +155,9 @@ class ModelConfig:
     _KNOWN = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
               "num_key_value_heads", "head_dim", "rms_norm_eps", "rope_theta", "rope_scaling", "attention_bias",
               "tie_word_embeddings", "max_position_embeddings", "model_type", "architectures",
-              "pad_token_id", "bos_token_id", "eos_token_id")
+              "pad_token_id", "bos_token_id", "eos_token_id", "embedding_multiplier", "residual_multiplier",
+              "attention_multiplier", "logits_scaling", "sliding_window", "use_sliding_window", "mlp_bias", "hidden_act")
+    _GRANITE_ONLY = ("embedding_multiplier", "residual_multiplier", "attention_multiplier", "logits_scaling")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
@@ -147,6 +190,14 @@ class ModelConfig:
             lst = out.pop(k + "_list", None)
             if lst is not None:
                 d[k] = lst
+        for k in self._GRANITE_ONLY:   # only Granite's config class knows these keys
+            if self.model_type != "granite":
+                d.pop(k)
+        for k in ("sliding_window", "use_sliding_window"):
+            if d[k] is None:
+                d.pop(k)
+        if not d["mlp_bias"]:
+            d.pop("mlp_bias")
         out.update(d)
         out.setdefault("hidden_act", "silu")
         out.setdefault("torch_dtype", "bfloat16")
@@ -159,6 +210,9 @@ class ModelConfig:
         with open(path, "w") as f:
             json.dump(self.to_hf_dict(), f, indent=2, sort_keys=True)
             f.write("\n")
+
+
+SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM")
 
 
 def _llama(**kw):

@@ -111,18 +111,19 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     n1, rstd1 = ops.rmsnorm(x, p["ln1"], cfg.rms_norm_eps)
     qkv = ops.linear(n1, p["wqkv"], p.get("bqkv"), gather=None if plan is None else (plan, 0))
     ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+    rm = cfg.residual_multiplier   # Granite scales every branch output before the residual add (1.0 elsewhere)
     if saved_attn is not None:
         attn, lse = saved_attn
     else:
         attn, lse = ops.attention(qkv, batch.cu_seqlens, batch.cu_seqlens_host, batch.max_seqlen,
-                                  cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
-    h1 = ops.linear(attn, p["wo"], None, x)
+                                  cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, scale=cfg.attention_scale)
+    h1 = ops.linear(attn, p["wo"], None, x, alpha=rm)
     n2, rstd2 = ops.rmsnorm(h1, p["ln2"], cfg.rms_norm_eps)
     gu = ops.linear(n2, p["wgu"], gather=None if plan is None else (plan, 1))
     # a recompute that stops before the down projection does not need the SwiGLU output: backward rebuilds it
     # inside the SwiGLU-gradient kernel
     act = ops.swiglu(gu) if need_out else None
-    out = ops.linear(act, p["wd"], None, h1) if need_out else None
+    out = ops.linear(act, p["wd"], None, h1, alpha=rm) if need_out else None
     acts = None
     if keep == "compact":   # kept from forward to backward: drop what one elementwise kernel can rebuild
         acts = BlockActs(x, None, rstd1, qkv, attn, lse, h1, None, rstd2, gu, None)
@@ -136,16 +137,17 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     """Writes every parameter gradient of the block into ``g`` (views of the block's flat
     gradient buffer, same names as ``p``) and returns the gradient of the block input."""
     a = acts
+    rm = cfg.residual_multiplier
     # activations kept in compact form: the normalised inputs and the SwiGLU output are rebuilt by
     # bandwidth-bound kernels (about 1 ms per block) instead of being held for the whole step
     # MLP
-    dact = ops.linear_dgrad(dout, p["wd"])
+    dact = ops.linear_dgrad(dout, p["wd"], alpha=rm)
     if a.act is not None:
-        ops.linear_wgrad(dout, a.act, g["wd"])
+        ops.linear_wgrad(dout, a.act, g["wd"], alpha=rm)
         dgu = ops.swiglu_bwd(dact, a.gu)
     else:   # one pass over gate/up gives its gradient and the SwiGLU output (written over dact)
         dgu, act = ops.swiglu_bwd_act(dact, a.gu)
-        ops.linear_wgrad(dout, act, g["wd"])
+        ops.linear_wgrad(dout, act, g["wd"], alpha=rm)
         del act
     del dact
     dn2 = ops.linear_dgrad(dgu, p["wgu"])
@@ -155,10 +157,11 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     dh1 = ops.rmsnorm_bwd(dn2, a.h1, a.rstd2, p["ln2"], g["ln2"], add_to=dout)
     del dn2
     # attention
-    dattn = ops.linear_dgrad(dh1, p["wo"])
-    ops.linear_wgrad(dh1, a.attn, g["wo"])
+    dattn = ops.linear_dgrad(dh1, p["wo"], alpha=rm)
+    ops.linear_wgrad(dh1, a.attn, g["wo"], alpha=rm)
     dqkv = ops.attention_bwd(dattn, a.qkv, a.attn, a.lse, batch.cu_seqlens, batch.cu_seqlens_host,
-                             batch.max_seqlen, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+                             batch.max_seqlen, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                             scale=cfg.attention_scale)
     del dattn
     ops.rope_(dqkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
               inverse=True)
@@ -178,9 +181,10 @@ def head_forward_backward(ops, cfg: ModelConfig, head_p: dict, head_g: dict, lm_
     of the global batch's loss-token count), so backward starts here without a separate call.
     """
     rows = batch.loss_rows
+    ls = 1.0 / cfg.logits_scaling   # Granite divides the logits by a constant
     if rows is None:
         n, rstd = ops.rmsnorm(x, head_p["norm"], cfg.rms_norm_eps)
-        loss, dn = ops.linear_ce(n, lm_w, batch.targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad)
+        loss, dn = ops.linear_ce(n, lm_w, batch.targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad, logit_scale=ls)
         dx = ops.rmsnorm_bwd(dn, x, rstd, head_p["norm"], head_g["norm"])
         return loss, dx
     # Masked positions (prompt tokens, the last token of every sample) have zero loss and zero
@@ -193,7 +197,8 @@ def head_forward_backward(ops, cfg: ModelConfig, head_p: dict, head_g: dict, lm_
         return loss, dx     # the gradient buffers of the head were zeroed by the caller
     xs = ops.embedding(x, rows)   # row gather
     n, rstd = ops.rmsnorm(xs, head_p["norm"], cfg.rms_norm_eps)
-    loss_s, dn = ops.linear_ce(n, lm_w, batch.loss_targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad)
+    loss_s, dn = ops.linear_ce(n, lm_w, batch.loss_targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad,
+                               logit_scale=ls)
     dxs = ops.rmsnorm_bwd(dn, xs, rstd, head_p["norm"], head_g["norm"])
     loss.index_copy_(0, rows, loss_s)
     dx.index_copy_(0, rows, dxs)
@@ -205,7 +210,9 @@ def forward_logits(ops, cfg: ModelConfig, embed_w, blocks: list, norm_w, lm_w, b
     """Plain inference forward returning ``[T, V]`` logits (tests, checkpoint round-trips)."""
     inv_freq = cfg.rope_inv_freq().to(embed_w.device)
     x = ops.embedding(embed_w, batch.input_ids)
+    if cfg.embedding_multiplier != 1.0:
+        x = x * cfg.embedding_multiplier
     for p in blocks:
         x, _, _ = block_forward(ops, cfg, p, x, batch, inv_freq)
     n, _ = ops.rmsnorm(x, norm_w, cfg.rms_norm_eps)
-    return n.float() @ lm_w.float().t()
+    return (n.float() @ lm_w.float().t()) / cfg.logits_scaling

@@ -33,7 +33,8 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
     T = input_ids.shape[0]
     inv_freq = cfg.rope_inv_freq().to(input_ids.device)
     starts = (position_ids == 0).nonzero().flatten().tolist() + [T]
-    x = sd["model.embed_tokens.weight"][input_ids]
+    x = sd["model.embed_tokens.weight"][input_ids] * cfg.embedding_multiplier
+    rm = cfg.residual_multiplier
     hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
@@ -45,15 +46,16 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
         outs = []
         for a, b in zip(starts[:-1], starts[1:]):
             o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1)[None], k[a:b].transpose(0, 1)[None],
-                                               v[a:b].transpose(0, 1)[None], is_causal=True, enable_gqa=True)
+                                               v[a:b].transpose(0, 1)[None], is_causal=True, enable_gqa=True,
+                                               scale=cfg.attention_scale)
             outs.append(o[0].transpose(0, 1).reshape(b - a, hq * d))
-        x = x + F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"])
+        x = x + rm * F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"])
         n = _rms(x, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
         act = F.silu(F.linear(n, sd[p + "mlp.gate_proj.weight"])) * F.linear(n, sd[p + "mlp.up_proj.weight"])
-        x = x + F.linear(act, sd[p + "mlp.down_proj.weight"])
+        x = x + rm * F.linear(act, sd[p + "mlp.down_proj.weight"])
     n = _rms(x, sd["model.norm.weight"], cfg.rms_norm_eps)
     lm = sd["model.embed_tokens.weight"] if cfg.tie_word_embeddings else sd["lm_head.weight"]
-    logits = F.linear(n, lm).float()
+    logits = F.linear(n, lm).float() / cfg.logits_scaling
     if return_logits:
         return logits
     targets = torch.full_like(labels, -100)

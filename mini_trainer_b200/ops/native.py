@@ -42,8 +42,8 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
 
 class _Sig:
-    mtb200_gemm_bf16 = [P, L, I, P, L, I, P, L, I, P, L, P, I, I, I, P, P]
-    mtb200_gemm2_bf16 = [P, L, I, P, L, I, P, L, I, P, L, P, I, I, I, P, P]
+    mtb200_gemm_bf16 = [P, L, I, P, L, I, P, L, I, P, L, P, I, I, I, F, P, P]
+    mtb200_gemm2_bf16 = [P, L, I, P, L, I, P, L, I, P, L, P, I, I, I, F, P, P]
     mtb200_rmsnorm_fwd = [P, P, P, P, F, I, I, P]
     mtb200_rmsnorm_bwd_blocks = [I]
     mtb200_rmsnorm_bwd = [P, P, P, P, P, P, P, P, I, I, P]
@@ -138,8 +138,8 @@ class NativeOps:
             raise RuntimeError(f"a device-side bounded wait expired (code {code})")
 
     # -- GEMM -------------------------------------------------------------------------
-    def gemm(self, a, a_mn, b, b_mn, out, M, N, K, residual=None, bias=None, tag=None, two_cta=None):
-        """out[M,N] = A*B (+bias) (+residual). ``a_mn``/``b_mn``: operand stored [K, rows].
+    def gemm(self, a, a_mn, b, b_mn, out, M, N, K, residual=None, bias=None, tag=None, two_cta=None, alpha=1.0):
+        """out[M,N] = alpha*A*B (+bias) (+residual). ``a_mn``/``b_mn``: operand stored [K, rows].
         ``two_cta``: force (True) or forbid (False) the cta_group::2 kernel; default by problem size."""
         out_f32 = out.dtype == torch.float32
         assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
@@ -148,7 +148,7 @@ class NativeOps:
             two_cta = self.use_gemm2 and (-(-M // 256)) * (-(-N // 256)) >= 64
         self._call("mtb200_gemm2_bf16" if two_cta else "mtb200_gemm_bf16", a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
                    out.data_ptr(), out.stride(0), int(out_f32), _ptr(residual),
-                   residual.stride(0) if residual is not None else 0, _ptr(bias), M, N, K,
+                   residual.stride(0) if residual is not None else 0, _ptr(bias), M, N, K, float(alpha),
                    self.status.data_ptr(), self._st(), tag=tag or f"gemm_{'t' if a_mn else 'n'}{'n' if b_mn else 't'}")
         return out
 
@@ -183,30 +183,30 @@ class NativeOps:
         return dx
 
     # -- linear -----------------------------------------------------------------------
-    def linear(self, x, w, bias=None, residual=None, gather=None):
-        """``gather = (GatherPlan, stage)`` runs the projection with the all-gather of its parameter
+    def linear(self, x, w, bias=None, residual=None, gather=None, alpha=1.0):
+        """``alpha * x @ w.T (+bias) (+residual)``. ``gather = (GatherPlan, stage)`` runs the projection with the all-gather of its parameter
         group fused into the same kernel (symmetric-memory backend only)."""
         T, K = x.shape
         N = w.shape[0]
         out = torch.empty(T, N, dtype=x.dtype, device=self.device)
         if gather is not None:
-            assert residual is None
+            assert residual is None and alpha == 1.0
             ev = self._ev()
             gather[0].launch(self, x, w, bias, out, gather[1])
             self._ev_end("gemm_nt_allgather", ev)
             return out
-        return self.gemm(x, False, w, False, out, T, N, K, residual=residual, bias=bias)
+        return self.gemm(x, False, w, False, out, T, N, K, residual=residual, bias=bias, alpha=alpha)
 
-    def linear_dgrad(self, dy, w):
+    def linear_dgrad(self, dy, w, alpha=1.0):
         T, N = dy.shape
         K = w.shape[1]
         out = torch.empty(T, K, dtype=dy.dtype, device=self.device)
-        return self.gemm(dy, False, w, True, out, T, K, N)
+        return self.gemm(dy, False, w, True, out, T, K, N, alpha=alpha)
 
-    def linear_wgrad(self, dy, x, dw_out, dbias_out=None):
+    def linear_wgrad(self, dy, x, dw_out, dbias_out=None, alpha=1.0):
         T, N = dy.shape
         K = x.shape[1]
-        self.gemm(dy, True, x, True, dw_out, N, K, T)
+        self.gemm(dy, True, x, True, dw_out, N, K, T, alpha=alpha)
         if dbias_out is not None:
             scratch = self._buf("colsum", 32 * N, torch.float32)
             self._call("mtb200_colsum", dy.data_ptr(), dy.stride(0), dbias_out.data_ptr(), scratch.data_ptr(), T, N,
@@ -242,44 +242,46 @@ class NativeOps:
         self._attn_plan_cache[key] = (cu_host, table)
         return table
 
-    def attention(self, qkv, cu_seqlens, cu_host, max_seqlen, hq, hkv, d):
+    def attention(self, qkv, cu_seqlens, cu_host, max_seqlen, hq, hkv, d, scale=None):
         T = qkv.shape[0]
+        scale = d ** -0.5 if scale is None else float(scale)
         if self.attention_impl == "flash_attn":
-            return self._fa_fwd(qkv, cu_seqlens, max_seqlen, hq, hkv, d)
+            return self._fa_fwd(qkv, cu_seqlens, max_seqlen, hq, hkv, d, scale)
         out = torch.empty(T, hq * d, dtype=qkv.dtype, device=self.device)
         lse = torch.empty(hq, T, dtype=torch.float32, device=self.device)
         plan = self._attn_plan(cu_host, 128, True)
         self._call("mtb200_attn_fwd", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), lse.data_ptr(),
-                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, 0, d ** -0.5, self.status.data_ptr(), self._st())
+                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, 0, scale, self.status.data_ptr(), self._st())
         return out, lse
 
-    def attention_bwd(self, dout, qkv, out, lse, cu_seqlens, cu_host, max_seqlen, hq, hkv, d):
+    def attention_bwd(self, dout, qkv, out, lse, cu_seqlens, cu_host, max_seqlen, hq, hkv, d, scale=None):
         T = qkv.shape[0]
+        scale = d ** -0.5 if scale is None else float(scale)
         if self.attention_impl == "flash_attn":
-            return self._fa_bwd(dout, qkv, out, lse, cu_seqlens, max_seqlen, hq, hkv, d)
+            return self._fa_bwd(dout, qkv, out, lse, cu_seqlens, max_seqlen, hq, hkv, d, scale)
         dqkv = torch.empty_like(qkv)
         plan = self._attn_plan(cu_host, 128, False)
         delta = torch.empty(hq, T, dtype=torch.float32, device=self.device)
         dq_acc = torch.zeros(T, hq * d, dtype=torch.float32, device=self.device)
         self._call("mtb200_attn_bwd", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), dout.data_ptr(),
                    dout.stride(0), dqkv.data_ptr(), dqkv.stride(0), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(),
-                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, int(os.environ.get("MTB200_ATTN_BWD_DEBUG", "0")), d ** -0.5,
+                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, int(os.environ.get("MTB200_ATTN_BWD_DEBUG", "0")), scale,
                    self.status.data_ptr(), self._st(), n=3)
         return dqkv
 
     # library baseline (flash-attn 2), selectable for A/B comparisons only
-    def _fa_fwd(self, qkv, cu, max_seqlen, hq, hkv, d):
+    def _fa_fwd(self, qkv, cu, max_seqlen, hq, hkv, d, scale):
         from flash_attn.flash_attn_interface import _flash_attn_varlen_forward
         T = qkv.shape[0]
         q = qkv[:, : hq * d].view(T, hq, d)
         k = qkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
         v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
         ev = self._ev()
-        out, lse, _, _ = _flash_attn_varlen_forward(q, k, v, cu, cu, max_seqlen, max_seqlen, 0.0, d ** -0.5, causal=True)
+        out, lse, _, _ = _flash_attn_varlen_forward(q, k, v, cu, cu, max_seqlen, max_seqlen, 0.0, scale, causal=True)
         self._ev_end("flash_attn_fwd", ev)
         return out.reshape(T, hq * d), lse
 
-    def _fa_bwd(self, dout, qkv, out, lse, cu, max_seqlen, hq, hkv, d):
+    def _fa_bwd(self, dout, qkv, out, lse, cu, max_seqlen, hq, hkv, d, scale):
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
         T = qkv.shape[0]
         q = qkv[:, : hq * d].view(T, hq, d)
@@ -291,7 +293,7 @@ class NativeOps:
         dv = dqkv[:, (hq + hkv) * d:].view(T, hkv, d)
         ev = self._ev()
         _flash_attn_varlen_backward(dout.view(T, hq, d), q, k, v, out.view(T, hq, d), lse, dq, dk, dv, cu, cu,
-                                    max_seqlen, max_seqlen, 0.0, d ** -0.5, True, -1, -1, 0.0, None, False)
+                                    max_seqlen, max_seqlen, 0.0, scale, True, -1, -1, 0.0, None, False)
         self._ev_end("flash_attn_bwd", ev)
         return dqkv
 
@@ -316,8 +318,8 @@ class NativeOps:
         return dgu, dact
 
     # -- fused linear + cross-entropy ---------------------------------------------------
-    def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100):
-        """Chunked over tokens: logits chunk (fp32) -> per-row softmax statistics, loss and bf16
+    def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100, logit_scale=1.0):
+        """Per-token CE of ``logit_scale * x @ w.T``. Chunked over tokens: logits chunk (fp32) -> per-row softmax statistics, loss and bf16
         dlogits -> dX chunk and dW accumulation, all with the tcgen05 GEMM. Only ``[chunk, V]``
         logits ever exist. dW is accumulated in fp32 and rounded to bf16 once at the end."""
         T, H = x.shape
@@ -331,11 +333,11 @@ class NativeOps:
         first = True
         for a in range(0, T, ck):
             n = min(ck, T - a)
-            self.gemm(x[a:a + n], False, w, False, logits, n, V, H)
+            self.gemm(x[a:a + n], False, w, False, logits, n, V, H, alpha=logit_scale)
             self._call("mtb200_ce_fwd_bwd", logits.data_ptr(), V, targets[a:a + n].data_ptr(), loss[a:a + n].data_ptr(),
                        dlog.data_ptr(), V, n, V, float(grad_scale), ignore_index, self._st())
-            self.gemm(dlog, False, w, True, dx[a:a + n], n, H, V)
-            self.gemm(dlog, True, x[a:a + n], True, dw32, V, H, n, residual=None if first else dw32)
+            self.gemm(dlog, False, w, True, dx[a:a + n], n, H, V, alpha=logit_scale)
+            self.gemm(dlog, True, x[a:a + n], True, dw32, V, H, n, residual=None if first else dw32, alpha=logit_scale)
             first = False
         self._call("mtb200_f32_to_bf16", dw_out.data_ptr(), dw32.data_ptr(), V * H, int(accumulate_dw), self._st())
         return loss, dx

@@ -53,19 +53,21 @@ class TorchOps:
         return dx.to(x.dtype)
 
     # -- linear -----------------------------------------------------------------------
-    def linear(self, x, w, bias=None, residual=None, gather=None):
+    def linear(self, x, w, bias=None, residual=None, gather=None, alpha=1.0):
         y = x @ w.t()
+        if alpha != 1.0:
+            y = y * alpha
         if bias is not None:
             y = y + bias
         if residual is not None:
             y = y + residual
         return y
 
-    def linear_dgrad(self, dy, w):
-        return dy @ w
+    def linear_dgrad(self, dy, w, alpha=1.0):
+        return dy @ w if alpha == 1.0 else (dy @ w) * alpha
 
-    def linear_wgrad(self, dy, x, dw_out, dbias_out=None):
-        dw_out.copy_((dy.float().t() @ x.float()).to(dw_out.dtype))
+    def linear_wgrad(self, dy, x, dw_out, dbias_out=None, alpha=1.0):
+        dw_out.copy_(((dy.float().t() @ x.float()) * alpha).to(dw_out.dtype))
         if dbias_out is not None:
             dbias_out.copy_(dy.float().sum(0).to(dbias_out.dtype))
 
@@ -94,12 +96,12 @@ class TorchOps:
         v = qkv[:, (hq + hkv) * d:].reshape(T, hkv, d)
         return q, k, v
 
-    def attention(self, qkv, cu_seqlens, cu_host, max_seqlen, hq, hkv, d):
+    def attention(self, qkv, cu_seqlens, cu_host, max_seqlen, hq, hkv, d, scale=None):
         """Causal attention inside each ``cu_seqlens`` segment. Returns ``out [T, hq*d]``, ``lse [hq, T]``."""
         T = qkv.shape[0]
         q, k, v = self._split(qkv, hq, hkv, d)
         g = hq // hkv
-        scale = d ** -0.5
+        scale = d ** -0.5 if scale is None else float(scale)
         out = torch.empty(T, hq, d, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(hq, T, dtype=torch.float32, device=qkv.device)
         bounds = list(cu_host) if cu_host is not None else cu_seqlens.tolist()
@@ -117,11 +119,11 @@ class TorchOps:
             lse[:, a:b] = l
         return out.reshape(T, hq * d), lse
 
-    def attention_bwd(self, dout, qkv, out, lse, cu_seqlens, cu_host, max_seqlen, hq, hkv, d):
+    def attention_bwd(self, dout, qkv, out, lse, cu_seqlens, cu_host, max_seqlen, hq, hkv, d, scale=None):
         T = qkv.shape[0]
         q, k, v = self._split(qkv, hq, hkv, d)
         g = hq // hkv
-        scale = d ** -0.5
+        scale = d ** -0.5 if scale is None else float(scale)
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = self._split(dqkv, hq, hkv, d)
         do = dout.reshape(T, hq, d)
@@ -168,8 +170,8 @@ class TorchOps:
         return self.swiglu_bwd(dact, gate_up), self.swiglu(gate_up)
 
     # -- fused linear + cross-entropy ---------------------------------------------------
-    def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100):
-        """Per-token CE of ``x @ w.T`` against ``targets`` without materialising all logits.
+    def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100, logit_scale=1.0):
+        """Per-token CE of ``logit_scale * x @ w.T`` against ``targets`` without materialising all logits.
 
         Returns ``(loss [T] fp32, dx [T, H])``; ``dw_out`` receives (or accumulates) ``dW``.
         Gradients are those of ``grad_scale * sum(loss)``, the uniform upstream scale the
@@ -183,7 +185,7 @@ class TorchOps:
         for a in range(0, T, self.ce_chunk):
             b = min(T, a + self.ce_chunk)
             xc, tc = x[a:b].float(), targets[a:b]
-            logits = xc @ wf.t()
+            logits = (xc @ wf.t()) * logit_scale
             valid = tc != ignore_index
             safe = tc.clamp_min(0)
             lse = torch.logsumexp(logits, -1)
@@ -192,7 +194,7 @@ class TorchOps:
             dl = torch.softmax(logits, -1)
             dl[torch.arange(b - a, device=x.device), safe] -= 1.0
             dl = dl * (valid.float() * grad_scale).unsqueeze(1)
-            dl = dl.to(x.dtype).float()  # the kernels round dlogits to the storage dtype
+            dl = dl.to(x.dtype).float() * logit_scale  # the kernels round dlogits to the storage dtype
             dx[a:b] = (dl @ wf).to(x.dtype)
             dw += dl.t() @ xc
         if accumulate_dw:

@@ -191,15 +191,26 @@ class ShardedEngine:
 
     def load_hf_tensors(self, get_tensor) -> None:
         """``get_tensor(hf_name) -> torch.Tensor`` (any dtype, CPU). Every rank reads the tensors
-        of one group at a time, so host memory holds one block, not the model."""
-        cfg = self.cfg
+        of one group at a time, so host memory holds one block, not the model.
+
+        A vocabulary larger than the checkpoint's (``align_model_and_tokenizer`` grew it to fit the
+        tokenizer, reference setup_model_for_training.py:54-60 ``resize_token_embeddings``) keeps
+        the checkpoint's rows and initialises every new row of the embedding and of the LM head
+        with the mean of the existing rows."""
         for grp, it in self._hf_iters():
             full = torch.zeros(grp.layout.padded_numel, dtype=torch.float32)
             views = grp.layout.views(full)
             for name, view in it(views):
-                view.copy_(get_tensor(name).to(torch.float32).reshape(view.shape))
+                src = get_tensor(name).to(torch.float32)
+                if src.dim() == 2 and src.shape[0] < view.shape[0] and src.shape[1:] == view.shape[1:] \
+                        and name in ("model.embed_tokens.weight", "lm_head.weight"):
+                    view[: src.shape[0]].copy_(src)
+                    view[src.shape[0]:].copy_(src.mean(0, keepdim=True).expand(view.shape[0] - src.shape[0], -1))
+                    continue
+                if src.numel() != view.numel():
+                    raise ValueError(f"{name}: checkpoint shape {tuple(src.shape)} does not fit {tuple(view.shape)}")
+                view.copy_(src.reshape(view.shape))
             self._set_group_from_full(grp, full.to(self.device))
-        del cfg
 
     def _hf_iters(self):
         cfg = self.cfg
@@ -451,6 +462,8 @@ class ShardedEngine:
         if not tied:
             eg_full = self._root_grad_buffer("embed")
             emb_g = self.embed.layout.views(eg_full)
+        if cfg.embedding_multiplier != 1.0:
+            dx.mul_(cfg.embedding_multiplier)
         ops.embedding_bwd(emb_g["embed"], batch.input_ids, dx)
         self._root_free["embed"] = self._reduce(self.embed, eg_full, last=last)
         return loss
@@ -463,6 +476,8 @@ class ShardedEngine:
         nL = len(self.blocks)
         emb_views, emb_full, _ = self._gather_group(self.embed)
         x = ops.embedding(emb_views["embed"], batch.input_ids)
+        if cfg.embedding_multiplier != 1.0:   # Granite
+            x.mul_(cfg.embedding_multiplier)
         if not cfg.tie_word_embeddings:
             emb_views = None
         del emb_full

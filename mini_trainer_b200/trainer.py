@@ -43,7 +43,7 @@ from .utils.log import log_rank_0
 from .utils.lr import LRSchedule
 from .utils.metrics import BatchMetrics
 
-SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM")
+from .models.config import SUPPORTED_ARCHITECTURES  # noqa: E402  (re-exported)
 
 
 def align_model_and_tokenizer(cfg: ModelConfig, tokenizer) -> ModelConfig:
@@ -65,6 +65,20 @@ def align_model_and_tokenizer(cfg: ModelConfig, tokenizer) -> ModelConfig:
     return cfg
 
 
+def resolve_model_path(model_name_or_path: str) -> str:
+    """A local directory is returned as is; anything else is taken for a hub id (the reference's
+    default is ``Qwen/Qwen2.5-1.5B-Instruct``, train.py:162) and resolved to its snapshot directory
+    in the local Hugging Face cache. There is no download here: a model that is not cached is an error."""
+    if os.path.isdir(model_name_or_path):
+        return model_name_or_path
+    try:
+        from huggingface_hub import snapshot_download
+        return snapshot_download(model_name_or_path, local_files_only=True)
+    except Exception as e:
+        raise FileNotFoundError(f"{model_name_or_path!r} is neither a directory nor a model in the local Hugging Face "
+                                f"cache ({type(e).__name__}); download it first or pass a checkpoint directory") from e
+
+
 def setup_model(model_name_or_path: str, use_liger_kernels: bool = True, device=None, comm_backend: str = "auto",
                 state_dtype: Optional[torch.dtype] = None, seed: int = 0, max_tokens_per_gpu: int = 65536,
                 ops_kind: str = "auto", optim: Optional[OptimConfig] = None) -> ShardedEngine:
@@ -83,15 +97,17 @@ def setup_model(model_name_or_path: str, use_liger_kernels: bool = True, device=
         spec = model_name_or_path.split(":", 1)[1]
         cfg = get_preset(spec) if spec in PRESETS else ModelConfig.from_pretrained(os.path.dirname(spec) if spec.endswith(".json") else spec)
     else:
+        model_name_or_path = resolve_model_path(model_name_or_path)
         cfg = ModelConfig.from_pretrained(model_name_or_path)
         try:
             from transformers import AutoTokenizer
             cfg = align_model_and_tokenizer(cfg, AutoTokenizer.from_pretrained(model_name_or_path))
         except Exception as e:  # a weights-only directory is fine
             log_rank_0(f"tokenizer not loaded ({type(e).__name__}); skipping vocabulary alignment")
-    arch = (cfg.architectures or ["?"])[0]
-    if arch not in SUPPORTED_ARCHITECTURES:
-        log_rank_0(f"\033[38;2;255;255;0mWarning: Model class name: {arch} is not in the list of supported models.\033[0m")
+    # The reference only warns about unknown classes because AutoModelForCausalLM brings each model's
+    # own forward (setup_model_for_training.py:111-123). The forward and backward here are written
+    # for one block structure, so a model whose math differs is refused, not trained wrongly.
+    cfg.validate_supported()
     comm = make_comm(comm_backend, device)
     if state_dtype is None:
         hbm = torch.cuda.get_device_properties(device).total_memory if device.type == "cuda" else 1e15

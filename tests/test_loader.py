@@ -1,0 +1,156 @@
+"""Model loading against real Hugging Face directories written by ``transformers`` (CPU).
+
+For every supported family a tiny random model is saved with ``save_pretrained``, loaded through
+``trainer.setup_model`` and its logits are compared with ``AutoModelForCausalLM``'s. Also: vocabulary
+growth when the tokenizer is larger than the embedding, refusal of architectures whose math the
+hand-written block does not implement, and hub-id resolution through the local cache only.
+"""
+import json
+import os
+
+import pytest
+import torch
+
+from mini_trainer_b200.data.sampler import mb_collate_fn
+from mini_trainer_b200.models import decoder as D
+from mini_trainer_b200.models.config import ModelConfig
+from mini_trainer_b200.trainer import align_model_and_tokenizer, resolve_model_path, setup_model
+
+transformers = pytest.importorskip("transformers")
+
+COMMON = dict(vocab_size=96, hidden_size=64, intermediate_size=112, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=512)
+
+
+def _hf_dir(tmp_path, kind, **over):
+    cls = {"llama": (transformers.LlamaConfig, {}), "qwen2": (transformers.Qwen2Config, {}),
+           "mistral": (transformers.MistralConfig, {"sliding_window": None}),
+           "granite": (transformers.GraniteConfig, {"embedding_multiplier": 12.0, "residual_multiplier": 0.22,
+                                                    "attention_multiplier": 0.0625, "logits_scaling": 8.0})}[kind]
+    kw = dict(COMMON, **cls[1])
+    kw.update(over)
+    cfg = cls[0](**kw)
+    torch.manual_seed(0)
+    model = transformers.AutoModelForCausalLM.from_config(cfg).to(torch.float32)
+    path = str(tmp_path / kind)
+    model.save_pretrained(path)
+    return path, model
+
+
+def _our_logits(eng, ids):
+    mb = mb_collate_fn([{"input_ids": ids, "labels": ids, "len": len(ids), "num_loss_counted_tokens": len(ids)}], len(ids))
+    pb = D.make_packed_batch(mb, "cpu")
+    blocks = [g.layout.views(g.master) for g in eng.blocks]
+    emb = eng.embed.layout.views(eng.embed.master)["embed"]
+    head = eng.head.layout.views(eng.head.master)
+    return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb)
+
+
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite"])
+def test_setup_model_matches_transformers(tmp_path, kind):
+    path, hf = _hf_dir(tmp_path, kind)
+    eng = setup_model(path, device="cpu")
+    ids = torch.randint(0, COMMON["vocab_size"], (23,))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    mine = _our_logits(eng, ids)
+    assert torch.allclose(mine, ref, atol=2e-4, rtol=2e-4), float((mine - ref).abs().max())
+
+
+def test_granite_multipliers_reach_the_gradients(tmp_path):
+    """The hand-written backward with all four Granite scalars agrees with autograd through transformers."""
+    path, hf = _hf_dir(tmp_path, "granite")
+    eng = setup_model(path, device="cpu")
+    ids = torch.randint(0, COMMON["vocab_size"], (19,))
+    labels = ids.clone()
+    labels[:5] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 19, "num_loss_counted_tokens": 14}], 14)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 14, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 14 - float(out.loss)) < 1e-4
+    got = eng.blocks[1].layout.views(eng.blocks[1].gacc)
+    want = dict(hf.named_parameters())
+    assert torch.allclose(got["wd"], want["model.layers.1.mlp.down_proj.weight"].grad, atol=1e-5, rtol=1e-3)
+    assert torch.allclose(got["wo"], want["model.layers.1.self_attn.o_proj.weight"].grad, atol=1e-5, rtol=1e-3)
+    q = eng.cfg.q_size
+    assert torch.allclose(got["wqkv"][:q], want["model.layers.1.self_attn.q_proj.weight"].grad, atol=1e-5, rtol=1e-3)
+    emb = eng.embed.layout.views(eng.embed.gacc)["embed"]
+    assert torch.allclose(emb, want["model.embed_tokens.weight"].grad, atol=1e-5, rtol=1e-3)
+
+
+class _Tok:
+    pad_token_id, bos_token_id, eos_token_id = 3, 1, 2
+
+    def __init__(self, n):
+        self.n = n
+
+    def __len__(self):
+        return self.n
+
+
+def test_vocabulary_growth_keeps_old_rows_and_initialises_new_ones(tmp_path):
+    path, hf = _hf_dir(tmp_path, "llama")
+    cfg = ModelConfig.from_pretrained(path)
+    cfg.bos_token_id, cfg.pad_token_id = 7, None
+    cfg = align_model_and_tokenizer(cfg, _Tok(101))
+    # next multiple of 8; an id both sides define is synced, one the model leaves unset stays unset (as the reference)
+    assert cfg.vocab_size == 104 and cfg.bos_token_id == 1 and cfg.pad_token_id is None
+    from mini_trainer_b200.ckpt.hf_checkpoint import load_hf_checkpoint
+    from mini_trainer_b200.ops import get_ops
+    from mini_trainer_b200.parallel.engine import ShardedEngine
+    eng = ShardedEngine(cfg, "cpu", get_ops("cpu"))
+    load_hf_checkpoint(eng, path)
+    emb = eng.embed.layout.views(eng.embed.master)["embed"]
+    old = hf.model.embed_tokens.weight.detach()
+    assert emb.shape == (104, 64) and torch.equal(emb[:96], old)
+    assert torch.allclose(emb[96:], old.mean(0, keepdim=True).expand(8, -1), atol=1e-6)
+    lm = eng.head.layout.views(eng.head.master)["lm_head"]
+    assert torch.equal(lm[:96], hf.lm_head.weight.detach()) and lm.shape[0] == 104
+    # the old tokens' logits are unchanged by the growth
+    ids = torch.randint(0, 96, (9,))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    assert torch.allclose(_our_logits(eng, ids)[:, :96], ref, atol=2e-4, rtol=2e-4)
+
+
+@pytest.mark.parametrize("kind,over,needle", [
+    ("mistral", {"sliding_window": 64}, "sliding_window"),
+    ("llama", {"attention_bias": True}, "o_proj bias"),
+    ("llama", {"mlp_bias": True}, "mlp_bias"),
+    ("llama", {"hidden_act": "gelu"}, "hidden_act"),
+])
+def test_models_the_block_cannot_compute_are_refused(tmp_path, kind, over, needle):
+    path, _ = _hf_dir(tmp_path, kind, **over)
+    with pytest.raises(ValueError, match=needle):
+        setup_model(path, device="cpu")
+
+
+def test_unknown_architecture_is_refused(tmp_path):
+    path, _ = _hf_dir(tmp_path, "llama")
+    cfg = json.load(open(os.path.join(path, "config.json")))
+    cfg["architectures"], cfg["model_type"] = ["GemmaForCausalLM"], "gemma"
+    json.dump(cfg, open(os.path.join(path, "config.json"), "w"))
+    with pytest.raises(ValueError, match="GemmaForCausalLM"):
+        setup_model(path, device="cpu")
+
+
+def test_hub_id_resolves_through_the_local_cache_only(tmp_path, monkeypatch):
+    monkeypatch.setenv("HF_HOME", str(tmp_path / "hf_home"))
+    monkeypatch.setenv("HF_HUB_OFFLINE", "1")
+    with pytest.raises(FileNotFoundError, match="local Hugging Face cache"):
+        resolve_model_path("nobody/not-a-cached-model")
+    path, _ = _hf_dir(tmp_path, "llama")
+    assert resolve_model_path(path) == path
+
+
+def test_granite_config_round_trips_its_scalars(tmp_path):
+    path, _ = _hf_dir(tmp_path, "granite")
+    cfg = ModelConfig.from_pretrained(path)
+    assert (cfg.embedding_multiplier, cfg.residual_multiplier, cfg.attention_multiplier, cfg.logits_scaling) == (12.0, 0.22, 0.0625, 8.0)
+    out = str(tmp_path / "again.json")
+    cfg.to_json_file(out)
+    d = json.load(open(out))
+    assert d["logits_scaling"] == 8.0 and d["model_type"] == "granite"
+    llama = ModelConfig.from_pretrained(_hf_dir(tmp_path, "llama")[0]).to_hf_dict()
+    assert "logits_scaling" not in llama and "embedding_multiplier" not in llama
