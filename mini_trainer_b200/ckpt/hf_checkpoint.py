@@ -67,7 +67,7 @@ def save_hf_checkpoint(engine, save_directory: str, model_name_or_path: str | No
             files.append((tmp, list(pending.keys())))
         pending, pending_bytes = {}, 0
 
-    for name, tensor in engine.iter_hf_tensors(dtype=torch.bfloat16):
+    for name, tensor in engine.iter_hf_tensors(dtype=torch.bfloat16, host_ranks=(0,)):
         if not rank0:
             continue
         n = tensor.numel() * tensor.element_size()

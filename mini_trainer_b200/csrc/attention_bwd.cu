@@ -35,11 +35,18 @@ int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_
 constexpr int AB_B = 128;          // block edge (queries and keys)
 constexpr int AB_THREADS = 352;     // TMA warp, MMA warp, 8 softmax warps (two threads per query row), dQ reduce warp
 
-// Optional phase timestamps (clock64) of CTA 0, switched on with debug_flags bit 1: per iteration
-// 4 values from the MMA thread (start, S/dP issued, P/dS seen, late MMAs issued) and 5 from one softmax
-// thread (S/dP seen, P/dS computed, P tile free, dQ complete, dQ staged). Read back with mtb200_attn_bwd_debug_read.
+// Phase timestamps for kernel development. They exist only in a library built with
+// -DMTB200_ATTN_BWD_TIMESTAMPS (the shipped build has neither the buffer nor the stores): per
+// iteration of CTA 0, 4 clock64 values from the MMA thread (start, S/dP issued, P/dS seen, late MMAs
+// issued) and 5 from one softmax thread (S/dP seen, P/dS computed, P tile free, dQ complete, dQ
+// staged), read back with mtb200_attn_bwd_debug_read.
+#ifdef MTB200_ATTN_BWD_TIMESTAMPS
 constexpr int DBG_ITERS = 256;
 __device__ long long g_attn_bwd_dbg[DBG_ITERS * 9];
+#define MTB_STAMP(cond, it, slot) do { if ((cond) && (it) < DBG_ITERS) g_attn_bwd_dbg[(it) * 9 + (slot)] = clock64(); } while (0)
+#else
+#define MTB_STAMP(cond, it, slot) do { } while (0)
+#endif
 
 template <int D>
 struct AttBwdSmem {
@@ -63,7 +70,6 @@ struct AttBwdParams {
   int T, Hq, Hkv;
   float scale;
   int* status;
-  int debug_flags;      // bit 0: skip the dQ accumulation (timing experiments only; results are then wrong)
 };
 
 template <int D>
@@ -161,8 +167,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         if (!mbar_wait(qdo_full, it & 1, abort_flag)) { atomicExch(p.status, 23); goto done; }
         if (it > 0 && !mbar_wait(dq_read, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 24); goto done; }
         tc_fence_after();
-        const bool dbg = (p.debug_flags & 2) && blockIdx.x == 0 && it < DBG_ITERS;
-        if (dbg) g_attn_bwd_dbg[it * 9 + 0] = clock64();
+        MTB_STAMP(blockIdx.x == 0, it, 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           umma_bf16(t_s, dQk + kstep(k), dKk + kstep(k), id_nt, k != 0);
@@ -174,10 +179,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
           umma_bf16(t_dp, dDOk + kstep(k), dVk + kstep(k), id_nt, k != 0);
         }
         umma_commit(sdp_full);
-        if (dbg) g_attn_bwd_dbg[it * 9 + 1] = clock64();
+        MTB_STAMP(blockIdx.x == 0, it, 1);
         if (!mbar_wait(pds_ready, it & 1, abort_flag)) { atomicExch(p.status, 25); goto done; }
         tc_fence_after();
-        if (dbg) g_attn_bwd_dbg[it * 9 + 2] = clock64();
+        MTB_STAMP(blockIdx.x == 0, it, 2);
         // dK += dS^T Q, then dV += P^T dO  (A = [query, key] tile read MN-major, B = [query, D] tile read MN-major)
 #pragma unroll
         for (int k = 0; k < AB_B / 16; ++k)
@@ -192,7 +197,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         for (int k = 0; k < AB_B / 16; ++k)
           umma_bf16(t_s, dDSk + kstep(k), dKm + mstep(k), id_dq, k != 0);
         umma_commit(mma_done);
-        if (dbg) g_attn_bwd_dbg[it * 9 + 3] = clock64();
+        MTB_STAMP(blockIdx.x == 0, it, 3);
       }
     }
   } else if (warp == 10) {
@@ -203,25 +208,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       for (int it = 0; it < n_iters; ++it) {
         const int h = hk * G + it / per_head, i = jblk + it % per_head;
         if (!mbar_wait(stage_full, it & 1, abort_flag)) { atomicExch(p.status, 30); goto done; }
-        if (!(p.debug_flags & 1)) {
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c)
-            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
-                         ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage_a + c * 16384)), "r"(h * D + c * 32),
-                           "r"(seq_start + i * AB_B) : "memory");
-        }
+        for (int c = 0; c < D / 64; ++c)
+          asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                       ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage_a + c * 16384)), "r"(h * D + c * 32),
+                         "r"(seq_start + i * AB_B) : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         // The second half is only issued once the P tile has been read: boxes in flight together share
         // the read-out bandwidth, and the next softmax is waiting for the P tile alone.
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         mbar_arrive(stage_free);
-        if (!(p.debug_flags & 1)) {
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c)
-            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
-                         ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage_b + c * 16384)), "r"(h * D + (D / 64 + c) * 32),
-                           "r"(seq_start + i * AB_B) : "memory");
-        }
+        for (int c = 0; c < D / 64; ++c)
+          asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                       ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage_b + c * 16384)), "r"(h * D + (D / 64 + c) * 32),
+                         "r"(seq_start + i * AB_B) : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         mbar_arrive(st2_free);
@@ -242,10 +243,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       const long long tok = static_cast<long long>(seq_start) + qpos;
       const float lse2 = qok ? p.lse[static_cast<long long>(h) * p.T + tok] * 1.4426950408889634f : 0.f;
       const float delta = qok ? p.delta[static_cast<long long>(h) * p.T + tok] : 0.f;
-      const bool dbg = (p.debug_flags & 2) && blockIdx.x == 0 && it < DBG_ITERS && threadIdx.x == 64;
       if (!mbar_wait(sdp_full, it & 1, abort_flag)) { atomicExch(p.status, 26); goto done; }
       tc_fence_after();
-      if (dbg) g_attn_bwd_dbg[it * 9 + 4] = clock64();
+      MTB_STAMP(blockIdx.x == 0 && threadIdx.x == 64, it, 4);
       const bool need_mask = (i == jblk) || (k0 + AB_B > seq_len) || (i * AB_B + AB_B > seq_len);
       // this thread's 64 columns of S and dP are fetched with all four loads in flight
       uint32_t sv_[2][32], dv_[2][32];
@@ -289,9 +289,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         }
       };
       compute(0);
-      if (dbg) g_attn_bwd_dbg[it * 9 + 5] = clock64();
+      MTB_STAMP(blockIdx.x == 0 && threadIdx.x == 64, it, 5);
       if (it > 0 && !mbar_wait(stage_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 27); goto done; }
-      if (dbg) g_attn_bwd_dbg[it * 9 + 6] = clock64();
+      MTB_STAMP(blockIdx.x == 0 && threadIdx.x == 64, it, 6);
       store(0);
       compute(1);
       store(1);
@@ -303,7 +303,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       if (!mbar_wait(mma_done, it & 1, abort_flag)) { atomicExch(p.status, 28); goto done; }
       if (half == 1 && it > 0 && !mbar_wait(st2_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, 31); goto done; }
       tc_fence_after();
-      if (dbg) g_attn_bwd_dbg[it * 9 + 7] = clock64();
+      MTB_STAMP(blockIdx.x == 0 && threadIdx.x == 64, it, 7);
       uint8_t* stage = half == 0 ? smem + L::OFF_P : smem + L::OFF_ST2;
       // both loads in flight; the S columns are released as soon as the tile is in registers, so the
       // next S = Q K^T runs under the staging stores
@@ -324,7 +324,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(stage_full);
-      if (dbg) g_attn_bwd_dbg[it * 9 + 8] = clock64();
+      MTB_STAMP(blockIdx.x == 0 && threadIdx.x == 64, it, 8);
     }
     // epilogue: dK, dV (rows = keys)
     if (n_iters > 0) {
@@ -428,15 +428,18 @@ extern "C" int mtb200_attn_bwd(const void* qkv, long long ld, const void* out, l
   const long long warps = static_cast<long long>(T) * Hq;
   attn_delta_kernel<<<static_cast<int>((warps * 32 + 255) / 256), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(out), ldo, reinterpret_cast<const __nv_bfloat16*>(dout), lddo, delta, T, Hq, D);
-  AttBwdParams p{reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, lse, delta, dq_acc, plan, T, Hq, Hkv, scale, status, reserved};
+  (void)reserved;
+  AttBwdParams p{reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, lse, delta, dq_acc, plan, T, Hq, Hkv, scale, status};
   rc = D == 128 ? launch_bwd<128>(tq, tdo, tdq, p, n_items, st) : launch_bwd<64>(tq, tdo, tdq, p, n_items, st);
   if (rc) return rc;
   attn_dq_store_kernel<<<dim3(static_cast<unsigned>(T), (Hq * D / 8 + 255) / 256), 256, 0, st>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), ldq, T, Hq * D);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-// Copies the phase timestamps recorded by the last debug run (debug_flags bit 1) to the host.
+#ifdef MTB200_ATTN_BWD_TIMESTAMPS
+// Copies the phase timestamps recorded by the last launch to the host (development builds only).
 extern "C" int mtb200_attn_bwd_debug_read(long long* out, int n) {
   if (n > mtb::DBG_ITERS * 9) n = mtb::DBG_ITERS * 9;
   return cudaMemcpyFromSymbol(out, mtb::g_attn_bwd_dbg, sizeof(long long) * n) == cudaSuccess ? 0 : -1;
 }
+#endif

@@ -15,6 +15,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 import torch
 
 from .. import build as _build
+from ..utils import nvtx
 
 _LIB = None
 
@@ -93,7 +94,11 @@ class NativeOps:
         if self.profile is not None:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
+        if nvtx.ENABLED:
+            nvtx.push(tag or name)
         rc = getattr(self.lib, name)(*args)
+        if nvtx.ENABLED:
+            nvtx.pop()
         if rc != 0:
             raise RuntimeError(f"{name} failed with code {rc}")
         self.launches += n
@@ -265,7 +270,7 @@ class NativeOps:
         dq_acc = torch.zeros(T, hq * d, dtype=torch.float32, device=self.device)
         self._call("mtb200_attn_bwd", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), dout.data_ptr(),
                    dout.stride(0), dqkv.data_ptr(), dqkv.stride(0), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(),
-                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, int(os.environ.get("MTB200_ATTN_BWD_DEBUG", "0")), scale,
+                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, 0, scale,
                    self.status.data_ptr(), self._st(), n=3)
         return dqkv
 

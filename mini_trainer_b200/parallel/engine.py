@@ -36,6 +36,7 @@ import torch
 from ..models import decoder as D
 from ..models import layout as L
 from ..models.config import ModelConfig
+from ..utils import nvtx
 from .comm import LocalComm
 
 
@@ -162,6 +163,10 @@ class ShardedEngine:
         # None = derive from free device memory; 0 = recompute every block like the reference
         self.activation_budget_bytes = activation_budget_bytes
         self._oom_retries = 0
+        # Test configuration: buffers that are about to be filled by a gather or by a block's weight
+        # gradients are first filled with NaN, so data consumed before it arrived (or a gradient that
+        # was never written) shows up as NaN in the loss / norm instead of as a plausible stale value.
+        self.poison = os.environ.get("MTB200_POISON", "0") == "1" and self.param_dtype != torch.int8
 
     # ------------------------------------------------------------------------------------
     # initialisation / state exchange
@@ -220,8 +225,10 @@ class ShardedEngine:
         yield self.head, (lambda v: L.hf_tensors_of_head(cfg, v))
 
     @torch.no_grad()
-    def iter_hf_tensors(self, dtype=torch.bfloat16, source: str = "master") -> Iterator[tuple]:
-        """Yields ``(hf_name, cpu_tensor)`` group by group on every rank (collective call).
+    def iter_hf_tensors(self, dtype=torch.bfloat16, source: str = "master", host_ranks=None) -> Iterator[tuple]:
+        """Yields ``(hf_name, cpu_tensor)`` group by group on every rank (collective call). Ranks not
+        in ``host_ranks`` (default: all) take part in the gathers but get ``None`` instead of a host
+        copy, so an export in which only rank 0 writes does not convert and copy the model on every rank.
 
         Only one gathered group is alive at a time, so exporting a 70B model needs one block
         of device memory, not a full replica per rank as the reference's
@@ -235,8 +242,9 @@ class ShardedEngine:
                 full = torch.empty(grp.layout.padded_numel, dtype=src.dtype, device=self.device)
                 self.comm.all_gather(src, full)
             views = grp.layout.views(full)
+            to_host = host_ranks is None or self.rank in host_ranks
             for name, view in it(views):
-                yield name, view.to(dtype).cpu()
+                yield name, (view.to(dtype).cpu() if to_host else None)
             del full, views
 
     # ------------------------------------------------------------------------------------
@@ -254,12 +262,16 @@ class ShardedEngine:
         buf = self._pbufs[slot]
         if fused and self.fused_gather:
             _Side.wait(self._pbuf_free[slot])
+            if self.poison:
+                buf.fill_(float("nan"))
             views = grp.layout.views(buf)
             views["_gather"] = self.comm.gather_plan(grp.shard, buf, grp.layout, split_before="wgu", small_until="wqkv")
             return views, None, slot
         with self.side.run(wait_current=False):
             if self.side.cuda and self._pbuf_free[slot] is not None:
                 self.side.stream.wait_event(self._pbuf_free[slot])
+            if self.poison:
+                buf.fill_(float("nan"))
             self.comm.all_gather(grp.shard, buf)
             ev = self.side.record()
         return grp.layout.views(buf), ev, slot
@@ -280,6 +292,8 @@ class ShardedEngine:
         if self.world == 1:
             return grp.layout.views(grp.shard), grp.shard, None
         full = torch.empty(grp.layout.padded_numel, dtype=self.param_dtype, device=self.device)
+        if self.poison:
+            full.fill_(float("nan"))
         if prefetch and self.side.cuda:
             with self.side.run(wait_current=True):
                 self.comm.all_gather(grp.shard, full)
@@ -318,6 +332,9 @@ class ShardedEngine:
         self._gbuf_free[slot] = None
         if self.symmetric:
             self._timed_comm(lambda: self.comm.wait_consumed(self._gbufs[slot]))
+        if self.poison:   # only the tensors themselves: alignment gaps are never written and must stay zero
+            for view in self.blocks[i].layout.views(self._gbufs[slot]).values():
+                view.fill_(float("nan"))
         return self._gbufs[slot], slot
 
     def _root_grad_buffer(self, which: str) -> torch.Tensor:
@@ -428,6 +445,7 @@ class ShardedEngine:
         _Side.wait(head_ev)
         hg_full = self._root_grad_buffer("head")
         head_g = self.head.layout.views(hg_full)
+        nvtx.push("head")
         if tied:
             eg_full = self._root_grad_buffer("embed")
             emb_g = self.embed.layout.views(eg_full)
@@ -436,6 +454,7 @@ class ShardedEngine:
         else:
             loss, dx = D.head_forward_backward(ops, cfg, head_views, head_g, head_views["lm_head"], head_g["lm_head"],
                                                False, x, batch, grad_scale)
+        nvtx.pop()
         del x, head_views, head_full, head
         self._root_free["head"] = self._reduce(self.head, hg_full, last=last)
 
@@ -451,12 +470,15 @@ class ShardedEngine:
             g = self.blocks[i].layout.views(gbuf)
             xin, acts, attn_state = saved.pop()
             if acts is None:   # recompute the block forward (attention is skipped when its output was kept)
-                _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True, saved_attn=attn_state,
-                                             need_out=False)
-            dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq)
+                with nvtx.range(f"recompute/block{i}"):
+                    _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True, saved_attn=attn_state,
+                                                 need_out=False)
+            with nvtx.range(f"backward/block{i}"):
+                dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq)
             del acts, xin, attn_state
             self._release_pbuf(slot)
-            self._reduce(self.blocks[i], gbuf, gslot, last=last)
+            with nvtx.range(f"reduce/block{i}"):
+                self._reduce(self.blocks[i], gbuf, gslot, last=last)
 
         # ---- embedding ----
         if not tied:
@@ -492,8 +514,9 @@ class ShardedEngine:
             if i == nL - 1:   # the head's parameters arrive while the last block computes
                 head = self._gather_group(self.head, prefetch=True)
             xin = x
-            x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq,
-                                                  keep="compact" if levels[i] == 0 else False, want_attn=levels[i] == 1)
+            with nvtx.range(f"forward/block{i}"):
+                x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq,
+                                                      keep="compact" if levels[i] == 0 else False, want_attn=levels[i] == 1)
             saved.append((xin, acts, attn_state))
             if i + 1 < nL or self.world == 1:
                 self._release_pbuf(slot)
@@ -506,6 +529,10 @@ class ShardedEngine:
     @torch.no_grad()
     def optimizer_step(self, lr: float) -> torch.Tensor:
         """Global-norm clip + AdamW on the shards. Returns the pre-clip gradient norm (0-dim)."""
+        with nvtx.range("optimizer"):
+            return self._optimizer_step(lr)
+
+    def _optimizer_step(self, lr: float) -> torch.Tensor:
         if self.side.cuda:
             _Side.wait(self.side.record())   # the last reductions must have landed
         o = self.optim

@@ -47,3 +47,30 @@ def test_lr_schedule_matches_transformers_primed():
     s = LRSchedule(1.0, "constant_with_warmup", 10)
     assert abs(s.current() - 0.1) < 1e-12  # first update never runs at zero
     assert lr_factor("constant_with_warmup", 20, 10) == 1.0
+
+
+def test_nvtx_ranges_cover_the_step_phases(monkeypatch):
+    """With ranges switched on, one training step opens a range per phase (and nothing when off)."""
+    import torch
+    from mini_trainer_b200.data.sampler import mb_collate_fn
+    from mini_trainer_b200.models.config import get_preset
+    from mini_trainer_b200.ops import get_ops
+    from mini_trainer_b200.parallel.engine import ShardedEngine
+    from mini_trainer_b200.utils import nvtx
+    cfg = get_preset("tiny-qwen2")
+    eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), activation_budget_bytes=0)
+    eng.init_random(seed=0)
+    ids = torch.randint(0, cfg.vocab_size, (17,))
+    mb = mb_collate_fn([{"input_ids": ids, "labels": ids, "len": 17, "num_loss_counted_tokens": 17}], 17)
+    del nvtx._pushed[:]
+    eng.train_step([mb], 1e-4)
+    assert nvtx._pushed == []
+    nvtx.enable(True)
+    try:
+        eng.train_step([mb], 1e-4)
+    finally:
+        nvtx.enable(False)
+    names = list(nvtx._pushed)
+    for want in ("forward/block0", "forward/block1", "head", "recompute/block1", "backward/block1", "reduce/block0", "optimizer"):
+        assert want in names, (want, names)
+    assert names.index("forward/block1") < names.index("head") < names.index("backward/block1") < names.index("optimizer")
