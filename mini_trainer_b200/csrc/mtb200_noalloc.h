@@ -31,7 +31,9 @@ extern "C" {
 //   nothing. Other argument errors return -10, a failed workspace lookup -12, a launch error -5.
 // * The first call on each device looks up the workspace's device address
 //   (cudaGetSymbolAddress, with that device current). Make that first call before starting any
-//   stream capture on that device.
+//   stream capture on that device. The address is cached per device for the life of the process;
+//   after cudaDeviceReset it is stale, so do not reset a device between calls. Two threads making
+//   the first call on a device at once both look the address up and store the same value.
 // * All calls on a device share the one workspace. Each call overwrites the part it uses before
 //   reading it, so stale contents never leak into a result, but two calls whose kernels overlap on
 //   the GPU (different streams) race on it: keep calls on one stream or order them with events.

@@ -21,6 +21,13 @@ def rel_err(a, b):
     return ((a - b).norm() / (b.norm() + 1e-12)).item()
 
 
+def max_err(a, b):
+    """Largest elementwise error in units of the reference's RMS value: a handful of wrong elements in
+    a large output barely moves the Frobenius norm but shows up here."""
+    a, b = a.float(), b.float()
+    return ((a - b).abs().max() / (b.pow(2).mean().sqrt() + 1e-12)).item()
+
+
 def bf(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda") * scale).bfloat16()
 
@@ -36,7 +43,7 @@ def test_gemm_forward_layout(ops, M, N, K):
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
     ops.gemm(x, False, w, False, out, M, N, K)
     ref = x.float() @ w.float().t()
-    assert rel_err(out, ref) < 6e-3
+    assert rel_err(out, ref) < 6e-3 and max_err(out, ref) < 5e-2
     ops.check_status()
 
 
@@ -47,7 +54,7 @@ def test_gemm_dgrad_layout(ops, M, N, K):
     a, b = bf(M, K), bf(K, N, scale=0.05)
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
     ops.gemm(a, False, b, True, out, M, N, K)
-    assert rel_err(out, a.float() @ b.float()) < 6e-3
+    assert rel_err(out, a.float() @ b.float()) < 6e-3 and max_err(out, a.float() @ b.float()) < 5e-2
     ops.check_status()
 
 
@@ -60,7 +67,7 @@ def test_gemm_wgrad_layout(ops, M, N, K):
     a, b = bf(K, M), bf(K, N, scale=0.05)
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
     ops.gemm(a, True, b, True, out, M, N, K)
-    assert rel_err(out, a.float().t() @ b.float()) < 6e-3
+    assert rel_err(out, a.float().t() @ b.float()) < 6e-3 and max_err(out, a.float().t() @ b.float()) < 5e-2
     ops.check_status()
 
 
@@ -76,9 +83,30 @@ def test_gemm_epilogues(ops):
     assert rel_err(o32, x.float() @ w.float().t()) < 1e-5 + 1e-3
     ops.gemm(x, False, w, False, o32, M, N, K, residual=o32)   # accumulate in place
     assert rel_err(o32, 2 * (x.float() @ w.float().t())) < 2e-3
-    # strided output / operands (views into wider buffers)
-    wide = torch.zeros(M, N + 64, dtype=torch.bfloat16, device="cuda")
-    ops.gemm(x, False, w, False, wide[:, 32:32 + N], M, N, K) if False else None
+    # alpha scales the product before bias and residual are added
+    ops.gemm(x, False, w, False, out, M, N, K, residual=res, bias=bias, alpha=0.25)
+    assert rel_err(out, 0.25 * (x.float() @ w.float().t()) + bias.float() + res.float()) < 6e-3
+    ops.check_status()
+
+
+@pytest.mark.parametrize("two_cta", [False, True])
+def test_gemm_strided_views(ops, two_cta):
+    """Outputs, residuals and operands that are column or row slices of wider buffers, which is how
+    the engine calls the kernel (dx[a:a+n], q/k/v column blocks of the fused qkv activation)."""
+    M, N, K = 384, 520, 320
+    xw = bf(M, K + 64)
+    x = xw[:, 32:32 + K]                       # operand with a leading dimension larger than K
+    w = bf(N, K, scale=0.05)
+    ref = x.float() @ w.float().t()
+    wide = torch.full((M, N + 64), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(x, False, w, False, wide[:, 32:32 + N], M, N, K, two_cta=two_cta)
+    assert rel_err(wide[:, 32:32 + N], ref) < 6e-3 and max_err(wide[:, 32:32 + N], ref) < 5e-2
+    assert (wide[:, :32] == 7.0).all() and (wide[:, 32 + N:] == 7.0).all()      # nothing outside the view is touched
+    tall = torch.full((M + 100, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    rw = bf(M, N + 8)
+    ops.gemm(x, False, w, False, tall[50:50 + M], M, N, K, residual=rw[:, 8:], two_cta=two_cta)
+    assert rel_err(tall[50:50 + M], ref + rw[:, 8:].float()) < 6e-3
+    assert (tall[:50] == 7.0).all() and (tall[50 + M:] == 7.0).all()
     ops.check_status()
 
 
@@ -197,7 +225,79 @@ def test_optimizer_kernels(ops):
     assert torch.equal(acc, src.float())
 
 
-ATTN_CASES = [(128, 4, 1, [300, 17, 129, 1, 640]), (64, 4, 2, [128, 256, 5]), (128, 8, 2, [1000]), (128, 4, 4, [127, 128, 129])]
+ATTN_CASES = [(128, 4, 1, [300, 17, 129, 1, 640]), (64, 4, 2, [128, 256, 5]), (128, 8, 2, [1000]), (128, 4, 4, [127, 128, 129]),
+              # the GQA ratios of the benchmark models (1.5B: 6, 7B: 7, 70B: 8) and sequences of many key tiles
+              (128, 6, 1, [4097, 200]), (128, 7, 1, [513, 2050]), (128, 8, 1, [3000])]
+
+
+def _cu(lens):
+    cu_host = [0]
+    for n in lens:
+        cu_host.append(cu_host[-1] + n)
+    return cu_host, torch.tensor(cu_host, dtype=torch.int32, device="cuda")
+
+
+def _attn_ref_one_head(q, k, v, do=None):
+    """fp32 causal attention of ONE head of ONE sequence in query chunks: (out, lse[, dq, dk, dv])."""
+    n, d = q.shape
+    scale = d ** -0.5
+    out = torch.empty_like(q)
+    lse = torch.empty(n, device=q.device)
+    dq = torch.zeros_like(q) if do is not None else None
+    dk = torch.zeros_like(k) if do is not None else None
+    dv = torch.zeros_like(v) if do is not None else None
+    for a in range(0, n, 2048):
+        b = min(n, a + 2048)
+        s = (q[a:b] @ k[:b].t()) * scale
+        s = s.masked_fill(torch.arange(b, device=q.device)[None, :] > torch.arange(a, b, device=q.device)[:, None], float("-inf"))
+        l = torch.logsumexp(s, -1)
+        p = torch.exp(s - l[:, None])
+        out[a:b] = p @ v[:b]
+        lse[a:b] = l
+        if do is not None:
+            dp = do[a:b] @ v[:b].t()
+            delta = (do[a:b] * out[a:b]).sum(-1, keepdim=True)
+            ds = p * (dp - delta) * scale
+            dq[a:b] = ds @ k[:b]
+            dk[:b] += ds.t() @ q[a:b]
+            dv[:b] += p.t() @ do[a:b]
+    return out, lse, dq, dk, dv
+
+
+@pytest.mark.parametrize("n,hq,hkv", [(16384, 8, 1), (65536, 2, 1)])
+def test_attention_long_sequences(ops, n, hq, hkv):
+    """Sequences as long as the benchmark's (hundreds of key tiles per query block: the S/P double
+    buffers and the rescale path run many times) against an fp32 reference computed head by head."""
+    D = 128
+    torch.manual_seed(n)
+    qkv = bf(n, (hq + 2 * hkv) * D)
+    dout = bf(n, hq * D)
+    cu_host, cu = _cu([n])
+    out, lse = ops.attention(qkv, cu, cu_host, n, hq, hkv, D)
+    out2, lse2 = ops.attention(qkv, cu, cu_host, n, hq, hkv, D)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2)          # forward has no order-dependent accumulation
+    dqkv = ops.attention_bwd(dout, qkv, out, lse, cu, cu_host, n, hq, hkv, D)
+    ops.check_status()
+    g = hq // hkv
+    for h in (0, hq - 1):
+        hk = h // g
+        q = qkv[:, h * D:(h + 1) * D].float()
+        k = qkv[:, (hq + hk) * D:(hq + hk + 1) * D].float()
+        v = qkv[:, (hq + hkv + hk) * D:(hq + hkv + hk + 1) * D].float()
+        ro, rl, rdq, _, _ = _attn_ref_one_head(q, k, v, dout[:, h * D:(h + 1) * D].float())
+        assert rel_err(out[:, h * D:(h + 1) * D], ro) < 1e-2 and max_err(out[:, h * D:(h + 1) * D], ro) < 0.1
+        assert (lse[h] - rl).abs().max() < 2e-2
+        assert rel_err(dqkv[:, h * D:(h + 1) * D], rdq) < 2e-2
+    # dK / dV of kv head 0 sum over its whole query-head group
+    rdk = torch.zeros(n, D, device="cuda")
+    rdv = torch.zeros(n, D, device="cuda")
+    k = qkv[:, hq * D:(hq + 1) * D].float()
+    v = qkv[:, (hq + hkv) * D:(hq + hkv + 1) * D].float()
+    for h in range(g):
+        _, _, _, dk, dv = _attn_ref_one_head(qkv[:, h * D:(h + 1) * D].float(), k, v, dout[:, h * D:(h + 1) * D].float())
+        rdk += dk
+        rdv += dv
+    assert rel_err(dqkv[:, hq * D:(hq + 1) * D], rdk) < 2e-2 and rel_err(dqkv[:, (hq + hkv) * D:(hq + hkv + 1) * D], rdv) < 2e-2
 
 
 @pytest.mark.parametrize("D,hq,hkv,lens", ATTN_CASES)
@@ -212,8 +312,10 @@ def test_attention_forward(ops, D, hq, hkv, lens):
     out, lse = ops.attention(qkv, cu, cu_host, max(lens), hq, hkv, D)
     ro, rl = REF.attention(qkv.float(), cu, cu_host, max(lens), hq, hkv, D)
     ops.check_status()
-    assert rel_err(lse, rl) < 2e-3
-    assert rel_err(out, ro) < 1e-2
+    assert rel_err(lse, rl) < 2e-3 and (lse - rl).abs().max() < 2e-2
+    assert rel_err(out, ro) < 1e-2 and max_err(out, ro) < 0.1
+    out2, lse2 = ops.attention(qkv, cu, cu_host, max(lens), hq, hkv, D)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2)   # run twice: bitwise identical
 
 
 @pytest.mark.parametrize("D,hq,hkv,lens", ATTN_CASES)
@@ -234,9 +336,9 @@ def test_attention_backward(ops, D, hq, hkv, lens):
     rd = REF.attention_bwd(dout.float(), qkv.float(), ro, rl, cu, cu_host, max(lens), hq, hkv, D)
     ops.check_status()
     q_end, k_end = hq * D, (hq + hkv) * D
-    assert rel_err(dqkv[:, :q_end], rd[:, :q_end]) < 2e-2
-    assert rel_err(dqkv[:, q_end:k_end], rd[:, q_end:k_end]) < 2e-2
-    assert rel_err(dqkv[:, k_end:], rd[:, k_end:]) < 2e-2
+    assert rel_err(dqkv[:, :q_end], rd[:, :q_end]) < 2e-2 and max_err(dqkv[:, :q_end], rd[:, :q_end]) < 0.25
+    assert rel_err(dqkv[:, q_end:k_end], rd[:, q_end:k_end]) < 2e-2 and max_err(dqkv[:, q_end:k_end], rd[:, q_end:k_end]) < 0.25
+    assert rel_err(dqkv[:, k_end:], rd[:, k_end:]) < 2e-2 and max_err(dqkv[:, k_end:], rd[:, k_end:]) < 0.25
 
 
 def test_bounded_wait_expires_with_status_and_context_stays_usable(ops):

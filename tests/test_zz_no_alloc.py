@@ -36,11 +36,17 @@ def test_colsum_noalloc_matches_regular_entry_point_twice():
         rc = lib.mtb200_colsum(x.data_ptr(), x.stride(0), expect.data_ptr(), scratch.data_ptr(), T, N, stream)
         assert rc == 0
         got = torch.full((N,), float("nan"), dtype=torch.bfloat16, device="cuda")
+        # warm-up call: the first call on a device resolves the workspace address and may load the module
+        assert noalloc(x.data_ptr(), x.stride(0), got.data_ptr(), T, N, stream) == 0
+        torch.cuda.synchronize()
+        got.fill_(float("nan"))
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]     # driver-level: would also see a cudaMalloc inside the library
         rc = noalloc(x.data_ptr(), x.stride(0), got.data_ptr(), T, N, stream)
         assert rc == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
         ref = x.float().sum(0)
         err = ((got.float() - ref).norm() / ref.norm()).item()
         assert err < 6e-3, err                        # same tolerance as the bias-gradient test
@@ -52,4 +58,8 @@ def test_colsum_noalloc_rejects_sizes_beyond_its_workspace():
     N = 16384 + 2
     x = torch.zeros(4, N, dtype=torch.bfloat16, device="cuda")
     out = torch.zeros(N, dtype=torch.bfloat16, device="cuda")
-    assert noalloc(x.data_ptr(), x.stride(0), out.data_ptr(), 4, N, torch.cuda.current_stream().cuda_stream) == -11
+    st = torch.cuda.current_stream().cuda_stream
+    assert noalloc(x.data_ptr(), x.stride(0), out.data_ptr(), 4, N, st) == -11
+    # other argument errors: an odd column count, a leading dimension smaller than the row
+    assert noalloc(x.data_ptr(), x.stride(0), out.data_ptr(), 4, 513, st) == -10
+    assert noalloc(x.data_ptr(), 256, out.data_ptr(), 4, 512, st) == -10
