@@ -80,50 +80,60 @@ def main():
 
     views = lay.views(full)
     remote = (world - 1) / world
-    for stage, wname, desc in ((0, "wqkv", "qkv (gathers ln1|wqkv|wo|ln2)"), (1, "wgu", "gate_up (gathers wgu|wd)")):
-        w = views[wname]
-        N, K = w.shape
+    for two_cta in (True, False):   # CTA pairs (cta_group::2, the default for large problems) and the one-CTA kernel
+        ops.use_gemm2 = two_cta
+        kern = "2-CTA 256x256" if two_cta else "1-CTA 128x256"
+        for stage, wname, desc in ((0, "wqkv", "qkv (gathers ln1|wqkv|wo|ln2)"), (1, "wgu", "gate_up (gathers wgu|wd)")):
+            w = views[wname]
+            N, K = w.shape
 
-        def fused():
+            def fused():
+                plan = comm.gather_plan(shard, full, lay, split_before="wgu", small_until="wqkv")
+                if stage == 1:   # stage 1 expects the chunks of stage 0 to carry the epoch already
+                    plan.flags[: plan.split] = plan.epoch
+                return ops.linear(x, w, None, None, gather=(plan, stage))
+
+            probe = comm.gather_plan(shard, full, lay, split_before="wgu", small_until="wqkv")
+            if stage == 0:
+                full.zero_()
+            else:
+                full[probe.split * 65536:].zero_()   # keep what stage 0 gathered (it owns the chunk that straddles the boundary)
+            out = fused()
+            torch.cuda.synchronize()
             plan = comm.gather_plan(shard, full, lay, split_before="wgu", small_until="wqkv")
-            if stage == 1:   # stage 1 expects the chunks of stage 0 to carry the epoch already
-                plan.flags[: plan.split] = plan.epoch
-            return ops.linear(x, w, None, None, gather=(plan, stage))
+            lo, hi = (0, plan.split) if stage == 0 else (plan.split, plan.n_chunks)
+            lo_e, hi_e = lo * 65536, min(hi * 65536, lay.padded_numel)
+            ok_gather = torch.equal(full[lo_e:hi_e], ref_full[lo_e:hi_e])
+            ref = x.float() @ ref_full[lay.specs[wname].offset: lay.specs[wname].offset + N * K].view(N, K).float().t()
+            err = ((out.float() - ref).norm() / ref.norm()).item()
+            t_fused = timeit(fused)
+            t_gemm = timeit(lambda: ops.linear(x, w))
 
-        probe = comm.gather_plan(shard, full, lay, split_before="wgu", small_until="wqkv")
-        if stage == 0:
-            full.zero_()
-        else:
-            full[probe.split * 65536:].zero_()   # keep what stage 0 gathered (it owns the chunk that straddles the boundary)
-        out = fused()
-        torch.cuda.synchronize()
-        plan = comm.gather_plan(shard, full, lay, split_before="wgu", small_until="wqkv")
-        lo, hi = (0, plan.split) if stage == 0 else (plan.split, plan.n_chunks)
-        lo_e, hi_e = lo * 65536, min(hi * 65536, lay.padded_numel)
-        ok_gather = torch.equal(full[lo_e:hi_e], ref_full[lo_e:hi_e])
-        ref = x.float() @ ref_full[lay.specs[wname].offset: lay.specs[wname].offset + N * K].view(N, K).float().t()
-        err = ((out.float() - ref).norm() / ref.norm()).item()
-        t_fused = timeit(fused)
-        t_gemm = timeit(lambda: ops.linear(x, w))
+            def nccl():
+                dist.all_gather_into_tensor(full, shard)
+                return ops.linear(x, w)
+            t_nccl = timeit(nccl)
+            flops = 2.0 * tokens * N * K
+            bytes_in = (hi_e - lo_e) * 2 * remote
+            roof = max(flops / (tf_peak * 1e9), bytes_in / (NVLINK_GBS * 1e6))
+            emit(op=f"allgather+gemm {desc}", kernel=kern, world=world, tokens=tokens, ms_fused=round(t_fused, 3), ms_gemm_only=round(t_gemm, 3),
+                 ms_nccl_allgather_whole_block_plus_gemm=round(t_nccl, 3), gathered_correct=bool(ok_gather), rel_err=round(err, 5),
+                 nvlink_mb_in=round(bytes_in / 1e6, 1), roofline_ms=round(roof, 3), frac_of_roofline=f"{roof / t_fused:.3f} {tag}",
+                 exposed_comm_ms=round(max(0.0, t_fused - t_gemm), 3))
 
-        def nccl():
-            dist.all_gather_into_tensor(full, shard)
-            return ops.linear(x, w)
-        t_nccl = timeit(nccl)
-        flops = 2.0 * tokens * N * K
-        bytes_in = (hi_e - lo_e) * 2 * remote
-        roof = max(flops / (tf_peak * 1e9), bytes_in / (NVLINK_GBS * 1e6))
-        emit(op=f"allgather+gemm {desc}", world=world, tokens=tokens, ms_fused=round(t_fused, 3), ms_gemm_only=round(t_gemm, 3),
-             ms_nccl_allgather_whole_block_plus_gemm=round(t_nccl, 3), gathered_correct=bool(ok_gather), rel_err=round(err, 5),
-             nvlink_mb_in=round(bytes_in / 1e6, 1), roofline_ms=round(roof, 3), frac_of_roofline=f"{roof / t_fused:.3f} {tag}",
-             exposed_comm_ms=round(max(0.0, t_fused - t_gemm), 3))
 
+    ops.use_gemm2 = True
     # stand-alone collectives
+    full.zero_()
+    comm.all_gather(shard, full)
+    torch.cuda.synchronize()
+    ag_ok = torch.tensor([int(torch.equal(full, ref_full))], device=device)
+    dist.all_reduce(ag_ok, op=dist.ReduceOp.MIN)
     t_ag = timeit(lambda: comm.all_gather(shard, full))
     t_ag_nccl = timeit(lambda: dist.all_gather_into_tensor(full, shard))
     nbytes = lay.padded_numel * 2 * remote
     emit(op="allgather block (peer loads)", world=world, ms=round(t_ag, 3), gbs_in=round(nbytes / t_ag / 1e6, 1),
-         frac_of_nvlink=round(nbytes / t_ag / 1e6 / NVLINK_GBS, 3), ms_nccl=round(t_ag_nccl, 3))
+         frac_of_nvlink=round(nbytes / t_ag / 1e6 / NVLINK_GBS, 3), ms_nccl=round(t_ag_nccl, 3), gathered_correct=bool(ag_ok.item()))
 
     def rs():
         comm.grad_ready(gbuf)

@@ -117,6 +117,29 @@ def main():
                 o = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
                 fn = lambda: ops.gemm(x, True, w, True, o, M, N, K, two_cta=a.two_cta)
             report(f"gemm{2 if a.two_cta else 1}cta_{lay}_{M}x{N}x{K}", timeit(fn, a.iters, a.warmup, flush), flops=2.0 * M * N * K)
+    if a.op == "shapes":
+        # the GEMMs of one Llama-3.1-8B block at --tokens tokens: one-CTA kernel, CTA-pair kernel and cuBLAS (torch.matmul)
+        T, H, F, Q = min(a.tokens, 16384), 4096, 14336, 6144
+        cases = [("qkv_fwd", "nt", T, Q, H), ("gate_up_fwd", "nt", T, 2 * F, H), ("down_fwd", "nt", T, H, F), ("o_fwd", "nt", T, H, H),
+                 ("gate_up_dgrad", "nn", T, H, 2 * F), ("down_dgrad", "nn", T, F, H),
+                 ("gate_up_wgrad", "tn", 2 * F, H, T), ("down_wgrad", "tn", H, F, T), ("qkv_wgrad", "tn", Q, H, T)]
+        for name, lay, M, N, K in cases:
+            torch.cuda.empty_cache()
+            o = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            if lay == "nt":
+                x, w = bf(M, K), bf(N, K, scale=0.02)
+                lib = lambda: torch.matmul(x, w.t(), out=o)
+            elif lay == "nn":
+                x, w = bf(M, K), bf(K, N, scale=0.02)
+                lib = lambda: torch.matmul(x, w, out=o)
+            else:
+                x, w = bf(K, M), bf(K, N, scale=0.02)
+                lib = lambda: torch.matmul(x.t(), w, out=o)
+            fl = 2.0 * M * N * K
+            for two in (False, True):
+                fn = lambda: ops.gemm(x, lay == "tn", w, lay != "nt", o, M, N, K, two_cta=two)
+                report(f"{name}_{lay}_{M}x{N}x{K}_{'2cta' if two else '1cta'}", timeit(fn, a.iters, a.warmup, flush), flops=fl)
+            report(f"{name}_{lay}_{M}x{N}x{K}_cublas", timeit(lib, a.iters, a.warmup, flush), flops=fl)
     if want("attn_fwd") or want("attn_bwd"):
         lens = [int(v) for v in a.lens.split(",")]
         T = sum(lens)
@@ -153,14 +176,14 @@ def main():
                bytes_=2.0 * T * (a.hq + a.hkv) * a.d * 2)
     def op_ce():
         R, V = 2048, a.vocab
-        logits = torch.randn(R, V, device="cuda")
+        logits = torch.randn(R, V, device="cuda").bfloat16()
         tg = torch.randint(0, V, (R,), device="cuda")
         loss = torch.empty(R, device="cuda")
         dlog = torch.empty(R, V, dtype=torch.bfloat16, device="cuda")
-        fn = lambda: ops._call("mtb200_ce_fwd_bwd", logits.data_ptr(), V, tg.data_ptr(), loss.data_ptr(), dlog.data_ptr(), V, R, V,
+        fn = lambda: ops._call("mtb200_ce_fwd_bwd", logits.data_ptr(), V, 1, tg.data_ptr(), loss.data_ptr(), dlog.data_ptr(), V, R, V,
                                1.0, -100, ops._st())
-        # two passes over the fp32 logits (online max/sum, then gradient) + the bf16 gradient write
-        report(f"ce_fwd_bwd_{R}x{V}", timeit(fn, a.iters, a.warmup, flush), bytes_=R * V * (4.0 + 4.0 + 2.0))
+        # two passes over the bf16 logits (online max/sum, then gradient) + the bf16 gradient write
+        report(f"ce_fwd_bwd_{R}x{V}", timeit(fn, a.iters, a.warmup, flush), bytes_=R * V * (2.0 + 2.0 + 2.0))
     def op_linear_ce():
         T, H, V = min(a.tokens, 8192), a.hidden, a.vocab
         x, w = bf(T, H), bf(V, H, scale=0.02)

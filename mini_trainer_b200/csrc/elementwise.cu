@@ -53,30 +53,55 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 // ------------------------------------------------------------------------------ RMSNorm fwd
-// y = bf16(x * rstd) * w ; rstd saved. One block per row; the row is read twice (second read hits L1/L2).
+// y = bf16(x * rstd) * w ; rstd saved. A row is read ONCE: a group of LANES threads (one to eight
+// warps) holds it in registers, VPT 8-wide vectors per thread with all loads issued before the first
+// use, and a 256-thread block works on 256 / LANES rows at a time. One block-wide barrier per row set
+// (none when a row fits one warp).
+template <int VPT>
 __global__ void __launch_bounds__(EW_THREADS) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                                 __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
-                                                                float eps, int H) {
-  __shared__ float red[32];
-  const long long row = blockIdx.x;
+                                                                float eps, int T, int H, int lanes) {
+  __shared__ float red[EW_THREADS / 32];
+  const int rows_per_block = EW_THREADS / lanes;
+  const int sub = threadIdx.x / lanes, l = threadIdx.x % lanes;
+  const long long row = static_cast<long long>(blockIdx.x) * rows_per_block + sub;
+  const bool row_ok = row < T;
   const __nv_bfloat16* xr = x + row * H;
+  bf16x8 v[VPT];
   float ss = 0.f;
-  for (int c = threadIdx.x * 8; c < H; c += EW_THREADS * 8) {
-    bf16x8 v; v.load(xr + c);
-    float f[8]; v.to_float(f);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = (l + k * lanes) * 8;
+    if (row_ok && c < H) v[k].load(xr + c); else v[k].u = make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    float f[8]; v[k].to_float(f);
 #pragma unroll
     for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
   }
-  ss = block_sum(ss, red);
+  ss = warp_sum(ss);
+  if (lanes > 32) {   // uniform over the block
+    const int wid = threadIdx.x >> 5, wpr = lanes >> 5;
+    if ((threadIdx.x & 31) == 0) red[wid] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int k = 0; k < wpr; ++k) ss += red[sub * wpr + k];
+  }
+  if (!row_ok) return;
   const float rstd = rsqrtf(ss / H + eps);
-  if (threadIdx.x == 0) rstd_out[row] = rstd;
+  if (l == 0) rstd_out[row] = rstd;
   __nv_bfloat16* yr = y + row * H;
-  for (int c = threadIdx.x * 8; c < H; c += EW_THREADS * 8) {
-    bf16x8 v, wv; v.load(xr + c); wv.load(w + c);
-    float f[8], g[8]; v.to_float(f); wv.to_float(g);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] * rstd)) * g[i];
-    v.from_float(f); v.store(yr + c);
+  for (int k = 0; k < VPT; ++k) {
+    const int c = (l + k * lanes) * 8;
+    if (c < H) {
+      bf16x8 wv; wv.load(w + c);
+      float f[8], g[8]; v[k].to_float(f); wv.to_float(g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] * rstd)) * g[i];
+      bf16x8 o; o.from_float(f); o.store(yr + c);
+    }
   }
 }
 
@@ -159,8 +184,11 @@ __global__ void reduce_rows_kernel(const float* __restrict__ part, __nv_bfloat16
 
 // ------------------------------------------------------------------------------ RoPE
 // In place on the first n_heads (q then k) heads of each row of qkv[T, ld]. Rotate-half
-// convention: (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin), angle = fp32(pos) * inv_freq[i].
-// The angle is reduced in double precision so positions up to 2^17 stay exact.
+// convention: (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin), angle = fp32(pos) * inv_freq[i]
+// (the fp32 product and fp32 sine / cosine that the Hugging Face rotary embedding computes).
+// A thread owns 8 frequencies of one token for ROPE_HPT consecutive heads (grid.y = head groups):
+// all of its loads are issued before the first store, so a thread keeps 2 * ROPE_HPT 16-byte loads in flight.
+constexpr int ROPE_HPT = 4;
 __global__ void __launch_bounds__(EW_THREADS) rope_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos,
                                                          const float* __restrict__ inv_freq, int T, long long ld,
                                                          int n_heads, int D, float sign) {
@@ -170,25 +198,29 @@ __global__ void __launch_bounds__(EW_THREADS) rope_kernel(__nv_bfloat16* __restr
   if (gid >= static_cast<long long>(T) * vec_per_tok) return;
   const int t = static_cast<int>(gid / vec_per_tok);
   const int i0 = static_cast<int>(gid % vec_per_tok) * 8;
+  const int h0 = blockIdx.y * ROPE_HPT;
+  __nv_bfloat16* row = qkv + static_cast<long long>(t) * ld;
+  bf16x8 a[ROPE_HPT], b[ROPE_HPT];
+#pragma unroll
+  for (int j = 0; j < ROPE_HPT; ++j) {
+    if (h0 + j < n_heads) { a[j].load(row + (h0 + j) * D + i0); b[j].load(row + (h0 + j) * D + i0 + half); }
+  }
   const float p = static_cast<float>(pos[t]);
   float cs[8], sn[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float ang = p * inv_freq[i0 + i];
-    double s, c;
-    sincos(static_cast<double>(ang), &s, &c);
-    cs[i] = static_cast<float>(c);
-    sn[i] = static_cast<float>(s) * sign;
+    sincosf(p * inv_freq[i0 + i], &sn[i], &cs[i]);
+    sn[i] *= sign;
   }
-  __nv_bfloat16* row = qkv + static_cast<long long>(t) * ld;
-  for (int h = 0; h < n_heads; ++h) {
-    __nv_bfloat16* p1 = row + h * D + i0;
-    __nv_bfloat16* p2 = p1 + half;
-    bf16x8 a, b; a.load(p1); b.load(p2);
-    float x1[8], x2[8], o1[8], o2[8]; a.to_float(x1); b.to_float(x2);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { o1[i] = x1[i] * cs[i] - x2[i] * sn[i]; o2[i] = x2[i] * cs[i] + x1[i] * sn[i]; }
-    a.from_float(o1); b.from_float(o2); a.store(p1); b.store(p2);
+  for (int j = 0; j < ROPE_HPT; ++j) {
+    if (h0 + j < n_heads) {
+      float x1[8], x2[8], o1[8], o2[8]; a[j].to_float(x1); b[j].to_float(x2);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { o1[i] = x1[i] * cs[i] - x2[i] * sn[i]; o2[i] = x2[i] * cs[i] + x1[i] * sn[i]; }
+      a[j].from_float(o1); b[j].from_float(o2);
+      a[j].store(row + (h0 + j) * D + i0); b[j].store(row + (h0 + j) * D + i0 + half);
+    }
   }
 }
 
@@ -272,15 +304,27 @@ __global__ void __launch_bounds__(128) embedding_bwd_kernel(__nv_bfloat16* __res
 }
 
 // ------------------------------------------------------------------------------ cross-entropy
-// One block per row of a logits chunk (fp32 [R, V], leading dimension ld). Pass 1: online
+// One block per row of a logits chunk ([R, V] fp32 or bf16, leading dimension ld). Pass 1: online
 // max / sum-exp. Pass 2: dlogits = (softmax - onehot) * scale in bf16. Rows whose target is
-// ignore_index get zero loss and zero gradient.
-__global__ void __launch_bounds__(1024) ce_fwd_bwd_kernel(const float* __restrict__ logits, long long ld, const long long* __restrict__ targets,
-                                                         float* __restrict__ loss, __nv_bfloat16* __restrict__ dlogits, long long ldd,
+// ignore_index get zero loss and zero gradient. With bf16 logits the gradient may be written over
+// the logits (dlogits == logits): a thread reads a vector of the row before it overwrites the same
+// vector, and pass 2 starts after the block-wide reductions that end pass 1.
+template <typename LogitT>
+__device__ __forceinline__ void load8(const LogitT* p, float (&f)[8]) {
+  if constexpr (sizeof(LogitT) == 2) { bf16x8 v; v.load(reinterpret_cast<const __nv_bfloat16*>(p)); v.to_float(f); }
+  else {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+}
+
+template <typename LogitT>
+__global__ void __launch_bounds__(1024) ce_fwd_bwd_kernel(const LogitT* logits, long long ld, const long long* __restrict__ targets,
+                                                         float* __restrict__ loss, __nv_bfloat16* dlogits, long long ldd,
                                                          int V, float grad_scale, long long ignore_index) {
   __shared__ float red[32];
   const long long row = blockIdx.x;
-  const float* lr = logits + row * ld;
+  const LogitT* lr = logits + row * ld;
   __nv_bfloat16* dr = dlogits + row * ldd;
   const long long tgt = targets[row];
   if (tgt == ignore_index) {
@@ -289,23 +333,32 @@ __global__ void __launch_bounds__(1024) ce_fwd_bwd_kernel(const float* __restric
     return;
   }
   float m = -INFINITY, s = 0.f;
-  for (int c = threadIdx.x * 4; c < V; c += blockDim.x * 4) {
-    const float4 v = *reinterpret_cast<const float4*>(lr + c);
-    const float mx = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    float v[8];
+    load8(lr + c, v);
+    float mx = v[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) mx = fmaxf(mx, v[i]);
     if (mx > m) { s *= __expf(m - mx); m = mx; }
-    s += __expf(v.x - m) + __expf(v.y - m) + __expf(v.z - m) + __expf(v.w - m);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += __expf(v[i] - m);
   }
   const float gm = block_max(m, red);
   s *= __expf(m - gm);
   const float gs = block_sum(s, red);
   const float lse = gm + logf(gs);
-  if (threadIdx.x == 0) loss[row] = lse - lr[tgt];
+  if (threadIdx.x == 0) {
+    float t;
+    if constexpr (sizeof(LogitT) == 2) t = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(lr)[tgt]); else t = lr[tgt];
+    loss[row] = lse - t;
+  }
+  __syncthreads();   // the target logit has been read before any thread overwrites the row
   const float inv = grad_scale / gs;
   for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
-    const float4 a = *reinterpret_cast<const float4*>(lr + c);
-    const float4 b = *reinterpret_cast<const float4*>(lr + c + 4);
-    float o[8] = {__expf(a.x - gm) * inv, __expf(a.y - gm) * inv, __expf(a.z - gm) * inv, __expf(a.w - gm) * inv,
-                  __expf(b.x - gm) * inv, __expf(b.y - gm) * inv, __expf(b.z - gm) * inv, __expf(b.w - gm) * inv};
+    float o[8];
+    load8(lr + c, o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = __expf(o[i] - gm) * inv;
     if (tgt >= c && tgt < c + 8) o[tgt - c] -= grad_scale;
     bf16x8 ov; ov.from_float(o); ov.store(dr + c);
   }
@@ -445,8 +498,16 @@ extern "C" {
 
 int mtb200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, float eps, int T, int H, cudaStream_t st) {
   if (T <= 0) return 0;
-  if (H % 8) return -10;
-  rmsnorm_fwd_kernel<<<T, EW_THREADS, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, eps, H);
+  if (H % 8 || H > 8 * 8 * EW_THREADS) return -10;
+  // about four vectors per thread; a row is held by 32 .. 256 threads (a power of two)
+  const int vecs = H / 8;
+  int lanes = 32;
+  while (lanes < EW_THREADS && lanes * 4 < vecs) lanes *= 2;
+  const int vpt = cdiv(vecs, lanes);
+  const int blocks = cdiv(T, EW_THREADS / lanes);
+#define RF(V) rmsnorm_fwd_kernel<V><<<blocks, EW_THREADS, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, eps, T, H, lanes)
+  if (vpt <= 1) RF(1); else if (vpt <= 2) RF(2); else if (vpt <= 4) RF(4); else RF(8);
+#undef RF
   return launch_ok();
 }
 
@@ -473,7 +534,8 @@ int mtb200_rope(void* qkv, const int* pos, const float* inv_freq, int T, long lo
   if (T <= 0) return 0;
   if (D % 16 || ld % 8) return -10;
   const long long n = static_cast<long long>(T) * (D / 16);
-  rope_kernel<<<cdiv(n, EW_THREADS), EW_THREADS, 0, st>>>((bf16*)qkv, pos, inv_freq, T, ld, n_heads, D, inverse ? -1.f : 1.f);
+  rope_kernel<<<dim3(cdiv(n, EW_THREADS), cdiv(n_heads, ROPE_HPT)), EW_THREADS, 0, st>>>((bf16*)qkv, pos, inv_freq, T, ld, n_heads, D,
+                                                                                        inverse ? -1.f : 1.f);
   return launch_ok();
 }
 
@@ -513,11 +575,13 @@ int mtb200_embedding_bwd(void* dw, const long long* sorted_ids, const long long*
   return launch_ok();
 }
 
-int mtb200_ce_fwd_bwd(const float* logits, long long ld, const long long* targets, float* loss, void* dlogits, long long ldd,
-                      int R, int V, float grad_scale, long long ignore_index, cudaStream_t st) {
+// logits: [R, V] fp32, or bf16 when logits_bf16 (dlogits may then be the same buffer).
+int mtb200_ce_fwd_bwd(const void* logits, long long ld, int logits_bf16, const long long* targets, float* loss, void* dlogits,
+                      long long ldd, int R, int V, float grad_scale, long long ignore_index, cudaStream_t st) {
   if (R <= 0) return 0;
-  if (V % 8 || ld % 4 || ldd % 8) return -10;
-  ce_fwd_bwd_kernel<<<R, 1024, 0, st>>>(logits, ld, targets, loss, (bf16*)dlogits, ldd, V, grad_scale, ignore_index);
+  if (V % 8 || ld % 8 || ldd % 8) return -10;
+  if (logits_bf16) ce_fwd_bwd_kernel<bf16><<<R, 1024, 0, st>>>((const bf16*)logits, ld, targets, loss, (bf16*)dlogits, ldd, V, grad_scale, ignore_index);
+  else ce_fwd_bwd_kernel<float><<<R, 1024, 0, st>>>((const float*)logits, ld, targets, loss, (bf16*)dlogits, ldd, V, grad_scale, ignore_index);
   return launch_ok();
 }
 

@@ -12,11 +12,17 @@
 //   tempty[a]  CTA 0 only; the 8 epilogue warps of the pair arrive (CTA 1 remotely).
 // Only CTA 0's MMA thread issues tcgen05.mma; every wait is bounded as in the one-CTA kernel.
 // The two CTAs synchronise with barrier.cluster once after set-up and once before teardown.
+//
+// GATHER = true is the fused all-gather variant (see gather.cuh): both CTAs of a pair carry eight
+// gather warps and a flag checker; each CTA's checker watches the chunks under ITS half of the B
+// tile (128 weight rows, one contiguous byte range) and only that CTA's producer waits for them.
+// No load in this file is multicast: every CTA issues its own TMA loads from local memory.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "gather.cuh"
 #include "ptx.cuh"
 
 namespace mtb {
@@ -36,6 +42,7 @@ constexpr int B_BYTES = BNH * BK * 2;    // 16 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr int GROUP_M = 8;               // band of 8 pair-tiles = 2048 rows
+constexpr int GATHER_GROUP_N = 4;        // column-tiles per band in the all-gather variant
 constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address -> CTA 0
 
@@ -83,9 +90,10 @@ __device__ __forceinline__ void mbar_arrive_cta0(uint64_t* bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & PEER_MASK) : "memory");
 }
 
-template <bool A_MN, bool B_MN, bool OUT_F32>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Params p) {
+template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? THREADS + GATHER_EXTRA_THREADS : THREADS, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Params p,
+             const __grid_constant__ GatherParams g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -94,6 +102,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint32_t* verified = tmem_slot + 2;      // gather variant: tiles whose chunks under this CTA's B half have arrived
+  uint32_t* ticket_slot = tmem_slot + 3;   // gather variant: broadcast of the chunk ticket among the gather warps
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -106,6 +116,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); }
     *abort_flag = 0;
+    *verified = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -121,6 +132,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
 
   auto tile_coords = [&](int t, int& tm, int& tn) {
+    if constexpr (GATHER) {   // bands of column-tiles: the weight is consumed front to back at an even rate
+      const int band = t / (GATHER_GROUP_N * tiles_m);
+      const int first_n = band * GATHER_GROUP_N;
+      const int cols = min(GATHER_GROUP_N, tiles_n - first_n);
+      const int local = t - band * GATHER_GROUP_N * tiles_m;
+      tn = first_n + local % cols;
+      tm = local / cols;
+      return;
+    }
     const int band = t / (GROUP_M * tiles_n);
     const int first_m = band * GROUP_M;
     const int rows = min(GROUP_M, tiles_m - first_m);
@@ -132,12 +152,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (elect_one()) {
-      uint32_t it = 0;
+      uint32_t it = 0, tl = 0;
+      unsigned long long waited_ns = 0;
       for (int t = pair; t < num_tiles; t += p.num_pairs) {
         int tm, tn;
         tile_coords(t, tm, tn);
         const int row0 = tm * 2 * BM + rank * BM;        // this CTA's rows of A
         const int col0 = tn * BN + rank * BNH;           // this CTA's half of the B tile
+        if (GATHER) {
+          if (!wait_verified(verified, tl, abort_flag, waited_ns)) { *abort_flag = 1; atomicExch(p.status, 55); goto done; }
+          asm volatile("fence.proxy.async;" ::: "memory");   // peer data was written with ordinary stores, TMA reads it
+          ++tl;
+        }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -159,6 +185,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             tma_load_2d_pair(sb, &tmap_b, fb, kb * BK, col0);
           }
         }
+      }
+      if (GATHER && g.wait_ns != nullptr) {
+        atomicAdd(g.wait_ns, waited_ns);
+        atomicAdd(g.wait_ns + 1, 1ull);
       }
     }
   } else if (warp == 1) {
@@ -190,6 +220,29 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         umma2_commit_pair(&tfull_bar[acc]);
       }
     }
+  } else if (GATHER && warp == 6 + GATHER_THREADS / 32) {
+    // ------------------------------------------------------------------ flag checker (warp 14, both CTAs)
+    uint32_t tl = 0;
+    for (int t = pair; t < num_tiles; t += p.num_pairs, ++tl) {
+      int tm, tn;
+      tile_coords(t, tm, tn);
+      const int col0 = tn * BN + rank * BNH;
+      bool ok = true;
+      if (col0 < p.N) {   // rows [col0, col0 + BNH) of the K-major weight: one contiguous byte range
+        const unsigned long long lo = g.b_byte_off + static_cast<unsigned long long>(col0) * p.K * 2;
+        const int rows = min(BNH, p.N - col0);
+        ok = wait_chunks(g, lo, lo + static_cast<unsigned long long>(rows) * p.K * 2 - 1, lane, abort_flag);
+      }
+      __syncwarp();
+      if (!ok) {
+        if (lane == 0) { *abort_flag = 1; atomicExch(p.status, 55); }
+        break;
+      }
+      if (lane == 0) st_release_cta_shared(verified, tl + 1);
+    }
+  } else if (GATHER && warp >= 6) {
+    // ------------------------------------------------------------------ gather warps (6..13, both CTAs)
+    gather_chunks(g, threadIdx.x - THREADS, ticket_slot);
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
@@ -273,20 +326,22 @@ done:
   }
 }
 
-static int g_pairs = -1;   // clusters of two that can be co-resident (0: unsupported)
+static int g_pairs[2] = {-1, -1};   // clusters of two that can be co-resident (0: unsupported), plain / gather variant
 
-template <bool A_MN, bool B_MN, bool OUT_F32>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t stream) {
-  auto kern = gemm2_kernel<A_MN, B_MN, OUT_F32>;
+template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t stream, const GatherParams* gp = nullptr) {
+  auto kern = gemm2_kernel<A_MN, B_MN, OUT_F32, GATHER>;
+  constexpr int threads = GATHER ? THREADS + GATHER_EXTRA_THREADS : THREADS;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -4;
     configured = true;
   }
-  if (g_pairs < 0) {
+  int& pairs = g_pairs[GATHER ? 1 : 0];
+  if (pairs < 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2, 1, 1);
-    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
     cfg.dynamicSmemBytes = SMEM;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -295,13 +350,27 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaSt
     cfg.numAttrs = 1;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
-    g_pairs = n;
+    pairs = n;
   }
-  if (g_pairs <= 0) return -6;
+  if (pairs <= 0) return -6;
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
-  p.num_pairs = tiles < g_pairs ? tiles : g_pairs;
-  kern<<<2 * p.num_pairs, THREADS, SMEM, stream>>>(ta, tb, p);
+  // the gathering variant always uses every pair: its extra warps carry the transfer
+  p.num_pairs = (GATHER || tiles >= pairs) ? pairs : tiles;
+  static const GatherParams none{};
+  kern<<<2 * p.num_pairs, threads, SMEM, stream>>>(ta, tb, p, gp ? *gp : none);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Fused all-gather + GEMM on CTA pairs; called by mtb200_gemm_bf16_allgather.
+int launch_gather(const void* A, long long lda, void* D, long long ldd, const void* bias, int M, int N, int K,
+                  const void* w, int* status, const GatherParams& g, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, w, K, N, K, BK, BNH);
+  if (rc) return rc - 10;
+  Params p{M, N, K, D, ldd, nullptr, 0, reinterpret_cast<const __nv_bfloat16*>(bias), status, 0, 1.0f};
+  return launch<false, false, false, true>(ta, tb, p, stream, &g);
 }
 
 }  // namespace g2

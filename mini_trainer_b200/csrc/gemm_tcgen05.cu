@@ -25,6 +25,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "gather.cuh"
 #include "ptx.cuh"
 
 namespace mtb {
@@ -50,45 +51,8 @@ struct GemmParams {
   float alpha;            // the product is multiplied by alpha before bias and residual are added
 };
 
-// Fused all-gather: while the GEMM runs, eight extra warps per CTA pull this parameter group's
-// shards from every peer's symmetric arena (plain peer loads over NVLink) into the local full
-// buffer that the B tensor map points at, 128 KB chunk by chunk, and publish each finished chunk
-// in a flag array. A ninth extra warp polls the flags of the chunks under each of the CTA's B tiles
-// (one lane per chunk) and publishes a tile count in shared memory; the TMA producer only loads a
-// B tile once that count covers it. Tiles are visited in bands of GATHER_GROUP_N column-tiles.
-constexpr int GATHER_THREADS = 256;
-constexpr int GATHER_EXTRA_THREADS = GATHER_THREADS + 32;   // gather warps + one flag-checker warp
-constexpr int GATHER_UNROLL = 8;     // 16-byte peer loads in flight per gather thread
-constexpr int GATHER_CHUNK_BYTES = 128 * 1024;
-constexpr int GATHER_MAX_RANKS = 16;
-
-struct GatherParams {
-  unsigned long long peer_base[GATHER_MAX_RANKS];  // every rank's arena, as mapped here
-  unsigned long long shard_off;    // byte offset of this group's shard inside each arena
-  unsigned long long shard_bytes;  // bytes per rank
-  unsigned char* dst;              // local full buffer (world * shard_bytes)
-  unsigned int* flags;             // [n_chunks] epoch per chunk, local
-  unsigned int epoch;
-  int world;
-  int chunk_lo, chunk_hi;          // chunks this launch gathers
-  int chunk_first;                 // gather order starts here (the chunks under B), wraps inside [lo, hi)
-  unsigned long long b_byte_off;   // byte offset of B's first element inside dst
-};
-
-__device__ __forceinline__ uint32_t ld_acquire_cta_shared(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_cta_shared(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
+// The fused all-gather variant (GATHER = true) adds the gather warps and the flag checker of gather.cuh;
+// its tiles are visited in bands of GATHER_GROUP_N column-tiles.
 template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false>
 __global__ void __launch_bounds__(GATHER ? GEMM_THREADS + GATHER_EXTRA_THREADS : GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p,
@@ -102,6 +66,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* verified = tmem_slot + 2;   // gather variant: tiles of this CTA whose weight chunks have all arrived
+  uint32_t* ticket_slot = tmem_slot + 3;   // gather variant: broadcast of the chunk ticket among the gather warps
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
@@ -148,15 +113,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       uint32_t it = 0, tl = 0;
+      unsigned long long waited_ns = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         int tm, tn;
         tile_coords(t, tm, tn);
         if (GATHER) {
           // the checker warp has seen the flags of every chunk under this tile's B rows
-          uint32_t spins = 0;
-          while (ld_acquire_cta_shared(verified) <= tl) {
-            if (++spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; atomicExch(p.status, 5); goto done; }
-          }
+          if (!wait_verified(verified, tl, abort_flag, waited_ns)) { *abort_flag = 1; atomicExch(p.status, 5); goto done; }
           asm volatile("fence.proxy.async;" ::: "memory");   // peer data was written with ordinary stores, TMA reads it
           ++tl;
         }
@@ -180,6 +143,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tma_load_2d(sb, &tmap_b, &full_bar[s], kb * BK, tn * BN);
           }
         }
+      }
+      if (GATHER && g.wait_ns != nullptr) {   // exposed-communication accounting: how long this producer starved
+        atomicAdd(g.wait_ns, waited_ns);
+        atomicAdd(g.wait_ns + 1, 1ull);
       }
     }
   } else if (warp == 1) {
@@ -213,9 +180,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (GATHER && warp == 6 + GATHER_THREADS / 32) {
     // ------------------------------------------------------------------ flag checker (warp 14)
-    // Runs ahead of the TMA producer: for each of this CTA's tiles, its lanes poll the flags of the
-    // chunks under the tile's B rows in parallel, then publish the tile count in shared memory. The
-    // producer thread therefore never waits on a chain of dependent global loads.
+    // Runs ahead of the TMA producer, so the producer thread never waits on a chain of dependent global loads.
     uint32_t tl = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tl) {
       int tm, tn;
@@ -224,22 +189,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const unsigned long long lo = g.b_byte_off + static_cast<unsigned long long>(tn) * BN * p.K * 2;
       const int rows = min(BN, p.N - tn * BN);
       const unsigned long long hi = lo + static_cast<unsigned long long>(rows) * p.K * 2 - 1;
-      const int c_hi = static_cast<int>(hi / GATHER_CHUNK_BYTES);
-      bool failed = false;
-      for (int c0 = static_cast<int>(lo / GATHER_CHUNK_BYTES); c0 <= c_hi && !failed; c0 += 32) {
-        const int c = c0 + lane;
-        bool ok = c > c_hi;
-        uint32_t spins = 0;
-        while (true) {
-          if (!ok) ok = ld_acquire_gpu(g.flags + c) == g.epoch;
-          if (__all_sync(0xffffffffu, ok)) break;
-          ++spins;
-          const bool stop = spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag);
-          if (__any_sync(0xffffffffu, stop)) { failed = true; break; }
-        }
-      }
+      const bool ok = wait_chunks(g, lo, hi, lane, abort_flag);
       __syncwarp();
-      if (failed) {
+      if (!ok) {
         if (lane == 0) { *abort_flag = 1; atomicExch(p.status, 5); }
         break;
       }
@@ -247,40 +199,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (GATHER && warp >= 6) {
     // ------------------------------------------------------------------ gather warps (6..13)
-    const int gt = threadIdx.x - GEMM_THREADS;
-    const int n_chunks = g.chunk_hi - g.chunk_lo;
-    const unsigned long long total = g.shard_bytes * g.world;
-    const unsigned long long vec_per_shard = g.shard_bytes >> 4;
-    for (int k = blockIdx.x; k < n_chunks; k += gridDim.x) {
-      int c = g.chunk_first + k;
-      if (c >= g.chunk_hi) c -= n_chunks;
-      const unsigned long long b0 = static_cast<unsigned long long>(c) * GATHER_CHUNK_BYTES;
-      const unsigned long long b1 = min(b0 + GATHER_CHUNK_BYTES, total);
-      const unsigned long long v0 = b0 >> 4, nv = (b1 - b0) >> 4;
-      uint4* dst = reinterpret_cast<uint4*>(g.dst) + v0;
-      // a chunk lies in one peer's shard, or straddles one boundary (shards are larger than a chunk);
-      // the peer is resolved once per chunk, not per vector
-      const unsigned long long pr0 = v0 / vec_per_shard;
-      const unsigned long long first = min(nv, (pr0 + 1) * vec_per_shard - v0);   // vectors that belong to peer pr0
-      const uint4* src0 = reinterpret_cast<const uint4*>(g.peer_base[pr0] + g.shard_off) + (v0 - pr0 * vec_per_shard);
-      const uint4* src1 = first < nv ? reinterpret_cast<const uint4*>(g.peer_base[pr0 + 1] + g.shard_off) - first : src0;
-      for (unsigned long long j = gt; j < nv; j += GATHER_UNROLL * GATHER_THREADS) {
-        uint4 v[GATHER_UNROLL];
-#pragma unroll
-        for (int u = 0; u < GATHER_UNROLL; ++u) {
-          const unsigned long long jj = j + u * GATHER_THREADS;
-          if (jj < nv) v[u] = jj < first ? src0[jj] : src1[jj];
-        }
-#pragma unroll
-        for (int u = 0; u < GATHER_UNROLL; ++u) {
-          const unsigned long long jj = j + u * GATHER_THREADS;
-          if (jj < nv) dst[jj] = v[u];
-        }
-      }
-      __threadfence();
-      asm volatile("bar.sync 1, %0;" ::"n"(GATHER_THREADS) : "memory");
-      if (gt == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.flags + c), "r"(g.epoch) : "memory");
-    }
+    gather_chunks(g, threadIdx.x - GEMM_THREADS, ticket_slot);
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -418,6 +337,11 @@ int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_
 
 static int g_num_sms = 0;
 
+namespace g2 {
+int launch_gather(const void* A, long long lda, void* D, long long ldd, const void* bias, int M, int N, int K,
+                  const void* w, int* status, const GatherParams& g, cudaStream_t stream);
+}
+
 template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream,
                   const GatherParams* gp = nullptr) {
@@ -483,11 +407,15 @@ int mtb200_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long
 //   full              local destination (world * shard_bytes); w_byte_off = offset of W inside it
 //   flags/epoch       per-chunk (128 KB) completion words; a chunk is ready when its word == epoch
 //   chunk_lo/chunk_hi chunks gathered by this launch (others must already carry `epoch`)
+//   ticket            device word used to hand chunks out to whichever CTAs are resident (zeroed here)
+//   wait_ns           optional device [2] counters: producer wait time summed over CTAs, CTA count
+//   two_cta           run on CTA pairs (cta_group::2, 256 x 256 tiles) when the device can schedule them
 // bias, if given, must lie in an already gathered part of `full` (or elsewhere).
 int mtb200_gemm_bf16_allgather(const void* A, long long lda, void* D, long long ldd, const void* bias, int M, int N, int K,
                                const unsigned long long* bases, int world, unsigned long long shard_off,
                                unsigned long long shard_bytes, void* full, unsigned long long w_byte_off, unsigned int* flags,
-                               unsigned int epoch, int chunk_lo, int chunk_hi, int* status, cudaStream_t stream) {
+                               unsigned int epoch, int chunk_lo, int chunk_hi, unsigned int* ticket, unsigned long long* wait_ns,
+                               int two_cta, int* status, cudaStream_t stream) {
   using namespace mtb;
   if (M <= 0 || N <= 0 || K <= 0) return -10;
   if (N % 8 || ldd % 8 || K % 8 || world < 1 || world > GATHER_MAX_RANKS || shard_bytes % 16 || w_byte_off % 16) return -10;
@@ -502,9 +430,16 @@ int mtb200_gemm_bf16_allgather(const void* A, long long lda, void* D, long long 
   for (int i = 0; i < world; ++i) g.peer_base[i] = bases[i];
   g.shard_off = shard_off; g.shard_bytes = shard_bytes; g.dst = reinterpret_cast<unsigned char*>(full);
   g.flags = flags; g.epoch = epoch; g.world = world; g.chunk_lo = chunk_lo; g.chunk_hi = chunk_hi;
+  g.ticket = ticket; g.wait_ns = wait_ns;
   g.b_byte_off = w_byte_off;
   int first = static_cast<int>(w_byte_off / GATHER_CHUNK_BYTES);
   g.chunk_first = first < chunk_lo ? chunk_lo : (first >= chunk_hi ? chunk_lo : first);
+  if (ticket == nullptr) return -10;
+  if (cudaMemsetAsync(ticket, 0, sizeof(unsigned int), stream) != cudaSuccess) return -5;   // chunk tickets start at 0 in every launch
+  if (two_cta) {
+    rc = g2::launch_gather(A, lda, D, ldd, bias, M, N, K, reinterpret_cast<const unsigned char*>(full) + w_byte_off, status, g, stream);
+    if (rc != -6) return rc;   // -6: CTA pairs cannot be scheduled here; fall through to the one-CTA kernel
+  }
   return launch<false, false, false, true>(ta, tb, p, stream, &g);
 }
 

@@ -54,7 +54,7 @@ class _Sig:
     mtb200_swiglu_bwd_act = [P, P, P, L, I, P]
     mtb200_embedding_fwd = [P, P, P, I, I, P]
     mtb200_embedding_bwd = [P, P, P, P, I, I, P]
-    mtb200_ce_fwd_bwd = [P, L, P, P, P, L, I, I, F, L, P]
+    mtb200_ce_fwd_bwd = [P, L, I, P, P, P, L, I, I, F, L, P]
     mtb200_colsum = [P, L, P, P, I, I, P]
     mtb200_accumulate = [P, P, L, I, I, P]
     mtb200_f32_to_bf16 = [P, P, L, I, P]
@@ -71,7 +71,7 @@ def _ptr(t):
 class NativeOps:
     name = "native"
 
-    def __init__(self, device, ce_chunk: int = 4096, attention: str | None = None):
+    def __init__(self, device, ce_chunk: int = 8192, attention: str | None = None):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("NativeOps needs a CUDA device")
@@ -79,8 +79,9 @@ class NativeOps:
         self.ce_chunk = ce_chunk
         self.attention_impl = attention or os.environ.get("MTB200_ATTENTION", "native")
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        # two-CTA (cta_group::2) GEMM tiles for problems with at least a full wave of 256x256 tiles
-        self.use_gemm2 = os.environ.get("MTB200_GEMM2", "0") == "1"
+        # two-CTA (cta_group::2, 256x256 tiles) GEMM for problems with about a full wave of such tiles or more;
+        # MTB200_GEMM2=0 forces the one-CTA 128x256 kernel everywhere (A/B comparisons)
+        self.use_gemm2 = os.environ.get("MTB200_GEMM2", "1") == "1"
         self.launches = 0
         self.profile = [] if os.environ.get("MTB200_PROFILE") else None
         self._scratch = {}
@@ -324,25 +325,26 @@ class NativeOps:
 
     # -- fused linear + cross-entropy ---------------------------------------------------
     def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100, logit_scale=1.0):
-        """Per-token CE of ``logit_scale * x @ w.T``. Chunked over tokens: logits chunk (fp32) -> per-row softmax statistics, loss and bf16
-        dlogits -> dX chunk and dW accumulation, all with the tcgen05 GEMM. Only ``[chunk, V]``
-        logits ever exist. dW is accumulated in fp32 and rounded to bf16 once at the end."""
+        """Per-token CE of ``logit_scale * x @ w.T``. Chunked over tokens (8192 rows): bf16 logits chunk
+        by the tcgen05 GEMM (fp32 accumulation, one rounding: what the reference's fused linear-CE holds
+        too) -> per-row softmax statistics, loss and the bf16 gradient written over the logits -> dX
+        chunk and dW accumulation, again on the tcgen05 GEMM. Only ``[chunk, V]`` logits ever exist.
+        dW is accumulated in fp32 and rounded to bf16 once at the end."""
         T, H = x.shape
         V = w.shape[0]
         loss = torch.empty(T, dtype=torch.float32, device=self.device)
         dx = torch.empty_like(x)
         ck = min(self.ce_chunk, T)
-        logits = self._buf("ce_logits", ck * V, torch.float32).view(ck, V)
-        dlog = self._buf("ce_dlogits", ck * V, torch.bfloat16).view(ck, V)
+        logits = self._buf("ce_logits", ck * V, torch.bfloat16).view(ck, V)
         dw32 = self._buf("ce_dw", V * H, torch.float32).view(V, H)
         first = True
         for a in range(0, T, ck):
             n = min(ck, T - a)
             self.gemm(x[a:a + n], False, w, False, logits, n, V, H, alpha=logit_scale)
-            self._call("mtb200_ce_fwd_bwd", logits.data_ptr(), V, targets[a:a + n].data_ptr(), loss[a:a + n].data_ptr(),
-                       dlog.data_ptr(), V, n, V, float(grad_scale), ignore_index, self._st())
-            self.gemm(dlog, False, w, True, dx[a:a + n], n, H, V, alpha=logit_scale)
-            self.gemm(dlog, True, x[a:a + n], True, dw32, V, H, n, residual=None if first else dw32, alpha=logit_scale)
+            self._call("mtb200_ce_fwd_bwd", logits.data_ptr(), V, 1, targets[a:a + n].data_ptr(), loss[a:a + n].data_ptr(),
+                       logits.data_ptr(), V, n, V, float(grad_scale), ignore_index, self._st())
+            self.gemm(logits, False, w, True, dx[a:a + n], n, H, V, alpha=logit_scale)
+            self.gemm(logits, True, x[a:a + n], True, dw32, V, H, n, residual=None if first else dw32, alpha=logit_scale)
             first = False
         self._call("mtb200_f32_to_bf16", dw_out.data_ptr(), dw32.data_ptr(), V * H, int(accumulate_dw), self._st())
         return loss, dx

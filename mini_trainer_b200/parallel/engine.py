@@ -400,7 +400,7 @@ class ShardedEngine:
         h, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
         base = tokens * 2 * h * len(self.blocks)
         work = tokens * 2 * (7 * h + cfg.qkv_size + 6 * f)
-        ce = getattr(self.ops, "ce_chunk", 2048) * v * 6 + v * h * 4
+        ce = getattr(self.ops, "ce_chunk", 2048) * v * 2 + v * h * 4
         root = 4 * v * h * 2
         bufs = sum(b.numel() * b.element_size() for b in self._pbufs + self._gbufs)
         transient = base + work + ce + root

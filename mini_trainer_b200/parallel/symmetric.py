@@ -66,7 +66,7 @@ class SymmetricComm:
         P, I, L, U, UL = c_void_p, c_int, c_longlong, c_uint, c_ulonglong
         sig = {
             "mtb200_symm_allgather": [P, I, UL, UL, P, UL, UL, I, P],
-            "mtb200_gemm_bf16_allgather": [P, L, P, L, P, I, I, I, P, I, UL, UL, P, UL, P, U, I, I, P, P],
+            "mtb200_gemm_bf16_allgather": [P, L, P, L, P, I, I, I, P, I, UL, UL, P, UL, P, U, I, I, P, P, I, P, P],
             "mtb200_symm_signal": [P, I, I, UL, U, P],
             "mtb200_symm_wait": [P, I, U, U, I, P, P],
             "mtb200_symm_reduce_scatter": [P, I, I, UL, L, P, I, P, P, UL, U, U, P, P, I, P],
@@ -98,6 +98,9 @@ class SymmetricComm:
         # flag rows: ready[ch][r], consumed[ch][r] (uint32) and vals[ch][r] (fp32 payload for scalar all-reduce)
         self._flags = self.alloc(MAX_CHANNELS * 3 * MAX_RANKS, torch.int32)
         self._counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._ticket = torch.zeros(1, dtype=torch.int32, device=self.device)       # chunk tickets of the fused gather
+        self._gather_wait = torch.zeros(2, dtype=torch.int64, device=self.device)  # producer wait (ns) summed over CTAs, CTA count
+        self._gather_launches = 0
         self._barrier_ch = self._new_channel("barrier")
         self._scalar_ch = [self._new_channel("scalar0"), self._new_channel("scalar1")]
         self._scalar_calls = 0
@@ -197,6 +200,17 @@ class SymmetricComm:
                    self.flag_spin_limit, vec.data_ptr(), self.status.data_ptr(), self._st())
         return vec
 
+    def take_gather_wait_ms(self) -> float:
+        """Time the TMA producers of the fused all-gather GEMMs spent waiting for weight chunks since
+        the last call: mean over the CTAs of each launch, summed over launches (one host sync)."""
+        ns, ctas = (int(x) for x in self._gather_wait.tolist())
+        launches = self._gather_launches
+        self._gather_wait.zero_()
+        self._gather_launches = 0
+        if not ctas or not launches:
+            return 0.0
+        return ns / (ctas / launches) / 1e6
+
     def check_status(self):
         code = int(self.status.item())
         if code:
@@ -247,9 +261,11 @@ class GatherPlan:
         rc = c.lib.mtb200_gemm_bf16_allgather(
             x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), None if bias is None else bias.data_ptr(), M, N, K,
             c._bases, c.world, c._offset(self.shard), self.shard.numel() * self.shard.element_size(), self.full.data_ptr(),
-            w.data_ptr() - self.full.data_ptr(), self.flags.data_ptr(), self.epoch, lo, hi, ops.status.data_ptr(), ops._st())
+            w.data_ptr() - self.full.data_ptr(), self.flags.data_ptr(), self.epoch, lo, hi, c._ticket.data_ptr(),
+            c._gather_wait.data_ptr(), int(getattr(ops, "use_gemm2", False) and M >= 4096), ops.status.data_ptr(), ops._st())
         if rc != 0:
             raise RuntimeError(f"mtb200_gemm_bf16_allgather failed with code {rc}")
         ops.launches += 1
         c.launches += 1
+        c._gather_launches += 1
         return out

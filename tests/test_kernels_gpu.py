@@ -387,6 +387,12 @@ def test_gemm_two_cta(ops, M, N, K, layout):
     if layout == "nt":
         ops.gemm(a, False, b, False, out, M, N, K, residual=res, bias=bias, two_cta=True)
         assert rel_err(out, ref + res.float() + bias.float()) < 6e-3
+    # fp32 output accumulated in place (the form the linear+CE weight gradient uses), scaled product
+    o32 = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        ops.gemm(a, layout == "tn", b, layout != "nt", o32, M, N, K, residual=o32, two_cta=True, alpha=0.5)
+    assert rel_err(o32, ref) < 2e-3 and max_err(o32, ref) < 2e-2
+    ops.check_status()
 
 
 def test_osft_projection_on_tcgen05_gemm(ops):
