@@ -150,7 +150,7 @@ def main():
     acc.zero_(); rs(); torch.cuda.synchronize(); dist.barrier()
     dist.reduce_scatter_tensor(tmp, gbuf)
     rs_err = ((acc - tmp.float()).norm() / tmp.float().norm()).item()
-    emit(op="reduce-scatter block + fp32 accumulate + sumsq (peer loads, flags)", world=world, ms=round(t_rs, 3),
+    emit(op="reduce-scatter block + fp32 accumulate + sumsq " + ("(multimem.ld_reduce in NVSwitch, flags)" if comm.nvls else "(peer loads, flags)"), world=world, ms=round(t_rs, 3),
          gbs_in=round(nbytes / t_rs / 1e6, 1), frac_of_nvlink=round(nbytes / t_rs / 1e6 / NVLINK_GBS, 3),
          ms_nccl_reduce_scatter_plus_torch_ops=round(t_rs_nccl, 3), rel_err_vs_nccl=round(rs_err, 5))
     ops.check_status(); comm.check_status()

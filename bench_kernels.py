@@ -50,6 +50,29 @@ def timeit(fn, iters, warmup, flush=None):
     return total / iters
 
 
+def sustained(fn, seconds):
+    """Mean time per call (ms) over back-to-back calls for ``seconds`` of device time, measured on the
+    second half only: the regime of a long training step, where the 1000 W power cap, not the burst
+    clock, sets the pace. Returns (ms per call, median SM MHz over the measured half)."""
+    import subprocess
+    fn(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+    n = max(4, int(seconds * 1e3 / max(e0.elapsed_time(e1), 1e-3)))
+    for _ in range(n // 2):
+        fn()
+    smi = subprocess.Popen(["nvidia-smi", "--query-gpu=clocks.sm", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                            str(torch.cuda.current_device())], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    e0.record()
+    for _ in range(n - n // 2):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    smi.terminate()
+    mhz = sorted(float(x) for x in smi.stdout.read().split() if x.strip().replace(".", "").isdigit())
+    return e0.elapsed_time(e1) / (n - n // 2), (mhz[len(mhz) // 2] if mhz else None)
+
+
 def bf(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda") * scale).bfloat16()
 
@@ -73,6 +96,8 @@ def main():
     ap.add_argument("--adamw-n", type=int, default=512 * 1024 * 1024, help="elements of the AdamW shard (14 bytes each with fp32 moments)")
     ap.add_argument("--ce-chunk", type=int, default=0, help="token rows per linear+CE chunk (0 = library default)")
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--sustain", type=float, default=0.0, help="--op shapes: also run every kernel back to back for this many "
+                    "seconds and report the throughput under the power cap")
     ap.add_argument("--two-cta", action="store_true", help="use the cta_group::2 GEMM kernel (256x256 tiles per CTA pair)")
     a = ap.parse_args()
     ops = NativeOps("cuda:0")
@@ -136,10 +161,15 @@ def main():
                 x, w = bf(K, M), bf(K, N, scale=0.02)
                 lib = lambda: torch.matmul(x.t(), w, out=o)
             fl = 2.0 * M * N * K
-            for two in (False, True):
-                fn = lambda: ops.gemm(x, lay == "tn", w, lay != "nt", o, M, N, K, two_cta=two)
-                report(f"{name}_{lay}_{M}x{N}x{K}_{'2cta' if two else '1cta'}", timeit(fn, a.iters, a.warmup, flush), flops=fl)
-            report(f"{name}_{lay}_{M}x{N}x{K}_cublas", timeit(lib, a.iters, a.warmup, flush), flops=fl)
+            variants = [("1cta", lambda: ops.gemm(x, lay == "tn", w, lay != "nt", o, M, N, K, two_cta=False)),
+                        ("2cta", lambda: ops.gemm(x, lay == "tn", w, lay != "nt", o, M, N, K, two_cta=True)), ("cublas", lib)]
+            for vname, fn in variants:
+                report(f"{name}_{lay}_{M}x{N}x{K}_{vname}", timeit(fn, a.iters, a.warmup, flush), flops=fl)
+                if a.sustain > 0:
+                    ms, mhz = sustained(fn, a.sustain)
+                    rec = {"op": f"{name}_{lay}_{M}x{N}x{K}_{vname}_sustained", "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+                           "sm_mhz_median": mhz}
+                    print(json.dumps(rec), flush=True)
     if want("attn_fwd") or want("attn_bwd"):
         lens = [int(v) for v in a.lens.split(",")]
         T = sum(lens)

@@ -93,10 +93,14 @@ __global__ void symm_wait_kernel(const uint32_t* __restrict__ my_flags, int worl
 }
 
 // ---------------------------------------------------------------------------------- reduce-scatter
-// acc[i] (+)= sum_p bf16 grad_p[rank * n + i]; optional sumsq of the result. After all blocks have
-// read, the last one signals "consumed" (epoch) to every peer.
+// acc[i] (+)= sum_p bf16 grad_p[start + i] for i < n; optional sumsq of the result. `start` is where
+// this rank's part of the region being reduced begins inside every rank's gradient buffer (the whole
+// slice of the rank, or its intersection with one tensor region when the reduction follows backward
+// tensor by tensor). n may be 0 (the region does not touch this rank's slice): nothing is read, but the
+// kernel still takes part in the handshake. After all blocks have read, the last one signals
+// "consumed" (epoch) to every peer.
 template <int MAXW>   // compile-time bound on the rank count keeps the per-peer vectors in registers
-__global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable peers, unsigned long long grad_off, long long n,
+__global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable peers, unsigned long long grad_off, long long start, long long n,
                                                                  float* __restrict__ acc, int accumulate, float* __restrict__ sumsq,
                                                                  const uint32_t* __restrict__ ready_flags, unsigned long long consumed_off,
                                                                  uint32_t epoch, uint32_t limit, int rank, int world,
@@ -105,7 +109,7 @@ __global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable peer
   __shared__ float red[32];
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
-  if (threadIdx.x < world && !wait_flag(ready_flags + threadIdx.x, epoch, limit)) {
+  if (n > 0 && threadIdx.x < world && !wait_flag(ready_flags + threadIdx.x, epoch, limit)) {
     ok_s = 0;
     atomicExch(status, 41 | (threadIdx.x << 8));
   }
@@ -113,7 +117,7 @@ __global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable peer
   float ss = 0.f;
   if (ok_s) {
     const long long nvec = n >> 3;
-    const unsigned long long slice_off = grad_off + static_cast<unsigned long long>(rank) * n * 2;
+    const unsigned long long slice_off = grad_off + static_cast<unsigned long long>(start) * 2;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     // two independent vectors per thread and iteration: 2 x world peer loads in flight
     for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += 2 * stride) {
@@ -163,6 +167,84 @@ __global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable peer
     }
   }
   // last block out tells every peer that its buffer has been consumed by this rank
+  __threadfence();
+  __syncthreads();
+  __shared__ int last_s;
+  if (threadIdx.x == 0) last_s = (atomicAdd(block_counter, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (last_s) {
+    if (threadIdx.x == 0) *block_counter = 0;
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(peers.base[threadIdx.x] + consumed_off) + rank, epoch);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------- reduce-scatter through NVSwitch
+// Same contract and handshake as symm_reduce_scatter_kernel, but the sum over ranks is formed INSIDE
+// the switch: one multimem.ld_reduce on the arena's multicast address returns, for 8 consecutive bf16
+// gradients, the sum of all ranks' copies (accumulated in fp32 by the switch, delivered as bf16), so a
+// rank receives 1/world of the bytes the peer-load version pulls. Only usable when the arena is bound
+// to a multicast object (opt-in: a rank that dies while bound can fault its peers' GPUs).
+__global__ void __launch_bounds__(512) symm_reduce_scatter_nvls_kernel(unsigned long long mc_base, PeerTable peers, unsigned long long grad_off,
+                                                                      long long start, long long n, float* __restrict__ acc, int accumulate,
+                                                                      float* __restrict__ sumsq, const uint32_t* __restrict__ ready_flags,
+                                                                      unsigned long long consumed_off, uint32_t epoch, uint32_t limit, int rank,
+                                                                      int world, unsigned int* __restrict__ block_counter, int* status) {
+  __shared__ int ok_s;
+  __shared__ float red[32];
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (n > 0 && threadIdx.x < world && !wait_flag(ready_flags + threadIdx.x, epoch, limit)) {
+    ok_s = 0;
+    atomicExch(status, 45 | (threadIdx.x << 8));
+  }
+  __syncthreads();
+  float ss = 0.f;
+  if (ok_s) {
+    const long long nvec = n >> 3;
+    const unsigned long long src = mc_base + grad_off + static_cast<unsigned long long>(start) * 2;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec)
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + static_cast<unsigned long long>(i) * 16) : "memory");
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= nvec) continue;
+        const float2 a = unpack_bf16(v[u].x), b = unpack_bf16(v[u].y), c = unpack_bf16(v[u].z), d = unpack_bf16(v[u].w);
+        float f[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+        float4* dst = reinterpret_cast<float4*>(acc) + 2 * i;
+        if (accumulate) {
+          const float4 p0 = dst[0], p1 = dst[1];
+          f[0] += p0.x; f[1] += p0.y; f[2] += p0.z; f[3] += p0.w; f[4] += p1.x; f[5] += p1.y; f[6] += p1.z; f[7] += p1.w;
+        }
+        dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+        dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+        if (sumsq != nullptr) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) ss += f[k] * f[k];
+        }
+      }
+    }
+  }
+  if (sumsq != nullptr) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+      t = warp_sum(t);
+      if (threadIdx.x == 0) atomicAdd(sumsq, t);
+    }
+  }
   __threadfence();
   __syncthreads();
   __shared__ int last_s;
@@ -240,17 +322,33 @@ int mtb200_symm_wait(const void* my_flags, int world, unsigned int epoch, unsign
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-int mtb200_symm_reduce_scatter(const unsigned long long* bases, int world, int rank, unsigned long long grad_off, long long n,
-                               float* acc, int accumulate, float* sumsq, const void* ready_flags, unsigned long long consumed_off,
-                               unsigned int epoch, unsigned int limit, unsigned int* block_counter, int* status, int blocks,
-                               cudaStream_t st) {
-  if (world < 1 || world > MAX_RANKS || n % 8 || grad_off % 16) return -10;
+int mtb200_symm_reduce_scatter(const unsigned long long* bases, int world, int rank, unsigned long long grad_off, long long start,
+                               long long n, float* acc, int accumulate, float* sumsq, const void* ready_flags,
+                               unsigned long long consumed_off, unsigned int epoch, unsigned int limit, unsigned int* block_counter,
+                               int* status, int blocks, cudaStream_t st) {
+  if (world < 1 || world > MAX_RANKS || n < 0 || n % 8 || start % 8 || grad_off % 16) return -10;
+  if (n == 0) blocks = 1;
+  else if (blocks > (n / 8 + 511) / 512) blocks = static_cast<int>((n / 8 + 511) / 512);
 #define MTB_RS(W)                                                                                                       \
-  symm_reduce_scatter_kernel<W><<<blocks, 512, 0, st>>>(make_table(bases, world), grad_off, n, acc, accumulate, sumsq,    \
+  symm_reduce_scatter_kernel<W><<<blocks, 512, 0, st>>>(make_table(bases, world), grad_off, start, n, acc, accumulate, sumsq, \
                                                         reinterpret_cast<const uint32_t*>(ready_flags), consumed_off, epoch, \
                                                         limit ? limit : FLAG_SPIN_LIMIT, rank, world, block_counter, status)
   if (world <= 2) MTB_RS(2); else if (world <= 4) MTB_RS(4); else if (world <= 8) MTB_RS(8); else MTB_RS(16);
 #undef MTB_RS
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// NVSwitch (multimem) form of mtb200_symm_reduce_scatter. mc_base: multicast address of the arena.
+int mtb200_symm_reduce_scatter_nvls(unsigned long long mc_base, const unsigned long long* bases, int world, int rank,
+                                    unsigned long long grad_off, long long start, long long n, float* acc, int accumulate, float* sumsq,
+                                    const void* ready_flags, unsigned long long consumed_off, unsigned int epoch, unsigned int limit,
+                                    unsigned int* block_counter, int* status, int blocks, cudaStream_t st) {
+  if (mc_base == 0 || world < 1 || world > MAX_RANKS || n < 0 || n % 8 || start % 8 || grad_off % 16) return -10;
+  if (n == 0) blocks = 1;
+  else if (blocks > (n / 8 + 511) / 512) blocks = static_cast<int>((n / 8 + 511) / 512);
+  symm_reduce_scatter_nvls_kernel<<<blocks, 512, 0, st>>>(mc_base, make_table(bases, world), grad_off, start, n, acc, accumulate, sumsq,
+                                                          reinterpret_cast<const uint32_t*>(ready_flags), consumed_off, epoch,
+                                                          limit ? limit : FLAG_SPIN_LIMIT, rank, world, block_counter, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -133,10 +133,16 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
 
 
 def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dout: torch.Tensor,
-                   batch: PackedBatch, inv_freq) -> torch.Tensor:
+                   batch: PackedBatch, inv_freq, notify=None) -> torch.Tensor:
     """Writes every parameter gradient of the block into ``g`` (views of the block's flat
-    gradient buffer, same names as ``p``) and returns the gradient of the block input."""
+    gradient buffer, same names as ``p``) and returns the gradient of the block input.
+
+    ``notify(name)`` is called right after the weight gradient of ``wd``, ``wgu`` and ``wo`` has been
+    queued: everything laid out from that tensor to the end of the buffer (to the previous
+    notification) is then complete, and the engine starts reducing that region while the rest of
+    the block's backward still runs."""
     a = acts
+    notify = notify or (lambda name: None)
     rm = cfg.residual_multiplier
     # activations kept in compact form: the normalised inputs and the SwiGLU output are rebuilt by
     # bandwidth-bound kernels (about 1 ms per block) instead of being held for the whole step
@@ -149,16 +155,19 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
         dgu, act = ops.swiglu_bwd_act(dact, a.gu)
         ops.linear_wgrad(dout, act, g["wd"], alpha=rm)
         del act
+    notify("wd")
     del dact
     dn2 = ops.linear_dgrad(dgu, p["wgu"])
     n2 = a.n2 if a.n2 is not None else ops.rmsnorm(a.h1, p["ln2"], cfg.rms_norm_eps)[0]
     ops.linear_wgrad(dgu, n2, g["wgu"])
+    notify("wgu")
     del dgu, n2
     dh1 = ops.rmsnorm_bwd(dn2, a.h1, a.rstd2, p["ln2"], g["ln2"], add_to=dout)
     del dn2
     # attention
     dattn = ops.linear_dgrad(dh1, p["wo"], alpha=rm)
     ops.linear_wgrad(dh1, a.attn, g["wo"], alpha=rm)
+    notify("wo")     # ln2's gradient was written by the rmsnorm backward above
     dqkv = ops.attention_bwd(dattn, a.qkv, a.attn, a.lse, batch.cu_seqlens, batch.cu_seqlens_host,
                              batch.max_seqlen, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                              scale=cfg.attention_scale)

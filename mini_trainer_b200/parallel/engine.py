@@ -163,6 +163,9 @@ class ShardedEngine:
         # None = derive from free device memory; 0 = recompute every block like the reference
         self.activation_budget_bytes = activation_budget_bytes
         self._oom_retries = 0
+        # Reduce a block's gradients tensor region by tensor region while its backward still runs
+        # (MTB200_REGION_OVERLAP=0: one reduction per block, after its backward).
+        self.region_overlap = os.environ.get("MTB200_REGION_OVERLAP", "1") != "0"
         # Test configuration: buffers that are about to be filled by a gather or by a block's weight
         # gradients are first filled with NaN, so data consumed before it arrived (or a gradient that
         # was never written) shows up as NaN in the loss / norm instead of as a plausible stale value.
@@ -303,35 +306,75 @@ class ShardedEngine:
         self._timed_comm(lambda: self.comm.all_gather(grp.shard, full))
         return grp.layout.views(full), full, None
 
-    def _reduce(self, grp: ShardedGroup, gfull: torch.Tensor, slot: int = -1, last: bool = False):
-        """Reduce-scatter ``gfull`` into the group's fp32 accumulator on the side stream.
+    # Tensor regions of a block's gradient buffer in the order backward completes them. The layout is
+    # ln1 | bqkv | wqkv | wo | ln2 | wgu | wd and backward writes from the back: region k spans from the
+    # named tensor to the start of the previous region; the last region is what is left at the front.
+    REGION_STARTS = ("wd", "wgu", "wo")
 
-        With the symmetric backend the compute stream first publishes "my buffer is complete" to the
-        peers; the reduction kernel itself waits for the peers' matching signals. On the last
-        microbatch of a step that kernel also adds the sum of squares of the finished accumulator
-        to the step's norm scalar, so the optimizer does not have to read the accumulator again."""
+    def _reduce(self, grp: ShardedGroup, gfull: torch.Tensor, slot: int = -1, last: bool = False,
+                region: int = 0, elem_lo: int = 0, elem_hi: Optional[int] = None, final: bool = True):
+        """Reduce-scatter ``gfull`` (or elements [elem_lo, elem_hi) of it, one tensor region) into the
+        group's fp32 accumulator on the side stream.
+
+        With the symmetric backend the compute stream first publishes "this region of my buffer is
+        complete" to the peers; the reduction kernel itself waits for the peers' matching signals. On
+        the last microbatch of a step that kernel also adds the sum of squares of the finished
+        accumulator to the step's norm scalar, so the optimizer does not have to read the accumulator
+        again. ``final`` marks the last region of the buffer (bookkeeping of the group and the slot)."""
         if self.symmetric:
-            self.comm.grad_ready(gfull)
+            self.comm.grad_ready(gfull, region)
         with self.side.run(wait_current=True):
             if self.world == 1 and hasattr(self.ops, "accumulate"):
-                self.ops.accumulate(grp.gacc, gfull[: grp.gacc.numel()], grp.has_grad)
+                hi = grp.gacc.numel() if elem_hi is None else min(elem_hi, grp.gacc.numel())
+                if hi > elem_lo:
+                    self.ops.accumulate(grp.gacc[elem_lo:hi], gfull[elem_lo:hi], grp.has_grad)
             elif self.symmetric:
-                self.comm.reduce_scatter_accumulate(gfull, grp.gacc, grp.has_grad, sumsq=self._sq if last else None)
-                grp.sq_done = last
+                self.comm.reduce_scatter_accumulate(gfull, grp.gacc, grp.has_grad, sumsq=self._sq if last else None,
+                                                    region=region, elem_lo=elem_lo, elem_hi=elem_hi)
+                if final:
+                    grp.sq_done = last
             else:
                 self.comm.reduce_scatter_accumulate(gfull, grp.gacc, grp.has_grad, self._rs_scratch)
             ev = self.side.record()
-        grp.has_grad = True
-        if slot >= 0:
-            self._gbuf_free[slot] = ev
+        if final:
+            grp.has_grad = True
+            if slot >= 0:
+                self._gbuf_free[slot] = ev
         return ev
+
+    def _region_reducer(self, i: int, gbuf: torch.Tensor, gslot: int, last: bool):
+        """Returns ``(notify, finish)`` for block ``i``: ``notify(name)`` reduces the region that ends
+        where the previous one started as soon as backward has written it; ``finish()`` reduces the
+        rest. Backends whose reduction is a collective over the whole buffer (NCCL, gloo) reduce once,
+        in ``finish``."""
+        grp = self.blocks[i]
+        per_region = self.region_overlap and (self.symmetric or (self.world == 1 and hasattr(self.ops, "accumulate")))
+        state = {"hi": grp.layout.padded_numel, "k": 0}
+
+        def notify(name):
+            if not per_region or name not in self.REGION_STARTS:
+                return
+            lo = grp.layout.specs[name].offset
+            with nvtx.range(f"reduce/block{i}/{name}"):
+                self._reduce(grp, gbuf, gslot, last, region=state["k"], elem_lo=lo, elem_hi=state["hi"], final=False)
+            state["hi"], state["k"] = lo, state["k"] + 1
+
+        def finish():
+            with nvtx.range(f"reduce/block{i}"):
+                if per_region:
+                    self._reduce(grp, gbuf, gslot, last, region=state["k"], elem_lo=0, elem_hi=state["hi"], final=True)
+                else:
+                    self._reduce(grp, gbuf, gslot, last)
+
+        return notify, finish
 
     def _grad_buffer(self, i: int):
         slot = i % len(self._gbufs)
         _Side.wait(self._gbuf_free[slot])
         self._gbuf_free[slot] = None
-        if self.symmetric:
-            self._timed_comm(lambda: self.comm.wait_consumed(self._gbufs[slot]))
+        if self.symmetric:   # the region reduced last (the front of the buffer) covers the earlier ones
+            last_region = len(self.REGION_STARTS) if self.region_overlap else 0
+            self._timed_comm(lambda: self.comm.wait_consumed(self._gbufs[slot], last_region))
         if self.poison:   # only the tensors themselves: alignment gaps are never written and must stay zero
             for view in self.blocks[i].layout.views(self._gbufs[slot]).values():
                 view.fill_(float("nan"))
@@ -473,12 +516,12 @@ class ShardedEngine:
                 with nvtx.range(f"recompute/block{i}"):
                     _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True, saved_attn=attn_state,
                                                  need_out=False)
+            notify, finish = self._region_reducer(i, gbuf, gslot, last)
             with nvtx.range(f"backward/block{i}"):
-                dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq)
+                dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq, notify=notify)
             del acts, xin, attn_state
             self._release_pbuf(slot)
-            with nvtx.range(f"reduce/block{i}"):
-                self._reduce(self.blocks[i], gbuf, gslot, last=last)
+            finish()
 
         # ---- embedding ----
         if not tied:

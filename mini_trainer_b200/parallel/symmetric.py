@@ -10,7 +10,8 @@ NCCL (through ``torch.distributed``) is only used once, for the rendezvous.
 Protocol (epochs are per-channel counters that advance identically on all ranks, because all
 ranks execute the same sequence of collectives):
 
-* ``grad_ready(buf)``      my gradient buffer is complete         -> ``ready[ch][me] = epoch`` on all peers
+* ``grad_ready(buf)``      my gradient buffer (or one tensor region of it) is complete
+                                                                  -> ``ready[ch][me] = epoch`` on all peers
 * ``reduce_scatter_...``   waits ``ready[ch][p] >= epoch`` for all p, reads, then
                            ``consumed[ch][me] = epoch`` on all peers
 * ``wait_consumed(buf)``   before overwriting my buffer: ``consumed[ch][p] >= last epoch`` for all p
@@ -25,9 +26,13 @@ from __future__ import annotations
 import ctypes
 import os
 
-# The arena is only ever accessed with plain peer loads/stores, so it is not bound to an NVLink
+# By default the arena is only accessed with plain peer loads/stores and is NOT bound to an NVLink
 # multicast object: a rank that dies while its memory is bound to one can fault its peers' GPUs.
-os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+# MTB200_NVLS=1 opts in: the arena is bound, and the gradient reduce-scatter sums inside the switch
+# (multimem.ld_reduce) instead of pulling every peer's copy. Failure-path tests never set it.
+NVLS_REQUESTED = os.environ.get("MTB200_NVLS", "0") == "1"
+if not NVLS_REQUESTED:
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 from ctypes import c_int, c_longlong, c_uint, c_ulonglong, c_void_p
 
@@ -36,7 +41,7 @@ import torch.distributed as dist
 
 from ..ops.native import load_library
 
-MAX_CHANNELS = 16
+MAX_CHANNELS = 64
 MAX_RANKS = 16
 _ALIGN = 256
 
@@ -61,6 +66,7 @@ class SymmetricComm:
         self._epoch = [0] * MAX_CHANNELS
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
+        self.nvls, self.mc_ptr = False, 0
 
     def _bind(self):
         P, I, L, U, UL = c_void_p, c_int, c_longlong, c_uint, c_ulonglong
@@ -69,8 +75,9 @@ class SymmetricComm:
             "mtb200_gemm_bf16_allgather": [P, L, P, L, P, I, I, I, P, I, UL, UL, P, UL, P, U, I, I, P, P, I, P, P],
             "mtb200_symm_signal": [P, I, I, UL, U, P],
             "mtb200_symm_wait": [P, I, U, U, I, P, P],
-            "mtb200_symm_reduce_scatter": [P, I, I, UL, L, P, I, P, P, UL, U, U, P, P, I, P],
+            "mtb200_symm_reduce_scatter": [P, I, I, UL, L, L, P, I, P, P, UL, U, U, P, P, I, P],
             "mtb200_symm_allreduce_scalar": [P, I, I, UL, UL, P, P, U, U, P, P, P],
+            "mtb200_symm_reduce_scatter_nvls": [UL, P, I, I, UL, L, L, P, I, P, P, UL, U, U, P, P, I, P],
         }
         for name, args in sig.items():
             fn = getattr(self.lib, name)
@@ -94,6 +101,9 @@ class SymmetricComm:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self._bases = (c_ulonglong * self.world)(*ptrs)
         assert ptrs[self.rank] == self.arena.data_ptr()
+        # multicast address of the arena: non-zero only when binding was requested and the fabric supports it
+        self.mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0) if NVLS_REQUESTED else 0
+        self.nvls = self.mc_ptr != 0
         self._off = 0
         # flag rows: ready[ch][r], consumed[ch][r] (uint32) and vals[ch][r] (fp32 payload for scalar all-reduce)
         self._flags = self.alloc(MAX_CHANNELS * 3 * MAX_RANKS, torch.int32)
@@ -129,8 +139,10 @@ class SymmetricComm:
         self._chan[key] = ch
         return ch
 
-    def _channel(self, t: torch.Tensor) -> int:
-        key = t.data_ptr()
+    def _channel(self, t: torch.Tensor, region: int = 0) -> int:
+        """Flag channel of (buffer, region). A block's gradient buffer is reduced region by region as
+        backward completes its tensors; each region has its own ready / consumed epochs."""
+        key = (t.data_ptr(), region)
         ch = self._chan.get(key)
         return self._new_channel(key) if ch is None else ch
 
@@ -162,21 +174,39 @@ class SymmetricComm:
         """Plan for gathering one parameter group INSIDE its consuming GEMMs (see ``GatherPlan``)."""
         return GatherPlan(self, shard, full, layout, split_before, small_until)
 
-    def grad_ready(self, gfull):
-        ch = self._channel(gfull)
+    def grad_ready(self, gfull, region: int = 0):
+        ch = self._channel(gfull, region)
         self._epoch[ch] += 1
         self._call("mtb200_symm_signal", self._bases, self.world, self.rank, self._ready_off(ch), self._epoch[ch], self._st())
 
-    def reduce_scatter_accumulate(self, gfull, acc, accumulate: bool, scratch=None, sumsq=None, blocks: int = 296):
-        ch = self._channel(gfull)
+    def reduce_scatter_accumulate(self, gfull, acc, accumulate: bool, scratch=None, sumsq=None, blocks: int = 296,
+                                  region: int = 0, elem_lo: int = 0, elem_hi: int | None = None):
+        """acc (+)= sum over ranks of this rank's slice of ``gfull``. With ``elem_lo`` / ``elem_hi`` only the
+        part of the slice inside elements [elem_lo, elem_hi) of the buffer is reduced (one tensor region;
+        possibly empty for this rank, which then only takes part in the handshake)."""
+        ch = self._channel(gfull, region)
         base = self.arena.data_ptr()
-        self._call("mtb200_symm_reduce_scatter", self._bases, self.world, self.rank, self._offset(gfull), acc.numel(),
-                   acc.data_ptr(), int(accumulate), None if sumsq is None else sumsq.data_ptr(),
+        s = acc.numel()
+        lo = max(self.rank * s, elem_lo)
+        hi = min((self.rank + 1) * s, gfull.numel() if elem_hi is None else elem_hi)
+        n = max(0, hi - lo)
+        acc_ptr = acc.data_ptr() + (lo - self.rank * s) * 4 if n else acc.data_ptr()
+        if self.nvls:   # sum formed inside NVSwitch
+            self._call("mtb200_symm_reduce_scatter_nvls", self.mc_ptr, self._bases, self.world, self.rank, self._offset(gfull),
+                       lo if n else 0, n, acc_ptr, int(accumulate), None if sumsq is None else sumsq.data_ptr(),
+                       base + self._ready_off(ch), self._consumed_off(ch), self._epoch[ch], self.flag_spin_limit,
+                       self._counter.data_ptr(), self.status.data_ptr(), blocks, self._st())
+            return
+        self._call("mtb200_symm_reduce_scatter", self._bases, self.world, self.rank, self._offset(gfull), lo if n else 0, n,
+                   acc_ptr, int(accumulate), None if sumsq is None else sumsq.data_ptr(),
                    base + self._ready_off(ch), self._consumed_off(ch), self._epoch[ch], self.flag_spin_limit,
                    self._counter.data_ptr(), self.status.data_ptr(), blocks, self._st())
 
-    def wait_consumed(self, gfull):
-        ch = self._channel(gfull)
+    def wait_consumed(self, gfull, region: int = 0):
+        """Blocks the stream until every peer has finished reading ``region`` of my buffer. Every peer
+        reduces the regions of a buffer in the same order on one stream, so waiting for the region
+        that is reduced last covers the earlier ones."""
+        ch = self._channel(gfull, region)
         if self._epoch[ch] == 0:
             return
         self._call("mtb200_symm_wait", self.arena.data_ptr() + self._consumed_off(ch), self.world, self._epoch[ch],
