@@ -76,6 +76,23 @@ __global__ void __launch_bounds__(1024) symm_allgather_kernel(PeerTable peers, u
   for (; i < hi; i += stride) out[i] = src[i];
 }
 
+// ---------------------------------------------------------------------------------- pull from one peer
+// dst[0 : nvec] = arena_peer[src_off : ...] in 16-byte vectors (peer loads). The caller orders it after
+// the owner's writes with a barrier.
+__global__ void __launch_bounds__(512) symm_pull_kernel(unsigned long long src, uint4* __restrict__ dst, unsigned long long nvec) {
+  const uint4* __restrict__ s = reinterpret_cast<const uint4*>(src);
+  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+  unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < nvec; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = s[i + u * stride];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) dst[i + u * stride] = v[u];
+  }
+  for (; i < nvec; i += stride) dst[i] = s[i];
+}
+
 // ---------------------------------------------------------------------------------- signalling
 // Writes `epoch` into slot [flag_off + 4 * rank] of every peer's arena (one thread per peer).
 __global__ void symm_signal_kernel(PeerTable peers, unsigned long long flag_off, int rank, int world, uint32_t epoch) {
@@ -307,6 +324,19 @@ int mtb200_symm_allgather(const unsigned long long* bases, int world, unsigned l
   blocks -= blocks % world;   // the same number of blocks per peer
   symm_allgather_kernel<<<blocks, 1024, 0, st>>>(make_table(bases, world), src_off, shard_bytes, reinterpret_cast<uint8_t*>(dst), world,
                                                  byte_lo >> 4, byte_hi >> 4);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Copies `bytes` (a multiple of 16) from byte offset src_off of rank `peer`'s arena to local memory.
+int mtb200_symm_pull(const unsigned long long* bases, int world, int peer, unsigned long long src_off, void* dst,
+                     unsigned long long bytes, int blocks, cudaStream_t st) {
+  if (world < 1 || world > MAX_RANKS || peer < 0 || peer >= world || src_off % 16 || bytes % 16 ||
+      (reinterpret_cast<uintptr_t>(dst) & 15)) return -10;
+  if (bytes == 0) return 0;
+  const unsigned long long nvec = bytes >> 4;
+  if (blocks < 1) blocks = 1;
+  if (static_cast<unsigned long long>(blocks) > (nvec + 511) / 512) blocks = static_cast<int>((nvec + 511) / 512);
+  symm_pull_kernel<<<blocks, 512, 0, st>>>(bases[peer] + src_off, reinterpret_cast<uint4*>(dst), nvec);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -347,6 +347,9 @@ class ShardedEngine:
         where the previous one started as soon as backward has written it; ``finish()`` reduces the
         rest. Backends whose reduction is a collective over the whole buffer (NCCL, gloo) reduce once,
         in ``finish``."""
+        osft = getattr(self, "osft", None)
+        if osft is not None and osft.owner_reduce:
+            return osft.reducer(i, gbuf, gslot, last)
         grp = self.blocks[i]
         per_region = self.region_overlap and (self.symmetric or (self.world == 1 and hasattr(self.ops, "accumulate")))
         state = {"hi": grp.layout.padded_numel, "k": 0}
@@ -373,7 +376,11 @@ class ShardedEngine:
         _Side.wait(self._gbuf_free[slot])
         self._gbuf_free[slot] = None
         if self.symmetric:   # the region reduced last (the front of the buffer) covers the earlier ones
-            last_region = len(self.REGION_STARTS) if self.region_overlap else 0
+            osft = getattr(self, "osft", None)
+            if osft is not None and osft.owner_reduce:
+                last_region = osft.last_region
+            else:
+                last_region = len(self.REGION_STARTS) if self.region_overlap else 0
             self._timed_comm(lambda: self.comm.wait_consumed(self._gbufs[slot], last_region))
         if self.poison:   # only the tensors themselves: alignment gaps are never written and must stay zero
             for view in self.blocks[i].layout.views(self._gbufs[slot]).values():

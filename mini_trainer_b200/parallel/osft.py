@@ -20,13 +20,29 @@ into it:
 AdamW runs on the factors, ``W`` is recomposed and written back into the engine's fp32 master /
 bf16 working shards, so checkpoints stay plain HF safetensors.
 
-Distribution: each projection matrix is OWNED by one rank (round robin), which keeps its factors,
-their AdamW moments and the frozen dense part. Per step the block's reduced gradient is gathered
-once (the engine's reduce-scatter has already summed it over ranks), owners update their matrices
-and broadcast the recomposed weights; every rank copies the slice it shards. All other parameters
-(norms, biases, embedding, head) are updated by the engine's ordinary sharded AdamW. The gradient
-norm that drives clipping is taken over the projected factor gradients plus those other
-parameters.
+Distribution: each projection matrix is OWNED by one rank (round robin over the 7 x L matrices, so
+the factor state is sharded 1/world), which keeps its factors, their AdamW moments and the frozen
+dense part. All other parameters (norms, biases, embedding, head) are updated by the engine's
+ordinary sharded AdamW. The gradient norm that drives clipping is taken over the projected factor
+gradients plus those other parameters.
+
+On the symmetric (NVLink) backend nothing on the step path calls NCCL:
+
+* backward: as soon as a projection's dense gradient is complete in the block's gradient buffer, the
+  in-kernel reduce-scatter runs with ownership by MATRIX instead of by flat slice: the owner pulls
+  that region from every peer, sums in fp32 and accumulates into its fp32 gradient of the matrix
+  (``SymmetricComm.reduce_to_owner``); the small tensors of the block go through the ordinary slice
+  reduction restricted to their region;
+* optimizer: on the owner the factor gradients ``G V_lo^T``, ``U_lo^T G``, the two projections (applied
+  twice, which squares the bf16 rounding residue left inside the frozen subspace) and the recomposition
+  ``W_hi + (U_lo S_lo) V_lo`` are tcgen05 GEMMs (bf16 operands, fp32 accumulate and output); AdamW on
+  all factors of a rank is ONE launch of the fused kernel over a flat buffer; the norm scalar is
+  all-reduced by the arena's scalar kernel;
+* the recomposed fp32 matrices sit in a symmetric staging buffer; every rank pulls exactly the part
+  that lies in its own flat slice (``SymmetricComm.pull``) into its master weights.
+
+On the other backends (one rank, NCCL, gloo: tests and the baseline-grade path) the engine reduces as
+usual, each block's reduced gradient is gathered once, owners update and broadcast their matrices.
 
 The reference snapshot contains no OSFT code; this module defines the behaviour from the
 description above, and ``tests/test_osft.py`` pins it against a float64 autograd oracle.
@@ -102,174 +118,349 @@ def project_orthogonal_tcgen05(ops, du, dv, u_hi, v_hi):
     return du_out.to(du.dtype), dv_out.to(dv.dtype)
 
 
+
+
 @dataclass
 class _Matrix:
+    index: int
     block: int
-    name: str
+    name: str           # tensor of the block layout that holds it (wqkv / wo / wgu / wd)
     r0: int
     r1: int
     owner: int
+    elem_lo: int = 0    # extent inside the block's flat buffer
+    elem_hi: int = 0
+    out: int = 0
+    cols: int = 0
+    k_hi: int = 0
+    k_lo: int = 0
     # owner-only state
-    w_hi: torch.Tensor = None
-    u_hi: torch.Tensor = None
-    v_hi: torch.Tensor = None
-    factors: list = None      # [U_lo, S_lo, V_lo]
-    m: list = None
-    v: list = None
-    grads: list = None
+    w_hi: torch.Tensor = None      # frozen dense part, fp32 [out, cols]
+    u_hi: torch.Tensor = None      # [out, k_hi]  (bf16 on the kernel path, factor dtype otherwise)
+    v_hi: torch.Tensor = None      # [k_hi, cols]
+    fac_off: int = 0               # offset of (U_lo | S_lo | V_lo) in the rank's flat factor buffers
+    g_acc: torch.Tensor = None     # fp32 [out, cols] reduced dense gradient (matrix-owned reduction only)
+    has_grad: bool = False
+    stage_off: int = 0             # offset of the recomposed matrix in the staging buffer
 
 
 class OSFT:
-    def __init__(self, engine, rank_ratio: float = 0.5, factor_dtype=torch.float32, projection: str = "auto"):
+    """Controller that replaces ``engine.optimizer_step`` (and, on the symmetric backend, the
+    reduction of the projection gradients) once ``enable_osft`` has run."""
+
+    def __init__(self, engine, rank_ratio: float = 0.5, factor_dtype=torch.float32, projection: str = "auto",
+                 projection_passes: int = 2):
         self.eng, self.rank_ratio, self.dtype = engine, rank_ratio, factor_dtype
-        # "tcgen05": projection GEMMs on the hand-written kernel (GPU, dims multiple of 8); "torch": PyTorch matmuls
-        self.projection = projection if projection != "auto" else ("tcgen05" if hasattr(engine.ops, "gemm") else "torch")
         self.world, self.rank = engine.world, engine.rank
+        # kernel path: every product on the tcgen05 GEMM (bf16 operands, fp32 out); torch path: PyTorch matmuls in the
+        # factor dtype (CPU, float64 oracle runs)
+        self.kernels = hasattr(engine.ops, "gemm") and projection in ("auto", "tcgen05") and factor_dtype == torch.float32
+        self.projection = "tcgen05" if self.kernels else "torch"
+        self.passes = projection_passes if self.kernels else 1
+        # ownership by matrix inside the reduction itself needs the symmetric backend's kernels
+        self.owner_reduce = bool(engine.symmetric) and self.world > 1 and self.kernels
         self.mats: list[_Matrix] = []
+        cfg = engine.cfg
+        lay = engine.blocks[0].layout
         idx = 0
         for b in range(len(engine.blocks)):
-            for name, r0, r1, _ in osft_targets(engine.cfg):
-                self.mats.append(_Matrix(b, name, r0, r1, idx % self.world))
+            for name, r0, r1, _ in osft_targets(cfg):
+                spec = lay.specs[name]
+                cols = spec.shape[1]
+                k = min(r1 - r0, cols)
+                k_hi = max(0, min(k - 1, int(round(k * rank_ratio))))
+                self.mats.append(_Matrix(idx, b, name, r0, r1, idx % self.world, spec.offset + r0 * cols, spec.offset + r1 * cols,
+                                         r1 - r0, cols, k_hi, k - k_hi))
                 idx += 1
-        self._decompose()
+        self.by_block = [[m for m in self.mats if m.block == b] for b in range(len(engine.blocks))]
+        self._alloc_and_decompose()
 
-    # -- helpers ------------------------------------------------------------------------
+    # -- set-up ---------------------------------------------------------------------------
+    def _mine(self):
+        return [m for m in self.mats if m.owner == self.rank]
+
+    def _fac_views(self, mt: _Matrix, flat: torch.Tensor):
+        a = mt.fac_off
+        u = flat[a: a + mt.out * mt.k_lo].view(mt.out, mt.k_lo)
+        a += mt.out * mt.k_lo
+        s = flat[a: a + mt.k_lo]
+        a += mt.k_lo
+        v = flat[a: a + mt.k_lo * mt.cols].view(mt.k_lo, mt.cols)
+        return u, s, v
+
+    def factors(self, mt: _Matrix):
+        """``(U_lo, S_lo, V_lo)`` views of a matrix this rank owns."""
+        return self._fac_views(mt, self.fac)
+
+    def _alloc_and_decompose(self) -> None:
+        eng, dev = self.eng, self.eng.device
+        total = 0
+        for mt in self._mine():
+            mt.fac_off = total
+            total += -(-(mt.out * mt.k_lo + mt.k_lo + mt.k_lo * mt.cols) // 8) * 8
+        self.fac = torch.zeros(total, dtype=self.dtype, device=dev)        # U_lo | S_lo | V_lo of every owned matrix
+        self.fac_m = torch.zeros_like(self.fac)
+        self.fac_v = torch.zeros_like(self.fac)
+        self.fac_g = torch.zeros_like(self.fac)
+        self.fac16 = torch.zeros(total, dtype=torch.bfloat16, device=dev) if self.kernels else None
+        # staging of the recomposed matrices: the same size and offsets on every rank (peers pull from it)
+        per_rank = [0] * self.world
+        for mt in self.mats:
+            mt.stage_off = per_rank[mt.owner]
+            per_rank[mt.owner] += mt.out * mt.cols
+        n_stage = max(per_rank) if per_rank else 0
+        if self.owner_reduce:
+            self.stage = eng.comm.alloc(n_stage, torch.float32)
+        else:
+            self.stage = torch.zeros(n_stage, dtype=torch.float32, device=dev)
+        for b, grp in enumerate(eng.blocks):
+            mine = [m for m in self.by_block[b] if m.owner == self.rank]
+            full = self._gather_fp32(grp.master, grp) if (mine or self.world > 1) else None
+            for mt in mine:
+                w = full[mt.elem_lo: mt.elem_hi].view(mt.out, mt.cols).to(self.dtype)
+                u_hi, s_hi, v_hi, u_lo, s_lo, v_lo = svd_split(w, self.rank_ratio)
+                assert u_hi.shape[1] == mt.k_hi and u_lo.shape[1] == mt.k_lo
+                mt.w_hi = ((u_hi * s_hi) @ v_hi).float().contiguous()
+                hdt = torch.bfloat16 if self.kernels else self.dtype
+                mt.u_hi, mt.v_hi = u_hi.to(hdt).contiguous(), v_hi.to(hdt).contiguous()
+                u, s, v = self._fac_views(mt, self.fac)
+                u.copy_(u_lo); s.copy_(s_lo); v.copy_(v_lo)
+                if self.owner_reduce:
+                    mt.g_acc = torch.zeros(mt.out, mt.cols, dtype=torch.float32, device=dev)
+            del full
+        if self.kernels:
+            self.fac16.copy_(self.fac)
+        if self.owner_reduce:
+            # the slice reduction never touches the projections' regions of the accumulators again: they must
+            # read as zero gradient for the engine's AdamW pass from now on
+            for grp in eng.blocks:
+                grp.gacc.zero_()
+
     def _gather_fp32(self, shard: torch.Tensor, grp) -> torch.Tensor:
         if self.world == 1:
             return shard
         full = torch.empty(grp.layout.padded_numel, dtype=shard.dtype, device=shard.device)
-        dist.all_gather_into_tensor(full, shard.contiguous())
+        try:
+            dist.all_gather_into_tensor(full, shard.contiguous())
+        except RuntimeError:   # a backend without the flat form
+            parts = [torch.empty_like(shard) for _ in range(self.world)]
+            dist.all_gather(parts, shard.contiguous())
+            full = torch.cat(parts)
         return full
 
-    def _decompose(self) -> None:
-        for b, grp in enumerate(self.eng.blocks):
-            full = self._gather_fp32(grp.master, grp)
-            views = grp.layout.views(full)
-            for mt in (m for m in self.mats if m.block == b and m.owner == self.rank):
-                w = views[mt.name][mt.r0:mt.r1].to(self.dtype)
-                u_hi, s_hi, v_hi, u_lo, s_lo, v_lo = svd_split(w, self.rank_ratio)
-                mt.u_hi, mt.v_hi = u_hi.contiguous(), v_hi.contiguous()
-                mt.w_hi = (u_hi * s_hi) @ v_hi
-                mt.factors = [u_lo, s_lo, v_lo]
-                mt.m = [torch.zeros_like(t) for t in mt.factors]
-                mt.v = [torch.zeros_like(t) for t in mt.factors]
+    # -- backward-time reduction (symmetric backend) --------------------------------------------
+    def reducer(self, i: int, gbuf: torch.Tensor, gslot: int, last: bool):
+        """``(notify, finish)`` for block ``i`` (see ``ShardedEngine._region_reducer``): every projection's
+        region is reduced to its owner as soon as backward has written it; the block's small tensors go
+        through the slice reduction restricted to their region. Region numbers index the flag channels."""
+        eng, grp = self.eng, self.eng.blocks[i]
+        specs = grp.layout.specs
+        mats = {m.index: m for m in self.by_block[i]}
+        order = {"wd": ["wd"], "wgu": ["wgu"], "wo": ["wo"]}
+        state = {"k": 0}
 
-    def _mask_targets(self, grp, block: int, tensor: torch.Tensor, value: float = 0.0) -> None:
-        """Sets this rank's slice of every target matrix region of ``tensor`` (a shard) to ``value``."""
-        s = grp.layout.shard_numel
-        lo = self.rank * s
-        for mt in (m for m in self.mats if m.block == block):
-            spec = grp.layout.specs[mt.name]
-            cols = spec.shape[1]
-            a, bnd = spec.offset + mt.r0 * cols, spec.offset + mt.r1 * cols
-            a, bnd = max(a, lo), min(bnd, lo + s)
-            if a < bnd:
-                tensor[a - lo: bnd - lo] = value
+        def reduce_tensor(name):
+            for mt in (m for m in mats.values() if m.name == name):
+                k = state["k"]; state["k"] += 1
+                eng.comm.grad_ready(gbuf, k)
+                with eng.side.run(wait_current=True):
+                    eng.comm.reduce_to_owner(gbuf, mt.g_acc, mt.has_grad, mt.owner, mt.elem_lo, mt.elem_hi, region=k)
+                if mt.owner == self.rank:
+                    mt.has_grad = True
+
+        def reduce_small(names, final):
+            lo = min(specs[n].offset for n in names)
+            hi = max(specs[n].offset + specs[n].numel for n in names)
+            k = state["k"]; state["k"] += 1
+            eng._reduce(grp, gbuf, gslot, last, region=k, elem_lo=lo, elem_hi=hi, final=final)
+
+        def notify(name):
+            if name in order:
+                reduce_tensor(name)
+            if name == "wo":
+                reduce_small(["ln2"], final=False)
+
+        def finish():
+            reduce_tensor("wqkv")
+            reduce_small(["ln1"] + (["bqkv"] if "bqkv" in specs else []), final=True)
+
+        return notify, finish
+
+    @property
+    def last_region(self) -> int:
+        """Index of the region a block reduces last (what ``wait_consumed`` must wait for)."""
+        return len(self.by_block[0]) + 1
+
+    # -- products -----------------------------------------------------------------------------
+    def _mm(self, x, x_t: bool, y, y_t: bool, alpha: float = 1.0, residual=None, out=None):
+        """fp32 ``alpha * op(x) @ op(y) (+ residual)`` with ``op`` = transpose when the flag is set. Kernel
+        path: bf16 operands on the tcgen05 GEMM; torch path: a plain matmul in the factor dtype."""
+        m = x.shape[1] if x_t else x.shape[0]
+        kk = x.shape[0] if x_t else x.shape[1]
+        n = y.shape[0] if y_t else y.shape[1]
+        if not self.kernels or m % 8 or n % 8 or kk % 8:   # TMA strides need multiples of 8 elements
+            x, y = (x.float(), y.float()) if self.kernels else (x, y)
+            r = (x.t() if x_t else x) @ (y.t() if y_t else y)
+            r = r * alpha if alpha != 1.0 else r
+            return r + residual if residual is not None else r
+        bf = torch.bfloat16
+        x16 = x if x.dtype == bf else x.to(bf)
+        y16 = y if y.dtype == bf else y.to(bf)
+        if out is None:
+            out = torch.empty(m, n, dtype=torch.float32, device=x.device)
+        # A operand: [M, K] row-major (a_mn = 0) or [K, M] (a_mn = 1); B operand: [N, K] (b_mn = 0) or [K, N] (b_mn = 1)
+        self.eng.ops.gemm(x16.contiguous(), x_t, y16.contiguous(), not y_t, out, m, n, kk, residual=residual, alpha=alpha, tag="osft_gemm")
+        return out
+
+    def _factor_grads(self, mt: _Matrix, g: torch.Tensor) -> None:
+        """Writes the projected gradients of (U_lo, S_lo, V_lo) of ``mt`` into ``fac_g`` from its dense gradient."""
+        u, s, v = self._fac_views(mt, self.fac)
+        u16, _, v16 = self._fac_views(mt, self.fac16) if self.kernels else (u, None, v)
+        gu, gs, gv = self._fac_views(mt, self.fac_g)
+        g = g.to(torch.bfloat16) if self.kernels else g.to(self.dtype)
+        a = self._mm(g, False, v16, True)                       # G V_lo^T   [out, k_lo]
+        gs.copy_((u * a).sum(0))
+        du = a * s
+        dv = self._mm(u16, True, g, False) * s.unsqueeze(1)     # S U_lo^T G [k_lo, cols]
+        if mt.k_hi:
+            for _ in range(self.passes):
+                p = self._mm(mt.u_hi, True, du, False)          # U_hi^T dU
+                du = self._mm(mt.u_hi, False, p, False, alpha=-1.0, residual=du.float() if self.kernels else du)
+                r = self._mm(dv, False, mt.v_hi, True)          # dV V_hi^T
+                dv = self._mm(r, False, mt.v_hi, False, alpha=-1.0, residual=dv.float() if self.kernels else dv)
+        gu.copy_(du)
+        gv.copy_(dv)
+
+    def _recompose(self, mt: _Matrix) -> torch.Tensor:
+        """fp32 ``W_hi + (U_lo S_lo) V_lo`` written into this rank's staging slot of ``mt``."""
+        u, s, v = self._fac_views(mt, self.fac)
+        out = self.stage[mt.stage_off: mt.stage_off + mt.out * mt.cols].view(mt.out, mt.cols)
+        if self.kernels:
+            self._mm((u * s), False, self._fac_views(mt, self.fac16)[2], False, residual=mt.w_hi, out=out)
+        else:
+            out.copy_((mt.w_hi.to(self.dtype) + (u * s) @ v).float())
+        return out
 
     # -- training-state checkpoints ------------------------------------------------------------
     def state_tensors(self) -> dict:
-        """Trainable factors and their AdamW moments of the matrices this rank owns (the frozen part
-        is rebuilt from the weights at start-up and is not stored)."""
-        out = {}
-        for i, mt in enumerate(self.mats):
-            if mt.owner == self.rank:
-                for kind, lst in (("f", mt.factors), ("m", mt.m), ("v", mt.v)):
-                    for j, t in enumerate(lst):
-                        out[f"osft.{i}.{kind}{j}"] = t
-        return out
+        """Trainable factors and their AdamW moments of the matrices this rank owns, as three flat
+        tensors (the frozen part is rebuilt from the weights at start-up and is not stored)."""
+        return {"osft.factors": self.fac, "osft.m": self.fac_m, "osft.v": self.fac_v}
 
     def load_state_tensors(self, tensors: dict) -> None:
-        for i, mt in enumerate(self.mats):
-            if mt.owner == self.rank:
-                for kind, lst in (("f", mt.factors), ("m", mt.m), ("v", mt.v)):
-                    for j, t in enumerate(lst):
-                        t.copy_(tensors[f"osft.{i}.{kind}{j}"].to(t.dtype))
+        for key, dst in (("osft.factors", self.fac), ("osft.m", self.fac_m), ("osft.v", self.fac_v)):
+            dst.copy_(tensors[key].to(dst.dtype))
+        if self.kernels:
+            self.fac16.copy_(self.fac)
 
     # -- the optimizer step -----------------------------------------------------------------
+    def _mask_targets(self, grp, block: int, tensor: torch.Tensor, value: float = 0.0) -> None:
+        """Sets this rank's slice of every projection's region of ``tensor`` (a shard) to ``value``."""
+        s = grp.layout.shard_numel
+        lo = self.rank * s
+        for mt in self.by_block[block]:
+            a, b = max(mt.elem_lo, lo), min(mt.elem_hi, lo + s)
+            if a < b:
+                tensor[a - lo: b - lo] = value
+
+    def _adamw_factors(self, lr: float, coef: torch.Tensor, t: int) -> None:
+        o = self.eng.optim
+        if self.fac.numel() == 0:
+            return
+        if self.kernels:   # one launch of the fused kernel over every factor this rank owns; refreshes the bf16 copies
+            self.eng.ops.adamw_step(self.fac, self.fac_m, self.fac_v, self.fac_g, self.fac16, lr, o.beta1, o.beta2, o.eps,
+                                    o.weight_decay, t, coef)
+            return
+        g = self.fac_g * coef.to(self.dtype)
+        if o.weight_decay:
+            self.fac.mul_(1.0 - lr * o.weight_decay)
+        self.fac_m.mul_(o.beta1).add_(g, alpha=1.0 - o.beta1)
+        self.fac_v.mul_(o.beta2).addcmul_(g, g, value=1.0 - o.beta2)
+        bc1, bc2 = 1.0 - o.beta1 ** t, 1.0 - o.beta2 ** t
+        self.fac.addcdiv_(self.fac_m, (self.fac_v.sqrt() / (bc2 ** 0.5)).add_(o.eps), value=-lr / bc1)
+
     @torch.no_grad()
     def optimizer_step(self, lr: float) -> torch.Tensor:
         eng, o = self.eng, self.eng.optim
         if eng.side.cuda:
-            torch.cuda.current_stream().wait_stream(eng.side.stream)
+            torch.cuda.current_stream().wait_stream(eng.side.stream)   # the last reductions have landed
         dev = eng.device
-        sq = torch.zeros(1, dtype=torch.float32, device=dev)
-        # 1. factor gradients (owners), projected; dense target gradients are then dropped from the shards
+        sq = eng._sq if self.owner_reduce else torch.zeros(1, dtype=torch.float32, device=dev)
+        stepped = False
+        # 1. projected factor gradients on the owners
+        self.fac_g.zero_()
         for b, grp in enumerate(eng.blocks):
+            if self.owner_reduce:
+                for mt in (m for m in self.by_block[b] if m.owner == self.rank and m.has_grad):
+                    self._factor_grads(mt, mt.g_acc)
+                    mt.has_grad = False
+                    stepped = True
+                continue
             if not grp.has_grad:
                 continue
+            stepped = True
             full = self._gather_fp32(grp.gacc, grp)
-            views = grp.layout.views(full)
-            for mt in (m for m in self.mats if m.block == b and m.owner == self.rank):
-                g = views[mt.name][mt.r0:mt.r1].to(self.dtype)
-                du, ds, dv = factor_grads(g, *mt.factors)
-                dims = (du.shape[0], du.shape[1], dv.shape[1], mt.u_hi.shape[1])
-                if self.projection == "tcgen05" and all(d % 8 == 0 and d > 0 for d in dims):
-                    du, dv = project_orthogonal_tcgen05(eng.ops, du, dv, mt.u_hi, mt.v_hi)
-                else:
-                    du, dv = project_orthogonal(du, dv, mt.u_hi, mt.v_hi)
-                mt.grads = [du, ds, dv]
-                sq += sum(t.float().pow(2).sum() for t in mt.grads).to(dev)
-            self._mask_targets(grp, b, grp.gacc, 0.0)
-            del full, views
-        # 2. global norm over factor gradients + every non-target parameter
+            for mt in (m for m in self.by_block[b] if m.owner == self.rank):
+                self._factor_grads(mt, full[mt.elem_lo: mt.elem_hi].view(mt.out, mt.cols))
+            self._mask_targets(grp, b, grp.gacc, 0.0)   # the dense gradients of the projections are not applied
+            del full
+        if self.fac_g.numel():
+            sq += (eng.ops.sumsq(self.fac_g) if self.kernels else self.fac_g.float().pow(2).sum()).reshape(1)
+        # 2. global norm over factor gradients + every other parameter
         for grp in eng.groups:
-            if grp.has_grad:
+            if grp.has_grad and not grp.sq_done:
                 sq += eng.ops.sumsq(grp.gacc).reshape(1)
-        if self.world > 1:
-            dist.all_reduce(sq)
+        eng.comm.all_reduce_sum(sq)
         norm = sq.sqrt().squeeze(0)
         coef = torch.clamp(o.max_grad_norm / (norm + 1e-6), max=1.0) if o.max_grad_norm and o.max_grad_norm > 0 \
             else torch.ones((), dtype=torch.float32, device=dev)
         eng.step_count += 1
         t = eng.step_count
-        # 3. engine AdamW for everything (target regions see zero gradients and are overwritten below)
+        # 3. the engine's AdamW for everything (the projections' regions see zero gradients and are overwritten below)
         for grp in eng.groups:
             if grp.has_grad:
                 eng.ops.adamw_step(grp.master, grp.m, grp.v, grp.gacc, grp.shard, lr, o.beta1, o.beta2, o.eps,
                                    o.weight_decay, t, coef)
                 grp.has_grad = False
                 grp.sq_done = False
-        # 4. AdamW on the factors, recompose, distribute
-        bc1, bc2 = 1.0 - o.beta1 ** t, 1.0 - o.beta2 ** t
-        c = coef.to(self.dtype)
+        # 4. AdamW on the factors, recomposition into the staging buffer
+        if stepped or self.world > 1:
+            self._adamw_factors(lr, coef, t)
+            for mt in self._mine():
+                self._recompose(mt)
+        # 5. every rank takes the part of each recomposed matrix that lies in its flat slice
+        if self.owner_reduce:
+            eng.comm.barrier()    # all staging buffers are complete
         for b, grp in enumerate(eng.blocks):
             s = grp.layout.shard_numel
             lo = self.rank * s
-            for mt in (m for m in self.mats if m.block == b):
-                spec = grp.layout.specs[mt.name]
-                cols = spec.shape[1]
-                if mt.owner == self.rank:
-                    if mt.grads is not None:
-                        for p, g, m1, v1 in zip(mt.factors, mt.grads, mt.m, mt.v):
-                            g = g * c
-                            if o.weight_decay:
-                                p.mul_(1.0 - lr * o.weight_decay)
-                            m1.mul_(o.beta1).add_(g, alpha=1.0 - o.beta1)
-                            v1.mul_(o.beta2).addcmul_(g, g, value=1.0 - o.beta2)
-                            p.addcdiv_(m1, (v1.sqrt() / (bc2 ** 0.5)).add_(o.eps), value=-lr / bc1)
-                        mt.grads = None
-                    u_lo, s_lo, v_lo = mt.factors
-                    w = (mt.w_hi + (u_lo * s_lo) @ v_lo).float().contiguous()
-                else:
-                    w = torch.empty(mt.r1 - mt.r0, cols, dtype=torch.float32, device=dev)
+            for mt in self.by_block[b]:
+                x0, x1 = max(mt.elem_lo, lo), min(mt.elem_hi, lo + s)
+                if self.owner_reduce:
+                    if x0 < x1:
+                        eng.comm.pull(mt.owner, self.stage, mt.stage_off + (x0 - mt.elem_lo), grp.master[x0 - lo: x1 - lo])
+                    continue
+                n = mt.out * mt.cols
+                w = self.stage[mt.stage_off: mt.stage_off + n]
                 if self.world > 1:
+                    if mt.owner != self.rank:
+                        w = torch.empty(n, dtype=torch.float32, device=dev)
                     dist.broadcast(w, src=mt.owner)
-                a, bnd = spec.offset + mt.r0 * cols, spec.offset + mt.r1 * cols
-                x0, x1 = max(a, lo), min(bnd, lo + s)
                 if x0 < x1:
-                    grp.master[x0 - lo: x1 - lo] = w.reshape(-1)[x0 - a: x1 - a]
+                    grp.master[x0 - lo: x1 - lo] = w[x0 - mt.elem_lo: x1 - mt.elem_lo]
             grp.shard.copy_(grp.master.to(grp.shard.dtype))
-        eng._sq.zero_()
-        if eng.symmetric:
+        eng._sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        if eng.symmetric:    # nobody pulls a shard (or overwrites a staging buffer) before every rank is done
             eng.comm.barrier()
         if eng.side.cuda:
             eng.side.stream.wait_stream(torch.cuda.current_stream())
         return norm
 
 
-def enable_osft(engine, rank_ratio: float = 0.5) -> OSFT:
-    """Switches ``engine.optimizer_step`` to the OSFT update. Returns the controller."""
-    ctl = OSFT(engine, rank_ratio)
+def enable_osft(engine, rank_ratio: float = 0.5, **kw) -> OSFT:
+    """Switches ``engine.optimizer_step`` (and the reduction of the projection gradients, where the
+    backend supports ownership by matrix) to the OSFT update. Returns the controller."""
+    ctl = OSFT(engine, rank_ratio, **kw)
     engine.osft = ctl
     engine.optimizer_step = ctl.optimizer_step
     return ctl

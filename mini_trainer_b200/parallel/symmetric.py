@@ -77,6 +77,7 @@ class SymmetricComm:
             "mtb200_symm_wait": [P, I, U, U, I, P, P],
             "mtb200_symm_reduce_scatter": [P, I, I, UL, L, L, P, I, P, P, UL, U, U, P, P, I, P],
             "mtb200_symm_allreduce_scalar": [P, I, I, UL, UL, P, P, U, U, P, P, P],
+            "mtb200_symm_pull": [P, I, I, UL, P, UL, I, P],
             "mtb200_symm_reduce_scatter_nvls": [UL, P, I, I, UL, L, L, P, I, P, P, UL, U, U, P, P, I, P],
         }
         for name, args in sig.items():
@@ -201,6 +202,30 @@ class SymmetricComm:
                    acc_ptr, int(accumulate), None if sumsq is None else sumsq.data_ptr(),
                    base + self._ready_off(ch), self._consumed_off(ch), self._epoch[ch], self.flag_spin_limit,
                    self._counter.data_ptr(), self.status.data_ptr(), blocks, self._st())
+
+    def reduce_to_owner(self, gfull, acc, accumulate: bool, owner: int, elem_lo: int, elem_hi: int, region: int,
+                        sumsq=None, blocks: int = 296):
+        """Sum of elements [elem_lo, elem_hi) of every rank's ``gfull``, delivered to rank ``owner`` only
+        (``acc`` fp32, ``elem_hi - elem_lo`` elements there; ignored elsewhere): the reduce-scatter kernel
+        with ownership by tensor instead of by flat slice. Every rank takes part in the handshake."""
+        ch = self._channel(gfull, region)
+        mine = self.rank == owner
+        n = (elem_hi - elem_lo) if mine else 0
+        fn = "mtb200_symm_reduce_scatter_nvls" if self.nvls else "mtb200_symm_reduce_scatter"
+        args = (self._bases, self.world, self.rank, self._offset(gfull), elem_lo if mine else 0, n,
+                acc.data_ptr() if mine else None, int(accumulate), None if (sumsq is None or not mine) else sumsq.data_ptr(),
+                self.arena.data_ptr() + self._ready_off(ch), self._consumed_off(ch), self._epoch[ch], self.flag_spin_limit,
+                self._counter.data_ptr(), self.status.data_ptr(), blocks, self._st())
+        self._call(fn, *(((self.mc_ptr,) + args) if self.nvls else args))
+
+    def pull(self, owner: int, src: torch.Tensor, src_elem_off: int, dst: torch.Tensor, blocks: int = 64):
+        """``dst[:] = owner's copy of src[src_elem_off : src_elem_off + dst.numel()]``. ``src`` is this rank's
+        view of a tensor that every rank allocated at the same arena offset. Order it after the owner's
+        writes with ``barrier()``."""
+        es = src.element_size()
+        assert dst.dtype == src.dtype and dst.is_contiguous()
+        self._call("mtb200_symm_pull", self._bases, self.world, owner, self._offset(src) + src_elem_off * es, dst.data_ptr(),
+                   dst.numel() * es, blocks, self._st())
 
     def wait_consumed(self, gfull, region: int = 0):
         """Blocks the stream until every peer has finished reading ``region`` of my buffer. Every peer

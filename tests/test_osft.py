@@ -40,7 +40,7 @@ def test_osft_training_matches_float64_oracle():
         pre = f"model.layers.{mt.block}." + ("self_attn." if "proj" in label[(mt.name, mt.r0)] and label[(mt.name, mt.r0)][0] in "qkvo" else "mlp.")
         key = pre + label[(mt.name, mt.r0)] + ".weight"
         fac[key] = dict(w_hi=mt.w_hi.double(), u_hi=mt.u_hi.double(), v_hi=mt.v_hi.double(),
-                        p=[t.double().clone().requires_grad_(True) for t in mt.factors])
+                        p=[t.double().clone().requires_grad_(True) for t in ctl.factors(mt)])
         del base[key]
     others = {k: v.clone().requires_grad_(True) for k, v in base.items()}
     leaves = [t for f in fac.values() for t in f["p"]] + list(others.values())
@@ -71,3 +71,52 @@ def test_osft_training_matches_float64_oracle():
         assert torch.allclose(new[k], ref, atol=3e-4, rtol=1e-3), k
     for k, v in others.items():
         assert torch.allclose(new[k], v.detach().float(), atol=3e-4, rtol=1e-3), k
+
+
+def _osft_worker(rank, world, port, out_path):
+    import os
+    import torch.distributed as dist
+    from mini_trainer_b200.parallel.comm import make_comm
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(2)
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = ModelConfig(vocab_size=61, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, tie_word_embeddings=False, attention_bias=True)
+    eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), comm=make_comm("auto"), optim=OptimConfig(max_grad_norm=1.0))
+    eng.init_random(seed=4, std=0.2)
+    ctl = O.enable_osft(eng, rank_ratio=0.5)
+    assert {m.owner for m in ctl.mats} == set(range(world))          # the factor state is spread over the ranks
+    norms = []
+    for step in range(3):
+        # every rank sees the same three samples; rank r trains on samples r, r + world, ... (disjoint shares)
+        lens = [9, 5, 7, 6]
+        mbs = [make_mb([n], cfg.vocab_size, seed=10 * step + j) for j, n in enumerate(lens)]
+        total = sum(mb["num_loss_counted_tokens"] for mb in mbs)
+        mine = mbs[rank::world]
+        for mb in mine:
+            mb["batch_num_loss_counted_tokens"] = total
+        out = eng.train_step(mine, lr=1e-2)
+        norms.append(out["grad_norm"].item())
+    weights = {k: v.clone() for k, v in eng.iter_hf_tensors(dtype=torch.float32)}
+    if rank == 0:
+        torch.save({"norms": norms, "weights": weights}, out_path)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_osft_two_gloo_ranks_match_one_rank(tmp_path):
+    """Ownership by matrix across two ranks (gradients gathered, owners update, recomposed weights handed back)
+    reproduces the single-rank run: same gradient norms, same weights after three steps."""
+    import socket
+    import torch.multiprocessing as mp
+    f1, f2 = str(tmp_path / "one.pt"), str(tmp_path / "two.pt")
+    _osft_worker(0, 1, 0, f1)
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    mp.spawn(_osft_worker, args=(2, port, f2), nprocs=2, join=True)
+    a, b = torch.load(f1), torch.load(f2)
+    for x, y in zip(a["norms"], b["norms"]):
+        assert abs(x - y) < 1e-4 * max(1.0, abs(x)), (a["norms"], b["norms"])
+    for k in a["weights"]:
+        assert torch.allclose(a["weights"][k], b["weights"][k], atol=2e-5, rtol=1e-4), k
