@@ -104,6 +104,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   const int nq = (seq_len + AB_B - 1) / AB_B;      // query blocks of the sequence
   const int per_head = nq - jblk;                  // query blocks at or below the diagonal
   const int n_iters = G * per_head;
+  // bounds check of the host-built work item (uniform over the CTA; nothing allocated or armed yet)
+  if (seq_start < 0 || seq_len <= 0 || k0 < 0 || k0 >= seq_len || static_cast<long long>(seq_start) + seq_len > p.T) {
+    if (threadIdx.x == 0) atomicExch(p.status, 61);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(sdp_full, 1); mbar_init(pds_ready, 8);

@@ -92,6 +92,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   const int hk = h / (p.Hq / p.Hkv);
   const int seq_start = p.plan[item * 3 + 0], seq_len = p.plan[item * 3 + 1], q0 = p.plan[item * 3 + 2];
   const int n_tiles = q0 / ATT_BN + 1;
+  // bounds check of the host-built work item (uniform over the CTA; nothing allocated or armed yet):
+  // a row that does not lie inside the packed batch is reported, not dereferenced
+  if (seq_start < 0 || seq_len <= 0 || q0 < 0 || q0 >= seq_len || static_cast<long long>(seq_start) + seq_len > p.T) {
+    if (threadIdx.x == 0) atomicExch(p.status, 61);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);

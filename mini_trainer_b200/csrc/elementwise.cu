@@ -267,11 +267,19 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(__nv_bfloat16* d
 }
 
 // ------------------------------------------------------------------------------ embedding
+// An id outside [0, V) (a tokenizer larger than the embedding table) is not dereferenced: the row is zero-filled
+// and code 60 is recorded in the status word, which the host turns into an exception.
 __global__ void __launch_bounds__(128) embedding_fwd_kernel(const __nv_bfloat16* __restrict__ w, const long long* __restrict__ ids,
-                                                           __nv_bfloat16* __restrict__ out, int H) {
+                                                           __nv_bfloat16* __restrict__ out, int H, int V, int* status) {
   const long long t = blockIdx.x;
-  const __nv_bfloat16* src = w + ids[t] * H;
+  const long long id = ids[t];
   __nv_bfloat16* dst = out + t * H;
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 60);
+    for (int c = threadIdx.x * 8; c < H; c += 128 * 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const __nv_bfloat16* src = w + id * H;
   for (int c = threadIdx.x * 8; c < H; c += 128 * 8) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
 }
 
@@ -282,10 +290,14 @@ __global__ void __launch_bounds__(128) embedding_fwd_kernel(const __nv_bfloat16*
 // blocks of the run exit at once. No atomics, so the result does not depend on scheduling.
 __global__ void __launch_bounds__(128) embedding_bwd_kernel(__nv_bfloat16* __restrict__ dw, const long long* __restrict__ sorted_ids,
                                                            const long long* __restrict__ order, const __nv_bfloat16* __restrict__ dx,
-                                                           int T, int H) {
+                                                           int T, int H, int V, int* status) {
   const int j = blockIdx.x;
   const long long id = sorted_ids[j];
   if (j > 0 && sorted_ids[j - 1] == id) return;
+  if (id < 0 || id >= V) {   // skipped and reported, never dereferenced
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 60);
+    return;
+  }
   __nv_bfloat16* dst = dw + id * H;
   for (int c = threadIdx.x * 8; c < H; c += 128 * 8) {
     float acc[8];
@@ -561,17 +573,18 @@ int mtb200_swiglu_bwd_act(void* dact_inout, const void* gu, void* dgu, long long
   return launch_ok();
 }
 
-int mtb200_embedding_fwd(const void* w, const long long* ids, void* out, int T, int H, cudaStream_t st) {
+int mtb200_embedding_fwd(const void* w, const long long* ids, void* out, int T, int H, int V, int* status, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8) return -10;
-  embedding_fwd_kernel<<<T, 128, 0, st>>>((const bf16*)w, ids, (bf16*)out, H);
+  embedding_fwd_kernel<<<T, 128, 0, st>>>((const bf16*)w, ids, (bf16*)out, H, V, status);
   return launch_ok();
 }
 
-int mtb200_embedding_bwd(void* dw, const long long* sorted_ids, const long long* order, const void* dx, int T, int H, cudaStream_t st) {
+int mtb200_embedding_bwd(void* dw, const long long* sorted_ids, const long long* order, const void* dx, int T, int H, int V,
+                         int* status, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8) return -10;
-  embedding_bwd_kernel<<<T, 128, 0, st>>>((bf16*)dw, sorted_ids, order, (const bf16*)dx, T, H);
+  embedding_bwd_kernel<<<T, 128, 0, st>>>((bf16*)dw, sorted_ids, order, (const bf16*)dx, T, H, V, status);
   return launch_ok();
 }
 

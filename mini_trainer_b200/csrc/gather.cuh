@@ -78,6 +78,7 @@ __device__ __forceinline__ void gather_chunks(const GatherParams& g, int gt, uin
     // a chunk lies in one peer's shard, or straddles one boundary (shards are larger than a chunk);
     // the peer is resolved once per chunk, not per vector
     const unsigned long long pr0 = v0 / vec_per_shard;
+    if (pr0 >= static_cast<unsigned long long>(g.world)) break;   // a chunk beyond the last shard: never dereference a peer that does not exist
     const unsigned long long first = min(nv, (pr0 + 1) * vec_per_shard - v0);   // vectors that belong to peer pr0
     const uint4* src0 = reinterpret_cast<const uint4*>(g.peer_base[pr0] + g.shard_off) + (v0 - pr0 * vec_per_shard);
     const uint4* src1 = first < nv ? reinterpret_cast<const uint4*>(g.peer_base[pr0 + 1] + g.shard_off) - first : src0;

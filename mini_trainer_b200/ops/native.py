@@ -52,8 +52,8 @@ class _Sig:
     mtb200_swiglu_fwd = [P, P, L, I, P]
     mtb200_swiglu_bwd = [P, P, P, L, I, P]
     mtb200_swiglu_bwd_act = [P, P, P, L, I, P]
-    mtb200_embedding_fwd = [P, P, P, I, I, P]
-    mtb200_embedding_bwd = [P, P, P, P, I, I, P]
+    mtb200_embedding_fwd = [P, P, P, I, I, I, P, P]
+    mtb200_embedding_bwd = [P, P, P, P, I, I, I, P, P]
     mtb200_ce_fwd_bwd = [P, L, I, P, P, P, L, I, I, F, L, P]
     mtb200_colsum = [P, L, P, P, I, I, P]
     mtb200_accumulate = [P, P, L, I, I, P]
@@ -79,9 +79,13 @@ class NativeOps:
         self.ce_chunk = ce_chunk
         self.attention_impl = attention or os.environ.get("MTB200_ATTENTION", "native")
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        # two-CTA (cta_group::2, 256x256 tiles) GEMM for problems with about a full wave of such tiles or more;
-        # MTB200_GEMM2=0 forces the one-CTA 128x256 kernel everywhere (A/B comparisons)
-        self.use_gemm2 = os.environ.get("MTB200_GEMM2", "1") == "1"
+        # MTB200_GEMM2=1: two-CTA (cta_group::2, 256x256 tiles) GEMM for problems with about a full wave of such
+        # tiles or more. It is the faster kernel in isolation (0.92-0.95 of the cuBLAS burst figure against
+        # 0.74-0.90), but a training step runs at the 1000 W power cap, where the clock settles at what the GEMMs
+        # draw: with the CTA-pair kernel the SM clock drops by 12-16 % for EVERY kernel of the step, and the
+        # latency-bound ones (attention, normalisation) lose more than the GEMMs gain: measured end to end on
+        # one GPU 25.2 s against 23.9 s per step. So the one-CTA kernel is the default.
+        self.use_gemm2 = os.environ.get("MTB200_GEMM2", "0") == "1"
         self.launches = 0
         self.profile = [] if os.environ.get("MTB200_PROFILE") else None
         self._scratch = {}
@@ -141,7 +145,9 @@ class NativeOps:
         code = int(self.status.item())
         if code:
             self.status.zero_()
-            raise RuntimeError(f"a device-side bounded wait expired (code {code})")
+            what = {60: "a token id outside the embedding table", 61: "an attention work item outside the packed batch"}.get(
+                code, "a device-side bounded wait expired")
+            raise RuntimeError(f"{what} (status code {code})")
 
     # -- GEMM -------------------------------------------------------------------------
     def gemm(self, a, a_mn, b, b_mn, out, M, N, K, residual=None, bias=None, tag=None, two_cta=None, alpha=1.0):
@@ -162,14 +168,15 @@ class NativeOps:
     def embedding(self, weight, ids):
         T, H = ids.shape[0], weight.shape[1]
         out = torch.empty(T, H, dtype=weight.dtype, device=self.device)
-        self._call("mtb200_embedding_fwd", weight.data_ptr(), ids.data_ptr(), out.data_ptr(), T, H, self._st())
+        self._call("mtb200_embedding_fwd", weight.data_ptr(), ids.data_ptr(), out.data_ptr(), T, H, weight.shape[0],
+                   self.status.data_ptr(), self._st())
         return out
 
     def embedding_bwd(self, dweight, ids, dx):
         """dweight[ids] += dx, deterministic: a stable sort groups equal ids; one block sums each group in fp32."""
         sorted_ids, order = torch.sort(ids, stable=True)
         self._call("mtb200_embedding_bwd", dweight.data_ptr(), sorted_ids.data_ptr(), order.data_ptr(), dx.data_ptr(),
-                   ids.shape[0], dweight.shape[1], self._st())
+                   ids.shape[0], dweight.shape[1], dweight.shape[0], self.status.data_ptr(), self._st())
 
     # -- rmsnorm ----------------------------------------------------------------------
     def rmsnorm(self, x, w, eps):

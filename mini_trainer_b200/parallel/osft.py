@@ -64,9 +64,38 @@ def osft_targets(cfg: ModelConfig) -> list:
             ("wo", 0, h, "o_proj"), ("wgu", 0, f, "gate_proj"), ("wgu", f, 2 * f, "up_proj"), ("wd", 0, h, "down_proj")]
 
 
-def svd_split(w: torch.Tensor, rank_ratio: float):
+def svd_thin(w: torch.Tensor, method: str = "auto"):
+    """Thin SVD ``w = U diag(S) Vh`` with singular values in descending order.
+
+    ``exact``: ``torch.linalg.svd``. ``gram``: eigendecomposition of the smaller Gram matrix (``w^T w`` or
+    ``w w^T``) and one GEMM for the other side: a few GEMMs and one symmetric eigenproblem of the small
+    dimension instead of a full bidiagonalisation, which is what makes decomposing the 196 projections
+    of a 7B model at start-up a matter of seconds. The side that comes from the eigenproblem is
+    orthonormal to working precision; the other side is ``w v / s``, so ``U diag(S) Vh`` reproduces ``w``
+    to that same precision whatever the conditioning, but its columns for singular values below about
+    ``sqrt(eps) * s_max`` are only approximately orthonormal. ``auto``: ``gram`` for fp32 matrices on a GPU
+    whose small dimension exceeds 1024, ``exact`` otherwise."""
+    rows, cols = w.shape
+    if method == "auto":
+        method = "gram" if (w.is_cuda and w.dtype == torch.float32 and min(rows, cols) > 1024) else "exact"
+    if method == "exact":
+        return torch.linalg.svd(w, full_matrices=False)
+    if rows >= cols:
+        lam, v = torch.linalg.eigh(w.t() @ w)                 # ascending
+        lam, v = lam.flip(0).clamp_min(0), v.flip(1)
+        s = lam.sqrt()
+        u = (w @ v) / s.clamp_min(torch.finfo(w.dtype).tiny)
+        return u, s, v.t().contiguous()
+    lam, u = torch.linalg.eigh(w @ w.t())
+    lam, u = lam.flip(0).clamp_min(0), u.flip(1)
+    s = lam.sqrt()
+    vh = (u.t() @ w) / s.clamp_min(torch.finfo(w.dtype).tiny).unsqueeze(1)
+    return u.contiguous(), s, vh
+
+
+def svd_split(w: torch.Tensor, rank_ratio: float, method: str = "exact"):
     """Returns ``(U_hi, S_hi, V_hi, U_lo, S_lo, V_lo)`` of ``w`` (float32/float64 input)."""
-    u, s, vh = torch.linalg.svd(w, full_matrices=False)
+    u, s, vh = svd_thin(w, method)
     k = s.numel()
     k_hi = max(0, min(k - 1, int(round(k * rank_ratio))))
     return u[:, :k_hi], s[:k_hi], vh[:k_hi], u[:, k_hi:].clone(), s[k_hi:].clone(), vh[k_hi:].clone()
@@ -149,8 +178,9 @@ class OSFT:
     reduction of the projection gradients) once ``enable_osft`` has run."""
 
     def __init__(self, engine, rank_ratio: float = 0.5, factor_dtype=torch.float32, projection: str = "auto",
-                 projection_passes: int = 2):
+                 projection_passes: int = 2, svd_method: str = "auto"):
         self.eng, self.rank_ratio, self.dtype = engine, rank_ratio, factor_dtype
+        self.svd_method = svd_method
         self.world, self.rank = engine.world, engine.rank
         # kernel path: every product on the tcgen05 GEMM (bf16 operands, fp32 out); torch path: PyTorch matmuls in the
         # factor dtype (CPU, float64 oracle runs)
@@ -218,7 +248,7 @@ class OSFT:
             full = self._gather_fp32(grp.master, grp) if (mine or self.world > 1) else None
             for mt in mine:
                 w = full[mt.elem_lo: mt.elem_hi].view(mt.out, mt.cols).to(self.dtype)
-                u_hi, s_hi, v_hi, u_lo, s_lo, v_lo = svd_split(w, self.rank_ratio)
+                u_hi, s_hi, v_hi, u_lo, s_lo, v_lo = svd_split(w, self.rank_ratio, self.svd_method)
                 assert u_hi.shape[1] == mt.k_hi and u_lo.shape[1] == mt.k_lo
                 mt.w_hi = ((u_hi * s_hi) @ v_hi).float().contiguous()
                 hdt = torch.bfloat16 if self.kernels else self.dtype

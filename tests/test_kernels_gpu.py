@@ -411,3 +411,30 @@ def test_osft_projection_on_tcgen05_gemm(ops):
     # what is left inside the frozen subspace is at bf16 rounding level
     assert (u_hi.float().t() @ got_u).norm() < 2e-2 * du.float().norm()
     assert (got_v @ v_hi.float().t()).norm() < 2e-2 * dv.float().norm()
+
+
+def test_out_of_range_inputs_are_reported_not_dereferenced(ops):
+    """Bounds checks that record a status code and skip the access: a token id outside the embedding
+    table, an attention work item outside the packed batch. The context stays usable."""
+    w = bf(100, 64)
+    ids = torch.tensor([3, 100, 7, -1], device="cuda")
+    out = ops.embedding(w, ids)
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], w[3]) and torch.equal(out[2], w[7]) and (out[1] == 0).all() and (out[3] == 0).all()
+    with pytest.raises(RuntimeError, match="token id outside"):
+        ops.check_status()
+    dw = torch.zeros(100, 64, dtype=torch.bfloat16, device="cuda")
+    ops.embedding_bwd(dw, ids, bf(4, 64))
+    with pytest.raises(RuntimeError, match="token id outside"):
+        ops.check_status()
+    assert dw[3].abs().sum() > 0 and dw[7].abs().sum() > 0
+    # an attention plan that claims a sequence longer than the batch
+    T, hq, hkv, D = 256, 2, 1, 128
+    qkv = bf(T, (hq + 2 * hkv) * D)
+    cu_host = [0, 300]
+    cu = torch.tensor(cu_host, dtype=torch.int32, device="cuda")
+    ops.attention(qkv, cu, cu_host, 300, hq, hkv, D)
+    with pytest.raises(RuntimeError, match="attention work item"):
+        ops.check_status()
+    ops.check_status()     # cleared; and the device still works
+    assert torch.ones(8, device="cuda").sum().item() == 8

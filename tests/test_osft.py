@@ -120,3 +120,22 @@ def test_osft_two_gloo_ranks_match_one_rank(tmp_path):
         assert abs(x - y) < 1e-4 * max(1.0, abs(x)), (a["norms"], b["norms"])
     for k in a["weights"]:
         assert torch.allclose(a["weights"][k], b["weights"][k], atol=2e-5, rtol=1e-4), k
+
+
+def test_gram_svd_reconstructs_and_spans_the_same_top_subspace():
+    """The fast decomposition (eigenproblem of the small Gram matrix) against the exact SVD: same singular
+    values, same frozen subspace, exact reconstruction; tall and wide matrices."""
+    torch.manual_seed(1)
+    for shape in ((96, 40), (40, 96), (64, 64)):
+        w = torch.randn(*shape, dtype=torch.float64)
+        u, s, vh = O.svd_thin(w, "gram")
+        ue, se, vhe = O.svd_thin(w, "exact")
+        assert torch.allclose(s, se, rtol=1e-8, atol=1e-10)
+        assert torch.allclose((u * s) @ vh, w, atol=1e-10)
+        k = s.numel() // 2
+        # projectors onto the top-k left / right singular subspaces agree
+        assert torch.allclose(u[:, :k] @ u[:, :k].t(), ue[:, :k] @ ue[:, :k].t(), atol=1e-7)
+        assert torch.allclose(vh[:k].t() @ vh[:k], vhe[:k].t() @ vhe[:k], atol=1e-7)
+    w32 = torch.randn(80, 48)
+    u, s, vh = O.svd_thin(w32, "gram")
+    assert ((u * s) @ vh - w32).abs().max() < 1e-4
