@@ -240,7 +240,7 @@ class OSFT:
             per_rank[mt.owner] += mt.out * mt.cols
         n_stage = max(per_rank) if per_rank else 0
         if self.owner_reduce:
-            self.stage = eng.comm.alloc(n_stage, torch.float32)
+            self.stage = eng.comm.alloc_region(n_stage, torch.float32)
         else:
             self.stage = torch.zeros(n_stage, dtype=torch.float32, device=dev)
         for b, grp in enumerate(eng.blocks):

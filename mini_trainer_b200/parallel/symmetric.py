@@ -67,6 +67,7 @@ class SymmetricComm:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
         self.nvls, self.mc_ptr = False, 0
+        self._regions = []
 
     def _bind(self):
         P, I, L, U, UL = c_void_p, c_int, c_longlong, c_uint, c_ulonglong
@@ -126,6 +127,32 @@ class SymmetricComm:
             raise RuntimeError("symmetric arena exhausted")
         self._off = start + nbytes
         return self.arena[start:start + nbytes].view(dtype)
+
+    def alloc_region(self, numel: int, dtype) -> torch.Tensor:
+        """A symmetric buffer of its own (same size on every rank, rendezvoused like the arena) for state
+        that is sized after the engine has laid out the arena, e.g. the OSFT staging of recomposed
+        matrices. Collective. Peers read it with ``pull``."""
+        import torch.distributed._symmetric_memory as symm_mem
+        es = torch.empty(0, dtype=dtype).element_size()
+        nbytes = -(-max(1, numel) * es // 4096) * 4096
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        buf.zero_()
+        handle = symm_mem.rendezvous(buf, self.group.group_name)
+        bases = (c_ulonglong * self.world)(*[int(p) for p in handle.buffer_ptrs])
+        self._regions.append((buf, handle, bases))
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        return buf[: numel * es].view(dtype)
+
+    def _locate(self, t: torch.Tensor):
+        """(peer base table, byte offset) of a tensor living in the arena or in one of the extra regions."""
+        p = t.data_ptr()
+        if self.arena is not None and 0 <= p - self.arena.data_ptr() < self.arena.numel():
+            return self._bases, p - self.arena.data_ptr()
+        for buf, _, bases in self._regions:
+            if 0 <= p - buf.data_ptr() < buf.numel():
+                return bases, p - buf.data_ptr()
+        raise ValueError("tensor does not live in symmetric memory")
 
     def _offset(self, t: torch.Tensor) -> int:
         off = t.data_ptr() - self.arena.data_ptr()
@@ -224,7 +251,8 @@ class SymmetricComm:
         writes with ``barrier()``."""
         es = src.element_size()
         assert dst.dtype == src.dtype and dst.is_contiguous()
-        self._call("mtb200_symm_pull", self._bases, self.world, owner, self._offset(src) + src_elem_off * es, dst.data_ptr(),
+        bases, off = self._locate(src)
+        self._call("mtb200_symm_pull", bases, self.world, owner, off + src_elem_off * es, dst.data_ptr(),
                    dst.numel() * es, blocks, self._st())
 
     def wait_consumed(self, gfull, region: int = 0):
