@@ -110,6 +110,14 @@ class _Side:
                 cur.wait_event(ev)
 
 
+class _HostInput:
+    """A block input that lives in pinned host memory between forward and backward."""
+
+    def __init__(self, host: torch.Tensor, shape: tuple):
+        self.host, self.shape = host, shape
+        self.device = self.ready = self.slot = None
+
+
 class ShardedEngine:
     def __init__(self, cfg: ModelConfig, device, ops, comm=None, param_dtype=None, state_dtype=None,
                  optim: Optional[OptimConfig] = None, activation_budget_bytes: Optional[int] = None):
@@ -166,6 +174,12 @@ class ShardedEngine:
         # Reduce a block's gradients tensor region by tensor region while its backward still runs
         # (MTB200_REGION_OVERLAP=0: one reduction per block, after its backward).
         self.region_overlap = os.environ.get("MTB200_REGION_OVERLAP", "1") != "0"
+        # checkpoint level 3: block inputs parked in pinned host memory, two device staging buffers for the way back
+        self._copy_stream = None
+        self._host_inputs = {}
+        self._dev_inputs = [None, None]
+        self._dev_input_free = [None, None]
+        self._pending_input_slot = None
         # Test configuration: buffers that are about to be filled by a gather or by a block's weight
         # gradients are first filled with NaN, so data consumed before it arrived (or a gradient that
         # was never written) shows up as NaN in the loss / norm instead of as a plausible stale value.
@@ -402,6 +416,7 @@ class ShardedEngine:
     def plan_checkpointing(self, tokens: int) -> list:
         """Per-block checkpoint level for a minibatch of ``tokens`` tokens.
 
+        3 = as 2, with the block input parked in pinned host memory (only when even the inputs do not fit);
         2 = keep only the block input and recompute the whole block in backward (what the reference
         does for every block, setup_model_for_training.py:28-29); 1 = also keep the attention
         output and its log-sum-exp so the recompute skips the attention kernel; 0 = keep every GEMM
@@ -414,6 +429,16 @@ class ShardedEngine:
         budget = self.activation_budget_bytes
         if budget is None:
             budget = self._auto_activation_budget(tokens)
+        force = int(os.environ.get("MTB200_OFFLOAD_BLOCKS", "0"))
+        if (budget < 0 or force) and self.device.type == "cuda":
+            # Not even the block inputs fit next to the optimizer state (a 70B model with a sample far longer
+            # than the per-GPU token budget): level 3 parks a block's input in pinned host memory during
+            # forward and brings it back one block ahead of its use in backward. The earliest blocks go first:
+            # their inputs would stay resident longest.
+            per_block = tokens * cfg.hidden_size * (2 if self.param_dtype != torch.float32 else 4)
+            n_off = max(force, -(-(-budget) // per_block) if budget < 0 else 0)
+            for i in range(min(n_off, nL - 1)):
+                levels[i] = 3
         if budget <= 0:
             return levels
         es = 2 if self.param_dtype != torch.float32 else 4
@@ -519,6 +544,10 @@ class ShardedEngine:
             gbuf, gslot = self._grad_buffer(i)
             g = self.blocks[i].layout.views(gbuf)
             xin, acts, attn_state = saved.pop()
+            if isinstance(xin, _HostInput):
+                xin = self._fetch_input(i, xin)
+            if i > 0 and isinstance(saved[i - 1][0], _HostInput):   # the next block's input travels while this block computes
+                self._prefetch_input(i - 1, saved[i - 1][0])
             if acts is None:   # recompute the block forward (attention is skipped when its output was kept)
                 with nvtx.range(f"recompute/block{i}"):
                     _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True, saved_attn=attn_state,
@@ -527,6 +556,7 @@ class ShardedEngine:
             with nvtx.range(f"backward/block{i}"):
                 dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq, notify=notify)
             del acts, xin, attn_state
+            self._release_input()
             self._release_pbuf(slot)
             finish()
 
@@ -539,6 +569,63 @@ class ShardedEngine:
         ops.embedding_bwd(emb_g["embed"], batch.input_ids, dx)
         self._root_free["embed"] = self._reduce(self.embed, eg_full, last=last)
         return loss
+
+    # ------------------------------------------------------------------------------------
+    # block inputs parked in host memory (checkpoint level 3)
+    # ------------------------------------------------------------------------------------
+    def _offload_input(self, i: int, x: torch.Tensor) -> "_HostInput":
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        host = self._host_inputs.get(i)
+        if host is None or host.numel() < x.numel():
+            host = torch.empty(x.numel(), dtype=x.dtype, pin_memory=True)
+            self._host_inputs[i] = host
+        cur = torch.cuda.current_stream()
+        self._copy_stream.wait_stream(cur)          # the block that reads x has been queued; x itself is complete
+        with torch.cuda.stream(self._copy_stream):
+            host[: x.numel()].view(x.shape).copy_(x, non_blocking=True)
+        x.record_stream(self._copy_stream)          # its memory is not reused before the copy has read it
+        return _HostInput(host, tuple(x.shape))
+
+    def _prefetch_input(self, i: int, h: "_HostInput") -> None:
+        if h.device is not None:
+            return
+        slot = i % 2
+        n = 1
+        for d in h.shape:
+            n *= d
+        buf = self._dev_inputs[slot]
+        if buf is None or buf.numel() < n:
+            if buf is not None:
+                buf.record_stream(self._copy_stream)
+            buf = torch.empty(n, dtype=h.host.dtype, device=self.device)
+            self._dev_inputs[slot] = buf
+            self._dev_input_free[slot] = None    # fresh memory: order the copy after everything queued so far
+        if self._dev_input_free[slot] is not None:   # the block that last used this staging buffer has finished
+            self._copy_stream.wait_event(self._dev_input_free[slot])
+        else:
+            self._copy_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self._copy_stream):
+            dev = buf[:n].view(h.shape)
+            dev.copy_(h.host[:n].view(h.shape), non_blocking=True)
+            h.ready = torch.cuda.Event()
+            h.ready.record(self._copy_stream)
+        h.device, h.slot = dev, slot
+
+    def _fetch_input(self, i: int, h: "_HostInput") -> torch.Tensor:
+        self._prefetch_input(i, h)
+        _Side.wait(h.ready)      # counted as exposed time when the copy is late
+        self._pending_input_slot = h.slot
+        return h.device
+
+    def _release_input(self) -> None:
+        """Called after a block's backward has been queued: its staged input may be overwritten afterwards."""
+        slot = self._pending_input_slot
+        if slot is not None:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self._dev_input_free[slot] = ev
+            self._pending_input_slot = None
 
     def _forward(self, batch: D.PackedBatch, levels: list):
         """Forward through the embedding and the blocks; returns the last hidden state, what each
@@ -567,6 +654,8 @@ class ShardedEngine:
             with nvtx.range(f"forward/block{i}"):
                 x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq,
                                                       keep="compact" if levels[i] == 0 else False, want_attn=levels[i] == 1)
+            if levels[i] == 3:
+                xin = self._offload_input(i, xin)
             saved.append((xin, acts, attn_state))
             if i + 1 < nL or self.world == 1:
                 self._release_pbuf(slot)
