@@ -186,6 +186,7 @@ def run_native(args) -> dict:
     ops = get_ops(device)
     eng = ShardedEngine(cfg, device, ops, comm=comm, state_dtype=sdt, optim=OptimConfig(lr=1e-5))
     eng.init_random(seed=893, on_device=on_gpu)
+    eng.reserve_host_offload(max(max_tokens, spec.hi))   # pinned buffers for the longest sample, if its inputs will not fit (70B)
     if args.osft:
         from mini_trainer_b200.parallel.osft import enable_osft
         enable_osft(eng, rank_ratio=0.5)

@@ -116,6 +116,9 @@ def main(
         loader = get_data_loader(data_path=data_path, batch_size=batch_size, max_tokens_per_gpu=max_tokens_per_gpu,
                                  seed=seed, num_workers=num_workers, pin_memory=device.type == "cuda", cost_len=cost_len,
                                  skip_batches=skip_batches)
+    ds = getattr(loader, "dataset", None)
+    if ds is not None and hasattr(ds, "lengths") and len(ds):
+        model.reserve_host_offload(max(max_tokens_per_gpu, int(ds.lengths.max())))
     train(model, optimizer, sched, loader, output_dir, min_samples_per_checkpoint, model_name_or_path,
           max_steps=max_steps, max_shard_bytes=int(max_shard_gb * 1e9), save_train_state=save_train_state,
           resume_state=resume_state)

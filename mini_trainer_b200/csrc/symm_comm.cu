@@ -12,7 +12,8 @@
 //                    is done it signals "consumed" so the owner may overwrite the buffer.
 //
 // Flags are 32-bit epochs in the owner's arena, written by peers with system-scope release
-// stores and polled with acquire loads. Every poll loop is bounded: when it runs out, the kernel
+// stores and polled with acquire loads. Every poll loop is bounded (a time limit on the global timer
+// plus a poll count): when it runs out, the kernel
 // records {code, peer} in the status word, skips its transfers and returns, so a missing peer ends
 // in a host-side error instead of a hung GPU.
 #include <cuda_bf16.h>
@@ -24,7 +25,11 @@
 namespace mtb {
 
 constexpr int MAX_RANKS = 16;
-constexpr uint32_t FLAG_SPIN_LIMIT = 1u << 24;   // polls (each with a short sleep) before giving up
+// Default bound of a wait on a peer's flag, in microseconds. It has to cover legitimate skew between
+// ranks (one rank holding an over-length sample, a first-touch allocation of pinned memory), which at 70B
+// scale is tens of seconds; a peer that is really gone still ends the wait, just later. Tests pass a
+// bound of a few milliseconds.
+constexpr uint32_t FLAG_SPIN_LIMIT = 180u * 1000u * 1000u;
 
 struct PeerTable {
   uint64_t base[MAX_RANKS];   // device address of every rank's arena, as mapped into this process
@@ -39,11 +44,21 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Waits until *flag >= epoch (wrap-safe). Returns false when the bound is hit.
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t limit) {
-  for (uint32_t i = 0; i < limit; ++i) {
+// Waits until *flag >= epoch (wrap-safe). Bounded twice: by `limit_us` microseconds of the global
+// timer and by a fixed number of polls. Returns false when a bound is hit.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t limit_us) {
+  if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  const unsigned long long budget = static_cast<unsigned long long>(limit_us) * 1000ull;
+  for (uint32_t i = 0; i < 0x7fffffffu; ++i) {
     if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    __nanosleep(64);
+    __nanosleep(200);
+    if ((i & 31u) == 31u) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (t - t0 > budget) return false;
+    }
   }
   return false;
 }

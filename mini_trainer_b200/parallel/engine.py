@@ -573,6 +573,24 @@ class ShardedEngine:
     # ------------------------------------------------------------------------------------
     # block inputs parked in host memory (checkpoint level 3)
     # ------------------------------------------------------------------------------------
+    def reserve_host_offload(self, tokens: int) -> int:
+        """Allocates, ahead of training, the pinned host buffers a minibatch of ``tokens`` tokens would park
+        its block inputs in (call it with the longest sample of the dataset, or the per-GPU token budget if
+        that is larger). Page-locking tens of gigabytes takes tens of seconds; done lazily it would stall
+        one rank in the middle of a step while every peer waits for it. Returns the number of blocks reserved."""
+        if self.device.type != "cuda":
+            return 0
+        levels = self.plan_checkpointing(tokens)
+        n = 0
+        for i, lv in enumerate(levels):
+            if lv == 3:
+                need = tokens * self.cfg.hidden_size
+                host = self._host_inputs.get(i)
+                if host is None or host.numel() < need:
+                    self._host_inputs[i] = torch.empty(need, dtype=self.param_dtype, pin_memory=True)
+                n += 1
+        return n
+
     def _offload_input(self, i: int, x: torch.Tensor) -> "_HostInput":
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream(device=self.device)

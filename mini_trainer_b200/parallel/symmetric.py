@@ -18,8 +18,9 @@ ranks execute the same sequence of collectives):
 * ``barrier()``            signal + wait on a dedicated channel (after the optimizer step, so that
                            no peer pulls a half-updated shard)
 
-All device-side waits are bounded (``flag_spin_limit`` polls); an expired wait records a code in
-``status`` which ``check_status()`` turns into an exception on the host.
+All device-side waits are bounded (``flag_spin_limit`` = time limit in microseconds, default three minutes:
+long enough for the skew an over-length sample causes at 70B scale; ``MTB200_FLAG_TIMEOUT_US`` overrides);
+an expired wait records a code in ``status`` which ``check_status()`` turns into an exception on the host.
 """
 from __future__ import annotations
 
@@ -59,7 +60,7 @@ class SymmetricComm:
             raise ValueError(f"symmetric backend supports up to {MAX_RANKS} ranks on one node")
         self.lib = load_library()
         self._bind()
-        self.flag_spin_limit = int(flag_spin_limit or os.environ.get("MTB200_FLAG_SPIN_LIMIT", 0))
+        self.flag_spin_limit = int(flag_spin_limit or os.environ.get("MTB200_FLAG_TIMEOUT_US", 0))   # 0 = the library default
         self.arena = None
         self._off = 0
         self._chan = {}
