@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "gather.cuh"
 #include "ptx.cuh"
@@ -49,6 +50,8 @@ struct GemmParams {
   const __nv_bfloat16* bias;  // optional, [N]
   int* status;            // device word; set non-zero when a bounded wait expired
   float alpha;            // the product is multiplied by alpha before bias and residual are added
+  int group_m;            // row-tiles per band of the tile order
+  unsigned wait_hint_ns;  // suspend-time hint of the epilogue's and the MMA thread's long waits (0: plain polling)
 };
 
 // The fused all-gather variant (GATHER = true) adds the gather warps and the flag checker of gather.cuh;
@@ -101,10 +104,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tm = local / cols;
       return;
     }
-    const int band = t / (GROUP_M * tiles_n);
-    const int first_m = band * GROUP_M;
-    const int rows = min(GROUP_M, tiles_m - first_m);
-    const int local = t - band * GROUP_M * tiles_n;
+    const int band = t / (p.group_m * tiles_n);
+    const int first_m = band * p.group_m;
+    const int rows = min(p.group_m, tiles_m - first_m);
+    const int local = t - band * p.group_m * tiles_n;
     tm = first_m + local % rows;
     tn = local / rows;
   };
@@ -157,7 +160,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tl) {
         const int acc = tl & 1;
         const uint32_t aph = (tl >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag)) { atomicExch(p.status, 2); goto done; }
+        if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag, p.wait_hint_ns)) { atomicExch(p.status, 2); goto done; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -209,7 +212,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tile_coords(t, tm, tn);
       const int acc = tl & 1;
       const uint32_t aph = (tl >> 1) & 1;
-      if (!mbar_wait(&tfull_bar[acc], aph, abort_flag)) { atomicExch(p.status, 4); goto done; }
+      if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.wait_hint_ns)) { atomicExch(p.status, 4); goto done; }
       tc_fence_after();
       const int row = tm * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -337,6 +340,18 @@ int make_tmap_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_
 
 static int g_num_sms = 0;
 
+// Tuning knobs read once from the environment (experiments; the defaults are what ships).
+static int tune_group_m() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("MTB200_GEMM_GROUP_M"); v = e ? atoi(e) : GROUP_M; if (v < 1) v = GROUP_M; }
+  return v;
+}
+static unsigned tune_wait_hint() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("MTB200_GEMM_WAIT_HINT_NS"); v = e ? atoi(e) : 0; if (v < 0) v = 0; }
+  return static_cast<unsigned>(v);
+}
+
 namespace g2 {
 int launch_gather(const void* A, long long lda, void* D, long long ldd, const void* bias, int M, int N, int K,
                   const void* w, int* status, const GatherParams& g, cudaStream_t stream);
@@ -387,7 +402,7 @@ int mtb200_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long
   if (b_mn) rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, 64);
   else rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);
   if (rc) return rc - 10;
-  GemmParams p{M, N, K, D, ldd, R, ldr, reinterpret_cast<const __nv_bfloat16*>(bias), status, alpha};
+  GemmParams p{M, N, K, D, ldd, R, ldr, reinterpret_cast<const __nv_bfloat16*>(bias), status, alpha, tune_group_m(), tune_wait_hint()};
   const int sel = (a_mn ? 4 : 0) | (b_mn ? 2 : 0) | (out_f32 ? 1 : 0);
   switch (sel) {
     case 0: return launch<false, false, false>(ta, tb, p, stream);
@@ -425,7 +440,7 @@ int mtb200_gemm_bf16_allgather(const void* A, long long lda, void* D, long long 
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&tb, reinterpret_cast<const unsigned char*>(full) + w_byte_off, K, N, K, BK, BN);
   if (rc) return rc - 10;
-  GemmParams p{M, N, K, D, ldd, nullptr, 0, reinterpret_cast<const __nv_bfloat16*>(bias), status, 1.0f};
+  GemmParams p{M, N, K, D, ldd, nullptr, 0, reinterpret_cast<const __nv_bfloat16*>(bias), status, 1.0f, tune_group_m(), tune_wait_hint()};
   GatherParams g{};
   for (int i = 0; i < world; ++i) g.peer_base[i] = bases[i];
   g.shard_off = shard_off; g.shard_bytes = shard_bytes; g.dst = reinterpret_cast<unsigned char*>(full);

@@ -50,10 +50,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the hardware may park the thread for up to `hint_ns` before it
+// answers, instead of the caller polling back to back.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait. `abort_flag` (shared memory) lets one role's timeout end all the others quickly.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// `hint_ns` > 0 uses the suspending form of try_wait (fewer polls while a long wait lasts).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t hint_ns = 0) {
   for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
