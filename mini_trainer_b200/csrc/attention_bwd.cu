@@ -271,16 +271,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       // The P tile still holds half of the previous dQ tile until its reduces have read it. The first 32
       // columns are computed before that wait; their stores then overlap the math of the other 32.
       uint32_t pk[2][16], dk[2][16];
+      const float2 sl2v = make_float2(sl2, sl2), nlse = make_float2(-lse2, -lse2);
+      const float2 scv = make_float2(p.scale, p.scale), nds = make_float2(-delta * p.scale, -delta * p.scale);
       auto compute = [&](int cc) {
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
+          // packed fp32 pairs: one FMA scales and shifts two scores, one FMA forms (dP - delta) * scale for both
+          const float2 a = ffma2(make_float2(__uint_as_float(sv_[cc][x]), __uint_as_float(sv_[cc][x + 1])), sl2v, nlse);
           // a quarter of the exponentials runs on the FMA pipe: the special-function unit bounds this phase
-          const float p0 = ex2_mufu(fmaf(__uint_as_float(sv_[cc][x]), sl2, -lse2));
-          const float a1 = fmaf(__uint_as_float(sv_[cc][x + 1]), sl2, -lse2);
-          const float p1 = (x & 2) ? ex2_fma(a1) : ex2_mufu(a1);
-          pk[cc][x >> 1] = pack_bf16(p0, p1);
-          dk[cc][x >> 1] = pack_bf16(p0 * (__uint_as_float(dv_[cc][x]) - delta) * p.scale,
-                                     p1 * (__uint_as_float(dv_[cc][x + 1]) - delta) * p.scale);
+          const float2 pr = make_float2(ex2_mufu(a.x), (x & 2) ? ex2_fma(a.y) : ex2_mufu(a.y));
+          const float2 dd = ffma2(make_float2(__uint_as_float(dv_[cc][x]), __uint_as_float(dv_[cc][x + 1])), scv, nds);
+          const float2 ds = fmul2(pr, dd);
+          pk[cc][x >> 1] = pack_bf16(pr.x, pr.y);
+          dk[cc][x >> 1] = pack_bf16(ds.x, ds.y);
         }
       };
       auto store = [&](int cc) {

@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mt = fmaxf(mt, __uint_as_float(sv[cc][i]));
+        for (int i = 0; i < 32; i += 2) mt = fmax3(mt, __uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1]));
       float factor = 1.f;
       bool rescale = false;
       if (mt > m_ref && (mt - m_ref) * sl2 > 8.f) {   // includes the first unmasked tile (m_ref = -inf)
@@ -251,25 +251,29 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       // probabilities -> bf16 P in shared memory (K-major, 128B swizzle), row sums; exp2(-inf) = 0 masks.
       // A state that has seen only masked entries so far (m_ref = -inf) writes zeros.
       const float mo = (m_ref == -INFINITY) ? 0.f : m_ref * sl2;
+      const float2 sl2v = make_float2(sl2, sl2), nmo = make_float2(-mo, -mo);
+      float2 l2 = make_float2(0.f, 0.f);   // this tile's row sum, two lanes of packed adds
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
         uint8_t* rowp = sp + (j & 1) * L::P_BYTES + (c >> 1) * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          float e[8];
+          float2 e[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float x = fmaf(__uint_as_float(sv[cc][g * 8 + i]), sl2, -mo);
-            e[i] = (i % POLY == POLY - 1) ? ex2_fma(x) : ex2_mufu(x);
-            l += e[i];
+          for (int i = 0; i < 4; ++i) {
+            // scale and shift two scores with one packed FMA; of every POLY pairs one runs its exponentials on the FMA pipe
+            const float2 x = ffma2(make_float2(__uint_as_float(sv[cc][g * 8 + 2 * i]), __uint_as_float(sv[cc][g * 8 + 2 * i + 1])), sl2v, nmo);
+            e[i] = (i % POLY == POLY - 1) ? ex2_fma2(x) : make_float2(ex2_mufu(x.x), ex2_mufu(x.y));
+            l2 = fadd2(l2, e[i]);
           }
           const int chunk = (c & 1) * 4 + g;
           uint4 o;
-          o.x = pack_bf16(e[0], e[1]); o.y = pack_bf16(e[2], e[3]); o.z = pack_bf16(e[4], e[5]); o.w = pack_bf16(e[6], e[7]);
+          o.x = pack_bf16(e[0].x, e[0].y); o.y = pack_bf16(e[1].x, e[1].y); o.z = pack_bf16(e[2].x, e[2].y); o.w = pack_bf16(e[3].x, e[3].y);
           *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = o;
         }
       }
+      l += l2.x + l2.y;
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();

@@ -216,6 +216,34 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
   return __bfloat1622float2(v);
 }
 
+// Packed fp32 pairs (sm_100): one instruction for two independent fp32 operations, and a three-input
+// maximum. The softmax warps of the attention kernels are bound by instruction issue, not by the
+// tensor core, so halving their FMA / ADD / MAX count is what these are for.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{.reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2,%3};\n mov.b64 rb, {%4,%5};\n mov.b64 rc, {%6,%7};\n"
+      " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0,%1}, rd;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{.reg .b64 ra, rb, rd;\n mov.b64 ra, {%2,%3};\n mov.b64 rb, {%4,%5};\n add.f32x2 rd, ra, rb;\n mov.b64 {%0,%1}, rd;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{.reg .b64 ra, rb, rd;\n mov.b64 ra, {%2,%3};\n mov.b64 rb, {%4,%5};\n mul.f32x2 rd, ra, rb;\n mov.b64 {%0,%1}, rd;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // 2^x on the special-function unit: one MUFU.EX2 (16 per clock per SM). ex2(-inf) = +0.
 __device__ __forceinline__ float ex2_mufu(float x) {
   float y;
@@ -236,6 +264,19 @@ __device__ __forceinline__ float ex2_fma(float x) {
   p = fmaf(f, p, 0.69328292f);
   p = fmaf(f, p, 1.0f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+// The same cubic on a pair of inputs with packed fp32 instructions.
+__device__ __forceinline__ float2 ex2_fma2(float2 x) {
+  x.x = fmaxf(x.x, -126.f); x.y = fmaxf(x.y, -126.f);
+  const float2 magic = make_float2(12582912.f, 12582912.f);
+  const float2 t = fadd2(x, magic);
+  const float2 f = fadd2(x, fadd2(magic, make_float2(-t.x, -t.y)));   // x - (t - magic)
+  float2 p = ffma2(f, make_float2(0.05500871f, 0.05500871f), make_float2(0.24221068f, 0.24221068f));
+  p = ffma2(f, p, make_float2(0.69328292f, 0.69328292f));
+  p = ffma2(f, p, make_float2(1.0f, 1.0f));
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
 }
 
 }  // namespace mtb
