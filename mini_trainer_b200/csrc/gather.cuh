@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "flags.cuh"
 #include "ptx.cuh"
 
 namespace mtb {
@@ -35,7 +36,17 @@ struct GatherParams {
   int world;
   int chunk_lo, chunk_hi;          // chunks this launch gathers
   int chunk_first;                 // gather order starts here (the chunks under B), wraps inside [lo, hi)
-  unsigned long long b_byte_off;   // byte offset of B's first element inside dst
+  unsigned long long b_byte_off;   // byte offset of the gathered GEMM operand's first element inside dst
+  // ---- reduce mode (the gathered operand is the SUM over ranks of a region of their gradient buffers) ----
+  unsigned long long src_off;      // byte offset of the region inside every rank's arena
+  unsigned long long total_bytes;  // bytes of the region (= bytes of dst)
+  const unsigned int* ready_flags; // local row of "my buffer is complete" epochs, one per rank
+  unsigned long long consumed_off; // byte offset of the "consumed" row inside every rank's arena
+  unsigned int* done;              // counter of CTAs whose gather warps have finished (zeroed by the host)
+  unsigned int rs_epoch;           // epoch of the ready / consumed handshake
+  unsigned int limit_us;           // bound of the wait for the peers' ready flags
+  int rank;
+  int* status;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_cta_shared(const uint32_t* p) {
@@ -98,6 +109,67 @@ __device__ __forceinline__ void gather_chunks(const GatherParams& g, int gt, uin
     __threadfence();
     asm volatile("bar.sync 1, %0;" ::"n"(GATHER_THREADS) : "memory");
     if (gt == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.flags + c), "r"(g.epoch) : "memory");
+  }
+}
+
+// Reduce form of the gather warps: chunk by chunk, dst = bf16(sum over all ranks of their copy of the
+// region), read with plain peer loads, summed in fp32. This is the gradient reduce-scatter with ownership
+// by tensor, run inside the GEMM that consumes the reduced gradient: the handshake is the reduce-scatter's
+// (wait for every rank's "ready" epoch before the first load, signal "consumed" to every rank after the
+// last one). A wait that runs out records code 46 and the kernel carries on (the host raises).
+template <int MAXW>
+__device__ __forceinline__ void reduce_chunks(const GatherParams& g, int gt, uint32_t* slot) {
+  if (gt < g.world && !wait_flag(g.ready_flags + gt, g.rs_epoch, g.limit_us)) atomicExch(g.status, 46 | (gt << 8));
+  asm volatile("bar.sync 1, %0;" ::"n"(GATHER_THREADS) : "memory");
+  const int n_chunks = g.chunk_hi - g.chunk_lo;
+  while (true) {
+    if (gt == 0) *slot = atomicAdd(g.ticket, 1u);
+    asm volatile("bar.sync 1, %0;" ::"n"(GATHER_THREADS) : "memory");
+    const uint32_t k = *slot;
+    asm volatile("bar.sync 1, %0;" ::"n"(GATHER_THREADS) : "memory");
+    if (k >= static_cast<uint32_t>(n_chunks)) break;
+    const int c = g.chunk_lo + static_cast<int>(k);      // front to back: the GEMM consumes its operand in row order
+    const unsigned long long b0 = static_cast<unsigned long long>(c) * GATHER_CHUNK_BYTES;
+    const unsigned long long b1 = min(b0 + GATHER_CHUNK_BYTES, g.total_bytes);
+    const unsigned long long nv = (b1 - b0) >> 4;
+    uint4* dst = reinterpret_cast<uint4*>(g.dst + b0);
+    for (unsigned long long j = gt; j < nv; j += 2 * GATHER_THREADS) {
+      uint4 v[2][MAXW];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const unsigned long long jj = j + u * GATHER_THREADS;
+        if (jj < nv) {
+#pragma unroll
+          for (int p = 0; p < MAXW; ++p)
+            if (p < g.world) v[u][p] = *(reinterpret_cast<const uint4*>(g.peer_base[p] + g.src_off + b0) + jj);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const unsigned long long jj = j + u * GATHER_THREADS;
+        if (jj >= nv) continue;
+        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int p = 0; p < MAXW; ++p) {
+          if (p < g.world) {
+            const float2 a = unpack_bf16(v[u][p].x), b = unpack_bf16(v[u][p].y), cc = unpack_bf16(v[u][p].z), d = unpack_bf16(v[u][p].w);
+            f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y; f[4] += cc.x; f[5] += cc.y; f[6] += d.x; f[7] += d.y;
+          }
+        }
+        dst[jj] = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+      }
+    }
+    __threadfence();
+    asm volatile("bar.sync 1, %0;" ::"n"(GATHER_THREADS) : "memory");
+    if (gt == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.flags + c), "r"(g.epoch) : "memory");
+  }
+  // The last CTA whose gather warps run out of chunks tells every rank that its buffer has been read.
+  __shared__ int last_s;
+  if (gt == 0) last_s = (atomicAdd(g.done, 1u) == gridDim.x - 1);
+  asm volatile("bar.sync 1, %0;" ::"n"(GATHER_THREADS) : "memory");
+  if (last_s && gt < g.world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(g.peer_base[gt] + g.consumed_off) + g.rank, g.rs_epoch);
   }
 }
 

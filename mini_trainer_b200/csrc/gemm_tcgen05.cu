@@ -56,7 +56,10 @@ struct GemmParams {
 
 // The fused all-gather variant (GATHER = true) adds the gather warps and the flag checker of gather.cuh;
 // its tiles are visited in bands of GATHER_GROUP_N column-tiles.
-template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false>
+// REDUCE (with GATHER): the gathered operand is A, and it is the SUM over ranks of a region of their gradient
+// buffers (reduce_chunks in gather.cuh): the gradient reduce-scatter with ownership by tensor, fused into the GEMM
+// that consumes the reduced gradient (OSFT factor gradients).
+template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false, bool REDUCE = false>
 __global__ void __launch_bounds__(GATHER ? GEMM_THREADS + GATHER_EXTRA_THREADS : GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p,
             const __grid_constant__ GatherParams g) {
@@ -92,7 +95,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
 
   auto tile_coords = [&](int t, int& tm, int& tn) {
-    if constexpr (GATHER) {
+    if constexpr (GATHER && !REDUCE) {
       // Bands of GROUP_N column-tiles, all row-tiles inside a band: the weight is consumed front to
       // back at an even rate over the whole launch (a band of row-tiles would need the ENTIRE weight
       // within its first band, i.e. within the first few waves, faster than the links deliver it).
@@ -188,9 +191,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tl) {
       int tm, tn;
       tile_coords(t, tm, tn);
-      // rows [tn*BN, tn*BN+BN) of the K-major weight are one contiguous byte range of the full buffer
-      const unsigned long long lo = g.b_byte_off + static_cast<unsigned long long>(tn) * BN * p.K * 2;
-      const int rows = min(BN, p.N - tn * BN);
+      // rows [tn*BN, tn*BN+BN) of the K-major weight (reduce mode: rows [tm*BM, tm*BM+BM) of the K-major A operand)
+      // are one contiguous byte range of the gathered buffer
+      const unsigned long long lo = g.b_byte_off + static_cast<unsigned long long>(REDUCE ? tm * BM : tn * BN) * p.K * 2;
+      const int rows = REDUCE ? min(BM, p.M - tm * BM) : min(BN, p.N - tn * BN);
       const unsigned long long hi = lo + static_cast<unsigned long long>(rows) * p.K * 2 - 1;
       const bool ok = wait_chunks(g, lo, hi, lane, abort_flag);
       __syncwarp();
@@ -202,7 +206,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (GATHER && warp >= 6) {
     // ------------------------------------------------------------------ gather warps (6..13)
-    gather_chunks(g, threadIdx.x - GEMM_THREADS, ticket_slot);
+    if constexpr (REDUCE) reduce_chunks<8>(g, threadIdx.x - GEMM_THREADS, ticket_slot);
+    else gather_chunks(g, threadIdx.x - GEMM_THREADS, ticket_slot);
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -357,11 +362,11 @@ int launch_gather(const void* A, long long lda, void* D, long long ldd, const vo
                   const void* w, int* status, const GatherParams& g, cudaStream_t stream);
 }
 
-template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false>
+template <bool A_MN, bool B_MN, bool OUT_F32, bool GATHER = false, bool REDUCE = false>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream,
                   const GatherParams* gp = nullptr) {
   static bool configured = false;
-  auto kern = gemm_kernel<A_MN, B_MN, OUT_F32, GATHER>;
+  auto kern = gemm_kernel<A_MN, B_MN, OUT_F32, GATHER, REDUCE>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess) return -4;
     configured = true;
@@ -456,6 +461,41 @@ int mtb200_gemm_bf16_allgather(const void* A, long long lda, void* D, long long 
     if (rc != -6) return rc;   // -6: CTA pairs cannot be scheduled here; fall through to the one-CTA kernel
   }
   return launch<false, false, false, true>(ta, tb, p, stream, &g);
+}
+
+// Fused gradient reduce + GEMM:  D[M,N] (fp32) = (sum over ranks of G_r)[M,K] * B[N,K]^T (+ R), where G_r is the region
+// [src_off, src_off + M*K*2) of rank r's arena (a tensor of its block gradient buffer). Gather warps pull the region from
+// every rank, sum in fp32 and write bf16 into `dst` (local, M*K elements), which the TMA producer reads as the A operand as
+// its chunks complete. Handshake of the reduce-scatter: waits for every rank's ready epoch, signals consumed when done.
+//   flags/epoch   per-chunk completion words of dst;  ticket, done: device words, zeroed here
+//   ready_flags   local row of ready epochs;  consumed_off: byte offset of the consumed row in every arena
+int mtb200_gemm_bf16_reduce_a(void* dst, const void* B, long long ldb, float* D, long long ldd, const float* R, long long ldr,
+                              int M, int N, int K, const unsigned long long* bases, int world, int rank,
+                              unsigned long long src_off, unsigned int* flags, unsigned int epoch, unsigned int* ticket,
+                              unsigned int* done, const void* ready_flags, unsigned long long consumed_off, unsigned int rs_epoch,
+                              unsigned int limit_us, int* status, cudaStream_t stream) {
+  using namespace mtb;
+  if (M <= 0 || N <= 0 || K <= 0) return -10;
+  if (N % 8 || ldd % 8 || K % 8 || (R && ldr % 8) || world < 1 || world > 8 || src_off % 16 || ticket == nullptr || done == nullptr) return -10;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, dst, K, M, K, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);
+  if (rc) return rc - 10;
+  GemmParams p{M, N, K, D, ldd, R, ldr, nullptr, status, 1.0f, tune_group_m(), tune_wait_hint()};
+  GatherParams g{};
+  for (int i = 0; i < world; ++i) g.peer_base[i] = bases[i];
+  g.dst = reinterpret_cast<unsigned char*>(dst);
+  g.total_bytes = static_cast<unsigned long long>(M) * K * 2;
+  g.flags = flags; g.epoch = epoch; g.world = world; g.rank = rank;
+  g.chunk_lo = 0; g.chunk_hi = static_cast<int>((g.total_bytes + GATHER_CHUNK_BYTES - 1) / GATHER_CHUNK_BYTES);
+  g.chunk_first = 0; g.b_byte_off = 0;
+  g.ticket = ticket; g.done = done; g.wait_ns = nullptr;
+  g.src_off = src_off; g.ready_flags = reinterpret_cast<const unsigned int*>(ready_flags); g.consumed_off = consumed_off;
+  g.rs_epoch = rs_epoch; g.limit_us = limit_us ? limit_us : FLAG_SPIN_LIMIT; g.status = status;
+  if (cudaMemsetAsync(ticket, 0, sizeof(unsigned int), stream) != cudaSuccess) return -5;
+  if (cudaMemsetAsync(done, 0, sizeof(unsigned int), stream) != cudaSuccess) return -5;
+  return launch<false, false, true, true, true>(ta, tb, p, stream, &g);
 }
 
 }  // extern "C"

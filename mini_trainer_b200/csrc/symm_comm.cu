@@ -20,48 +20,16 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "flags.cuh"
 #include "ptx.cuh"
 
 namespace mtb {
 
 constexpr int MAX_RANKS = 16;
-// Default bound of a wait on a peer's flag, in microseconds. It has to cover legitimate skew between
-// ranks (one rank holding an over-length sample, a first-touch allocation of pinned memory), which at 70B
-// scale is tens of seconds; a peer that is really gone still ends the wait, just later. Tests pass a
-// bound of a few milliseconds.
-constexpr uint32_t FLAG_SPIN_LIMIT = 180u * 1000u * 1000u;
 
 struct PeerTable {
   uint64_t base[MAX_RANKS];   // device address of every rank's arena, as mapped into this process
 };
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// Waits until *flag >= epoch (wrap-safe). Bounded twice: by `limit_us` microseconds of the global
-// timer and by a fixed number of polls. Returns false when a bound is hit.
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t limit_us) {
-  if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-  unsigned long long t0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  const unsigned long long budget = static_cast<unsigned long long>(limit_us) * 1000ull;
-  for (uint32_t i = 0; i < 0x7fffffffu; ++i) {
-    if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    __nanosleep(200);
-    if ((i & 31u) == 31u) {
-      unsigned long long t;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-      if (t - t0 > budget) return false;
-    }
-  }
-  return false;
-}
 
 // ---------------------------------------------------------------------------------- all-gather
 // dst[p * shard_bytes + i] = arena_p[src_off + i] for every rank p; 16-byte accesses.

@@ -189,6 +189,10 @@ class OSFT:
         self.passes = projection_passes if self.kernels else 1
         # ownership by matrix inside the reduction itself needs the symmetric backend's kernels
         self.owner_reduce = bool(engine.symmetric) and self.world > 1 and self.kernels
+        # the reduction of a projection's gradient runs INSIDE the tcgen05 GEMM that forms G V_lo^T (up to 8 ranks)
+        import os as _os
+        self.fused = self.owner_reduce and self.world <= 8 and _os.environ.get("MTB200_OSFT_FUSED", "1") != "0"
+        self._want_fused = self.fused
         self.mats: list[_Matrix] = []
         cfg = engine.cfg
         lay = engine.blocks[0].layout
@@ -203,6 +207,8 @@ class OSFT:
                                          r1 - r0, cols, k_hi, k - k_hi))
                 idx += 1
         self.by_block = [[m for m in self.mats if m.block == b] for b in range(len(engine.blocks))]
+        if any(m.out % 8 or m.cols % 8 or m.k_lo % 8 for m in self.mats):   # TMA strides of the fused kernel's operands
+            self.fused = False
         self._alloc_and_decompose()
 
     # -- set-up ---------------------------------------------------------------------------
@@ -255,11 +261,18 @@ class OSFT:
                 mt.u_hi, mt.v_hi = u_hi.to(hdt).contiguous(), v_hi.to(hdt).contiguous()
                 u, s, v = self._fac_views(mt, self.fac)
                 u.copy_(u_lo); s.copy_(s_lo); v.copy_(v_lo)
-                if self.owner_reduce:
+                if self.owner_reduce and not self.fused:
                     mt.g_acc = torch.zeros(mt.out, mt.cols, dtype=torch.float32, device=dev)
             del full
         if self.kernels:
             self.fac16.copy_(self.fac)
+        if self.fused:
+            # one staging buffer for the reduced bf16 gradient of whichever projection is being processed, and the
+            # completion words of its 128 KB chunks
+            biggest = max((m.out * m.cols for m in self._mine()), default=8)
+            self.g_red = torch.empty(biggest, dtype=torch.bfloat16, device=dev)
+            self.red_flags = torch.zeros(-(-biggest * 2 // (128 * 1024)) + 1, dtype=torch.int32, device=dev)
+            self.red_epoch = 0
         if self.owner_reduce:
             # the slice reduction never touches the projections' regions of the accumulators again: they must
             # read as zero gradient for the engine's AdamW pass from now on
@@ -293,9 +306,23 @@ class OSFT:
             for mt in (m for m in mats.values() if m.name == name):
                 k = state["k"]; state["k"] += 1
                 eng.comm.grad_ready(gbuf, k)
+                mine = mt.owner == self.rank
                 with eng.side.run(wait_current=True):
-                    eng.comm.reduce_to_owner(gbuf, mt.g_acc, mt.has_grad, mt.owner, mt.elem_lo, mt.elem_hi, region=k)
-                if mt.owner == self.rank:
+                    if not self.fused:
+                        eng.comm.reduce_to_owner(gbuf, mt.g_acc, mt.has_grad, mt.owner, mt.elem_lo, mt.elem_hi, region=k)
+                    elif not mine:
+                        eng.comm.reduce_gemm_to_owner(eng.ops, gbuf, mt.owner, mt.elem_lo, mt.out, mt.cols, k, None, None, None, False, None, 0)
+                    else:
+                        # G V_lo^T with the reduction fused in (accumulated over microbatches in the gradient slot of
+                        # U_lo), then U_lo^T G on the reduced gradient the kernel left behind (slot of V_lo)
+                        u16, _, v16 = self._fac_views(mt, self.fac16)
+                        gu, _, gv = self._fac_views(mt, self.fac_g)
+                        self.red_epoch += 1
+                        staged = self.g_red[: mt.out * mt.cols].view(mt.out, mt.cols)
+                        eng.comm.reduce_gemm_to_owner(eng.ops, gbuf, mt.owner, mt.elem_lo, mt.out, mt.cols, k, staged, v16, gu,
+                                                      mt.has_grad, self.red_flags, self.red_epoch)
+                        self._mm(u16, True, staged, False, residual=gv if mt.has_grad else None, out=gv)
+                if mine:
                     mt.has_grad = True
 
         def reduce_small(names, final):
@@ -332,7 +359,11 @@ class OSFT:
             x, y = (x.float(), y.float()) if self.kernels else (x, y)
             r = (x.t() if x_t else x) @ (y.t() if y_t else y)
             r = r * alpha if alpha != 1.0 else r
-            return r + residual if residual is not None else r
+            r = r + residual if residual is not None else r
+            if out is not None:
+                out.copy_(r)
+                return out
+            return r
         bf = torch.bfloat16
         x16 = x if x.dtype == bf else x.to(bf)
         y16 = y if y.dtype == bf else y.to(bf)
@@ -358,6 +389,23 @@ class OSFT:
                 du = self._mm(mt.u_hi, False, p, False, alpha=-1.0, residual=du.float() if self.kernels else du)
                 r = self._mm(dv, False, mt.v_hi, True)          # dV V_hi^T
                 dv = self._mm(r, False, mt.v_hi, False, alpha=-1.0, residual=dv.float() if self.kernels else dv)
+        gu.copy_(du)
+        gv.copy_(dv)
+
+    def _finish_factor_grads(self, mt: _Matrix) -> None:
+        """Fused path: the gradient slots of U_lo and V_lo hold the raw products ``G V_lo^T`` and ``U_lo^T G``
+        accumulated during backward; turns them into the projected factor gradients in place."""
+        u, s, v = self._fac_views(mt, self.fac)
+        gu, gs, gv = self._fac_views(mt, self.fac_g)
+        gs.copy_((u * gu).sum(0))
+        du = gu * s
+        dv = gv * s.unsqueeze(1)
+        if mt.k_hi:
+            for _ in range(self.passes):
+                p = self._mm(mt.u_hi, True, du, False)
+                du = self._mm(mt.u_hi, False, p, False, alpha=-1.0, residual=du)
+                r = self._mm(dv, False, mt.v_hi, True)
+                dv = self._mm(r, False, mt.v_hi, False, alpha=-1.0, residual=dv)
         gu.copy_(du)
         gv.copy_(dv)
 
@@ -418,11 +466,20 @@ class OSFT:
         sq = eng._sq if self.owner_reduce else torch.zeros(1, dtype=torch.float32, device=dev)
         stepped = False
         # 1. projected factor gradients on the owners
-        self.fac_g.zero_()
+        if not self.fused:
+            self.fac_g.zero_()
         for b, grp in enumerate(eng.blocks):
             if self.owner_reduce:
-                for mt in (m for m in self.by_block[b] if m.owner == self.rank and m.has_grad):
-                    self._factor_grads(mt, mt.g_acc)
+                for mt in (m for m in self.by_block[b] if m.owner == self.rank):
+                    gu, gs, gv = self._fac_views(mt, self.fac_g)
+                    if not mt.has_grad:
+                        if self.fused:
+                            gu.zero_(); gs.zero_(); gv.zero_()
+                        continue
+                    if self.fused:
+                        self._finish_factor_grads(mt)
+                    else:
+                        self._factor_grads(mt, mt.g_acc)
                     mt.has_grad = False
                     stepped = True
                 continue

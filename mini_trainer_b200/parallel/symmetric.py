@@ -80,6 +80,7 @@ class SymmetricComm:
             "mtb200_symm_reduce_scatter": [P, I, I, UL, L, L, P, I, P, P, UL, U, U, P, P, I, P],
             "mtb200_symm_allreduce_scalar": [P, I, I, UL, UL, P, P, U, U, P, P, P],
             "mtb200_symm_pull": [P, I, I, UL, P, UL, I, P],
+            "mtb200_gemm_bf16_reduce_a": [P, P, L, P, L, P, L, I, I, I, P, I, I, UL, P, U, P, P, P, UL, U, U, P, P],
             "mtb200_symm_reduce_scatter_nvls": [UL, P, I, I, UL, L, L, P, I, P, P, UL, U, U, P, P, I, P],
         }
         for name, args in sig.items():
@@ -114,6 +115,8 @@ class SymmetricComm:
         self._ticket = torch.zeros(1, dtype=torch.int32, device=self.device)       # chunk tickets of the fused gather
         self._gather_wait = torch.zeros(2, dtype=torch.int64, device=self.device)  # producer wait (ns) summed over CTAs, CTA count
         self._gather_launches = 0
+        # the fused reduce + GEMM runs on the side stream next to gathering GEMMs of the compute stream: words of its own
+        self._red_words = torch.zeros(2, dtype=torch.int32, device=self.device)    # chunk ticket, CTA counter
         self._barrier_ch = self._new_channel("barrier")
         self._scalar_ch = [self._new_channel("scalar0"), self._new_channel("scalar1")]
         self._scalar_calls = 0
@@ -245,6 +248,31 @@ class SymmetricComm:
                 self.arena.data_ptr() + self._ready_off(ch), self._consumed_off(ch), self._epoch[ch], self.flag_spin_limit,
                 self._counter.data_ptr(), self.status.data_ptr(), blocks, self._st())
         self._call(fn, *(((self.mc_ptr,) + args) if self.nvls else args))
+
+    def reduce_gemm_to_owner(self, ops, gfull, owner: int, elem_lo: int, rows: int, cols: int, region: int, staged, b16, out32,
+                             accumulate: bool, flags, epoch: int):
+        """Fused gradient reduction + GEMM on rank ``owner``: ``out32 (+)= (sum over ranks of G) @ b16.T`` where ``G`` is
+        the ``[rows, cols]`` tensor at element ``elem_lo`` of every rank's ``gfull``. The kernel's gather warps pull the
+        region from all ranks, sum in fp32 and leave the reduced bf16 gradient in ``staged`` (the GEMM's A operand,
+        consumed as its chunks complete; it stays valid afterwards for further products). The other ranks only take part
+        in the ready / consumed handshake."""
+        ch = self._channel(gfull, region)
+        if self.rank != owner:
+            self._call("mtb200_symm_reduce_scatter", self._bases, self.world, self.rank, self._offset(gfull), 0, 0, None, 0, None,
+                       self.arena.data_ptr() + self._ready_off(ch), self._consumed_off(ch), self._epoch[ch], self.flag_spin_limit,
+                       self._counter.data_ptr(), self.status.data_ptr(), 1, self._st())
+            return
+        n = out32.shape[1]
+        rc = self.lib.mtb200_gemm_bf16_reduce_a(
+            staged.data_ptr(), b16.data_ptr(), b16.stride(0), out32.data_ptr(), out32.stride(0),
+            out32.data_ptr() if accumulate else None, out32.stride(0), rows, n, cols, self._bases, self.world, self.rank,
+            self._offset(gfull) + elem_lo * 2, flags.data_ptr(), epoch, self._red_words.data_ptr(), self._red_words.data_ptr() + 4,
+            self.arena.data_ptr() + self._ready_off(ch), self._consumed_off(ch), self._epoch[ch], self.flag_spin_limit,
+            ops.status.data_ptr(), ops._st())
+        if rc != 0:
+            raise RuntimeError(f"mtb200_gemm_bf16_reduce_a failed with code {rc}")
+        ops.launches += 1
+        self.launches += 1
 
     def pull(self, owner: int, src: torch.Tensor, src_elem_off: int, dst: torch.Tensor, blocks: int = 64):
         """``dst[:] = owner's copy of src[src_elem_off : src_elem_off + dst.numel()]``. ``src`` is this rank's

@@ -40,6 +40,7 @@ if os.environ.get("MTB200_OSFT") == "1":
     ctl = enable_osft(eng, rank_ratio=0.5)
     if world > 1 and os.environ.get("MTB200_COMM") == "symmetric":
         assert ctl.owner_reduce and ctl.kernels      # ownership by matrix inside the reduction, products on tcgen05
+        assert ctl.fused == (os.environ.get("MTB200_OSFT_FUSED", "1") != "0")   # ... and the reduction inside the GEMM itself
 init = [g.master.clone() for g in eng.groups]
 ds = synthetic_dataset(64, LengthSpec(5.0, 0.7, 8, 700), cfg.vocab_size, seed=1)
 loader = iter(get_data_loader(dataset=ds, batch_size=16, max_tokens_per_gpu=1500, seed=3, rank=rank, world_size=world, prefetch=0))
@@ -72,13 +73,13 @@ dist.destroy_process_group()
 '''
 
 
-def _run(world: int, comm: str, budget: str = "0", out: str = "", osft: bool = False):
+def _run(world: int, comm: str, budget: str = "0", out: str = "", osft: bool = False, extra_env=None):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     # MTB200_POISON: gather targets and gradient buffers are NaN-filled before use, so anything consumed before it
     # arrived (or never written) turns the loss / gradient norm into NaN
     env = dict(os.environ, MTB200_REPO=REPO, MTB200_COMM=comm, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1",
                MASTER_PORT=str(port), MTB200_TEST_BUDGET=budget, MTB200_OUT=out, MTB200_POISON="1",
-               MTB200_OSFT="1" if osft else "0")
+               MTB200_OSFT="1" if osft else "0", **(extra_env or {}))
     if world == 1:
         cmd = [sys.executable, "-c", WORKER]
     else:
@@ -117,16 +118,18 @@ def test_two_gpus_match_one_gpu(comm, budget, tmp_path):
     _compare(one, two, f1, f2)
 
 
-@pytest.mark.parametrize("comm", ["symmetric", "torchdist"])
-def test_osft_two_gpus_match_one_gpu(comm, tmp_path):
-    """OSFT on 2 GPUs against OSFT on 1 GPU. Symmetric backend: projection gradients reduced to the owning
-    rank inside the reduce-scatter kernel, factor products on the tcgen05 GEMM, recomposed weights pulled over
-    NVLink, no NCCL call in the step. NCCL backend: gather / broadcast form of the same update."""
+@pytest.mark.parametrize("comm,fused", [("symmetric", "1"), ("symmetric", "0"), ("torchdist", "1")])
+def test_osft_two_gpus_match_one_gpu(comm, fused, tmp_path):
+    """OSFT on 2 GPUs against OSFT on 1 GPU. Symmetric backend: each projection's gradient is pulled from all
+    ranks, summed and multiplied by V_lo^T in ONE tcgen05 GEMM kernel on the owning rank (fused = 1), or reduced to
+    the owner by the reduce-scatter kernel first (fused = 0); the other factor products run on the tcgen05 GEMM, the
+    recomposed weights are pulled over NVLink, and no NCCL call is made in the step. NCCL backend: gather /
+    broadcast form of the same update."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     f1, f2 = str(tmp_path / "one.pt"), str(tmp_path / "two.pt")
     one = _run(1, "auto", out=f1, osft=True)
-    two = _run(2, comm, "0", out=f2, osft=True)
+    two = _run(2, comm, "0", out=f2, osft=True, extra_env={"MTB200_OSFT_FUSED": fused})
     _compare(one, two, f1, f2)
 
 
