@@ -175,8 +175,10 @@ __device__ __forceinline__ void reduce_chunks(const GatherParams& g, int gt, uin
 
 // Flag checker (one warp): waits until every chunk that overlaps bytes [lo, hi] of the full buffer
 // carries this launch's epoch. Returns false when the bound ran out or another role aborted.
+// `limit_us` > 0: time bound instead of the poll count (reduce mode, see mbar_wait).
 __device__ __forceinline__ bool wait_chunks(const GatherParams& g, unsigned long long lo, unsigned long long hi, int lane,
-                                            volatile int* abort_flag) {
+                                            volatile int* abort_flag, uint32_t limit_us = 0) {
+  const unsigned long long t0 = globaltimer_ns(), budget = static_cast<unsigned long long>(limit_us) * 1000ull;
   const int c_hi = static_cast<int>(hi / GATHER_CHUNK_BYTES);
   for (int c0 = static_cast<int>(lo / GATHER_CHUNK_BYTES); c0 <= c_hi; c0 += 32) {
     const int c = c0 + lane;
@@ -186,7 +188,9 @@ __device__ __forceinline__ bool wait_chunks(const GatherParams& g, unsigned long
       if (!ok) ok = ld_acquire_gpu(g.flags + c) == g.epoch;
       if (__all_sync(0xffffffffu, ok)) break;
       ++spins;
-      const bool stop = spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag);
+      bool stop;
+      if (limit_us == 0) stop = spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag);
+      else stop = (spins & 1023u) == 0 && (*abort_flag || globaltimer_ns() - t0 > budget);
       if (__any_sync(0xffffffffu, stop)) return false;
     }
   }
@@ -196,12 +200,14 @@ __device__ __forceinline__ bool wait_chunks(const GatherParams& g, unsigned long
 // TMA producer side: waits until the checker has verified tile number `tl` of this CTA; adds the
 // time spent waiting to `waited_ns`. Returns false on timeout / abort.
 __device__ __forceinline__ bool wait_verified(const uint32_t* verified, uint32_t tl, volatile int* abort_flag,
-                                              unsigned long long& waited_ns) {
+                                              unsigned long long& waited_ns, uint32_t limit_us = 0) {
   if (ld_acquire_cta_shared(verified) > tl) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  const unsigned long long t0 = globaltimer_ns(), budget = static_cast<unsigned long long>(limit_us) * 1000ull;
   uint32_t spins = 0;
   while (ld_acquire_cta_shared(verified) <= tl) {
-    if (++spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag)) return false;
+    ++spins;
+    if (limit_us == 0) { if (spins > SPIN_LIMIT || ((spins & 1023u) == 0 && *abort_flag)) return false; }
+    else if ((spins & 1023u) == 0 && (*abort_flag || globaltimer_ns() - t0 > budget)) return false;
   }
   waited_ns += globaltimer_ns() - t0;
   return true;

@@ -52,6 +52,7 @@ struct GemmParams {
   float alpha;            // the product is multiplied by alpha before bias and residual are added
   int group_m;            // row-tiles per band of the tile order
   unsigned wait_hint_ns;  // suspend-time hint of the epilogue's and the MMA thread's long waits (0: plain polling)
+  unsigned wait_limit_us; // > 0: every pipeline wait is bounded by this time instead of a poll count (fused reduce + GEMM)
 };
 
 // The fused all-gather variant (GATHER = true) adds the gather warps and the flag checker of gather.cuh;
@@ -125,14 +126,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         tile_coords(t, tm, tn);
         if (GATHER) {
           // the checker warp has seen the flags of every chunk under this tile's B rows
-          if (!wait_verified(verified, tl, abort_flag, waited_ns)) { *abort_flag = 1; atomicExch(p.status, 5); goto done; }
+          if (!wait_verified(verified, tl, abort_flag, waited_ns, p.wait_limit_us)) { *abort_flag = 1; atomicExch(p.status, 5); goto done; }
           asm volatile("fence.proxy.async;" ::: "memory");   // peer data was written with ordinary stores, TMA reads it
           ++tl;
         }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { atomicExch(p.status, 1); goto done; }
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, 0, p.wait_limit_us)) { atomicExch(p.status, 1); goto done; }
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
           mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
@@ -163,13 +164,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tl) {
         const int acc = tl & 1;
         const uint32_t aph = (tl >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag, p.wait_hint_ns)) { atomicExch(p.status, 2); goto done; }
+        if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abort_flag, p.wait_hint_ns, p.wait_limit_us)) { atomicExch(p.status, 2); goto done; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { atomicExch(p.status, 3); goto done; }
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, 0, p.wait_limit_us)) { atomicExch(p.status, 3); goto done; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sb = sa + A_TILE_BYTES;
@@ -196,7 +197,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const unsigned long long lo = g.b_byte_off + static_cast<unsigned long long>(REDUCE ? tm * BM : tn * BN) * p.K * 2;
       const int rows = REDUCE ? min(BM, p.M - tm * BM) : min(BN, p.N - tn * BN);
       const unsigned long long hi = lo + static_cast<unsigned long long>(rows) * p.K * 2 - 1;
-      const bool ok = wait_chunks(g, lo, hi, lane, abort_flag);
+      const bool ok = wait_chunks(g, lo, hi, lane, abort_flag, p.wait_limit_us);
       __syncwarp();
       if (!ok) {
         if (lane == 0) { *abort_flag = 1; atomicExch(p.status, 5); }
@@ -217,7 +218,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tile_coords(t, tm, tn);
       const int acc = tl & 1;
       const uint32_t aph = (tl >> 1) & 1;
-      if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.wait_hint_ns)) { atomicExch(p.status, 4); goto done; }
+      if (!mbar_wait(&tfull_bar[acc], aph, abort_flag, p.wait_hint_ns, p.wait_limit_us)) { atomicExch(p.status, 4); goto done; }
       tc_fence_after();
       const int row = tm * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -407,7 +408,7 @@ int mtb200_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long
   if (b_mn) rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, 64);
   else rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);
   if (rc) return rc - 10;
-  GemmParams p{M, N, K, D, ldd, R, ldr, reinterpret_cast<const __nv_bfloat16*>(bias), status, alpha, tune_group_m(), tune_wait_hint()};
+  GemmParams p{M, N, K, D, ldd, R, ldr, reinterpret_cast<const __nv_bfloat16*>(bias), status, alpha, tune_group_m(), tune_wait_hint(), 0u};
   const int sel = (a_mn ? 4 : 0) | (b_mn ? 2 : 0) | (out_f32 ? 1 : 0);
   switch (sel) {
     case 0: return launch<false, false, false>(ta, tb, p, stream);
@@ -445,7 +446,7 @@ int mtb200_gemm_bf16_allgather(const void* A, long long lda, void* D, long long 
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&tb, reinterpret_cast<const unsigned char*>(full) + w_byte_off, K, N, K, BK, BN);
   if (rc) return rc - 10;
-  GemmParams p{M, N, K, D, ldd, nullptr, 0, reinterpret_cast<const __nv_bfloat16*>(bias), status, 1.0f, tune_group_m(), tune_wait_hint()};
+  GemmParams p{M, N, K, D, ldd, nullptr, 0, reinterpret_cast<const __nv_bfloat16*>(bias), status, 1.0f, tune_group_m(), tune_wait_hint(), 0u};
   GatherParams g{};
   for (int i = 0; i < world; ++i) g.peer_base[i] = bases[i];
   g.shard_off = shard_off; g.shard_bytes = shard_bytes; g.dst = reinterpret_cast<unsigned char*>(full);
@@ -482,7 +483,9 @@ int mtb200_gemm_bf16_reduce_a(void* dst, const void* B, long long ldb, float* D,
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);
   if (rc) return rc - 10;
-  GemmParams p{M, N, K, D, ldd, R, ldr, nullptr, status, 1.0f, tune_group_m(), tune_wait_hint()};
+  // every pipeline wait sits out the peers' skew: a little longer than the bound of the ready-flag wait itself
+  const unsigned lim = limit_us ? limit_us : FLAG_SPIN_LIMIT;
+  GemmParams p{M, N, K, D, ldd, R, ldr, nullptr, status, 1.0f, tune_group_m(), tune_wait_hint(), lim + lim / 2 + 10000000u};
   GatherParams g{};
   for (int i = 0; i < world; ++i) g.peer_base[i] = bases[i];
   g.dst = reinterpret_cast<unsigned char*>(dst);

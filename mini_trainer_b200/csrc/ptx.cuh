@@ -63,10 +63,31 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
 }
 // Bounded wait. `abort_flag` (shared memory) lets one role's timeout end all the others quickly.
 // `hint_ns` > 0 uses the suspending form of try_wait (fewer polls while a long wait lasts).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t hint_ns = 0) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-    if (hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+// `limit_us` > 0 replaces the poll-count bound by a time bound on the global timer: a kernel whose pipeline
+// is fed by data that other GPUs must first declare ready (the fused gradient reduce + GEMM) has to sit out
+// the skew between ranks, which can be seconds.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t hint_ns = 0,
+                                          uint32_t limit_us = 0) {
+  if (limit_us == 0) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+      if (hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity)) return true;
+      if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+  }
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  const unsigned long long budget = static_cast<unsigned long long>(limit_us) * 1000ull;
+  for (uint32_t i = 0; i < 0x7fffffffu; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u) {
+      if (*abort_flag) return false;
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (t - t0 > budget) break;
+    }
   }
   *abort_flag = 1;
   return false;

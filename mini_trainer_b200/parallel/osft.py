@@ -28,14 +28,15 @@ gradients plus those other parameters.
 
 On the symmetric (NVLink) backend nothing on the step path calls NCCL:
 
-* backward: as soon as a projection's dense gradient is complete in the block's gradient buffer, the
-  in-kernel reduce-scatter runs with ownership by MATRIX instead of by flat slice: the owner pulls
-  that region from every peer, sums in fp32 and accumulates into its fp32 gradient of the matrix
-  (``SymmetricComm.reduce_to_owner``); the small tensors of the block go through the ordinary slice
-  reduction restricted to their region;
-* optimizer: on the owner the factor gradients ``G V_lo^T``, ``U_lo^T G``, the two projections (applied
-  twice, which squares the bf16 rounding residue left inside the frozen subspace) and the recomposition
-  ``W_hi + (U_lo S_lo) V_lo`` are tcgen05 GEMMs (bf16 operands, fp32 accumulate and output); AdamW on
+* backward: as soon as a projection's dense gradient is complete in the block's gradient buffer, ONE tcgen05
+  GEMM kernel on the owning rank pulls that region from every rank, sums it in fp32 and multiplies it by
+  ``V_lo^T`` (``SymmetricComm.reduce_gemm_to_owner``: the reduce-scatter with ownership by MATRIX, fused into
+  the GEMM that consumes the reduced gradient), accumulating over microbatches into the gradient slot of
+  ``U_lo``; ``U_lo^T G`` follows on the reduced gradient the kernel leaves behind. ``MTB200_OSFT_FUSED=0`` runs
+  the reduction as a kernel of its own into an fp32 matrix gradient (``reduce_to_owner``). The small tensors of
+  the block go through the ordinary slice reduction restricted to their region;
+* optimizer: on the owner the two projections (applied twice, which squares the bf16 rounding residue left
+  inside the frozen subspace) and the recomposition ``W_hi + (U_lo S_lo) V_lo`` are tcgen05 GEMMs (bf16 operands, fp32 accumulate and output); AdamW on
   all factors of a rank is ONE launch of the fused kernel over a flat buffer; the norm scalar is
   all-reduced by the arena's scalar kernel;
 * the recomposed fp32 matrices sit in a symmetric staging buffer; every rank pulls exactly the part
