@@ -121,6 +121,10 @@ def main(
         for r in results:
             print(f"{r['token_budget']:>9} {r['num_sequences']:>6} {r['sequence_length']:>8} "
                   f"{r.get('tokens_per_second', 0):>12.0f} {r.get('peak_memory_gb', 0):>8.1f}  {r['status']}")
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
