@@ -139,3 +139,34 @@ def test_gram_svd_reconstructs_and_spans_the_same_top_subspace():
     w32 = torch.randn(80, 48)
     u, s, vh = O.svd_thin(w32, "gram")
     assert ((u * s) @ vh - w32).abs().max() < 1e-4
+
+
+def test_training_state_carries_the_osft_factors(tmp_path):
+    """A training-state checkpoint of an OSFT run holds the trainable factors and their moments; loading it into a
+    fresh engine (which decomposes the ORIGINAL weights again) restores them, so the resumed run continues the
+    same trajectory instead of restarting the low subspace from the export."""
+    from mini_trainer_b200.ckpt.train_state import load_train_state, save_train_state
+    cfg = ModelConfig(vocab_size=61, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, tie_word_embeddings=False, attention_bias=True)
+
+    def fresh():
+        eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), optim=OptimConfig(max_grad_norm=1.0))
+        eng.init_random(seed=4, std=0.2)
+        return eng, O.enable_osft(eng, rank_ratio=0.5)
+
+    eng, ctl = fresh()
+    mbs = [make_mb([9, 5, 7], cfg.vocab_size, seed=s) for s in range(3)]
+    for mb in mbs[:2]:
+        eng.train_step([mb], lr=1e-2)
+    save_train_state(eng, str(tmp_path / "state"))
+    out_a = eng.train_step([mbs[2]], lr=1e-2)
+    wa = {k: v.clone() for k, v in eng.iter_hf_tensors(dtype=torch.float32)}
+
+    eng2, ctl2 = fresh()
+    load_train_state(eng2, str(tmp_path / "state"))
+    assert eng2.step_count == 2 and ctl2.fac_m.abs().sum() > 0          # moments restored, not zero as after a fresh start
+    out_b = eng2.train_step([mbs[2]], lr=1e-2)
+    assert abs(out_a["grad_norm"].item() - out_b["grad_norm"].item()) < 1e-5
+    wb = {k: v for k, v in eng2.iter_hf_tensors(dtype=torch.float32)}
+    for k in wa:
+        assert torch.allclose(wa[k], wb[k], atol=1e-6), k
