@@ -20,6 +20,11 @@
 // by more than 2^8 (exact: the final merge uses the same references), so the TMEM round trip for the
 // rescale is rare. Only the last key tile of a query block touches the causal diagonal and is masked.
 //
+// Masked scores are -inf. The exponentials that run on the special-function unit turn them into exact zeros;
+// the quarter that runs on the FMA pipe (ex2_fma2) clamps its argument at -126 and returns about 1e-38 instead, so
+// on the diagonal tile one masked key in four adds a term of that size to a row sum that is at least 1 (the row's
+// maximum contributes exp2(0)) and a bf16 zero to P: below fp32 resolution, no effect on out or lse.
+//
 // Outputs: out [T, Hq*D] bf16 and lse [Hq, T] fp32 (natural log, scaled scores), as needed by
 // the backward. Sequence boundaries come from a host-built work table (seq_start, seq_len, q0),
 // so there is no device-side search in cu_seqlens.
