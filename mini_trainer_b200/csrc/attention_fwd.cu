@@ -69,7 +69,12 @@ struct AttFwdParams {
   int* status;
 };
 
-template <int D, int POLY>   // every POLY-th exponential runs on the FMA pipe instead of the special-function unit
+// PT: P stays in tensor memory. The softmax threads write bf16 P over the S columns they just read
+// (tcgen05.st; keys 0-63 of a tile into columns 0-31 of its S buffer, keys 64-127 into columns 64-95, so a
+// thread only ever overwrites S columns that it owns) and P V is issued with the A operand in tensor memory.
+// No P tile in shared memory: no st.shared / proxy fence in the softmax loop, no shared-memory reads of P by
+// the tensor core. Q K^T of tile j+2 overwrites the buffer after P V of tile j in the tensor pipe's issue order.
+template <int D, int POLY, bool PT>   // every POLY-th exponential pair runs on the FMA pipe instead of the special-function unit
 __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, AttFwdParams p) {
   using L = AttFwdSmem<D>;
   constexpr int KB = D / 64;  // 64-element (128 B) column blocks of a D-wide row
@@ -178,8 +183,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
         for (int k = 0; k < ATT_BN / 16; ++k) {   // key columns 0-63 accumulate into O_a, 64-127 into O_b
           constexpr int KH = ATT_BN / 32;
-          umma_bf16(k < KH ? tmem_oa : tmem_ob, dP + kstep(k), dV + static_cast<uint64_t>(k * 128), idesc_pv,
-                    j != 0 || (k != 0 && k != KH));
+          if constexpr (PT) {
+            // 16 keys = 8 packed columns; the two halves of P sit at columns 0 and 64 of the S buffer
+            const uint32_t pa = tmem_s0 + b * ATT_BN + (k < KH ? k * 8 : 64 + (k - KH) * 8);
+            umma_bf16_ts(k < KH ? tmem_oa : tmem_ob, pa, dV + static_cast<uint64_t>(k * 128), idesc_pv,
+                         j != 0 || (k != 0 && k != KH));
+          } else {
+            umma_bf16(k < KH ? tmem_oa : tmem_ob, dP + kstep(k), dV + static_cast<uint64_t>(k * 128), idesc_pv,
+                      j != 0 || (k != 0 && k != KH));
+          }
         }
         umma_commit(&v_empty[b]);
         umma_commit(&p_empty[b]);
@@ -234,7 +246,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         m_ref = mt;
         l *= factor;
       }
-      if (j >= 2) {   // the P buffer of this tile must have been read by P V of tile j-2
+      if (!PT && j >= 2) {   // the shared-memory P buffer of this tile must have been read by P V of tile j-2
         if (!mbar_wait(&p_empty[j & 1], ((j - 2) >> 1) & 1, abort_flag)) { atomicExch(p.status, 18); goto done; }
       }
       if (j > 0) {
@@ -262,6 +274,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
         uint8_t* rowp = sp + (j & 1) * L::P_BYTES + (c >> 1) * 16384 + r * 128;
+        uint32_t pk[16];   // PT: the 32 probabilities of this chunk as 16 packed bf16 pairs
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float2 e[4];
@@ -272,14 +285,21 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
             e[i] = (i % POLY == POLY - 1) ? ex2_fma2(x) : make_float2(ex2_mufu(x.x), ex2_mufu(x.y));
             l2 = fadd2(l2, e[i]);
           }
-          const int chunk = (c & 1) * 4 + g;
-          uint4 o;
-          o.x = pack_bf16(e[0].x, e[0].y); o.y = pack_bf16(e[1].x, e[1].y); o.z = pack_bf16(e[2].x, e[2].y); o.w = pack_bf16(e[3].x, e[3].y);
-          *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = o;
+          if constexpr (PT) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pk[g * 4 + i] = pack_bf16(e[i].x, e[i].y);
+          } else {
+            const int chunk = (c & 1) * 4 + g;
+            uint4 o;
+            o.x = pack_bf16(e[0].x, e[0].y); o.y = pack_bf16(e[1].x, e[1].y); o.z = pack_bf16(e[2].x, e[2].y); o.w = pack_bf16(e[3].x, e[3].y);
+            *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = o;
+          }
         }
+        if constexpr (PT) tmem_st_32x16(ts + half * 64 + cc * 16, pk);   // keys (half*64 + cc*32 ..+32) -> 16 packed columns
       }
+      if constexpr (PT) tmem_st_wait();
       l += l2.x + l2.y;
-      fence_proxy_async_smem();
+      if constexpr (!PT) fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[j & 1]);
@@ -338,10 +358,10 @@ done:
   }
 }
 
-template <int D, int POLY>
+template <int D, int POLY, bool PT>
 static int launch_fwd(const CUtensorMap& tm, const AttFwdParams& p, int n_items, cudaStream_t st) {
   static bool configured = false;
-  auto kern = attn_fwd_kernel<D, POLY>;
+  auto kern = attn_fwd_kernel<D, POLY, PT>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttFwdSmem<D>::TOTAL) != cudaSuccess) return -4;
     configured = true;
@@ -362,5 +382,7 @@ extern "C" int mtb200_attn_fwd(const void* qkv, long long ld, void* out, long lo
   if (rc) return rc;
   AttFwdParams p{reinterpret_cast<__nv_bfloat16*>(out), ldo, lse, plan, T, Hq, Hkv, scale, status};
   // a quarter of the exponentials on the FMA pipe: 1011 vs 972 TFLOP/s (2 x 16384 tokens); half of them: no gain
-  return D == 128 ? launch_fwd<128, 4>(tm, p, n_items, st) : launch_fwd<64, 4>(tm, p, n_items, st);
+  // reserved bit 0: P through a shared-memory tile (the earlier form, kept for A/B timing) instead of tensor memory
+  if (reserved & 1) return D == 128 ? launch_fwd<128, 4, false>(tm, p, n_items, st) : launch_fwd<64, 4, false>(tm, p, n_items, st);
+  return D == 128 ? launch_fwd<128, 4, true>(tm, p, n_items, st) : launch_fwd<64, 4, true>(tm, p, n_items, st);
 }

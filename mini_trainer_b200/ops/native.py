@@ -86,6 +86,8 @@ class NativeOps:
         # latency-bound ones (attention, normalisation) lose more than the GEMMs gain: measured end to end on
         # one GPU 25.2 s against 23.9 s per step. So the one-CTA kernel is the default.
         self.use_gemm2 = os.environ.get("MTB200_GEMM2", "0") == "1"
+        # bit 0: attention forward keeps P in a shared-memory tile instead of tensor memory (A/B timing)
+        self.attn_fwd_flags = int(os.environ.get("MTB200_ATTN_P_SMEM", "0"))
         self.launches = 0
         self.profile = [] if os.environ.get("MTB200_PROFILE") else None
         self._scratch = {}
@@ -264,7 +266,7 @@ class NativeOps:
         lse = torch.empty(hq, T, dtype=torch.float32, device=self.device)
         plan = self._attn_plan(cu_host, 128, True)
         self._call("mtb200_attn_fwd", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), lse.data_ptr(),
-                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, 0, scale, self.status.data_ptr(), self._st())
+                   plan.data_ptr(), plan.shape[0], T, hq, hkv, d, self.attn_fwd_flags, scale, self.status.data_ptr(), self._st())
         return out, lse
 
     def attention_bwd(self, dout, qkv, out, lse, cu_seqlens, cu_host, max_seqlen, hq, hkv, d, scale=None):
