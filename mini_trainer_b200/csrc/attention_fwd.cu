@@ -384,5 +384,6 @@ extern "C" int mtb200_attn_fwd(const void* qkv, long long ld, void* out, long lo
   // a quarter of the exponentials on the FMA pipe: 1011 vs 972 TFLOP/s (2 x 16384 tokens); half of them: no gain
   // reserved bit 0: P through a shared-memory tile (the earlier form, kept for A/B timing) instead of tensor memory
   if (reserved & 1) return D == 128 ? launch_fwd<128, 4, false>(tm, p, n_items, st) : launch_fwd<64, 4, false>(tm, p, n_items, st);
+  // one exponential pair in four on the FMA pipe; one in two and one in eight measured the same within the spread
   return D == 128 ? launch_fwd<128, 4, true>(tm, p, n_items, st) : launch_fwd<64, 4, true>(tm, p, n_items, st);
 }
