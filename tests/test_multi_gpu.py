@@ -118,6 +118,19 @@ def test_two_gpus_match_one_gpu(comm, budget, tmp_path):
     _compare(one, two, f1, f2)
 
 
+@pytest.mark.parametrize("switch", ["MTB200_REGION_OVERLAP=0", "MTB200_GEMM2=1", "MTB200_FUSED_GATHER=0"])
+def test_two_gpus_symmetric_with_switches(switch, tmp_path):
+    """The documented switches of the symmetric backend: one reduction per block instead of one per tensor region,
+    the CTA-pair GEMM (and its fused all-gather form) for large problems, stand-alone all-gathers instead of fused ones."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    f1, f2 = str(tmp_path / "one.pt"), str(tmp_path / "two.pt")
+    one = _run(1, "auto", out=f1)
+    k, v = switch.split("=")
+    two = _run(2, "symmetric", "0", out=f2, extra_env={k: v})
+    _compare(one, two, f1, f2)
+
+
 @pytest.mark.parametrize("comm,fused", [("symmetric", "1"), ("symmetric", "0"), ("torchdist", "1")])
 def test_osft_two_gpus_match_one_gpu(comm, fused, tmp_path):
     """OSFT on 2 GPUs against OSFT on 1 GPU. Symmetric backend: each projection's gradient is pulled from all
