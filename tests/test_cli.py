@@ -108,3 +108,41 @@ def test_resume_continues_weights_optimizer_schedule_and_data(tmp_path):
     wa = st.load_file(os.path.join(a, "hf_format", "samples_32.0", "model.safetensors"))
     wb = st.load_file(os.path.join(b, "hf_format", "samples_32.0", "model.safetensors"))
     assert set(wa) == set(wb) and all(torch.equal(wa[k], wb[k]) for k in wa)
+
+
+def _train_cli_ranks(out, extra, port, world=2):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_PORT"):
+        env.pop(k, None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:tiny-qwen2",
+           "--data-path", "synthetic:tiny-qwen2:40:200", "--batch-size", "8", "--max-tokens-per-gpu", "1024",
+           "--output-dir", out, "--learning-rate", "1e-3", "--num-warmup-steps", "3", "--seed", "893",
+           "--logging-level", "WARNING", "--save-train-state"] + extra
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+
+
+def test_resume_two_ranks_with_osft(tmp_path):
+    """The same stop-and-resume on two gloo ranks with OSFT on: every rank writes and reads its own shard of the
+    training state, including the trainable factors (and their moments) of the matrices it owns."""
+    import torch
+    from mini_trainer_b200.ckpt import safetensors_io as st
+    a, b = str(tmp_path / "straight"), str(tmp_path / "resumed")
+    common = ["--min-samples-per-checkpoint", "16", "--osft", "--osft-rank-ratio", "0.5"]
+    _train_cli_ranks(a, ["--max-steps", "4"] + common, 29661)
+    _train_cli_ranks(b, ["--max-steps", "2"] + common, 29662)
+    state = os.path.join(b, "train_state", "samples_16.0")
+    assert sorted(f for f in os.listdir(state) if f.endswith(".safetensors")) == ["rank0-of-2.safetensors", "rank1-of-2.safetensors"]
+    shard1 = st.load_file(os.path.join(state, "rank1-of-2.safetensors"))
+    assert any(k.startswith("osft.") for k in shard1), sorted(shard1)[:8]
+    _train_cli_ranks(b, ["--max-steps", "4", "--resume-from", state] + common, 29663)
+    rows_a = [json.loads(l) for l in open(os.path.join(a, "training_metrics_0.jsonl"))]
+    rows_b = [json.loads(l) for l in open(os.path.join(b, "training_metrics_0.jsonl"))]
+    assert [r["step"] for r in rows_b] == [1, 2, 3, 4]
+    for ra, rb in zip(rows_a, rows_b):
+        assert ra["lr"] == rb["lr"] and ra["num_total_tokens"] == rb["num_total_tokens"]
+        assert abs(ra["loss"] - rb["loss"]) < 1e-5 and abs(ra["grad_norm"] - rb["grad_norm"]) < 1e-4
+    wa = st.load_file(os.path.join(a, "hf_format", "samples_32.0", "model.safetensors"))
+    wb = st.load_file(os.path.join(b, "hf_format", "samples_32.0", "model.safetensors"))
+    assert set(wa) == set(wb) and all(torch.equal(wa[k], wb[k]) for k in wa)
