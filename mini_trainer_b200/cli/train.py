@@ -118,6 +118,11 @@ def main(
                                  skip_batches=skip_batches)
     ds = getattr(loader, "dataset", None)
     if ds is not None and hasattr(ds, "lengths") and len(ds):
+        win = model.cfg.attention_window
+        if win is not None and int(ds.lengths.max()) > win:   # refused here, before any rank has started a step
+            raise ValueError(f"the longest sample has {int(ds.lengths.max())} tokens but the model attends through a sliding "
+                             f"window of {win}; only full causal attention is implemented, which is the same function up to "
+                             "that length. Filter the data (process_data --max-sample-num-tokens) or use a model without a window")
         model.reserve_host_offload(max(max_tokens_per_gpu, int(ds.lengths.max())))
     train(model, optimizer, sched, loader, output_dir, min_samples_per_checkpoint, model_name_or_path,
           max_steps=max_steps, max_shard_bytes=int(max_shard_gb * 1e9), save_train_state=save_train_state,

@@ -9,8 +9,9 @@ The reference's allow-list (setup_model_for_training.py:111-123) also names GPTD
 Starcoder2, Gemma and Mixtral and merely warns for anything else, because whatever
 ``AutoModelForCausalLM`` loads brings its own forward. Here the forward and backward are
 hand-written for ONE block structure, so an architecture whose math differs (LayerNorm or
-GeGLU blocks, MoE routing, sliding-window attention, biases on o_proj / the MLP) is refused by
-``validate_supported`` instead of being trained with the wrong function.
+GeGLU blocks, MoE routing, biases on o_proj / the MLP) is refused by ``validate_supported`` instead of
+being trained with the wrong function. Sliding-window models are accepted for samples no longer than the
+window, where the window changes nothing (``attention_window``).
 """
 from __future__ import annotations
 
@@ -64,6 +65,17 @@ class ModelConfig:
         """Scale applied to q.k before the softmax."""
         return float(self.attention_multiplier) if self.attention_multiplier is not None else self.head_dim ** -0.5
 
+    @property
+    def attention_window(self) -> Optional[int]:
+        """Sliding-window length where the model applies one (Mistral always, Qwen2 with ``use_sliding_window``), else
+        ``None``. A query sees the last ``window`` keys including itself (masking_utils.sliding_window_overlay), so for
+        samples of at most ``window`` tokens windowed and full causal attention are the same function. The attention
+        kernels here are full causal: the engine accepts such a model and refuses a minibatch that holds a longer sample."""
+        if self.sliding_window is None or self.sliding_window >= self.max_position_embeddings:
+            return None
+        on = self.use_sliding_window if self.use_sliding_window is not None else self.model_type == "mistral"
+        return int(self.sliding_window) if on else None
+
     def validate_supported(self) -> None:
         """Raises ``ValueError`` when the hand-written block would not compute this model's function."""
         arch = (self.architectures or ["?"])[0]
@@ -76,9 +88,6 @@ class ModelConfig:
             problems.append("mlp_bias=true (MLP biases are not implemented)")
         if self.attention_bias and self.model_type != "qwen2":
             problems.append("attention_bias=true outside Qwen2 adds an o_proj bias, which is not implemented")
-        windowed = self.sliding_window is not None and self.sliding_window < self.max_position_embeddings
-        if windowed and (self.use_sliding_window or (self.use_sliding_window is None and self.model_type == "mistral")):
-            problems.append(f"sliding_window={self.sliding_window} (attention here is full causal attention)")
         if problems:
             raise ValueError("this model cannot be trained faithfully: " + "; ".join(problems))
 

@@ -500,6 +500,10 @@ class ShardedEngine:
         cfg, ops = self.cfg, self.ops
         nL = len(self.blocks)
         tied = cfg.tie_word_embeddings
+        win = cfg.attention_window
+        if win is not None and batch.max_seqlen > win:
+            raise ValueError(f"a sample of {batch.max_seqlen} tokens exceeds the model's sliding window of {win}: attention "
+                             "here is full causal attention, which equals the windowed one only up to that length")
 
         # ---- forward ----
         levels = self.plan_checkpointing(batch.num_tokens)

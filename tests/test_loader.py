@@ -115,7 +115,6 @@ def test_vocabulary_growth_keeps_old_rows_and_initialises_new_ones(tmp_path):
 
 
 @pytest.mark.parametrize("kind,over,needle", [
-    ("mistral", {"sliding_window": 64}, "sliding_window"),
     ("llama", {"attention_bias": True}, "o_proj bias"),
     ("llama", {"mlp_bias": True}, "mlp_bias"),
     ("llama", {"hidden_act": "gelu"}, "hidden_act"),
@@ -124,6 +123,26 @@ def test_models_the_block_cannot_compute_are_refused(tmp_path, kind, over, needl
     path, _ = _hf_dir(tmp_path, kind, **over)
     with pytest.raises(ValueError, match=needle):
         setup_model(path, device="cpu")
+
+
+def test_sliding_window_model_is_trained_up_to_the_window_and_refused_beyond(tmp_path):
+    """A Mistral with a 32-token window: a 23-token sample gives transformers' logits (the window changes nothing up to
+    its length), a 40-token sample is refused instead of being run through full causal attention."""
+    path, hf = _hf_dir(tmp_path, "mistral", sliding_window=32)
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.attention_window == 32
+    ids = torch.randint(0, COMMON["vocab_size"], (23,))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    assert torch.allclose(_our_logits(eng, ids), ref, atol=2e-4, rtol=2e-4)
+    long = torch.randint(0, COMMON["vocab_size"], (40,))
+    mb = mb_collate_fn([{"input_ids": long, "labels": long, "len": 40, "num_loss_counted_tokens": 40}], 40)
+    with pytest.raises(ValueError, match="sliding window of 32"):
+        eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 40, last=True)
+    # Qwen2 carries a window in its config but only applies it with use_sliding_window
+    assert ModelConfig.from_hf_dict({**COMMON, "model_type": "qwen2", "sliding_window": 32}).attention_window is None
+    assert ModelConfig.from_hf_dict({**COMMON, "model_type": "qwen2", "sliding_window": 32,
+                                     "use_sliding_window": True}).attention_window == 32
 
 
 def test_unknown_architecture_is_refused(tmp_path):
