@@ -9,8 +9,9 @@ The reference's allow-list (setup_model_for_training.py:111-123) also names GPTD
 Starcoder2, Gemma and Mixtral and merely warns for anything else, because whatever
 ``AutoModelForCausalLM`` loads brings its own forward. Here the forward and backward are
 hand-written for ONE block structure, so an architecture whose math differs (LayerNorm or
-GeGLU blocks, MoE routing, biases on o_proj / the MLP) is refused by ``validate_supported`` instead of
-being trained with the wrong function. Sliding-window models are accepted for samples no longer than the
+GeGLU blocks, MoE routing) is refused by ``validate_supported`` instead of being trained with the
+wrong function. Llama-style ``attention_bias`` (q/k/v AND o_proj) and ``mlp_bias`` (gate, up, down), which
+the Granite code models use, are part of the block. Sliding-window models are accepted for samples no longer than the
 window, where the window changes nothing (``attention_window``).
 """
 from __future__ import annotations
@@ -84,10 +85,6 @@ class ModelConfig:
             problems.append(f"architecture {arch} is not one of {', '.join(SUPPORTED_ARCHITECTURES)}")
         if self.hidden_act not in ("silu", "swish"):
             problems.append(f"hidden_act={self.hidden_act!r} (only the SwiGLU MLP is implemented)")
-        if self.mlp_bias:
-            problems.append("mlp_bias=true (MLP biases are not implemented)")
-        if self.attention_bias and self.model_type != "qwen2":
-            problems.append("attention_bias=true outside Qwen2 adds an o_proj bias, which is not implemented")
         if problems:
             raise ValueError("this model cannot be trained faithfully: " + "; ".join(problems))
 
@@ -104,10 +101,18 @@ class ModelConfig:
     def qkv_size(self) -> int:
         return self.q_size + 2 * self.kv_size
 
+    @property
+    def o_proj_bias(self) -> bool:
+        """``attention_bias`` covers q, k, v and o_proj in the Llama-style classes (modeling_llama.py,
+        modeling_granite.py); Qwen2 has the q/k/v biases only (modeling_qwen2.py)."""
+        return self.attention_bias and self.model_type != "qwen2"
+
     def block_param_count(self) -> int:
         h, f = self.hidden_size, self.intermediate_size
         n = 2 * h + self.qkv_size * h + self.q_size * h + 3 * h * f
-        return n + (self.qkv_size if self.attention_bias else 0)
+        n += self.qkv_size if self.attention_bias else 0
+        n += h if self.o_proj_bias else 0
+        return n + (2 * f + h if self.mlp_bias else 0)
 
     def param_count(self) -> int:
         emb = self.vocab_size * self.hidden_size

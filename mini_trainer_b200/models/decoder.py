@@ -7,9 +7,11 @@ and can be reduced. The same functions run on the PyTorch reference ops (CPU, te
 sm_100a kernels; ``ops`` is the backend object.
 
 Architecture (HF Llama/Qwen2, modeling_llama.py:303-332): ``x + Attn(RMSNorm(x))`` followed by
-``h + MLP(RMSNorm(h))`` with rotary GQA attention and a SwiGLU MLP. Activation checkpointing is
-per block as in the reference (setup_model_for_training.py:28-29): forward keeps only the block
-input; backward first re-runs the block forward (``block_forward(..., keep=True)``).
+``h + MLP(RMSNorm(h))`` with rotary GQA attention and a SwiGLU MLP; every projection may carry a bias
+(``attention_bias``, ``mlp_bias``), added in the GEMM epilogue, its gradient a column sum of the
+output gradient. Activation checkpointing is per block as in the reference
+(setup_model_for_training.py:28-29): forward keeps only the block input; backward first re-runs
+the block forward (``block_forward(..., keep=True)``).
 """
 from __future__ import annotations
 
@@ -112,18 +114,22 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     qkv = ops.linear(n1, p["wqkv"], p.get("bqkv"), gather=None if plan is None else (plan, 0))
     ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
     rm = cfg.residual_multiplier   # Granite scales every branch output before the residual add (1.0 elsewhere)
+    # the GEMM epilogue computes alpha * product + bias + residual; the models scale (product + bias)
+    bo, bd = p.get("bo"), p.get("bd")
+    if rm != 1.0:
+        bo, bd = (None if bo is None else bo * rm), (None if bd is None else bd * rm)
     if saved_attn is not None:
         attn, lse = saved_attn
     else:
         attn, lse = ops.attention(qkv, batch.cu_seqlens, batch.cu_seqlens_host, batch.max_seqlen,
                                   cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, scale=cfg.attention_scale)
-    h1 = ops.linear(attn, p["wo"], None, x, alpha=rm)
+    h1 = ops.linear(attn, p["wo"], bo, x, alpha=rm)
     n2, rstd2 = ops.rmsnorm(h1, p["ln2"], cfg.rms_norm_eps)
-    gu = ops.linear(n2, p["wgu"], gather=None if plan is None else (plan, 1))
+    gu = ops.linear(n2, p["wgu"], p.get("bgu"), gather=None if plan is None else (plan, 1))
     # a recompute that stops before the down projection does not need the SwiGLU output: backward rebuilds it
     # inside the SwiGLU-gradient kernel
     act = ops.swiglu(gu) if need_out else None
-    out = ops.linear(act, p["wd"], None, h1, alpha=rm) if need_out else None
+    out = ops.linear(act, p["wd"], bd, h1, alpha=rm) if need_out else None
     acts = None
     if keep == "compact":   # kept from forward to backward: drop what one elementwise kernel can rebuild
         acts = BlockActs(x, None, rstd1, qkv, attn, lse, h1, None, rstd2, gu, None)
@@ -149,25 +155,29 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     # MLP
     dact = ops.linear_dgrad(dout, p["wd"], alpha=rm)
     if a.act is not None:
-        ops.linear_wgrad(dout, a.act, g["wd"], alpha=rm)
+        ops.linear_wgrad(dout, a.act, g["wd"], g.get("bd"), alpha=rm)
         dgu = ops.swiglu_bwd(dact, a.gu)
     else:   # one pass over gate/up gives its gradient and the SwiGLU output (written over dact)
         dgu, act = ops.swiglu_bwd_act(dact, a.gu)
-        ops.linear_wgrad(dout, act, g["wd"], alpha=rm)
+        ops.linear_wgrad(dout, act, g["wd"], g.get("bd"), alpha=rm)
         del act
+    if rm != 1.0 and "bd" in g:   # the bias sits inside the scaled branch; the column sum is not scaled by alpha
+        g["bd"].mul_(rm)
     notify("wd")
     del dact
     dn2 = ops.linear_dgrad(dgu, p["wgu"])
     n2 = a.n2 if a.n2 is not None else ops.rmsnorm(a.h1, p["ln2"], cfg.rms_norm_eps)[0]
-    ops.linear_wgrad(dgu, n2, g["wgu"])
+    ops.linear_wgrad(dgu, n2, g["wgu"], g.get("bgu"))
     notify("wgu")
     del dgu, n2
     dh1 = ops.rmsnorm_bwd(dn2, a.h1, a.rstd2, p["ln2"], g["ln2"], add_to=dout)
     del dn2
     # attention
     dattn = ops.linear_dgrad(dh1, p["wo"], alpha=rm)
-    ops.linear_wgrad(dh1, a.attn, g["wo"], alpha=rm)
-    notify("wo")     # ln2's gradient was written by the rmsnorm backward above
+    ops.linear_wgrad(dh1, a.attn, g["wo"], g.get("bo"), alpha=rm)
+    if rm != 1.0 and "bo" in g:
+        g["bo"].mul_(rm)
+    notify("wo")     # ln2's gradient was written by the rmsnorm backward above, bgu's with wgu's
     dqkv = ops.attention_bwd(dattn, a.qkv, a.attn, a.lse, batch.cu_seqlens, batch.cu_seqlens_host,
                              batch.max_seqlen, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                              scale=cfg.attention_scale)

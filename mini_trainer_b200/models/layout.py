@@ -64,7 +64,19 @@ def block_entries(cfg: ModelConfig) -> list:
     e = [("ln1", (h,))]
     if cfg.attention_bias:
         e.append(("bqkv", (cfg.qkv_size,)))
-    e += [("wqkv", (cfg.qkv_size, h)), ("wo", (h, cfg.q_size)), ("ln2", (h,)), ("wgu", (2 * f, h)), ("wd", (h, f))]
+    e += [("wqkv", (cfg.qkv_size, h)), ("wo", (h, cfg.q_size))]
+    # Optional biases sit where both schedules want them: ``bo`` and ``bgu`` in front of ``wgu``, so the
+    # gather fused into the QKV projection has brought them in before o_proj / gate-up run and backward has
+    # written their gradients before the region that starts at ``wo`` is reduced; ``bd`` behind ``wd``, inside
+    # the gather fused into gate/up and inside the first region backward completes.
+    if cfg.o_proj_bias:
+        e.append(("bo", (h,)))
+    e.append(("ln2", (h,)))
+    if cfg.mlp_bias:
+        e.append(("bgu", (2 * f,)))
+    e += [("wgu", (2 * f, h)), ("wd", (h, f))]
+    if cfg.mlp_bias:
+        e.append(("bd", (h,)))
     return e
 
 
@@ -97,10 +109,18 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
     if cfg.attention_bias:
         yield p + "self_attn.v_proj.bias", views["bqkv"][q + kv:]
     yield p + "self_attn.o_proj.weight", views["wo"]
+    if cfg.o_proj_bias:
+        yield p + "self_attn.o_proj.bias", views["bo"]
     f = cfg.intermediate_size
     yield p + "mlp.gate_proj.weight", views["wgu"][:f]
+    if cfg.mlp_bias:
+        yield p + "mlp.gate_proj.bias", views["bgu"][:f]
     yield p + "mlp.up_proj.weight", views["wgu"][f:]
+    if cfg.mlp_bias:
+        yield p + "mlp.up_proj.bias", views["bgu"][f:]
     yield p + "mlp.down_proj.weight", views["wd"]
+    if cfg.mlp_bias:
+        yield p + "mlp.down_proj.bias", views["bd"]
     yield p + "input_layernorm.weight", views["ln1"]
     yield p + "post_attention_layernorm.weight", views["ln2"]
 

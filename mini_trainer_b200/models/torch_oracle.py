@@ -49,10 +49,11 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
                                                v[a:b].transpose(0, 1)[None], is_causal=True, enable_gqa=True,
                                                scale=cfg.attention_scale)
             outs.append(o[0].transpose(0, 1).reshape(b - a, hq * d))
-        x = x + rm * F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"])
+        x = x + rm * F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
         n = _rms(x, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
-        act = F.silu(F.linear(n, sd[p + "mlp.gate_proj.weight"])) * F.linear(n, sd[p + "mlp.up_proj.weight"])
-        x = x + rm * F.linear(act, sd[p + "mlp.down_proj.weight"])
+        act = F.silu(F.linear(n, sd[p + "mlp.gate_proj.weight"], sd.get(p + "mlp.gate_proj.bias"))) \
+            * F.linear(n, sd[p + "mlp.up_proj.weight"], sd.get(p + "mlp.up_proj.bias"))
+        x = x + rm * F.linear(act, sd[p + "mlp.down_proj.weight"], sd.get(p + "mlp.down_proj.bias"))
     n = _rms(x, sd["model.norm.weight"], cfg.rms_norm_eps)
     lm = sd["model.embed_tokens.weight"] if cfg.tie_word_embeddings else sd["lm_head.weight"]
     logits = F.linear(n, lm).float() / cfg.logits_scaling

@@ -326,28 +326,36 @@ class OSFT:
                 if mine:
                     mt.has_grad = True
 
-        def reduce_small(names, final):
-            lo = min(specs[n].offset for n in names)
-            hi = max(specs[n].offset + specs[n].numel for n in names)
+        def reduce_small(lo, hi, final):
+            """The tensors that are not projections (norm weights, biases) between two element offsets: plain
+            reduce-scatter by flat slice, like a region of a dense block."""
             k = state["k"]; state["k"] += 1
             eng._reduce(grp, gbuf, gslot, last, region=k, elem_lo=lo, elem_hi=hi, final=final)
+
+        names = list(specs)
+
+        def end(n):   # where the tensor laid out after ``n`` starts: tensor starts are 256-byte aligned, tensor ends need not be
+            k = names.index(n) + 1
+            return specs[names[k]].offset if k < len(names) else grp.layout.numel
 
         def notify(name):
             if name in order:
                 reduce_tensor(name)
-            if name == "wo":
-                reduce_small(["ln2"], final=False)
+            if name == "wd" and end("wd") < grp.layout.numel:   # the down projection's bias lies behind it
+                reduce_small(end("wd"), grp.layout.numel, final=False)
+            if name == "wo":    # o_proj bias | post-attention norm | gate/up bias
+                reduce_small(end("wo"), specs["wgu"].offset, final=False)
 
         def finish():
             reduce_tensor("wqkv")
-            reduce_small(["ln1"] + (["bqkv"] if "bqkv" in specs else []), final=True)
+            reduce_small(0, specs["wqkv"].offset, final=True)   # input norm | q/k/v bias
 
         return notify, finish
 
     @property
     def last_region(self) -> int:
         """Index of the region a block reduces last (what ``wait_consumed`` must wait for)."""
-        return len(self.by_block[0]) + 1
+        return len(self.by_block[0]) + 1 + int("bd" in self.eng.blocks[0].layout.specs)
 
     # -- products -----------------------------------------------------------------------------
     def _mm(self, x, x_t: bool, y, y_t: bool, alpha: float = 1.0, residual=None, out=None):

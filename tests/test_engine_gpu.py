@@ -50,6 +50,47 @@ def test_native_engine_matches_fp32_reference(attention):
     assert ops.launches > 0
 
 
+@pytest.mark.parametrize("residual_multiplier", [1.0, 0.25])
+def test_native_engine_with_projection_biases_matches_fp32_reference(residual_multiplier):
+    """``attention_bias`` (q, k, v, o_proj) and ``mlp_bias`` (gate, up, down): bias and residual in one GEMM epilogue,
+    bias gradients by the column-sum kernel, with and without Granite's scaling of the biased branch."""
+    import dataclasses
+    from mini_trainer_b200.ops.native import NativeOps
+    cfg = dataclasses.replace(get_preset("smoke-llama"), attention_bias=True, mlp_bias=True)
+    if residual_multiplier != 1.0:
+        cfg = dataclasses.replace(cfg, model_type="granite", architectures=["GraniteForCausalLM"],
+                                  residual_multiplier=residual_multiplier)
+    ops = NativeOps("cuda:0")
+    eng = ShardedEngine(cfg, "cuda:0", ops, optim=OptimConfig())
+    eng.init_random(seed=12, std=0.05)
+    biases = ("bqkv", "bo", "bgu", "bd")
+    gen = torch.Generator(device="cuda:0").manual_seed(3)
+    for grp in eng.blocks:     # random initialisation leaves biases at zero
+        views = grp.layout.views(grp.master)
+        for n in biases:
+            views[n].normal_(0.0, 0.3, generator=gen)
+        grp.shard.copy_(grp.master)
+    ref = ShardedEngine(cfg, "cuda:0", get_ops("cuda:0", "torch"), param_dtype=torch.float32, optim=OptimConfig())
+    for a, b in zip(eng.groups, ref.groups):
+        b.master.copy_(a.shard.float()); b.shard.copy_(b.master)
+    mb = make_mb([300, 17, 129, 1, 640], cfg.vocab_size)
+    batch = D.make_packed_batch(mb, "cuda:0")
+    scale = 1.0 / mb["batch_num_loss_counted_tokens"]
+    l1 = eng.forward_backward(batch, scale)
+    l2 = ref.forward_backward(batch, scale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert abs(l1.sum().item() - l2.sum().item()) < 2e-2 * abs(l2.sum().item())
+    for a, b in zip(eng.groups, ref.groups):
+        err = (a.gacc - b.gacc).norm() / (b.gacc.norm() + 1e-12)
+        assert err < 5e-2, (a.layout.name, err.item())
+    for a, b in zip(eng.blocks, ref.blocks):
+        ga, gb = a.layout.views(a.gacc), b.layout.views(b.gacc)
+        for n in biases:
+            err = (ga[n] - gb[n]).norm() / (gb[n].norm() + 1e-12)
+            assert gb[n].norm() > 0 and err < 5e-2, (a.layout.name, n, err.item())
+
+
 def test_osft_step_runs_with_native_kernels():
     from mini_trainer_b200.ops.native import NativeOps
     from mini_trainer_b200.parallel.osft import enable_osft

@@ -114,9 +114,51 @@ def test_vocabulary_growth_keeps_old_rows_and_initialises_new_ones(tmp_path):
     assert torch.allclose(_our_logits(eng, ids)[:, :96], ref, atol=2e-4, rtol=2e-4)
 
 
+@pytest.mark.parametrize("kind", ["llama", "granite"])
+def test_projection_biases_reach_logits_gradients_and_exports(tmp_path, kind):
+    """``attention_bias`` (q, k, v and o_proj) and ``mlp_bias`` (gate, up, down), as the Granite code models have them:
+    logits and every bias gradient against transformers (for Granite with its residual multiplier scaling the
+    biased branch), and the exported checkpoint carries the biases under their Hugging Face names."""
+    path, hf = _hf_dir(tmp_path, kind, attention_bias=True, mlp_bias=True)
+    with torch.no_grad():   # transformers initialises biases to zero; give them values
+        for n, p_ in hf.named_parameters():
+            if n.endswith(".bias"):
+                p_.normal_(0.0, 0.5)
+    hf.save_pretrained(path)
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.o_proj_bias and {"bqkv", "bo", "bgu", "bd"} <= set(eng.blocks[0].layout.specs)
+    ids = torch.randint(0, COMMON["vocab_size"], (21,))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    mine = _our_logits(eng, ids)
+    assert torch.allclose(mine, ref, atol=3e-4, rtol=3e-4), float((mine - ref).abs().max())
+    labels = ids.clone()
+    labels[:4] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 21, "num_loss_counted_tokens": 17}], 17)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 17, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 17 - float(out.loss)) < 1e-4
+    got = eng.blocks[0].layout.views(eng.blocks[0].gacc)
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    L, q, kv, f = "model.layers.0.", eng.cfg.q_size, eng.cfg.kv_size, eng.cfg.intermediate_size
+    pairs = [(got["bo"], want[L + "self_attn.o_proj.bias"]), (got["bd"], want[L + "mlp.down_proj.bias"]),
+             (got["bgu"][:f], want[L + "mlp.gate_proj.bias"]), (got["bgu"][f:], want[L + "mlp.up_proj.bias"]),
+             (got["bqkv"][:q], want[L + "self_attn.q_proj.bias"]), (got["bqkv"][q + kv:], want[L + "self_attn.v_proj.bias"]),
+             (got["wd"], want[L + "mlp.down_proj.weight"]), (got["wo"], want[L + "self_attn.o_proj.weight"])]
+    for a, b in pairs:
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-3), float((a - b).abs().max())
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    with torch.no_grad():
+        again = back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
+    assert back.model.layers[1].mlp.down_proj.bias.abs().sum() > 0
+
+
 @pytest.mark.parametrize("kind,over,needle", [
-    ("llama", {"attention_bias": True}, "o_proj bias"),
-    ("llama", {"mlp_bias": True}, "mlp_bias"),
     ("llama", {"hidden_act": "gelu"}, "hidden_act"),
 ])
 def test_models_the_block_cannot_compute_are_refused(tmp_path, kind, over, needle):
