@@ -1,16 +1,17 @@
 """Decoder configuration, read from / written to Hugging Face ``config.json``.
 
-Covers the Llama / Qwen2 / Mistral / Granite family the reference trains through
+Covers the Llama / Qwen2 / Mistral / Granite / Mixtral family the reference trains through
 ``AutoModelForCausalLM`` (setup_model_for_training.py:86-130): pre-norm decoder blocks with
-RMSNorm, rotary GQA attention (optional q/k/v bias), SwiGLU MLP, tied or untied LM head, plus
-Granite's four scalars (embedding, residual, attention and logits multipliers).
+RMSNorm, rotary GQA attention (optional biases), a SwiGLU MLP or Mixtral's routed SwiGLU experts,
+tied or untied LM head, plus Granite's four scalars (embedding, residual, attention and logits
+multipliers).
 
 The reference's allow-list (setup_model_for_training.py:111-123) also names GPTDolomite,
-Starcoder2, Gemma and Mixtral and merely warns for anything else, because whatever
+Starcoder2 and Gemma and merely warns for anything else, because whatever
 ``AutoModelForCausalLM`` loads brings its own forward. Here the forward and backward are
 hand-written for ONE block structure, so an architecture whose math differs (LayerNorm or
-GeGLU blocks, MoE routing) is refused by ``validate_supported`` instead of being trained with the
-wrong function. Llama-style ``attention_bias`` (q/k/v AND o_proj) and ``mlp_bias`` (gate, up, down), which
+GeGLU blocks) is refused by ``validate_supported`` instead of being trained with the wrong
+function. Llama-style ``attention_bias`` (q/k/v AND o_proj) and ``mlp_bias`` (gate, up, down), which
 the Granite code models use, are part of the block. Sliding-window models are accepted for samples no longer than the
 window, where the window changes nothing (``attention_window``).
 """
@@ -53,6 +54,12 @@ class ModelConfig:
     use_sliding_window: Optional[bool] = None
     mlp_bias: bool = False
     hidden_act: str = "silu"
+    # Mixtral (modeling_mixtral.py): the MLP of every block is num_local_experts SwiGLU experts, of which a
+    # softmax router picks num_experts_per_tok per token; 0 experts = dense MLP
+    num_local_experts: int = 0
+    num_experts_per_tok: int = 2
+    output_router_logits: bool = False
+    router_jitter_noise: float = 0.0
     extra: dict = field(default_factory=dict)  # unknown keys of config.json, written back verbatim
 
     def __post_init__(self):
@@ -77,10 +84,23 @@ class ModelConfig:
         on = self.use_sliding_window if self.use_sliding_window is not None else self.model_type == "mistral"
         return int(self.sliding_window) if on else None
 
+    @property
+    def is_moe(self) -> bool:
+        return self.num_local_experts > 0
+
     def validate_supported(self) -> None:
         """Raises ``ValueError`` when the hand-written block would not compute this model's function."""
         arch = (self.architectures or ["?"])[0]
         problems = []
+        if self.is_moe:
+            if self.output_router_logits:
+                problems.append("output_router_logits=true adds the router's load-balancing loss, which is not implemented")
+            if self.router_jitter_noise:
+                problems.append(f"router_jitter_noise={self.router_jitter_noise} (input jitter is not implemented)")
+            if self.mlp_bias:
+                problems.append("mlp_bias=true with experts")
+            if not 0 < self.num_experts_per_tok <= self.num_local_experts:
+                problems.append(f"num_experts_per_tok={self.num_experts_per_tok} of {self.num_local_experts} experts")
         if arch not in SUPPORTED_ARCHITECTURES:
             problems.append(f"architecture {arch} is not one of {', '.join(SUPPORTED_ARCHITECTURES)}")
         if self.hidden_act not in ("silu", "swish"):
@@ -107,9 +127,15 @@ class ModelConfig:
         modeling_granite.py); Qwen2 has the q/k/v biases only (modeling_qwen2.py)."""
         return self.attention_bias and self.model_type != "qwen2"
 
+    @property
+    def mlp_rows_factor(self) -> int:
+        """Rows that go through an MLP per token: the number of experts a token is sent to (1 for a dense MLP)."""
+        return self.num_experts_per_tok if self.is_moe else 1
+
     def block_param_count(self) -> int:
         h, f = self.hidden_size, self.intermediate_size
-        n = 2 * h + self.qkv_size * h + self.q_size * h + 3 * h * f
+        n = 2 * h + self.qkv_size * h + self.q_size * h + 3 * h * f * max(1, self.num_local_experts)
+        n += self.num_local_experts * h   # router
         n += self.qkv_size if self.attention_bias else 0
         n += h if self.o_proj_bias else 0
         return n + (2 * f + h if self.mlp_bias else 0)
@@ -119,9 +145,11 @@ class ModelConfig:
         return self.num_hidden_layers * self.block_param_count() + self.hidden_size + emb * (1 if self.tie_word_embeddings else 2)
 
     def flops_per_token(self, avg_context: float = 0.0, recompute: bool = True) -> float:
-        """Training FLOPs per token: 6 x matmul params (+2 x with full recompute) + attention."""
+        """Training FLOPs per token: 6 x matmul params (+2 x with full recompute) + attention. With experts
+        only the ``num_experts_per_tok`` chosen ones (and the router) count."""
         h, f = self.hidden_size, self.intermediate_size
-        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + 3 * h * f)
+        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + 3 * h * f * self.mlp_rows_factor
+                                       + self.num_local_experts * h)
         head = self.vocab_size * h
         k = 8 if recompute else 6
         attn = self.num_hidden_layers * 2 * 2 * self.q_size * avg_context  # QK^T and PV, forward
@@ -136,7 +164,7 @@ class ModelConfig:
         the two kernel families on a power-capped B200.
         """
         h, f = self.hidden_size, self.intermediate_size
-        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + 3 * h * f)
+        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + 3 * h * f * self.mlp_rows_factor)
         gemm = (8 if recompute else 6) * mm + 6 * self.vocab_size * h
         attn = 3.5 * 2 * self.q_size * self.num_hidden_layers
         return (gemm / gemm_rate) / (attn / attn_rate)
@@ -170,7 +198,9 @@ class ModelConfig:
               "num_key_value_heads", "head_dim", "rms_norm_eps", "rope_theta", "rope_scaling", "attention_bias",
               "tie_word_embeddings", "max_position_embeddings", "model_type", "architectures",
               "pad_token_id", "bos_token_id", "eos_token_id", "embedding_multiplier", "residual_multiplier",
-              "attention_multiplier", "logits_scaling", "sliding_window", "use_sliding_window", "mlp_bias", "hidden_act")
+              "attention_multiplier", "logits_scaling", "sliding_window", "use_sliding_window", "mlp_bias", "hidden_act",
+              "num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise")
+    _MOE_ONLY = ("num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise")
     _GRANITE_ONLY = ("embedding_multiplier", "residual_multiplier", "attention_multiplier", "logits_scaling")
 
     @classmethod
@@ -207,6 +237,9 @@ class ModelConfig:
         for k in self._GRANITE_ONLY:   # only Granite's config class knows these keys
             if self.model_type != "granite":
                 d.pop(k)
+        for k in self._MOE_ONLY:
+            if not self.is_moe:
+                d.pop(k)
         for k in ("sliding_window", "use_sliding_window"):
             if d[k] is None:
                 d.pop(k)
@@ -226,7 +259,8 @@ class ModelConfig:
             f.write("\n")
 
 
-SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM")
+SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
+                           "MixtralForCausalLM")
 
 
 def _llama(**kw):
@@ -251,6 +285,11 @@ PRESETS = {
                                  num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6, rms_norm_eps=1e-6),
     "llama-3.1-70b": lambda: _llama(vocab_size=128256, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
                                     num_attention_heads=64, num_key_value_heads=8, rope_theta=5e5, rms_norm_eps=1e-5),
+    # a small Mixtral (4 experts, 2 per token) for CPU and GPU tests (head_dim 128 on the GPU kernels' account)
+    "tiny-mixtral": lambda: ModelConfig(model_type="mixtral", architectures=["MixtralForCausalLM"], vocab_size=4096,
+                                        hidden_size=256, intermediate_size=384, num_hidden_layers=2, num_attention_heads=2,
+                                        num_key_value_heads=1, rope_theta=1e6, rms_norm_eps=1e-5, num_local_experts=4,
+                                        num_experts_per_tok=2),
     # a small Llama used by GPU smoke tests (head_dim 128, GQA 4:1)
     "smoke-llama": lambda: _llama(vocab_size=4096, hidden_size=512, intermediate_size=1536, num_hidden_layers=2,
                                   num_attention_heads=4, num_key_value_heads=1, rope_theta=5e5, rms_norm_eps=1e-5),

@@ -22,6 +22,7 @@ from typing import Optional
 import torch
 
 from .config import ModelConfig
+from .moe import moe_backward, moe_forward
 
 
 @dataclass
@@ -93,6 +94,7 @@ class BlockActs:
     rstd2: torch.Tensor
     gu: torch.Tensor
     act: torch.Tensor
+    moe: Optional[object] = None   # routing and expert pre-activations of a mixture-of-experts block (``moe.MoeState``)
 
 
 def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: PackedBatch, inv_freq, keep: bool = False,
@@ -125,6 +127,14 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
                                   cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, scale=cfg.attention_scale)
     h1 = ops.linear(attn, p["wo"], bo, x, alpha=rm)
     n2, rstd2 = ops.rmsnorm(h1, p["ln2"], cfg.rms_norm_eps)
+    if cfg.is_moe:
+        out, st = moe_forward(ops, cfg, p, n2, h1, need_out, keep_act=keep is True)
+        acts = None
+        if keep == "compact":
+            acts = BlockActs(x, None, rstd1, qkv, attn, lse, h1, None, rstd2, None, None, st)
+        elif keep:
+            acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, None, None, st)
+        return out, acts, ((attn, lse) if want_attn else None)
     gu = ops.linear(n2, p["wgu"], p.get("bgu"), gather=None if plan is None else (plan, 1))
     # a recompute that stops before the down projection does not need the SwiGLU output: backward rebuilds it
     # inside the SwiGLU-gradient kernel
@@ -153,6 +163,11 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     # activations kept in compact form: the normalised inputs and the SwiGLU output are rebuilt by
     # bandwidth-bound kernels (about 1 ms per block) instead of being held for the whole step
     # MLP
+    if cfg.is_moe:
+        n2 = a.n2 if a.n2 is not None else ops.rmsnorm(a.h1, p["ln2"], cfg.rms_norm_eps)[0]
+        dn2 = moe_backward(ops, cfg, p, g, a.moe, n2, dout)
+        del n2
+        return _attention_backward(ops, cfg, p, g, a, dn2, dout, batch, inv_freq, notify, rm)
     dact = ops.linear_dgrad(dout, p["wd"], alpha=rm)
     if a.act is not None:
         ops.linear_wgrad(dout, a.act, g["wd"], g.get("bd"), alpha=rm)
@@ -170,6 +185,13 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     ops.linear_wgrad(dgu, n2, g["wgu"], g.get("bgu"))
     notify("wgu")
     del dgu, n2
+    return _attention_backward(ops, cfg, p, g, a, dn2, dout, batch, inv_freq, notify, rm)
+
+
+def _attention_backward(ops, cfg: ModelConfig, p: dict, g: dict, a: BlockActs, dn2: torch.Tensor, dout: torch.Tensor,
+                        batch: PackedBatch, inv_freq, notify, rm: float) -> torch.Tensor:
+    """The part of the block backward in front of the MLP: post-attention norm, o_proj, attention, rotary,
+    q/k/v projection, input norm. ``dn2`` is the gradient of the normalised MLP input."""
     dh1 = ops.rmsnorm_bwd(dn2, a.h1, a.rstd2, p["ln2"], g["ln2"], add_to=dout)
     del dn2
     # attention

@@ -72,6 +72,11 @@ def block_entries(cfg: ModelConfig) -> list:
     if cfg.o_proj_bias:
         e.append(("bo", (h,)))
     e.append(("ln2", (h,)))
+    if cfg.is_moe:   # router, then every expert's fused gate/up and down matrices
+        e.append(("router", (cfg.num_local_experts, h)))
+        for x in range(cfg.num_local_experts):
+            e += [(f"wgu{x}", (2 * f, h)), (f"wd{x}", (h, f))]
+        return e
     if cfg.mlp_bias:
         e.append(("bgu", (2 * f,)))
     e += [("wgu", (2 * f, h)), ("wd", (h, f))]
@@ -112,6 +117,16 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
     if cfg.o_proj_bias:
         yield p + "self_attn.o_proj.bias", views["bo"]
     f = cfg.intermediate_size
+    if cfg.is_moe:   # names of the published Mixtral checkpoints (w1 = gate, w3 = up, w2 = down)
+        m = p + "block_sparse_moe."
+        for x in range(cfg.num_local_experts):
+            yield m + f"experts.{x}.w1.weight", views[f"wgu{x}"][:f]
+            yield m + f"experts.{x}.w2.weight", views[f"wd{x}"]
+            yield m + f"experts.{x}.w3.weight", views[f"wgu{x}"][f:]
+        yield m + "gate.weight", views["router"]
+        yield p + "input_layernorm.weight", views["ln1"]
+        yield p + "post_attention_layernorm.weight", views["ln2"]
+        return
     yield p + "mlp.gate_proj.weight", views["wgu"][:f]
     if cfg.mlp_bias:
         yield p + "mlp.gate_proj.bias", views["bgu"][:f]

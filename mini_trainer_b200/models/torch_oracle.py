@@ -51,6 +51,17 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
             outs.append(o[0].transpose(0, 1).reshape(b - a, hq * d))
         x = x + rm * F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
         n = _rms(x, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
+        if cfg.is_moe:   # dense restatement: every expert on every token, masked by the routing weights
+            m = p + "block_sparse_moe."
+            probs = F.softmax(F.linear(n, sd[m + "gate.weight"]).float(), -1)
+            topv, topi = probs.topk(cfg.num_experts_per_tok, -1)
+            gatew = torch.zeros_like(probs).scatter(1, topi, topv / topv.sum(-1, keepdim=True))
+            y = 0
+            for e in range(cfg.num_local_experts):
+                a = F.silu(F.linear(n, sd[m + f"experts.{e}.w1.weight"])) * F.linear(n, sd[m + f"experts.{e}.w3.weight"])
+                y = y + gatew[:, e: e + 1].to(n.dtype) * F.linear(a, sd[m + f"experts.{e}.w2.weight"])
+            x = x + rm * y
+            continue
         act = F.silu(F.linear(n, sd[p + "mlp.gate_proj.weight"], sd.get(p + "mlp.gate_proj.bias"))) \
             * F.linear(n, sd[p + "mlp.up_proj.weight"], sd.get(p + "mlp.up_proj.bias"))
         x = x + rm * F.linear(act, sd[p + "mlp.down_proj.weight"], sd.get(p + "mlp.down_proj.bias"))

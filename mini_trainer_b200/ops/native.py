@@ -198,12 +198,14 @@ class NativeOps:
         return dx
 
     # -- linear -----------------------------------------------------------------------
-    def linear(self, x, w, bias=None, residual=None, gather=None, alpha=1.0):
+    def linear(self, x, w, bias=None, residual=None, gather=None, alpha=1.0, out=None):
         """``alpha * x @ w.T (+bias) (+residual)``. ``gather = (GatherPlan, stage)`` runs the projection with the all-gather of its parameter
-        group fused into the same kernel (symmetric-memory backend only)."""
+        group fused into the same kernel (symmetric-memory backend only). ``out``: write into this ``[T, N]`` view (rows of a
+        larger buffer) instead of a new tensor."""
         T, K = x.shape
         N = w.shape[0]
-        out = torch.empty(T, N, dtype=x.dtype, device=self.device)
+        if out is None:
+            out = torch.empty(T, N, dtype=x.dtype, device=self.device)
         if gather is not None:
             assert residual is None and alpha == 1.0
             ev = self._ev()
@@ -212,10 +214,11 @@ class NativeOps:
             return out
         return self.gemm(x, False, w, False, out, T, N, K, residual=residual, bias=bias, alpha=alpha)
 
-    def linear_dgrad(self, dy, w, alpha=1.0):
+    def linear_dgrad(self, dy, w, alpha=1.0, out=None):
         T, N = dy.shape
         K = w.shape[1]
-        out = torch.empty(T, K, dtype=dy.dtype, device=self.device)
+        if out is None:
+            out = torch.empty(T, K, dtype=dy.dtype, device=self.device)
         return self.gemm(dy, False, w, True, out, T, K, N, alpha=alpha)
 
     def linear_wgrad(self, dy, x, dw_out, dbias_out=None, alpha=1.0):

@@ -53,7 +53,7 @@ class TorchOps:
         return dx.to(x.dtype)
 
     # -- linear -----------------------------------------------------------------------
-    def linear(self, x, w, bias=None, residual=None, gather=None, alpha=1.0):
+    def linear(self, x, w, bias=None, residual=None, gather=None, alpha=1.0, out=None):
         y = x @ w.t()
         if alpha != 1.0:
             y = y * alpha
@@ -61,10 +61,11 @@ class TorchOps:
             y = y + bias
         if residual is not None:
             y = y + residual
-        return y
+        return y if out is None else out.copy_(y)
 
-    def linear_dgrad(self, dy, w, alpha=1.0):
-        return dy @ w if alpha == 1.0 else (dy @ w) * alpha
+    def linear_dgrad(self, dy, w, alpha=1.0, out=None):
+        y = dy @ w if alpha == 1.0 else (dy @ w) * alpha
+        return y if out is None else out.copy_(y)
 
     def linear_wgrad(self, dy, x, dw_out, dbias_out=None, alpha=1.0):
         dw_out.copy_(((dy.float().t() @ x.float()) * alpha).to(dw_out.dtype))

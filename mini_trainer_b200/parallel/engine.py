@@ -139,7 +139,9 @@ class ShardedEngine:
         # symmetric arena when it has one; otherwise they are ordinary device tensors.
         self.symmetric = hasattr(self.comm, "setup")
         # the fused gather resolves one shard boundary per 128 KB chunk, so shards must be at least that large
-        self.fused_gather = (self.symmetric and os.environ.get("MTB200_FUSED_GATHER", "1") != "0"
+        # (a mixture-of-experts block has no single gate/up GEMM to carry the second half of the gather: its
+        # parameters are prefetched by the stand-alone all-gather, one block ahead, on the side stream)
+        self.fused_gather = (self.symmetric and os.environ.get("MTB200_FUSED_GATHER", "1") != "0" and not cfg.is_moe
                              and layouts[1].shard_numel * torch.empty(0, dtype=self.param_dtype).element_size() >= 128 * 1024)
         if self.symmetric:
             es = torch.empty(0, dtype=self.param_dtype).element_size()
@@ -173,7 +175,8 @@ class ShardedEngine:
         self._oom_retries = 0
         # Reduce a block's gradients tensor region by tensor region while its backward still runs
         # (MTB200_REGION_OVERLAP=0: one reduction per block, after its backward).
-        self.region_overlap = os.environ.get("MTB200_REGION_OVERLAP", "1") != "0"
+        # A mixture-of-experts block is reduced once: its experts' gradients complete in no fixed layout order.
+        self.region_overlap = os.environ.get("MTB200_REGION_OVERLAP", "1") != "0" and not cfg.is_moe
         # checkpoint level 3: block inputs parked in pinned host memory, two device staging buffers for the way back
         self._copy_stream = None
         self._host_inputs = {}
@@ -442,7 +445,7 @@ class ShardedEngine:
         if budget <= 0:
             return levels
         es = 2 if self.param_dtype != torch.float32 else 4
-        h, f = cfg.hidden_size, cfg.intermediate_size
+        h, f = cfg.hidden_size, cfg.intermediate_size * cfg.mlp_rows_factor
         lvl1 = tokens * (cfg.q_size * es + cfg.num_attention_heads * 4)
         # level 0 keeps qkv, the attention output, h1 and gate/up (the normalised inputs and the SwiGLU
         # output are rebuilt in backward by elementwise kernels)
@@ -472,7 +475,7 @@ class ShardedEngine:
             return 0
         cfg = self.cfg
         total = torch.cuda.get_device_properties(self.device).total_memory
-        h, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+        h, f, v = cfg.hidden_size, cfg.intermediate_size * cfg.mlp_rows_factor, cfg.vocab_size
         base = tokens * 2 * h * len(self.blocks)
         work = tokens * 2 * (7 * h + cfg.qkv_size + 6 * f)
         ce = getattr(self.ops, "ce_chunk", 2048) * v * 2 + v * h * 4

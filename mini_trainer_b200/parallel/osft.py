@@ -556,6 +556,9 @@ class OSFT:
 def enable_osft(engine, rank_ratio: float = 0.5, **kw) -> OSFT:
     """Switches ``engine.optimizer_step`` (and the reduction of the projection gradients, where the
     backend supports ownership by matrix) to the OSFT update. Returns the controller."""
+    if engine.cfg.is_moe:
+        raise ValueError("OSFT is defined here for the seven dense projections of a block; a mixture-of-experts model "
+                         "is trained with the plain AdamW update")
     ctl = OSFT(engine, rank_ratio, **kw)
     engine.osft = ctl
     engine.optimizer_step = ctl.optimizer_step

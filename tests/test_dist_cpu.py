@@ -30,15 +30,15 @@ def free_port():
     return p
 
 
-def run_training(rank, world, port, out_dir, steps):
+def run_training(rank, world, port, out_dir, steps, preset="tiny-qwen2"):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
                       MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.set_num_threads(2)
     if world > 1:
         dist.init_process_group("gloo", rank=rank, world_size=world)
     spec, vocab, max_tokens, batch_size = CONFIG_DATA["tiny-qwen2"]
-    ds = synthetic_dataset(512, spec, vocab, seed=893)
-    cfg = get_preset("tiny-qwen2")
+    cfg = get_preset(preset)
+    ds = synthetic_dataset(512, spec, min(vocab, cfg.vocab_size), seed=893)
     eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), comm=make_comm("auto"), optim=OptimConfig())
     eng.init_random(seed=893)
     model, opt, sched = setup_training_components(eng, learning_rate=1e-4, num_warmup_steps=2)
@@ -50,8 +50,8 @@ def run_training(rank, world, port, out_dir, steps):
         dist.destroy_process_group()
 
 
-def _spawn_entry(rank, world, port, out_dir, steps):
-    run_training(rank, world, port, out_dir, steps)
+def _spawn_entry(rank, world, port, out_dir, steps, preset="tiny-qwen2"):
+    run_training(rank, world, port, out_dir, steps, preset)
 
 
 @pytest.mark.timeout(900)
@@ -105,3 +105,26 @@ def test_three_ranks_match_one_rank(tmp_path):
     assert abs(a["loss"] - b["loss"]) < 2e-4 * abs(a["loss"]), (a["loss"], b["loss"])
     assert abs(a["grad_norm"] - b["grad_norm"]) < 2e-3 * a["grad_norm"]
     assert a["num_loss_counted_tokens"] == b["num_loss_counted_tokens"] and b["num_samples"] == 32
+
+
+@pytest.mark.timeout(900)
+def test_two_ranks_match_one_rank_mixture_of_experts(tmp_path):
+    """A small Mixtral (4 experts, 2 per token): expert and router parameters are sharded, gathered and reduced like any
+    other tensor of the block's flat buffer, and the export carries the published checkpoint names."""
+    one, two = str(tmp_path / "w1"), str(tmp_path / "w2")
+    os.makedirs(one); os.makedirs(two)
+    run_training(0, 1, free_port(), one, 2, "tiny-mixtral")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    mp.spawn(_spawn_entry, args=(2, free_port(), two, 2, "tiny-mixtral"), nprocs=2, join=True)
+    r1 = [json.loads(l) for l in open(os.path.join(one, "training_metrics_0.jsonl"))]
+    r2 = [json.loads(l) for l in open(os.path.join(two, "training_metrics_0.jsonl"))]
+    for a, b in zip(r1, r2):
+        assert abs(a["loss"] - b["loss"]) < 2e-4 * abs(a["loss"]), (a["loss"], b["loss"])
+        assert abs(a["grad_norm"] - b["grad_norm"]) < 2e-3 * a["grad_norm"]
+    d2 = os.path.join(two, "hf_format", "samples_64.0")
+    from mini_trainer_b200.ckpt import safetensors_io as st
+    names = set(st.load_file(os.path.join(d2, "model.safetensors")))
+    assert {"model.layers.1.block_sparse_moe.gate.weight", "model.layers.0.block_sparse_moe.experts.3.w2.weight"} <= names
+    cfg = ModelConfig.from_pretrained(d2)
+    assert cfg.is_moe and cfg.num_local_experts == 4 and cfg.architectures == ["MixtralForCausalLM"]

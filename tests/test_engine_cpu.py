@@ -32,9 +32,16 @@ def hf_state(engine):
     return {k: v.clone() for k, v in engine.iter_hf_tensors(dtype=torch.float32)}
 
 
-def check_grads(tied, bias):
+def moe_cfg(experts: int = 4, top_k: int = 2) -> ModelConfig:
+    return ModelConfig(vocab_size=97, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, rope_theta=1e4, rms_norm_eps=1e-6,
+                       model_type="mixtral", architectures=["MixtralForCausalLM"],
+                       num_local_experts=experts, num_experts_per_tok=top_k)
+
+
+def check_grads(tied, bias, cfg=None):
     torch.manual_seed(0)
-    cfg = small_cfg(tied, bias)
+    cfg = cfg or small_cfg(tied, bias)
     eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), optim=OptimConfig(lr=1e-3))
     eng.init_random(seed=3, std=0.2)
     mb = make_mb([7, 1, 12, 5], cfg.vocab_size)
@@ -67,6 +74,18 @@ def test_grads_tied_bias():
     check_grads(True, True)
 
 
+def test_grads_mixture_of_experts():
+    """Router (softmax, top-k, renormalisation) and routed SwiGLU experts against a dense autograd restatement."""
+    check_grads(False, False, moe_cfg())
+
+
+def test_grads_mixture_of_experts_with_an_idle_expert(monkeypatch):
+    """16 experts for 25 tokens x 1 choice: several experts get no token; their gradients must be zero, not what the
+    (here NaN-poisoned) gradient buffer held before."""
+    monkeypatch.setenv("MTB200_POISON", "1")
+    check_grads(False, False, moe_cfg(experts=16, top_k=1))
+
+
 def test_adamw_matches_torch():
     cfg = small_cfg(False, True)
     eng = ShardedEngine(cfg, "cpu", get_ops("cpu"), optim=OptimConfig(lr=1e-2, max_grad_norm=1.0))
@@ -90,7 +109,14 @@ def test_adamw_matches_torch():
 
 def test_checkpoint_levels_give_identical_gradients():
     """Keeping the attention output (level 1) or every GEMM output (level 0) must not change the math."""
-    cfg = small_cfg(False, True)
+    _check_levels(small_cfg(False, True))
+
+
+def test_checkpoint_levels_give_identical_gradients_mixture_of_experts():
+    _check_levels(moe_cfg())
+
+
+def _check_levels(cfg):
     mb = make_mb([11, 3, 8], cfg.vocab_size, seed=4)
     grads = []
     for budget in (0, None, 10 ** 12):

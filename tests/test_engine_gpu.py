@@ -91,6 +91,53 @@ def test_native_engine_with_projection_biases_matches_fp32_reference(residual_mu
             assert gb[n].norm() > 0 and err < 5e-2, (a.layout.name, n, err.item())
 
 
+def test_native_engine_mixture_of_experts_matches_fp32_reference(monkeypatch):
+    """A small Mixtral on the kernels: expert slabs of uneven height through the tcgen05 GEMM (row slices of shared
+    buffers), row gathers by the embedding kernel, router in torch. The fp32 reference replays the experts the native run
+    selected (a near-tie in bf16 may otherwise pick another expert) while its weights follow its own logits."""
+    from mini_trainer_b200.models import moe as M
+    from mini_trainer_b200.ops.native import NativeOps
+    cfg = get_preset("tiny-mixtral")
+    ops = NativeOps("cuda:0")
+    eng = ShardedEngine(cfg, "cuda:0", ops, optim=OptimConfig(), activation_budget_bytes=0)
+    eng.init_random(seed=13, std=0.05)
+    ref = ShardedEngine(cfg, "cuda:0", get_ops("cuda:0", "torch"), param_dtype=torch.float32, optim=OptimConfig(),
+                        activation_budget_bytes=0)
+    for a, b in zip(eng.groups, ref.groups):
+        b.master.copy_(a.shard.float()); b.shard.copy_(b.master)
+    mb = make_mb([300, 17, 129, 1, 640], cfg.vocab_size)
+    batch = D.make_packed_batch(mb, "cuda:0")
+    scale = 1.0 / mb["batch_num_loss_counted_tokens"]
+    chosen, orig = [], M.route
+
+    def record(cfg_, w, n2):
+        r = orig(cfg_, w, n2)
+        chosen.append(r[1])
+        return r
+
+    monkeypatch.setattr(M, "route", record)
+    l1 = eng.forward_backward(batch, scale)
+    replay = list(chosen)
+    monkeypatch.setattr(M, "route", lambda cfg_, w, n2: orig(cfg_, w, n2, topi=replay.pop(0)))
+    l2 = ref.forward_backward(batch, scale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert not replay and len(chosen) == 2 * cfg.num_hidden_layers      # forward + recompute of every block
+    counts = torch.bincount(chosen[0].reshape(-1), minlength=cfg.num_local_experts)
+    assert counts.sum() == 2 * batch.num_tokens and (counts > 0).all()
+    assert abs(l1.sum().item() - l2.sum().item()) < 2e-2 * abs(l2.sum().item())
+    for a, b in zip(eng.groups, ref.groups):
+        err = (a.gacc - b.gacc).norm() / (b.gacc.norm() + 1e-12)
+        assert err < 5e-2, (a.layout.name, err.item())
+    for a, b in zip(eng.blocks, ref.blocks):
+        ga, gb = a.layout.views(a.gacc), b.layout.views(b.gacc)
+        for n in ("router", "wgu0", "wd3"):
+            err = (ga[n] - gb[n]).norm() / (gb[n].norm() + 1e-12)
+            assert err < 6e-2, (a.layout.name, n, err.item())
+    n1, n2 = eng.optimizer_step(1e-4), ref.optimizer_step(1e-4)
+    assert abs(n1.item() - n2.item()) < 3e-2 * n2.item()
+
+
 def test_osft_step_runs_with_native_kernels():
     from mini_trainer_b200.ops.native import NativeOps
     from mini_trainer_b200.parallel.osft import enable_osft

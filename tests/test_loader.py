@@ -26,7 +26,9 @@ def _hf_dir(tmp_path, kind, **over):
     cls = {"llama": (transformers.LlamaConfig, {}), "qwen2": (transformers.Qwen2Config, {}),
            "mistral": (transformers.MistralConfig, {"sliding_window": None}),
            "granite": (transformers.GraniteConfig, {"embedding_multiplier": 12.0, "residual_multiplier": 0.22,
-                                                    "attention_multiplier": 0.0625, "logits_scaling": 8.0})}[kind]
+                                                    "attention_multiplier": 0.0625, "logits_scaling": 8.0}),
+           "mixtral": (transformers.MixtralConfig, {"sliding_window": None, "num_local_experts": 4,
+                                                    "num_experts_per_tok": 2})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
     cfg = cls[0](**kw)
@@ -46,7 +48,7 @@ def _our_logits(eng, ids):
     return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb)
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -77,6 +79,44 @@ def test_granite_multipliers_reach_the_gradients(tmp_path):
     assert torch.allclose(got["wqkv"][:q], want["model.layers.1.self_attn.q_proj.weight"].grad, atol=1e-5, rtol=1e-3)
     emb = eng.embed.layout.views(eng.embed.gacc)["embed"]
     assert torch.allclose(emb, want["model.embed_tokens.weight"].grad, atol=1e-5, rtol=1e-3)
+
+
+def test_mixture_of_experts_gradients_and_export_against_transformers(tmp_path):
+    """Mixtral: router and expert gradients of the hand-written backward against autograd through transformers, and
+    the exported checkpoint (published tensor names) loads there and gives the same logits."""
+    path, hf = _hf_dir(tmp_path, "mixtral")
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.is_moe and not eng.region_overlap
+    ids = torch.randint(0, COMMON["vocab_size"], (26,))
+    labels = ids.clone()
+    labels[:6] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 26, "num_loss_counted_tokens": 20}], 20)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 20, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 20 - float(out.loss)) < 1e-4
+    got = eng.blocks[0].layout.views(eng.blocks[0].gacc)
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    f = eng.cfg.intermediate_size
+    L = "model.layers.0.mlp."
+    assert torch.allclose(got["router"], want[L + "gate.weight"], atol=1e-5, rtol=1e-3)
+    for e in range(4):
+        assert torch.allclose(got[f"wgu{e}"], want[L + "experts.gate_up_proj"][e], atol=1e-5, rtol=1e-3)
+        assert torch.allclose(got[f"wd{e}"], want[L + "experts.down_proj"][e], atol=1e-5, rtol=1e-3)
+    assert torch.allclose(got["wo"], want["model.layers.0.self_attn.o_proj.weight"], atol=1e-5, rtol=1e-3)
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    with torch.no_grad():
+        ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
+
+
+def test_mixture_of_experts_with_auxiliary_loss_is_refused(tmp_path):
+    path, _ = _hf_dir(tmp_path, "mixtral", output_router_logits=True)
+    with pytest.raises(ValueError, match="load-balancing loss"):
+        setup_model(path, device="cpu")
 
 
 class _Tok:

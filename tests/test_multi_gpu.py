@@ -29,7 +29,7 @@ from mini_trainer_b200.data.synthetic import LengthSpec, synthetic_dataset
 
 device = init_distributed_environment(timeout_minutes=3)
 rank, world = dist.get_rank(), dist.get_world_size()
-cfg = get_preset("smoke-llama")
+cfg = get_preset(os.environ.get("MTB200_PRESET", "smoke-llama"))
 comm = make_comm(os.environ.get("MTB200_COMM", "auto"), device)
 budget = os.environ.get("MTB200_TEST_BUDGET", "0")
 eng = ShardedEngine(cfg, device, get_ops(device), comm=comm, optim=OptimConfig(),
@@ -143,6 +143,18 @@ def test_osft_two_gpus_match_one_gpu(comm, fused, tmp_path):
     f1, f2 = str(tmp_path / "one.pt"), str(tmp_path / "two.pt")
     one = _run(1, "auto", out=f1, osft=True)
     two = _run(2, comm, "0", out=f2, osft=True, extra_env={"MTB200_OSFT_FUSED": fused})
+    _compare(one, two, f1, f2)
+
+
+def test_two_gpus_mixture_of_experts_match_one_gpu(tmp_path):
+    """A small Mixtral over the symmetric backend: the block (router and experts included) arrives by the stand-alone
+    peer-load all-gather one block ahead and its gradient buffer is reduced in one piece."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    f1, f2 = str(tmp_path / "one.pt"), str(tmp_path / "two.pt")
+    env = {"MTB200_PRESET": "tiny-mixtral"}
+    one = _run(1, "auto", out=f1, extra_env=env)
+    two = _run(2, "symmetric", "0", out=f2, extra_env=env)
     _compare(one, two, f1, f2)
 
 
