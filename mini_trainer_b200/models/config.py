@@ -285,6 +285,10 @@ PRESETS = {
                                  num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6, rms_norm_eps=1e-6),
     "llama-3.1-70b": lambda: _llama(vocab_size=128256, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
                                     num_attention_heads=64, num_key_value_heads=8, rope_theta=5e5, rms_norm_eps=1e-5),
+    "mixtral-8x7b": lambda: ModelConfig(model_type="mixtral", architectures=["MixtralForCausalLM"], vocab_size=32000,
+                                        hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                                        num_attention_heads=32, num_key_value_heads=8, rope_theta=1e6, rms_norm_eps=1e-5,
+                                        num_local_experts=8, num_experts_per_tok=2),
     # a small Mixtral (4 experts, 2 per token) for CPU and GPU tests (head_dim 128 on the GPU kernels' account)
     "tiny-mixtral": lambda: ModelConfig(model_type="mixtral", architectures=["MixtralForCausalLM"], vocab_size=4096,
                                         hidden_size=256, intermediate_size=384, num_hidden_layers=2, num_attention_heads=2,
