@@ -75,14 +75,20 @@ class ModelConfig:
 
     @property
     def attention_window(self) -> Optional[int]:
-        """Sliding-window length where the model applies one (Mistral always, Qwen2 with ``use_sliding_window``), else
+        """Sliding-window length where the model applies one (Mistral, Mixtral, Phi-3 always; Qwen2 with ``use_sliding_window``), else
         ``None``. A query sees the last ``window`` keys including itself (masking_utils.sliding_window_overlay), so for
         samples of at most ``window`` tokens windowed and full causal attention are the same function. The attention
         kernels here are full causal: the engine accepts such a model and refuses a minibatch that holds a longer sample."""
         if self.sliding_window is None or self.sliding_window >= self.max_position_embeddings:
             return None
-        on = self.use_sliding_window if self.use_sliding_window is not None else self.model_type == "mistral"
+        on = self.use_sliding_window if self.use_sliding_window is not None else self.model_type in ("mistral", "mixtral", "phi3")
         return int(self.sliding_window) if on else None
+
+    @property
+    def fused_hf_names(self) -> bool:
+        """Phi-3 checkpoints store q|k|v and gate|up already fused (``qkv_proj``, ``gate_up_proj``), in the order
+        the flat layout uses."""
+        return self.model_type == "phi3"
 
     @property
     def is_moe(self) -> bool:
@@ -103,6 +109,12 @@ class ModelConfig:
                 problems.append(f"num_experts_per_tok={self.num_experts_per_tok} of {self.num_local_experts} experts")
         if arch not in SUPPORTED_ARCHITECTURES:
             problems.append(f"architecture {arch} is not one of {', '.join(SUPPORTED_ARCHITECTURES)}")
+        for k in ("attention_dropout", "resid_pdrop", "embd_pdrop", "residual_dropout", "embedding_dropout", "hidden_dropout"):
+            if self.extra.get(k):
+                problems.append(f"{k}={self.extra[k]} (dropout is not implemented; set it to 0 to train without)")
+        prf = (self.extra.get("rope_parameters") or {}).get("partial_rotary_factor", self.extra.get("partial_rotary_factor", 1.0))
+        if prf not in (None, 1.0):
+            problems.append(f"partial_rotary_factor={prf} (the rotary kernel turns the whole head)")
         if self.hidden_act not in ("silu", "swish"):
             problems.append(f"hidden_act={self.hidden_act!r} (only the SwiGLU MLP is implemented)")
         if problems:
@@ -260,7 +272,7 @@ class ModelConfig:
 
 
 SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
-                           "MixtralForCausalLM")
+                           "MixtralForCausalLM", "Phi3ForCausalLM")
 
 
 def _llama(**kw):

@@ -103,6 +103,14 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
     """Yields ``(hf_name, tensor_view)`` for one block, in HF ``state_dict`` order."""
     p = f"model.layers.{layer}."
     q, kv = cfg.q_size, cfg.kv_size
+    if cfg.fused_hf_names:   # Phi-3: the checkpoint's tensors are the layout's
+        yield p + "self_attn.qkv_proj.weight", views["wqkv"]
+        yield p + "self_attn.o_proj.weight", views["wo"]
+        yield p + "mlp.gate_up_proj.weight", views["wgu"]
+        yield p + "mlp.down_proj.weight", views["wd"]
+        yield p + "input_layernorm.weight", views["ln1"]
+        yield p + "post_attention_layernorm.weight", views["ln2"]
+        return
     w = views["wqkv"]
     yield p + "self_attn.q_proj.weight", w[:q]
     if cfg.attention_bias:

@@ -28,7 +28,8 @@ def _hf_dir(tmp_path, kind, **over):
            "granite": (transformers.GraniteConfig, {"embedding_multiplier": 12.0, "residual_multiplier": 0.22,
                                                     "attention_multiplier": 0.0625, "logits_scaling": 8.0}),
            "mixtral": (transformers.MixtralConfig, {"sliding_window": None, "num_local_experts": 4,
-                                                    "num_experts_per_tok": 2})}[kind]
+                                                    "num_experts_per_tok": 2}),
+           "phi3": (transformers.Phi3Config, {"pad_token_id": 0, "eos_token_id": 2})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
     cfg = cls[0](**kw)
@@ -48,7 +49,7 @@ def _our_logits(eng, ids):
     return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb)
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -108,6 +109,24 @@ def test_mixture_of_experts_gradients_and_export_against_transformers(tmp_path):
     out_dir = str(tmp_path / "export")
     save_hf_checkpoint(eng, out_dir)
     back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    with torch.no_grad():
+        ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
+
+
+def test_phi3_export_keeps_the_fused_tensor_names(tmp_path):
+    """Phi-3 stores q|k|v and gate|up fused; the export writes them the same way and transformers loads it."""
+    path, hf = _hf_dir(tmp_path, "phi3", sliding_window=64)
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.attention_window == 64
+    from mini_trainer_b200.ckpt import safetensors_io as st
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
+    names = set(st.load_file(os.path.join(out_dir, "model.safetensors")))
+    assert "model.layers.0.self_attn.qkv_proj.weight" in names and "model.layers.1.mlp.gate_up_proj.weight" in names
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    ids = torch.randint(0, COMMON["vocab_size"], (17,))
     with torch.no_grad():
         ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
     assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
@@ -200,6 +219,8 @@ def test_projection_biases_reach_logits_gradients_and_exports(tmp_path, kind):
 
 @pytest.mark.parametrize("kind,over,needle", [
     ("llama", {"hidden_act": "gelu"}, "hidden_act"),
+    ("llama", {"attention_dropout": 0.1}, "attention_dropout"),
+    ("phi3", {"resid_pdrop": 0.1}, "resid_pdrop"),
 ])
 def test_models_the_block_cannot_compute_are_refused(tmp_path, kind, over, needle):
     path, _ = _hf_dir(tmp_path, kind, **over)
