@@ -182,6 +182,16 @@ __global__ void reduce_rows_kernel(const float* __restrict__ part, __nv_bfloat16
   out[c] = __float2bfloat16(s);
 }
 
+// Same for rows that hold two vectors of D columns each, delivered to two outputs.
+__global__ void reduce_rows_pair_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out_a, __nv_bfloat16* __restrict__ out_b,
+                                        int R, int D) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * D) return;
+  float s = 0.f;
+  for (int r = 0; r < R; ++r) s += part[static_cast<long long>(r) * 2 * D + c];
+  if (c < D) out_a[c] = __float2bfloat16(s); else out_b[c - D] = __float2bfloat16(s);
+}
+
 // ------------------------------------------------------------------------------ RoPE
 // In place on the first n_heads (q then k) heads of each row of qkv[T, ld]. Rotate-half
 // convention: (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin), angle = fp32(pos) * inv_freq[i]
@@ -221,6 +231,122 @@ __global__ void __launch_bounds__(EW_THREADS) rope_kernel(__nv_bfloat16* __restr
       a[j].from_float(o1); b[j].from_float(o2);
       a[j].store(row + (h0 + j) * D + i0); b[j].store(row + (h0 + j) * D + i0 + half);
     }
+  }
+}
+
+// ------------------------------------------------------------------------------ per-head RMSNorm (q_norm / k_norm)
+// Qwen3 normalises every q and k head over head_dim before the rotary embedding, with one weight vector for all q
+// heads and one for all k heads. In place on the first n_heads (q then k) heads of each row of qkv[T, ld]: one warp per
+// (token, head), a lane holds EPL = head_dim / 32 consecutive elements, the sum of squares is a shuffle reduction.
+// y = bf16(x * rstd) * w, rstd[token * n_heads + head] saved.
+template <int EPL>
+struct HeadVec {
+  uint32_t raw[EPL / 2];
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+    if constexpr (EPL == 8) { const uint4 v = *reinterpret_cast<const uint4*>(p); raw[0] = v.x; raw[1] = v.y; raw[2] = v.z; raw[3] = v.w; }
+    else if constexpr (EPL == 4) { const uint2 v = *reinterpret_cast<const uint2*>(p); raw[0] = v.x; raw[1] = v.y; }
+    else { raw[0] = *reinterpret_cast<const uint32_t*>(p); }
+  }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+    if constexpr (EPL == 8) *reinterpret_cast<uint4*>(p) = make_uint4(raw[0], raw[1], raw[2], raw[3]);
+    else if constexpr (EPL == 4) *reinterpret_cast<uint2*>(p) = make_uint2(raw[0], raw[1]);
+    else *reinterpret_cast<uint32_t*>(p) = raw[0];
+  }
+  __device__ __forceinline__ void to_float(float (&f)[EPL]) const {
+#pragma unroll
+    for (int i = 0; i < EPL / 2; ++i) { const float2 a = unpack_bf16(raw[i]); f[2 * i] = a.x; f[2 * i + 1] = a.y; }
+  }
+  __device__ __forceinline__ void from_float(const float (&f)[EPL]) {
+#pragma unroll
+    for (int i = 0; i < EPL / 2; ++i) raw[i] = pack_bf16(f[2 * i], f[2 * i + 1]);
+  }
+};
+
+template <int EPL>
+__global__ void __launch_bounds__(EW_THREADS) head_rmsnorm_fwd_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq,
+                                                                     const __nv_bfloat16* __restrict__ wk, float* __restrict__ rstd_out,
+                                                                     float eps, long long n_rows, long long ld, int n_q, int n_heads) {
+  constexpr int D = EPL * 32;
+  const long long r = static_cast<long long>(blockIdx.x) * (EW_THREADS / 32) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= n_rows) return;   // whole warps leave together
+  const long long t = r / n_heads;
+  const int h = static_cast<int>(r - t * n_heads);
+  __nv_bfloat16* p = qkv + t * ld + static_cast<long long>(h) * D + lane * EPL;
+  HeadVec<EPL> xv, wv;
+  xv.load(p);
+  wv.load((h < n_q ? wq : wk) + lane * EPL);
+  float f[EPL], g[EPL];
+  xv.to_float(f); wv.to_float(g);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) ss += f[i] * f[i];
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / D + eps);
+  if (lane == 0) rstd_out[r] = rstd;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] * rstd)) * g[i];
+  xv.from_float(f);
+  xv.store(p);
+}
+
+// Backward, in place on dqkv (gradient of the normalised heads in, gradient of the projection output out):
+// dx = rstd * (g - xhat * mean(g * xhat)), g = dy * w, xhat = x * rstd with x the heads BEFORE the norm (pre[T, ld_pre],
+// q then k heads). Weight gradients: dwp[block, 2, D] += dy * bf16(xhat) per block in fp32 (q heads in row 0, k heads in
+// row 1), summed over blocks by reduce_rows_kernel: no atomics. Persistent warps loop over (token, head) rows; a lane
+// keeps the same columns throughout, so its partial sums stay in registers.
+template <int EPL>
+__global__ void __launch_bounds__(EW_THREADS) head_rmsnorm_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __restrict__ pre,
+                                                                     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ wq,
+                                                                     const __nv_bfloat16* __restrict__ wk, float* __restrict__ dwp,
+                                                                     long long n_rows, long long ld, long long ld_pre, int n_q, int n_heads) {
+  constexpr int D = EPL * 32;
+  constexpr int WARPS = EW_THREADS / 32;
+  __shared__ float sm[WARPS][2][D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float wqf[EPL], wkf[EPL], accq[EPL], acck[EPL];
+  {
+    HeadVec<EPL> a, b;
+    a.load(wq + lane * EPL); b.load(wk + lane * EPL);
+    a.to_float(wqf); b.to_float(wkf);
+  }
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) { accq[i] = 0.f; acck[i] = 0.f; }
+  const long long stride = static_cast<long long>(gridDim.x) * WARPS;
+  for (long long r = static_cast<long long>(blockIdx.x) * WARPS + warp; r < n_rows; r += stride) {
+    const long long t = r / n_heads;
+    const int h = static_cast<int>(r - t * n_heads);
+    const bool is_q = h < n_q;
+    __nv_bfloat16* gp = dqkv + t * ld + static_cast<long long>(h) * D + lane * EPL;
+    HeadVec<EPL> gv, xv;
+    gv.load(gp);
+    xv.load(pre + t * ld_pre + static_cast<long long>(h) * D + lane * EPL);
+    const float rstd = rstd_in[r];
+    float dy[EPL], x[EPL], g[EPL], xh[EPL];
+    gv.to_float(dy); xv.to_float(x);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      xh[i] = x[i] * rstd;
+      g[i] = dy[i] * (is_q ? wqf[i] : wkf[i]);
+      dot += g[i] * xh[i];
+      const float c = dy[i] * __bfloat162float(__float2bfloat16(xh[i]));
+      if (is_q) accq[i] += c; else acck[i] += c;
+    }
+    dot = warp_sum(dot) / D;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) g[i] = rstd * (g[i] - xh[i] * dot);
+    gv.from_float(g);
+    gv.store(gp);
+  }
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) { sm[warp][0][lane * EPL + i] = accq[i]; sm[warp][1][lane * EPL + i] = acck[i]; }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * D; c += EW_THREADS) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) s += sm[w][c / D][c % D];
+    dwp[static_cast<long long>(blockIdx.x) * 2 * D + c] = s;
   }
 }
 
@@ -548,6 +674,43 @@ int mtb200_rope(void* qkv, const int* pos, const float* inv_freq, int T, long lo
   const long long n = static_cast<long long>(T) * (D / 16);
   rope_kernel<<<dim3(cdiv(n, EW_THREADS), cdiv(n_heads, ROPE_HPT)), EW_THREADS, 0, st>>>((bf16*)qkv, pos, inv_freq, T, ld, n_heads, D,
                                                                                         inverse ? -1.f : 1.f);
+  return launch_ok();
+}
+
+// Per-head RMSNorm of the q and k heads (n_q then n_heads - n_q) of qkv[T, ld], in place; rstd: [T * n_heads] fp32.
+int mtb200_head_rmsnorm_fwd(void* qkv, const void* wq, const void* wk, float* rstd, float eps, int T, long long ld, int n_q, int n_heads,
+                            int D, cudaStream_t st) {
+  if (T <= 0 || n_heads <= 0) return 0;
+  if ((D != 64 && D != 128 && D != 256) || ld % 8 || n_q < 0 || n_q > n_heads) return -10;
+  const long long n_rows = static_cast<long long>(T) * n_heads;
+  const unsigned blocks = static_cast<unsigned>(cdiv(n_rows, EW_THREADS / 32));
+#define HF(E) head_rmsnorm_fwd_kernel<E><<<blocks, EW_THREADS, 0, st>>>((bf16*)qkv, (const bf16*)wq, (const bf16*)wk, rstd, eps, n_rows, ld, n_q, n_heads)
+  if (D == 64) HF(2); else if (D == 128) HF(4); else HF(8);
+#undef HF
+  return launch_ok();
+}
+
+// Rows of the dw_partial scratch ([blocks, 2, D] fp32) the backward writes.
+int mtb200_head_rmsnorm_bwd_blocks(int T, int n_heads) {
+  const long long rows = static_cast<long long>(T) * n_heads;
+  const long long want = cdiv(rows, EW_THREADS / 32);
+  const long long cap = num_sms() * 4;
+  return static_cast<int>(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+// dqkv (q and k heads) in place; pre: the heads before the norm, [T, ld_pre]; dwq_out / dwk_out: [D] bf16 each.
+int mtb200_head_rmsnorm_bwd(void* dqkv, const void* pre, const float* rstd, const void* wq, const void* wk, float* dw_partial,
+                            void* dwq_out, void* dwk_out, int T, long long ld, long long ld_pre, int n_q, int n_heads, int D,
+                            cudaStream_t st) {
+  if (T <= 0 || n_heads <= 0) return 0;
+  if ((D != 64 && D != 128 && D != 256) || ld % 8 || ld_pre % 8 || n_q < 0 || n_q > n_heads) return -10;
+  const long long n_rows = static_cast<long long>(T) * n_heads;
+  const int blocks = mtb200_head_rmsnorm_bwd_blocks(T, n_heads);
+#define HB(E) head_rmsnorm_bwd_kernel<E><<<blocks, EW_THREADS, 0, st>>>((bf16*)dqkv, (const bf16*)pre, rstd, (const bf16*)wq, (const bf16*)wk, dw_partial, n_rows, ld, ld_pre, n_q, n_heads)
+  if (D == 64) HB(2); else if (D == 128) HB(4); else HB(8);
+#undef HB
+  // partial rows are [2, D]: columns 0..D-1 belong to the q weight, D..2D-1 to the k weight
+  reduce_rows_pair_kernel<<<cdiv(2 * D, 256), 256, 0, st>>>(dw_partial, (bf16*)dwq_out, (bf16*)dwk_out, blocks, D);
   return launch_ok();
 }
 

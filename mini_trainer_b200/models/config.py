@@ -1,8 +1,8 @@
 """Decoder configuration, read from / written to Hugging Face ``config.json``.
 
-Covers the Llama / Qwen2 / Mistral / Granite / Mixtral family the reference trains through
+Covers the Llama / Qwen2 / Qwen3 / Mistral / Phi-3 / Granite / Mixtral family the reference trains through
 ``AutoModelForCausalLM`` (setup_model_for_training.py:86-130): pre-norm decoder blocks with
-RMSNorm, rotary GQA attention (optional biases), a SwiGLU MLP or Mixtral's routed SwiGLU experts,
+RMSNorm, rotary GQA attention (optional biases, optional per-head q/k norm), a SwiGLU MLP or Mixtral's routed SwiGLU experts,
 tied or untied LM head, plus Granite's four scalars (embedding, residual, attention and logits
 multipliers).
 
@@ -56,6 +56,8 @@ class ModelConfig:
     hidden_act: str = "silu"
     # Mixtral (modeling_mixtral.py): the MLP of every block is num_local_experts SwiGLU experts, of which a
     # softmax router picks num_experts_per_tok per token; 0 experts = dense MLP
+    # Qwen3 (modeling_qwen3.py): RMSNorm over head_dim on every q and k head before the rotary embedding
+    qk_norm: bool = False
     num_local_experts: int = 0
     num_experts_per_tok: int = 2
     output_router_logits: bool = False
@@ -149,6 +151,7 @@ class ModelConfig:
         n = 2 * h + self.qkv_size * h + self.q_size * h + 3 * h * f * max(1, self.num_local_experts)
         n += self.num_local_experts * h   # router
         n += self.qkv_size if self.attention_bias else 0
+        n += 2 * self.head_dim if self.qk_norm else 0
         n += h if self.o_proj_bias else 0
         return n + (2 * f + h if self.mlp_bias else 0)
 
@@ -227,6 +230,8 @@ class ModelConfig:
                 kw.setdefault("rope_scaling", rp)
         if kw.get("model_type") == "qwen2":
             kw.setdefault("attention_bias", True)  # Qwen2 always has q/k/v biases
+        if kw.get("model_type") == "qwen3":
+            kw["qk_norm"] = True
         for k in ("bos_token_id", "eos_token_id", "pad_token_id"):
             if isinstance(kw.get(k), list):
                 d[k + "_list"] = kw[k]
@@ -241,6 +246,7 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         d = asdict(self)
         extra = d.pop("extra")
+        d.pop("qk_norm")   # implied by the model type, not a key of any Hugging Face config
         out = dict(extra)
         for k in ("bos_token_id", "eos_token_id", "pad_token_id"):
             lst = out.pop(k + "_list", None)
@@ -272,7 +278,7 @@ class ModelConfig:
 
 
 SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
-                           "MixtralForCausalLM", "Phi3ForCausalLM")
+                           "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM")
 
 
 def _llama(**kw):

@@ -94,6 +94,8 @@ class BlockActs:
     rstd2: torch.Tensor
     gu: torch.Tensor
     act: torch.Tensor
+    qk_pre: Optional[torch.Tensor] = None    # q|k heads before the per-head norm (Qwen3), [T, (Hq + Hkv) * D]
+    rstd_qk: Optional[torch.Tensor] = None   # reciprocal RMS per (token, head)
     moe: Optional[object] = None   # routing and expert pre-activations of a mixture-of-experts block (``moe.MoeState``)
 
 
@@ -114,6 +116,11 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
         plan.prefetch_small()
     n1, rstd1 = ops.rmsnorm(x, p["ln1"], cfg.rms_norm_eps)
     qkv = ops.linear(n1, p["wqkv"], p.get("bqkv"), gather=None if plan is None else (plan, 0))
+    qk_pre = rstd_qk = None
+    if cfg.qk_norm:   # the backward of the norm needs its input; the qkv tensor itself goes on normalised and rotated
+        qk_pre = qkv[:, : cfg.q_size + cfg.kv_size].clone()
+        rstd_qk = ops.head_rmsnorm_(qkv, p["qn"], p["kn"], cfg.rms_norm_eps, cfg.num_attention_heads,
+                                    cfg.num_key_value_heads, cfg.head_dim)
     ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
     rm = cfg.residual_multiplier   # Granite scales every branch output before the residual add (1.0 elsewhere)
     # the GEMM epilogue computes alpha * product + bias + residual; the models scale (product + bias)
@@ -131,9 +138,9 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
         out, st = moe_forward(ops, cfg, p, n2, h1, need_out, keep_act=keep is True)
         acts = None
         if keep == "compact":
-            acts = BlockActs(x, None, rstd1, qkv, attn, lse, h1, None, rstd2, None, None, st)
+            acts = BlockActs(x, None, rstd1, qkv, attn, lse, h1, None, rstd2, None, None, qk_pre, rstd_qk, st)
         elif keep:
-            acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, None, None, st)
+            acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, None, None, qk_pre, rstd_qk, st)
         return out, acts, ((attn, lse) if want_attn else None)
     gu = ops.linear(n2, p["wgu"], p.get("bgu"), gather=None if plan is None else (plan, 1))
     # a recompute that stops before the down projection does not need the SwiGLU output: backward rebuilds it
@@ -142,9 +149,9 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     out = ops.linear(act, p["wd"], bd, h1, alpha=rm) if need_out else None
     acts = None
     if keep == "compact":   # kept from forward to backward: drop what one elementwise kernel can rebuild
-        acts = BlockActs(x, None, rstd1, qkv, attn, lse, h1, None, rstd2, gu, None)
+        acts = BlockActs(x, None, rstd1, qkv, attn, lse, h1, None, rstd2, gu, None, qk_pre, rstd_qk)
     elif keep:
-        acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, gu, act)
+        acts = BlockActs(x, n1, rstd1, qkv, attn, lse, h1, n2, rstd2, gu, act, qk_pre, rstd_qk)
     return out, acts, ((attn, lse) if want_attn else None)
 
 
@@ -206,6 +213,9 @@ def _attention_backward(ops, cfg: ModelConfig, p: dict, g: dict, a: BlockActs, d
     del dattn
     ops.rope_(dqkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
               inverse=True)
+    if cfg.qk_norm:
+        ops.head_rmsnorm_bwd_(dqkv, a.qk_pre, a.rstd_qk, p["qn"], p["kn"], g["qn"], g["kn"], cfg.num_attention_heads,
+                              cfg.num_key_value_heads, cfg.head_dim)
     dn1 = ops.linear_dgrad(dqkv, p["wqkv"])
     n1 = a.n1 if a.n1 is not None else ops.rmsnorm(a.x, p["ln1"], cfg.rms_norm_eps)[0]
     ops.linear_wgrad(dqkv, n1, g["wqkv"], g.get("bqkv"))

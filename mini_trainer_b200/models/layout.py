@@ -64,6 +64,8 @@ def block_entries(cfg: ModelConfig) -> list:
     e = [("ln1", (h,))]
     if cfg.attention_bias:
         e.append(("bqkv", (cfg.qkv_size,)))
+    if cfg.qk_norm:
+        e += [("qn", (cfg.head_dim,)), ("kn", (cfg.head_dim,))]
     e += [("wqkv", (cfg.qkv_size, h)), ("wo", (h, cfg.q_size))]
     # Optional biases sit where both schedules want them: ``bo`` and ``bgu`` in front of ``wgu``, so the
     # gather fused into the QKV projection has brought them in before o_proj / gate-up run and backward has
@@ -122,6 +124,9 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
     if cfg.attention_bias:
         yield p + "self_attn.v_proj.bias", views["bqkv"][q + kv:]
     yield p + "self_attn.o_proj.weight", views["wo"]
+    if cfg.qk_norm:
+        yield p + "self_attn.q_norm.weight", views["qn"]
+        yield p + "self_attn.k_norm.weight", views["kn"]
     if cfg.o_proj_bias:
         yield p + "self_attn.o_proj.bias", views["bo"]
     f = cfg.intermediate_size

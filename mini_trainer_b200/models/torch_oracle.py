@@ -42,6 +42,9 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
         q = F.linear(n, sd[p + "self_attn.q_proj.weight"], sd.get(p + "self_attn.q_proj.bias")).view(T, hq, d)
         k = F.linear(n, sd[p + "self_attn.k_proj.weight"], sd.get(p + "self_attn.k_proj.bias")).view(T, hkv, d)
         v = F.linear(n, sd[p + "self_attn.v_proj.weight"], sd.get(p + "self_attn.v_proj.bias")).view(T, hkv, d)
+        if cfg.qk_norm:
+            q = _rms(q, sd[p + "self_attn.q_norm.weight"], cfg.rms_norm_eps)
+            k = _rms(k, sd[p + "self_attn.k_norm.weight"], cfg.rms_norm_eps)
         q, k = _rope(q, position_ids, inv_freq), _rope(k, position_ids, inv_freq)
         outs = []
         for a, b in zip(starts[:-1], starts[1:]):

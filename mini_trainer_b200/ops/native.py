@@ -49,6 +49,9 @@ class _Sig:
     mtb200_rmsnorm_bwd_blocks = [I]
     mtb200_rmsnorm_bwd = [P, P, P, P, P, P, P, P, I, I, P]
     mtb200_rope = [P, P, P, I, L, I, I, I, P]
+    mtb200_head_rmsnorm_fwd = [P, P, P, P, F, I, L, I, I, I, P]
+    mtb200_head_rmsnorm_bwd_blocks = [I, I]
+    mtb200_head_rmsnorm_bwd = [P, P, P, P, P, P, P, P, I, L, L, I, I, I, P]
     mtb200_swiglu_fwd = [P, P, L, I, P]
     mtb200_swiglu_bwd = [P, P, P, L, I, P]
     mtb200_swiglu_bwd_act = [P, P, P, L, I, P]
@@ -236,6 +239,27 @@ class NativeOps:
         self._call("mtb200_rope", qkv.data_ptr(), position_ids.data_ptr(), inv_freq.data_ptr(), qkv.shape[0],
                    qkv.stride(0), n_q_heads + n_kv_heads, head_dim, int(inverse), self._st())
         return qkv
+
+    # -- per-head RMSNorm of q and k (Qwen3) -----------------------------------------------
+    def head_rmsnorm_(self, qkv, wq, wk, eps, n_q_heads, n_kv_heads, head_dim):
+        """Normalises every q head (weight ``wq``) and k head (``wk``) of ``qkv`` over ``head_dim``, in place;
+        returns the reciprocal RMS per (token, head), ``[T * (n_q + n_kv)]`` fp32."""
+        T, nh = qkv.shape[0], n_q_heads + n_kv_heads
+        rstd = torch.empty(T * nh, dtype=torch.float32, device=self.device)
+        self._call("mtb200_head_rmsnorm_fwd", qkv.data_ptr(), wq.data_ptr(), wk.data_ptr(), rstd.data_ptr(), eps, T,
+                   qkv.stride(0), n_q_heads, nh, head_dim, self._st())
+        return rstd
+
+    def head_rmsnorm_bwd_(self, dqkv, pre, rstd, wq, wk, dwq_out, dwk_out, n_q_heads, n_kv_heads, head_dim):
+        """In place on the q and k columns of ``dqkv``: gradient of the normalised heads in, gradient of the projection
+        output out. ``pre``: the q|k heads before the norm, ``[T, (n_q + n_kv) * head_dim]``."""
+        T, nh = dqkv.shape[0], n_q_heads + n_kv_heads
+        blocks = self.lib.mtb200_head_rmsnorm_bwd_blocks(T, nh)
+        part = self._buf("head_rmsnorm_dw", blocks * 2 * head_dim, torch.float32)
+        self._call("mtb200_head_rmsnorm_bwd", dqkv.data_ptr(), pre.data_ptr(), rstd.data_ptr(), wq.data_ptr(), wk.data_ptr(),
+                   part.data_ptr(), dwq_out.data_ptr(), dwk_out.data_ptr(), T, dqkv.stride(0), pre.stride(0), n_q_heads, nh,
+                   head_dim, self._st(), n=2)
+        return dqkv
 
     # -- attention --------------------------------------------------------------------
     def _attn_plan(self, cu_host, block, most_work_last_block: bool):

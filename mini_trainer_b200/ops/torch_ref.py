@@ -88,6 +88,30 @@ class TorchOps:
         qkv[:, : nh * head_dim] = torch.cat([o1, o2], -1).reshape(T, nh * head_dim).to(qkv.dtype)
         return qkv
 
+    # -- per-head RMSNorm of q and k (Qwen3 q_norm / k_norm) --------------------------------
+    def head_rmsnorm_(self, qkv, wq, wk, eps, n_q_heads, n_kv_heads, head_dim):
+        T, nh = qkv.shape[0], n_q_heads + n_kv_heads
+        v = qkv[:, : nh * head_dim].reshape(T, nh, head_dim).float()
+        rstd = torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+        w = torch.cat([wq.expand(n_q_heads, head_dim), wk.expand(n_kv_heads, head_dim)], 0)
+        y = (v * rstd).to(qkv.dtype) * w
+        qkv[:, : nh * head_dim] = y.reshape(T, nh * head_dim).to(qkv.dtype)
+        return rstd.reshape(-1)
+
+    def head_rmsnorm_bwd_(self, dqkv, pre, rstd, wq, wk, dwq_out, dwk_out, n_q_heads, n_kv_heads, head_dim):
+        T, nh = dqkv.shape[0], n_q_heads + n_kv_heads
+        dy = dqkv[:, : nh * head_dim].reshape(T, nh, head_dim).float()
+        r = rstd.reshape(T, nh, 1)
+        xhat = pre.reshape(T, nh, head_dim).float() * r
+        c = dy * xhat.to(dqkv.dtype).float()
+        dwq_out.copy_(c[:, :n_q_heads].sum((0, 1)).to(dwq_out.dtype))
+        dwk_out.copy_(c[:, n_q_heads:].sum((0, 1)).to(dwk_out.dtype))
+        w = torch.cat([wq.expand(n_q_heads, head_dim), wk.expand(n_kv_heads, head_dim)], 0).float()
+        g = dy * w
+        dx = r * (g - xhat * (g * xhat).mean(-1, keepdim=True))
+        dqkv[:, : nh * head_dim] = dx.reshape(T, nh * head_dim).to(dqkv.dtype)
+        return dqkv
+
     # -- attention --------------------------------------------------------------------
     @staticmethod
     def _split(qkv, hq, hkv, d):

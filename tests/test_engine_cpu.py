@@ -74,6 +74,14 @@ def test_grads_tied_bias():
     check_grads(True, True)
 
 
+def test_grads_head_norm():
+    """Qwen3's per-head q/k norm against the autograd oracle, in all three checkpoint levels."""
+    import dataclasses
+    cfg = dataclasses.replace(small_cfg(False, False), model_type="qwen3", architectures=["Qwen3ForCausalLM"], qk_norm=True)
+    check_grads(False, False, cfg)
+    _check_levels(cfg)
+
+
 def test_grads_mixture_of_experts():
     """Router (softmax, top-k, renormalisation) and routed SwiGLU experts against a dense autograd restatement."""
     check_grads(False, False, moe_cfg())

@@ -91,6 +91,43 @@ def test_native_engine_with_projection_biases_matches_fp32_reference(residual_mu
             assert gb[n].norm() > 0 and err < 5e-2, (a.layout.name, n, err.item())
 
 
+def test_native_engine_with_head_norm_matches_fp32_reference():
+    """Qwen3's per-head q/k norm through the engine on the kernels (recompute and kept-activation schedules)."""
+    import dataclasses
+    from mini_trainer_b200.ops.native import NativeOps
+    cfg = dataclasses.replace(get_preset("smoke-llama"), model_type="qwen3", architectures=["Qwen3ForCausalLM"], qk_norm=True)
+    mb = make_mb([300, 17, 129, 1, 640], cfg.vocab_size)
+    batch = D.make_packed_batch(mb, "cuda:0")
+    scale = 1.0 / mb["batch_num_loss_counted_tokens"]
+    for budget in (0, 10 ** 12):
+        ops = NativeOps("cuda:0")
+        eng = ShardedEngine(cfg, "cuda:0", ops, optim=OptimConfig(), activation_budget_bytes=budget)
+        eng.init_random(seed=14, std=0.05)
+        gen = torch.Generator(device="cuda:0").manual_seed(5)
+        for grp in eng.blocks:     # random initialisation leaves norm weights at one
+            views = grp.layout.views(grp.master)
+            for n in ("qn", "kn"):
+                views[n].uniform_(0.5, 1.5, generator=gen)
+            grp.shard.copy_(grp.master)
+        ref = ShardedEngine(cfg, "cuda:0", get_ops("cuda:0", "torch"), param_dtype=torch.float32, optim=OptimConfig(),
+                            activation_budget_bytes=budget)
+        for a, b in zip(eng.groups, ref.groups):
+            b.master.copy_(a.shard.float()); b.shard.copy_(b.master)
+        l1 = eng.forward_backward(batch, scale)
+        l2 = ref.forward_backward(batch, scale)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert abs(l1.sum().item() - l2.sum().item()) < 2e-2 * abs(l2.sum().item())
+        for a, b in zip(eng.groups, ref.groups):
+            err = (a.gacc - b.gacc).norm() / (b.gacc.norm() + 1e-12)
+            assert err < 5e-2, (a.layout.name, err.item())
+        for a, b in zip(eng.blocks, ref.blocks):
+            ga, gb = a.layout.views(a.gacc), b.layout.views(b.gacc)
+            for n in ("qn", "kn"):
+                err = (ga[n] - gb[n]).norm() / (gb[n].norm() + 1e-12)
+                assert gb[n].norm() > 0 and err < 5e-2, (a.layout.name, n, err.item())
+
+
 def test_native_engine_mixture_of_experts_matches_fp32_reference(monkeypatch):
     """A small Mixtral on the kernels: expert slabs of uneven height through the tcgen05 GEMM (row slices of shared
     buffers), row gathers by the embedding kernel, router in torch. The fp32 reference replays the experts the native run

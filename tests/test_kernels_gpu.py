@@ -155,6 +155,38 @@ def test_rope_forward_and_inverse(ops, D, hq, hkv):
     assert rel_err(qkv, orig) < 8e-3
 
 
+@pytest.mark.parametrize("D,hq,hkv,T", [(128, 4, 1, 257), (64, 4, 2, 33), (256, 2, 1, 100), (128, 28, 4, 1031)])
+def test_head_rmsnorm_forward_and_backward(ops, D, hq, hkv, T):
+    """Per-head RMSNorm of the q and k heads inside the fused qkv rows (Qwen3), in place, v untouched; backward in place
+    on the gradient with the pre-norm heads as input, weight gradients without atomics (run twice: bitwise equal)."""
+    nh = hq + hkv
+    qkv = bf(T, (hq + 2 * hkv) * D)
+    wq, wk = (1.0 + 0.3 * torch.randn(D, device="cuda")).bfloat16(), (1.0 + 0.3 * torch.randn(D, device="cuda")).bfloat16()
+    orig = qkv.clone()
+    pre = qkv[:, : nh * D].clone()
+    ref = qkv.float().clone()
+    rstd_ref = REF.head_rmsnorm_(ref, wq.float(), wk.float(), 1e-6, hq, hkv, D)
+    rstd = ops.head_rmsnorm_(qkv, wq, wk, 1e-6, hq, hkv, D)
+    assert rel_err(qkv, ref) < 4e-3 and max_err(qkv, ref) < 5e-2 and rel_err(rstd, rstd_ref) < 1e-5
+    assert torch.equal(qkv[:, nh * D:], orig[:, nh * D:])
+    dy = bf(T, (hq + 2 * hkv) * D)
+    dref = dy.float().clone()
+    gq_ref, gk_ref = torch.empty(D, device="cuda"), torch.empty(D, device="cuda")
+    REF.head_rmsnorm_bwd_(dref, pre.float(), rstd_ref, wq.float(), wk.float(), gq_ref, gk_ref, hq, hkv, D)
+    outs = []
+    for _ in range(2):
+        d = dy.clone()
+        gq, gk = torch.empty(D, dtype=torch.bfloat16, device="cuda"), torch.empty(D, dtype=torch.bfloat16, device="cuda")
+        ops.head_rmsnorm_bwd_(d, pre, rstd, wq, wk, gq, gk, hq, hkv, D)
+        outs.append((d, gq, gk))
+    d, gq, gk = outs[0]
+    assert rel_err(d, dref) < 5e-3 and max_err(d, dref) < 5e-2
+    assert torch.equal(d[:, nh * D:], dy[:, nh * D:])
+    assert rel_err(gq, gq_ref) < 6e-3 and rel_err(gk, gk_ref) < 6e-3
+    assert all(torch.equal(a, b) for a, b in zip(outs[0], outs[1]))
+    ops.check_status()
+
+
 def test_swiglu(ops):
     T, F = 123, 688
     gu, da = bf(T, 2 * F), bf(T, F)

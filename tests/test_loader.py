@@ -29,7 +29,8 @@ def _hf_dir(tmp_path, kind, **over):
                                                     "attention_multiplier": 0.0625, "logits_scaling": 8.0}),
            "mixtral": (transformers.MixtralConfig, {"sliding_window": None, "num_local_experts": 4,
                                                     "num_experts_per_tok": 2}),
-           "phi3": (transformers.Phi3Config, {"pad_token_id": 0, "eos_token_id": 2})}[kind]
+           "phi3": (transformers.Phi3Config, {"pad_token_id": 0, "eos_token_id": 2}),
+           "qwen3": (transformers.Qwen3Config, {"head_dim": 32})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
     cfg = cls[0](**kw)
@@ -49,7 +50,7 @@ def _our_logits(eng, ids):
     return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb)
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -105,6 +106,41 @@ def test_mixture_of_experts_gradients_and_export_against_transformers(tmp_path):
         assert torch.allclose(got[f"wgu{e}"], want[L + "experts.gate_up_proj"][e], atol=1e-5, rtol=1e-3)
         assert torch.allclose(got[f"wd{e}"], want[L + "experts.down_proj"][e], atol=1e-5, rtol=1e-3)
     assert torch.allclose(got["wo"], want["model.layers.0.self_attn.o_proj.weight"], atol=1e-5, rtol=1e-3)
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    with torch.no_grad():
+        ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
+
+
+def test_qwen3_head_norm_gradients_and_export_against_transformers(tmp_path):
+    """Qwen3's RMSNorm over head_dim on every q and k head (before the rotary embedding): gradients of both norm weights
+    and of the q/k projections against autograd through transformers; the export loads there."""
+    path, hf = _hf_dir(tmp_path, "qwen3")
+    with torch.no_grad():   # transformers initialises norm weights to one
+        for n, p_ in hf.named_parameters():
+            if "q_norm" in n or "k_norm" in n:
+                p_.uniform_(0.5, 1.5)
+    hf.save_pretrained(path)
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.qk_norm and eng.cfg.head_dim == 32
+    ids = torch.randint(0, COMMON["vocab_size"], (22,))
+    labels = ids.clone()
+    labels[:3] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 22, "num_loss_counted_tokens": 19}], 19)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 19, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 19 - float(out.loss)) < 1e-4
+    got = eng.blocks[0].layout.views(eng.blocks[0].gacc)
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    L, q, kv = "model.layers.0.self_attn.", eng.cfg.q_size, eng.cfg.kv_size
+    for a, b in [(got["qn"], want[L + "q_norm.weight"]), (got["kn"], want[L + "k_norm.weight"]),
+                 (got["wqkv"][:q], want[L + "q_proj.weight"]), (got["wqkv"][q: q + kv], want[L + "k_proj.weight"]),
+                 (got["wqkv"][q + kv:], want[L + "v_proj.weight"])]:
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-3), float((a - b).abs().max())
     from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
     out_dir = str(tmp_path / "export")
     save_hf_checkpoint(eng, out_dir)
