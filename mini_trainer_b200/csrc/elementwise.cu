@@ -350,7 +350,31 @@ __global__ void __launch_bounds__(EW_THREADS) head_rmsnorm_bwd_kernel(__nv_bfloa
   }
 }
 
-// ------------------------------------------------------------------------------ SwiGLU
+// ------------------------------------------------------------------------------ gated MLP activations
+// act(gate) * up over gu = [gate | up]. ACT 0: SiLU (SwiGLU: Llama, Qwen, Mistral, Granite, Mixtral, Phi-3);
+// ACT 1: tanh-approximated GELU (GeGLU: Gemma's gelu_pytorch_tanh).
+template <int ACT>
+__device__ __forceinline__ float glu_act(float g) {
+  if constexpr (ACT == 0) {
+    return __fdividef(g, 1.f + __expf(-g));
+  } else {
+    const float th = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+    return 0.5f * g * (1.f + th);
+  }
+}
+// d act(g) / d g
+template <int ACT>
+__device__ __forceinline__ float glu_act_grad(float g) {
+  if constexpr (ACT == 0) {
+    const float sig = __fdividef(1.f, 1.f + __expf(-g));
+    return sig * (1.f + g * (1.f - sig));
+  } else {
+    const float th = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+    return 0.5f * (1.f + th) + 0.5f * g * (1.f - th * th) * 0.7978845608028654f * (1.f + 0.134145f * g * g);
+  }
+}
+
+template <int ACT>
 __global__ void __launch_bounds__(EW_THREADS) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
                                                                long long T, int F) {
   // grid = (tokens, column blocks): no 64-bit division per thread
@@ -360,14 +384,14 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_fwd_kernel(const __nv_bfloa
   bf16x8 g, u; g.load(gu + t * 2 * F + c); u.load(gu + t * 2 * F + F + c);
   float fg[8], fu[8], o[8]; g.to_float(fg); u.to_float(fu);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) o[i] = __fdividef(fg[i], 1.f + __expf(-fg[i])) * fu[i];
+  for (int i = 0; i < 8; ++i) o[i] = glu_act<ACT>(fg[i]) * fu[i];
   g.from_float(o); g.store(act + t * F + c);
 }
 
-// WITH_ACT: the forward output silu(gate) * up is also produced, written over dact (each thread reads its
+// WITH_ACT: the forward output act(gate) * up is also produced, written over dact (each thread reads its
 // dact vector before it stores there), for a backward that did not keep it: one pass over gate/up
 // instead of a forward kernel plus this one.
-template <bool WITH_ACT>
+template <bool WITH_ACT, int ACT>
 __global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(__nv_bfloat16* dact, const __nv_bfloat16* __restrict__ gu,
                                                                __nv_bfloat16* __restrict__ dgu, long long T, int F) {
   // grid = (tokens, column blocks): no 64-bit division per thread
@@ -378,18 +402,46 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(__nv_bfloat16* d
   float fg[8], fu[8], fd[8], og[8], ou[8]; g.to_float(fg); u.to_float(fu); d.to_float(fd);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float sig = __fdividef(1.f, 1.f + __expf(-fg[i]));
-    og[i] = fd[i] * fu[i] * sig * (1.f + fg[i] * (1.f - sig));
-    ou[i] = fd[i] * fg[i] * sig;
+    if constexpr (ACT == 0) {
+      const float sig = __fdividef(1.f, 1.f + __expf(-fg[i]));
+      og[i] = fd[i] * fu[i] * sig * (1.f + fg[i] * (1.f - sig));
+      ou[i] = fd[i] * fg[i] * sig;
+    } else {
+      og[i] = fd[i] * fu[i] * glu_act_grad<ACT>(fg[i]);
+      ou[i] = fd[i] * glu_act<ACT>(fg[i]);
+    }
   }
   if (WITH_ACT) {
     float o[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = __fdividef(fg[i], 1.f + __expf(-fg[i])) * fu[i];   // same expression as the forward kernel
+    for (int i = 0; i < 8; ++i) o[i] = glu_act<ACT>(fg[i]) * fu[i];   // same expression as the forward kernel
     d.from_float(o); d.store(dact + t * F + c);
   }
   g.from_float(og); u.from_float(ou);
   g.store(dgu + t * 2 * F + c); u.store(dgu + t * 2 * F + F + c);
+}
+
+// Plain (not gated) activation over n elements, forward and backward: Starcoder2's MLP is c_proj(gelu(c_fc(x))).
+template <int ACT>
+__global__ void __launch_bounds__(EW_THREADS) act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n) {
+  const long long i0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i0 >= n) return;
+  bf16x8 v; v.load(x + i0);
+  float f[8]; v.to_float(f);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = glu_act<ACT>(f[i]);
+  v.from_float(f); v.store(y + i0);
+}
+template <int ACT>
+__global__ void __launch_bounds__(EW_THREADS) act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                            __nv_bfloat16* __restrict__ dx, long long n) {
+  const long long i0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i0 >= n) return;
+  bf16x8 v, d; v.load(x + i0); d.load(dy + i0);
+  float f[8], g[8]; v.to_float(f); d.to_float(g);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) g[i] *= glu_act_grad<ACT>(f[i]);
+  d.from_float(g); d.store(dx + i0);
 }
 
 // ------------------------------------------------------------------------------ embedding
@@ -717,14 +769,14 @@ int mtb200_head_rmsnorm_bwd(void* dqkv, const void* pre, const float* rstd, cons
 int mtb200_swiglu_fwd(const void* gu, void* act, long long T, int F, cudaStream_t st) {
   if (T <= 0) return 0;
   if (F % 8) return -10;
-  swiglu_fwd_kernel<<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((const bf16*)gu, (bf16*)act, T, F);
+  swiglu_fwd_kernel<0><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((const bf16*)gu, (bf16*)act, T, F);
   return launch_ok();
 }
 
 int mtb200_swiglu_bwd(const void* dact, const void* gu, void* dgu, long long T, int F, cudaStream_t st) {
   if (T <= 0) return 0;
   if (F % 8) return -10;
-  swiglu_bwd_kernel<false><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((bf16*)const_cast<void*>(dact), (const bf16*)gu, (bf16*)dgu, T, F);
+  swiglu_bwd_kernel<false, 0><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((bf16*)const_cast<void*>(dact), (const bf16*)gu, (bf16*)dgu, T, F);
   return launch_ok();
 }
 
@@ -732,7 +784,41 @@ int mtb200_swiglu_bwd(const void* dact, const void* gu, void* dgu, long long T, 
 int mtb200_swiglu_bwd_act(void* dact_inout, const void* gu, void* dgu, long long T, int F, cudaStream_t st) {
   if (T <= 0) return 0;
   if (F % 8) return -10;
-  swiglu_bwd_kernel<true><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((bf16*)dact_inout, (const bf16*)gu, (bf16*)dgu, T, F);
+  swiglu_bwd_kernel<true, 0><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((bf16*)dact_inout, (const bf16*)gu, (bf16*)dgu, T, F);
+  return launch_ok();
+}
+
+// GeGLU (tanh-approximated GELU on the gate): same three entry points as SwiGLU.
+int mtb200_geglu_fwd(const void* gu, void* act, long long T, int F, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (F % 8) return -10;
+  swiglu_fwd_kernel<1><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((const bf16*)gu, (bf16*)act, T, F);
+  return launch_ok();
+}
+int mtb200_geglu_bwd(const void* dact, const void* gu, void* dgu, long long T, int F, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (F % 8) return -10;
+  swiglu_bwd_kernel<false, 1><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((bf16*)const_cast<void*>(dact), (const bf16*)gu, (bf16*)dgu, T, F);
+  return launch_ok();
+}
+int mtb200_geglu_bwd_act(void* dact_inout, const void* gu, void* dgu, long long T, int F, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (F % 8) return -10;
+  swiglu_bwd_kernel<true, 1><<<dim3(static_cast<unsigned>(T), cdiv(F / 8, EW_THREADS)), EW_THREADS, 0, st>>>((bf16*)dact_inout, (const bf16*)gu, (bf16*)dgu, T, F);
+  return launch_ok();
+}
+
+// y = gelu_tanh(x) over n elements; dx = dy * gelu_tanh'(x) (dx may be dy).
+int mtb200_gelu_fwd(const void* x, void* y, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 8) return -10;
+  act_fwd_kernel<1><<<static_cast<unsigned>(cdiv(n / 8, EW_THREADS)), EW_THREADS, 0, st>>>((const bf16*)x, (bf16*)y, n);
+  return launch_ok();
+}
+int mtb200_gelu_bwd(const void* dy, const void* x, void* dx, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 8) return -10;
+  act_bwd_kernel<1><<<static_cast<unsigned>(cdiv(n / 8, EW_THREADS)), EW_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, n);
   return launch_ok();
 }
 

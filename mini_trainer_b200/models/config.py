@@ -1,13 +1,13 @@
 """Decoder configuration, read from / written to Hugging Face ``config.json``.
 
-Covers the Llama / Qwen2 / Qwen3 / Mistral / Phi-3 / Granite / Mixtral family the reference trains through
+Covers the Llama / Qwen2 / Qwen3 / Mistral / Phi-3 / Gemma / Granite / Mixtral family the reference trains through
 ``AutoModelForCausalLM`` (setup_model_for_training.py:86-130): pre-norm decoder blocks with
 RMSNorm, rotary GQA attention (optional biases, optional per-head q/k norm), a SwiGLU MLP or Mixtral's routed SwiGLU experts,
 tied or untied LM head, plus Granite's four scalars (embedding, residual, attention and logits
 multipliers).
 
 The reference's allow-list (setup_model_for_training.py:111-123) also names GPTDolomite,
-Starcoder2 and Gemma and merely warns for anything else, because whatever
+and Starcoder2 and merely warns for anything else, because whatever
 ``AutoModelForCausalLM`` loads brings its own forward. Here the forward and backward are
 hand-written for ONE block structure, so an architecture whose math differs (LayerNorm or
 GeGLU blocks) is refused by ``validate_supported`` instead of being trained with the wrong
@@ -56,6 +56,10 @@ class ModelConfig:
     hidden_act: str = "silu"
     # Mixtral (modeling_mixtral.py): the MLP of every block is num_local_experts SwiGLU experts, of which a
     # softmax router picks num_experts_per_tok per token; 0 experts = dense MLP
+    # Gemma (modeling_gemma.py): the norms multiply by (1 + weight); embeddings are scaled by sqrt(hidden_size),
+    # a constant that is first rounded to the embedding's dtype (55.4256 becomes 55.5 in bf16)
+    norm_weight_offset: float = 0.0
+    embedding_multiplier_in_param_dtype: bool = False
     # Qwen3 (modeling_qwen3.py): RMSNorm over head_dim on every q and k head before the rotary embedding
     qk_norm: bool = False
     num_local_experts: int = 0
@@ -85,6 +89,19 @@ class ModelConfig:
             return None
         on = self.use_sliding_window if self.use_sliding_window is not None else self.model_type in ("mistral", "mixtral", "phi3")
         return int(self.sliding_window) if on else None
+
+    def embed_scale(self, dtype) -> float:
+        """Factor applied to the embedding output (1.0 for most models) as the model itself computes it in ``dtype``."""
+        m = float(self.embedding_multiplier)
+        if self.embedding_multiplier_in_param_dtype and m != 1.0:
+            import torch
+            m = float(torch.tensor(m, dtype=dtype))
+        return m
+
+    @property
+    def mlp_act(self) -> str:
+        """Activation of the gated MLP: ``silu`` (SwiGLU) or ``gelu_tanh`` (GeGLU)."""
+        return "gelu_tanh" if self.hidden_act == "gelu_pytorch_tanh" else "silu"
 
     @property
     def fused_hf_names(self) -> bool:
@@ -117,8 +134,9 @@ class ModelConfig:
         prf = (self.extra.get("rope_parameters") or {}).get("partial_rotary_factor", self.extra.get("partial_rotary_factor", 1.0))
         if prf not in (None, 1.0):
             problems.append(f"partial_rotary_factor={prf} (the rotary kernel turns the whole head)")
-        if self.hidden_act not in ("silu", "swish"):
-            problems.append(f"hidden_act={self.hidden_act!r} (only the SwiGLU MLP is implemented)")
+        if self.hidden_act not in ("silu", "swish", "gelu_pytorch_tanh"):
+            problems.append(f"hidden_act={self.hidden_act!r} (the gated MLP is implemented with SiLU and with the "
+                            "tanh-approximated GELU)")
         if problems:
             raise ValueError("this model cannot be trained faithfully: " + "; ".join(problems))
 
@@ -232,6 +250,13 @@ class ModelConfig:
             kw.setdefault("attention_bias", True)  # Qwen2 always has q/k/v biases
         if kw.get("model_type") == "qwen3":
             kw["qk_norm"] = True
+        if kw.get("model_type") == "gemma":
+            kw.update(norm_weight_offset=1.0, embedding_multiplier_in_param_dtype=True,
+                      embedding_multiplier=float(kw["hidden_size"]) ** 0.5)
+            kw.setdefault("hidden_act", "gelu_pytorch_tanh")
+            kw.setdefault("tie_word_embeddings", True)
+            if d.get("hidden_activation"):   # older Gemma configs carry the real activation under this key
+                kw["hidden_act"] = d["hidden_activation"]
         for k in ("bos_token_id", "eos_token_id", "pad_token_id"):
             if isinstance(kw.get(k), list):
                 d[k + "_list"] = kw[k]
@@ -246,7 +271,8 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         d = asdict(self)
         extra = d.pop("extra")
-        d.pop("qk_norm")   # implied by the model type, not a key of any Hugging Face config
+        for k in ("qk_norm", "norm_weight_offset", "embedding_multiplier_in_param_dtype"):
+            d.pop(k)   # implied by the model type, not keys of any Hugging Face config
         out = dict(extra)
         for k in ("bos_token_id", "eos_token_id", "pad_token_id"):
             lst = out.pop(k + "_list", None)
@@ -278,7 +304,7 @@ class ModelConfig:
 
 
 SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
-                           "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM")
+                           "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM", "GemmaForCausalLM")
 
 
 def _llama(**kw):

@@ -79,7 +79,7 @@ def moe_forward(ops, cfg, p: dict, n2: torch.Tensor, h1: torch.Tensor, need_out:
     st = MoeState(probs, topi, w, order, tok, bounds, gu, None)
     if not need_out:
         return None, st
-    act = ops.swiglu(gu)
+    act = ops.swiglu(gu, cfg.mlp_act)
     yr = torch.empty(T * k, H, dtype=n2.dtype, device=n2.device)
     for e, a, b in _slabs(bounds):
         if b > a:
@@ -101,7 +101,7 @@ def moe_backward(ops, cfg, p: dict, g: dict, st: MoeState, n2: torch.Tensor, dou
     gr = ops.embedding(dout, tok)                     # output gradient of every routed row, before its weight
     if rm != 1.0:
         gr = gr * rm
-    act = st.act if st.act is not None else ops.swiglu(st.gu)
+    act = st.act if st.act is not None else ops.swiglu(st.gu, cfg.mlp_act)
     # y_row = wd act, weighted by w: d(weight) = dout . y_row = (wd^T dout) . act, so the unweighted
     # data gradient of the down projection gives both the weight's and (scaled) the activation's gradient
     du = torch.empty_like(act)
@@ -118,7 +118,7 @@ def moe_backward(ops, cfg, p: dict, g: dict, st: MoeState, n2: torch.Tensor, dou
             g[f"wd{e}"].zero_()                       # an expert no token chose: its gradient is zero, not stale
     dact = (du.float() * wr[:, None]).to(du.dtype)
     del du, actw, act, gr
-    dgu = ops.swiglu_bwd(dact, st.gu)
+    dgu = ops.swiglu_bwd(dact, st.gu, cfg.mlp_act)
     del dact
     xs = ops.embedding(n2, tok)
     dxs = torch.empty(T * k, H, dtype=n2.dtype, device=n2.device)

@@ -13,9 +13,9 @@ import torch.nn.functional as F
 from .config import ModelConfig
 
 
-def _rms(x, w, eps):
+def _rms(x, w, eps, offset=0.0):
     xf = x.float()
-    return ((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)) * w
+    return ((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)) * (w + offset)
 
 
 def _rope(x, pos, inv_freq):
@@ -33,12 +33,13 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
     T = input_ids.shape[0]
     inv_freq = cfg.rope_inv_freq().to(input_ids.device)
     starts = (position_ids == 0).nonzero().flatten().tolist() + [T]
-    x = sd["model.embed_tokens.weight"][input_ids] * cfg.embedding_multiplier
+    x = sd["model.embed_tokens.weight"][input_ids] * cfg.embed_scale(sd["model.embed_tokens.weight"].dtype)
     rm = cfg.residual_multiplier
     hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    mlp_act = F.silu if cfg.mlp_act == "silu" else (lambda t: F.gelu(t, approximate="tanh"))
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        n = _rms(x, sd[p + "input_layernorm.weight"], cfg.rms_norm_eps)
+        n = _rms(x, sd[p + "input_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
         q = F.linear(n, sd[p + "self_attn.q_proj.weight"], sd.get(p + "self_attn.q_proj.bias")).view(T, hq, d)
         k = F.linear(n, sd[p + "self_attn.k_proj.weight"], sd.get(p + "self_attn.k_proj.bias")).view(T, hkv, d)
         v = F.linear(n, sd[p + "self_attn.v_proj.weight"], sd.get(p + "self_attn.v_proj.bias")).view(T, hkv, d)
@@ -53,7 +54,7 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
                                                scale=cfg.attention_scale)
             outs.append(o[0].transpose(0, 1).reshape(b - a, hq * d))
         x = x + rm * F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
-        n = _rms(x, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
+        n = _rms(x, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
         if cfg.is_moe:   # dense restatement: every expert on every token, masked by the routing weights
             m = p + "block_sparse_moe."
             probs = F.softmax(F.linear(n, sd[m + "gate.weight"]).float(), -1)
@@ -65,10 +66,10 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
                 y = y + gatew[:, e: e + 1].to(n.dtype) * F.linear(a, sd[m + f"experts.{e}.w2.weight"])
             x = x + rm * y
             continue
-        act = F.silu(F.linear(n, sd[p + "mlp.gate_proj.weight"], sd.get(p + "mlp.gate_proj.bias"))) \
+        act = mlp_act(F.linear(n, sd[p + "mlp.gate_proj.weight"], sd.get(p + "mlp.gate_proj.bias"))) \
             * F.linear(n, sd[p + "mlp.up_proj.weight"], sd.get(p + "mlp.up_proj.bias"))
         x = x + rm * F.linear(act, sd[p + "mlp.down_proj.weight"], sd.get(p + "mlp.down_proj.bias"))
-    n = _rms(x, sd["model.norm.weight"], cfg.rms_norm_eps)
+    n = _rms(x, sd["model.norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
     lm = sd["model.embed_tokens.weight"] if cfg.tie_word_embeddings else sd["lm_head.weight"]
     logits = F.linear(n, lm).float() / cfg.logits_scaling
     if return_logits:

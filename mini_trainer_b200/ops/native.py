@@ -55,6 +55,11 @@ class _Sig:
     mtb200_swiglu_fwd = [P, P, L, I, P]
     mtb200_swiglu_bwd = [P, P, P, L, I, P]
     mtb200_swiglu_bwd_act = [P, P, P, L, I, P]
+    mtb200_geglu_fwd = [P, P, L, I, P]
+    mtb200_geglu_bwd = [P, P, P, L, I, P]
+    mtb200_geglu_bwd_act = [P, P, P, L, I, P]
+    mtb200_gelu_fwd = [P, P, L, P]
+    mtb200_gelu_bwd = [P, P, P, L, P]
     mtb200_embedding_fwd = [P, P, P, I, I, I, P, P]
     mtb200_embedding_bwd = [P, P, P, P, I, I, I, P, P]
     mtb200_ce_fwd_bwd = [P, L, I, P, P, P, L, I, I, F, L, P]
@@ -65,6 +70,10 @@ class _Sig:
     mtb200_adamw = [P, P, P, I, P, P, L, F, F, F, F, F, I, P, P]
     mtb200_attn_fwd = [P, L, P, L, P, P, I, I, I, I, I, I, F, P, P]
     mtb200_attn_bwd = [P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, F, P, P]
+
+
+_GLU = {"silu": "mtb200_swiglu", "gelu_tanh": "mtb200_geglu"}
+NATIVE_HEAD_DIMS = (64, 128)   # head dimensions of the hand-written attention kernels
 
 
 def _ptr(t):
@@ -287,7 +296,7 @@ class NativeOps:
     def attention(self, qkv, cu_seqlens, cu_host, max_seqlen, hq, hkv, d, scale=None):
         T = qkv.shape[0]
         scale = d ** -0.5 if scale is None else float(scale)
-        if self.attention_impl == "flash_attn":
+        if self.attention_impl == "flash_attn" or d not in NATIVE_HEAD_DIMS:
             return self._fa_fwd(qkv, cu_seqlens, max_seqlen, hq, hkv, d, scale)
         out = torch.empty(T, hq * d, dtype=qkv.dtype, device=self.device)
         lse = torch.empty(hq, T, dtype=torch.float32, device=self.device)
@@ -299,7 +308,7 @@ class NativeOps:
     def attention_bwd(self, dout, qkv, out, lse, cu_seqlens, cu_host, max_seqlen, hq, hkv, d, scale=None):
         T = qkv.shape[0]
         scale = d ** -0.5 if scale is None else float(scale)
-        if self.attention_impl == "flash_attn":
+        if self.attention_impl == "flash_attn" or d not in NATIVE_HEAD_DIMS:
             return self._fa_bwd(dout, qkv, out, lse, cu_seqlens, max_seqlen, hq, hkv, d, scale)
         dqkv = torch.empty_like(qkv)
         plan = self._attn_plan(cu_host, 128, False)
@@ -311,7 +320,9 @@ class NativeOps:
                    self.status.data_ptr(), self._st(), n=3)
         return dqkv
 
-    # library baseline (flash-attn 2), selectable for A/B comparisons only
+    # Library attention (flash-attn 2): selectable for A/B comparisons, and the path of head dimensions the
+    # tcgen05 kernels are not built for (Gemma's 256: S plus a 256-column output accumulator would fill tensor memory
+    # with no second S buffer to overlap softmax and MMA, so it needs a kernel of its own design).
     def _fa_fwd(self, qkv, cu, max_seqlen, hq, hkv, d, scale):
         from flash_attn.flash_attn_interface import _flash_attn_varlen_forward
         T = qkv.shape[0]
@@ -340,24 +351,36 @@ class NativeOps:
         return dqkv
 
     # -- swiglu -----------------------------------------------------------------------
-    def swiglu(self, gate_up):
+    def swiglu(self, gate_up, act="silu"):
+        """``act(gate) * up`` over ``[gate | up]``: SiLU (SwiGLU) or the tanh-approximated GELU (GeGLU)."""
         T, F2 = gate_up.shape
-        act = torch.empty(T, F2 // 2, dtype=gate_up.dtype, device=self.device)
-        self._call("mtb200_swiglu_fwd", gate_up.data_ptr(), act.data_ptr(), T, F2 // 2, self._st())
-        return act
+        out = torch.empty(T, F2 // 2, dtype=gate_up.dtype, device=self.device)
+        self._call(_GLU[act] + "_fwd", gate_up.data_ptr(), out.data_ptr(), T, F2 // 2, self._st())
+        return out
 
-    def swiglu_bwd(self, dact, gate_up):
+    def swiglu_bwd(self, dact, gate_up, act="silu"):
         T, F2 = gate_up.shape
         dgu = torch.empty_like(gate_up)
-        self._call("mtb200_swiglu_bwd", dact.data_ptr(), gate_up.data_ptr(), dgu.data_ptr(), T, F2 // 2, self._st())
+        self._call(_GLU[act] + "_bwd", dact.data_ptr(), gate_up.data_ptr(), dgu.data_ptr(), T, F2 // 2, self._st())
         return dgu
 
-    def swiglu_bwd_act(self, dact, gate_up):
+    def swiglu_bwd_act(self, dact, gate_up, act="silu"):
         """Returns ``(dgate_up, act)``; ``act`` (the forward output) is written over ``dact``."""
         T, F2 = gate_up.shape
         dgu = torch.empty_like(gate_up)
-        self._call("mtb200_swiglu_bwd_act", dact.data_ptr(), gate_up.data_ptr(), dgu.data_ptr(), T, F2 // 2, self._st())
+        self._call(_GLU[act] + "_bwd_act", dact.data_ptr(), gate_up.data_ptr(), dgu.data_ptr(), T, F2 // 2, self._st())
         return dgu, dact
+
+    # -- plain GELU (tanh approximation) of a not gated MLP ----------------------------------
+    def gelu(self, x):
+        y = torch.empty_like(x)
+        self._call("mtb200_gelu_fwd", x.data_ptr(), y.data_ptr(), x.numel(), self._st())
+        return y
+
+    def gelu_bwd(self, dy, x):
+        dx = torch.empty_like(x)
+        self._call("mtb200_gelu_bwd", dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(), self._st())
+        return dx
 
     # -- fused linear + cross-entropy ---------------------------------------------------
     def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100, logit_scale=1.0):

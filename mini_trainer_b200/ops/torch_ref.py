@@ -176,23 +176,40 @@ class TorchOps:
         return dqkv
 
     # -- swiglu -----------------------------------------------------------------------
-    def swiglu(self, gate_up):
+    def swiglu(self, gate_up, act="silu"):
         f = gate_up.shape[1] // 2
         g, u = gate_up[:, :f].float(), gate_up[:, f:].float()
-        return (F.silu(g) * u).to(gate_up.dtype)
+        a = F.silu(g) if act == "silu" else F.gelu(g, approximate="tanh")
+        return (a * u).to(gate_up.dtype)
 
-    def swiglu_bwd(self, dact, gate_up):
+    def swiglu_bwd(self, dact, gate_up, act="silu"):
         f = gate_up.shape[1] // 2
         g, u = gate_up[:, :f].float(), gate_up[:, f:].float()
         da = dact.float()
-        sig = torch.sigmoid(g)
-        dg = da * u * sig * (1 + g * (1 - sig))
-        du = da * g * sig
+        if act == "silu":
+            sig = torch.sigmoid(g)
+            dg = da * u * sig * (1 + g * (1 - sig))
+            du = da * g * sig
+        else:
+            dg = da * u * self._gelu_tanh_grad(g)
+            du = da * F.gelu(g, approximate="tanh")
         return torch.cat([dg, du], 1).to(gate_up.dtype)
 
-    def swiglu_bwd_act(self, dact, gate_up):
+    def swiglu_bwd_act(self, dact, gate_up, act="silu"):
         """``(dgate_up, act)``: the gradient and the forward output in one call."""
-        return self.swiglu_bwd(dact, gate_up), self.swiglu(gate_up)
+        return self.swiglu_bwd(dact, gate_up, act), self.swiglu(gate_up, act)
+
+    @staticmethod
+    def _gelu_tanh_grad(x):
+        k = 0.7978845608028654
+        th = torch.tanh(k * (x + 0.044715 * x ** 3))
+        return 0.5 * (1 + th) + 0.5 * x * (1 - th * th) * k * (1 + 3 * 0.044715 * x * x)
+
+    def gelu(self, x):
+        return F.gelu(x.float(), approximate="tanh").to(x.dtype)
+
+    def gelu_bwd(self, dy, x):
+        return (dy.float() * self._gelu_tanh_grad(x.float())).to(x.dtype)
 
     # -- fused linear + cross-entropy ---------------------------------------------------
     def linear_ce(self, x, w, targets, grad_scale, dw_out, accumulate_dw=False, ignore_index=-100, logit_scale=1.0):

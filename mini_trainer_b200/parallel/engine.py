@@ -208,7 +208,7 @@ class ShardedEngine:
             for name, spec in grp.layout.specs.items():
                 v = full[spec.offset: spec.offset + spec.numel]
                 if len(spec.shape) == 1:
-                    v.fill_(0.0 if name.startswith("b") else 1.0)
+                    v.fill_(0.0 if name.startswith("b") else 1.0 - self.cfg.norm_weight_offset)   # biases 0, norms identity
                 else:
                     v.normal_(0.0, std, generator=gen)
             self._set_group_from_full(grp, full.to(self.device))
@@ -574,7 +574,7 @@ class ShardedEngine:
             eg_full = self._root_grad_buffer("embed")
             emb_g = self.embed.layout.views(eg_full)
         if cfg.embedding_multiplier != 1.0:
-            dx.mul_(cfg.embedding_multiplier)
+            dx.mul_(cfg.embed_scale(dx.dtype))
         ops.embedding_bwd(emb_g["embed"], batch.input_ids, dx)
         self._root_free["embed"] = self._reduce(self.embed, eg_full, last=last)
         return loss
@@ -662,8 +662,8 @@ class ShardedEngine:
         nL = len(self.blocks)
         emb_views, emb_full, _ = self._gather_group(self.embed)
         x = ops.embedding(emb_views["embed"], batch.input_ids)
-        if cfg.embedding_multiplier != 1.0:   # Granite
-            x.mul_(cfg.embedding_multiplier)
+        if cfg.embedding_multiplier != 1.0:   # Granite, Gemma
+            x.mul_(cfg.embed_scale(x.dtype))
         if not cfg.tie_word_embeddings:
             emb_views = None
         del emb_full

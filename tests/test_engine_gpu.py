@@ -91,6 +91,40 @@ def test_native_engine_with_projection_biases_matches_fp32_reference(residual_mu
             assert gb[n].norm() > 0 and err < 5e-2, (a.layout.name, n, err.item())
 
 
+def test_native_engine_gemma_matches_fp32_reference():
+    """A Gemma-shaped model: GeGLU kernel, norms that multiply by (1 + weight), scaled tied embeddings, and head_dim 256,
+    for which attention runs through the library kernel (the tcgen05 attention kernels are built for 64 and 128)."""
+    from mini_trainer_b200.models.config import ModelConfig
+    from mini_trainer_b200.ops.native import NativeOps
+    cfg = ModelConfig.from_hf_dict(dict(model_type="gemma", architectures=["GemmaForCausalLM"], vocab_size=4096, hidden_size=512,
+                                        intermediate_size=1536, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
+                                        head_dim=256, rope_theta=1e4, rms_norm_eps=1e-6))
+    cfg.validate_supported()
+    ops = NativeOps("cuda:0")
+    eng = ShardedEngine(cfg, "cuda:0", ops, optim=OptimConfig())
+    eng.init_random(seed=15, std=0.05)
+    gen = torch.Generator(device="cuda:0").manual_seed(6)
+    for grp in eng.blocks:     # random initialisation leaves Gemma's norm weights at zero
+        views = grp.layout.views(grp.master)
+        for n in ("ln1", "ln2"):
+            views[n].normal_(0.0, 0.3, generator=gen)
+        grp.shard.copy_(grp.master)
+    ref = ShardedEngine(cfg, "cuda:0", get_ops("cuda:0", "torch"), param_dtype=torch.float32, optim=OptimConfig())
+    for a, b in zip(eng.groups, ref.groups):
+        b.master.copy_(a.shard.float()); b.shard.copy_(b.master)
+    mb = make_mb([300, 17, 129, 1, 640], cfg.vocab_size)
+    batch = D.make_packed_batch(mb, "cuda:0")
+    scale = 1.0 / mb["batch_num_loss_counted_tokens"]
+    l1 = eng.forward_backward(batch, scale)
+    l2 = ref.forward_backward(batch, scale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert abs(l1.sum().item() - l2.sum().item()) < 2e-2 * abs(l2.sum().item())
+    for a, b in zip(eng.groups, ref.groups):
+        err = (a.gacc - b.gacc).norm() / (b.gacc.norm() + 1e-12)
+        assert err < 5e-2, (a.layout.name, err.item())
+
+
 def test_native_engine_with_head_norm_matches_fp32_reference():
     """Qwen3's per-head q/k norm through the engine on the kernels (recompute and kept-activation schedules)."""
     import dataclasses

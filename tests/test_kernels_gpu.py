@@ -155,6 +155,23 @@ def test_rope_forward_and_inverse(ops, D, hq, hkv):
     assert rel_err(qkv, orig) < 8e-3
 
 
+def test_geglu_and_gelu(ops):
+    """The tanh-approximated GELU as the gate of a gated MLP (Gemma) and as a plain activation (Starcoder2)."""
+    T, F = 123, 688
+    gu, da = bf(T, 2 * F), bf(T, F)
+    assert rel_err(ops.swiglu(gu, "gelu_tanh"), REF.swiglu(gu.float(), "gelu_tanh")) < 4e-3
+    assert rel_err(ops.swiglu_bwd(da, gu, "gelu_tanh"), REF.swiglu_bwd(da.float(), gu.float(), "gelu_tanh")) < 5e-3
+    assert max_err(ops.swiglu_bwd(da, gu, "gelu_tanh"), REF.swiglu_bwd(da.float(), gu.float(), "gelu_tanh")) < 5e-2
+    act_ref, dgu_ref = ops.swiglu(gu, "gelu_tanh"), ops.swiglu_bwd(da, gu, "gelu_tanh")
+    buf = da.clone()
+    dgu, act = ops.swiglu_bwd_act(buf, gu, "gelu_tanh")
+    assert act.data_ptr() == buf.data_ptr() and torch.equal(act, act_ref) and torch.equal(dgu, dgu_ref)
+    x, dy = bf(T, F, scale=2.0), bf(T, F)
+    assert rel_err(ops.gelu(x), REF.gelu(x.float())) < 4e-3 and max_err(ops.gelu(x), REF.gelu(x.float())) < 5e-2
+    assert rel_err(ops.gelu_bwd(dy, x), REF.gelu_bwd(dy.float(), x.float())) < 5e-3
+    ops.check_status()
+
+
 @pytest.mark.parametrize("D,hq,hkv,T", [(128, 4, 1, 257), (64, 4, 2, 33), (256, 2, 1, 100), (128, 28, 4, 1031)])
 def test_head_rmsnorm_forward_and_backward(ops, D, hq, hkv, T):
     """Per-head RMSNorm of the q and k heads inside the fused qkv rows (Qwen3), in place, v untouched; backward in place

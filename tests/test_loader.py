@@ -30,7 +30,8 @@ def _hf_dir(tmp_path, kind, **over):
            "mixtral": (transformers.MixtralConfig, {"sliding_window": None, "num_local_experts": 4,
                                                     "num_experts_per_tok": 2}),
            "phi3": (transformers.Phi3Config, {"pad_token_id": 0, "eos_token_id": 2}),
-           "qwen3": (transformers.Qwen3Config, {"head_dim": 32})}[kind]
+           "qwen3": (transformers.Qwen3Config, {"head_dim": 32}),
+           "gemma": (transformers.GemmaConfig, {"head_dim": 32})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
     cfg = cls[0](**kw)
@@ -50,7 +51,7 @@ def _our_logits(eng, ids):
     return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb)
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -148,6 +149,47 @@ def test_qwen3_head_norm_gradients_and_export_against_transformers(tmp_path):
     with torch.no_grad():
         ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
     assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
+
+
+def test_gemma_gradients_and_export_against_transformers(tmp_path):
+    """Gemma: norms that multiply by (1 + weight), GeGLU with the tanh GELU, embeddings scaled by sqrt(hidden), tied head.
+    Norm-weight, MLP and embedding gradients against autograd through transformers; the export holds ``weight`` itself."""
+    path, hf = _hf_dir(tmp_path, "gemma")
+    with torch.no_grad():   # transformers initialises Gemma's norm weights to zero
+        for n, p_ in hf.named_parameters():
+            if "norm" in n:
+                p_.normal_(0.0, 0.3)
+    hf.save_pretrained(path)
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.mlp_act == "gelu_tanh" and eng.cfg.norm_weight_offset == 1.0 and eng.cfg.tie_word_embeddings
+    assert abs(eng.cfg.embedding_multiplier - 8.0) < 1e-6
+    ids = torch.randint(0, COMMON["vocab_size"], (24,))
+    labels = ids.clone()
+    labels[:5] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 24, "num_loss_counted_tokens": 19}], 19)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 19, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 19 - float(out.loss)) < 1e-4
+    got = eng.blocks[1].layout.views(eng.blocks[1].gacc)
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    L, f = "model.layers.1.", eng.cfg.intermediate_size
+    for a, b in [(got["ln1"], want[L + "input_layernorm.weight"]), (got["ln2"], want[L + "post_attention_layernorm.weight"]),
+                 (got["wgu"][:f], want[L + "mlp.gate_proj.weight"]), (got["wgu"][f:], want[L + "mlp.up_proj.weight"]),
+                 (got["wd"], want[L + "mlp.down_proj.weight"]),
+                 (eng.head.layout.views(eng.head.gacc)["norm"], want["model.norm.weight"]),
+                 (eng.embed.layout.views(eng.embed.gacc)["embed"], want["model.embed_tokens.weight"])]:
+        assert torch.allclose(a, b, atol=2e-5, rtol=1e-3), float((a - b).abs().max())
+    from mini_trainer_b200.ckpt import safetensors_io as st
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
+    saved = st.load_file(os.path.join(out_dir, "model.safetensors"))
+    assert torch.allclose(saved["model.norm.weight"].float(), hf.model.norm.weight.detach(), atol=5e-3)
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    with torch.no_grad():
+        ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.08, rtol=0.05)   # the export is bf16
 
 
 def test_phi3_export_keeps_the_fused_tensor_names(tmp_path):
@@ -287,9 +329,9 @@ def test_sliding_window_model_is_trained_up_to_the_window_and_refused_beyond(tmp
 def test_unknown_architecture_is_refused(tmp_path):
     path, _ = _hf_dir(tmp_path, "llama")
     cfg = json.load(open(os.path.join(path, "config.json")))
-    cfg["architectures"], cfg["model_type"] = ["GemmaForCausalLM"], "gemma"
+    cfg["architectures"], cfg["model_type"] = ["FalconForCausalLM"], "falcon"
     json.dump(cfg, open(os.path.join(path, "config.json"), "w"))
-    with pytest.raises(ValueError, match="GemmaForCausalLM"):
+    with pytest.raises(ValueError, match="FalconForCausalLM"):
         setup_model(path, device="cpu")
 
 
