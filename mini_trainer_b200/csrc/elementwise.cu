@@ -192,6 +192,122 @@ __global__ void reduce_rows_pair_kernel(const float* __restrict__ part, __nv_bfl
   if (c < D) out_a[c] = __float2bfloat16(s); else out_b[c - D] = __float2bfloat16(s);
 }
 
+// ------------------------------------------------------------------------------ LayerNorm (Starcoder2)
+// y = ((x - mean) * rstd) * w + b, statistics in fp32 over the row held in registers (two-pass: the mean first, then
+// the centred sum of squares), mean and rstd saved. One 256-thread block per row, VPT 8-wide vectors per thread.
+template <int VPT>
+__global__ void __launch_bounds__(EW_THREADS) layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                                  const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                                  float* __restrict__ mean_out, float* __restrict__ rstd_out, float eps, int H) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  float f[VPT][8];
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = (threadIdx.x + k * EW_THREADS) * 8;
+    if (c < H) {
+      bf16x8 v; v.load(xr + c); v.to_float(f[k]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += f[k][i];
+    }
+  }
+  const float mean = block_sum(s, red) / H;
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = (threadIdx.x + k * EW_THREADS) * 8;
+    if (c < H) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { f[k][i] -= mean; ss += f[k][i] * f[k][i]; }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / H + eps);
+  if (threadIdx.x == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = (threadIdx.x + k * EW_THREADS) * 8;
+    if (c < H) {
+      bf16x8 wv, bv; wv.load(w + c); bv.load(b + c);
+      float fw[8], fb[8], o[8]; wv.to_float(fw); bv.to_float(fb);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = f[k][i] * rstd * fw[i] + fb[i];
+      bf16x8 ov; ov.from_float(o); ov.store(y + row * H + c);
+    }
+  }
+}
+
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) (+ add_to), g = dy * w, xhat = (x - mean) * rstd.
+// Partials per block in fp32: dwp[block, 0, :] += dy * xhat, dwp[block, 1, :] += dy (the bias gradient); summed over
+// blocks by reduce_rows_pair_kernel. Persistent blocks loop over rows.
+template <int VPT>
+__global__ void __launch_bounds__(EW_THREADS) layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                  const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                                                  const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ add_to,
+                                                                  __nv_bfloat16* __restrict__ dx, float* __restrict__ dwp, int T, int H) {
+  __shared__ float red[32];
+  float dwacc[VPT][8], dbacc[VPT][8], wreg[VPT][8];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int c = (threadIdx.x + v * EW_THREADS) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dwacc[v][i] = 0.f; dbacc[v][i] = 0.f; wreg[v][i] = 0.f; }
+    if (c < H) { bf16x8 wv; wv.load(w + c); wv.to_float(wreg[v]); }
+  }
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float g[VPT][8], xh[VPT][8];
+    float d1 = 0.f, d2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = (threadIdx.x + v * EW_THREADS) * 8;
+      if (c < H) {
+        bf16x8 a, b; a.load(dy + row * H + c); b.load(x + row * H + c);
+        float fa[8], fb[8]; a.to_float(fa); b.to_float(fb);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[v][i] = (fb[i] - mean) * rstd;
+          g[v][i] = fa[i] * wreg[v][i];
+          d1 += g[v][i];
+          d2 += g[v][i] * xh[v][i];
+          dwacc[v][i] += fa[i] * xh[v][i];
+          dbacc[v][i] += fa[i];
+        }
+      }
+    }
+    d1 = block_sum(d1, red) / H;
+    d2 = block_sum(d2, red) / H;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int c = (threadIdx.x + v * EW_THREADS) * 8;
+      if (c < H) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (g[v][i] - d1 - xh[v][i] * d2);
+        if (add_to != nullptr) {
+          bf16x8 r; r.load(add_to + row * H + c);
+          float fr[8]; r.to_float(fr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += fr[i];
+        }
+        bf16x8 ov; ov.from_float(o); ov.store(dx + row * H + c);
+      }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int c = (threadIdx.x + v * EW_THREADS) * 8;
+    if (c < H) {
+      float* dst = dwp + static_cast<long long>(blockIdx.x) * 2 * H + c;
+      *reinterpret_cast<float4*>(dst) = make_float4(dwacc[v][0], dwacc[v][1], dwacc[v][2], dwacc[v][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[v][4], dwacc[v][5], dwacc[v][6], dwacc[v][7]);
+      *reinterpret_cast<float4*>(dst + H) = make_float4(dbacc[v][0], dbacc[v][1], dbacc[v][2], dbacc[v][3]);
+      *reinterpret_cast<float4*>(dst + H + 4) = make_float4(dbacc[v][4], dbacc[v][5], dbacc[v][6], dbacc[v][7]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------ RoPE
 // In place on the first n_heads (q then k) heads of each row of qkv[T, ld]. Rotate-half
 // convention: (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin), angle = fp32(pos) * inv_freq[i]
@@ -717,6 +833,32 @@ int mtb200_rmsnorm_bwd(const void* dy, const void* x, const float* rstd, const v
   }
 #undef RB
   reduce_rows_kernel<<<cdiv(H, 256), 256, 0, st>>>(dw_partial, (bf16*)dw_out, blocks, H);
+  return launch_ok();
+}
+
+// LayerNorm with bias over rows of H <= 8192 elements; mean / rstd: [T] fp32 each.
+int mtb200_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, float eps, int T, int H,
+                         cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8 || H > 4 * 8 * EW_THREADS) return -10;
+  const int vpt = cdiv(H, 8 * EW_THREADS);
+#define LF(V) layernorm_fwd_kernel<V><<<T, EW_THREADS, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)b, (bf16*)y, mean, rstd, eps, H)
+  if (vpt <= 1) LF(1); else if (vpt == 2) LF(2); else if (vpt == 3) LF(3); else LF(4);
+#undef LF
+  return launch_ok();
+}
+
+// dw_partial: [mtb200_rmsnorm_bwd_blocks(T), 2, H] fp32 scratch; dw_out / db_out: [H] bf16 each.
+int mtb200_layernorm_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* w, const void* add_to, void* dx,
+                         float* dw_partial, void* dw_out, void* db_out, int T, int H, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8 || H > 4 * 8 * EW_THREADS) return -10;
+  const int blocks = mtb200_rmsnorm_bwd_blocks(T);
+  const int vpt = cdiv(H, 8 * EW_THREADS);
+#define LB(V) layernorm_bwd_kernel<V><<<blocks, EW_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, (const bf16*)w, (const bf16*)add_to, (bf16*)dx, dw_partial, T, H)
+  if (vpt <= 1) LB(1); else if (vpt == 2) LB(2); else if (vpt == 3) LB(3); else LB(4);
+#undef LB
+  reduce_rows_pair_kernel<<<cdiv(2 * H, 256), 256, 0, st>>>(dw_partial, (bf16*)dw_out, (bf16*)db_out, blocks, H);
   return launch_ok();
 }
 

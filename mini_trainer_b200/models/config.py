@@ -1,13 +1,13 @@
 """Decoder configuration, read from / written to Hugging Face ``config.json``.
 
-Covers the Llama / Qwen2 / Qwen3 / Mistral / Phi-3 / Gemma / Granite / Mixtral family the reference trains through
+Covers the Llama / Qwen2 / Qwen3 / Mistral / Phi-3 / Gemma / Granite / Mixtral / Starcoder2 families the reference trains through
 ``AutoModelForCausalLM`` (setup_model_for_training.py:86-130): pre-norm decoder blocks with
 RMSNorm, rotary GQA attention (optional biases, optional per-head q/k norm), a SwiGLU MLP or Mixtral's routed SwiGLU experts,
 tied or untied LM head, plus Granite's four scalars (embedding, residual, attention and logits
 multipliers).
 
-The reference's allow-list (setup_model_for_training.py:111-123) also names GPTDolomite,
-and Starcoder2 and merely warns for anything else, because whatever
+The reference's allow-list (setup_model_for_training.py:111-123) also names GPTDolomite
+and merely warns for anything else, because whatever
 ``AutoModelForCausalLM`` loads brings its own forward. Here the forward and backward are
 hand-written for ONE block structure, so an architecture whose math differs (LayerNorm or
 GeGLU blocks) is refused by ``validate_supported`` instead of being trained with the wrong
@@ -56,6 +56,10 @@ class ModelConfig:
     hidden_act: str = "silu"
     # Mixtral (modeling_mixtral.py): the MLP of every block is num_local_experts SwiGLU experts, of which a
     # softmax router picks num_experts_per_tok per token; 0 experts = dense MLP
+    # Starcoder2 (modeling_starcoder2.py): LayerNorm with bias instead of RMSNorm, and an MLP without a gate,
+    # c_proj(gelu(c_fc(x))); its config spells the epsilon ``norm_epsilon`` and has one ``use_bias`` for every projection
+    norm_type: str = "rmsnorm"
+    mlp_gated: bool = True
     # Gemma (modeling_gemma.py): the norms multiply by (1 + weight); embeddings are scaled by sqrt(hidden_size),
     # a constant that is first rounded to the embedding's dtype (55.4256 becomes 55.5 in bf16)
     norm_weight_offset: float = 0.0
@@ -87,7 +91,8 @@ class ModelConfig:
         kernels here are full causal: the engine accepts such a model and refuses a minibatch that holds a longer sample."""
         if self.sliding_window is None or self.sliding_window >= self.max_position_embeddings:
             return None
-        on = self.use_sliding_window if self.use_sliding_window is not None else self.model_type in ("mistral", "mixtral", "phi3")
+        on = self.use_sliding_window if self.use_sliding_window is not None else \
+            self.model_type in ("mistral", "mixtral", "phi3", "starcoder2")
         return int(self.sliding_window) if on else None
 
     def embed_scale(self, dtype) -> float:
@@ -134,6 +139,8 @@ class ModelConfig:
         prf = (self.extra.get("rope_parameters") or {}).get("partial_rotary_factor", self.extra.get("partial_rotary_factor", 1.0))
         if prf not in (None, 1.0):
             problems.append(f"partial_rotary_factor={prf} (the rotary kernel turns the whole head)")
+        if not self.mlp_gated and (self.hidden_act != "gelu_pytorch_tanh" or self.is_moe):
+            problems.append(f"an MLP without a gate is implemented with the tanh-approximated GELU only (hidden_act={self.hidden_act!r})")
         if self.hidden_act not in ("silu", "swish", "gelu_pytorch_tanh"):
             problems.append(f"hidden_act={self.hidden_act!r} (the gated MLP is implemented with SiLU and with the "
                             "tanh-approximated GELU)")
@@ -160,28 +167,35 @@ class ModelConfig:
         return self.attention_bias and self.model_type != "qwen2"
 
     @property
+    def mlp_mats(self) -> int:
+        """Matrices of one MLP: gate, up, down, or up and down only."""
+        return 3 if self.mlp_gated else 2
+
+    @property
     def mlp_rows_factor(self) -> int:
         """Rows that go through an MLP per token: the number of experts a token is sent to (1 for a dense MLP)."""
         return self.num_experts_per_tok if self.is_moe else 1
 
     def block_param_count(self) -> int:
         h, f = self.hidden_size, self.intermediate_size
-        n = 2 * h + self.qkv_size * h + self.q_size * h + 3 * h * f * max(1, self.num_local_experts)
+        n = 2 * h + self.qkv_size * h + self.q_size * h + self.mlp_mats * h * f * max(1, self.num_local_experts)
+        n += 2 * h if self.norm_type == "layernorm" else 0
         n += self.num_local_experts * h   # router
         n += self.qkv_size if self.attention_bias else 0
         n += 2 * self.head_dim if self.qk_norm else 0
         n += h if self.o_proj_bias else 0
-        return n + (2 * f + h if self.mlp_bias else 0)
+        return n + ((self.mlp_mats - 1) * f + h if self.mlp_bias else 0)
 
     def param_count(self) -> int:
         emb = self.vocab_size * self.hidden_size
-        return self.num_hidden_layers * self.block_param_count() + self.hidden_size + emb * (1 if self.tie_word_embeddings else 2)
+        final_norm = self.hidden_size * (2 if self.norm_type == "layernorm" else 1)
+        return self.num_hidden_layers * self.block_param_count() + final_norm + emb * (1 if self.tie_word_embeddings else 2)
 
     def flops_per_token(self, avg_context: float = 0.0, recompute: bool = True) -> float:
         """Training FLOPs per token: 6 x matmul params (+2 x with full recompute) + attention. With experts
         only the ``num_experts_per_tok`` chosen ones (and the router) count."""
         h, f = self.hidden_size, self.intermediate_size
-        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + 3 * h * f * self.mlp_rows_factor
+        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + self.mlp_mats * h * f * self.mlp_rows_factor
                                        + self.num_local_experts * h)
         head = self.vocab_size * h
         k = 8 if recompute else 6
@@ -197,7 +211,7 @@ class ModelConfig:
         the two kernel families on a power-capped B200.
         """
         h, f = self.hidden_size, self.intermediate_size
-        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + 3 * h * f * self.mlp_rows_factor)
+        mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + self.mlp_mats * h * f * self.mlp_rows_factor)
         gemm = (8 if recompute else 6) * mm + 6 * self.vocab_size * h
         attn = 3.5 * 2 * self.q_size * self.num_hidden_layers
         return (gemm / gemm_rate) / (attn / attn_rate)
@@ -250,6 +264,12 @@ class ModelConfig:
             kw.setdefault("attention_bias", True)  # Qwen2 always has q/k/v biases
         if kw.get("model_type") == "qwen3":
             kw["qk_norm"] = True
+        if kw.get("model_type") == "starcoder2":
+            use_bias = bool(d.pop("use_bias", True))
+            kw.update(norm_type="layernorm", mlp_gated=False, attention_bias=use_bias, mlp_bias=use_bias,
+                      rms_norm_eps=float(d.pop("norm_epsilon", 1e-5)))
+            kw.setdefault("hidden_act", "gelu_pytorch_tanh")
+            kw.setdefault("tie_word_embeddings", True)
         if kw.get("model_type") == "gemma":
             kw.update(norm_weight_offset=1.0, embedding_multiplier_in_param_dtype=True,
                       embedding_multiplier=float(kw["hidden_size"]) ** 0.5)
@@ -271,8 +291,11 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         d = asdict(self)
         extra = d.pop("extra")
-        for k in ("qk_norm", "norm_weight_offset", "embedding_multiplier_in_param_dtype"):
+        for k in ("qk_norm", "norm_weight_offset", "embedding_multiplier_in_param_dtype", "norm_type", "mlp_gated"):
             d.pop(k)   # implied by the model type, not keys of any Hugging Face config
+        if self.model_type == "starcoder2":   # back to its own spelling
+            d["norm_epsilon"], d["use_bias"] = d.pop("rms_norm_eps"), d.pop("attention_bias")
+            d["mlp_bias"] = False
         out = dict(extra)
         for k in ("bos_token_id", "eos_token_id", "pad_token_id"):
             lst = out.pop(k + "_list", None)
@@ -304,7 +327,8 @@ class ModelConfig:
 
 
 SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
-                           "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM", "GemmaForCausalLM")
+                           "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM", "GemmaForCausalLM",
+                           "Starcoder2ForCausalLM")
 
 
 def _llama(**kw):

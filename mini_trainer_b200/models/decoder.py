@@ -86,6 +86,19 @@ def _nw(cfg: ModelConfig, w: torch.Tensor) -> torch.Tensor:
     return w if cfg.norm_weight_offset == 0.0 else (w.float() + cfg.norm_weight_offset).to(w.dtype)
 
 
+def _norm(ops, cfg: ModelConfig, x: torch.Tensor, p: dict, w: str, b: str):
+    """The model's normalisation of ``x`` with the weight (and bias) named ``w`` (``b``) in ``p``: ``(y, stats)``."""
+    if cfg.norm_type == "layernorm":
+        return ops.layernorm(x, p[w], p[b], cfg.rms_norm_eps)
+    return ops.rmsnorm(x, _nw(cfg, p[w]), cfg.rms_norm_eps)
+
+
+def _norm_bwd(ops, cfg: ModelConfig, dy, x, stats, p: dict, g: dict, w: str, b: str, add_to=None):
+    if cfg.norm_type == "layernorm":
+        return ops.layernorm_bwd(dy, x, stats, p[w], g[w], g[b], add_to=add_to)
+    return ops.rmsnorm_bwd(dy, x, stats, _nw(cfg, p[w]), g[w], add_to=add_to)
+
+
 @dataclass
 class BlockActs:
     """Everything the block backward reads, produced by ``block_forward(keep=True)``."""
@@ -120,7 +133,7 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     plan = p.get("_gather")   # all-gather of this block's parameters fused into its first GEMMs
     if plan is not None:
         plan.prefetch_small()
-    n1, rstd1 = ops.rmsnorm(x, _nw(cfg, p["ln1"]), cfg.rms_norm_eps)
+    n1, rstd1 = _norm(ops, cfg, x, p, "ln1", "bln1")
     qkv = ops.linear(n1, p["wqkv"], p.get("bqkv"), gather=None if plan is None else (plan, 0))
     qk_pre = rstd_qk = None
     if cfg.qk_norm:   # the backward of the norm needs its input; the qkv tensor itself goes on normalised and rotated
@@ -139,7 +152,7 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
         attn, lse = ops.attention(qkv, batch.cu_seqlens, batch.cu_seqlens_host, batch.max_seqlen,
                                   cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, scale=cfg.attention_scale)
     h1 = ops.linear(attn, p["wo"], bo, x, alpha=rm)
-    n2, rstd2 = ops.rmsnorm(h1, _nw(cfg, p["ln2"]), cfg.rms_norm_eps)
+    n2, rstd2 = _norm(ops, cfg, h1, p, "ln2", "bln2")
     if cfg.is_moe:
         out, st = moe_forward(ops, cfg, p, n2, h1, need_out, keep_act=keep is True)
         acts = None
@@ -151,7 +164,7 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     gu = ops.linear(n2, p["wgu"], p.get("bgu"), gather=None if plan is None else (plan, 1))
     # a recompute that stops before the down projection does not need the SwiGLU output: backward rebuilds it
     # inside the SwiGLU-gradient kernel
-    act = ops.swiglu(gu, cfg.mlp_act) if need_out else None
+    act = (ops.swiglu(gu, cfg.mlp_act) if cfg.mlp_gated else ops.gelu(gu)) if need_out else None
     out = ops.linear(act, p["wd"], bd, h1, alpha=rm) if need_out else None
     acts = None
     if keep == "compact":   # kept from forward to backward: drop what one elementwise kernel can rebuild
@@ -177,14 +190,18 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     # bandwidth-bound kernels (about 1 ms per block) instead of being held for the whole step
     # MLP
     if cfg.is_moe:
-        n2 = a.n2 if a.n2 is not None else ops.rmsnorm(a.h1, _nw(cfg, p["ln2"]), cfg.rms_norm_eps)[0]
+        n2 = a.n2 if a.n2 is not None else _norm(ops, cfg, a.h1, p, "ln2", "bln2")[0]
         dn2 = moe_backward(ops, cfg, p, g, a.moe, n2, dout)
         del n2
         return _attention_backward(ops, cfg, p, g, a, dn2, dout, batch, inv_freq, notify, rm)
     dact = ops.linear_dgrad(dout, p["wd"], alpha=rm)
     if a.act is not None:
         ops.linear_wgrad(dout, a.act, g["wd"], g.get("bd"), alpha=rm)
-        dgu = ops.swiglu_bwd(dact, a.gu, cfg.mlp_act)
+        dgu = ops.swiglu_bwd(dact, a.gu, cfg.mlp_act) if cfg.mlp_gated else ops.gelu_bwd(dact, a.gu)
+    elif not cfg.mlp_gated:
+        act, dgu = ops.gelu(a.gu), ops.gelu_bwd(dact, a.gu)
+        ops.linear_wgrad(dout, act, g["wd"], g.get("bd"), alpha=rm)
+        del act
     else:   # one pass over gate/up gives its gradient and the SwiGLU output (written over dact)
         dgu, act = ops.swiglu_bwd_act(dact, a.gu, cfg.mlp_act)
         ops.linear_wgrad(dout, act, g["wd"], g.get("bd"), alpha=rm)
@@ -194,7 +211,7 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     notify("wd")
     del dact
     dn2 = ops.linear_dgrad(dgu, p["wgu"])
-    n2 = a.n2 if a.n2 is not None else ops.rmsnorm(a.h1, _nw(cfg, p["ln2"]), cfg.rms_norm_eps)[0]
+    n2 = a.n2 if a.n2 is not None else _norm(ops, cfg, a.h1, p, "ln2", "bln2")[0]
     ops.linear_wgrad(dgu, n2, g["wgu"], g.get("bgu"))
     notify("wgu")
     del dgu, n2
@@ -205,7 +222,7 @@ def _attention_backward(ops, cfg: ModelConfig, p: dict, g: dict, a: BlockActs, d
                         batch: PackedBatch, inv_freq, notify, rm: float) -> torch.Tensor:
     """The part of the block backward in front of the MLP: post-attention norm, o_proj, attention, rotary,
     q/k/v projection, input norm. ``dn2`` is the gradient of the normalised MLP input."""
-    dh1 = ops.rmsnorm_bwd(dn2, a.h1, a.rstd2, _nw(cfg, p["ln2"]), g["ln2"], add_to=dout)
+    dh1 = _norm_bwd(ops, cfg, dn2, a.h1, a.rstd2, p, g, "ln2", "bln2", add_to=dout)
     del dn2
     # attention
     dattn = ops.linear_dgrad(dh1, p["wo"], alpha=rm)
@@ -223,10 +240,10 @@ def _attention_backward(ops, cfg: ModelConfig, p: dict, g: dict, a: BlockActs, d
         ops.head_rmsnorm_bwd_(dqkv, a.qk_pre, a.rstd_qk, p["qn"], p["kn"], g["qn"], g["kn"], cfg.num_attention_heads,
                               cfg.num_key_value_heads, cfg.head_dim)
     dn1 = ops.linear_dgrad(dqkv, p["wqkv"])
-    n1 = a.n1 if a.n1 is not None else ops.rmsnorm(a.x, _nw(cfg, p["ln1"]), cfg.rms_norm_eps)[0]
+    n1 = a.n1 if a.n1 is not None else _norm(ops, cfg, a.x, p, "ln1", "bln1")[0]
     ops.linear_wgrad(dqkv, n1, g["wqkv"], g.get("bqkv"))
     del dqkv, n1
-    dx = ops.rmsnorm_bwd(dn1, a.x, a.rstd1, _nw(cfg, p["ln1"]), g["ln1"], add_to=dh1)
+    dx = _norm_bwd(ops, cfg, dn1, a.x, a.rstd1, p, g, "ln1", "bln1", add_to=dh1)
     return dx
 
 
@@ -240,9 +257,9 @@ def head_forward_backward(ops, cfg: ModelConfig, head_p: dict, head_g: dict, lm_
     rows = batch.loss_rows
     ls = 1.0 / cfg.logits_scaling   # Granite divides the logits by a constant
     if rows is None:
-        n, rstd = ops.rmsnorm(x, _nw(cfg, head_p["norm"]), cfg.rms_norm_eps)
+        n, rstd = _norm(ops, cfg, x, head_p, "norm", "bnorm")
         loss, dn = ops.linear_ce(n, lm_w, batch.targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad, logit_scale=ls)
-        dx = ops.rmsnorm_bwd(dn, x, rstd, _nw(cfg, head_p["norm"]), head_g["norm"])
+        dx = _norm_bwd(ops, cfg, dn, x, rstd, head_p, head_g, "norm", "bnorm")
         return loss, dx
     # Masked positions (prompt tokens, the last token of every sample) have zero loss and zero
     # gradient, so the final norm, the three vocabulary-sized GEMMs and the CE kernel only see the
@@ -253,17 +270,17 @@ def head_forward_backward(ops, cfg: ModelConfig, head_p: dict, head_g: dict, lm_
     if rows.numel() == 0:   # nothing to learn from in this minibatch (e.g. only the idle-rank dummy sample);
         return loss, dx     # the gradient buffers of the head were zeroed by the caller
     xs = ops.embedding(x, rows)   # row gather
-    n, rstd = ops.rmsnorm(xs, _nw(cfg, head_p["norm"]), cfg.rms_norm_eps)
+    n, rstd = _norm(ops, cfg, xs, head_p, "norm", "bnorm")
     loss_s, dn = ops.linear_ce(n, lm_w, batch.loss_targets, grad_scale, lm_g, accumulate_dw=accumulate_lm_grad,
                                logit_scale=ls)
-    dxs = ops.rmsnorm_bwd(dn, xs, rstd, _nw(cfg, head_p["norm"]), head_g["norm"])
+    dxs = _norm_bwd(ops, cfg, dn, xs, rstd, head_p, head_g, "norm", "bnorm")
     loss.index_copy_(0, rows, loss_s)
     dx.index_copy_(0, rows, dxs)
     return loss, dx
 
 
 @torch.no_grad()
-def forward_logits(ops, cfg: ModelConfig, embed_w, blocks: list, norm_w, lm_w, batch: PackedBatch) -> torch.Tensor:
+def forward_logits(ops, cfg: ModelConfig, embed_w, blocks: list, norm_w, lm_w, batch: PackedBatch, norm_b=None) -> torch.Tensor:
     """Plain inference forward returning ``[T, V]`` logits (tests, checkpoint round-trips)."""
     inv_freq = cfg.rope_inv_freq().to(embed_w.device)
     x = ops.embedding(embed_w, batch.input_ids)
@@ -271,5 +288,5 @@ def forward_logits(ops, cfg: ModelConfig, embed_w, blocks: list, norm_w, lm_w, b
         x = x * cfg.embed_scale(x.dtype)
     for p in blocks:
         x, _, _ = block_forward(ops, cfg, p, x, batch, inv_freq)
-    n, _ = ops.rmsnorm(x, _nw(cfg, norm_w), cfg.rms_norm_eps)
+    n, _ = _norm(ops, cfg, x, {"norm": norm_w, "bnorm": norm_b}, "norm", "bnorm")
     return (n.float() @ lm_w.float().t()) / cfg.logits_scaling

@@ -61,7 +61,11 @@ class GroupLayout:
 def block_entries(cfg: ModelConfig) -> list:
     h, f = cfg.hidden_size, cfg.intermediate_size
     # the small tensors needed before the first GEMM come first (see parallel.symmetric.GatherPlan)
+    ln = cfg.norm_type == "layernorm"   # LayerNorm carries a bias next to its weight
+    gu = (2 if cfg.mlp_gated else 1) * f   # rows of the first MLP matrix: gate|up, or c_fc alone
     e = [("ln1", (h,))]
+    if ln:
+        e.append(("bln1", (h,)))
     if cfg.attention_bias:
         e.append(("bqkv", (cfg.qkv_size,)))
     if cfg.qk_norm:
@@ -74,14 +78,16 @@ def block_entries(cfg: ModelConfig) -> list:
     if cfg.o_proj_bias:
         e.append(("bo", (h,)))
     e.append(("ln2", (h,)))
+    if ln:
+        e.append(("bln2", (h,)))
     if cfg.is_moe:   # router, then every expert's fused gate/up and down matrices
         e.append(("router", (cfg.num_local_experts, h)))
         for x in range(cfg.num_local_experts):
             e += [(f"wgu{x}", (2 * f, h)), (f"wd{x}", (h, f))]
         return e
     if cfg.mlp_bias:
-        e.append(("bgu", (2 * f,)))
-    e += [("wgu", (2 * f, h)), ("wd", (h, f))]
+        e.append(("bgu", (gu,)))
+    e += [("wgu", (gu, h)), ("wd", (h, f))]
     if cfg.mlp_bias:
         e.append(("bd", (h,)))
     return e
@@ -93,6 +99,8 @@ def embed_entries(cfg: ModelConfig) -> list:
 
 def head_entries(cfg: ModelConfig) -> list:
     e = [("norm", (cfg.hidden_size,))]
+    if cfg.norm_type == "layernorm":
+        e.append(("bnorm", (cfg.hidden_size,)))
     if not cfg.tie_word_embeddings:
         e.append(("lm_head", (cfg.vocab_size, cfg.hidden_size)))
     return e
@@ -140,6 +148,19 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
         yield p + "input_layernorm.weight", views["ln1"]
         yield p + "post_attention_layernorm.weight", views["ln2"]
         return
+    if not cfg.mlp_gated:   # Starcoder2: c_fc, c_proj and LayerNorm biases
+        yield p + "mlp.c_fc.weight", views["wgu"]
+        if cfg.mlp_bias:
+            yield p + "mlp.c_fc.bias", views["bgu"]
+        yield p + "mlp.c_proj.weight", views["wd"]
+        if cfg.mlp_bias:
+            yield p + "mlp.c_proj.bias", views["bd"]
+        yield p + "input_layernorm.weight", views["ln1"]
+        yield p + "post_attention_layernorm.weight", views["ln2"]
+        if cfg.norm_type == "layernorm":
+            yield p + "input_layernorm.bias", views["bln1"]
+            yield p + "post_attention_layernorm.bias", views["bln2"]
+        return
     yield p + "mlp.gate_proj.weight", views["wgu"][:f]
     if cfg.mlp_bias:
         yield p + "mlp.gate_proj.bias", views["bgu"][:f]
@@ -159,6 +180,8 @@ def hf_tensors_of_embed(cfg: ModelConfig, views: dict) -> Iterator[tuple]:
 
 def hf_tensors_of_head(cfg: ModelConfig, views: dict) -> Iterator[tuple]:
     yield "model.norm.weight", views["norm"]
+    if cfg.norm_type == "layernorm":
+        yield "model.norm.bias", views["bnorm"]
     if not cfg.tie_word_embeddings:
         yield "lm_head.weight", views["lm_head"]
 

@@ -18,6 +18,12 @@ def _rms(x, w, eps, offset=0.0):
     return ((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)) * (w + offset)
 
 
+def _norm(cfg, sd, name, x):
+    if cfg.norm_type == "layernorm":
+        return F.layer_norm(x, (x.shape[-1],), sd[name + ".weight"], sd[name + ".bias"], cfg.rms_norm_eps)
+    return _rms(x, sd[name + ".weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+
+
 def _rope(x, pos, inv_freq):
     # x: [T, heads, D]
     ang = pos.float()[:, None] * inv_freq[None, :]
@@ -39,7 +45,7 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
     mlp_act = F.silu if cfg.mlp_act == "silu" else (lambda t: F.gelu(t, approximate="tanh"))
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        n = _rms(x, sd[p + "input_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+        n = _norm(cfg, sd, p + "input_layernorm", x)
         q = F.linear(n, sd[p + "self_attn.q_proj.weight"], sd.get(p + "self_attn.q_proj.bias")).view(T, hq, d)
         k = F.linear(n, sd[p + "self_attn.k_proj.weight"], sd.get(p + "self_attn.k_proj.bias")).view(T, hkv, d)
         v = F.linear(n, sd[p + "self_attn.v_proj.weight"], sd.get(p + "self_attn.v_proj.bias")).view(T, hkv, d)
@@ -54,7 +60,7 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
                                                scale=cfg.attention_scale)
             outs.append(o[0].transpose(0, 1).reshape(b - a, hq * d))
         x = x + rm * F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
-        n = _rms(x, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+        n = _norm(cfg, sd, p + "post_attention_layernorm", x)
         if cfg.is_moe:   # dense restatement: every expert on every token, masked by the routing weights
             m = p + "block_sparse_moe."
             probs = F.softmax(F.linear(n, sd[m + "gate.weight"]).float(), -1)
@@ -66,10 +72,14 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
                 y = y + gatew[:, e: e + 1].to(n.dtype) * F.linear(a, sd[m + f"experts.{e}.w2.weight"])
             x = x + rm * y
             continue
+        if not cfg.mlp_gated:
+            act = mlp_act(F.linear(n, sd[p + "mlp.c_fc.weight"], sd.get(p + "mlp.c_fc.bias")))
+            x = x + rm * F.linear(act, sd[p + "mlp.c_proj.weight"], sd.get(p + "mlp.c_proj.bias"))
+            continue
         act = mlp_act(F.linear(n, sd[p + "mlp.gate_proj.weight"], sd.get(p + "mlp.gate_proj.bias"))) \
             * F.linear(n, sd[p + "mlp.up_proj.weight"], sd.get(p + "mlp.up_proj.bias"))
         x = x + rm * F.linear(act, sd[p + "mlp.down_proj.weight"], sd.get(p + "mlp.down_proj.bias"))
-    n = _rms(x, sd["model.norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+    n = _norm(cfg, sd, "model.norm", x)
     lm = sd["model.embed_tokens.weight"] if cfg.tie_word_embeddings else sd["lm_head.weight"]
     logits = F.linear(n, lm).float() / cfg.logits_scaling
     if return_logits:

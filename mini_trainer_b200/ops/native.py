@@ -48,6 +48,8 @@ class _Sig:
     mtb200_rmsnorm_fwd = [P, P, P, P, F, I, I, P]
     mtb200_rmsnorm_bwd_blocks = [I]
     mtb200_rmsnorm_bwd = [P, P, P, P, P, P, P, P, I, I, P]
+    mtb200_layernorm_fwd = [P, P, P, P, P, P, F, I, I, P]
+    mtb200_layernorm_bwd = [P, P, P, P, P, P, P, P, P, P, I, I, P]
     mtb200_rope = [P, P, P, I, L, I, I, I, P]
     mtb200_head_rmsnorm_fwd = [P, P, P, P, F, I, L, I, I, I, P]
     mtb200_head_rmsnorm_bwd_blocks = [I, I]
@@ -207,6 +209,26 @@ class NativeOps:
         part = self._buf("rms_part", blocks * H, torch.float32)
         self._call("mtb200_rmsnorm_bwd", dy.data_ptr(), x.data_ptr(), rstd.data_ptr(), w.data_ptr(), _ptr(add_to),
                    dx.data_ptr(), part.data_ptr(), dw_out.data_ptr(), T, H, self._st(), n=2)
+        return dx
+
+    # -- layernorm (Starcoder2) -----------------------------------------------------------
+    def layernorm(self, x, w, b, eps):
+        """``((x - mean) * rstd) * w + b``; returns ``(y, (mean, rstd))`` with fp32 row statistics."""
+        T, H = x.shape
+        y = torch.empty_like(x)
+        mean = torch.empty(T, dtype=torch.float32, device=self.device)
+        rstd = torch.empty(T, dtype=torch.float32, device=self.device)
+        self._call("mtb200_layernorm_fwd", x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr(),
+                   rstd.data_ptr(), eps, T, H, self._st())
+        return y, (mean, rstd)
+
+    def layernorm_bwd(self, dy, x, stats, w, dw_out, db_out, add_to=None):
+        T, H = x.shape
+        dx = torch.empty_like(x)
+        blocks = self.lib.mtb200_rmsnorm_bwd_blocks(T)
+        part = self._buf("layernorm_dw", blocks * 2 * H, torch.float32)
+        self._call("mtb200_layernorm_bwd", dy.data_ptr(), x.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(), w.data_ptr(),
+                   _ptr(add_to), dx.data_ptr(), part.data_ptr(), dw_out.data_ptr(), db_out.data_ptr(), T, H, self._st(), n=2)
         return dx
 
     # -- linear -----------------------------------------------------------------------

@@ -52,6 +52,26 @@ class TorchOps:
             dx = dx + add_to.float()
         return dx.to(x.dtype)
 
+    # -- layernorm (Starcoder2) -----------------------------------------------------------
+    def layernorm(self, x, w, b, eps):
+        xf = x.float()
+        mean = xf.mean(-1, keepdim=True)
+        rstd = torch.rsqrt((xf - mean).pow(2).mean(-1, keepdim=True) + eps)
+        y = ((xf - mean) * rstd * w.float() + b.float()).to(x.dtype)
+        return y, (mean.squeeze(-1), rstd.squeeze(-1))
+
+    def layernorm_bwd(self, dy, x, stats, w, dw_out, db_out, add_to=None):
+        xf, dyf = x.float(), dy.float()
+        mean, r = stats[0].unsqueeze(-1), stats[1].unsqueeze(-1)
+        xhat = (xf - mean) * r
+        dw_out.copy_((dyf * xhat).sum(0).to(dw_out.dtype))
+        db_out.copy_(dyf.sum(0).to(db_out.dtype))
+        g = dyf * w.float()
+        dx = r * (g - g.mean(-1, keepdim=True) - xhat * (g * xhat).mean(-1, keepdim=True))
+        if add_to is not None:
+            dx = dx + add_to.float()
+        return dx.to(x.dtype)
+
     # -- linear -----------------------------------------------------------------------
     def linear(self, x, w, bias=None, residual=None, gather=None, alpha=1.0, out=None):
         y = x @ w.t()

@@ -61,8 +61,10 @@ from ..models.config import ModelConfig
 def osft_targets(cfg: ModelConfig) -> list:
     """(param name in the block layout, first row, last row, HF-style label) of every projection."""
     q, kv, f, h = cfg.q_size, cfg.kv_size, cfg.intermediate_size, cfg.hidden_size
-    return [("wqkv", 0, q, "q_proj"), ("wqkv", q, q + kv, "k_proj"), ("wqkv", q + kv, q + 2 * kv, "v_proj"),
-            ("wo", 0, h, "o_proj"), ("wgu", 0, f, "gate_proj"), ("wgu", f, 2 * f, "up_proj"), ("wd", 0, h, "down_proj")]
+    attn = [("wqkv", 0, q, "q_proj"), ("wqkv", q, q + kv, "k_proj"), ("wqkv", q + kv, q + 2 * kv, "v_proj"), ("wo", 0, h, "o_proj")]
+    if not cfg.mlp_gated:
+        return attn + [("wgu", 0, f, "c_fc"), ("wd", 0, h, "c_proj")]
+    return attn + [("wgu", 0, f, "gate_proj"), ("wgu", f, 2 * f, "up_proj"), ("wd", 0, h, "down_proj")]
 
 
 def svd_thin(w: torch.Tensor, method: str = "auto"):

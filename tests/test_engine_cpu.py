@@ -82,6 +82,19 @@ def test_grads_head_norm():
     _check_levels(cfg)
 
 
+def starcoder2_cfg() -> ModelConfig:
+    return ModelConfig.from_hf_dict(dict(model_type="starcoder2", architectures=["Starcoder2ForCausalLM"], vocab_size=97,
+                                         hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4,
+                                         num_key_value_heads=2, norm_epsilon=1e-5, use_bias=True))
+
+
+def test_grads_layernorm_and_plain_gelu_mlp():
+    """Starcoder2's block (LayerNorm with bias, c_proj(gelu(c_fc(x))), biases everywhere, tied head) against the
+    autograd oracle, in all three checkpoint levels."""
+    check_grads(True, True, starcoder2_cfg())
+    _check_levels(starcoder2_cfg())
+
+
 def test_grads_mixture_of_experts():
     """Router (softmax, top-k, renormalisation) and routed SwiGLU experts against a dense autograd restatement."""
     check_grads(False, False, moe_cfg())

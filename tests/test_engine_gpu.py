@@ -91,6 +91,50 @@ def test_native_engine_with_projection_biases_matches_fp32_reference(residual_mu
             assert gb[n].norm() > 0 and err < 5e-2, (a.layout.name, n, err.item())
 
 
+def test_native_engine_starcoder2_matches_fp32_reference():
+    """A Starcoder2-shaped model on the kernels: LayerNorm forward / backward, plain tanh GELU, a bias on every projection,
+    tied head; recompute and kept-activation schedules."""
+    from mini_trainer_b200.models.config import ModelConfig
+    from mini_trainer_b200.ops.native import NativeOps
+    cfg = ModelConfig.from_hf_dict(dict(model_type="starcoder2", architectures=["Starcoder2ForCausalLM"], vocab_size=4096,
+                                        hidden_size=512, intermediate_size=1536, num_hidden_layers=2, num_attention_heads=4,
+                                        num_key_value_heads=1, norm_epsilon=1e-5, use_bias=True, rope_theta=1e5))
+    cfg.validate_supported()
+    mb = make_mb([300, 17, 129, 1, 640], cfg.vocab_size)
+    batch = D.make_packed_batch(mb, "cuda:0")
+    scale = 1.0 / mb["batch_num_loss_counted_tokens"]
+    for budget in (0, 10 ** 12):
+        ops = NativeOps("cuda:0")
+        eng = ShardedEngine(cfg, "cuda:0", ops, optim=OptimConfig(), activation_budget_bytes=budget)
+        eng.init_random(seed=16, std=0.05)
+        gen = torch.Generator(device="cuda:0").manual_seed(7)
+        for grp in eng.blocks + [eng.head]:     # random initialisation leaves biases at zero and norm weights at one
+            views = grp.layout.views(grp.master)
+            for n, v in views.items():
+                if n.startswith("b"):
+                    v.normal_(0.0, 0.3, generator=gen)
+                elif v.dim() == 1:
+                    v.uniform_(0.5, 1.5, generator=gen)
+            grp.shard.copy_(grp.master)
+        ref = ShardedEngine(cfg, "cuda:0", get_ops("cuda:0", "torch"), param_dtype=torch.float32, optim=OptimConfig(),
+                            activation_budget_bytes=budget)
+        for a, b in zip(eng.groups, ref.groups):
+            b.master.copy_(a.shard.float()); b.shard.copy_(b.master)
+        l1 = eng.forward_backward(batch, scale)
+        l2 = ref.forward_backward(batch, scale)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert abs(l1.sum().item() - l2.sum().item()) < 2e-2 * abs(l2.sum().item())
+        for a, b in zip(eng.groups, ref.groups):
+            err = (a.gacc - b.gacc).norm() / (b.gacc.norm() + 1e-12)
+            assert err < 5e-2, (a.layout.name, err.item())
+        for a, b in zip(eng.blocks, ref.blocks):
+            ga, gb = a.layout.views(a.gacc), b.layout.views(b.gacc)
+            for n in ("ln1", "bln1", "ln2", "bln2", "bgu", "bd"):
+                err = (ga[n] - gb[n]).norm() / (gb[n].norm() + 1e-12)
+                assert gb[n].norm() > 0 and err < 5e-2, (a.layout.name, n, err.item())
+
+
 def test_native_engine_gemma_matches_fp32_reference():
     """A Gemma-shaped model: GeGLU kernel, norms that multiply by (1 + weight), scaled tied embeddings, and head_dim 256,
     for which attention runs through the library kernel (the tcgen05 attention kernels are built for 64 and 128)."""

@@ -155,6 +155,30 @@ def test_rope_forward_and_inverse(ops, D, hq, hkv):
     assert rel_err(qkv, orig) < 8e-3
 
 
+@pytest.mark.parametrize("T,H", [(77, 512), (33, 3072), (9, 6144), (130, 200)])
+def test_layernorm_forward_and_backward(ops, T, H):
+    """LayerNorm with bias (Starcoder2): statistics, output, input gradient (+ residual gradient), weight and bias
+    gradients; partial sums without atomics (run twice: bitwise equal)."""
+    x, dy, res = bf(T, H, scale=2.0) + 0.5, bf(T, H), bf(T, H)
+    w, b = (1.0 + 0.3 * torch.randn(H, device="cuda")).bfloat16(), (0.3 * torch.randn(H, device="cuda")).bfloat16()
+    y, stats = ops.layernorm(x, w, b, 1e-5)
+    y_ref, stats_ref = REF.layernorm(x.float(), w.float(), b.float(), 1e-5)
+    assert rel_err(y, y_ref) < 4e-3 and max_err(y, y_ref) < 5e-2
+    assert rel_err(stats[0], stats_ref[0]) < 1e-4 and rel_err(stats[1], stats_ref[1]) < 1e-4
+    gw_ref, gb_ref = torch.empty(H, device="cuda"), torch.empty(H, device="cuda")
+    dx_ref = REF.layernorm_bwd(dy.float(), x.float(), stats_ref, w.float(), gw_ref, gb_ref, add_to=res.float())
+    outs = []
+    for _ in range(2):
+        gw, gb = torch.empty(H, dtype=torch.bfloat16, device="cuda"), torch.empty(H, dtype=torch.bfloat16, device="cuda")
+        dx = ops.layernorm_bwd(dy, x, stats, w, gw, gb, add_to=res)
+        outs.append((dx, gw, gb))
+    dx, gw, gb = outs[0]
+    assert rel_err(dx, dx_ref) < 5e-3 and max_err(dx, dx_ref) < 5e-2
+    assert rel_err(gw, gw_ref) < 6e-3 and rel_err(gb, gb_ref) < 6e-3
+    assert all(torch.equal(a, c) for a, c in zip(outs[0], outs[1]))
+    ops.check_status()
+
+
 def test_geglu_and_gelu(ops):
     """The tanh-approximated GELU as the gate of a gated MLP (Gemma) and as a plain activation (Starcoder2)."""
     T, F = 123, 688

@@ -31,7 +31,8 @@ def _hf_dir(tmp_path, kind, **over):
                                                     "num_experts_per_tok": 2}),
            "phi3": (transformers.Phi3Config, {"pad_token_id": 0, "eos_token_id": 2}),
            "qwen3": (transformers.Qwen3Config, {"head_dim": 32}),
-           "gemma": (transformers.GemmaConfig, {"head_dim": 32})}[kind]
+           "gemma": (transformers.GemmaConfig, {"head_dim": 32}),
+           "starcoder2": (transformers.Starcoder2Config, {"sliding_window": None, "bos_token_id": 1, "eos_token_id": 2})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
     cfg = cls[0](**kw)
@@ -48,10 +49,10 @@ def _our_logits(eng, ids):
     blocks = [g.layout.views(g.master) for g in eng.blocks]
     emb = eng.embed.layout.views(eng.embed.master)["embed"]
     head = eng.head.layout.views(eng.head.master)
-    return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb)
+    return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb, norm_b=head.get("bnorm"))
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -192,6 +193,53 @@ def test_gemma_gradients_and_export_against_transformers(tmp_path):
     assert torch.allclose(again, ref, atol=0.08, rtol=0.05)   # the export is bf16
 
 
+def test_starcoder2_gradients_and_export_against_transformers(tmp_path):
+    """Starcoder2: LayerNorm with bias, an MLP without a gate (c_fc, tanh GELU, c_proj), a bias on every projection, tied
+    head. Gradients of norms, biases and MLP matrices against autograd through transformers; the export loads there."""
+    path, hf = _hf_dir(tmp_path, "starcoder2")
+    with torch.no_grad():   # biases start at zero and norm weights at one in transformers
+        for n, p_ in hf.named_parameters():
+            if n.endswith(".bias"):
+                p_.normal_(0.0, 0.3)
+            elif "norm" in n:
+                p_.uniform_(0.5, 1.5)
+    hf.save_pretrained(path)
+    eng = setup_model(path, device="cpu")
+    cfg = eng.cfg
+    assert cfg.norm_type == "layernorm" and not cfg.mlp_gated and cfg.o_proj_bias and cfg.mlp_bias and cfg.tie_word_embeddings
+    ids = torch.randint(0, COMMON["vocab_size"], (25,))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    assert torch.allclose(_our_logits(eng, ids), ref, atol=3e-4, rtol=3e-4)
+    labels = ids.clone()
+    labels[:4] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 25, "num_loss_counted_tokens": 21}], 21)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 21, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 21 - float(out.loss)) < 1e-4
+    got = eng.blocks[0].layout.views(eng.blocks[0].gacc)
+    hg = eng.head.layout.views(eng.head.gacc)
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    L = "model.layers.0."
+    for a, b in [(got["ln1"], want[L + "input_layernorm.weight"]), (got["bln1"], want[L + "input_layernorm.bias"]),
+                 (got["ln2"], want[L + "post_attention_layernorm.weight"]), (got["bln2"], want[L + "post_attention_layernorm.bias"]),
+                 (got["wgu"], want[L + "mlp.c_fc.weight"]), (got["bgu"], want[L + "mlp.c_fc.bias"]),
+                 (got["wd"], want[L + "mlp.c_proj.weight"]), (got["bd"], want[L + "mlp.c_proj.bias"]),
+                 (got["bo"], want[L + "self_attn.o_proj.bias"]), (hg["norm"], want["model.norm.weight"]),
+                 (hg["bnorm"], want["model.norm.bias"])]:
+        assert torch.allclose(a, b, atol=2e-5, rtol=1e-3), float((a - b).abs().max())
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
+    saved_cfg = json.load(open(os.path.join(out_dir, "config.json")))
+    assert saved_cfg["use_bias"] is True and "norm_epsilon" in saved_cfg and "rms_norm_eps" not in saved_cfg
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    with torch.no_grad():
+        again = back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.08, rtol=0.05)   # the export is bf16
+
+
 def test_phi3_export_keeps_the_fused_tensor_names(tmp_path):
     """Phi-3 stores q|k|v and gate|up fused; the export writes them the same way and transformers loads it."""
     path, hf = _hf_dir(tmp_path, "phi3", sliding_window=64)
@@ -299,6 +347,7 @@ def test_projection_biases_reach_logits_gradients_and_exports(tmp_path, kind):
     ("llama", {"hidden_act": "gelu"}, "hidden_act"),
     ("llama", {"attention_dropout": 0.1}, "attention_dropout"),
     ("phi3", {"resid_pdrop": 0.1}, "resid_pdrop"),
+    ("starcoder2", {"residual_dropout": 0.1}, "residual_dropout"),
 ])
 def test_models_the_block_cannot_compute_are_refused(tmp_path, kind, over, needle):
     path, _ = _hf_dir(tmp_path, kind, **over)
