@@ -60,6 +60,8 @@ class ModelConfig:
     # c_proj(gelu(c_fc(x))); its config spells the epsilon ``norm_epsilon`` and has one ``use_bias`` for every projection
     norm_type: str = "rmsnorm"
     mlp_gated: bool = True
+    # dropout is not implemented: a config that sets one is refused unless the user asks to train without it
+    ignore_dropout: bool = False
     # Gemma (modeling_gemma.py): the norms multiply by (1 + weight); embeddings are scaled by sqrt(hidden_size),
     # a constant that is first rounded to the embedding's dtype (55.4256 becomes 55.5 in bf16)
     norm_weight_offset: float = 0.0
@@ -134,8 +136,8 @@ class ModelConfig:
         if arch not in SUPPORTED_ARCHITECTURES:
             problems.append(f"architecture {arch} is not one of {', '.join(SUPPORTED_ARCHITECTURES)}")
         for k in ("attention_dropout", "resid_pdrop", "embd_pdrop", "residual_dropout", "embedding_dropout", "hidden_dropout"):
-            if self.extra.get(k):
-                problems.append(f"{k}={self.extra[k]} (dropout is not implemented; set it to 0 to train without)")
+            if self.extra.get(k) and not self.ignore_dropout:
+                problems.append(f"{k}={self.extra[k]} (dropout is not implemented; pass --no-dropout to train without it)")
         prf = (self.extra.get("rope_parameters") or {}).get("partial_rotary_factor", self.extra.get("partial_rotary_factor", 1.0))
         if prf not in (None, 1.0):
             problems.append(f"partial_rotary_factor={prf} (the rotary kernel turns the whole head)")
@@ -291,7 +293,7 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         d = asdict(self)
         extra = d.pop("extra")
-        for k in ("qk_norm", "norm_weight_offset", "embedding_multiplier_in_param_dtype", "norm_type", "mlp_gated"):
+        for k in ("qk_norm", "norm_weight_offset", "embedding_multiplier_in_param_dtype", "norm_type", "mlp_gated", "ignore_dropout"):
             d.pop(k)   # implied by the model type, not keys of any Hugging Face config
         if self.model_type == "starcoder2":   # back to its own spelling
             d["norm_epsilon"], d["use_bias"] = d.pop("rms_norm_eps"), d.pop("attention_bias")

@@ -81,13 +81,14 @@ def resolve_model_path(model_name_or_path: str) -> str:
 
 def setup_model(model_name_or_path: str, use_liger_kernels: bool = True, device=None, comm_backend: str = "auto",
                 state_dtype: Optional[torch.dtype] = None, seed: int = 0, max_tokens_per_gpu: int = 65536,
-                ops_kind: str = "auto", optim: Optional[OptimConfig] = None) -> ShardedEngine:
+                ops_kind: str = "auto", optim: Optional[OptimConfig] = None, no_dropout: bool = False) -> ShardedEngine:
     """Builds the sharded model.
 
     ``model_name_or_path`` is an HF checkpoint directory (``config.json`` + safetensors), or
     ``random:<preset>`` / ``random:<config.json path>`` for a random-initialised architecture.
     ``use_liger_kernels`` is accepted for CLI parity: the fused linear + cross-entropy is always
-    used on GPUs (the unfused logits path exists only as the CPU oracle).
+    used on GPUs (the unfused logits path exists only as the CPU oracle). ``no_dropout`` accepts a model whose
+    config sets a dropout probability and trains it without (the exported config keeps the model's own values).
     """
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
@@ -107,7 +108,12 @@ def setup_model(model_name_or_path: str, use_liger_kernels: bool = True, device=
     # The reference only warns about unknown classes because AutoModelForCausalLM brings each model's
     # own forward (setup_model_for_training.py:111-123). The forward and backward here are written
     # for one block structure, so a model whose math differs is refused, not trained wrongly.
+    cfg.ignore_dropout = bool(no_dropout)
     cfg.validate_supported()
+    if no_dropout:
+        set_ = {k: v for k, v in cfg.extra.items() if "drop" in k and v}
+        if set_:
+            log_rank_0(f"\033[38;5;226mWARNING: training without the model's dropout {set_}\033[0m")
     comm = make_comm(comm_backend, device)
     if state_dtype is None:
         hbm = torch.cuda.get_device_properties(device).total_memory if device.type == "cuda" else 1e15

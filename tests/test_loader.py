@@ -375,6 +375,12 @@ def test_sliding_window_model_is_trained_up_to_the_window_and_refused_beyond(tmp
                                      "use_sliding_window": True}).attention_window == 32
 
 
+def test_dropout_can_be_waived_and_the_export_keeps_the_models_value(tmp_path):
+    path, _ = _hf_dir(tmp_path, "starcoder2", residual_dropout=0.1)
+    eng = setup_model(path, device="cpu", no_dropout=True)
+    assert eng.cfg.to_hf_dict()["residual_dropout"] == 0.1 and "ignore_dropout" not in eng.cfg.to_hf_dict()
+
+
 def test_unknown_architecture_is_refused(tmp_path):
     path, _ = _hf_dir(tmp_path, "llama")
     cfg = json.load(open(os.path.join(path, "config.json")))
