@@ -1,6 +1,6 @@
 """Decoder configuration, read from / written to Hugging Face ``config.json``.
 
-Covers the Llama / Qwen2 / Qwen3 / Mistral / Phi-3 / Gemma / Granite / Mixtral / Starcoder2 families the reference trains through
+Covers the Llama / Qwen2 / Qwen3 / Qwen3-MoE / Mistral / Phi-3 / Gemma / Granite / Mixtral / Starcoder2 families the reference trains through
 ``AutoModelForCausalLM`` (setup_model_for_training.py:86-130): pre-norm decoder blocks with
 RMSNorm, rotary GQA attention (optional biases, optional per-head q/k norm), a SwiGLU MLP or Mixtral's routed SwiGLU experts,
 tied or untied LM head, plus Granite's four scalars (embedding, residual, attention and logits
@@ -68,8 +68,12 @@ class ModelConfig:
     embedding_multiplier_in_param_dtype: bool = False
     # Qwen3 (modeling_qwen3.py): RMSNorm over head_dim on every q and k head before the rotary embedding
     qk_norm: bool = False
+    # Qwen3-MoE (modeling_qwen3_moe.py): experts of their own width, optional renormalisation of the chosen weights,
+    # experts stored as mlp.experts.N.{gate,up,down}_proj; Mixtral always renormalises and stores w1 / w3 / w2
     num_local_experts: int = 0
     num_experts_per_tok: int = 2
+    moe_intermediate_size: Optional[int] = None
+    norm_topk_prob: bool = True
     output_router_logits: bool = False
     router_jitter_noise: float = 0.0
     extra: dict = field(default_factory=dict)  # unknown keys of config.json, written back verbatim
@@ -120,6 +124,10 @@ class ModelConfig:
     def is_moe(self) -> bool:
         return self.num_local_experts > 0
 
+    @property
+    def expert_intermediate_size(self) -> int:
+        return int(self.moe_intermediate_size or self.intermediate_size)
+
     def validate_supported(self) -> None:
         """Raises ``ValueError`` when the hand-written block would not compute this model's function."""
         arch = (self.architectures or ["?"])[0]
@@ -131,6 +139,9 @@ class ModelConfig:
                 problems.append(f"router_jitter_noise={self.router_jitter_noise} (input jitter is not implemented)")
             if self.mlp_bias:
                 problems.append("mlp_bias=true with experts")
+            if self.extra.get("decoder_sparse_step", 1) != 1 or self.extra.get("mlp_only_layers"):
+                problems.append("dense and expert layers mixed (decoder_sparse_step / mlp_only_layers): every block must have "
+                                "the same layout")
             if not 0 < self.num_experts_per_tok <= self.num_local_experts:
                 problems.append(f"num_experts_per_tok={self.num_experts_per_tok} of {self.num_local_experts} experts")
         if arch not in SUPPORTED_ARCHITECTURES:
@@ -179,7 +190,7 @@ class ModelConfig:
         return self.num_experts_per_tok if self.is_moe else 1
 
     def block_param_count(self) -> int:
-        h, f = self.hidden_size, self.intermediate_size
+        h, f = self.hidden_size, (self.expert_intermediate_size if self.is_moe else self.intermediate_size)
         n = 2 * h + self.qkv_size * h + self.q_size * h + self.mlp_mats * h * f * max(1, self.num_local_experts)
         n += 2 * h if self.norm_type == "layernorm" else 0
         n += self.num_local_experts * h   # router
@@ -196,7 +207,7 @@ class ModelConfig:
     def flops_per_token(self, avg_context: float = 0.0, recompute: bool = True) -> float:
         """Training FLOPs per token: 6 x matmul params (+2 x with full recompute) + attention. With experts
         only the ``num_experts_per_tok`` chosen ones (and the router) count."""
-        h, f = self.hidden_size, self.intermediate_size
+        h, f = self.hidden_size, (self.expert_intermediate_size if self.is_moe else self.intermediate_size)
         mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + self.mlp_mats * h * f * self.mlp_rows_factor
                                        + self.num_local_experts * h)
         head = self.vocab_size * h
@@ -212,7 +223,7 @@ class ModelConfig:
         by causality, times 3.5 for forward + backward. The rates are typical sustained throughputs of
         the two kernel families on a power-capped B200.
         """
-        h, f = self.hidden_size, self.intermediate_size
+        h, f = self.hidden_size, (self.expert_intermediate_size if self.is_moe else self.intermediate_size)
         mm = self.num_hidden_layers * (self.qkv_size * h + self.q_size * h + self.mlp_mats * h * f * self.mlp_rows_factor)
         gemm = (8 if recompute else 6) * mm + 6 * self.vocab_size * h
         attn = 3.5 * 2 * self.q_size * self.num_hidden_layers
@@ -248,8 +259,10 @@ class ModelConfig:
               "tie_word_embeddings", "max_position_embeddings", "model_type", "architectures",
               "pad_token_id", "bos_token_id", "eos_token_id", "embedding_multiplier", "residual_multiplier",
               "attention_multiplier", "logits_scaling", "sliding_window", "use_sliding_window", "mlp_bias", "hidden_act",
-              "num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise")
-    _MOE_ONLY = ("num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise")
+              "num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise",
+              "moe_intermediate_size", "norm_topk_prob")
+    _MOE_ONLY = ("num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise",
+                 "moe_intermediate_size", "norm_topk_prob")
     _GRANITE_ONLY = ("embedding_multiplier", "residual_multiplier", "attention_multiplier", "logits_scaling")
 
     @classmethod
@@ -264,8 +277,17 @@ class ModelConfig:
                 kw.setdefault("rope_scaling", rp)
         if kw.get("model_type") == "qwen2":
             kw.setdefault("attention_bias", True)  # Qwen2 always has q/k/v biases
-        if kw.get("model_type") == "qwen3":
+        if kw.get("model_type") in ("qwen3", "qwen3_moe"):
             kw["qk_norm"] = True
+        if kw.get("model_type") == "qwen3_moe":
+            if "num_experts" in d:   # the published configs' key; transformers also writes num_local_experts
+                kw["num_local_experts"] = d["num_experts"]
+            kw.setdefault("norm_topk_prob", False)
+            kw.setdefault("moe_intermediate_size", 768)
+            kw.setdefault("num_experts_per_tok", 8)
+        if kw.get("model_type") == "mixtral":
+            kw.pop("moe_intermediate_size", None)
+            kw["norm_topk_prob"] = True
         if kw.get("model_type") == "starcoder2":
             use_bias = bool(d.pop("use_bias", True))
             kw.update(norm_type="layernorm", mlp_gated=False, attention_bias=use_bias, mlp_bias=use_bias,
@@ -307,8 +329,10 @@ class ModelConfig:
             if self.model_type != "granite":
                 d.pop(k)
         for k in self._MOE_ONLY:
-            if not self.is_moe:
+            if not self.is_moe or (self.model_type == "mixtral" and k in ("moe_intermediate_size", "norm_topk_prob")):
                 d.pop(k)
+        if self.model_type == "qwen3_moe":
+            d["num_experts"] = self.num_local_experts
         for k in ("sliding_window", "use_sliding_window"):
             if d[k] is None:
                 d.pop(k)
@@ -330,7 +354,7 @@ class ModelConfig:
 
 SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
                            "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM", "GemmaForCausalLM",
-                           "Starcoder2ForCausalLM")
+                           "Starcoder2ForCausalLM", "Qwen3MoeForCausalLM")
 
 
 def _llama(**kw):

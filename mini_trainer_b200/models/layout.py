@@ -81,9 +81,10 @@ def block_entries(cfg: ModelConfig) -> list:
     if ln:
         e.append(("bln2", (h,)))
     if cfg.is_moe:   # router, then every expert's fused gate/up and down matrices
+        fe = cfg.expert_intermediate_size
         e.append(("router", (cfg.num_local_experts, h)))
         for x in range(cfg.num_local_experts):
-            e += [(f"wgu{x}", (2 * f, h)), (f"wd{x}", (h, f))]
+            e += [(f"wgu{x}", (2 * fe, h)), (f"wd{x}", (h, fe))]
         return e
     if cfg.mlp_bias:
         e.append(("bgu", (gu,)))
@@ -138,13 +139,21 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
     if cfg.o_proj_bias:
         yield p + "self_attn.o_proj.bias", views["bo"]
     f = cfg.intermediate_size
-    if cfg.is_moe:   # names of the published Mixtral checkpoints (w1 = gate, w3 = up, w2 = down)
-        m = p + "block_sparse_moe."
-        for x in range(cfg.num_local_experts):
-            yield m + f"experts.{x}.w1.weight", views[f"wgu{x}"][:f]
-            yield m + f"experts.{x}.w2.weight", views[f"wd{x}"]
-            yield m + f"experts.{x}.w3.weight", views[f"wgu{x}"][f:]
-        yield m + "gate.weight", views["router"]
+    if cfg.is_moe:   # names of the published checkpoints
+        fe = cfg.expert_intermediate_size
+        if cfg.model_type == "mixtral":   # w1 = gate, w3 = up, w2 = down
+            m = p + "block_sparse_moe."
+            for x in range(cfg.num_local_experts):
+                yield m + f"experts.{x}.w1.weight", views[f"wgu{x}"][:fe]
+                yield m + f"experts.{x}.w2.weight", views[f"wd{x}"]
+                yield m + f"experts.{x}.w3.weight", views[f"wgu{x}"][fe:]
+            yield m + "gate.weight", views["router"]
+        else:   # Qwen3-MoE
+            for x in range(cfg.num_local_experts):
+                yield p + f"mlp.experts.{x}.gate_proj.weight", views[f"wgu{x}"][:fe]
+                yield p + f"mlp.experts.{x}.up_proj.weight", views[f"wgu{x}"][fe:]
+                yield p + f"mlp.experts.{x}.down_proj.weight", views[f"wd{x}"]
+            yield p + "mlp.gate.weight", views["router"]
         yield p + "input_layernorm.weight", views["ln1"]
         yield p + "post_attention_layernorm.weight", views["ln2"]
         return

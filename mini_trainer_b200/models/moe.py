@@ -2,9 +2,9 @@
 
 The reference trains Mixtral through ``AutoModelForCausalLM`` (it is on the allow-list of
 setup_model_for_training.py:111-123); the function reproduced here is transformers'
-``MixtralSparseMoeBlock`` (modeling_mixtral.py): router logits in the compute dtype, softmax in
-fp32, top-k, weights renormalised over the chosen experts, each expert a SwiGLU MLP, outputs
-combined with the weights. No auxiliary load-balancing loss (transformers only adds one with
+``MixtralSparseMoeBlock`` (modeling_mixtral.py) and ``Qwen3MoeSparseMoeBlock`` (modeling_qwen3_moe.py):
+router logits in the compute dtype, softmax in fp32, top-k, weights renormalised over the chosen
+experts (optional for Qwen3-MoE), each expert a SwiGLU MLP, outputs combined with the weights. No auxiliary load-balancing loss (transformers only adds one with
 ``output_router_logits``; a config that asks for it is refused at load time).
 
 Schedule: the (token, slot) pairs are sorted by expert once per block, so every expert sees one
@@ -45,7 +45,7 @@ def route(cfg, router_w: torch.Tensor, n2: torch.Tensor, topi: Optional[torch.Te
         topv, topi = torch.topk(probs, k, dim=-1)
     else:
         topv = probs.gather(1, topi)
-    w = topv / topv.sum(-1, keepdim=True)
+    w = topv / topv.sum(-1, keepdim=True) if cfg.norm_topk_prob else topv
     flat = topi.reshape(-1)
     order = torch.argsort(flat, stable=True)
     bounds = [0] + torch.cumsum(torch.bincount(flat, minlength=E), 0).tolist()   # the block's one host read
@@ -72,7 +72,7 @@ def moe_forward(ops, cfg, p: dict, n2: torch.Tensor, h1: torch.Tensor, need_out:
     k = cfg.num_experts_per_tok
     probs, topi, w, order, tok, bounds = route(cfg, p["router"], n2)
     xs = ops.embedding(n2, tok)                       # rows gathered expert by expert
-    gu = torch.empty(T * k, 2 * cfg.intermediate_size, dtype=n2.dtype, device=n2.device)
+    gu = torch.empty(T * k, 2 * cfg.expert_intermediate_size, dtype=n2.dtype, device=n2.device)
     for e, a, b in _slabs(bounds):
         if b > a:
             ops.linear(xs[a:b], p[f"wgu{e}"], out=gu[a:b])
@@ -134,8 +134,11 @@ def moe_backward(ops, cfg, p: dict, g: dict, st: MoeState, n2: torch.Tensor, dou
     dw = torch.empty(T * k, dtype=torch.float32, device=n2.device)
     dw[order] = dwr
     dw = dw.view(T, k)
-    s = st.probs.gather(1, st.topi).sum(-1, keepdim=True)
-    dtop = (dw - (dw * st.w).sum(-1, keepdim=True)) / s
+    if cfg.norm_topk_prob:
+        s = st.probs.gather(1, st.topi).sum(-1, keepdim=True)
+        dtop = (dw - (dw * st.w).sum(-1, keepdim=True)) / s
+    else:   # Qwen3-MoE may use the chosen probabilities as they are
+        dtop = dw
     dprobs = torch.zeros_like(st.probs).scatter_(1, st.topi, dtop)
     dlogits = (st.probs * (dprobs - (dprobs * st.probs).sum(-1, keepdim=True))).to(n2.dtype)
     g["router"].copy_(dlogits.t() @ n2)

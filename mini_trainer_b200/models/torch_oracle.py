@@ -62,14 +62,16 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
         x = x + rm * F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
         n = _norm(cfg, sd, p + "post_attention_layernorm", x)
         if cfg.is_moe:   # dense restatement: every expert on every token, masked by the routing weights
-            m = p + "block_sparse_moe."
+            mix = cfg.model_type == "mixtral"
+            m = p + ("block_sparse_moe." if mix else "mlp.")
+            names = ("w1", "w3", "w2") if mix else ("gate_proj", "up_proj", "down_proj")
             probs = F.softmax(F.linear(n, sd[m + "gate.weight"]).float(), -1)
             topv, topi = probs.topk(cfg.num_experts_per_tok, -1)
-            gatew = torch.zeros_like(probs).scatter(1, topi, topv / topv.sum(-1, keepdim=True))
+            gatew = torch.zeros_like(probs).scatter(1, topi, topv / topv.sum(-1, keepdim=True) if cfg.norm_topk_prob else topv)
             y = 0
             for e in range(cfg.num_local_experts):
-                a = F.silu(F.linear(n, sd[m + f"experts.{e}.w1.weight"])) * F.linear(n, sd[m + f"experts.{e}.w3.weight"])
-                y = y + gatew[:, e: e + 1].to(n.dtype) * F.linear(a, sd[m + f"experts.{e}.w2.weight"])
+                a = F.silu(F.linear(n, sd[m + f"experts.{e}.{names[0]}.weight"])) * F.linear(n, sd[m + f"experts.{e}.{names[1]}.weight"])
+                y = y + gatew[:, e: e + 1].to(n.dtype) * F.linear(a, sd[m + f"experts.{e}.{names[2]}.weight"])
             x = x + rm * y
             continue
         if not cfg.mlp_gated:

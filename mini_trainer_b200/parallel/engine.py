@@ -445,7 +445,7 @@ class ShardedEngine:
         if budget <= 0:
             return levels
         es = 2 if self.param_dtype != torch.float32 else 4
-        h, f = cfg.hidden_size, cfg.intermediate_size * cfg.mlp_rows_factor
+        h, f = cfg.hidden_size, (cfg.expert_intermediate_size if cfg.is_moe else cfg.intermediate_size) * cfg.mlp_rows_factor
         lvl1 = tokens * (cfg.q_size * es + cfg.num_attention_heads * 4)
         # level 0 keeps qkv, the attention output, h1 and gate/up (the normalised inputs and the SwiGLU
         # output are rebuilt in backward by elementwise kernels)
@@ -477,7 +477,8 @@ class ShardedEngine:
             return 0
         cfg = self.cfg
         total = torch.cuda.get_device_properties(self.device).total_memory
-        h, f, v = cfg.hidden_size, cfg.intermediate_size * cfg.mlp_rows_factor, cfg.vocab_size
+        h, v = cfg.hidden_size, cfg.vocab_size
+        f = (cfg.expert_intermediate_size if cfg.is_moe else cfg.intermediate_size) * cfg.mlp_rows_factor
         base = tokens * 2 * h * len(self.blocks)
         work = tokens * 2 * (7 * h + cfg.qkv_size + 6 * f)
         ce = getattr(self.ops, "ce_chunk", 2048) * v * 2 + v * h * 4

@@ -32,6 +32,8 @@ def _hf_dir(tmp_path, kind, **over):
            "phi3": (transformers.Phi3Config, {"pad_token_id": 0, "eos_token_id": 2}),
            "qwen3": (transformers.Qwen3Config, {"head_dim": 32}),
            "gemma": (transformers.GemmaConfig, {"head_dim": 32}),
+           "qwen3_moe": (transformers.Qwen3MoeConfig, {"head_dim": 32, "num_experts": 4, "num_experts_per_tok": 2,
+                                                       "moe_intermediate_size": 48}),
            "starcoder2": (transformers.Starcoder2Config, {"sliding_window": None, "bos_token_id": 1, "eos_token_id": 2})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
@@ -52,7 +54,7 @@ def _our_logits(eng, ids):
     return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb, norm_b=head.get("bnorm"))
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2", "qwen3_moe"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -253,6 +255,39 @@ def test_phi3_export_keeps_the_fused_tensor_names(tmp_path):
     assert "model.layers.0.self_attn.qkv_proj.weight" in names and "model.layers.1.mlp.gate_up_proj.weight" in names
     back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
     ids = torch.randint(0, COMMON["vocab_size"], (17,))
+    with torch.no_grad():
+        ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
+
+
+@pytest.mark.parametrize("renorm", [False, True])
+def test_qwen3_moe_gradients_against_transformers(tmp_path, renorm):
+    """Qwen3-MoE: per-head q/k norm plus routed experts of their own width, with and without renormalising the chosen
+    weights; router, expert and norm gradients against autograd through transformers; export under the published names."""
+    path, hf = _hf_dir(tmp_path, "qwen3_moe", norm_topk_prob=renorm)
+    eng = setup_model(path, device="cpu")
+    cfg = eng.cfg
+    assert cfg.is_moe and cfg.qk_norm and cfg.norm_topk_prob == renorm and cfg.expert_intermediate_size == 48
+    ids = torch.randint(0, COMMON["vocab_size"], (26,))
+    labels = ids.clone()
+    labels[:6] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 26, "num_loss_counted_tokens": 20}], 20)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 20, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 20 - float(out.loss)) < 1e-4
+    got = eng.blocks[0].layout.views(eng.blocks[0].gacc)
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    L = "model.layers.0."
+    assert torch.allclose(got["router"], want[L + "mlp.gate.weight"], atol=1e-5, rtol=1e-3)
+    for e in range(4):
+        assert torch.allclose(got[f"wgu{e}"], want[L + "mlp.experts.gate_up_proj"][e], atol=1e-5, rtol=1e-3)
+        assert torch.allclose(got[f"wd{e}"], want[L + "mlp.experts.down_proj"][e], atol=1e-5, rtol=1e-3)
+    assert torch.allclose(got["qn"], want[L + "self_attn.q_norm.weight"], atol=1e-5, rtol=1e-3)
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
     with torch.no_grad():
         ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
     assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
