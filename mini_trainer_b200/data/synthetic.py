@@ -30,6 +30,8 @@ CONFIG_DATA = {
     "llama-3.1-8b": (LengthSpec(7.5, 1.0, 64, 65536), 128256, 64000, 128),
     "qwen2.5-7b": (LengthSpec(7.5, 1.0, 64, 65536), 152064, 48000, 128),
     "llama-3.1-70b": (LengthSpec(7.5, 1.0, 64, 32768), 128256, 16000, 64),
+    "tiny-mixtral": (LengthSpec(5.5, 0.8, 16, 2048), 4096, 4096, 32),
+    "mixtral-8x7b": (LengthSpec(7.5, 1.0, 64, 32768), 32000, 32000, 128),
 }
 
 
