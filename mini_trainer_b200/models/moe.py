@@ -69,31 +69,38 @@ def moe_forward(ops, cfg, p: dict, n2: torch.Tensor, h1: torch.Tensor, need_out:
     """``(h1 + residual_multiplier * MoE(n2), state)``; the output is ``None`` when ``need_out`` is false
     (a recompute inside backward stops after the gate/up projections)."""
     T, H = n2.shape
-    k = cfg.num_experts_per_tok
+    k, fe = cfg.num_experts_per_tok, cfg.expert_intermediate_size
     probs, topi, w, order, tok, bounds = route(cfg, p["router"], n2)
     xs = ops.embedding(n2, tok)                       # rows gathered expert by expert
-    gu = torch.empty(T * k, 2 * cfg.expert_intermediate_size, dtype=n2.dtype, device=n2.device)
+    gu = torch.empty(T * k, 2 * fe, dtype=n2.dtype, device=n2.device)
     for e, a, b in _slabs(bounds):
         if b > a:
             ops.linear(xs[a:b], p[f"wgu{e}"], out=gu[a:b])
+    del xs
     st = MoeState(probs, topi, w, order, tok, bounds, gu, None)
     if not need_out:
         return None, st
-    act = ops.swiglu(gu, cfg.mlp_act)
+    # activation and down projection slab by slab: only the slab's activation is alive unless backward wants all of it
+    act = torch.empty(T * k, fe, dtype=n2.dtype, device=n2.device) if keep_act else None
     yr = torch.empty(T * k, H, dtype=n2.dtype, device=n2.device)
     for e, a, b in _slabs(bounds):
         if b > a:
-            ops.linear(act[a:b], p[f"wd{e}"], out=yr[a:b])
+            act_e = ops.swiglu(gu[a:b], cfg.mlp_act)
+            ops.linear(act_e, p[f"wd{e}"], out=yr[a:b])
+            if keep_act:
+                act[a:b] = act_e
     wr = w.reshape(-1)[order]
     y = _combine((yr.float() * wr[:, None]).to(yr.dtype), order, T, k)
-    if keep_act:
-        st.act = act
+    st.act = act
     return (h1.float() + cfg.residual_multiplier * y).to(h1.dtype), st
 
 
 def moe_backward(ops, cfg, p: dict, g: dict, st: MoeState, n2: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
     """Writes the gradients of the router and of every expert into ``g`` and returns the gradient of
-    ``n2`` (the normalised MLP input). ``dout`` is the gradient of the block output."""
+    ``n2`` (the normalised MLP input). ``dout`` is the gradient of the block output.
+
+    Everything between the gathered output gradient and the gathered input gradient runs slab by slab, so the
+    intermediates (activation, its gradient, the gate/up gradient) only ever exist for one expert's rows."""
     T, H = n2.shape
     k = cfg.num_experts_per_tok
     rm = cfg.residual_multiplier
@@ -101,35 +108,30 @@ def moe_backward(ops, cfg, p: dict, g: dict, st: MoeState, n2: torch.Tensor, dou
     gr = ops.embedding(dout, tok)                     # output gradient of every routed row, before its weight
     if rm != 1.0:
         gr = gr * rm
-    act = st.act if st.act is not None else ops.swiglu(st.gu, cfg.mlp_act)
-    # y_row = wd act, weighted by w: d(weight) = dout . y_row = (wd^T dout) . act, so the unweighted
-    # data gradient of the down projection gives both the weight's and (scaled) the activation's gradient
-    du = torch.empty_like(act)
-    for e, a, b in _slabs(bounds):
-        if b > a:
-            ops.linear_dgrad(gr[a:b], p[f"wd{e}"], out=du[a:b])
-    wr = st.w.reshape(-1)[order]
-    dwr = (du.float() * act.float()).sum(-1)
-    actw = (act.float() * wr[:, None]).to(act.dtype)
-    for e, a, b in _slabs(bounds):
-        if b > a:
-            ops.linear_wgrad(gr[a:b], actw[a:b], g[f"wd{e}"])
-        else:
-            g[f"wd{e}"].zero_()                       # an expert no token chose: its gradient is zero, not stale
-    dact = (du.float() * wr[:, None]).to(du.dtype)
-    del du, actw, act, gr
-    dgu = ops.swiglu_bwd(dact, st.gu, cfg.mlp_act)
-    del dact
     xs = ops.embedding(n2, tok)
+    wr = st.w.reshape(-1)[order]
+    dwr = torch.zeros(T * k, dtype=torch.float32, device=n2.device)
     dxs = torch.empty(T * k, H, dtype=n2.dtype, device=n2.device)
     for e, a, b in _slabs(bounds):
-        if b > a:
-            ops.linear_dgrad(dgu[a:b], p[f"wgu{e}"], out=dxs[a:b])
-            ops.linear_wgrad(dgu[a:b], xs[a:b], g[f"wgu{e}"])
-        else:
+        if b == a:   # an expert no token chose: its gradients are zero, not what the buffer held before
+            g[f"wd{e}"].zero_()
             g[f"wgu{e}"].zero_()
+            continue
+        gu_e, w_e = st.gu[a:b], wr[a:b, None]
+        act = st.act[a:b] if st.act is not None else ops.swiglu(gu_e, cfg.mlp_act)
+        # y_row = wd act, weighted by w: d(weight) = dout . y_row = (wd^T dout) . act, so the unweighted data
+        # gradient of the down projection gives both the weight's and (scaled) the activation's gradient
+        du = ops.linear_dgrad(gr[a:b], p[f"wd{e}"])
+        duf, actf = du.float(), act.float()
+        dwr[a:b] = (duf * actf).sum(-1)
+        ops.linear_wgrad(gr[a:b], (actf * w_e).to(act.dtype), g[f"wd{e}"])
+        dgu = ops.swiglu_bwd((duf * w_e).to(du.dtype), gu_e, cfg.mlp_act)
+        del du, duf, actf, act
+        ops.linear_dgrad(dgu, p[f"wgu{e}"], out=dxs[a:b])
+        ops.linear_wgrad(dgu, xs[a:b], g[f"wgu{e}"])
+        del dgu
     dn2 = _combine(dxs, order, T, k)
-    del dgu, xs, dxs
+    del xs, dxs, gr
     # router: weights -> renormalisation -> top-k selection -> softmax -> logits
     dw = torch.empty(T * k, dtype=torch.float32, device=n2.device)
     dw[order] = dwr
