@@ -1,6 +1,6 @@
 """Decoder configuration, read from / written to Hugging Face ``config.json``.
 
-Covers the Llama / Qwen2 / Qwen3 / Qwen3-MoE / Mistral / Phi-3 / Gemma / Granite / Mixtral / Starcoder2 families the reference trains through
+Covers the Llama / Qwen2 / Qwen3 / Qwen3-MoE / Mistral / Phi-3 / Gemma / Granite / Granite-MoE / Mixtral / Starcoder2 families the reference trains through
 ``AutoModelForCausalLM`` (setup_model_for_training.py:86-130): pre-norm decoder blocks with
 RMSNorm, rotary GQA attention (optional biases, optional per-head q/k norm), a SwiGLU MLP or Mixtral's routed SwiGLU experts,
 tied or untied LM head, plus Granite's four scalars (embedding, residual, attention and logits
@@ -285,7 +285,9 @@ class ModelConfig:
             kw.setdefault("norm_topk_prob", False)
             kw.setdefault("moe_intermediate_size", 768)
             kw.setdefault("num_experts_per_tok", 8)
-        if kw.get("model_type") == "mixtral":
+        if kw.get("model_type") in ("mixtral", "granitemoe"):
+            # GraniteMoe takes the softmax over the chosen logits only, which is the softmax over all of them
+            # renormalised over the chosen ones: the same weights as Mixtral's
             kw.pop("moe_intermediate_size", None)
             kw["norm_topk_prob"] = True
         if kw.get("model_type") == "starcoder2":
@@ -326,10 +328,10 @@ class ModelConfig:
             if lst is not None:
                 d[k] = lst
         for k in self._GRANITE_ONLY:   # only Granite's config class knows these keys
-            if self.model_type != "granite":
+            if self.model_type not in ("granite", "granitemoe"):
                 d.pop(k)
         for k in self._MOE_ONLY:
-            if not self.is_moe or (self.model_type == "mixtral" and k in ("moe_intermediate_size", "norm_topk_prob")):
+            if not self.is_moe or (self.model_type in ("mixtral", "granitemoe") and k in ("moe_intermediate_size", "norm_topk_prob")):
                 d.pop(k)
         if self.model_type == "qwen3_moe":
             d["num_experts"] = self.num_local_experts
@@ -354,7 +356,7 @@ class ModelConfig:
 
 SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
                            "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM", "GemmaForCausalLM",
-                           "Starcoder2ForCausalLM", "Qwen3MoeForCausalLM")
+                           "Starcoder2ForCausalLM", "Qwen3MoeForCausalLM", "GraniteMoeForCausalLM")
 
 
 def _llama(**kw):

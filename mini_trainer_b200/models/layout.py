@@ -111,7 +111,8 @@ def head_entries(cfg: ModelConfig) -> list:
 # HF name mapping
 # ------------------------------------------------------------------------------------------
 def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[tuple]:
-    """Yields ``(hf_name, tensor_view)`` for one block, in HF ``state_dict`` order."""
+    """Yields ``(hf_name, tensor_view)`` for one block, in HF ``state_dict`` order. Where the checkpoint stacks
+    the experts of a projection into one 3-D tensor (Granite-MoE) the second item is a tuple of views, one per expert."""
     p = f"model.layers.{layer}."
     q, kv = cfg.q_size, cfg.kv_size
     if cfg.fused_hf_names:   # Phi-3: the checkpoint's tensors are the layout's
@@ -148,6 +149,11 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
                 yield m + f"experts.{x}.w2.weight", views[f"wd{x}"]
                 yield m + f"experts.{x}.w3.weight", views[f"wgu{x}"][fe:]
             yield m + "gate.weight", views["router"]
+        elif cfg.model_type == "granitemoe":   # one 3-D tensor per projection: a tuple of views, one per expert
+            m = p + "block_sparse_moe."
+            yield m + "input_linear.weight", tuple(views[f"wgu{x}"] for x in range(cfg.num_local_experts))
+            yield m + "output_linear.weight", tuple(views[f"wd{x}"] for x in range(cfg.num_local_experts))
+            yield m + "router.layer.weight", views["router"]
         else:   # Qwen3-MoE
             for x in range(cfg.num_local_experts):
                 yield p + f"mlp.experts.{x}.gate_proj.weight", views[f"wgu{x}"][:fe]

@@ -62,16 +62,28 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
         x = x + rm * F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
         n = _norm(cfg, sd, p + "post_attention_layernorm", x)
         if cfg.is_moe:   # dense restatement: every expert on every token, masked by the routing weights
-            mix = cfg.model_type == "mixtral"
-            m = p + ("block_sparse_moe." if mix else "mlp.")
-            names = ("w1", "w3", "w2") if mix else ("gate_proj", "up_proj", "down_proj")
-            probs = F.softmax(F.linear(n, sd[m + "gate.weight"]).float(), -1)
+            fe = cfg.expert_intermediate_size
+            if cfg.model_type == "mixtral":
+                m = p + "block_sparse_moe."
+                router = sd[m + "gate.weight"]
+                experts = [(sd[m + f"experts.{e}.w1.weight"], sd[m + f"experts.{e}.w3.weight"], sd[m + f"experts.{e}.w2.weight"])
+                           for e in range(cfg.num_local_experts)]
+            elif cfg.model_type == "granitemoe":   # stacked [E, 2F, H] and [E, H, F]
+                m = p + "block_sparse_moe."
+                router = sd[m + "router.layer.weight"]
+                experts = [(sd[m + "input_linear.weight"][e, :fe], sd[m + "input_linear.weight"][e, fe:],
+                            sd[m + "output_linear.weight"][e]) for e in range(cfg.num_local_experts)]
+            else:
+                m = p + "mlp."
+                router = sd[m + "gate.weight"]
+                experts = [(sd[m + f"experts.{e}.gate_proj.weight"], sd[m + f"experts.{e}.up_proj.weight"],
+                            sd[m + f"experts.{e}.down_proj.weight"]) for e in range(cfg.num_local_experts)]
+            probs = F.softmax(F.linear(n, router).float(), -1)
             topv, topi = probs.topk(cfg.num_experts_per_tok, -1)
             gatew = torch.zeros_like(probs).scatter(1, topi, topv / topv.sum(-1, keepdim=True) if cfg.norm_topk_prob else topv)
             y = 0
-            for e in range(cfg.num_local_experts):
-                a = F.silu(F.linear(n, sd[m + f"experts.{e}.{names[0]}.weight"])) * F.linear(n, sd[m + f"experts.{e}.{names[1]}.weight"])
-                y = y + gatew[:, e: e + 1].to(n.dtype) * F.linear(a, sd[m + f"experts.{e}.{names[2]}.weight"])
+            for e, (wg, wu, wdn) in enumerate(experts):
+                y = y + gatew[:, e: e + 1].to(n.dtype) * F.linear(F.silu(F.linear(n, wg)) * F.linear(n, wu), wdn)
             x = x + rm * y
             continue
         if not cfg.mlp_gated:

@@ -227,6 +227,12 @@ class ShardedEngine:
             views = grp.layout.views(full)
             for name, view in it(views):
                 src = get_tensor(name).to(torch.float32)
+                if isinstance(view, tuple):   # experts stacked along the first dimension of one checkpoint tensor
+                    if src.shape[0] != len(view) or src[0].numel() != view[0].numel():
+                        raise ValueError(f"{name}: checkpoint shape {tuple(src.shape)} does not fit {len(view)} x {tuple(view[0].shape)}")
+                    for x, v in enumerate(view):
+                        v.copy_(src[x].reshape(v.shape))
+                    continue
                 if src.dim() == 2 and src.shape[0] < view.shape[0] and src.shape[1:] == view.shape[1:] \
                         and name in ("model.embed_tokens.weight", "lm_head.weight"):
                     view[: src.shape[0]].copy_(src)
@@ -264,7 +270,10 @@ class ShardedEngine:
             views = grp.layout.views(full)
             to_host = host_ranks is None or self.rank in host_ranks
             for name, view in it(views):
-                yield name, (view.to(dtype).cpu() if to_host else None)
+                if isinstance(view, tuple):
+                    yield name, (torch.stack([v.to(dtype) for v in view]).cpu() if to_host else None)
+                else:
+                    yield name, (view.to(dtype).cpu() if to_host else None)
             del full, views
 
     # ------------------------------------------------------------------------------------

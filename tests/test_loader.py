@@ -34,6 +34,9 @@ def _hf_dir(tmp_path, kind, **over):
            "gemma": (transformers.GemmaConfig, {"head_dim": 32}),
            "qwen3_moe": (transformers.Qwen3MoeConfig, {"head_dim": 32, "num_experts": 4, "num_experts_per_tok": 2,
                                                        "moe_intermediate_size": 48}),
+           "granitemoe": (transformers.GraniteMoeConfig, {"num_local_experts": 4, "num_experts_per_tok": 2,
+                                                         "embedding_multiplier": 12.0, "residual_multiplier": 0.22,
+                                                         "attention_multiplier": 0.0625, "logits_scaling": 8.0}),
            "starcoder2": (transformers.Starcoder2Config, {"sliding_window": None, "bos_token_id": 1, "eos_token_id": 2})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
@@ -54,7 +57,7 @@ def _our_logits(eng, ids):
     return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb, norm_b=head.get("bnorm"))
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2", "qwen3_moe"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2", "qwen3_moe", "granitemoe"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -287,6 +290,39 @@ def test_qwen3_moe_gradients_against_transformers(tmp_path, renorm):
     from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
     out_dir = str(tmp_path / "export")
     save_hf_checkpoint(eng, out_dir)
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    with torch.no_grad():
+        ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
+
+
+def test_granite_moe_gradients_and_stacked_export_against_transformers(tmp_path):
+    """Granite-MoE: Granite's multipliers around routed experts whose checkpoint stacks every projection into one 3-D
+    tensor. Router and expert gradients against autograd through transformers; the export stacks them again."""
+    path, hf = _hf_dir(tmp_path, "granitemoe")
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.is_moe and eng.cfg.residual_multiplier == 0.22
+    ids = torch.randint(0, COMMON["vocab_size"], (26,))
+    labels = ids.clone()
+    labels[:6] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 26, "num_loss_counted_tokens": 20}], 20)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 20, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 20 - float(out.loss)) < 1e-4
+    got = eng.blocks[1].layout.views(eng.blocks[1].gacc)
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    L = "model.layers.1.block_sparse_moe."
+    assert torch.allclose(got["router"], want[L + "router.layer.weight"], atol=1e-5, rtol=1e-3)
+    for e in range(4):
+        assert torch.allclose(got[f"wgu{e}"], want[L + "input_linear.weight"][e], atol=1e-5, rtol=1e-3)
+        assert torch.allclose(got[f"wd{e}"], want[L + "output_linear.weight"][e], atol=1e-5, rtol=1e-3)
+    from mini_trainer_b200.ckpt import safetensors_io as st
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
+    saved = st.load_file(os.path.join(out_dir, "model.safetensors"))
+    assert tuple(saved[L + "input_linear.weight"].shape) == (4, 2 * COMMON["intermediate_size"], COMMON["hidden_size"])
     back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
     with torch.no_grad():
         ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
