@@ -3,6 +3,7 @@
     python bench_kernels.py --op gemm --layout nt --m 8192 --n 8192 --k 8192
     python bench_kernels.py --op attn_fwd --lens 16384,16384
     python bench_kernels.py --op all
+    python bench_kernels.py --op families      # LayerNorm, per-head q/k norm, GeGLU / GELU
     (ops: gemm, attn_fwd, attn_bwd, rmsnorm, swiglu, rope, ce, linear_ce, embedding, adamw)
 
 Each op is timed with CUDA events on the launching stream after warm-up, with a synchronize on
@@ -235,6 +236,39 @@ def main():
         coef = torch.ones(1, device="cuda")
         report(f"adamw_{n}", timeit(lambda: ops.adamw_step(master, m, v, g, p, 1e-4, 0.9, 0.95, 1e-8, 0.0, 2, coef), a.iters, a.warmup, flush),
                bytes_=n * (4 * 4 + 3 * 4 + 2.0))
+    def op_layernorm():
+        T, H = a.tokens, min(a.hidden, 6144)
+        x, w, b, dy = bf(T, H), bf(H), bf(H), bf(T, H)
+        y, stats = ops.layernorm(x, w, b, 1e-5)
+        dw, db = torch.empty_like(w), torch.empty_like(b)
+        report(f"layernorm_fwd_{T}x{H}", timeit(lambda: ops.layernorm(x, w, b, 1e-5), a.iters, a.warmup, flush), bytes_=2.0 * T * H * 2)
+        report(f"layernorm_bwd_{T}x{H}", timeit(lambda: ops.layernorm_bwd(dy, x, stats, w, dw, db, add_to=dy), a.iters, a.warmup, flush),
+               bytes_=4.0 * T * H * 2)
+    def op_head_rmsnorm():
+        T, nh = a.tokens, a.hq + a.hkv
+        qkv, dqkv = bf(T, (a.hq + 2 * a.hkv) * a.d), bf(T, (a.hq + 2 * a.hkv) * a.d)
+        wq, wk = bf(a.d), bf(a.d)
+        pre = qkv[:, : nh * a.d].clone()
+        rstd = ops.head_rmsnorm_(qkv.clone(), wq, wk, 1e-6, a.hq, a.hkv, a.d)
+        gq, gk = torch.empty_like(wq), torch.empty_like(wk)
+        # in place on the q and k heads: read + write (forward), read gradient and pre-norm heads + write (backward)
+        report(f"head_rmsnorm_fwd_{T}x{a.hq}+{a.hkv}x{a.d}", timeit(lambda: ops.head_rmsnorm_(qkv, wq, wk, 1e-6, a.hq, a.hkv, a.d), a.iters, a.warmup, flush),
+               bytes_=2.0 * T * nh * a.d * 2)
+        report(f"head_rmsnorm_bwd_{T}x{a.hq}+{a.hkv}x{a.d}",
+               timeit(lambda: ops.head_rmsnorm_bwd_(dqkv, pre, rstd, wq, wk, gq, gk, a.hq, a.hkv, a.d), a.iters, a.warmup, flush),
+               bytes_=3.0 * T * nh * a.d * 2)
+    def op_geglu():
+        T, F = a.tokens, 14336
+        gu, da = bf(T, 2 * F), bf(T, F)
+        report(f"geglu_fwd_{T}x{F}", timeit(lambda: ops.swiglu(gu, "gelu_tanh"), a.iters, a.warmup, flush), bytes_=3.0 * T * F * 2)
+        report(f"geglu_bwd_{T}x{F}", timeit(lambda: ops.swiglu_bwd(da, gu, "gelu_tanh"), a.iters, a.warmup, flush), bytes_=5.0 * T * F * 2)
+        x = bf(T, F)
+        report(f"gelu_fwd_{T}x{F}", timeit(lambda: ops.gelu(x), a.iters, a.warmup, flush), bytes_=2.0 * T * F * 2)
+        report(f"gelu_bwd_{T}x{F}", timeit(lambda: ops.gelu_bwd(da, x), a.iters, a.warmup, flush), bytes_=3.0 * T * F * 2)
+    for name, fn in (("layernorm", op_layernorm), ("head_rmsnorm", op_head_rmsnorm), ("geglu", op_geglu)):
+        if a.op in (name, "families"):   # kernels of the model families beyond the Llama block; not part of --op all
+            torch.cuda.empty_cache()
+            fn()
     for name, fn in (("rmsnorm", op_rmsnorm), ("swiglu", op_swiglu), ("rope", op_rope), ("ce", op_ce), ("linear_ce", op_linear_ce),
                      ("embedding", op_embedding), ("adamw", op_adamw)):
         if want(name):
