@@ -50,6 +50,8 @@ def main(
     balance_by: str = Option("cost", help="cost | tokens: what the LPT packer balances across ranks (same global batch either way)"),
     osft: bool = Option(False, help="Orthogonal-subspace fine-tuning of the attention/MLP projections"),
     osft_rank_ratio: float = Option(0.5, help="Fraction of each projection's singular directions that is frozen"),
+    engine: str = Option("auto", help="auto | native | torch: the sm_100a kernels (default on a GPU) or the plain PyTorch ops "
+                                      "(the CPU oracle; on a GPU a slow cross-check of the kernels)"),
     no_dropout: bool = Option(False, help="Train a model whose config sets a dropout probability without dropout "
                                           "(dropout is not implemented; such a model is refused otherwise)"),
     save_train_state: bool = Option(False, help="With every exported checkpoint also write the sharded training state "
@@ -90,7 +92,8 @@ def main(
     model = setup_model(model_name_or_path=model_name_or_path, use_liger_kernels=use_liger_kernels, device=device,
                         comm_backend=comm_backend, state_dtype=sd, seed=seed, max_tokens_per_gpu=max_tokens_per_gpu,
                         optim=OptimConfig(max_grad_norm=max_grad_norm, weight_decay=weight_decay, beta1=adam_beta1,
-                                          beta2=adam_beta2, eps=adam_eps), no_dropout=no_dropout)
+                                          beta2=adam_beta2, eps=adam_eps), no_dropout=no_dropout,
+                        ops_kind=engine)
     if osft:
         from ..parallel.osft import enable_osft
         enable_osft(model, rank_ratio=osft_rank_ratio)
