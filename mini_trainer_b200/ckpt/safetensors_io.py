@@ -26,8 +26,8 @@ _FROM = {v: k for k, v in _DTYPES.items()}
 
 
 def _raw_bytes(t: torch.Tensor) -> memoryview:
-    t = t.detach().contiguous().cpu()
-    return memoryview(t.view(torch.uint8).numpy().reshape(-1)) if t.numel() else memoryview(b"")
+    t = t.detach().contiguous().cpu().reshape(-1)   # flat first: a 0-dim tensor has no last dimension to reinterpret
+    return memoryview(t.view(torch.uint8).numpy()) if t.numel() else memoryview(b"")
 
 
 def save_file(tensors: dict, path: str, metadata: dict | None = None) -> None:
@@ -73,6 +73,8 @@ class SafeTensorsFile:
         e = self.header[name]
         a, b = e["data_offsets"]
         dt = _FROM[e["dtype"]]
+        if b == a:   # an empty tensor has no bytes to reinterpret
+            return torch.empty(e["shape"], dtype=dt)
         buf = np.frombuffer(self._mm, dtype=np.uint8, count=b - a, offset=self.base + a).copy()
         return torch.from_numpy(buf).view(dt).reshape(e["shape"])
 

@@ -99,3 +99,40 @@ def test_train_state_resume(tmp_path):
         assert False, "corrupt shard must raise"
     except (RuntimeError, ValueError):
         pass
+
+
+def test_property_safetensors_roundtrip_with_upstream(tmp_path_factory):
+    """Any mix of dtypes and shapes (scalars, empty tensors, non-contiguous views): what this writer stores the upstream
+    package reads back bit for bit, and the other way round."""
+    import pytest
+    pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as hs
+    from safetensors.torch import load_file, save_file
+    dtypes = [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int64, torch.int32, torch.int16, torch.int8,
+              torch.uint8, torch.bool]
+    spec = hs.lists(hs.tuples(hs.sampled_from(range(len(dtypes))), hs.lists(hs.integers(0, 7), min_size=0, max_size=3),
+                              hs.booleans()), min_size=1, max_size=8)
+    root = tmp_path_factory.mktemp("st")
+
+    @settings(max_examples=60, deadline=None)
+    @given(spec=spec, seed=hs.integers(0, 10 ** 6))
+    def run(spec, seed):
+        g = torch.Generator().manual_seed(seed)
+        tensors = {}
+        for i, (d, shape, transpose) in enumerate(spec):
+            r = torch.randn(tuple(shape), generator=g)
+            t = (r * 50).to(dtypes[d]) if dtypes[d] != torch.bool else r > 0
+            if transpose and t.dim() >= 2:
+                t = t.transpose(0, 1)   # a non-contiguous view
+            tensors[f"t{i}.weight"] = t
+        st.save_file(tensors, str(root / "mine.safetensors"), metadata={"format": "pt"})
+        up = load_file(str(root / "mine.safetensors"))
+        save_file({k: v.contiguous() for k, v in tensors.items()}, str(root / "up.safetensors"))
+        mine = st.load_file(str(root / "up.safetensors"))
+        for k, t in tensors.items():
+            for other in (up[k], mine[k]):
+                assert other.dtype == t.dtype and other.shape == t.shape
+                if t.numel():   # bit for bit (NaN-safe): compare the raw bytes
+                    assert torch.equal(other.contiguous().reshape(-1).view(torch.uint8), t.contiguous().reshape(-1).view(torch.uint8))
+
+    run()

@@ -75,3 +75,57 @@ def test_loader_two_ranks_see_same_batches():
         assert sum(m["num_samples"] for m in b0 + b1) == bs
         for m in b0 + b1:
             assert m["input_ids"].shape[1] <= mt
+
+
+# ---------------------------------------------------------------------------------------------
+# property-based: the collator over any batch and any world size
+# ---------------------------------------------------------------------------------------------
+import pytest  # noqa: E402
+
+hypothesis = pytest.importorskip("hypothesis")
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+
+def _sample(n, masked, seed):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, 1000, (n,), generator=g)
+    labels = ids.clone()
+    labels[:masked] = -100
+    return {"input_ids": ids, "labels": labels, "len": n, "num_loss_counted_tokens": n - masked}
+
+
+@settings(max_examples=60, deadline=None)
+@given(lens=st.lists(st.integers(min_value=2, max_value=600), min_size=1, max_size=40), world=st.integers(min_value=1, max_value=6),
+       budget=st.integers(min_value=50, max_value=2000), frac=st.floats(min_value=0.0, max_value=0.95))
+def test_property_collator_partitions_the_batch_and_builds_consistent_minibatches(lens, world, budget, frac):
+    """Over all ranks every sample appears once with its tokens and labels intact; every minibatch is one padding-free
+    row whose position ids restart per sample and whose cu_seqlens, max_seqlen and token counts agree with it; every
+    rank has the same number of minibatches; idle slots hold the dummy sample; the batch-wide loss-token count is the
+    same everywhere; the targets are the labels shifted over the whole packed row, as the reference's models compute
+    them (the last position of a sample gets the next sample's first label, which tokenised chat data always masks)."""
+    batch = [_sample(n, min(n - 1, int(n * frac)), i) for i, n in enumerate(lens)]
+    outs = [MaxTokensPerRankCollator(budget, rank=r, world_size=world)(batch) for r in range(world)]
+    assert len({len(o) for o in outs}) == 1
+    total = sum(s["num_loss_counted_tokens"] for s in batch)
+    seen = []
+    for o in outs:
+        for mb in o:
+            ids, labels, pos = mb["input_ids"][0], mb["labels"][0], mb["position_ids"][0]
+            cu = mb["cu_seqlens"].tolist()
+            assert mb["batch_num_loss_counted_tokens"] == total and cu[0] == 0 and cu[-1] == ids.numel()
+            assert mb["max_seqlen"] == max(b - a for a, b in zip(cu[:-1], cu[1:]))
+            if mb["num_samples"] == 0:   # the dummy sample of an idle rank
+                assert (labels == -100).all() and mb["num_loss_counted_tokens"] == 0
+                continue
+            assert mb["num_samples"] == len(cu) - 1
+            assert ids.numel() <= budget or mb["num_samples"] == 1
+            assert mb["num_loss_counted_tokens"] == int((labels != -100).sum())
+            targets = make_packed_batch(mb, "cpu").targets
+            for a, b in zip(cu[:-1], cu[1:]):
+                assert pos[a:b].tolist() == list(range(b - a))
+                assert targets[a:b - 1].tolist() == labels[a + 1:b].tolist()
+                assert targets[b - 1] == (labels[b] if b < ids.numel() else -100)
+                seen.append((tuple(ids[a:b].tolist()), tuple(labels[a:b].tolist())))
+            assert targets[-1] == -100
+    want = sorted((tuple(s["input_ids"].tolist()), tuple(s["labels"].tolist())) for s in batch)
+    assert sorted(seen) == want

@@ -150,3 +150,51 @@ def test_cost_aware_packing_balances_compute_not_tokens():
     assert step_cost(cst) <= step_cost(tok)
     ideal = sum(cost(l) for l in lengths) / 8
     assert step_cost(cst) < 1.05 * ideal or step_cost(cst) < 0.97 * step_cost(tok)
+
+
+# ---------------------------------------------------------------------------------------------
+# property-based: any batch, any budget, any world size
+# ---------------------------------------------------------------------------------------------
+hypothesis = pytest.importorskip("hypothesis")
+from hypothesis import given, settings, strategies as st   # noqa: E402
+
+_batches = st.lists(st.integers(min_value=1, max_value=70000), min_size=1, max_size=120)
+
+
+@settings(max_examples=120, deadline=None)
+@given(lengths=_batches, max_tokens=st.integers(min_value=1, max_value=70000), ranks=st.integers(min_value=1, max_value=9),
+       cost_len=st.sampled_from([None, 500.0, 8000.0, 1e9]))
+def test_property_every_schedule_is_a_partition_within_budget(lengths, max_tokens, ranks, cost_len):
+    """Every sample exactly once, every rank the same number of minibatches, the token budget only exceeded by a sample
+    that is alone, padding minibatches are exactly ``[-1]``: for the token-balancing and the cost-balancing LPT packer
+    and the greedy one, whatever the input (ties, samples above the budget, more ranks than samples)."""
+    check_invariants(lengths, max_tokens, ranks, P.lpt_pack_all(lengths, max_tokens, ranks, cost_len=cost_len))
+    if cost_len is None:
+        check_invariants(lengths, max_tokens, ranks, all_ranks(P.batch_lengths_to_minibatches, lengths, max_tokens, ranks))
+
+
+@settings(max_examples=80, deadline=None)
+@given(lengths=_batches, max_tokens=st.integers(min_value=1, max_value=70000), ranks=st.integers(min_value=1, max_value=9),
+       cost_len=st.sampled_from([None, 2000.0]))
+def test_property_compiled_packer_equals_python_oracle(lengths, max_tokens, ranks, cost_len):
+    if not P.native_available():
+        pytest.skip("host library not built")
+    assert P.lpt_pack_all(lengths, max_tokens, ranks, cost_len=cost_len, use_native=True) == \
+        P.lpt_pack_all(lengths, max_tokens, ranks, cost_len=cost_len, use_native=False)
+    for r in range(ranks):
+        assert P.batch_lengths_to_minibatches(lengths, max_tokens, ranks, r, use_native=True) == \
+            P.batch_lengths_to_minibatches(lengths, max_tokens, ranks, r, use_native=False)
+
+
+@settings(max_examples=60, deadline=None)
+@given(lengths=_batches, ranks=st.integers(min_value=1, max_value=8))
+def test_property_lpt_never_needs_more_minibatches_than_samples_and_is_order_invariant(lengths, ranks):
+    """The schedule depends on the multiset of lengths, not on the order of the batch (stable ties aside: compare loads)."""
+    budget = max(lengths)
+    a = P.lpt_pack_all(lengths, budget, ranks)
+    b = P.lpt_pack_all(list(reversed(lengths)), budget, ranks)
+    assert len(a[0]) == len(b[0]) <= len(lengths)
+    rev = list(reversed(lengths))
+    loads_a = sorted(sum(lengths[i] for i in mb if i != -1) for r in a for mb in r)
+    loads_b = sorted(sum(rev[i] for i in mb if i != -1) for r in b for mb in r)
+    assert loads_a == loads_b
