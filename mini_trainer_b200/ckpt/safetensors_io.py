@@ -78,6 +78,18 @@ class SafeTensorsFile:
         buf = np.frombuffer(self._mm, dtype=np.uint8, count=b - a, offset=self.base + a).copy()
         return torch.from_numpy(buf).view(dt).reshape(e["shape"])
 
+    def get_slice(self, name: str, lo: int, hi: int) -> torch.Tensor:
+        """Elements [lo, hi) of a stored tensor taken as flat, reading only those bytes."""
+        e = self.header[name]
+        a, b = e["data_offsets"]
+        dt = _FROM[e["dtype"]]
+        es = torch.empty(0, dtype=dt).element_size()
+        lo, hi = max(0, lo), min(hi, (b - a) // es)
+        if hi <= lo:
+            return torch.empty(0, dtype=dt)
+        buf = np.frombuffer(self._mm, dtype=np.uint8, count=(hi - lo) * es, offset=self.base + a + lo * es).copy()
+        return torch.from_numpy(buf).view(dt)
+
     def close(self) -> None:
         self._mm.close()
         self._f.close()

@@ -6,8 +6,8 @@ AdamW moments for every group (plus the OSFT factors it owns, when that mode is 
 ``state.json``: optimizer step, world size and whatever the training loop passes in ``extra``
 (scheduler state, optimizer steps taken, global batches consumed, samples seen, samples at the
 last export). A state written by another number of ranks is re-sliced on load (every group is one flat
-buffer cut into equal slices, so a rank reads the parts of the old slices that overlap its new one);
-only the OSFT factors, which are owned by matrix, need the world size they were written with.
+buffer cut into equal slices, so a rank reads the parts of the old slices that overlap its new one;
+OSFT factors are owned by matrix, so a rank fetches each matrix it owns now from the rank that owned it then).
 ``trainer.train`` writes one next to every
 exported checkpoint when ``save_train_state`` is on, and ``train.py --resume-from`` restores it
 and continues the data stream where it stopped.
@@ -54,7 +54,7 @@ def _flat_slice(files: list, key: str, lo: int, hi: int) -> torch.Tensor:
         a, b = max(lo, r * s_old), min(hi, (r + 1) * s_old)
         if a >= b:
             continue
-        part = f.get_tensor(key)[a - r * s_old: b - r * s_old]
+        part = f.get_slice(key, a - r * s_old, b - r * s_old)
         if out is None:
             out = torch.zeros(hi - lo, dtype=part.dtype)
         out[a - lo: b - lo] = part
@@ -66,9 +66,6 @@ def load_train_state(engine, directory: str) -> dict:
         meta = json.load(f)
     old_world = int(meta["world"])
     osft = getattr(engine, "osft", None)
-    if old_world != engine.world and osft is not None:
-        raise ValueError(f"training state with OSFT factors was saved by {old_world} ranks, now {engine.world}: the factors "
-                         "are owned by matrix and are not re-sliced; resume with the same number of ranks")
     ranks = [engine.rank] if old_world == engine.world else list(range(old_world))
     files = []
     try:
@@ -96,8 +93,10 @@ def load_train_state(engine, directory: str) -> dict:
                 dst.copy_(src.to(dst.dtype))
             g.shard.copy_(g.master.to(g.shard.dtype))
             g.has_grad = False
-        if osft is not None:
+        if osft is not None and old_world == engine.world:
             osft.load_state_tensors({k: files[0].get_tensor(k) for k in files[0].keys() if k.startswith("osft.")})
+        elif osft is not None:   # every matrix this rank owns now is fetched from the rank that owned it then
+            osft.load_state_from(files, old_world)
     finally:
         for f in files:
             f.close()

@@ -132,6 +132,15 @@ def main(
     train(model, optimizer, sched, loader, output_dir, min_samples_per_checkpoint, model_name_or_path,
           max_steps=max_steps, max_shard_bytes=int(max_shard_gb * 1e9), save_train_state=save_train_state,
           resume_state=resume_state)
+    # Leave together: a rank that exits while a peer is still inside its last collective (or tearing down its
+    # connections) makes that peer abort, and the launcher then reports a finished run as failed.
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        if device.type == "cuda":
+            import torch
+            torch.cuda.synchronize(device)
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -258,7 +258,10 @@ class PackedBatchLoader:
                     raise item
                 yield item
         finally:
+            # the thread is joined, not left to the interpreter's shutdown: a daemon thread that is still inside a
+            # tensor operation when the runtime is torn down aborts the process after a finished run
             stop.set()
+            t.join(timeout=10)
 
 
 def get_data_loader(**kwargs):

@@ -442,6 +442,31 @@ class OSFT:
         if self.kernels:
             self.fac16.copy_(self.fac)
 
+    def _factor_layout(self, world: int) -> dict:
+        """``{matrix index: (owner, offset in the owner's flat factor buffers, elements)}`` for a run of ``world`` ranks
+        (round-robin ownership, offsets in matrix order, sizes rounded up to 8 elements: what ``_alloc_and_decompose`` does)."""
+        out, total = {}, [0] * world
+        for mt in self.mats:
+            n = mt.out * mt.k_lo + mt.k_lo + mt.k_lo * mt.cols
+            owner = mt.index % world
+            out[mt.index] = (owner, total[owner], n)
+            total[owner] += -(-n // 8) * 8
+        return out
+
+    def load_state_from(self, files: list, old_world: int) -> None:
+        """Factors and moments from a training state written by ``old_world`` ranks (``files``: one open reader per
+        old rank): every matrix this rank owns now is read from the flat buffers of the rank that owned it then."""
+        then = self._factor_layout(old_world)
+        for mt in self._mine():
+            owner, off, n = then[mt.index]
+            for key, dst in (("osft.factors", self.fac), ("osft.m", self.fac_m), ("osft.v", self.fac_v)):
+                src = files[owner].get_slice(key, off, off + n)
+                if src.numel() != n:
+                    raise RuntimeError(f"{key}: matrix {mt.index} not found in the state of rank {owner} of {old_world}")
+                dst[mt.fac_off: mt.fac_off + n].copy_(src.to(dst.dtype))
+        if self.kernels:
+            self.fac16.copy_(self.fac)
+
     # -- the optimizer step -----------------------------------------------------------------
     def _mask_targets(self, grp, block: int, tensor: torch.Tensor, value: float = 0.0) -> None:
         """Sets this rank's slice of every projection's region of ``tensor`` (a shard) to ``value``."""

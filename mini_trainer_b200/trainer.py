@@ -166,7 +166,8 @@ def train(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule, data_loader
     if max_steps is not None and step >= max_steps:
         metric_logger.close()
         return last
-    for batch in data_loader:
+    batches = iter(data_loader)
+    for batch in batches:
         batch_start = time.time()
         batch_totals.reset_batch()
         if device.type == "cuda":
@@ -231,5 +232,7 @@ def train(model: ShardedEngine, optimizer, lr_scheduler: LRSchedule, data_loader
                                    "last_saved_samples": last_saved_samples})
         if max_steps is not None and step >= max_steps:
             break
+    if hasattr(batches, "close"):   # stops and joins the packing thread: it must not be mid-batch when the process exits
+        batches.close()
     metric_logger.close()
     return last

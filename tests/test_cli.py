@@ -64,7 +64,7 @@ def test_smoke_run_two_gloo_ranks():
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_PORT"):
         env.pop(k, None)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", "29657", "-m", "mini_trainer_b200.cli.smoke_run", "--num-steps", "2", "--sequence-length", "32"]
+           "--master-port", str(_free_port()), "-m", "mini_trainer_b200.cli.smoke_run", "--num-steps", "2", "--sequence-length", "32"]
     proc = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
     assert "smoke run ok" in proc.stdout
@@ -72,8 +72,14 @@ def test_smoke_run_two_gloo_ranks():
     assert [r["step"] for r in recs] == [1, 2] and recs[1]["loss"] < recs[0]["loss"]
 
 
-def _train_cli(out, extra, port):
-    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT=str(port))
+def _free_port():
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
+    return p
+
+
+def _train_cli(out, extra, port=None):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT=str(_free_port()))   # a fresh port per launch
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
         env.pop(k, None)
     cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:tiny-qwen2",
@@ -110,7 +116,8 @@ def test_resume_continues_weights_optimizer_schedule_and_data(tmp_path):
     assert set(wa) == set(wb) and all(torch.equal(wa[k], wb[k]) for k in wa)
 
 
-def _train_cli_ranks(out, extra, port, world=2):
+def _train_cli_ranks(out, extra, port=None, world=2):
+    port = _free_port()
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_PORT"):
         env.pop(k, None)
@@ -148,20 +155,25 @@ def test_resume_two_ranks_with_osft(tmp_path):
     assert set(wa) == set(wb) and all(torch.equal(wa[k], wb[k]) for k in wa)
 
 
-def test_resume_on_another_number_of_ranks(tmp_path):
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("osft", [False, True])
+def test_resume_on_another_number_of_ranks(tmp_path, osft):
     """A training state written by two ranks continues on one rank and on three: every group's flat buffer is re-sliced
-    on load, the data stream and the schedule go on where they stopped, and the run matches an uninterrupted one to
-    the precision the different reduction orders allow."""
+    on load (OSFT factors follow their matrices to the new owners), the data stream and the schedule go on where they
+    stopped, and the run matches an uninterrupted one to the precision the different reduction orders allow."""
     import torch
     from mini_trainer_b200.ckpt import safetensors_io as st
     a, b, c = str(tmp_path / "straight"), str(tmp_path / "two_then_one"), str(tmp_path / "two_then_three")
-    common = ["--min-samples-per-checkpoint", "16"]
-    _train_cli(a, ["--max-steps", "4"] + common, 29671)
-    for out, port in ((b, 29672), (c, 29673)):
-        _train_cli_ranks(out, ["--max-steps", "2"] + common, port, world=2)
+    common = ["--min-samples-per-checkpoint", "16"] + (["--osft"] if osft else [])
+    port = lambda: None   # the launch helpers take a fresh port each time
+    _train_cli(a, ["--max-steps", "4"] + common, port())
+    for out in (b, c):
+        _train_cli_ranks(out, ["--max-steps", "2"] + common, port(), world=2)
     state_b, state_c = (os.path.join(d, "train_state", "samples_16.0") for d in (b, c))
-    _train_cli(b, ["--max-steps", "4", "--resume-from", state_b] + common, 29674)
-    _train_cli_ranks(c, ["--max-steps", "4", "--resume-from", state_c] + common, 29675, world=3)
+    _train_cli(b, ["--max-steps", "4", "--resume-from", state_b] + common, port())
+    _train_cli_ranks(c, ["--max-steps", "4", "--resume-from", state_c] + common, port(), world=3)
     rows_a = [json.loads(l) for l in open(os.path.join(a, "training_metrics_0.jsonl"))]
     wa = st.load_file(os.path.join(a, "hf_format", "samples_32.0", "model.safetensors"))
     for d in (b, c):
