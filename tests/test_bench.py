@@ -38,7 +38,9 @@ def test_guard_cuts_steps_when_warmup_was_slow():
     assert bench.guard_steps(20, warmup_wall_s=300.0, warmup=3, budget_s=0.0) == 1
 
 
-def _run(nproc, extra, port):
+def _run(nproc, extra, port=None):
+    import socket
+    sk = socket.socket(); sk.bind(("127.0.0.1", 0)); port = sk.getsockname()[1]; sk.close()   # a fresh port per launch
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT=str(port), MASTER_ADDR="127.0.0.1")
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
         env.pop(k, None)

@@ -7,9 +7,15 @@ import sys
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _free_port():
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
+    return p
+
+
 def test_train_cli_runs_and_writes_reference_layout(tmp_path):
     out = str(tmp_path / "run")
-    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT="29641")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT=str(_free_port()))
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
         env.pop(k, None)
     cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:tiny-qwen2",
@@ -32,7 +38,7 @@ def test_train_cli_runs_and_writes_reference_layout(tmp_path):
 
 def test_bench_reference_arm_reports_unavailable_without_a_gpu():
     """Without CUDA the reference arm cannot run; the contract is one JSON line and exit code 0."""
-    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT="29643")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT=str(_free_port()))
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
         env.pop(k, None)
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
@@ -44,7 +50,7 @@ def test_bench_reference_arm_reports_unavailable_without_a_gpu():
 
 def test_train_cli_synthetic_spec_caps_sample_length(tmp_path):
     out = str(tmp_path / "run")
-    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT="29644")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT=str(_free_port()))
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
         env.pop(k, None)
     cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:tiny-qwen2",
@@ -70,12 +76,6 @@ def test_smoke_run_two_gloo_ranks():
     assert "smoke run ok" in proc.stdout
     recs = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
     assert [r["step"] for r in recs] == [1, 2] and recs[1]["loss"] < recs[0]["loss"]
-
-
-def _free_port():
-    import socket
-    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
-    return p
 
 
 def _train_cli(out, extra, port=None):
