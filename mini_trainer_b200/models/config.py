@@ -390,6 +390,9 @@ PRESETS = {
                                         hidden_size=256, intermediate_size=384, num_hidden_layers=2, num_attention_heads=2,
                                         num_key_value_heads=1, rope_theta=1e6, rms_norm_eps=1e-5, num_local_experts=4,
                                         num_experts_per_tok=2),
+    # the smallest useful Llama: command-line and resume tests on CPU
+    "nano-llama": lambda: _llama(vocab_size=2048, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                                 num_attention_heads=4, num_key_value_heads=2, rope_theta=1e4, rms_norm_eps=1e-5),
     # a small Llama used by GPU smoke tests (head_dim 128, GQA 4:1)
     "smoke-llama": lambda: _llama(vocab_size=4096, hidden_size=512, intermediate_size=1536, num_hidden_layers=2,
                                   num_attention_heads=4, num_key_value_heads=1, rope_theta=5e5, rms_norm_eps=1e-5),

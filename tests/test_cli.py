@@ -82,7 +82,7 @@ def _train_cli(out, extra, port=None):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_PORT=str(_free_port()))   # a fresh port per launch
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
         env.pop(k, None)
-    cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:tiny-qwen2",
+    cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:nano-llama",
            "--data-path", "synthetic:tiny-qwen2:40:200", "--batch-size", "8", "--max-tokens-per-gpu", "1024",
            "--output-dir", out, "--learning-rate", "1e-3", "--num-warmup-steps", "3", "--seed", "893",
            "--logging-level", "WARNING", "--save-train-state"] + extra
@@ -122,7 +122,7 @@ def _train_cli_ranks(out, extra, port=None, world=2):
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_PORT"):
         env.pop(k, None)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
-           "--master-port", str(port), os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:tiny-qwen2",
+           "--master-port", str(port), os.path.join(ROOT, "train.py"), "--model-name-or-path", "random:nano-llama",
            "--data-path", "synthetic:tiny-qwen2:40:200", "--batch-size", "8", "--max-tokens-per-gpu", "1024",
            "--output-dir", out, "--learning-rate", "1e-3", "--num-warmup-steps", "3", "--seed", "893",
            "--logging-level", "WARNING", "--save-train-state"] + extra
