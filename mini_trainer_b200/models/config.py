@@ -66,6 +66,8 @@ class ModelConfig:
     # a constant that is first rounded to the embedding's dtype (55.4256 becomes 55.5 in bf16)
     norm_weight_offset: float = 0.0
     embedding_multiplier_in_param_dtype: bool = False
+    # SmolLM3 (modeling_smollm3.py): layers whose entry is 0 apply no rotary embedding (NoPE); None = every layer rotates
+    no_rope_layers: Optional[list] = None
     # Qwen3 (modeling_qwen3.py): RMSNorm over head_dim on every q and k head before the rotary embedding
     qk_norm: bool = False
     # Qwen3-MoE (modeling_qwen3_moe.py): experts of their own width, optional renormalisation of the chosen weights,
@@ -97,6 +99,7 @@ class ModelConfig:
         kernels here are full causal: the engine accepts such a model and refuses a minibatch that holds a longer sample."""
         if self.sliding_window is None or self.sliding_window >= self.max_position_embeddings:
             return None
+        # (SmolLM3 windows only its NoPE layers; treating the window as model-wide is the stricter reading)
         on = self.use_sliding_window if self.use_sliding_window is not None else \
             self.model_type in ("mistral", "mixtral", "phi3", "starcoder2")
         return int(self.sliding_window) if on else None
@@ -108,6 +111,9 @@ class ModelConfig:
             import torch
             m = float(torch.tensor(m, dtype=dtype))
         return m
+
+    def layer_uses_rope(self, layer: int) -> bool:
+        return self.no_rope_layers is None or bool(self.no_rope_layers[layer])
 
     @property
     def mlp_act(self) -> str:
@@ -132,6 +138,8 @@ class ModelConfig:
         """Raises ``ValueError`` when the hand-written block would not compute this model's function."""
         arch = (self.architectures or ["?"])[0]
         problems = []
+        if self.no_rope_layers is not None and len(self.no_rope_layers) != self.num_hidden_layers:
+            problems.append(f"no_rope_layers has {len(self.no_rope_layers)} entries for {self.num_hidden_layers} layers")
         if self.is_moe:
             if self.output_router_logits:
                 problems.append("output_router_logits=true adds the router's load-balancing loss, which is not implemented")
@@ -260,7 +268,7 @@ class ModelConfig:
               "pad_token_id", "bos_token_id", "eos_token_id", "embedding_multiplier", "residual_multiplier",
               "attention_multiplier", "logits_scaling", "sliding_window", "use_sliding_window", "mlp_bias", "hidden_act",
               "num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise",
-              "moe_intermediate_size", "norm_topk_prob")
+              "moe_intermediate_size", "norm_topk_prob", "no_rope_layers")
     _MOE_ONLY = ("num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise",
                  "moe_intermediate_size", "norm_topk_prob")
     _GRANITE_ONLY = ("embedding_multiplier", "residual_multiplier", "attention_multiplier", "logits_scaling")
@@ -290,6 +298,9 @@ class ModelConfig:
             # renormalised over the chosen ones: the same weights as Mixtral's
             kw.pop("moe_intermediate_size", None)
             kw["norm_topk_prob"] = True
+        if kw.get("model_type") == "smollm3" and kw.get("no_rope_layers") is None:   # the config class's default rule
+            step = int(d.get("no_rope_layer_interval", 4))
+            kw["no_rope_layers"] = [int((i + 1) % step != 0) for i in range(int(kw["num_hidden_layers"]))]
         if kw.get("model_type") == "starcoder2":
             use_bias = bool(d.pop("use_bias", True))
             kw.update(norm_type="layernorm", mlp_gated=False, attention_bias=use_bias, mlp_bias=use_bias,
@@ -319,6 +330,8 @@ class ModelConfig:
         extra = d.pop("extra")
         for k in ("qk_norm", "norm_weight_offset", "embedding_multiplier_in_param_dtype", "norm_type", "mlp_gated", "ignore_dropout"):
             d.pop(k)   # implied by the model type, not keys of any Hugging Face config
+        if d["no_rope_layers"] is None:
+            d.pop("no_rope_layers")
         if self.model_type == "starcoder2":   # back to its own spelling
             d["norm_epsilon"], d["use_bias"] = d.pop("rms_norm_eps"), d.pop("attention_bias")
             d["mlp_bias"] = False
@@ -356,7 +369,7 @@ class ModelConfig:
 
 SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
                            "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM", "GemmaForCausalLM",
-                           "Starcoder2ForCausalLM", "Qwen3MoeForCausalLM", "GraniteMoeForCausalLM")
+                           "Starcoder2ForCausalLM", "Qwen3MoeForCausalLM", "GraniteMoeForCausalLM", "SmolLM3ForCausalLM")
 
 
 def _llama(**kw):

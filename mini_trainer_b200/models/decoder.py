@@ -140,7 +140,8 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
         qk_pre = qkv[:, : cfg.q_size + cfg.kv_size].clone()
         rstd_qk = ops.head_rmsnorm_(qkv, p["qn"], p["kn"], cfg.rms_norm_eps, cfg.num_attention_heads,
                                     cfg.num_key_value_heads, cfg.head_dim)
-    ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+    if inv_freq is not None:   # None: a layer without positional rotation (SmolLM3's NoPE layers)
+        ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
     rm = cfg.residual_multiplier   # Granite scales every branch output before the residual add (1.0 elsewhere)
     # the GEMM epilogue computes alpha * product + bias + residual; the models scale (product + bias)
     bo, bd = p.get("bo"), p.get("bd")
@@ -234,8 +235,9 @@ def _attention_backward(ops, cfg: ModelConfig, p: dict, g: dict, a: BlockActs, d
                              batch.max_seqlen, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                              scale=cfg.attention_scale)
     del dattn
-    ops.rope_(dqkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
-              inverse=True)
+    if inv_freq is not None:
+        ops.rope_(dqkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                  inverse=True)
     if cfg.qk_norm:
         ops.head_rmsnorm_bwd_(dqkv, a.qk_pre, a.rstd_qk, p["qn"], p["kn"], g["qn"], g["kn"], cfg.num_attention_heads,
                               cfg.num_key_value_heads, cfg.head_dim)
@@ -286,7 +288,7 @@ def forward_logits(ops, cfg: ModelConfig, embed_w, blocks: list, norm_w, lm_w, b
     x = ops.embedding(embed_w, batch.input_ids)
     if cfg.embedding_multiplier != 1.0:
         x = x * cfg.embed_scale(x.dtype)
-    for p in blocks:
-        x, _, _ = block_forward(ops, cfg, p, x, batch, inv_freq)
+    for i, p in enumerate(blocks):
+        x, _, _ = block_forward(ops, cfg, p, x, batch, inv_freq if cfg.layer_uses_rope(i) else None)
     n, _ = _norm(ops, cfg, x, {"norm": norm_w, "bnorm": norm_b}, "norm", "bnorm")
     return (n.float() @ lm_w.float().t()) / cfg.logits_scaling

@@ -52,7 +52,8 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
         if cfg.qk_norm:
             q = _rms(q, sd[p + "self_attn.q_norm.weight"], cfg.rms_norm_eps)
             k = _rms(k, sd[p + "self_attn.k_norm.weight"], cfg.rms_norm_eps)
-        q, k = _rope(q, position_ids, inv_freq), _rope(k, position_ids, inv_freq)
+        if cfg.layer_uses_rope(i):
+            q, k = _rope(q, position_ids, inv_freq), _rope(k, position_ids, inv_freq)
         outs = []
         for a, b in zip(starts[:-1], starts[1:]):
             o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1)[None], k[a:b].transpose(0, 1)[None],

@@ -188,6 +188,10 @@ class ShardedEngine:
         # was never written) shows up as NaN in the loss / norm instead of as a plausible stale value.
         self.poison = os.environ.get("MTB200_POISON", "0") == "1" and self.param_dtype != torch.int8
 
+    def _inv_freq(self, layer: int):
+        """Rotary frequencies of a layer, or ``None`` where the model applies no positional rotation."""
+        return self.inv_freq if self.cfg.layer_uses_rope(layer) else None
+
     # ------------------------------------------------------------------------------------
     # initialisation / state exchange
     # ------------------------------------------------------------------------------------
@@ -569,11 +573,11 @@ class ShardedEngine:
                 self._prefetch_input(i - 1, saved[i - 1][0])
             if acts is None:   # recompute the block forward (attention is skipped when its output was kept)
                 with nvtx.range(f"recompute/block{i}"):
-                    _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self.inv_freq, keep=True, saved_attn=attn_state,
+                    _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self._inv_freq(i), keep=True, saved_attn=attn_state,
                                                  need_out=False)
             notify, finish = self._region_reducer(i, gbuf, gslot, last)
             with nvtx.range(f"backward/block{i}"):
-                dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self.inv_freq, notify=notify)
+                dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self._inv_freq(i), notify=notify)
             del acts, xin, attn_state
             self._release_input()
             self._release_pbuf(slot)
@@ -689,7 +693,7 @@ class ShardedEngine:
                 head = self._gather_group(self.head, prefetch=True)
             xin = x
             with nvtx.range(f"forward/block{i}"):
-                x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self.inv_freq,
+                x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self._inv_freq(i),
                                                       keep="compact" if levels[i] == 0 else False, want_attn=levels[i] == 1)
             if levels[i] == 3:
                 xin = self._offload_input(i, xin)

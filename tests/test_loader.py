@@ -37,6 +37,7 @@ def _hf_dir(tmp_path, kind, **over):
            "granitemoe": (transformers.GraniteMoeConfig, {"num_local_experts": 4, "num_experts_per_tok": 2,
                                                          "embedding_multiplier": 12.0, "residual_multiplier": 0.22,
                                                          "attention_multiplier": 0.0625, "logits_scaling": 8.0}),
+           "smollm3": (transformers.SmolLM3Config, {"num_hidden_layers": 4, "no_rope_layer_interval": 2, "pad_token_id": 0}),
            "starcoder2": (transformers.Starcoder2Config, {"sliding_window": None, "bos_token_id": 1, "eos_token_id": 2})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
@@ -57,7 +58,7 @@ def _our_logits(eng, ids):
     return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb, norm_b=head.get("bnorm"))
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2", "qwen3_moe", "granitemoe"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2", "qwen3_moe", "granitemoe", "smollm3"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -243,6 +244,25 @@ def test_starcoder2_gradients_and_export_against_transformers(tmp_path):
     with torch.no_grad():
         again = back(input_ids=ids[None]).logits[0]
     assert torch.allclose(again, ref, atol=0.08, rtol=0.05)   # the export is bf16
+
+
+def test_smollm3_layers_without_rotary_embedding(tmp_path):
+    """SmolLM3: every second layer of this tiny model applies no rotary embedding; gradients of a rotated and of a
+    not rotated layer against autograd through transformers."""
+    path, hf = _hf_dir(tmp_path, "smollm3")
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.no_rope_layers == [1, 0, 1, 0] and not eng.cfg.layer_uses_rope(1)
+    ids = torch.randint(0, COMMON["vocab_size"], (20,))
+    mb = mb_collate_fn([{"input_ids": ids, "labels": ids, "len": 20, "num_loss_counted_tokens": 20}], 20)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 19, last=True)
+    out = hf(input_ids=ids[None], labels=ids[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 19 - float(out.loss)) < 1e-4
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    q = eng.cfg.q_size
+    for layer in (0, 1):
+        got = eng.blocks[layer].layout.views(eng.blocks[layer].gacc)
+        assert torch.allclose(got["wqkv"][:q], want[f"model.layers.{layer}.self_attn.q_proj.weight"], atol=1e-5, rtol=1e-3)
 
 
 def test_phi3_export_keeps_the_fused_tensor_names(tmp_path):
