@@ -88,8 +88,9 @@ class ModelConfig:
 
     @property
     def attention_scale(self) -> float:
-        """Scale applied to q.k before the softmax."""
-        return float(self.attention_multiplier) if self.attention_multiplier is not None else self.head_dim ** -0.5
+        """Scale applied to q.k before the softmax (with YaRN's factor on q and k folded in)."""
+        base = float(self.attention_multiplier) if self.attention_multiplier is not None else self.head_dim ** -0.5
+        return base * self.rope_attention_factor ** 2
 
     @property
     def attention_window(self) -> Optional[int]:
@@ -165,6 +166,10 @@ class ModelConfig:
         if self.hidden_act not in ("silu", "swish", "gelu_pytorch_tanh"):
             problems.append(f"hidden_act={self.hidden_act!r} (the gated MLP is implemented with SiLU and with the "
                             "tanh-approximated GELU)")
+        try:
+            self.rope_inv_freq()
+        except ValueError as e:   # e.g. Phi-3's "longrope" or "yarn": per-position frequency rescaling is not implemented
+            problems.append(str(e))
         if problems:
             raise ValueError("this model cannot be trained faithfully: " + "; ".join(problems))
 
@@ -257,9 +262,45 @@ class ModelConfig:
             smooth = (old / wavelen - lo) / (hi - lo)
             mid = (1 - smooth) * inv / factor + smooth * inv
             inv = torch.where(wavelen > old / lo, inv / factor, torch.where(wavelen < old / hi, inv, mid))
+        elif kind == "yarn":   # modeling_rope_utils._compute_yarn_parameters: interpolate low frequencies, keep high ones
+            factor = float(rs["factor"])
+            old = float(rs.get("original_max_position_embeddings") or self.max_position_embeddings)
+            fast, slow = float(rs.get("beta_fast") or 32), float(rs.get("beta_slow") or 1)
+
+            def corr_dim(rot):
+                return d * math.log(old / (rot * 2 * math.pi)) / (2 * math.log(self.rope_theta))
+
+            lo, hi = corr_dim(fast), corr_dim(slow)
+            if rs.get("truncate", True):
+                lo, hi = math.floor(lo), math.ceil(hi)
+            lo, hi = max(lo, 0), min(hi, d - 1)
+            if lo == hi:
+                hi += 0.001
+            ramp = ((torch.arange(d // 2, dtype=torch.float32) - lo) / (hi - lo)).clamp(0, 1)
+            pos = self.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d)
+            keep = 1 - ramp
+            inv = (1.0 / (factor * pos)) * (1 - keep) + (1.0 / pos) * keep
         else:
             raise ValueError(f"unsupported rope scaling {kind!r}")
         return inv.to(torch.float32)
+
+    @property
+    def rope_attention_factor(self) -> float:
+        """YaRN multiplies the rotary cosines and sines by this factor, i.e. q and k each, i.e. the scores by its square
+        (1.0 for every other kind of rope)."""
+        rs = self.rope_scaling or {}
+        if rs.get("rope_type", rs.get("type")) != "yarn":
+            return 1.0
+        if rs.get("attention_factor") is not None:
+            return float(rs["attention_factor"])
+        factor = float(rs["factor"])
+
+        def mscale(scale, m=1.0):
+            return 1.0 if scale <= 1 else 0.1 * m * math.log(scale) + 1.0
+
+        if rs.get("mscale") and rs.get("mscale_all_dim"):
+            return float(mscale(factor, rs["mscale"]) / mscale(factor, rs["mscale_all_dim"]))
+        return float(mscale(factor))
 
     # HF I/O -------------------------------------------------------------------------
     _KNOWN = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",

@@ -246,6 +246,26 @@ def test_starcoder2_gradients_and_export_against_transformers(tmp_path):
     assert torch.allclose(again, ref, atol=0.08, rtol=0.05)   # the export is bf16
 
 
+@pytest.mark.parametrize("rope", [
+    {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 128, "rope_theta": 10000.0},
+    {"rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 64, "rope_theta": 10000.0, "beta_fast": 16, "beta_slow": 2,
+     "attention_factor": 1.3},
+    {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 64,
+     "rope_theta": 10000.0},
+    {"rope_type": "linear", "factor": 2.0, "rope_theta": 10000.0},
+])
+def test_rope_scaling_kinds_match_transformers(tmp_path, rope):
+    """YaRN (frequencies and the attention factor on q and k), llama3 and linear scaling: logits of a 300-token sample,
+    long enough for the scaled frequencies to matter, against transformers."""
+    path, hf = _hf_dir(tmp_path, "llama", rope_parameters=rope)
+    eng = setup_model(path, device="cpu")
+    ids = torch.randint(0, COMMON["vocab_size"], (300,))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    mine = _our_logits(eng, ids)
+    assert torch.allclose(mine, ref, atol=5e-4, rtol=5e-4), float((mine - ref).abs().max())
+
+
 def test_smollm3_layers_without_rotary_embedding(tmp_path):
     """SmolLM3: every second layer of this tiny model applies no rotary embedding; gradients of a rotated and of a
     not rotated layer against autograd through transformers."""
@@ -439,6 +459,7 @@ def test_projection_biases_reach_logits_gradients_and_exports(tmp_path, kind):
     ("llama", {"attention_dropout": 0.1}, "attention_dropout"),
     ("phi3", {"resid_pdrop": 0.1}, "resid_pdrop"),
     ("starcoder2", {"residual_dropout": 0.1}, "residual_dropout"),
+    ("llama", {"rope_parameters": {"rope_type": "dynamic", "factor": 4.0, "rope_theta": 10000.0}}, "rope scaling"),
 ])
 def test_models_the_block_cannot_compute_are_refused(tmp_path, kind, over, needle):
     path, _ = _hf_dir(tmp_path, kind, **over)
