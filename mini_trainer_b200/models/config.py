@@ -88,7 +88,7 @@ class ModelConfig:
 
     @property
     def attention_scale(self) -> float:
-        """Scale applied to q.k before the softmax (with YaRN's factor on q and k folded in)."""
+        """Scale applied to q.k before the softmax (with YaRN's / longrope's factor on q and k folded in)."""
         base = float(self.attention_multiplier) if self.attention_multiplier is not None else self.head_dim ** -0.5
         return base * self.rope_attention_factor ** 2
 
@@ -243,8 +243,18 @@ class ModelConfig:
         return (gemm / gemm_rate) / (attn / attn_rate)
 
     # rotary ------------------------------------------------------------------------
-    def rope_inv_freq(self):
-        """fp32 inverse frequencies [head_dim/2], with ``linear`` and ``llama3`` scaling."""
+    def rope_long_context_threshold(self) -> Optional[int]:
+        """``longrope`` (Phi-3 128k) rescales the frequencies with one table up to this many tokens and with another
+        beyond; ``None`` for every other kind of rope."""
+        rs = self.rope_scaling or {}
+        if rs.get("rope_type", rs.get("type")) != "longrope":
+            return None
+        return int(rs.get("original_max_position_embeddings") or self.extra.get("original_max_position_embeddings")
+                   or self.max_position_embeddings)
+
+    def rope_inv_freq(self, seq_len: Optional[int] = None):
+        """fp32 inverse frequencies [head_dim/2], with ``linear``, ``llama3``, ``yarn`` and ``longrope`` scaling.
+        ``seq_len``: the longest sample of the minibatch (only ``longrope`` looks at it)."""
         import torch
         d = self.head_dim
         inv = 1.0 / (self.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float64) / d))
@@ -262,6 +272,12 @@ class ModelConfig:
             smooth = (old / wavelen - lo) / (hi - lo)
             mid = (1 - smooth) * inv / factor + smooth * inv
             inv = torch.where(wavelen > old / lo, inv / factor, torch.where(wavelen < old / hi, inv, mid))
+        elif kind == "longrope":   # modeling_rope_utils._compute_longrope_parameters: one divisor per frequency
+            long_ctx = seq_len is not None and seq_len > self.rope_long_context_threshold()
+            ext = torch.tensor(rs["long_factor"] if long_ctx else rs["short_factor"], dtype=torch.float64)
+            if ext.numel() != inv.numel():
+                raise ValueError(f"longrope factors have {ext.numel()} entries for {inv.numel()} frequencies")
+            inv = inv / ext
         elif kind == "yarn":   # modeling_rope_utils._compute_yarn_parameters: interpolate low frequencies, keep high ones
             factor = float(rs["factor"])
             old = float(rs.get("original_max_position_embeddings") or self.max_position_embeddings)
@@ -286,13 +302,18 @@ class ModelConfig:
 
     @property
     def rope_attention_factor(self) -> float:
-        """YaRN multiplies the rotary cosines and sines by this factor, i.e. q and k each, i.e. the scores by its square
-        (1.0 for every other kind of rope)."""
+        """YaRN and longrope multiply the rotary cosines and sines by this factor, i.e. q and k each, i.e. the scores by
+        its square (1.0 for every other kind of rope)."""
         rs = self.rope_scaling or {}
-        if rs.get("rope_type", rs.get("type")) != "yarn":
+        kind = rs.get("rope_type", rs.get("type"))
+        if kind not in ("yarn", "longrope"):
             return 1.0
         if rs.get("attention_factor") is not None:
             return float(rs["attention_factor"])
+        if kind == "longrope":
+            old = self.rope_long_context_threshold()
+            factor = float(rs.get("factor") or self.max_position_embeddings / old)
+            return 1.0 if factor <= 1.0 else math.sqrt(1 + math.log(factor) / math.log(old))
         factor = float(rs["factor"])
 
         def mscale(scale, m=1.0):

@@ -284,7 +284,7 @@ def head_forward_backward(ops, cfg: ModelConfig, head_p: dict, head_g: dict, lm_
 @torch.no_grad()
 def forward_logits(ops, cfg: ModelConfig, embed_w, blocks: list, norm_w, lm_w, batch: PackedBatch, norm_b=None) -> torch.Tensor:
     """Plain inference forward returning ``[T, V]`` logits (tests, checkpoint round-trips)."""
-    inv_freq = cfg.rope_inv_freq().to(embed_w.device)
+    inv_freq = cfg.rope_inv_freq(seq_len=batch.max_seqlen).to(embed_w.device)
     x = ops.embedding(embed_w, batch.input_ids)
     if cfg.embedding_multiplier != 1.0:
         x = x * cfg.embed_scale(x.dtype)

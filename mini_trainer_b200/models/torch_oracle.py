@@ -37,7 +37,7 @@ def _rope(x, pos, inv_freq):
 def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, position_ids, return_logits=False):
     """``sd``: HF-named tensors (requires_grad as needed). Inputs are 1-D packed rows."""
     T = input_ids.shape[0]
-    inv_freq = cfg.rope_inv_freq().to(input_ids.device)
+    inv_freq = cfg.rope_inv_freq(seq_len=int(position_ids.max()) + 1).to(input_ids.device)
     starts = (position_ids == 0).nonzero().flatten().tolist() + [T]
     x = sd["model.embed_tokens.weight"][input_ids] * cfg.embed_scale(sd["model.embed_tokens.weight"].dtype)
     rm = cfg.residual_multiplier

@@ -129,6 +129,9 @@ class ShardedEngine:
         self.optim = optim or OptimConfig()
         self.step_count = 0
         self.inv_freq = cfg.rope_inv_freq().to(self.device)
+        # longrope: a second table for minibatches whose longest sample exceeds the original context length
+        self._rope_threshold = cfg.rope_long_context_threshold()
+        self.inv_freq_long = cfg.rope_inv_freq(seq_len=self._rope_threshold + 1).to(self.device) if self._rope_threshold else None
 
         layouts = ([L.GroupLayout("embed", L.embed_entries(cfg), self.world)]
                    + [L.GroupLayout(f"block{i}", L.block_entries(cfg), self.world) for i in range(cfg.num_hidden_layers)]
@@ -188,9 +191,13 @@ class ShardedEngine:
         # was never written) shows up as NaN in the loss / norm instead of as a plausible stale value.
         self.poison = os.environ.get("MTB200_POISON", "0") == "1" and self.param_dtype != torch.int8
 
-    def _inv_freq(self, layer: int):
-        """Rotary frequencies of a layer, or ``None`` where the model applies no positional rotation."""
-        return self.inv_freq if self.cfg.layer_uses_rope(layer) else None
+    def _inv_freq(self, layer: int, batch=None):
+        """Rotary frequencies of a layer for this minibatch, or ``None`` where the model applies no positional rotation."""
+        if not self.cfg.layer_uses_rope(layer):
+            return None
+        if self.inv_freq_long is not None and batch is not None and batch.max_seqlen > self._rope_threshold:
+            return self.inv_freq_long
+        return self.inv_freq
 
     # ------------------------------------------------------------------------------------
     # initialisation / state exchange
@@ -573,11 +580,11 @@ class ShardedEngine:
                 self._prefetch_input(i - 1, saved[i - 1][0])
             if acts is None:   # recompute the block forward (attention is skipped when its output was kept)
                 with nvtx.range(f"recompute/block{i}"):
-                    _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self._inv_freq(i), keep=True, saved_attn=attn_state,
+                    _, acts, _ = D.block_forward(ops, cfg, p, xin, batch, self._inv_freq(i, batch), keep=True, saved_attn=attn_state,
                                                  need_out=False)
             notify, finish = self._region_reducer(i, gbuf, gslot, last)
             with nvtx.range(f"backward/block{i}"):
-                dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self._inv_freq(i), notify=notify)
+                dx = D.block_backward(ops, cfg, p, g, acts, dx, batch, self._inv_freq(i, batch), notify=notify)
             del acts, xin, attn_state
             self._release_input()
             self._release_pbuf(slot)
@@ -693,7 +700,7 @@ class ShardedEngine:
                 head = self._gather_group(self.head, prefetch=True)
             xin = x
             with nvtx.range(f"forward/block{i}"):
-                x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self._inv_freq(i),
+                x, acts, attn_state = D.block_forward(ops, cfg, p, x, batch, self._inv_freq(i, batch),
                                                       keep="compact" if levels[i] == 0 else False, want_attn=levels[i] == 1)
             if levels[i] == 3:
                 xin = self._offload_input(i, xin)

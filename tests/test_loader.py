@@ -266,6 +266,34 @@ def test_rope_scaling_kinds_match_transformers(tmp_path, rope):
     assert torch.allclose(mine, ref, atol=5e-4, rtol=5e-4), float((mine - ref).abs().max())
 
 
+def test_longrope_switches_tables_with_the_longest_sample(tmp_path):
+    """Phi-3's long-context rope: per-frequency divisors from the short table up to the original context length, from
+    the long table beyond (decided per minibatch by its longest sample), and a constant factor on q and k. Logits of a
+    short and of a long sample against transformers, and a training step of each through the engine."""
+    short, long = [1.0 + 0.05 * i for i in range(8)], [1.5 + 0.4 * i for i in range(8)]
+    path, hf = _hf_dir(tmp_path, "phi3", max_position_embeddings=512, original_max_position_embeddings=64,
+                       rope_parameters={"rope_type": "longrope", "short_factor": short, "long_factor": long, "rope_theta": 10000.0,
+                                        "original_max_position_embeddings": 64})
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.rope_long_context_threshold() == 64 and eng.cfg.rope_attention_factor > 1.0
+    for n in (40, 200):
+        ids = torch.randint(0, COMMON["vocab_size"], (n,))
+        with torch.no_grad():
+            ref = hf(input_ids=ids[None]).logits[0]
+        mine = _our_logits(eng, ids)
+        assert torch.allclose(mine, ref, atol=5e-4, rtol=5e-4), (n, float((mine - ref).abs().max()))
+        mb = mb_collate_fn([{"input_ids": ids, "labels": ids, "len": n, "num_loss_counted_tokens": n}], n)
+        loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / (n - 1), last=True)
+        hf.zero_grad()
+        out = hf(input_ids=ids[None], labels=ids[None])
+        out.loss.backward()
+        assert abs(float(loss.sum()) / (n - 1) - float(out.loss)) < 1e-4
+        got = eng.blocks[0].layout.views(eng.blocks[0].gacc)["wqkv"]
+        assert torch.allclose(got, hf.model.layers[0].self_attn.qkv_proj.weight.grad, atol=1e-5, rtol=1e-3)
+        for g in eng.groups:
+            g.has_grad = False
+
+
 def test_smollm3_layers_without_rotary_embedding(tmp_path):
     """SmolLM3: every second layer of this tiny model applies no rotary embedding; gradients of a rotated and of a
     not rotated layer against autograd through transformers."""
