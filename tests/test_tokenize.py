@@ -169,3 +169,34 @@ def test_sequence_length_sweep_tool_on_cpu(tmp_path):
         [(256, 2, 128), (256, 1, 256), (512, 4, 128), (512, 2, 256), (512, 1, 512)]
     assert all(r["status"] == "ok" and r["tokens_per_second"] > 0 for r in res)
     assert "tok/s" in p.stdout
+
+
+def test_property_only_assistant_turns_are_trained_on():
+    """Any conversation (optional system turn, any number of user / assistant turns in any order, any words): the
+    unmasked tokens are exactly the assistant turns' words with their end-of-turn token, in order, labels equal the
+    inputs where unmasked, and the counts add up."""
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+    words = st.lists(st.sampled_from(["alpha", "beta", "gamma", "delta", "x1", "y2", "zed"]), min_size=1, max_size=6)
+    turns = st.lists(st.tuples(st.sampled_from(["user", "assistant"]), words), min_size=1, max_size=8)
+
+    @settings(max_examples=80, deadline=None)
+    @given(system=st.one_of(st.none(), words), turns=turns)
+    def run(system, turns):
+        tok = FakeChatTokenizer()
+        msgs = ([{"role": "system", "content": " ".join(system)}] if system else []) + \
+               [{"role": r, "content": " ".join(w)} for r, w in turns]
+        out, n_err, n_long = process_samples([{"messages": msgs}], tok)
+        if not any(r == "assistant" for r, _ in turns):   # nothing to learn from: the sample is dropped or fully masked
+            assert n_err == 1 or all(l == T.IGNORE for l in out[0]["labels"])
+            return
+        assert (n_err, n_long) == (0, 0)
+        s = out[0]
+        inv = {v: k for k, v in tok.vocab.items()}
+        trained = [inv[t] for t, l in zip(s["input_ids"], s["labels"]) if l != T.IGNORE]
+        want = [w for r, ws in turns if r == "assistant" for w in ws + ["<|end|>"]]
+        assert trained == want
+        assert all(l == t for t, l in zip(s["input_ids"], s["labels"]) if l != T.IGNORE)
+        assert s["num_loss_counted_tokens"] == len(want) and s["len"] == len(s["input_ids"])
+
+    run()
