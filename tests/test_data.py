@@ -77,6 +77,37 @@ def test_loader_two_ranks_see_same_batches():
             assert m["input_ids"].shape[1] <= mt
 
 
+def test_worker_process_loader_yields_the_same_stream_as_the_packing_thread(tmp_path):
+    """``num_workers > 0`` (the reference's DataLoader worker processes, sampler.py:285) and the in-process packing thread
+    draw the same batches and cut them into the same minibatches; a resumed stream (``skip_batches``) continues both."""
+    import json
+    spec, vocab, mt, bs = CONFIG_DATA["tiny-qwen2"]
+    ds = synthetic_dataset(96, spec, vocab, seed=1)
+    path = str(tmp_path / "data.jsonl")
+    with open(path, "w") as f:
+        for i in range(len(ds)):
+            s = ds[i]
+            f.write(json.dumps({"input_ids": s["input_ids"].tolist(), "labels": s["labels"].tolist(), "len": s["len"],
+                                "num_loss_counted_tokens": s["num_loss_counted_tokens"]}) + "\n")
+    kw = dict(data_path=path, batch_size=8, max_tokens_per_gpu=mt, seed=5, rank=1, world_size=2)
+    thread = iter(get_data_loader(**kw))
+    procs = iter(get_data_loader(**kw, num_workers=2))
+    seen = []
+    for _ in range(4):
+        a, b = next(thread), next(procs)
+        assert len(a) == len(b)
+        for x, y in zip(a, b):
+            assert torch.equal(x["input_ids"], y["input_ids"]) and torch.equal(x["labels"], y["labels"])
+            assert torch.equal(x["position_ids"], y["position_ids"]) and x["num_samples"] == y["num_samples"]
+        seen.append(a)
+    resumed = iter(get_data_loader(**kw, skip_batches=2, num_workers=2))
+    for want in seen[2:]:
+        got = next(resumed)
+        assert all(torch.equal(x["input_ids"], y["input_ids"]) for x, y in zip(want, got))
+    if hasattr(thread, "close"):
+        thread.close()
+
+
 # ---------------------------------------------------------------------------------------------
 # property-based: the collator over any batch and any world size
 # ---------------------------------------------------------------------------------------------
