@@ -76,6 +76,9 @@ class ModelConfig:
     num_experts_per_tok: int = 2
     moe_intermediate_size: Optional[int] = None
     norm_topk_prob: bool = True
+    # Qwen2-MoE (modeling_qwen2_moe.py): next to the routed experts one shared SwiGLU expert of this width, whose output
+    # is weighted by sigmoid(shared_expert_gate(x))
+    shared_expert_intermediate_size: Optional[int] = None
     output_router_logits: bool = False
     router_jitter_noise: float = 0.0
     extra: dict = field(default_factory=dict)  # unknown keys of config.json, written back verbatim
@@ -148,6 +151,8 @@ class ModelConfig:
                 problems.append(f"router_jitter_noise={self.router_jitter_noise} (input jitter is not implemented)")
             if self.mlp_bias:
                 problems.append("mlp_bias=true with experts")
+            if self.shared_expert_intermediate_size and self.model_type != "qwen2_moe":
+                problems.append("a shared expert outside Qwen2-MoE")
             if self.extra.get("decoder_sparse_step", 1) != 1 or self.extra.get("mlp_only_layers"):
                 problems.append("dense and expert layers mixed (decoder_sparse_step / mlp_only_layers): every block must have "
                                 "the same layout")
@@ -190,7 +195,7 @@ class ModelConfig:
     def o_proj_bias(self) -> bool:
         """``attention_bias`` covers q, k, v and o_proj in the Llama-style classes (modeling_llama.py,
         modeling_granite.py); Qwen2 has the q/k/v biases only (modeling_qwen2.py)."""
-        return self.attention_bias and self.model_type != "qwen2"
+        return self.attention_bias and self.model_type not in ("qwen2", "qwen2_moe")
 
     @property
     def mlp_mats(self) -> int:
@@ -207,6 +212,8 @@ class ModelConfig:
         n = 2 * h + self.qkv_size * h + self.q_size * h + self.mlp_mats * h * f * max(1, self.num_local_experts)
         n += 2 * h if self.norm_type == "layernorm" else 0
         n += self.num_local_experts * h   # router
+        if self.shared_expert_intermediate_size:
+            n += 3 * h * self.shared_expert_intermediate_size + h
         n += self.qkv_size if self.attention_bias else 0
         n += 2 * self.head_dim if self.qk_norm else 0
         n += h if self.o_proj_bias else 0
@@ -330,9 +337,9 @@ class ModelConfig:
               "pad_token_id", "bos_token_id", "eos_token_id", "embedding_multiplier", "residual_multiplier",
               "attention_multiplier", "logits_scaling", "sliding_window", "use_sliding_window", "mlp_bias", "hidden_act",
               "num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise",
-              "moe_intermediate_size", "norm_topk_prob", "no_rope_layers")
+              "moe_intermediate_size", "norm_topk_prob", "no_rope_layers", "shared_expert_intermediate_size")
     _MOE_ONLY = ("num_local_experts", "num_experts_per_tok", "output_router_logits", "router_jitter_noise",
-                 "moe_intermediate_size", "norm_topk_prob")
+                 "moe_intermediate_size", "norm_topk_prob", "shared_expert_intermediate_size")
     _GRANITE_ONLY = ("embedding_multiplier", "residual_multiplier", "attention_multiplier", "logits_scaling")
 
     @classmethod
@@ -345,16 +352,19 @@ class ModelConfig:
             kw.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
             if rp.get("rope_type", "default") != "default":
                 kw.setdefault("rope_scaling", rp)
-        if kw.get("model_type") == "qwen2":
+        if kw.get("model_type") in ("qwen2", "qwen2_moe"):
             kw.setdefault("attention_bias", True)  # Qwen2 always has q/k/v biases
         if kw.get("model_type") in ("qwen3", "qwen3_moe"):
             kw["qk_norm"] = True
-        if kw.get("model_type") == "qwen3_moe":
+        if kw.get("model_type") in ("qwen3_moe", "qwen2_moe"):
             if "num_experts" in d:   # the published configs' key; transformers also writes num_local_experts
                 kw["num_local_experts"] = d["num_experts"]
             kw.setdefault("norm_topk_prob", False)
-            kw.setdefault("moe_intermediate_size", 768)
-            kw.setdefault("num_experts_per_tok", 8)
+            qwen3 = kw["model_type"] == "qwen3_moe"   # the defaults of the two config classes
+            kw.setdefault("moe_intermediate_size", 768 if qwen3 else 1408)
+            kw.setdefault("num_experts_per_tok", 8 if qwen3 else 4)
+            if not qwen3:
+                kw.setdefault("shared_expert_intermediate_size", 5632)
         if kw.get("model_type") in ("mixtral", "granitemoe"):
             # GraniteMoe takes the softmax over the chosen logits only, which is the softmax over all of them
             # renormalised over the chosen ones: the same weights as Mixtral's
@@ -406,10 +416,13 @@ class ModelConfig:
             if self.model_type not in ("granite", "granitemoe"):
                 d.pop(k)
         for k in self._MOE_ONLY:
-            if not self.is_moe or (self.model_type in ("mixtral", "granitemoe") and k in ("moe_intermediate_size", "norm_topk_prob")):
+            if not self.is_moe or d[k] is None or (self.model_type in ("mixtral", "granitemoe")
+                                                   and k in ("moe_intermediate_size", "norm_topk_prob")):
                 d.pop(k)
-        if self.model_type == "qwen3_moe":
+        if self.model_type in ("qwen3_moe", "qwen2_moe"):
             d["num_experts"] = self.num_local_experts
+        if self.model_type == "qwen2_moe":
+            d.pop("attention_bias", None)
         for k in ("sliding_window", "use_sliding_window"):
             if d[k] is None:
                 d.pop(k)
@@ -431,7 +444,8 @@ class ModelConfig:
 
 SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
                            "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM", "GemmaForCausalLM",
-                           "Starcoder2ForCausalLM", "Qwen3MoeForCausalLM", "GraniteMoeForCausalLM", "SmolLM3ForCausalLM")
+                           "Starcoder2ForCausalLM", "Qwen3MoeForCausalLM", "GraniteMoeForCausalLM", "SmolLM3ForCausalLM",
+                           "Qwen2MoeForCausalLM")
 
 
 def _llama(**kw):

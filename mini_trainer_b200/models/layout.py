@@ -85,6 +85,9 @@ def block_entries(cfg: ModelConfig) -> list:
         e.append(("router", (cfg.num_local_experts, h)))
         for x in range(cfg.num_local_experts):
             e += [(f"wgu{x}", (2 * fe, h)), (f"wd{x}", (h, fe))]
+        if cfg.shared_expert_intermediate_size:   # Qwen2-MoE: a shared expert and the vector that gates it
+            fs = cfg.shared_expert_intermediate_size
+            e += [("wgus", (2 * fs, h)), ("wds", (h, fs)), ("wsg", (1, h))]
         return e
     if cfg.mlp_bias:
         e.append(("bgu", (gu,)))
@@ -160,6 +163,12 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
                 yield p + f"mlp.experts.{x}.up_proj.weight", views[f"wgu{x}"][fe:]
                 yield p + f"mlp.experts.{x}.down_proj.weight", views[f"wd{x}"]
             yield p + "mlp.gate.weight", views["router"]
+            if cfg.shared_expert_intermediate_size:
+                fs = cfg.shared_expert_intermediate_size
+                yield p + "mlp.shared_expert.gate_proj.weight", views["wgus"][:fs]
+                yield p + "mlp.shared_expert.up_proj.weight", views["wgus"][fs:]
+                yield p + "mlp.shared_expert.down_proj.weight", views["wds"]
+                yield p + "mlp.shared_expert_gate.weight", views["wsg"]
         yield p + "input_layernorm.weight", views["ln1"]
         yield p + "post_attention_layernorm.weight", views["ln2"]
         return

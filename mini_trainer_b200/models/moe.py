@@ -33,6 +33,8 @@ class MoeState:
     bounds: list                 # E+1 host ints: routed rows [bounds[e], bounds[e+1]) belong to expert e
     gu: torch.Tensor             # [T*k, 2F] gate/up pre-activations of the routed rows
     act: Optional[torch.Tensor]  # [T*k, F] SwiGLU output (None: rebuilt in backward)
+    gu_s: Optional[torch.Tensor] = None    # [T, 2Fs] gate/up pre-activations of the shared expert (Qwen2-MoE)
+    act_s: Optional[torch.Tensor] = None   # [T, Fs] its SwiGLU output (None: rebuilt in backward)
 
 
 def route(cfg, router_w: torch.Tensor, n2: torch.Tensor, topi: Optional[torch.Tensor] = None):
@@ -78,6 +80,9 @@ def moe_forward(ops, cfg, p: dict, n2: torch.Tensor, h1: torch.Tensor, need_out:
             ops.linear(xs[a:b], p[f"wgu{e}"], out=gu[a:b])
     del xs
     st = MoeState(probs, topi, w, order, tok, bounds, gu, None)
+    shared = "wgus" in p   # Qwen2-MoE: every token also goes through one shared expert, weighted by a sigmoid gate
+    if shared:
+        st.gu_s = ops.linear(n2, p["wgus"])
     if not need_out:
         return None, st
     # activation and down projection slab by slab: only the slab's activation is alive unless backward wants all of it
@@ -91,6 +96,10 @@ def moe_forward(ops, cfg, p: dict, n2: torch.Tensor, h1: torch.Tensor, need_out:
                 act[a:b] = act_e
     wr = w.reshape(-1)[order]
     y = _combine((yr.float() * wr[:, None]).to(yr.dtype), order, T, k)
+    if shared:
+        act_s = ops.swiglu(st.gu_s, cfg.mlp_act)
+        y += torch.sigmoid((n2 @ p["wsg"].t()).float()) * ops.linear(act_s, p["wds"]).float()
+        st.act_s = act_s if keep_act else None
     st.act = act
     return (h1.float() + cfg.residual_multiplier * y).to(h1.dtype), st
 
@@ -132,6 +141,23 @@ def moe_backward(ops, cfg, p: dict, g: dict, st: MoeState, n2: torch.Tensor, dou
         del dgu
     dn2 = _combine(dxs, order, T, k)
     del xs, dxs, gr
+    if "wgus" in p:   # shared expert: y_s = sigmoid(n2 wsg^T) * MLP_s(n2)
+        act_s = st.act_s if st.act_s is not None else ops.swiglu(st.gu_s, cfg.mlp_act)
+        ys = ops.linear(act_s, p["wds"]).float()          # its output again: the gate's gradient needs it
+        sg = torch.sigmoid((n2 @ p["wsg"].t()).float())   # [T, 1]
+        df = dout.float() * rm
+        dz = ((df * ys).sum(-1, keepdim=True) * sg * (1 - sg)).to(n2.dtype)
+        g["wsg"].copy_(dz.t() @ n2)
+        dn2 += (dz @ p["wsg"]).float()
+        dys = (df * sg).to(n2.dtype)
+        del ys, df
+        dact_s = ops.linear_dgrad(dys, p["wds"])
+        ops.linear_wgrad(dys, act_s, g["wds"])
+        dgu_s = ops.swiglu_bwd(dact_s, st.gu_s, cfg.mlp_act)
+        del dact_s, act_s, dys
+        dn2 += ops.linear_dgrad(dgu_s, p["wgus"]).float()
+        ops.linear_wgrad(dgu_s, n2, g["wgus"])
+        del dgu_s
     # router: weights -> renormalisation -> top-k selection -> softmax -> logits
     dw = torch.empty(T * k, dtype=torch.float32, device=n2.device)
     dw[order] = dwr

@@ -85,6 +85,11 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
             y = 0
             for e, (wg, wu, wdn) in enumerate(experts):
                 y = y + gatew[:, e: e + 1].to(n.dtype) * F.linear(F.silu(F.linear(n, wg)) * F.linear(n, wu), wdn)
+            if cfg.shared_expert_intermediate_size:
+                se = m + "shared_expert."
+                ys = F.linear(F.silu(F.linear(n, sd[se + "gate_proj.weight"])) * F.linear(n, sd[se + "up_proj.weight"]),
+                              sd[se + "down_proj.weight"])
+                y = y + torch.sigmoid(F.linear(n, sd[m + "shared_expert_gate.weight"])) * ys
             x = x + rm * y
             continue
         if not cfg.mlp_gated:

@@ -137,6 +137,17 @@ def test_checkpoint_levels_give_identical_gradients_mixture_of_experts():
     _check_levels(moe_cfg())
 
 
+def test_grads_and_checkpoint_levels_with_a_shared_expert():
+    """Qwen2-MoE's block (q/k/v biases, routed experts of their own width without renormalisation, a sigmoid-gated
+    shared expert) against the autograd oracle and across the checkpoint levels."""
+    cfg = ModelConfig.from_hf_dict(dict(model_type="qwen2_moe", architectures=["Qwen2MoeForCausalLM"], vocab_size=97,
+                                        hidden_size=32, intermediate_size=48, moe_intermediate_size=24,
+                                        shared_expert_intermediate_size=40, num_hidden_layers=2, num_attention_heads=4,
+                                        num_key_value_heads=2, num_experts=4, num_experts_per_tok=2))
+    check_grads(False, True, cfg)
+    _check_levels(cfg)
+
+
 def _check_levels(cfg):
     mb = make_mb([11, 3, 8], cfg.vocab_size, seed=4)
     grads = []

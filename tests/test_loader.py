@@ -38,6 +38,8 @@ def _hf_dir(tmp_path, kind, **over):
                                                          "embedding_multiplier": 12.0, "residual_multiplier": 0.22,
                                                          "attention_multiplier": 0.0625, "logits_scaling": 8.0}),
            "smollm3": (transformers.SmolLM3Config, {"num_hidden_layers": 4, "no_rope_layer_interval": 2, "pad_token_id": 0}),
+           "qwen2_moe": (transformers.Qwen2MoeConfig, {"num_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 48,
+                                                       "shared_expert_intermediate_size": 80}),
            "starcoder2": (transformers.Starcoder2Config, {"sliding_window": None, "bos_token_id": 1, "eos_token_id": 2})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
@@ -58,7 +60,7 @@ def _our_logits(eng, ids):
     return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb, norm_b=head.get("bnorm"))
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2", "qwen3_moe", "granitemoe", "smollm3"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2", "qwen3_moe", "granitemoe", "smollm3", "qwen2_moe"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -391,6 +393,37 @@ def test_granite_moe_gradients_and_stacked_export_against_transformers(tmp_path)
     save_hf_checkpoint(eng, out_dir)
     saved = st.load_file(os.path.join(out_dir, "model.safetensors"))
     assert tuple(saved[L + "input_linear.weight"].shape) == (4, 2 * COMMON["intermediate_size"], COMMON["hidden_size"])
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    with torch.no_grad():
+        ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
+
+
+def test_qwen2_moe_shared_expert_gradients_against_transformers(tmp_path):
+    """Qwen2-MoE: routed experts plus one shared expert weighted by a sigmoid gate; gradients of the gate vector, the
+    shared expert, a routed expert and the router against autograd through transformers; the export loads there."""
+    path, hf = _hf_dir(tmp_path, "qwen2_moe")
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.shared_expert_intermediate_size == 80 and eng.cfg.attention_bias and not eng.cfg.o_proj_bias
+    ids = torch.randint(0, COMMON["vocab_size"], (26,))
+    labels = ids.clone()
+    labels[:6] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 26, "num_loss_counted_tokens": 20}], 20)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 20, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 20 - float(out.loss)) < 1e-4
+    got = eng.blocks[0].layout.views(eng.blocks[0].gacc)
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    L, fs = "model.layers.0.mlp.", 80
+    for a, b in [(got["wsg"], want[L + "shared_expert_gate.weight"]), (got["wgus"][:fs], want[L + "shared_expert.gate_proj.weight"]),
+                 (got["wgus"][fs:], want[L + "shared_expert.up_proj.weight"]), (got["wds"], want[L + "shared_expert.down_proj.weight"]),
+                 (got["router"], want[L + "gate.weight"]), (got["wgu2"], want[L + "experts.gate_up_proj"][2]),
+                 (got["wd2"], want[L + "experts.down_proj"][2]), (got["bqkv"][: eng.cfg.q_size], want["model.layers.0.self_attn.q_proj.bias"])]:
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-3), float((a - b).abs().max())
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
     back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
     with torch.no_grad():
         ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
