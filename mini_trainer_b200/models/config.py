@@ -116,6 +116,13 @@ class ModelConfig:
             m = float(torch.tensor(m, dtype=dtype))
         return m
 
+    @property
+    def rotary_dim(self) -> int:
+        """Leading dimensions of every head the rotary embedding turns (``partial_rotary_factor``: Phi-4-mini turns
+        three quarters of a head); the rest passes through."""
+        prf = (self.extra.get("rope_parameters") or {}).get("partial_rotary_factor", self.extra.get("partial_rotary_factor"))
+        return self.head_dim if prf in (None, 1.0) else int(self.head_dim * float(prf))
+
     def layer_uses_rope(self, layer: int) -> bool:
         return self.no_rope_layers is None or bool(self.no_rope_layers[layer])
 
@@ -163,9 +170,8 @@ class ModelConfig:
         for k in ("attention_dropout", "resid_pdrop", "embd_pdrop", "residual_dropout", "embedding_dropout", "hidden_dropout"):
             if self.extra.get(k) and not self.ignore_dropout:
                 problems.append(f"{k}={self.extra[k]} (dropout is not implemented; pass --no-dropout to train without it)")
-        prf = (self.extra.get("rope_parameters") or {}).get("partial_rotary_factor", self.extra.get("partial_rotary_factor", 1.0))
-        if prf not in (None, 1.0):
-            problems.append(f"partial_rotary_factor={prf} (the rotary kernel turns the whole head)")
+        if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
+            problems.append(f"partial_rotary_factor gives a rotary width of {self.rotary_dim} for head_dim {self.head_dim}")
         if not self.mlp_gated and (self.hidden_act != "gelu_pytorch_tanh" or self.is_moe):
             problems.append(f"an MLP without a gate is implemented with the tanh-approximated GELU only (hidden_act={self.hidden_act!r})")
         if self.hidden_act not in ("silu", "swish", "gelu_pytorch_tanh"):
@@ -260,10 +266,10 @@ class ModelConfig:
                    or self.max_position_embeddings)
 
     def rope_inv_freq(self, seq_len: Optional[int] = None):
-        """fp32 inverse frequencies [head_dim/2], with ``linear``, ``llama3``, ``yarn`` and ``longrope`` scaling.
+        """fp32 inverse frequencies [rotary_dim/2], with ``linear``, ``llama3``, ``yarn`` and ``longrope`` scaling.
         ``seq_len``: the longest sample of the minibatch (only ``longrope`` looks at it)."""
         import torch
-        d = self.head_dim
+        d = self.rotary_dim
         inv = 1.0 / (self.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float64) / d))
         rs = self.rope_scaling or {}
         kind = rs.get("rope_type", rs.get("type", "default"))

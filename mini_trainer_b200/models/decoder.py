@@ -141,7 +141,8 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
         rstd_qk = ops.head_rmsnorm_(qkv, p["qn"], p["kn"], cfg.rms_norm_eps, cfg.num_attention_heads,
                                     cfg.num_key_value_heads, cfg.head_dim)
     if inv_freq is not None:   # None: a layer without positional rotation (SmolLM3's NoPE layers)
-        ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+        ops.rope_(qkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                  rot_dim=cfg.rotary_dim)
     rm = cfg.residual_multiplier   # Granite scales every branch output before the residual add (1.0 elsewhere)
     # the GEMM epilogue computes alpha * product + bias + residual; the models scale (product + bias)
     bo, bd = p.get("bo"), p.get("bd")
@@ -237,7 +238,7 @@ def _attention_backward(ops, cfg: ModelConfig, p: dict, g: dict, a: BlockActs, d
     del dattn
     if inv_freq is not None:
         ops.rope_(dqkv, batch.position_ids, inv_freq, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
-                  inverse=True)
+                  inverse=True, rot_dim=cfg.rotary_dim)
     if cfg.qk_norm:
         ops.head_rmsnorm_bwd_(dqkv, a.qk_pre, a.rstd_qk, p["qn"], p["kn"], g["qn"], g["kn"], cfg.num_attention_heads,
                               cfg.num_key_value_heads, cfg.head_dim)

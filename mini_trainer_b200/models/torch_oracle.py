@@ -25,13 +25,14 @@ def _norm(cfg, sd, name, x):
 
 
 def _rope(x, pos, inv_freq):
-    # x: [T, heads, D]
+    # x: [T, heads, D]; the first 2 * len(inv_freq) dimensions of every head are turned
     ang = pos.float()[:, None] * inv_freq[None, :]
     cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, :]
     sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, :]
-    d = x.shape[-1]
-    rot = torch.cat([-x[..., d // 2:], x[..., : d // 2]], -1)
-    return (x.float() * cos + rot.float() * sin).to(x.dtype)
+    r = 2 * inv_freq.shape[0]
+    xr, rest = x[..., :r], x[..., r:]
+    rot = torch.cat([-xr[..., r // 2:], xr[..., : r // 2]], -1)
+    return torch.cat([(xr.float() * cos + rot.float() * sin).to(x.dtype), rest], -1)
 
 
 def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, position_ids, return_logits=False):

@@ -265,7 +265,12 @@ class NativeOps:
                        self._st(), n=2)
 
     # -- rope -------------------------------------------------------------------------
-    def rope_(self, qkv, position_ids, inv_freq, n_q_heads, n_kv_heads, head_dim, inverse=False):
+    def rope_(self, qkv, position_ids, inv_freq, n_q_heads, n_kv_heads, head_dim, inverse=False, rot_dim=None):
+        if rot_dim is not None and rot_dim != head_dim:
+            # A partial rotary embedding (Phi-4-mini) pairs dimension i with i + rot_dim / 2 and leaves the tail of the head
+            # alone; the kernel pairs i with i + head_dim / 2. Such models take the PyTorch-op form of the rotation.
+            from .torch_ref import TorchOps
+            return TorchOps.rope_(self, qkv, position_ids, inv_freq, n_q_heads, n_kv_heads, head_dim, inverse, rot_dim)
         assert position_ids.dtype == torch.int32
         self._call("mtb200_rope", qkv.data_ptr(), position_ids.data_ptr(), inv_freq.data_ptr(), qkv.shape[0],
                    qkv.stride(0), n_q_heads + n_kv_heads, head_dim, int(inverse), self._st())

@@ -93,19 +93,22 @@ class TorchOps:
             dbias_out.copy_(dy.float().sum(0).to(dbias_out.dtype))
 
     # -- rope (in place on the q and k column blocks of the fused qkv tensor) ------------
-    def rope_(self, qkv, position_ids, inv_freq, n_q_heads, n_kv_heads, head_dim, inverse=False):
+    def rope_(self, qkv, position_ids, inv_freq, n_q_heads, n_kv_heads, head_dim, inverse=False, rot_dim=None):
+        """``rot_dim``: leading dimensions of each head that are turned (default: the whole head)."""
         T = qkv.shape[0]
-        ang = position_ids.to(torch.float32).unsqueeze(-1) * inv_freq.to(qkv.device).unsqueeze(0)  # [T, D/2]
+        rot = head_dim if rot_dim is None else rot_dim
+        ang = position_ids.to(torch.float32).unsqueeze(-1) * inv_freq.to(qkv.device).unsqueeze(0)  # [T, rot/2]
         cos, sin = ang.cos(), ang.sin()
         if inverse:
             sin = -sin
         nh = n_q_heads + n_kv_heads
         v = qkv[:, : nh * head_dim].reshape(T, nh, head_dim)
-        x1, x2 = v[..., : head_dim // 2].float(), v[..., head_dim // 2:].float()
+        x1, x2 = v[..., : rot // 2].float(), v[..., rot // 2: rot].float()
         c, s = cos.unsqueeze(1), sin.unsqueeze(1)
         o1 = x1 * c - x2 * s
         o2 = x2 * c + x1 * s
-        qkv[:, : nh * head_dim] = torch.cat([o1, o2], -1).reshape(T, nh * head_dim).to(qkv.dtype)
+        out = torch.cat([o1.to(qkv.dtype), o2.to(qkv.dtype), v[..., rot:]], -1)
+        qkv[:, : nh * head_dim] = out.reshape(T, nh * head_dim)
         return qkv
 
     # -- per-head RMSNorm of q and k (Qwen3 q_norm / k_norm) --------------------------------

@@ -296,6 +296,24 @@ def test_longrope_switches_tables_with_the_longest_sample(tmp_path):
             g.has_grad = False
 
 
+def test_partial_rotary_embedding(tmp_path):
+    """Phi-4-mini turns only the leading part of every head: logits and the q/k/v gradient against transformers."""
+    path, hf = _hf_dir(tmp_path, "phi3", rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5})
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.rotary_dim == 8 and eng.cfg.head_dim == 16 and eng.inv_freq.numel() == 4
+    ids = torch.randint(0, COMMON["vocab_size"], (31,))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    assert torch.allclose(_our_logits(eng, ids), ref, atol=3e-4, rtol=3e-4)
+    mb = mb_collate_fn([{"input_ids": ids, "labels": ids, "len": 31, "num_loss_counted_tokens": 31}], 31)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 30, last=True)
+    out = hf(input_ids=ids[None], labels=ids[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 30 - float(out.loss)) < 1e-4
+    got = eng.blocks[0].layout.views(eng.blocks[0].gacc)["wqkv"]
+    assert torch.allclose(got, hf.model.layers[0].self_attn.qkv_proj.weight.grad, atol=1e-5, rtol=1e-3)
+
+
 def test_smollm3_layers_without_rotary_embedding(tmp_path):
     """SmolLM3: every second layer of this tiny model applies no rotary embedding; gradients of a rotated and of a
     not rotated layer against autograd through transformers."""
