@@ -58,7 +58,8 @@ def main(
                                                 "(fp32 master weights, AdamW moments, scheduler, data position) under "
                                                 "<output-dir>/train_state/samples_<N>"),
     resume_from: Optional[str] = Option(None, help="A train_state/samples_<N> directory written by --save-train-state: "
-                                                   "weights, optimizer, scheduler, counters and the data stream continue from it"),
+                                                   "weights, optimizer, scheduler, counters and the data stream continue from it "
+                                                   "(on the same or on another number of GPUs)"),
 ):
     import torch
 
