@@ -66,6 +66,9 @@ class ModelConfig:
     # a constant that is first rounded to the embedding's dtype (55.4256 becomes 55.5 in bf16)
     norm_weight_offset: float = 0.0
     embedding_multiplier_in_param_dtype: bool = False
+    # OLMo-2 (modeling_olmo2.py): no norm in front of a branch but one behind it (x + Norm(Attn(x)), h + Norm(MLP(h))),
+    # and an RMSNorm over the whole query and the whole key projection
+    post_norm: bool = False
     # SmolLM3 (modeling_smollm3.py): layers whose entry is 0 apply no rotary embedding (NoPE); None = every layer rotates
     no_rope_layers: Optional[list] = None
     # Qwen3 (modeling_qwen3.py): RMSNorm over head_dim on every q and k head before the rotary embedding
@@ -151,6 +154,9 @@ class ModelConfig:
         problems = []
         if self.no_rope_layers is not None and len(self.no_rope_layers) != self.num_hidden_layers:
             problems.append(f"no_rope_layers has {len(self.no_rope_layers)} entries for {self.num_hidden_layers} layers")
+        if self.post_norm and (self.is_moe or self.norm_type != "rmsnorm" or not self.mlp_gated or self.qk_norm
+                               or self.norm_weight_offset or self.residual_multiplier != 1.0):
+            problems.append("the post-norm block is implemented for OLMo-2's combination only (dense gated MLP, RMSNorm)")
         if self.is_moe:
             if self.output_router_logits:
                 problems.append("output_router_logits=true adds the router's load-balancing loss, which is not implemented")
@@ -222,6 +228,7 @@ class ModelConfig:
             n += 3 * h * self.shared_expert_intermediate_size + h
         n += self.qkv_size if self.attention_bias else 0
         n += 2 * self.head_dim if self.qk_norm else 0
+        n += self.q_size + self.kv_size if self.post_norm else 0
         n += h if self.o_proj_bias else 0
         return n + ((self.mlp_mats - 1) * f + h if self.mlp_bias else 0)
 
@@ -379,6 +386,8 @@ class ModelConfig:
         if kw.get("model_type") == "smollm3" and kw.get("no_rope_layers") is None:   # the config class's default rule
             step = int(d.get("no_rope_layer_interval", 4))
             kw["no_rope_layers"] = [int((i + 1) % step != 0) for i in range(int(kw["num_hidden_layers"]))]
+        if kw.get("model_type") == "olmo2":
+            kw["post_norm"] = True
         if kw.get("model_type") == "starcoder2":
             use_bias = bool(d.pop("use_bias", True))
             kw.update(norm_type="layernorm", mlp_gated=False, attention_bias=use_bias, mlp_bias=use_bias,
@@ -406,7 +415,7 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         d = asdict(self)
         extra = d.pop("extra")
-        for k in ("qk_norm", "norm_weight_offset", "embedding_multiplier_in_param_dtype", "norm_type", "mlp_gated", "ignore_dropout"):
+        for k in ("qk_norm", "norm_weight_offset", "embedding_multiplier_in_param_dtype", "norm_type", "mlp_gated", "ignore_dropout", "post_norm"):
             d.pop(k)   # implied by the model type, not keys of any Hugging Face config
         if d["no_rope_layers"] is None:
             d.pop("no_rope_layers")
@@ -451,7 +460,7 @@ class ModelConfig:
 SUPPORTED_ARCHITECTURES = ("LlamaForCausalLM", "Qwen2ForCausalLM", "MistralForCausalLM", "GraniteForCausalLM",
                            "MixtralForCausalLM", "Phi3ForCausalLM", "Qwen3ForCausalLM", "GemmaForCausalLM",
                            "Starcoder2ForCausalLM", "Qwen3MoeForCausalLM", "GraniteMoeForCausalLM", "SmolLM3ForCausalLM",
-                           "Qwen2MoeForCausalLM")
+                           "Qwen2MoeForCausalLM", "Olmo2ForCausalLM")
 
 
 def _llama(**kw):

@@ -23,6 +23,7 @@ import torch
 
 from .config import ModelConfig
 from .moe import moe_backward, moe_forward
+from . import postnorm
 
 
 @dataclass
@@ -130,6 +131,8 @@ def block_forward(ops, cfg: ModelConfig, p: dict, x: torch.Tensor, batch: Packed
     ``saved_attn = (attn, lse)`` from an earlier forward skips the attention kernel (used by the
     recompute of blocks whose attention output was kept); ``want_attn`` returns that pair.
     """
+    if cfg.post_norm:
+        return postnorm.block_forward(ops, cfg, p, x, batch, inv_freq, keep, saved_attn, want_attn, need_out)
     plan = p.get("_gather")   # all-gather of this block's parameters fused into its first GEMMs
     if plan is not None:
         plan.prefetch_small()
@@ -185,6 +188,8 @@ def block_backward(ops, cfg: ModelConfig, p: dict, g: dict, acts: BlockActs, dou
     queued: everything laid out from that tensor to the end of the buffer (to the previous
     notification) is then complete, and the engine starts reducing that region while the rest of
     the block's backward still runs."""
+    if cfg.post_norm:
+        return postnorm.block_backward(ops, cfg, p, g, acts, dout, batch, inv_freq, notify)
     a = acts
     notify = notify or (lambda name: None)
     rm = cfg.residual_multiplier

@@ -70,6 +70,8 @@ def block_entries(cfg: ModelConfig) -> list:
         e.append(("bqkv", (cfg.qkv_size,)))
     if cfg.qk_norm:
         e += [("qn", (cfg.head_dim,)), ("kn", (cfg.head_dim,))]
+    if cfg.post_norm:   # OLMo-2 normalises the whole query and the whole key projection
+        e += [("qn", (cfg.q_size,)), ("kn", (cfg.kv_size,))]
     e += [("wqkv", (cfg.qkv_size, h)), ("wo", (h, cfg.q_size))]
     # Optional biases sit where both schedules want them: ``bo`` and ``bgu`` in front of ``wgu``, so the
     # gather fused into the QKV projection has brought them in before o_proj / gate-up run and backward has
@@ -137,7 +139,7 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
     if cfg.attention_bias:
         yield p + "self_attn.v_proj.bias", views["bqkv"][q + kv:]
     yield p + "self_attn.o_proj.weight", views["wo"]
-    if cfg.qk_norm:
+    if cfg.qk_norm or cfg.post_norm:
         yield p + "self_attn.q_norm.weight", views["qn"]
         yield p + "self_attn.k_norm.weight", views["kn"]
     if cfg.o_proj_bias:
@@ -194,6 +196,10 @@ def hf_tensors_of_block(cfg: ModelConfig, layer: int, views: dict) -> Iterator[t
     yield p + "mlp.down_proj.weight", views["wd"]
     if cfg.mlp_bias:
         yield p + "mlp.down_proj.bias", views["bd"]
+    if cfg.post_norm:   # OLMo-2: the two norms sit behind the attention and the MLP branch
+        yield p + "post_attention_layernorm.weight", views["ln1"]
+        yield p + "post_feedforward_layernorm.weight", views["ln2"]
+        return
     yield p + "input_layernorm.weight", views["ln1"]
     yield p + "post_attention_layernorm.weight", views["ln2"]
 

@@ -46,10 +46,13 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
     mlp_act = F.silu if cfg.mlp_act == "silu" else (lambda t: F.gelu(t, approximate="tanh"))
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        n = _norm(cfg, sd, p + "input_layernorm", x)
+        n = x if cfg.post_norm else _norm(cfg, sd, p + "input_layernorm", x)
         q = F.linear(n, sd[p + "self_attn.q_proj.weight"], sd.get(p + "self_attn.q_proj.bias")).view(T, hq, d)
         k = F.linear(n, sd[p + "self_attn.k_proj.weight"], sd.get(p + "self_attn.k_proj.bias")).view(T, hkv, d)
         v = F.linear(n, sd[p + "self_attn.v_proj.weight"], sd.get(p + "self_attn.v_proj.bias")).view(T, hkv, d)
+        if cfg.post_norm:   # over the whole projection, not per head
+            q = _rms(q.reshape(T, hq * d), sd[p + "self_attn.q_norm.weight"], cfg.rms_norm_eps).view(T, hq, d)
+            k = _rms(k.reshape(T, hkv * d), sd[p + "self_attn.k_norm.weight"], cfg.rms_norm_eps).view(T, hkv, d)
         if cfg.qk_norm:
             q = _rms(q, sd[p + "self_attn.q_norm.weight"], cfg.rms_norm_eps)
             k = _rms(k, sd[p + "self_attn.k_norm.weight"], cfg.rms_norm_eps)
@@ -61,7 +64,13 @@ def oracle_per_token_loss(cfg: ModelConfig, sd: dict, input_ids, labels, positio
                                                v[a:b].transpose(0, 1)[None], is_causal=True, enable_gqa=True,
                                                scale=cfg.attention_scale)
             outs.append(o[0].transpose(0, 1).reshape(b - a, hq * d))
-        x = x + rm * F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
+        ao = F.linear(torch.cat(outs, 0), sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
+        if cfg.post_norm:
+            x = x + _rms(ao, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
+            a = F.silu(F.linear(x, sd[p + "mlp.gate_proj.weight"])) * F.linear(x, sd[p + "mlp.up_proj.weight"])
+            x = x + _rms(F.linear(a, sd[p + "mlp.down_proj.weight"]), sd[p + "post_feedforward_layernorm.weight"], cfg.rms_norm_eps)
+            continue
+        x = x + rm * ao
         n = _norm(cfg, sd, p + "post_attention_layernorm", x)
         if cfg.is_moe:   # dense restatement: every expert on every token, masked by the routing weights
             fe = cfg.expert_intermediate_size

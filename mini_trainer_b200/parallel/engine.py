@@ -470,6 +470,8 @@ class ShardedEngine:
         # level 0 keeps qkv, the attention output, h1 and gate/up (the normalised inputs and the SwiGLU
         # output are rebuilt in backward by elementwise kernels)
         lvl0 = lvl1 + tokens * ((h + cfg.qkv_size + 2 * f) * es + 8)
+        if cfg.post_norm:   # both branch outputs before their norms and the q|k projections before theirs
+            lvl0 += tokens * (2 * h + cfg.q_size + cfg.kv_size) * es
         if cfg.qk_norm:   # the q|k heads before their norm and one reciprocal RMS per head
             lvl0 += tokens * ((cfg.q_size + cfg.kv_size) * es + (cfg.num_attention_heads + cfg.num_key_value_heads) * 4)
         for i in range(nL - 1, -1, -1):      # cheapest upgrade first: keep attention everywhere it fits

@@ -95,6 +95,14 @@ def test_grads_layernorm_and_plain_gelu_mlp():
     _check_levels(starcoder2_cfg())
 
 
+def test_grads_post_norm_block():
+    """OLMo-2's block against the autograd oracle, in all three checkpoint levels."""
+    cfg = ModelConfig.from_hf_dict(dict(model_type="olmo2", architectures=["Olmo2ForCausalLM"], vocab_size=97, hidden_size=32,
+                                        intermediate_size=48, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2))
+    check_grads(False, False, cfg)
+    _check_levels(cfg)
+
+
 def test_grads_mixture_of_experts():
     """Router (softmax, top-k, renormalisation) and routed SwiGLU experts against a dense autograd restatement."""
     check_grads(False, False, moe_cfg())

@@ -40,6 +40,7 @@ def _hf_dir(tmp_path, kind, **over):
            "smollm3": (transformers.SmolLM3Config, {"num_hidden_layers": 4, "no_rope_layer_interval": 2, "pad_token_id": 0}),
            "qwen2_moe": (transformers.Qwen2MoeConfig, {"num_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 48,
                                                        "shared_expert_intermediate_size": 80}),
+           "olmo2": (transformers.Olmo2Config, {"pad_token_id": 0}),
            "starcoder2": (transformers.Starcoder2Config, {"sliding_window": None, "bos_token_id": 1, "eos_token_id": 2})}[kind]
     kw = dict(COMMON, **cls[1])
     kw.update(over)
@@ -60,7 +61,7 @@ def _our_logits(eng, ids):
     return D.forward_logits(eng.ops, eng.cfg, emb, blocks, head["norm"], head.get("lm_head", emb), pb, norm_b=head.get("bnorm"))
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2", "qwen3_moe", "granitemoe", "smollm3", "qwen2_moe"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "mistral", "granite", "mixtral", "phi3", "qwen3", "gemma", "starcoder2", "qwen3_moe", "granitemoe", "smollm3", "qwen2_moe", "olmo2"])
 def test_setup_model_matches_transformers(tmp_path, kind):
     path, hf = _hf_dir(tmp_path, kind)
     eng = setup_model(path, device="cpu")
@@ -312,6 +313,42 @@ def test_partial_rotary_embedding(tmp_path):
     assert abs(float(loss.sum()) / 30 - float(out.loss)) < 1e-4
     got = eng.blocks[0].layout.views(eng.blocks[0].gacc)["wqkv"]
     assert torch.allclose(got, hf.model.layers[0].self_attn.qkv_proj.weight.grad, atol=1e-5, rtol=1e-3)
+
+
+def test_olmo2_post_norm_block_gradients_against_transformers(tmp_path):
+    """OLMo-2: norms behind the branches and an RMSNorm over the whole q and the whole k projection; every kind of
+    gradient of a block against autograd through transformers, and the export."""
+    path, hf = _hf_dir(tmp_path, "olmo2")
+    with torch.no_grad():
+        for n, p_ in hf.named_parameters():
+            if "norm" in n:
+                p_.uniform_(0.5, 1.5)
+    hf.save_pretrained(path)
+    eng = setup_model(path, device="cpu")
+    assert eng.cfg.post_norm and tuple(eng.blocks[0].layout.specs["qn"].shape) == (eng.cfg.q_size,)
+    ids = torch.randint(0, COMMON["vocab_size"], (27,))
+    labels = ids.clone()
+    labels[:5] = -100
+    mb = mb_collate_fn([{"input_ids": ids, "labels": labels, "len": 27, "num_loss_counted_tokens": 22}], 22)
+    loss = eng.forward_backward(D.make_packed_batch(mb, "cpu"), 1.0 / 22, last=True)
+    out = hf(input_ids=ids[None], labels=labels[None])
+    out.loss.backward()
+    assert abs(float(loss.sum()) / 22 - float(out.loss)) < 1e-4
+    got = eng.blocks[0].layout.views(eng.blocks[0].gacc)
+    want = {n: p_.grad for n, p_ in hf.named_parameters()}
+    L, q, f = "model.layers.0.", eng.cfg.q_size, eng.cfg.intermediate_size
+    for a, b in [(got["qn"], want[L + "self_attn.q_norm.weight"]), (got["kn"], want[L + "self_attn.k_norm.weight"]),
+                 (got["ln1"], want[L + "post_attention_layernorm.weight"]), (got["ln2"], want[L + "post_feedforward_layernorm.weight"]),
+                 (got["wqkv"][:q], want[L + "self_attn.q_proj.weight"]), (got["wo"], want[L + "self_attn.o_proj.weight"]),
+                 (got["wgu"][:f], want[L + "mlp.gate_proj.weight"]), (got["wd"], want[L + "mlp.down_proj.weight"])]:
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-3), float((a - b).abs().max())
+    from mini_trainer_b200.ckpt.hf_checkpoint import save_hf_checkpoint
+    out_dir = str(tmp_path / "export")
+    save_hf_checkpoint(eng, out_dir)
+    back = transformers.AutoModelForCausalLM.from_pretrained(out_dir, torch_dtype=torch.float32)
+    with torch.no_grad():
+        ref, again = hf(input_ids=ids[None]).logits[0], back(input_ids=ids[None]).logits[0]
+    assert torch.allclose(again, ref, atol=0.05, rtol=0.05)   # the export is bf16
 
 
 def test_smollm3_layers_without_rotary_embedding(tmp_path):
