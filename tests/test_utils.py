@@ -74,3 +74,19 @@ def test_nvtx_ranges_cover_the_step_phases(monkeypatch):
     for want in ("forward/block0", "forward/block1", "head", "recompute/block1", "backward/block1", "reduce/block0", "optimizer"):
         assert want in names, (want, names)
     assert names.index("forward/block1") < names.index("head") < names.index("backward/block1") < names.index("optimizer")
+
+
+def test_static_memory_plan():
+    """The planning tool reproduces the decisions recorded for the benchmark configurations: a 70B model on eight 183 GiB
+    GPUs needs bf16 moments and keeps a few attention outputs at 16 000 tokens; a 1.5B model keeps everything in fp32; a
+    70B model on ONE GPU does not fit."""
+    from mini_trainer_b200.cli.plan import memory_plan
+    from mini_trainer_b200.models.config import get_preset
+    big = memory_plan(get_preset("llama-3.1-70b"), 8, 16000)
+    assert big["moment_dtype"] == "bf16" and big["fits"] and 100 < big["per_gpu_gb"]["optimizer_and_parameter_state"] < 130
+    assert big["blocks"]["keeping_every_gemm_output"] == 0
+    small = memory_plan(get_preset("qwen2.5-1.5b"), 8, 128000)
+    assert small["moment_dtype"] == "fp32" and small["fits"] and small["blocks"]["keeping_attention_output"] == 28
+    assert not memory_plan(get_preset("llama-3.1-70b"), 1, 16000)["fits"]
+    moe = memory_plan(get_preset("mixtral-8x7b"), 8, 32000)
+    assert 46 < moe["model_parameters_billion"] < 47.5 and moe["fits"]
